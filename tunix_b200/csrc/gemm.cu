@@ -1,0 +1,455 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] = epilogue( A[M,K] * B[N,K]^T )            fp32 accumulation in TMEM
+//
+// * one CTA per SM, tile 128 x BN (BN = 256 or 128), K block 64 (one 128-byte swizzle row)
+// * warp 0      : TMA producer (cp.async.bulk.tensor, no multicast) into a 4/6-stage smem ring
+// * warp 1      : single-thread tcgen05.mma issue, accumulators double-buffered in TMEM
+// * warps 2..5  : epilogue, tcgen05.ld -> registers -> (bias / residual / accumulate) -> global
+// * A and B may each be "K-major" (contraction dimension contiguous) or "MN-major"
+//   (the M or N dimension contiguous), which covers forward, dgrad and wgrad of a
+//   linear layer without any transposed copy of activations or weights.
+// * every mbarrier wait is bounded (common.cuh); a timeout sets *status and unwinds.
+//
+// Role in the framework: replaces the XLA dot -> cuBLAS lowering of the reference's dense
+// projections and gated MLP (tunix/models/llama3/model.py:311-334, 489-496).
+#include "common.cuh"
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+#include <cstdio>
+
+using namespace tb;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GROUP_M = 16;  // rasterisation: 16 M-tiles share one sweep over N (L2 reuse)
+
+enum GemmFlags : int {
+  GF_A_MN = 1,         // A stored [K, M] (M contiguous)
+  GF_B_MN = 2,         // B stored [K, N] (N contiguous)
+  GF_OUT_F32 = 4,      // C is fp32 (else bf16)
+  GF_ACCUM = 8,        // C += result (reads C)
+  GF_BIAS = 16,        // + bias[N] (bf16)
+  GF_RESIDUAL = 32,    // + R[M,N] (bf16, row stride ldr)
+};
+
+struct GemmArgs {
+  int M, N, K;
+  int flags;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* resid;
+  long long ldr;
+  float alpha;
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulator stages
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs args) {
+  using C_ = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C_::STAGES * C_::STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2], then tmem ptr, abort
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C_::STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * C_::STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * C_::STAGES + 2 + s); };
+  volatile uint32_t* tmem_ptr_smem =
+      reinterpret_cast<volatile uint32_t*>(smem_al + C_::STAGES * C_::STAGE_BYTES + 8 * (2 * C_::STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int M = args.M, N = args.N, K = args.K;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_kb = (K + BK - 1) / BK;
+  const int num_tiles = num_m * num_n;
+  const bool a_mn = args.flags & GF_A_MN;
+  const bool b_mn = args.flags & GF_B_MN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C_::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 4);  // one arrive per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_ptr_smem), C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  auto tile_coords = [&](int t, int& mt, int& nt) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(GROUP_M, num_m - first_m);
+    const int r = t - g * per_group;
+    mt = first_m + (r % gsz);
+    nt = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mt, nt;
+        tile_coords(t, mt, nt);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, args.status,
+                                 ST_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * C_::STAGE_BYTES;
+          const uint32_t sb = sa + C_::A_BYTES;
+          mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!a_mn) {
+            tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &tmA, full_bar(stage), m0 + 64 * j, k0);
+          }
+          if (!b_mn) {
+            tma_load_2d(sb, &tmB, full_bar(stage), k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &tmB, full_bar(stage), n0 + 64 * j, k0);
+          }
+          if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
+      const uint32_t a_lbo = a_mn ? 8192u : 16u, b_lbo = b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = a_mn ? 2048u : 32u, b_kstep = b_mn ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag, args.status,
+                               ST_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * C_::STAGE_BYTES;
+          const uint32_t sb = sa + C_::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            umma_f16_ss(tmem_d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the smem slot when these MMAs retire
+          if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = args.flags & GF_OUT_F32;
+    const bool accum = args.flags & GF_ACCUM;
+    const bool has_bias = args.flags & GF_BIAS;
+    const bool has_res = args.flags & GF_RESIDUAL;
+    const float alpha = args.alpha;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, mt, nt);
+      const int row = mt * BM + q * 32 + lane;
+      const int n0 = nt * BN;
+      if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status,
+                             ST_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < M) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+          const bool full = (col0 + 32 <= N);
+          if (has_bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (full || col0 + i < N) v[i] += __bfloat162float(args.bias[col0 + i]);
+          }
+          if (has_res) {
+            const __nv_bfloat16* rp = args.resid + (long long)row * args.ldr + col0;
+            if (full && (args.ldr % 8 == 0)) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 u = reinterpret_cast<const uint4*>(rp)[g];
+                uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[g * 8 + 2 * j] += bf16_lo(w[j]);
+                  v[g * 8 + 2 * j + 1] += bf16_hi(w[j]);
+                }
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) v[i] += __bfloat162float(rp[i]);
+            }
+          }
+          if (out_f32) {
+            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col0;
+            if (full && (args.ldc % 4 == 0)) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                float4 o = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                if (accum) {
+                  float4 p = reinterpret_cast<float4*>(cp)[g];
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                reinterpret_cast<float4*>(cp)[g] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) cp[i] = accum ? cp[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* cp =
+                reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col0;
+            if (full && (args.ldc % 8 == 0)) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (accum) {
+                  uint4 u = reinterpret_cast<uint4*>(cp)[g];
+                  uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    v[g * 8 + 2 * j] += bf16_lo(w[j]);
+                    v[g * 8 + 2 * j + 1] += bf16_hi(w[j]);
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+                o.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+                o.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+                o.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+                reinterpret_cast<uint4*>(cp)[g] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) {
+                  float o = v[i] + (accum ? __bfloat162float(cp[i]) : 0.f);
+                  cp[i] = __float2bfloat16(o);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give TMA copies that may still be in flight time to land before smem is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C_::TMEM_COLS);
+  }
+}
+
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, box_cols;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && box_cols == o.box_cols;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1315423911u ^ k.rows;
+    h = h * 1315423911u ^ k.cols;
+    h = h * 1315423911u ^ k.ld;
+    h = h * 1315423911u ^ (((uint64_t)k.box_rows << 32) | k.box_cols);
+    return h;
+  }
+};
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+int g_sm_count = 0;
+
+}  // namespace
+
+tb_encode_tiled_fn tb_get_encode_tiled() {
+  static tb_encode_tiled_fn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<tb_encode_tiled_fn>(p);
+  });
+  return fn;
+}
+
+int tb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t ld, uint32_t box_rows, uint32_t box_cols, int swizzle128) {
+  tb_encode_tiled_fn enc = tb_get_encode_tiled();
+  if (!enc) return -1;
+  TmapKey key{base, rows, cols, ld, box_rows, box_cols | (swizzle128 ? 0x80000000u : 0)};
+  {
+    std::lock_guard<std::mutex> lk(g_tmap_mu);
+    auto it = g_tmap_cache.find(key);
+    if (it != g_tmap_cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return (int)r;
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
+  g_tmap_cache.emplace(key, *out);
+  return 0;
+}
+
+// Forget cached tensor maps (call when device memory is released back to the driver).
+TB_API void tb_tmap_cache_clear() {
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  g_tmap_cache.clear();
+}
+
+// C[M,N] = alpha * A*B^T (+bias)(+resid)(+C). Strides in elements.
+//   A: K-major -> [M,K] ld=lda ; MN-major (flags&1) -> [K,M] ld=lda
+//   B: K-major -> [N,K] ld=ldb ; MN-major (flags&2) -> [K,N] ld=ldb
+// Requirements: bf16 operands 16-byte aligned, lda/ldb multiples of 8, K > 0.
+// max_ctas <= 0 means one CTA per SM. Returns 0 or a negative error code.
+TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                        long long ldb, long long ldc, int flags, const void* bias,
+                        const void* resid, long long ldr, float alpha, int* status, int max_ctas,
+                        cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  // Narrow outputs use the 128-wide tile so more CTAs stream the weights.
+  const int num_m = (M + BM - 1) / BM;
+  const bool bn256 = (N >= 256) && ((long long)num_m * ((N + 255) / 256) >= g_sm_count / 2);
+  const int BN = bn256 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
+  if (r) return -3;
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
+  if (r) return -4;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K; args.flags = flags;
+  args.C = C; args.ldc = ldc;
+  args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  args.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  args.ldr = ldr; args.alpha = alpha; args.status = status;
+  const int tiles = num_m * ((N + BN - 1) / BN);
+  int ctas = g_sm_count;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<256>::SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<128>::SMEM_BYTES);
+    attr_set = true;
+  }
+  if (bn256)
+    gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  else
+    gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

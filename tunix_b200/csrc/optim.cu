@@ -1,0 +1,160 @@
+// Optimizer-side kernels over flat parameter buffers: global grad-norm, fused AdamW with
+// fp32 master weights (clip factor read from device memory, bf16 working copy written in the
+// same pass), and dtype casts / scaling for gradient buckets.
+//
+// Replaces the optax update + clip_by_global_norm chain of the reference trainer
+// (tunix/sft/peft_trainer.py:517-548, tunix/cli/config.py:286-378).
+#include "common.cuh"
+
+using namespace tb;
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// out[0] += sum(g^2)
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float red[33];
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = to_f<T>(g[i]);
+    acc += v * v;
+  }
+  acc = block_sum(acc, red);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;  // bc = 1 - beta^t
+  float grad_scale;     // multiplies every gradient (e.g. 1 / accumulated denominator)
+  float max_norm;       // <= 0 disables clipping
+  const float* sumsq;   // device scalar holding sum(g^2) of the *unscaled* grads (may be null)
+  const float* denom;   // device scalar; when non-null grads are divided by max(*denom, 1e-8)
+};
+
+// AdamW as optax.adamw: p -= lr * (m_hat / (sqrt(v_hat) + eps) + wd * p).
+// Clipping as optax.clip_by_global_norm: g *= max_norm / max(norm, max_norm).
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ g, __nv_bfloat16* __restrict__ p16, long long n,
+                             AdamArgs a) {
+  float scale = a.grad_scale;
+  if (a.denom) scale /= fmaxf(*a.denom, 1e-8f);
+  if (a.max_norm > 0.f && a.sumsq) {
+    const float norm = sqrtf(*a.sumsq) * fabsf(scale);
+    scale *= a.max_norm / fmaxf(norm, a.max_norm);
+  }
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float gi = to_f<G>(g[i]) * scale;
+    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gi;
+    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    float p = p32[i];
+    const float upd = (mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps) + a.weight_decay * p;
+    p -= a.lr * upd;
+    p32[i] = p;
+    if (p16) p16[i] = __float2bfloat16(p);
+  }
+}
+
+// SGD with optional momentum, same flat-buffer contract.
+template <typename G>
+__global__ void sgd_kernel(float* __restrict__ p32, float* __restrict__ mom,
+                           const G* __restrict__ g, __nv_bfloat16* __restrict__ p16, long long n,
+                           float lr, float momentum, float weight_decay, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float p = p32[i];
+    float gi = to_f<G>(g[i]) * scale + weight_decay * p;
+    if (mom) {
+      gi = momentum * mom[i] + gi;
+      mom[i] = gi;
+    }
+    p -= lr * gi;
+    p32[i] = p;
+    if (p16) p16[i] = __float2bfloat16(p);
+  }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                        long long n, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(in[i] * scale);
+}
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out,
+                                        long long n, float scale, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = __bfloat162float(in[i]) * scale;
+    out[i] = accumulate ? out[i] + v : v;
+  }
+}
+
+inline int grid_for(long long n, int block) {
+  long long g = (n + block - 1) / block;
+  const long long cap = 148LL * 8;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+TB_API int tb_sumsq(const void* g, long long n, int is_bf16, float* out, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (is_bf16)
+    sumsq_kernel<__nv_bfloat16><<<grid_for(n, 512), 512, 0, stream>>>((const __nv_bfloat16*)g, n, out);
+  else
+    sumsq_kernel<float><<<grid_for(n, 512), 512, 0, stream>>>((const float*)g, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16, void* p16,
+                    long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                    float bc1, float bc2, float grad_scale, float max_norm, const float* sumsq,
+                    const float* denom, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, max_norm, sumsq, denom};
+  if (g_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(
+        p32, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)p16, n, a);
+  else
+    adamw_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>(p32, m, v, (const float*)g,
+                                                              (__nv_bfloat16*)p16, n, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_sgd(float* p32, float* mom, const void* g, int g_is_bf16, void* p16, long long n,
+                  float lr, float momentum, float weight_decay, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (g_is_bf16)
+    sgd_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(
+        p32, mom, (const __nv_bfloat16*)g, (__nv_bfloat16*)p16, n, lr, momentum, weight_decay, scale);
+  else
+    sgd_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>(p32, mom, (const float*)g,
+                                                            (__nv_bfloat16*)p16, n, lr, momentum,
+                                                            weight_decay, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_cast_f32_bf16(const float* in, void* out, long long n, float scale,
+                            cudaStream_t stream) {
+  if (n <= 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, n, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+TB_API int tb_cast_bf16_f32(const void* in, float* out, long long n, float scale, int accumulate,
+                            cudaStream_t stream) {
+  if (n <= 0) return 0;
+  cast_bf16_to_f32_kernel<<<grid_for(n, 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out, n,
+                                                                scale, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -1,0 +1,235 @@
+"""Thin launchers for the sm_100a kernels (no autograd here; see `ops/functional.py`).
+
+Each function validates shapes/dtypes, picks strides and calls one `extern "C"`
+entry point on the current CUDA stream. Tensors are bf16 unless stated.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+
+GF_A_MN, GF_B_MN, GF_OUT_F32, GF_ACCUM, GF_BIAS, GF_RESIDUAL = 1, 2, 4, 8, 16, 32
+
+launch_count = 0  # number of native kernel launches issued through this module
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _is2d_rowmajor(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         accumulate: bool = False, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, alpha: float = 1.0,
+         max_ctas: int = 0) -> torch.Tensor:
+    """C = alpha * op(A) @ op(B)^T on the tcgen05 GEMM.
+
+    a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
+    Row-major 2-D views with unit inner stride; leading strides multiples of 8.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert _is2d_rowmajor(a) and _is2d_rowmajor(b), "operands must be 2-D with unit inner stride"
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        assert not accumulate
+    assert out.shape == (M, N) and out.stride(1) == 1
+    flags = (GF_A_MN if a_mn else 0) | (GF_B_MN if b_mn else 0)
+    if out.dtype == torch.float32:
+        flags |= GF_OUT_F32
+    else:
+        assert out.dtype == torch.bfloat16
+    if accumulate:
+        flags |= GF_ACCUM
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+        flags |= GF_BIAS
+    ldr = 0
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+        flags |= GF_RESIDUAL
+        ldr = residual.stride(0)
+    if M == 0 or N == 0:
+        return out
+    status = _lib.status_buffer(a.device)
+    rc = _lib.cuda().tb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        flags, _lib.ptr(bias), _lib.ptr(residual), ldr, float(alpha), status.data_ptr(), int(max_ctas),
+        _lib.stream_ptr())
+    _lib.check(rc, "tb_gemm_bf16")
+    _count()
+    return out
+
+
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, add_one: bool = False,
+                want_rstd: bool = True):
+    """x: [rows, D] (unit inner stride). Returns (y, rstd[rows] fp32 or None)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    rows, D = x.shape
+    y = torch.empty((rows, D), dtype=torch.bfloat16, device=x.device)
+    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device) if want_rstd else None
+    rc = _lib.cuda().tb_rmsnorm_fwd(x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), y.stride(0),
+                                    _lib.ptr(rstd), rows, D, float(eps), 1.0 if add_one else 0.0,
+                                    _lib.stream_ptr())
+    _lib.check(rc, "tb_rmsnorm_fwd")
+    _count()
+    return y, rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, add_one: bool = False, want_dw: bool = True,
+                dx_accumulate_into: torch.Tensor | None = None):
+    """Returns (dx bf16 [rows,D], dw fp32 [D] or None)."""
+    rows, D = x.shape
+    assert dy.stride(1) == 1 and x.stride(1) == 1
+    if dx_accumulate_into is not None:
+        dx = dx_accumulate_into
+        acc = 1
+    else:
+        dx = torch.empty((rows, D), dtype=torch.bfloat16, device=x.device)
+        acc = 0
+    dw = torch.zeros((D,), dtype=torch.float32, device=x.device) if want_dw else None
+    rc = _lib.cuda().tb_rmsnorm_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(),
+                                    rstd.data_ptr(), dx.data_ptr(), dx.stride(0), _lib.ptr(dw), rows, D,
+                                    1.0 if add_one else 0.0, acc, _lib.stream_ptr())
+    _lib.check(rc, "tb_rmsnorm_bwd")
+    _count(2 if want_dw else 1)
+    return dx, dw
+
+
+def rope_(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+          backward: bool = False) -> torch.Tensor:
+    """In-place half-split RoPE on x [tokens, heads, H] (heads*H contiguous per token).
+
+    positions: int32 [tokens]; cos/sin: fp32 [max_pos, H/2].
+    """
+    assert x.dtype == torch.bfloat16 and x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.shape[2]
+    tokens, heads, H = x.shape
+    assert positions.dtype == torch.int32 and positions.numel() == tokens and positions.is_contiguous()
+    assert cos.dtype == torch.float32 and cos.shape[1] == H // 2 and cos.is_contiguous() and sin.is_contiguous()
+    rc = _lib.cuda().tb_rope(x.data_ptr(), x.stride(0), positions.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                             tokens, heads, H, 1 if backward else 0, _lib.stream_ptr())
+    _lib.check(rc, "tb_rope")
+    _count()
+    return x
+
+
+GLU_SILU, GLU_GELU = 0, 1
+
+
+def glu_fwd(g: torch.Tensor, u: torch.Tensor, kind: int) -> torch.Tensor:
+    rows, Fdim = g.shape
+    h = torch.empty((rows, Fdim), dtype=torch.bfloat16, device=g.device)
+    rc = _lib.cuda().tb_glu_fwd(g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), h.data_ptr(), h.stride(0),
+                                rows, Fdim, kind, _lib.stream_ptr())
+    _lib.check(rc, "tb_glu_fwd")
+    _count()
+    return h
+
+
+def glu_bwd(dh, g, u, kind: int, inplace: bool = False):
+    rows, Fdim = g.shape
+    dg = g if inplace else torch.empty_like(g)
+    du = u if inplace else torch.empty_like(u)
+    rc = _lib.cuda().tb_glu_bwd(dh.data_ptr(), dh.stride(0), g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0),
+                                dg.data_ptr(), dg.stride(0), du.data_ptr(), du.stride(0), rows, Fdim, kind,
+                                _lib.stream_ptr())
+    _lib.check(rc, "tb_glu_bwd")
+    _count()
+    return dg, du
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and table.dtype == torch.bfloat16
+    tokens = ids.numel()
+    V, D = table.shape
+    out = torch.empty((tokens, D), dtype=torch.bfloat16, device=table.device)
+    rc = _lib.cuda().tb_embedding_fwd(ids.data_ptr(), table.data_ptr(), table.stride(0), out.data_ptr(), D,
+                                      tokens, D, V, float(scale), _lib.stream_ptr())
+    _lib.check(rc, "tb_embedding_fwd")
+    _count()
+    return out
+
+
+def embedding_bwd(ids: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor, scale: float = 1.0) -> None:
+    """dtable[ids] += dout * scale (dtable bf16, accumulated in place)."""
+    tokens = ids.numel()
+    V, D = dtable.shape
+    rc = _lib.cuda().tb_embedding_bwd(ids.data_ptr(), dout.data_ptr(), dout.stride(0), dtable.data_ptr(),
+                                      dtable.stride(0), tokens, D, V, float(scale), _lib.stream_ptr())
+    _lib.check(rc, "tb_embedding_bwd")
+    _count()
+
+
+def logsoftmax_gather(logits: torch.Tensor, targets: torch.Tensor, *, softcap: float = 0.0,
+                      temperature: float = 1.0, want_entropy: bool = False):
+    """logits fp32 [rows, V]; targets int32 [rows]. Returns (logp, lse, entropy|None), all fp32 [rows]."""
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    rows, V = logits.shape
+    logp = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    lse = torch.empty_like(logp)
+    ent = torch.empty_like(logp) if want_entropy else None
+    rc = _lib.cuda().tb_logsoftmax_gather(logits.data_ptr(), logits.stride(0), targets.data_ptr(), logp.data_ptr(),
+                                          lse.data_ptr(), _lib.ptr(ent), rows, V, float(softcap), float(temperature),
+                                          _lib.stream_ptr())
+    _lib.check(rc, "tb_logsoftmax_gather")
+    _count()
+    return logp, lse, ent
+
+
+def dlogits(logits, targets, lse, entropy, dlogp, dent, *, softcap: float = 0.0, temperature: float = 1.0,
+            out: torch.Tensor | None = None):
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows, V), dtype=torch.bfloat16, device=logits.device)
+    rc = _lib.cuda().tb_dlogits(logits.data_ptr(), logits.stride(0), _lib.ptr(targets), lse.data_ptr(),
+                                _lib.ptr(entropy), _lib.ptr(dlogp), _lib.ptr(dent), out.data_ptr(), out.stride(0),
+                                rows, V, float(softcap), float(temperature), _lib.stream_ptr())
+    _lib.check(rc, "tb_dlogits")
+    _count()
+    return out
+
+
+def sumsq(g: torch.Tensor, out: torch.Tensor) -> None:
+    """out[0] += sum(g^2); g flat bf16 or fp32, out fp32 scalar tensor on device."""
+    assert g.is_contiguous() and out.dtype == torch.float32
+    rc = _lib.cuda().tb_sumsq(g.data_ptr(), g.numel(), 1 if g.dtype == torch.bfloat16 else 0, out.data_ptr(),
+                              _lib.stream_ptr())
+    _lib.check(rc, "tb_sumsq")
+    _count()
+
+
+def adamw(p32, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, max_norm=0.0,
+          sumsq_buf=None, denom_buf=None) -> None:
+    assert p32.dtype == torch.float32 and p32.is_contiguous() and g.is_contiguous()
+    n = p32.numel()
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    rc = _lib.cuda().tb_adamw(p32.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(),
+                              1 if g.dtype == torch.bfloat16 else 0, _lib.ptr(p16), n, float(lr), float(beta1),
+                              float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
+                              float(grad_scale), float(max_norm), _lib.ptr(sumsq_buf), _lib.ptr(denom_buf),
+                              _lib.stream_ptr())
+    _lib.check(rc, "tb_adamw")
+    _count()
+
+
+def sgd(p32, mom, g, p16, *, lr, momentum=0.0, weight_decay=0.0, scale=1.0) -> None:
+    rc = _lib.cuda().tb_sgd(p32.data_ptr(), _lib.ptr(mom), g.data_ptr(), 1 if g.dtype == torch.bfloat16 else 0,
+                            _lib.ptr(p16), p32.numel(), float(lr), float(momentum), float(weight_decay), float(scale),
+                            _lib.stream_ptr())
+    _lib.check(rc, "tb_sgd")
+    _count()
