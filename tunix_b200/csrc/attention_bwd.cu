@@ -1,0 +1,487 @@
+// Flash-attention backward for sm_100a on tcgen05 tensor cores.
+//
+// One CTA owns 128 keys of one kv head and walks over every (query head of the group,
+// 64-row query tile) that can see them. All five GEMMs of the backward run on tcgen05 with
+// the accumulators in TMEM; the transposed orientation (keys on TMEM lanes) makes every
+// element-wise step thread-local (one thread per key row):
+//
+//   St  = K  Q^T          [128 keys x 64 queries]     P  = exp(z - lse)
+//   dPt = V  dO^T         [128 x 64]                  dS = P * (dP - delta) * scale
+//   dV += Pt  dO          [128 x HO]   (accumulates in TMEM over all query tiles / heads)
+//   dK += dSt Q           [128 x HO]
+//   dQt = K^T dS^T        [HO  x 64]   -> fp32 atomics into dQ (coalesced along the head dim)
+//
+// HO = min(H, 128): for head_dim 256 two CTAs share the keys, each producing one 128-column
+// half of dK / dV / dQ (S and dP need the full contraction and are computed by both).
+// Masks and soft-cap as in the forward kernel. Waits are bounded (common.cuh).
+//
+// Counterpart in the reference: autodiff of the attention in tunix/models/*/model.py
+// (e.g. tunix/models/llama3/model.py:379-396); no hand-written backward exists there.
+#include "common.cuh"
+
+using namespace tb;
+
+namespace {
+
+constexpr int BK_ = 128;  // keys per CTA
+constexpr int BQ_ = 64;   // queries per iteration
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct BwdArgs {
+  int B, Tq, Tk, N, KH;
+  float scale, softcap;
+  int causal, window, q_off;
+  const int* seg_q;
+  const int* seg_k;
+  const float* lse;     // [B, N, Tq]
+  const float* delta;   // [B, N, Tq]
+  float* dQ;            // fp32 [B*Tq, N*H], zero-initialised by the caller
+  __nv_bfloat16* dK;    // [B*Tk, KH*H]
+  __nv_bfloat16* dV;
+  long long lddk, lddv;
+  int* status;
+};
+
+template <int H>
+struct BwdCfg {
+  static constexpr int HS = H / 64;
+  static constexpr int HO = H < 128 ? H : 128;
+  static constexpr int NHALF = H / HO;
+  static constexpr int NST = (H <= 128) ? 2 : 1;
+  static constexpr int KV_BYTES = HS * BK_ * 128;
+  static constexpr int Q_BYTES = HS * BQ_ * 128;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = OFF_K + KV_BYTES;
+  static constexpr int OFF_Q = OFF_V + KV_BYTES;
+  static constexpr int OFF_DO = OFF_Q + NST * Q_BYTES;
+  static constexpr int OFF_PT = OFF_DO + NST * Q_BYTES;
+  static constexpr int OFF_DST = OFF_PT + BK_ * 128;
+  static constexpr int OFF_STAT = OFF_DST + BK_ * 128;      // [2][3][64] 4-byte values
+  static constexpr int OFF_BAR = OFF_STAT + 2 * 3 * 64 * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;
+  static constexpr int TM_ST = 0, TM_DPT = 64, TM_DQT = 128, TM_DV = 192, TM_DK = 192 + HO;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <int H>
+__global__ void __launch_bounds__(160, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const BwdArgs a) {
+  using C_ = BwdCfg<H>;
+  constexpr int HO = C_::HO;
+  constexpr int NST = C_::NST;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t sK = sbase + C_::OFF_K, sV = sbase + C_::OFF_V, sQ = sbase + C_::OFF_Q,
+                 sdO = sbase + C_::OFF_DO, sPt = sbase + C_::OFF_PT, sdSt = sbase + C_::OFF_DST,
+                 bars = sbase + C_::OFF_BAR;
+  // barriers: 0 KV, 1-2 Q[2], 3-4 Qfree[2], 5 St, 6 dPt, 7 Pt, 8 dSt, 9 dQ, (10: tmem slot + abort), 11 row-thread sync
+  const uint32_t barKV = bars, barQ0 = bars + 8, barQF0 = bars + 24, barSt = bars + 40,
+                 bardPt = bars + 48, barPt = bars + 56, bardSt = bars + 64, bardQ = bars + 72, barSync = bars + 88;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sptr + C_::OFF_BAR + 80);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sptr + C_::OFF_BAR + 84);
+  float* s_stat = reinterpret_cast<float*>(sptr + C_::OFF_STAT);
+
+  const int warp = threadIdx.x >> 5;
+  const int kt = blockIdx.x;
+  const int half = (C_::NHALF > 1) ? (blockIdx.y % C_::NHALF) : 0;
+  const int kvh = blockIdx.y / C_::NHALF;
+  const int b = blockIdx.z;
+  const int G = a.N / a.KH;
+  const int k0 = kt * BK_;
+
+  // query tiles that can see keys [k0, k0+128)
+  int q_lo = 0, q_hi = a.Tq;
+  if (a.causal) q_lo = max(0, k0 - a.q_off);
+  if (a.window > 0) q_hi = min(a.Tq, k0 + BK_ + a.window - 1 - a.q_off);
+  const int qt0 = q_lo / BQ_;
+  const int nq = q_hi > qt0 * BQ_ ? (q_hi - qt0 * BQ_ + BQ_ - 1) / BQ_ : 0;
+  const int nit = nq * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(barKV, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(barQ0 + 8 * s, 1);
+      mbar_init(barQF0 + 8 * s, 1);
+    }
+    mbar_init(barSt, 1);
+    mbar_init(bardPt, 1);
+    mbar_init(barPt, 128);
+    mbar_init(bardSt, 128);
+    mbar_init(bardQ, 1);
+    mbar_init(barSync, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32((const void*)tmem_slot), C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ issuer warp
+    if (nit > 0 && elect_one()) {
+      const uint32_t idesc_s = make_idesc_bf16(128, BQ_, 0, 0);     // K-major x K-major, N = 64
+      const uint32_t idesc_dv = make_idesc_bf16(128, HO, 0, 1);     // A K-major, B MN-major, N = HO
+      const uint32_t idesc_dq = make_idesc_bf16(128, BQ_, 1, 1);    // both MN-major, N = 64
+      auto load_q = [&](int it, int st) {
+        const int g = it / nq, qt = qt0 + it % nq;
+        const int n = kvh * G + g;
+        const uint32_t bar = barQ0 + 8 * st;
+        mbar_expect_tx(bar, 2 * C_::Q_BYTES);
+#pragma unroll
+        for (int c = 0; c < C_::HS; ++c) {
+          tma_load_2d(sQ + st * C_::Q_BYTES + c * (BQ_ * 128), &tmQ, bar, n * H + 64 * c, b * a.Tq + qt * BQ_);
+          tma_load_2d(sdO + st * C_::Q_BYTES + c * (BQ_ * 128), &tmdO, bar, n * H + 64 * c, b * a.Tq + qt * BQ_);
+        }
+      };
+      bool ok = true;
+      mbar_expect_tx(barKV, 2 * C_::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < C_::HS; ++c) {
+        tma_load_2d(sK + c * (BK_ * 128), &tmK, barKV, kvh * H + 64 * c, b * a.Tk + k0);
+        tma_load_2d(sV + c * (BK_ * 128), &tmV, barKV, kvh * H + 64 * c, b * a.Tk + k0);
+      }
+      load_q(0, 0);
+      if (NST == 2 && nit > 1) load_q(1, 1);
+      ok = mbar_wait_bounded(barKV, 0, abort_flag, a.status, ST_TIMEOUT_PRODUCER);
+      for (int it = 0; it < nit && ok; ++it) {
+        const int st = it % NST;
+        if (NST == 1 && it >= 1) {
+          if (!mbar_wait_bounded(barQF0, (it - 1) & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          load_q(it, 0);
+        }
+        if (!mbar_wait_bounded(barQ0 + 8 * st, (it / NST) & 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t q_s = sQ + st * C_::Q_BYTES, do_s = sdO + st * C_::Q_BYTES;
+        // St = K Q^T ; dPt = V dO^T  (contraction over the full head dim)
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sK + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(q_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16_ss(tmem + C_::TM_ST, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(barSt);
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sV + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(do_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16_ss(tmem + C_::TM_DPT, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(bardPt);
+        if (NST == 2 && it >= 1 && it + 1 < nit) {
+          // stage (it+1)&1 was used by tile it-1, whose MMAs precede the ones just issued
+          if (!mbar_wait_bounded(barQF0 + 8 * ((it + 1) & 1), ((it - 1) >> 1) & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          load_q(it + 1, (it + 1) & 1);
+        }
+        // dV += Pt dO   (A = Pt K-major over 64 queries, B = dO MN-major, this CTA's column half)
+        if (!mbar_wait_bounded(barPt, it & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t col_off = half * (HO / 64) * (BQ_ * 128);  // slab offset of this half in Q/dO tiles
+#pragma unroll
+        for (int kk = 0; kk < BQ_ / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sPt + kk * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(do_s + col_off + kk * 2048, BQ_ * 128, 1024);
+          umma_f16_ss(tmem + C_::TM_DV, ad, bd, idesc_dv, (it | kk) != 0);
+        }
+        // dK += dSt Q ; dQt = K^T dS^T
+        if (!mbar_wait_bounded(bardSt, it & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BQ_ / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sdSt + kk * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(q_s + col_off + kk * 2048, BQ_ * 128, 1024);
+          umma_f16_ss(tmem + C_::TM_DK, ad, bd, idesc_dv, (it | kk) != 0);
+        }
+        const uint32_t k_half = sK + half * (HO / 64) * (BK_ * 128);
+#pragma unroll
+        for (int kk = 0; kk < BK_ / 16; ++kk) {
+          // A = K^T: M (head dim) contiguous, 64-wide M chunks BK_*128 bytes apart; 16 keys per step
+          const uint64_t ad = make_smem_desc(k_half + kk * 2048, BK_ * 128, 1024);
+          const uint64_t bd = make_smem_desc(sdSt + kk * 2048, BK_ * 128, 1024);
+          umma_f16_ss(tmem + C_::TM_DQT, ad, bd, idesc_dq, kk != 0);
+        }
+        umma_commit(barQF0 + 8 * st);
+        umma_commit(bardQ);
+      }
+    }
+  } else {
+    // ------------------------------------------------------- per-key-row math
+    const int r = threadIdx.x;  // key row in tile == TMEM lane
+    const int kp = k0 + r;
+    const bool key_valid = kp < a.Tk;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int my_seg = (a.seg_k && key_valid) ? a.seg_k[(long long)b * a.Tk + kp] : 0;
+    bool ok = true;
+    // stats of the first tile
+    auto stat_ptr = [&](int buf, int which) { return s_stat + (buf * 3 + which) * 64; };
+    auto fetch_stats = [&](int it, float& v_lse, float& v_delta, int& v_seg) {
+      const int g = it / nq, qt = qt0 + it % nq;
+      const int n = kvh * G + g;
+      const int qi = qt * BQ_ + r;
+      if (r < 64 && qi < a.Tq) {
+        const long long o = ((long long)b * a.N + n) * a.Tq + qi;
+        v_lse = a.lse[o] * LOG2E;
+        v_delta = a.delta[o];
+        v_seg = a.seg_q ? a.seg_q[(long long)b * a.Tq + qi] : 0;
+      } else {
+        v_lse = INFINITY;
+        v_delta = 0.f;
+        v_seg = -1;
+      }
+    };
+    if (nit > 0) {
+      float f0, f1;
+      int i2;
+      fetch_stats(0, f0, f1, i2);
+      if (r < 64) {
+        stat_ptr(0, 0)[r] = f0;
+        stat_ptr(0, 1)[r] = f1;
+        reinterpret_cast<int*>(stat_ptr(0, 2))[r] = i2;
+      }
+    }
+    for (int it = 0; it < nit && ok; ++it) {
+      // stats of tile `it` visible to every row thread; previous tile fully consumed
+      mbar_arrive(barSync);
+      if (!mbar_wait_bounded(barSync, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      float nx_lse = INFINITY, nx_delta = 0.f;
+      int nx_seg = -1;
+      if (it + 1 < nit) fetch_stats(it + 1, nx_lse, nx_delta, nx_seg);
+      const int g = it / nq, qt = qt0 + it % nq;
+      const int n = kvh * G + g;
+      const int qbase = qt * BQ_;
+      const float* st_lse = stat_ptr(it & 1, 0);
+      const float* st_delta = stat_ptr(it & 1, 1);
+      const int* st_seg = reinterpret_cast<const int*>(stat_ptr(it & 1, 2));
+
+      if (!mbar_wait_bounded(barSt, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      float p[64];
+      {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_ST, t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_ST + 32, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float s = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
+          const int qpos = qbase + i + a.q_off;
+          float z;
+          if (a.softcap > 0.f) z = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
+          else z = s * a.scale * LOG2E;
+          bool keep = key_valid && (qbase + i < a.Tq);
+          if (a.causal) keep = keep && (kp <= qpos);
+          if (a.window > 0) keep = keep && (kp > qpos - a.window);
+          if (a.seg_k) keep = keep && (st_seg[i] == my_seg);
+          p[i] = keep ? exp2f(z - st_lse[i]) : 0.f;
+        }
+      }
+      {
+        uint8_t* prow = sptr + C_::OFF_PT + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 v;
+          v.x = pack_bf16(p[8 * c + 0], p[8 * c + 1]);
+          v.y = pack_bf16(p[8 * c + 2], p[8 * c + 3]);
+          v.z = pack_bf16(p[8 * c + 4], p[8 * c + 5]);
+          v.w = pack_bf16(p[8 * c + 6], p[8 * c + 7]);
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(barPt);
+      }
+      if (!mbar_wait_bounded(bardPt, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_DPT, t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_DPT + 32, t1);
+        tmem_ld_wait();
+        if (a.softcap > 0.f) {
+          uint32_t s0[32], s1[32];
+          tmem_ld_32x32(tmem + lane_addr + C_::TM_ST, s0);
+          tmem_ld_32x32(tmem + lane_addr + C_::TM_ST + 32, s1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float s = __uint_as_float(i < 32 ? s0[i & 31] : s1[i & 31]);
+            const float t = tanhf(s * a.scale / a.softcap);
+            p[i] *= (1.f - t * t);
+          }
+        }
+        uint8_t* drow = sptr + C_::OFF_DST + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float d[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int i = 8 * c + e;
+            const float dp = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
+            d[e] = p[i] * (dp - st_delta[i]) * a.scale;
+          }
+          uint4 v;
+          v.x = pack_bf16(d[0], d[1]);
+          v.y = pack_bf16(d[2], d[3]);
+          v.z = pack_bf16(d[4], d[5]);
+          v.w = pack_bf16(d[6], d[7]);
+          *reinterpret_cast<uint4*>(drow + ((c ^ (r & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bardSt);
+      }
+      // dQt tile: lane = head-dim index (within this CTA's half), column = query
+      if (!mbar_wait_bounded(bardQ, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_DQT, t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::TM_DQT + 32, t1);
+        tmem_ld_wait();
+        if (r < HO) {
+          float* dq = a.dQ + ((long long)b * a.Tq + qbase) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if (qbase + i < a.Tq) {
+              const float v = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
+              atomicAdd(dq + (long long)i * a.N * H, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      if (it + 1 < nit && r < 64) {
+        stat_ptr((it + 1) & 1, 0)[r] = nx_lse;
+        stat_ptr((it + 1) & 1, 1)[r] = nx_delta;
+        reinterpret_cast<int*>(stat_ptr((it + 1) & 1, 2))[r] = nx_seg;
+      }
+    }
+    // ------------------------------------------------------------- dK / dV
+    // All MMAs retired when the last bardQ phase completed (waited above).
+    tc_fence_after();
+    __nv_bfloat16* dkrow = a.dK + ((long long)b * a.Tk + kp) * a.lddk + (long long)kvh * H + half * HO;
+    __nv_bfloat16* dvrow = a.dV + ((long long)b * a.Tk + kp) * a.lddv + (long long)kvh * H + half * HO;
+#pragma unroll 1
+    for (int c = 0; c < HO / 32; ++c) {
+      uint32_t o[32];
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        if (nit > 0 && ok) {
+          tmem_ld_32x32(tmem + lane_addr + (which ? C_::TM_DK : C_::TM_DV) + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+        if (key_valid) {
+          __nv_bfloat16* dst = (which ? dkrow : dvrow) + c * 32;
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[8 * g4 + 0]), __uint_as_float(o[8 * g4 + 1]));
+            v.y = pack_bf16(__uint_as_float(o[8 * g4 + 2]), __uint_as_float(o[8 * g4 + 3]));
+            v.z = pack_bf16(__uint_as_float(o[8 * g4 + 4]), __uint_as_float(o[8 * g4 + 5]));
+            v.w = pack_bf16(__uint_as_float(o[8 * g4 + 6]), __uint_as_float(o[8 * g4 + 7]));
+            *reinterpret_cast<uint4*>(dst + g4 * 8) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C_::TMEM_COLS);
+  }
+}
+
+// delta[b, n, t] = sum_h dO * O
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
+                                  const __nv_bfloat16* __restrict__ dout, long long lddo,
+                                  float* __restrict__ delta, int B, int T, int N, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * T * N;
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
+       w += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const int n = (int)(w % N);
+    const long long bt = w / N;
+    const int t = (int)(bt % T);
+    const int b = (int)(bt / T);
+    const __nv_bfloat16* po = o + bt * ldo + (long long)n * H;
+    const __nv_bfloat16* pd = dout + bt * lddo + (long long)n * H;
+    float acc = 0.f;
+    for (int c = lane * 2; c < H; c += 64) {
+      const uint32_t x = *reinterpret_cast<const uint32_t*>(po + c);
+      const uint32_t y = *reinterpret_cast<const uint32_t*>(pd + c);
+      acc += bf16_lo(x) * bf16_lo(y) + bf16_hi(x) * bf16_hi(y);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) delta[((long long)b * N + n) * T + t] = acc;
+  }
+}
+
+template <int H>
+int launch_bwd(const void* q, const void* k, const void* v, const void* dout, const BwdArgs& a,
+               long long ldq, long long ldk, long long ldv, long long lddo, cudaStream_t stream) {
+  using C_ = BwdCfg<H>;
+  CUtensorMap tq, tk, tv, tdo;
+  if (tb_make_tmap_2d_bf16(&tq, q, (uint64_t)a.B * a.Tq, (uint64_t)a.N * H, ldq, BQ_, 64, 1)) return -3;
+  if (tb_make_tmap_2d_bf16(&tdo, dout, (uint64_t)a.B * a.Tq, (uint64_t)a.N * H, lddo, BQ_, 64, 1)) return -3;
+  if (tb_make_tmap_2d_bf16(&tk, k, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldk, BK_, 64, 1)) return -3;
+  if (tb_make_tmap_2d_bf16(&tv, v, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldv, BK_, 64, 1)) return -3;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(attn_bwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
+    attr = true;
+  }
+  dim3 grid((a.Tk + BK_ - 1) / BK_, a.KH * C_::NHALF, a.B);
+  attn_bwd_kernel<H><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+TB_API int tb_attn_delta(const void* o, long long ldo, const void* dout, long long lddo, float* delta,
+                         int B, int T, int N, int H, cudaStream_t stream) {
+  const long long total = (long long)B * T * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  attn_delta_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, ldo, (const __nv_bfloat16*)dout,
+                                                     lddo, delta, B, T, N, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// dq_accum: fp32 [B*Tq, N*H] zero-initialised; dk, dv: bf16 [B*Tk, KH*H] (fully written).
+TB_API int tb_attn_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                       const float* delta, float* dq_accum, void* dk, void* dv, int B, int Tq, int Tk,
+                       int N, int KH, int H, long long ldq, long long ldk, long long ldv, long long lddo,
+                       long long lddk, long long lddv, float scale, float softcap, int causal, int window,
+                       int q_off, const int* seg_q, const int* seg_k, int* status, cudaStream_t stream) {
+  if (B <= 0 || Tk <= 0 || KH <= 0) return 0;
+  if (N % KH || (ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (lddk % 8) || (lddv % 8)) return -2;
+  BwdArgs a;
+  a.B = B; a.Tq = Tq; a.Tk = Tk; a.N = N; a.KH = KH;
+  a.scale = scale; a.softcap = softcap; a.causal = causal; a.window = window; a.q_off = q_off;
+  a.seg_q = seg_q; a.seg_k = seg_k; a.lse = lse; a.delta = delta; a.dQ = dq_accum;
+  a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.lddk = lddk; a.lddv = lddv; a.status = status;
+  switch (H) {
+    case 64: return launch_bwd<64>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
+    case 128: return launch_bwd<128>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
+    case 256: return launch_bwd<256>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
+    default: return -2;
+  }
+}

@@ -233,3 +233,71 @@ def sgd(p32, mom, g, p16, *, lr, momentum=0.0, weight_decay=0.0, scale=1.0) -> N
                             _lib.stream_ptr())
     _lib.check(rc, "tb_sgd")
     _count()
+
+
+_lib.register_cuda_sigs({
+    "tb_attn_fwd": [_lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.I,
+                    _lib.LL, _lib.LL, _lib.LL, _lib.LL, _lib.F, _lib.F, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P,
+                    _lib.P, _lib.P],
+    "tb_attn_delta": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P],
+    "tb_attn_bwd": [_lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I,
+                    _lib.I, _lib.I, _lib.I, _lib.I, _lib.LL, _lib.LL, _lib.LL, _lib.LL, _lib.LL, _lib.LL,
+                    _lib.F, _lib.F, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.P],
+})
+
+
+def _attn_views(q, k, v):
+    """q [B,Tq,N,H], k/v [B,Tk,KH,H] with heads*H contiguous per token and tokens evenly strided."""
+    B, Tq, N, H = q.shape
+    _, Tk, KH, _ = k.shape
+    for t in (q, k, v):
+        assert t.dtype == torch.bfloat16 and t.stride(3) == 1 and t.stride(2) == H
+        assert t.stride(0) == t.shape[1] * t.stride(1), "batch and time must flatten to one row index"
+    return B, Tq, Tk, N, KH, H
+
+
+def attn_fwd(q, k, v, *, scale: float, causal: bool = True, window: int = 0, softcap: float = 0.0,
+             q_off: int | None = None, seg_q=None, seg_k=None, want_lse: bool = True):
+    """Flash attention forward. Returns (o [B,Tq,N,H] bf16, lse [B,N,Tq] fp32 | None)."""
+    B, Tq, Tk, N, KH, H = _attn_views(q, k, v)
+    if q_off is None:
+        q_off = Tk - Tq
+    o = torch.empty((B, Tq, N, H), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, N, Tq), dtype=torch.float32, device=q.device) if want_lse else None
+    status = _lib.status_buffer(q.device)
+    rc = _lib.cuda().tb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), _lib.ptr(lse), B, Tq, Tk,
+                                 N, KH, H, q.stride(1), k.stride(1), v.stride(1), o.stride(1), float(scale),
+                                 float(softcap), 1 if causal else 0, int(window), int(q_off), _lib.ptr(seg_q),
+                                 _lib.ptr(seg_k), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_attn_fwd")
+    _count()
+    return o, lse
+
+
+def attn_bwd(dout, q, k, v, o, lse, *, scale: float, causal: bool = True, window: int = 0, softcap: float = 0.0,
+             q_off: int | None = None, seg_q=None, seg_k=None):
+    """Flash attention backward. Returns (dq, dk, dv) in bf16 with the shapes of q, k, v."""
+    B, Tq, Tk, N, KH, H = _attn_views(q, k, v)
+    if q_off is None:
+        q_off = Tk - Tq
+    assert dout.stride(3) == 1 and dout.stride(2) == H and dout.stride(0) == Tq * dout.stride(1)
+    delta = torch.empty((B, N, Tq), dtype=torch.float32, device=q.device)
+    lib = _lib.cuda()
+    rc = lib.tb_attn_delta(o.data_ptr(), o.stride(1), dout.data_ptr(), dout.stride(1), delta.data_ptr(), B, Tq, N, H,
+                           _lib.stream_ptr())
+    _lib.check(rc, "tb_attn_delta")
+    dq32 = torch.zeros((B, Tq, N, H), dtype=torch.float32, device=q.device)
+    dk = torch.empty((B, Tk, KH, H), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty((B, Tk, KH, H), dtype=torch.bfloat16, device=q.device)
+    status = _lib.status_buffer(q.device)
+    rc = lib.tb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                         dq32.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Tq, Tk, N, KH, H, q.stride(1), k.stride(1),
+                         v.stride(1), dout.stride(1), dk.stride(1), dv.stride(1), float(scale), float(softcap),
+                         1 if causal else 0, int(window), int(q_off), _lib.ptr(seg_q), _lib.ptr(seg_k),
+                         status.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_attn_bwd")
+    dq = torch.empty((B, Tq, N, H), dtype=torch.bfloat16, device=q.device)
+    rc = lib.tb_cast_f32_bf16(dq32.data_ptr(), dq.data_ptr(), dq32.numel(), 1.0, _lib.stream_ptr())
+    _lib.check(rc, "tb_cast_f32_bf16")
+    _count(4)
+    return dq, dk, dv
