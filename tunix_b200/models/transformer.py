@@ -1,0 +1,329 @@
+"""Generic pre-norm decoder covering Llama 3.x, Qwen2.5, Qwen3 (dense + MoE), Gemma 1/2/3 (text).
+
+Model contract (the one every trainer / sampler in this package relies on; it mirrors
+tunix/models/qwen3/model.py:1359-1463):
+
+    logits_or_hidden, cache = model(input_tokens, positions=None, cache=None, attention_mask=None,
+                                    segment_ids=None, skip_lm_head=False, output_hidden_states=False)
+    model.compute_final_logits(hidden)            # fp32 logits, final soft-cap applied
+    model.token_logprobs(hidden, targets, ...)    # fused lm_head -> log-softmax -> gather
+    model.init_cache(batch, cache_size, dtype)    # dense KV cache for the vanilla sampler
+    model.get_model_input()                       # dummy inputs (LoRA tracing helper in the reference)
+
+Weights keep the HF `[out, in]` layout, so safetensors import/export is a rename.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint as _torch_checkpoint
+
+from ..ops import functional as F
+from ..ops import reference as R
+from .config import ModelConfig, RematConfig
+
+
+class Linear(nn.Module):
+    """Linear layer with optional bias, LoRA adapters and NF4-quantised frozen base (QLoRA)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=torch.float32, device=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        self.lora_a: Optional[nn.Parameter] = None
+        self.lora_b: Optional[nn.Parameter] = None
+        self.lora_scale = 0.0
+        self.lora_enabled = True
+        self.quant = None  # set by lora.quantize_base_nf4
+
+    def base_weight(self) -> torch.Tensor:
+        if self.quant is not None:
+            return self.quant.dequantize()
+        return self.weight
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w = self.base_weight()
+        if self.lora_a is not None and self.lora_enabled:
+            y = F.linear(x, w, self.bias)
+            y = F.lora_delta(x, self.lora_a, self.lora_b, y, self.lora_scale)
+            return y if residual is None else y + residual
+        return F.linear(x, w, self.bias, residual)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, add_one: bool, dtype=torch.float32, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.zeros(dim, dtype=dtype, device=device) if add_one
+                                   else torch.ones(dim, dtype=dtype, device=device))
+        self.eps, self.add_one = eps, add_one
+
+    def forward(self, x):
+        return F.rmsnorm(x, self.weight, self.eps, self.add_one)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device=None):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        D, N, K, H = cfg.embed_dim, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        dt = cfg.dtype
+        self.q_proj = Linear(D, N * H, cfg.qkv_bias, dt, device)
+        self.k_proj = Linear(D, K * H, cfg.qkv_bias, dt, device)
+        self.v_proj = Linear(D, K * H, cfg.qkv_bias, dt, device)
+        self.o_proj = Linear(N * H, D, False, dt, device)
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(H, cfg.norm_eps, cfg.norm_add_one, dt, device)
+            self.k_norm = RMSNorm(H, cfg.norm_eps, cfg.norm_add_one, dt, device)
+        self.is_local = cfg.layer_type(layer_idx) == "local"
+        self.window = cfg.sliding_window if self.is_local else 0
+        qpas = cfg.query_pre_attn_scalar if cfg.query_pre_attn_scalar else float(H)
+        self.scale = 1.0 / math.sqrt(qpas)
+
+    def forward(self, x, positions, rope, cache=None, segment_ids=None, attention_mask=None, residual=None):
+        cfg = self.cfg
+        B, T, _ = x.shape
+        N, K, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        q = self.q_proj(x).view(B, T, N, H)
+        k = self.k_proj(x).view(B, T, K, H)
+        v = self.v_proj(x).view(B, T, K, H)
+        if cfg.qk_norm:
+            q = self.q_norm(q)
+            k = self.k_norm(k)
+        cos, sin = rope
+        q = F.rope(q, positions, cos, sin)
+        k = F.rope(k, positions, cos, sin)
+        seg_q = seg_k = segment_ids
+        q_off = None
+        new_cache = None
+        if cache is not None:
+            # dense cache [B,S,K,H]; this call writes positions [end, end+T)
+            ck, cv, cseg, end = cache["k"], cache["v"], cache["seg"], cache["end"]
+            ck[:, end:end + T] = k.detach()
+            cv[:, end:end + T] = v.detach()
+            if segment_ids is not None:
+                cseg[:, end:end + T] = segment_ids.to(cseg.dtype)
+            else:
+                cseg[:, end:end + T] = 1
+            new_end = end + T
+            k, v = ck[:, :new_end], cv[:, :new_end]
+            seg_k = cseg[:, :new_end]
+            seg_q = seg_k[:, end:new_end]
+            q_off = end
+            new_cache = {"k": ck, "v": cv, "seg": cseg, "end": new_end}
+        if attention_mask is not None:
+            o = R.attention_ref(q, k, v, scale=self.scale, softcap=cfg.attn_logit_softcap,
+                                mask=attention_mask[:, None] if attention_mask.dim() == 3 else attention_mask)
+        else:
+            o = F.attention(q, k, v, scale=self.scale, causal=True, window=self.window,
+                            softcap=cfg.attn_logit_softcap, q_off=q_off, seg_q=seg_q, seg_k=seg_k)
+        o = o.reshape(B, T, N * H)
+        return self.o_proj(o, residual=residual), new_cache
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelConfig, device=None):
+        super().__init__()
+        D, Fd, dt = cfg.embed_dim, cfg.hidden_dim, cfg.dtype
+        self.gate_proj = Linear(D, Fd, False, dt, device)
+        self.up_proj = Linear(D, Fd, False, dt, device)
+        self.down_proj = Linear(Fd, D, False, dt, device)
+        self.kind = cfg.activation
+
+    def forward(self, x, residual=None):
+        h = F.glu(self.gate_proj(x), self.up_proj(x), self.kind)
+        return self.down_proj(h, residual=residual)
+
+
+class MoELayer(nn.Module):
+    """Top-k softmax-routed experts with SwiGLU (tunix/models/qwen3/model.py:851-1149).
+
+    Router: softmax over experts -> top-k -> renormalise. Expert weights are stacked
+    `[E, F, D]` (gate, up) and `[E, D, F]` (down). The optional auxiliary load-balancing loss
+    (Switch-style: E * sum_e f_e * P_e) is stored in `self.last_aux_loss`.
+    """
+
+    def __init__(self, cfg: ModelConfig, device=None):
+        super().__init__()
+        E, D, Fd, dt = cfg.num_experts, cfg.embed_dim, cfg.moe_hidden_dim, cfg.dtype
+        self.cfg = cfg
+        self.router = Linear(D, E, False, dt, device)
+        self.gate_proj = nn.Parameter(torch.empty(E, Fd, D, dtype=dt, device=device))
+        self.up_proj = nn.Parameter(torch.empty(E, Fd, D, dtype=dt, device=device))
+        self.down_proj = nn.Parameter(torch.empty(E, D, Fd, dtype=dt, device=device))
+        self.last_aux_loss: Optional[torch.Tensor] = None
+        self.last_routed_experts: Optional[torch.Tensor] = None
+        self.ep_group = None  # set by parallel.ep.shard_experts
+
+    def forward(self, x, residual=None, forced_experts: Optional[torch.Tensor] = None):
+        cfg = self.cfg
+        B, T, D = x.shape
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        xt = x.reshape(B * T, D)
+        logits = self.router(xt).float()
+        w, idx, probs = R.topk_router_ref(logits, k, cfg.norm_topk_prob)
+        if forced_experts is not None:  # router replay: reuse the sampler's expert choice
+            fe = forced_experts.reshape(B * T, k).long()
+            use = (fe >= 0).all(-1, keepdim=True)
+            idx = torch.where(use, fe.clamp(min=0), idx)
+            w_forced = probs.gather(1, idx)
+            w = w_forced / w_forced.sum(-1, keepdim=True) if cfg.norm_topk_prob else w_forced
+        self.last_routed_experts = idx.view(B, T, k)
+        if cfg.router_aux_loss_coef > 0:
+            frac = torch.zeros(E, device=x.device, dtype=torch.float32)
+            frac.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), device=x.device))
+            frac = frac / max(idx.numel(), 1)
+            self.last_aux_loss = cfg.router_aux_loss_coef * E * (frac * probs.mean(0)).sum()
+        from ..parallel import moe_dispatch
+        y = moe_dispatch.expert_forward(self, xt, w.to(x.dtype), idx)
+        y = y.view(B, T, D)
+        return y if residual is None else y + residual
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device=None):
+        super().__init__()
+        dt = cfg.dtype
+        mk = lambda: RMSNorm(cfg.embed_dim, cfg.norm_eps, cfg.norm_add_one, dt, device)  # noqa: E731
+        self.cfg = cfg
+        self.input_layernorm = mk()
+        self.self_attn = Attention(cfg, layer_idx, device)
+        self.post_attention_layernorm = mk()
+        self.mlp = MoELayer(cfg, device) if cfg.is_moe else MLP(cfg, device)
+        if cfg.post_norms:
+            self.post_attn_norm = mk()   # Gemma-2/3: norm on the attention output before the residual add
+            self.post_ffw_norm = mk()
+
+    def forward(self, x, positions, rope, cache=None, segment_ids=None, attention_mask=None):
+        cfg = self.cfg
+        h = self.input_layernorm(x)
+        if cfg.post_norms:
+            a, new_cache = self.self_attn(h, positions, rope, cache, segment_ids, attention_mask)
+            x = x + self.post_attn_norm(a)
+            m = self.mlp(self.post_attention_layernorm(x))
+            x = x + self.post_ffw_norm(m)
+        else:
+            x, new_cache = self.self_attn(h, positions, rope, cache, segment_ids, attention_mask, residual=x)
+            x = self.mlp(self.post_attention_layernorm(x), residual=x)
+        return x, new_cache
+
+
+class Transformer(nn.Module):
+    def __init__(self, cfg: ModelConfig, device=None):
+        super().__init__()
+        self.config = cfg
+        dt = cfg.dtype
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.embed_dim, dtype=dt, device=device))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, device) for i in range(cfg.num_layers)])
+        self.norm = RMSNorm(cfg.embed_dim, cfg.norm_eps, cfg.norm_add_one, dt, device)
+        self.lm_head = None if cfg.weight_tying else nn.Parameter(
+            torch.empty(cfg.vocab_size, cfg.embed_dim, dtype=dt, device=device))
+        self._rope_cache: dict = {}
+
+    # ------------------------------------------------------------------ weights
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> "Transformer":
+        """Random normal(0, std) for matrices, identity scale for norms, zero biases and LoRA-B."""
+        dev = self.embed_tokens.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if p.dim() >= 2 and "lora_b" not in name:
+                if p.numel() > (1 << 28):  # fill huge tensors in slices to bound temporaries
+                    flat = p.view(-1)
+                    step = 1 << 26
+                    for s0 in range(0, flat.numel(), step):
+                        flat[s0:s0 + step].normal_(0.0, std, generator=gen)
+                else:
+                    p.normal_(0.0, std, generator=gen)
+            elif "lora_b" in name or name.endswith("bias"):
+                p.zero_()
+        return self
+
+    def head_weight(self) -> torch.Tensor:
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    def _rope(self, local: bool, device):
+        cfg = self.config
+        key = (local, str(device))
+        tab = self._rope_cache.get(key)
+        if tab is None:
+            theta = cfg.local_rope_theta if (local and cfg.local_rope_theta) else cfg.rope_theta
+            sf = 1.0 if local else cfg.rope_scale_factor
+            tab = R.rope_tables(cfg.head_dim, cfg.max_position, theta, sf, device,
+                                None if local else cfg.rope_llama3_scaling)
+            self._rope_cache[key] = tab
+        return tab
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_tokens, positions=None, cache=None, attention_mask=None, segment_ids=None,
+                skip_lm_head: bool = False, output_hidden_states: bool = False):
+        cfg = self.config
+        B, T = input_tokens.shape
+        dev = input_tokens.device
+        if positions is None:
+            start = 0 if cache is None else cache[0]["end"]
+            positions = torch.arange(start, start + T, device=dev, dtype=torch.int32)[None].expand(B, T)
+        positions = positions.to(torch.int32).contiguous()
+        x = F.embedding(input_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
+        new_cache = [] if cache is not None else None
+        use_remat = cfg.remat_config != RematConfig.NONE and torch.is_grad_enabled() and cache is None
+        for i, layer in enumerate(self.layers):
+            rope = self._rope(cfg.layer_type(i) == "local", dev)
+            if use_remat:
+                x, _ = _torch_checkpoint(layer, x, positions, rope, None, segment_ids, attention_mask,
+                                         use_reentrant=False)
+            else:
+                x, c = layer(x, positions, rope, None if cache is None else cache[i], segment_ids, attention_mask)
+                if new_cache is not None:
+                    new_cache.append(c)
+        x = self.norm(x)
+        if skip_lm_head or output_hidden_states:
+            return x, new_cache
+        return self.compute_final_logits(x), new_cache
+
+    def compute_final_logits(self, hidden):
+        return F.lm_head_logits(hidden, self.head_weight(), softcap=self.config.final_logit_softcap)
+
+    def token_logprobs(self, hidden, targets, *, temperature: float = 1.0, want_entropy: bool = False,
+                       chunk: Optional[int] = None):
+        """log p(targets) from final hidden states without materialising [tokens, vocab] logits."""
+        return F.lm_head_logprobs(hidden, self.head_weight(), targets, softcap=self.config.final_logit_softcap,
+                                  temperature=temperature, want_entropy=want_entropy,
+                                  chunk=chunk or self.config.logprob_chunk)
+
+    def aux_loss(self):
+        """Sum of MoE router auxiliary losses of the last forward (None for dense models)."""
+        losses = [l.mlp.last_aux_loss for l in self.layers
+                  if isinstance(l.mlp, MoELayer) and l.mlp.last_aux_loss is not None]
+        return sum(losses) if losses else None
+
+    # -------------------------------------------------------------------- cache
+    def init_cache(self, batch_size: int, cache_size: int, dtype=None, device=None):
+        cfg = self.config
+        dtype = dtype or cfg.dtype
+        device = device or self.embed_tokens.device
+        mk = lambda: torch.zeros(batch_size, cache_size, cfg.num_kv_heads, cfg.head_dim, dtype=dtype, device=device)  # noqa: E731
+        return [{"k": mk(), "v": mk(), "seg": torch.zeros(batch_size, cache_size, dtype=torch.int32, device=device),
+                 "end": 0} for _ in range(cfg.num_layers)]
+
+    def get_model_input(self):
+        dev = self.embed_tokens.device
+        return {"input_tokens": torch.ones(2, 1, dtype=torch.int32, device=dev),
+                "positions": torch.ones(2, 1, dtype=torch.int32, device=dev), "cache": None,
+                "attention_mask": None}
+
+    @property
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+
+def create_model(cfg: ModelConfig, device=None, seed: int = 0, init: bool = True) -> Transformer:
+    """Random-init model of the given architecture (dummy-model creator of the reference:
+    tunix/models/dummy_model_creator.py:29-92)."""
+    model = Transformer(cfg, device=device)
+    if init:
+        model.init_weights(seed)
+    return model

@@ -76,11 +76,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, add_one: bool = False,
-                want_rstd: bool = True):
+                want_rstd: bool = True, out: torch.Tensor | None = None):
     """x: [rows, D] (unit inner stride). Returns (y, rstd[rows] fp32 or None)."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     rows, D = x.shape
-    y = torch.empty((rows, D), dtype=torch.bfloat16, device=x.device)
+    y = out if out is not None else torch.empty((rows, D), dtype=torch.bfloat16, device=x.device)
     rstd = torch.empty((rows,), dtype=torch.float32, device=x.device) if want_rstd else None
     rc = _lib.cuda().tb_rmsnorm_fwd(x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), y.stride(0),
                                     _lib.ptr(rstd), rows, D, float(eps), 1.0 if add_one else 0.0,

@@ -1,0 +1,250 @@
+"""Checkpoint save / restore with the directory layout of the reference's Orbax checkpoints.
+
+Layout (tunix/sft/checkpoint_manager.py:124-358, fixture tests/sft/test_data/checkpoints/1/):
+
+    <root>/<step>/_CHECKPOINT_METADATA           JSON, includes `custom_metadata`
+    <root>/<step>/model_params/_METADATA         JSON tree: "('layers', '0', 'weight')" -> array info
+    <root>/<step>/model_params/<dotted.name>/.zarray + 0   zarr-v2 array, one chunk, raw little-endian bytes
+    <root>/<step>/optimizer_state/...            same, keys ('mu'|'nu'|'master', <param name>)
+
+Arrays are written as plain (non-OCDBT) zarr-v2 chunk files; bfloat16 uses dtype string "bfloat16"
+with the raw 2-byte payload. LoRA models save / restore adapter parameters only (partial restore).
+Saves run on a background thread after a device->host copy (async checkpointing); policies:
+fixed step interval or "at least N seconds since the last save", keep the latest `max_to_keep`.
+`maybe_restore` returns `(step, custom_metadata)`.
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import threading
+import time
+from typing import Any, Optional
+
+import numpy as np
+import torch
+
+from ..common.configs import CheckpointingOptions
+
+_DT = {torch.float32: "<f4", torch.float16: "<f2", torch.bfloat16: "bfloat16", torch.int32: "<i4",
+       torch.int64: "<i8", torch.uint8: "|u1", torch.int8: "|i1", torch.bool: "|b1", torch.float64: "<f8",
+       torch.int16: "<i2"}
+_DT_INV = {v: k for k, v in _DT.items()}
+
+
+def _write_array(path: str, t: torch.Tensor) -> dict:
+    os.makedirs(path, exist_ok=True)
+    t = t.detach().contiguous().cpu()
+    meta = {"zarr_format": 2, "shape": list(t.shape), "chunks": list(t.shape) or [1], "dtype": _DT[t.dtype],
+            "compressor": None, "fill_value": 0, "order": "C", "filters": None}
+    with open(os.path.join(path, ".zarray"), "w") as f:
+        json.dump(meta, f)
+    raw = t.view(torch.uint8).numpy() if t.dtype != torch.bool else t.to(torch.uint8).numpy()
+    chunk_name = ".".join(["0"] * max(t.dim(), 1))
+    with open(os.path.join(path, chunk_name), "wb") as f:
+        f.write(raw.tobytes())
+    return {"shape": list(t.shape), "dtype": _DT[t.dtype]}
+
+
+def _read_array(path: str) -> torch.Tensor:
+    with open(os.path.join(path, ".zarray")) as f:
+        meta = json.load(f)
+    dt = _DT_INV[meta["dtype"]]
+    shape = meta["shape"]
+    chunk_name = ".".join(["0"] * max(len(shape), 1))
+    with open(os.path.join(path, chunk_name), "rb") as f:
+        raw = np.frombuffer(f.read(), dtype=np.uint8).copy()
+    t = torch.from_numpy(raw)
+    if dt == torch.bool:
+        return t.view(torch.uint8).bool().view(shape)
+    return t.view(dt).view(shape)
+
+
+def _flatten(tree: Any, prefix=()) -> dict:
+    out = {}
+    if isinstance(tree, dict):
+        for k, v in tree.items():
+            out.update(_flatten(v, prefix + (str(k),)))
+    else:
+        out[prefix] = tree
+    return out
+
+
+def _save_item(path: str, tree: dict) -> None:
+    os.makedirs(path, exist_ok=True)
+    flat = _flatten(tree)
+    md = {}
+    for key, val in flat.items():
+        name = ".".join(key)
+        if isinstance(val, torch.Tensor):
+            info = _write_array(os.path.join(path, name), val)
+            md[str(key)] = {"key_metadata": [{"key": k, "key_type": 2} for k in key],
+                            "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, **info}}
+        else:
+            md[str(key)] = {"key_metadata": [{"key": k, "key_type": 2} for k in key],
+                            "value_metadata": {"value_type": "scalar", "value": val}}
+    with open(os.path.join(path, "_METADATA"), "w") as f:
+        json.dump({"tree_metadata": md, "use_zarr3": False}, f)
+
+
+def _load_item(path: str) -> dict:
+    with open(os.path.join(path, "_METADATA")) as f:
+        md = json.load(f)["tree_metadata"]
+    out: dict = {}
+    for skey, info in md.items():
+        key = tuple(k["key"] for k in info["key_metadata"])
+        vm = info["value_metadata"]
+        val = _read_array(os.path.join(path, ".".join(key))) if vm["value_type"] == "jax.Array" else vm["value"]
+        d = out
+        for k in key[:-1]:
+            d = d.setdefault(k, {})
+        d[key[-1]] = val
+    return out
+
+
+class CheckpointManager:
+    def __init__(self, root_directory: Optional[str] = None, options: Any = None):
+        self._root = root_directory
+        if isinstance(options, dict) or options is None:
+            options = CheckpointingOptions.from_dict(options)
+        self._opts: CheckpointingOptions = options
+        self._last_save_time = time.time()
+        self._thread: Optional[threading.Thread] = None
+        self._error: Optional[BaseException] = None
+        if self._root:
+            os.makedirs(self._root, exist_ok=True)
+
+    # ------------------------------------------------------------------ queries
+    def all_steps(self) -> list[int]:
+        if not self._root or not os.path.isdir(self._root):
+            return []
+        steps = []
+        for d in os.listdir(self._root):
+            if d.isdigit() and os.path.exists(os.path.join(self._root, d, "_CHECKPOINT_METADATA")):
+                steps.append(int(d))
+        return sorted(steps)
+
+    def latest_step(self) -> Optional[int]:
+        s = self.all_steps()
+        return s[-1] if s else None
+
+    def _should_save(self, step: int, force: bool) -> bool:
+        if not self._root:
+            return False
+        if force:
+            return step not in self.all_steps()
+        o = self._opts
+        if o.save_interval_steps:
+            return step % o.save_interval_steps == 0
+        if o.save_interval_secs is not None:
+            return time.time() - self._last_save_time >= o.save_interval_secs
+        return False
+
+    # --------------------------------------------------------------------- save
+    def save(self, step: int, model, optimizer=None, save_only_lora_params: bool = False, force: bool = False,
+             custom_metadata: Optional[dict] = None) -> bool:
+        if not self._should_save(step, force):
+            return False
+        self.wait_until_finished()
+        from ..lora import is_lora_param_name
+        # Device -> host copies happen here (synchronously); file IO on the worker thread.
+        params = {n: p.detach().to("cpu", copy=True) for n, p in model.named_parameters()
+                  if (not save_only_lora_params) or is_lora_param_name(n)}
+        opt_state = None
+        if optimizer is not None:
+            sd = optimizer.state_dict()
+            opt_state = {k: ({n: t.detach().to("cpu", copy=True) for n, t in v.items()} if isinstance(v, dict) else v)
+                         for k, v in sd.items()}
+        meta = {"step": step, "custom_metadata": custom_metadata or {}, "init_timestamp_nsecs": time.time_ns(),
+                "item_handlers": {"model_params": "StandardCheckpointHandler",
+                                  "optimizer_state": "StandardCheckpointHandler"}}
+
+        def work():
+            try:
+                tmp = os.path.join(self._root, f"{step}.orbax-checkpoint-tmp")
+                final = os.path.join(self._root, str(step))
+                shutil.rmtree(tmp, ignore_errors=True)
+                os.makedirs(tmp)
+                _save_item(os.path.join(tmp, "model_params"), params)
+                if opt_state is not None:
+                    _save_item(os.path.join(tmp, "optimizer_state"), opt_state)
+                with open(os.path.join(tmp, "_CHECKPOINT_METADATA"), "w") as f:
+                    json.dump(meta, f)
+                shutil.rmtree(final, ignore_errors=True)
+                os.replace(tmp, final)
+                self._apply_retention()
+            except BaseException as e:  # surfaced on the next wait
+                self._error = e
+
+        self._last_save_time = time.time()
+        if self._opts.enable_async_checkpointing:
+            self._thread = threading.Thread(target=work, name="ckpt-save", daemon=True)
+            self._thread.start()
+        else:
+            work()
+            self._raise_pending()
+        return True
+
+    def _apply_retention(self) -> None:
+        keep = self._opts.max_to_keep
+        if not keep:
+            return
+        steps = self.all_steps()
+        for s in steps[:-keep]:
+            shutil.rmtree(os.path.join(self._root, str(s)), ignore_errors=True)
+
+    def _raise_pending(self):
+        if self._error is not None:
+            e, self._error = self._error, None
+            raise RuntimeError("checkpoint save failed") from e
+
+    def wait_until_finished(self) -> None:
+        if self._thread is not None:
+            self._thread.join(self._opts.timeout_secs)
+            if self._thread.is_alive():
+                raise TimeoutError("checkpoint save did not finish in time")
+            self._thread = None
+        self._raise_pending()
+
+    # ------------------------------------------------------------------ restore
+    def maybe_restore(self, model, optimizer=None, step: Optional[int] = None, restore_only_lora_params: bool = False):
+        """Restore the latest (or given) step in place. Returns (step, custom_metadata); (0, {}) if none."""
+        if not self._root:
+            return 0, {}
+        self.wait_until_finished()
+        step = self.latest_step() if step is None else step
+        if step is None:
+            return 0, {}
+        d = os.path.join(self._root, str(step))
+        with open(os.path.join(d, "_CHECKPOINT_METADATA")) as f:
+            meta = json.load(f)
+        from ..lora import is_lora_param_name
+        saved = _flatten(_load_item(os.path.join(d, "model_params")))
+        saved = {".".join(k): v for k, v in saved.items()}
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                if restore_only_lora_params and not is_lora_param_name(n):
+                    continue
+                if n in saved:
+                    p.copy_(saved[n].to(p.device, p.dtype))
+                elif not restore_only_lora_params and not saved_is_partial(saved):
+                    raise KeyError(f"parameter {n} missing from checkpoint {d}")
+        if optimizer is not None and os.path.isdir(os.path.join(d, "optimizer_state")):
+            sd = _load_item(os.path.join(d, "optimizer_state"))
+            fixed = {}
+            for k, v in sd.items():
+                if isinstance(v, dict):
+                    fixed[k] = {".".join(kk): vv for kk, vv in _flatten(v).items()}
+                else:
+                    fixed[k] = v
+            optimizer.load_state_dict(fixed)
+        return int(meta.get("step", step)), meta.get("custom_metadata", {}) or {}
+
+    def close(self) -> None:
+        self.wait_until_finished()
+
+
+def saved_is_partial(saved: dict) -> bool:
+    from ..lora import is_lora_param_name
+    return bool(saved) and all(is_lora_param_name(n) for n in saved)
