@@ -137,7 +137,7 @@ def main() -> int:
         mb = args.micro_batch
     else:
         # optimizer state + fp32 grads of an unsharded 8B model leave room for ~2 sequences of activations
-        mb = seqs if world >= 2 else 2
+        mb = {1: 2, 2: 4}.get(world, seqs)
     mb = min(mb, seqs)
     accum = seqs // mb
     opt = optim.AdamW(2e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.0, max_grad_norm=1.0)

@@ -1,0 +1,30 @@
+"""Sharded AdamW over NVLink peer memory (and its NCCL baseline) against single-GPU training."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("comm", ["p2p", "nccl"])
+def test_sharded_training_matches_single_gpu(comm, tmp_path):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2
+    out = str(tmp_path / "res.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29713", os.path.join(ROOT, "tests", "fsdp_worker.py"),
+           comm, out]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    r = json.load(open(out))
+    assert r["same"], "ranks disagree on parameters after the all-gather"
+    assert r["rel"] < 2e-2, r
+    assert abs(r["loss_sharded"][0] - r["loss_single"][0]) < 5e-2, r

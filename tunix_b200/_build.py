@@ -102,8 +102,33 @@ def build_host(force: bool = False) -> Path:
     return HOST_LIB
 
 
+TRAJJSON_LIB = PKG_DIR / "utils" / "_trajjson.so"
+
+
+def build_pyext(force: bool = False) -> Path:
+    """Compile the CPython extension modules under csrc/pyext (need Python.h)."""
+    import sysconfig
+    src = CSRC / "pyext" / "trajjson.cc"
+    stamp = BUILD_DIR / "pyext.stamp"
+    digest = _digest([src], " ".join(CXX_FLAGS) + sys.version)
+    if not force and TRAJJSON_LIB.exists() and stamp.exists() and stamp.read_text() == digest:
+        return TRAJJSON_LIB
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    inc = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(inc, "Python.h")):
+        raise RuntimeError("Python.h not found; the pure-Python serializer will be used")
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    _run([cxx, *CXX_FLAGS, "-fvisibility=default", "-shared", "-I", inc, "-o", str(TRAJJSON_LIB), str(src)])
+    stamp.write_text(digest)
+    return TRAJJSON_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_host(force)
+    try:
+        build_pyext(force)
+    except RuntimeError as e:  # optional: a Python fallback exists
+        print(f"[tunix_b200 build] pyext skipped: {e}", file=sys.stderr)
     build_cuda(force, verbose)
 
 

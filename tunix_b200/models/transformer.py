@@ -211,10 +211,25 @@ class DecoderLayer(nn.Module):
         return x, new_cache
 
 
+class _GradBoundary(torch.autograd.Function):
+    """Identity whose backward tells a listener that backward has passed this point of the network."""
+
+    @staticmethod
+    def forward(ctx, x, idx, hook):
+        ctx.idx, ctx.hook = idx, hook
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.hook(ctx.idx)
+        return g, None, None
+
+
 class Transformer(nn.Module):
     def __init__(self, cfg: ModelConfig, device=None):
         super().__init__()
         self.config = cfg
+        self.layer_grad_hook = None  # callable(int): backward reached the input of layer i (L = after last layer)
         dt = cfg.dtype
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.embed_dim, dtype=dt, device=device))
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, device) for i in range(cfg.num_layers)])
@@ -270,8 +285,11 @@ class Transformer(nn.Module):
         x = F.embedding(input_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         new_cache = [] if cache is not None else None
         use_remat = cfg.remat_config != RematConfig.NONE and torch.is_grad_enabled() and cache is None
+        hook = self.layer_grad_hook if (torch.is_grad_enabled() and cache is None) else None
         for i, layer in enumerate(self.layers):
             rope = self._rope(cfg.layer_type(i) == "local", dev)
+            if hook is not None and x.requires_grad:
+                x = _GradBoundary.apply(x, i, hook)
             if use_remat:
                 x, _ = _torch_checkpoint(layer, x, positions, rope, None, segment_ids, attention_mask,
                                          use_reentrant=False)
@@ -279,6 +297,8 @@ class Transformer(nn.Module):
                 x, c = layer(x, positions, rope, None if cache is None else cache[i], segment_ids, attention_mask)
                 if new_cache is not None:
                     new_cache.append(c)
+        if hook is not None and x.requires_grad:
+            x = _GradBoundary.apply(x, len(self.layers), hook)
         x = self.norm(x)
         if skip_lm_head or output_hidden_states:
             return x, new_cache

@@ -103,6 +103,8 @@ class PeftTrainer:
         if optimizer.buffers is None:
             grad_dtype = torch.float32 if (self.grad_accum_steps > 1 or self.device.type != "cuda") else None
             optimizer.bind(named, grad_dtype=grad_dtype)
+        if hasattr(optimizer, "install_hooks"):
+            optimizer.install_hooks(model)
         self.loss_fn: Callable = _default_loss_fn
         self.eval_loss_fn: Callable = _default_loss_fn
         self.gen_model_input_fn: Callable = lambda x: x if isinstance(x, dict) else {
@@ -190,6 +192,9 @@ class PeftTrainer:
         inputs = self.gen_model_input_fn(batch)
         out = self.loss_fn(self.model, **inputs)
         to_diff, metric, denom, aux = self._unpack_loss(out)
+        prepare = getattr(self.optimizer, "prepare_backward", None)
+        if prepare is not None:
+            prepare(is_update_step)   # sharded optimizers overlap the gradient reduction with this backward
         to_diff.backward()
         self.optimizer.buffers.collect_autograd_grads()
         self._denoms.append(denom.detach() if denom is not None else None)
