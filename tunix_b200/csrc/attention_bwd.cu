@@ -485,3 +485,104 @@ TB_API int tb_attn_bwd(const void* q, const void* k, const void* v, const void* 
     default: return -2;
   }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in noalloc.h; it has no counterpart in the reference).
+//
+// tb_attn_bwd above expects its caller to hand it two scratch buffers (delta and the fp32 dQ
+// accumulator), which in this package come from torch's caching allocator. Some callers cannot
+// allocate device memory at all: code running inside a CUDA-graph capture or a stream-ordered
+// region where cudaMalloc is illegal, a serving process whose memory pool is owned and fully
+// reserved by another component, or a plain C/C++ host that links this library without torch.
+// For them the scratch lives in the library image itself.
+// ---------------------------------------------------------------------------------------------
+#include "noalloc.h"
+#include <cstdio>
+
+namespace {
+
+// Fixed scratch, resident on every GPU that loads this library until the process exits.
+static __device__ __align__(256) float g_noalloc_dq_scratch[TB_NOALLOC_MAX_DQ_ELEMS];
+static __device__ __align__(256) float g_noalloc_delta_scratch[TB_NOALLOC_MAX_ROWS];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_dq_ptr[kMaxDevices] = {nullptr};
+float* g_noalloc_delta_ptr[kMaxDevices] = {nullptr};
+char g_noalloc_error[256] = "";
+
+__global__ void noalloc_zero_kernel(float* p, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    p[i] = 0.f;
+}
+__global__ void noalloc_cast_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(in[i]);
+}
+
+int noalloc_fail(int code, const char* msg) {
+  snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", msg);
+  return code;
+}
+
+// In host code the array names above are host-side stand-ins, not device addresses; the real
+// addresses are looked up once per device, with that device current.
+int noalloc_setup(int dev) {
+  if (g_noalloc_dq_ptr[dev] && g_noalloc_delta_ptr[dev]) return 0;
+  float* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_dq_scratch);
+  if (e != cudaSuccess || !p) return noalloc_fail(-10, "cudaGetSymbolAddress(dq scratch) failed");
+  g_noalloc_dq_ptr[dev] = p;
+  p = nullptr;
+  e = cudaGetSymbolAddress((void**)&p, g_noalloc_delta_scratch);
+  if (e != cudaSuccess || !p) return noalloc_fail(-10, "cudaGetSymbolAddress(delta scratch) failed");
+  g_noalloc_delta_ptr[dev] = p;
+  return 0;
+}
+
+}  // namespace
+
+TB_API const char* tb_noalloc_last_error() { return g_noalloc_error; }
+
+TB_API int tb_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                               const float* lse, void* dq, void* dk, void* dv, int B, int Tq, int Tk, int N,
+                               int KH, int H, float scale, float softcap, int causal, int window,
+                               int* status, cudaStream_t stream) {
+  g_noalloc_error[0] = 0;
+  if (B <= 0 || Tq <= 0 || Tk <= 0 || N <= 0 || KH <= 0 || N % KH) return noalloc_fail(-2, "bad shape");
+  if (H != 64 && H != 128 && H != 256) return noalloc_fail(-2, "head dim must be 64, 128 or 256");
+  const long long dq_elems = (long long)B * Tq * N * H;
+  const long long rows = (long long)B * N * Tq;
+  if (dq_elems > TB_NOALLOC_MAX_DQ_ELEMS || rows > TB_NOALLOC_MAX_ROWS) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+             "problem too large for the built-in scratch: B*Tq*N*H = %lld (max %lld), B*N*Tq = %lld (max %lld)",
+             dq_elems, (long long)TB_NOALLOC_MAX_DQ_ELEMS, rows, (long long)TB_NOALLOC_MAX_ROWS);
+    return -11;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return noalloc_fail(-10, "no current device");
+  if (int rc = noalloc_setup(dev)) return rc;
+  float* dq32 = g_noalloc_dq_ptr[dev];
+  float* delta = g_noalloc_delta_ptr[dev];
+  const long long ldq = (long long)N * H, ldkv = (long long)KH * H;
+  // The scratch keeps the previous call's contents: the dQ accumulator must start at zero.
+  noalloc_zero_kernel<<<592, 256, 0, stream>>>(dq32, dq_elems);
+  long long blocks = (rows + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  attn_delta_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)o, ldq, (const __nv_bfloat16*)dout, ldq,
+                                                     delta, B, Tq, N, H);
+  BwdArgs a;
+  a.B = B; a.Tq = Tq; a.Tk = Tk; a.N = N; a.KH = KH;
+  a.scale = scale; a.softcap = softcap; a.causal = causal; a.window = window; a.q_off = Tk - Tq;
+  a.seg_q = nullptr; a.seg_k = nullptr; a.lse = lse; a.delta = delta; a.dQ = dq32;
+  a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.lddk = ldkv; a.lddv = ldkv; a.status = status;
+  int rc;
+  switch (H) {
+    case 64: rc = launch_bwd<64>(q, k, v, dout, a, ldq, ldkv, ldkv, ldq, stream); break;
+    case 128: rc = launch_bwd<128>(q, k, v, dout, a, ldq, ldkv, ldkv, ldq, stream); break;
+    default: rc = launch_bwd<256>(q, k, v, dout, a, ldq, ldkv, ldkv, ldq, stream); break;
+  }
+  if (rc) return noalloc_fail(rc, "backward launch failed");
+  noalloc_cast_kernel<<<592, 256, 0, stream>>>(dq32, (__nv_bfloat16*)dq, dq_elems);
+  return cudaGetLastError() == cudaSuccess ? 0 : noalloc_fail(-5, "kernel launch failed");
+}
