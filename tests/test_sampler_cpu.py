@@ -1,0 +1,99 @@
+"""Vanilla sampler behaviour on CPU with a tiny model and a character tokenizer."""
+import numpy as np
+import torch
+
+from tunix_b200.common.configs import CacheConfig
+from tunix_b200.generate import sampling
+from tunix_b200.generate.sampler import Sampler
+from tunix_b200.models.config import ModelConfig
+from tunix_b200.models.transformer import create_model
+
+
+class CharTok:
+    def encode(self, s):
+        return [3 + (ord(c) % 60) for c in s]
+
+    def decode(self, ids):
+        return "".join(chr(97 + (int(i) % 26)) for i in ids)
+
+    def bos_id(self):
+        return 1
+
+    def eos_id(self):
+        return 2
+
+    def pad_id(self):
+        return 0
+
+
+def _sampler():
+    cfg = ModelConfig.tiny_llama().replace(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2,
+                                           head_dim=16, num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+    return model, Sampler(model, CharTok(), CacheConfig(cache_size=64, num_layers=2, num_kv_heads=1, head_dim=16))
+
+
+def test_greedy_matches_full_recompute_and_is_padding_invariant():
+    model, s = _sampler()
+    out = s(["hello", "hi"], max_generation_steps=6, return_logprobs=True, eos_tokens=[63])
+    # recompute greedily without a cache, one prompt at a time (no padding)
+    for i, prompt in enumerate(["hello", "hi"]):
+        ids = s.tokenize(prompt).tolist()
+        for step in range(6):
+            logits, _ = model(torch.tensor([ids]))
+            nxt = int(logits[0, -1].argmax())
+            assert nxt == int(out.tokens[i][step]), (i, step)
+            lp = torch.log_softmax(logits[0, -1].float(), -1)[nxt].item()
+            assert abs(lp - out.logprobs[i][step]) < 1e-4
+            ids.append(nxt)
+
+
+def test_sampling_is_reproducible_per_seed_and_step():
+    _, s = _sampler()
+    a = s(["abc"], max_generation_steps=8, temperature=1.0, top_p=0.9, top_k=20, seed=7, eos_tokens=[63])
+    b = s(["abc"], max_generation_steps=8, temperature=1.0, top_p=0.9, top_k=20, seed=7, eos_tokens=[63])
+    c = s(["abc"], max_generation_steps=8, temperature=1.0, top_p=0.9, top_k=20, seed=8, eos_tokens=[63])
+    assert np.array_equal(a.tokens[0], b.tokens[0])
+    assert not np.array_equal(a.tokens[0], c.tokens[0])
+
+
+def test_eos_stops_and_pad_output_and_echo():
+    model, s = _sampler()
+    first = int(s(["zz"], max_generation_steps=1, eos_tokens=[63]).tokens[0][0])
+    out = s(["zz"], max_generation_steps=5, eos_tokens=[first], pad_output=True, echo=True)
+    row = out.tokens[0]
+    assert row.shape[0] == 5 + out.padded_prompt_tokens.shape[1]
+    assert first in row.tolist()
+    forb = s(["zz"], max_generation_steps=1, forbidden_tokens=[first], eos_tokens=[63])
+    assert int(forb.tokens[0][0]) != first
+
+
+def test_top_p_filter_keeps_minimal_prefix():
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]]))
+    z = sampling.filter_logits(logits, 1.0, 0.7, None)
+    assert torch.isinf(z[0, 2]) and torch.isinf(z[0, 3]) and not torch.isinf(z[0, 1])
+    z = sampling.filter_logits(logits, 1.0, None, 1)
+    assert torch.isinf(z[0, 1:]).all()
+
+
+def test_beam_search_finds_higher_score_than_greedy():
+    model, s = _sampler()
+    g = s(["hey"], max_generation_steps=5, eos_tokens=[63])
+    b = s(["hey"], max_generation_steps=5, beam_size=4, eos_tokens=[63])
+
+    def score(tokens):
+        ids = s.tokenize("hey").tolist()
+        tot = 0.0
+        for t in tokens:
+            logits, _ = model(torch.tensor([ids]))
+            tot += torch.log_softmax(logits[0, -1].float(), -1)[int(t)].item()
+            ids.append(int(t))
+        return tot
+    assert score(b.tokens[0]) >= score(g.tokens[0]) - 1e-5
+
+
+def test_update_params_copies_lora_only():
+    model, s = _sampler()
+    name, p = next(iter(model.named_parameters()))
+    s.update_params({name: torch.zeros_like(p)})
+    assert float(dict(model.named_parameters())[name].abs().sum()) == 0.0

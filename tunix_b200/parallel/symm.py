@@ -42,8 +42,9 @@ def symm_available(group=None) -> bool:
     if dist.get_world_size(group) <= 1:
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
-        return dist.get_backend(group) == "nccl" or "nccl" in str(dist.get_backend(group))
+        import importlib
+        importlib.import_module("torch.distributed._symmetric_memory")
+        return "nccl" in str(dist.get_backend(group))
     except Exception:
         return False
 
