@@ -1,0 +1,82 @@
+"""End-to-end learner runs on tiny models (CPU): GRPO with the real sampler, PPO with a critic."""
+import numpy as np
+import torch
+
+from tunix_b200 import optim
+from tunix_b200.common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+from tunix_b200.lora import LoraProvider, apply_lora_to_model
+from tunix_b200.models.config import ModelConfig
+from tunix_b200.models.transformer import create_model
+from tunix_b200.rl import utils as rl_utils
+from tunix_b200.rl.algorithm_config import GRPOConfig, PPOConfig
+from tunix_b200.rl.grpo.grpo_learner import GRPOLearner
+from tunix_b200.rl.ppo.ppo_learner import PPOLearner
+from tunix_b200.rl.rl_cluster import RLCluster
+from tests.test_sampler_cpu import CharTok
+
+
+def _cfg():
+    return ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2,
+                                            head_dim=16, num_kv_heads=1)
+
+
+def reward_mod7(prompts, completions, completion_ids=None, completion_lengths=None, **kw):
+    out = []
+    for ids, n in zip(completion_ids, completion_lengths):
+        ids = ids[:n]
+        out.append(float((ids % 7 == 0).mean()) - 0.001 * n if n else 0.0)
+    return out
+
+
+def _cluster(actor, critic=None, reference=None, steps=2, tmp=None, mini=4, micro=2):
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=steps, actor_optimizer=optim.AdamW(1e-3),
+                          critic_optimizer=optim.AdamW(1e-3), mini_batch_size=mini, train_micro_batch_size=micro,
+                          checkpoint_root_directory=tmp)
+    rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3,
+                       kv_cache_size=32, eos_tokens=[63])
+    cc = ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc)
+    return RLCluster(actor=actor, reference=reference, critic=critic, tokenizer=CharTok(), cluster_config=cc)
+
+
+def test_grpo_learner_runs_and_updates_lora_only(tmp_path):
+    actor = create_model(_cfg(), seed=0)
+    apply_lora_to_model(actor, LoraProvider(module_path=r".*(q_proj|v_proj)", rank=4, alpha=8.0))
+    before = {n: p.detach().clone() for n, p in actor.named_parameters()}
+    cl = _cluster(actor, tmp=str(tmp_path))
+    learner = GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.04))
+    data = [{"prompts": ["ab", "cd", "ef", "gh"]} for _ in range(2)]
+    learner.train(data)
+    assert cl.global_steps == 2
+    changed = [n for n, p in actor.named_parameters() if not torch.equal(p, before[n])]
+    assert changed and all("lora" in n for n in changed)
+    hist = cl.metrics_logger.get_metric_history("", "rewards/score/mean", "train")
+    assert len(hist) == 2
+    assert cl.metrics_logger.metric_exists("actor", "kl", "train")
+    # resume: the actor checkpoint carries the global step
+    actor2 = create_model(_cfg(), seed=0)
+    apply_lora_to_model(actor2, LoraProvider(module_path=r".*(q_proj|v_proj)", rank=4, alpha=8.0))
+    cl2 = _cluster(actor2, tmp=str(tmp_path))
+    assert cl2.global_steps == 2
+    cl2.close()
+
+
+def test_grpo_full_weight_with_reference_and_gspo():
+    actor = create_model(_cfg(), seed=0)
+    ref = create_model(_cfg(), seed=0)
+    cl = _cluster(actor, reference=ref, steps=1)
+    learner = GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.04, loss_algo="gspo-token",
+                                                        num_iterations=2))
+    learner.train([{"prompts": ["ab", "cd", "ef", "gh"]}])
+    assert cl.global_steps == 1
+    assert cl.actor_trainer.train_steps == 2          # mu = 2 iterations over the same rollouts
+
+
+def test_ppo_learner_runs():
+    actor = create_model(_cfg(), seed=0)
+    critic = rl_utils.create_critic_model(actor)
+    ref = create_model(_cfg(), seed=0)
+    cl = _cluster(actor, critic=critic, reference=ref, steps=1)
+    learner = PPOLearner(cl, PPOConfig(), reward_fns=[reward_mod7])
+    learner.train([{"prompts": ["ab", "cd", "ef", "gh"]}])
+    assert cl.global_steps == 1
+    assert cl.critic_trainer.train_steps == 1

@@ -42,25 +42,69 @@ struct AdamArgs {
 // AdamW as optax.adamw: p -= lr * (m_hat / (sqrt(v_hat) + eps) + wd * p).
 // Clipping as optax.clip_by_global_norm: g *= max_norm / max(norm, max_norm).
 template <typename G>
-__global__ void adamw_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
-                             const G* __restrict__ g, __nv_bfloat16* __restrict__ p16, long long n,
-                             AdamArgs a) {
+__device__ __forceinline__ void load4g(const G* g, long long i, float (&o)[4]);
+template <>
+__device__ __forceinline__ void load4g<float>(const float* g, long long i, float (&o)[4]) {
+  const float4 q = *reinterpret_cast<const float4*>(g + i);
+  o[0] = q.x; o[1] = q.y; o[2] = q.z; o[3] = q.w;
+}
+template <>
+__device__ __forceinline__ void load4g<__nv_bfloat16>(const __nv_bfloat16* g, long long i, float (&o)[4]) {
+  const uint2 q = *reinterpret_cast<const uint2*>(g + i);
+  o[0] = bf16_lo(q.x); o[1] = bf16_hi(q.x); o[2] = bf16_lo(q.y); o[3] = bf16_hi(q.y);
+}
+
+// Four elements per thread with 16-byte accesses; buffers come from flat allocations, so every pointer is
+// 16-byte aligned and only the last n % 4 elements take the scalar tail.
+template <typename G>
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+             const G* __restrict__ g, __nv_bfloat16* __restrict__ p16, long long n, AdamArgs a) {
   float scale = a.grad_scale;
   if (a.denom) scale /= fmaxf(*a.denom, 1e-8f);
   if (a.max_norm > 0.f && a.sumsq) {
     const float norm = sqrtf(*a.sumsq) * fabsf(scale);
     scale *= a.max_norm / fmaxf(norm, a.max_norm);
   }
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+  const float ib1 = 1.f / a.bc1, ib2 = 1.f / a.bc2;
+  const long long n4 = n >> 2;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4;
+       q += (long long)gridDim.x * blockDim.x) {
+    const long long i = q << 2;
+    float gi[4];
+    load4g<G>(g, i, gi);
+    float4 mm = *reinterpret_cast<float4*>(m + i);
+    float4 vv = *reinterpret_cast<float4*>(v + i);
+    float4 pp = *reinterpret_cast<float4*>(p32 + i);
+    float* mp = &mm.x; float* vp = &vv.x; float* p = &pp.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = gi[k] * scale;
+      mp[k] = a.beta1 * mp[k] + (1.f - a.beta1) * gk;
+      vp[k] = a.beta2 * vp[k] + (1.f - a.beta2) * gk * gk;
+      const float upd = (mp[k] * ib1) / (sqrtf(vp[k] * ib2) + a.eps) + a.weight_decay * p[k];
+      p[k] -= a.lr * upd;
+    }
+    *reinterpret_cast<float4*>(m + i) = mm;
+    *reinterpret_cast<float4*>(v + i) = vv;
+    *reinterpret_cast<float4*>(p32 + i) = pp;
+    if (p16) {
+      uint2 o;
+      o.x = pack_bf16(p[0], p[1]);
+      o.y = pack_bf16(p[2], p[3]);
+      *reinterpret_cast<uint2*>(p16 + i) = o;
+    }
+  }
+  // scalar tail
+  for (long long i = (n4 << 2) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
-    const float gi = to_f<G>(g[i]) * scale;
-    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gi;
-    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * gi * gi;
+    const float gk = to_f<G>(g[i]) * scale;
+    const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gk;
+    const float vi = a.beta2 * v[i] + (1.f - a.beta2) * gk * gk;
     m[i] = mi;
     v[i] = vi;
     float p = p32[i];
-    const float upd = (mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps) + a.weight_decay * p;
-    p -= a.lr * upd;
+    p -= a.lr * ((mi * ib1) / (sqrtf(vi * ib2) + a.eps) + a.weight_decay * p);
     p32[i] = p;
     if (p16) p16[i] = __float2bfloat16(p);
   }
@@ -123,11 +167,15 @@ TB_API int tb_adamw(float* p32, float* m, float* v, const void* g, int g_is_bf16
                     const float* denom, cudaStream_t stream) {
   if (n <= 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, max_norm, sumsq, denom};
+  const uintptr_t align = reinterpret_cast<uintptr_t>(p32) | reinterpret_cast<uintptr_t>(m) |
+                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(g) |
+                          (reinterpret_cast<uintptr_t>(p16) << 1);
+  if (align & 15) return -2;  // flat buffers are always 16-byte aligned
   if (g_is_bf16)
-    adamw_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(
+    adamw_kernel<__nv_bfloat16><<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(
         p32, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)p16, n, a);
   else
-    adamw_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>(p32, m, v, (const float*)g,
+    adamw_kernel<float><<<grid_for((n + 3) / 4, 256), 256, 0, stream>>>(p32, m, v, (const float*)g,
                                                               (__nv_bfloat16*)p16, n, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

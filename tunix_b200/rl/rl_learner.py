@@ -1,0 +1,200 @@
+"""RLLearner: the outer RL loop shared by GRPO / PPO learners (tunix/rl/rl_learner.py:54-850).
+
+    global step -> (rollout + scoring on the producer thread) -> mini-batch steps -> micro-batch steps
+
+* `_prepare_data` (producer, :278-503): merges prompt micro-batches up to lcm(rollout_mb, logps_mb), repeats
+  every prompt G times, calls the algorithm's `_generate_and_compute_advantage`, splits the result into
+  train micro-batches and enqueues them; repeats the same data `num_iterations` times (mu) with an optional
+  seeded shuffle; a `None` sentinel ends the step. It runs on a thread so that, when rollout and actor live
+  on different ranks, generation of the next batch overlaps training of the current one; in the colocated
+  layout the queue degenerates to a synchronous hand-off (:151-156).
+* the consumer (main thread, :722-841) pulls micro-batches, optionally packs them, and calls
+  `rl_cluster.update_actor` (and `update_critic`);
+* after every global step: weight sync, metric flush, perf export (:627-658);
+* resume: the first `restored_global_step` batches of the dataset are skipped (:404-411).
+"""
+from __future__ import annotations
+
+import abc
+import math
+import threading
+from concurrent import futures
+from typing import Any, Callable, Iterable, Iterator, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..common.datatypes import Mode
+from . import algo_core, common, function_registry, reward_manager as _reward_manager, utils as rl_utils  # noqa: F401 (registrations)
+from .queue.data_queue import SimpleDataQueue
+from .rl_cluster import RLCluster
+
+
+class RLLearner(abc.ABC):
+    def __init__(self, rl_cluster: RLCluster, algo_config, reward_fns=None, metric_fns: Optional[Sequence[Callable]] = None,
+                 data_shuffle_seed: Optional[int] = None):
+        self.rl_cluster = rl_cluster
+        self.algo_config = algo_config
+        self.metric_fns = list(metric_fns or [])
+        self.tcfg = rl_cluster.cluster_config.training_config
+        rc = rl_cluster._rollout_config(Mode.TRAIN)
+        self.algo_config.temperature = rc.temperature if rc.temperature and rc.temperature > 0 else None
+        self.reward_manager = None
+        if reward_fns is not None:
+            cls = function_registry.get_reward_manager(algo_config.reward_manager)
+            self.reward_manager = cls(reward_fns, algo_config)
+        self.grad_acc_steps = self.tcfg.get_with_default("gradient_accumulation_steps", 1)
+        self._data_shuffle_seed = data_shuffle_seed
+        self._iter_steps = 0
+        self._eval_iter_steps = 0
+        self.should_sync_weights = not rl_cluster._rollout_shares_weights
+        self._producer_error: Optional[BaseException] = None
+        self.pad_id = rl_cluster.rollout.pad_id()
+        self.eos_id = rl_cluster.rollout.eos_id()
+        self.device = next(rl_cluster.train_actor.parameters()).device
+
+    # ---------------------------------------------------------- to implement
+    @abc.abstractmethod
+    def _generate_and_compute_advantage(self, training_input: dict, mode: Mode = Mode.TRAIN) -> common.TrainExample: ...
+
+    @abc.abstractmethod
+    def _num_generations(self) -> int: ...
+
+    @abc.abstractmethod
+    def _num_iterations(self) -> int: ...
+
+    def _compute_trajectory_ids(self, batch: dict, step: int) -> list[str]:
+        n = len(batch["prompts"])
+        G = self._num_generations()
+        return [f"{step}_{i // G}_{i % G}" for i in range(n)]
+
+    # ------------------------------------------------------------- rewards
+    def _compute_rewards(self, prompts: list, completions: list, mode: Mode, **kwargs) -> np.ndarray:
+        if self.reward_manager is None:
+            raise ValueError("no reward functions configured")
+        out = self.reward_manager(prompts, completions, **kwargs)
+        r = out["rewards"]
+        m = {"rewards/score/mean": (float(r.mean()), np.mean), "rewards/score/max": (float(r.max()), np.max),
+             "rewards/score/min": (float(r.min()), np.min)}
+        for name, col in out["per_fn"].items():
+            m[f"rewards/{name}"] = (float(np.mean(col)), np.mean)
+        self.rl_cluster.buffer_metrics(m, mode)
+        return r
+
+    # ------------------------------------------------------------- producer
+    def _repeat(self, batch: dict, G: int) -> dict:
+        out = {}
+        for k, v in batch.items():
+            if isinstance(v, (list, tuple)):
+                out[k] = [x for x in v for _ in range(G)]
+            elif isinstance(v, np.ndarray):
+                out[k] = np.repeat(v, G, axis=0)
+            elif isinstance(v, torch.Tensor):
+                out[k] = v.repeat_interleave(G, dim=0)
+            else:
+                out[k] = v
+        return out
+
+    def _prepare_data(self, iterator: Iterator, data_queue: SimpleDataQueue, mode: Mode, num_batches: int) -> None:
+        """Producer: consume `num_batches` prompt batches, enqueue train micro-batches, then a None sentinel."""
+        try:
+            G, mu = self._num_generations(), self._num_iterations()
+            mb = self.tcfg.train_micro_batch_size
+            produced: list[common.TrainExample] = []
+            for _ in range(num_batches):
+                try:
+                    batch = next(iterator)
+                except StopIteration:
+                    break
+                batch = self._repeat(batch, G)
+                with torch.no_grad():
+                    ex = self._generate_and_compute_advantage(batch, mode)
+                n = ex.completion_ids.shape[0]
+                step_mb = (mb * G) if mb else n
+                for sl in rl_utils.chunk_slices(n, step_mb):
+                    piece = rl_utils.slice_example(ex, sl)
+                    produced.append(piece)
+                    data_queue.put(piece)
+            if mode == Mode.TRAIN:
+                for it in range(1, mu):
+                    order = list(range(len(produced)))
+                    if self._data_shuffle_seed is not None:
+                        np.random.default_rng(self._data_shuffle_seed + it).shuffle(order)
+                    for i in order:
+                        data_queue.put(produced[i])
+        except BaseException as e:  # forwarded to the consumer
+            self._producer_error = e
+        finally:
+            data_queue.put(None)
+
+    # ------------------------------------------------------------- consumer
+    def _batches_from_queue(self, q: SimpleDataQueue) -> Iterator[common.TrainExample]:
+        while True:
+            item = q.get()
+            if item is None:
+                if self._producer_error is not None:
+                    e, self._producer_error = self._producer_error, None
+                    raise RuntimeError("rollout producer failed") from e
+                return
+            yield item
+
+    def _maybe_pack(self, examples: Iterable[common.TrainExample]) -> Iterable[common.TrainExample]:
+        if not self.tcfg.sequence_packing_enabled:
+            return examples
+        budget = self.tcfg.max_seq_token_per_tpu
+        return rl_utils.pack_sequences(examples, budget, pack_size=max(self.tcfg.train_micro_batch_size or 1, 1),
+                                       pad_id=self.pad_id, device=self.device,
+                                       max_segments=self.tcfg.max_segments_per_packed_row)
+
+    def _train_on(self, examples: Iterable[common.TrainExample]) -> None:
+        self.rl_cluster.update_actor(self._maybe_pack(examples), None)
+
+    def train(self, train_ds: Iterable[dict], eval_ds: Optional[Iterable[dict]] = None, skip_jit: bool = False) -> None:
+        """`train_ds` yields dicts with at least `prompts` (list[str]) or `prompt_token_ids`; one item = one
+        global batch of prompts (mini_batch_size prompts)."""
+        it = iter(train_ds)
+        max_steps = self.tcfg.max_steps
+        # resume: skip consumed prompt batches
+        for _ in range(self.rl_cluster.global_steps):
+            try:
+                next(it)
+            except StopIteration:
+                return
+        executor = futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="rl-producer")
+        try:
+            while True:
+                if max_steps is not None and self.rl_cluster.global_steps >= max_steps:
+                    break
+                q: SimpleDataQueue = SimpleDataQueue()
+                fut = executor.submit(self._prepare_data, it, q, Mode.TRAIN, 1)
+                got_any = False
+
+                def counted():
+                    nonlocal got_any
+                    for ex in self._batches_from_queue(q):
+                        got_any = True
+                        self._iter_steps += 1
+                        yield ex
+                self._train_on(counted())
+                fut.result()
+                if not got_any:
+                    break
+                self.rl_cluster.sync_weights()
+                self.rl_cluster.flush_metrics()
+                if eval_ds is not None and self.tcfg.eval_every_n_steps and \
+                        self.rl_cluster.global_steps % self.tcfg.eval_every_n_steps == 0:
+                    self._run_eval(eval_ds)
+        finally:
+            executor.shutdown(wait=True)
+            self.rl_cluster.close()
+            if self.reward_manager is not None and hasattr(self.reward_manager, "close"):
+                self.reward_manager.close()
+
+    def _run_eval(self, eval_ds: Iterable[dict]) -> None:
+        rewards = []
+        for batch in eval_ds:
+            with torch.no_grad():
+                ex = self._generate_and_compute_advantage(dict(batch), Mode.EVAL)
+            rewards.append(float(ex.advantages.float().mean()))
+            self._eval_iter_steps += 1
+        self.rl_cluster.flush_metrics()

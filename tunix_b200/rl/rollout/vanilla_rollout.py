@@ -1,0 +1,53 @@
+"""Rollout on the in-framework sampler (tunix/rl/rollout/vanilla_rollout.py:31-106)."""
+from __future__ import annotations
+
+import numpy as np
+
+from ...common.configs import CacheConfig, RolloutConfig
+from ...generate.sampler import Sampler
+from .. import common
+from .base_rollout import BaseRollout, RolloutOutput
+
+
+class VanillaRollout(BaseRollout):
+    def __init__(self, model, tokenizer, cache_config_or_size, engine: str = "dense"):
+        cfg = model.config
+        if isinstance(cache_config_or_size, int):
+            cache_config_or_size = CacheConfig(cache_config_or_size, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim)
+        self._tokenizer = tokenizer
+        self._sampler = Sampler(model, tokenizer, cache_config_or_size)
+        self._engine = None
+        if engine == "paged":
+            from ...generate.engine import PagedEngine
+            self._engine = PagedEngine(model, tokenizer, cache_config_or_size)
+
+    def generate(self, prompts, rollout_config: RolloutConfig, **kwargs) -> RolloutOutput:
+        tok_prompts = kwargs.get("prompt_token_ids")
+        call = self._engine if self._engine is not None else self._sampler
+        out = call(input_strings=None if tok_prompts is not None else prompts,
+                   prompt_token_ids=tok_prompts,
+                   max_generation_steps=rollout_config.max_tokens_to_generate,
+                   max_prompt_length=rollout_config.max_prompt_length, temperature=rollout_config.temperature,
+                   top_p=rollout_config.top_p, top_k=rollout_config.top_k, seed=rollout_config.seed,
+                   eos_tokens=rollout_config.eos_tokens, return_logprobs=rollout_config.return_logprobs,
+                   echo=False, pad_output=False)
+        lps = [np.asarray(l, np.float32) for l in out.logprobs] if out.logprobs is not None else None
+        return RolloutOutput(text=out.text, logits=None, tokens=[np.asarray(t) for t in out.tokens],
+                             left_padded_prompt_tokens=out.padded_prompt_tokens, logprobs=lps,
+                             routed_experts=out.routed_experts, prompt_lengths=out.prompt_lengths)
+
+    def get_per_token_logps(self, prompt_tokens, completion_tokens, completion_mask=None):
+        return common.compute_per_token_logps(self.model(), prompt_tokens, completion_tokens, self.pad_id(), self.eos_id(),
+                                              completion_mask=completion_mask, stop_gradient=True)
+
+    def update_params(self, params, filter_types=None) -> None:
+        self._sampler.update_params(params, filter_types)
+
+    def pad_id(self) -> int:
+        return self._tokenizer.pad_id()
+
+    def eos_id(self) -> int:
+        return self._tokenizer.eos_id()
+
+    def model(self):
+        return self._sampler.transformer
