@@ -74,7 +74,8 @@ class PPOLearner(RLLearner):
             score = score.float()
         else:
             extra = {k: v for k, v in training_input.items() if k not in ("prompts", "prompt_token_ids")}
-            score = torch.from_numpy(self._compute_rewards(list(prompts or [""] * B), list(out.text), mode, **extra)).to(dev)
+            score = torch.from_numpy(self._compute_rewards(list(prompts or [""] * B), list(out.text), mode, completion_ids=comp,
+                                                            completion_lengths=lens, **extra)).to(dev)
         rewards = torch.zeros(B, C, device=dev)
         last = torch.as_tensor(np.maximum(lens - 1, 0), device=dev)
         rewards[torch.arange(B, device=dev), last] = score
