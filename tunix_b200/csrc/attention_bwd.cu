@@ -44,25 +44,37 @@ struct BwdArgs {
 
 template <int H>
 struct BwdCfg {
+  static constexpr bool PIPE = (H <= 128);          // software-pipelined schedule (needs double buffers)
   static constexpr int HS = H / 64;
   static constexpr int HO = H < 128 ? H : 128;
   static constexpr int NHALF = H / HO;
-  static constexpr int NST = (H <= 128) ? 2 : 1;
+  static constexpr int NST = PIPE ? 3 : 1;          // Q / dO tile stages
+  static constexpr int NPB = PIPE ? 2 : 1;          // Pt / dSt staging buffers
   static constexpr int KV_BYTES = HS * BK_ * 128;
   static constexpr int Q_BYTES = HS * BQ_ * 128;
+  static constexpr int P_BYTES = BK_ * 128;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + KV_BYTES;
   static constexpr int OFF_Q = OFF_V + KV_BYTES;
   static constexpr int OFF_DO = OFF_Q + NST * Q_BYTES;
   static constexpr int OFF_PT = OFF_DO + NST * Q_BYTES;
-  static constexpr int OFF_DST = OFF_PT + BK_ * 128;
-  static constexpr int OFF_STAT = OFF_DST + BK_ * 128;      // [2][3][64] 4-byte values
+  static constexpr int OFF_DST = OFF_PT + NPB * P_BYTES;
+  static constexpr int OFF_STAT = OFF_DST + NPB * P_BYTES;   // [2][3][64] 4-byte values
   static constexpr int OFF_BAR = OFF_STAT + 2 * 3 * 64 * 4;
-  static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;
-  static constexpr int TM_ST = 0, TM_DPT = 64, TM_DQT = 128, TM_DV = 192, TM_DK = 192 + HO;
+  static constexpr int SMEM_BYTES = OFF_BAR + 192 + 1024;
+  // TMEM columns. PIPE: St/dQt buffers at 0 and 64, dPt buffers at 128 and 192, dV at 256, dK after it.
+  // Otherwise: St 0, dPt 64, dQt 128, dV 192, dK after it.
+  static constexpr int TM_DV = PIPE ? 256 : 192;
+  static constexpr int TM_DK = TM_DV + HO;
   static constexpr int TMEM_COLS = 512;
+  __host__ __device__ static constexpr int tm_st(int buf) { return PIPE ? buf * 64 : 0; }
+  __host__ __device__ static constexpr int tm_dpt(int buf) { return PIPE ? 128 + buf * 64 : 64; }
+  __host__ __device__ static constexpr int tm_dqt(int buf) { return PIPE ? buf * 64 : 128; }
 };
 
+// Schedule (PIPE): while the row threads work on query tile `it` (P, then dS), the tensor core already
+// holds St/dPt of tile it+1 (issued at mid-iteration) and finishes dV/dK/dQt of tile it-1; the dQt of
+// tile it-1 is drained between the two phases of tile it. Handoffs never wait on a just-issued MMA.
 template <int H>
 __global__ void __launch_bounds__(160, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -71,17 +83,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   using C_ = BwdCfg<H>;
   constexpr int HO = C_::HO;
   constexpr int NST = C_::NST;
+  constexpr bool PIPE = C_::PIPE;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t sK = sbase + C_::OFF_K, sV = sbase + C_::OFF_V, sQ = sbase + C_::OFF_Q,
                  sdO = sbase + C_::OFF_DO, sPt = sbase + C_::OFF_PT, sdSt = sbase + C_::OFF_DST,
                  bars = sbase + C_::OFF_BAR;
-  // barriers: 0 KV, 1-2 Q[2], 3-4 Qfree[2], 5 St, 6 dPt, 7 Pt, 8 dSt, 9 dQ, (10: tmem slot + abort), 11 row-thread sync
-  const uint32_t barKV = bars, barQ0 = bars + 8, barQF0 = bars + 24, barSt = bars + 40,
-                 bardPt = bars + 48, barPt = bars + 56, bardSt = bars + 64, bardQ = bars + 72, barSync = bars + 88;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sptr + C_::OFF_BAR + 80);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sptr + C_::OFF_BAR + 84);
+  // barriers (8 bytes each): 0 KV | 1-3 Q[3] | 4-6 Qfree[3] | 7-8 St[2] | 9-10 dPt[2] | 11 Pt | 12 dSt |
+  //                          13 dQ | 14 dQ drained | 15 row-thread sync ; then tmem slot + abort flag
+  const uint32_t barKV = bars, barQ0 = bars + 8, barQF0 = bars + 32, barSt0 = bars + 56, bardPt0 = bars + 72,
+                 barPt = bars + 88, bardSt = bars + 96, bardQ = bars + 104, barDQfree = bars + 112,
+                 barSync = bars + 120;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sptr + C_::OFF_BAR + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sptr + C_::OFF_BAR + 132);
   float* s_stat = reinterpret_cast<float*>(sptr + C_::OFF_STAT);
 
   const int warp = threadIdx.x >> 5;
@@ -102,15 +117,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(barKV, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(barQ0 + 8 * s, 1);
       mbar_init(barQF0 + 8 * s, 1);
     }
-    mbar_init(barSt, 1);
-    mbar_init(bardPt, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(barSt0 + 8 * s, 1);
+      mbar_init(bardPt0 + 8 * s, 1);
+    }
     mbar_init(barPt, 128);
     mbar_init(bardSt, 128);
     mbar_init(bardQ, 1);
+    mbar_init(barDQfree, 128);
     mbar_init(barSync, 128);
     *abort_flag = 0;
     mbar_fence_init();
@@ -123,6 +141,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // TMEM buffer / barrier index and parity of the per-tile St and dPt results
+  auto sbuf = [&](int it) { return PIPE ? (it & 1) : 0; };
+  auto spar = [&](int it) { return PIPE ? ((it >> 1) & 1) : (it & 1); };
 
   if (warp == 4) {
     // ------------------------------------------------------------ issuer warp
@@ -130,7 +151,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_s = make_idesc_bf16(128, BQ_, 0, 0);     // K-major x K-major, N = 64
       const uint32_t idesc_dv = make_idesc_bf16(128, HO, 0, 1);     // A K-major, B MN-major, N = HO
       const uint32_t idesc_dq = make_idesc_bf16(128, BQ_, 1, 1);    // both MN-major, N = 64
-      auto load_q = [&](int it, int st) {
+      const uint32_t col_off = half * (HO / 64) * (BQ_ * 128);      // slab offset of this half in Q/dO tiles
+      const uint32_t k_half = sK + half * (HO / 64) * (BK_ * 128);
+      auto load_q = [&](int it) {
+        const int st = it % NST;
         const int g = it / nq, qt = qt0 + it % nq;
         const int n = kvh * G + g;
         const uint32_t bar = barQ0 + 8 * st;
@@ -141,6 +165,58 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tma_load_2d(sdO + st * C_::Q_BYTES + c * (BQ_ * 128), &tmdO, bar, n * H + 64 * c, b * a.Tq + qt * BQ_);
         }
       };
+      // St = K Q^T ; dPt = V dO^T  (contraction over the full head dim)
+      auto issue_s_dp = [&](int it) {
+        const int st = it % NST;
+        const uint32_t q_s = sQ + st * C_::Q_BYTES, do_s = sdO + st * C_::Q_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sK + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(q_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16_ss(tmem + C_::tm_st(sbuf(it)), ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(barSt0 + 8 * sbuf(it));
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sV + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(do_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16_ss(tmem + C_::tm_dpt(sbuf(it)), ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(bardPt0 + 8 * sbuf(it));
+      };
+      // dV += Pt dO   (A = Pt K-major over 64 queries, B = dO MN-major, this CTA's column half)
+      auto issue_dv = [&](int it) {
+        const uint32_t do_s = sdO + (it % NST) * C_::Q_BYTES;
+        const uint32_t pt = sPt + (PIPE ? (it & 1) : 0) * C_::P_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BQ_ / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(pt + kk * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(do_s + col_off + kk * 2048, BQ_ * 128, 1024);
+          umma_f16_ss(tmem + C_::TM_DV, ad, bd, idesc_dv, (it | kk) != 0);
+        }
+      };
+      // dK += dSt Q ; dQt = K^T dS^T
+      auto issue_dk_dq = [&](int it) {
+        const uint32_t q_s = sQ + (it % NST) * C_::Q_BYTES;
+        const uint32_t ds = sdSt + (PIPE ? (it & 1) : 0) * C_::P_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BQ_ / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(ds + kk * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(q_s + col_off + kk * 2048, BQ_ * 128, 1024);
+          umma_f16_ss(tmem + C_::TM_DK, ad, bd, idesc_dv, (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BK_ / 16; ++kk) {
+          // A = K^T: M (head dim) contiguous, 64-wide M chunks BK_*128 bytes apart; 16 keys per step
+          const uint64_t ad = make_smem_desc(k_half + kk * 2048, BK_ * 128, 1024);
+          const uint64_t bd = make_smem_desc(ds + kk * 2048, BK_ * 128, 1024);
+          umma_f16_ss(tmem + C_::tm_dqt(sbuf(it)), ad, bd, idesc_dq, kk != 0);
+        }
+        umma_commit(barQF0 + 8 * (it % NST));
+        umma_commit(bardQ);
+      };
+#define BWD_WAIT(bar, par, code) \
+  if (!mbar_wait_bounded((bar), (par), abort_flag, a.status, (code))) { ok = false; break; }
       bool ok = true;
       mbar_expect_tx(barKV, 2 * C_::KV_BYTES);
 #pragma unroll
@@ -148,67 +224,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tma_load_2d(sK + c * (BK_ * 128), &tmK, barKV, kvh * H + 64 * c, b * a.Tk + k0);
         tma_load_2d(sV + c * (BK_ * 128), &tmV, barKV, kvh * H + 64 * c, b * a.Tk + k0);
       }
-      load_q(0, 0);
-      if (NST == 2 && nit > 1) load_q(1, 1);
+      for (int i = 0; i < NST && i < nit; ++i) load_q(i);
       ok = mbar_wait_bounded(barKV, 0, abort_flag, a.status, ST_TIMEOUT_PRODUCER);
-      for (int it = 0; it < nit && ok; ++it) {
-        const int st = it % NST;
-        if (NST == 1 && it >= 1) {
-          if (!mbar_wait_bounded(barQF0, (it - 1) & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-          load_q(it, 0);
+      if (PIPE) {
+        ok = ok && mbar_wait_bounded(barQ0, 0, abort_flag, a.status, ST_TIMEOUT_PRODUCER);
+        if (ok) {
+          tc_fence_after();
+          issue_s_dp(0);
         }
-        if (!mbar_wait_bounded(barQ0 + 8 * st, (it / NST) & 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t q_s = sQ + st * C_::Q_BYTES, do_s = sdO + st * C_::Q_BYTES;
-        // St = K Q^T ; dPt = V dO^T  (contraction over the full head dim)
-#pragma unroll
-        for (int kk = 0; kk < H / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(sK + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(q_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
-          umma_f16_ss(tmem + C_::TM_ST, ad, bd, idesc_s, kk != 0);
+        for (int it = 0; it < nit && ok; ++it) {
+          BWD_WAIT(barPt, it & 1, ST_TIMEOUT_MMA);
+          tc_fence_after();
+          issue_dv(it);
+          if (it + 1 < nit) {
+            BWD_WAIT(barQ0 + 8 * ((it + 1) % NST), ((it + 1) / NST) & 1, ST_TIMEOUT_PRODUCER);
+            // St_{it+1} overwrites the TMEM buffer that held dQt_{it-1}: wait until it was drained
+            if (it >= 1) BWD_WAIT(barDQfree, (it - 1) & 1, ST_TIMEOUT_MMA);
+            tc_fence_after();
+            issue_s_dp(it + 1);
+          }
+          if (it >= 1 && it + 2 < nit) {
+            // the stage of tile it-1 is free once its dK / dQt retired
+            BWD_WAIT(barQF0 + 8 * ((it - 1) % NST), ((it - 1) / NST) & 1, ST_TIMEOUT_MMA);
+            load_q(it + 2);
+          }
+          BWD_WAIT(bardSt, it & 1, ST_TIMEOUT_MMA);
+          tc_fence_after();
+          issue_dk_dq(it);
         }
-        umma_commit(barSt);
-#pragma unroll
-        for (int kk = 0; kk < H / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(sV + (kk >> 2) * (BK_ * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(do_s + (kk >> 2) * (BQ_ * 128) + (kk & 3) * 32, 16, 1024);
-          umma_f16_ss(tmem + C_::TM_DPT, ad, bd, idesc_s, kk != 0);
+      } else {
+        for (int it = 0; it < nit && ok; ++it) {
+          if (it >= 1) {
+            BWD_WAIT(barQF0, (it - 1) & 1, ST_TIMEOUT_MMA);
+            load_q(it);
+          }
+          BWD_WAIT(barQ0, it & 1, ST_TIMEOUT_PRODUCER);
+          tc_fence_after();
+          issue_s_dp(it);
+          BWD_WAIT(barPt, it & 1, ST_TIMEOUT_MMA);
+          tc_fence_after();
+          issue_dv(it);
+          BWD_WAIT(bardSt, it & 1, ST_TIMEOUT_MMA);
+          tc_fence_after();
+          issue_dk_dq(it);
         }
-        umma_commit(bardPt);
-        if (NST == 2 && it >= 1 && it + 1 < nit) {
-          // stage (it+1)&1 was used by tile it-1, whose MMAs precede the ones just issued
-          if (!mbar_wait_bounded(barQF0 + 8 * ((it + 1) & 1), ((it - 1) >> 1) & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-          load_q(it + 1, (it + 1) & 1);
-        }
-        // dV += Pt dO   (A = Pt K-major over 64 queries, B = dO MN-major, this CTA's column half)
-        if (!mbar_wait_bounded(barPt, it & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t col_off = half * (HO / 64) * (BQ_ * 128);  // slab offset of this half in Q/dO tiles
-#pragma unroll
-        for (int kk = 0; kk < BQ_ / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(sPt + kk * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(do_s + col_off + kk * 2048, BQ_ * 128, 1024);
-          umma_f16_ss(tmem + C_::TM_DV, ad, bd, idesc_dv, (it | kk) != 0);
-        }
-        // dK += dSt Q ; dQt = K^T dS^T
-        if (!mbar_wait_bounded(bardSt, it & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < BQ_ / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(sdSt + kk * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(q_s + col_off + kk * 2048, BQ_ * 128, 1024);
-          umma_f16_ss(tmem + C_::TM_DK, ad, bd, idesc_dv, (it | kk) != 0);
-        }
-        const uint32_t k_half = sK + half * (HO / 64) * (BK_ * 128);
-#pragma unroll
-        for (int kk = 0; kk < BK_ / 16; ++kk) {
-          // A = K^T: M (head dim) contiguous, 64-wide M chunks BK_*128 bytes apart; 16 keys per step
-          const uint64_t ad = make_smem_desc(k_half + kk * 2048, BK_ * 128, 1024);
-          const uint64_t bd = make_smem_desc(sdSt + kk * 2048, BK_ * 128, 1024);
-          umma_f16_ss(tmem + C_::TM_DQT, ad, bd, idesc_dq, kk != 0);
-        }
-        umma_commit(barQF0 + 8 * st);
-        umma_commit(bardQ);
       }
     }
   } else {
@@ -219,12 +278,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     const int my_seg = (a.seg_k && key_valid) ? a.seg_k[(long long)b * a.Tk + kp] : 0;
     bool ok = true;
-    // stats of the first tile
     auto stat_ptr = [&](int buf, int which) { return s_stat + (buf * 3 + which) * 64; };
+    auto tile_of = [&](int it, int& n, int& qbase) {
+      n = kvh * G + it / nq;
+      qbase = (qt0 + it % nq) * BQ_;
+    };
     auto fetch_stats = [&](int it, float& v_lse, float& v_delta, int& v_seg) {
-      const int g = it / nq, qt = qt0 + it % nq;
-      const int n = kvh * G + g;
-      const int qi = qt * BQ_ + r;
+      int n, qbase;
+      tile_of(it, n, qbase);
+      const int qi = qbase + r;
       if (r < 64 && qi < a.Tq) {
         const long long o = ((long long)b * a.N + n) * a.Tq + qi;
         v_lse = a.lse[o] * LOG2E;
@@ -234,6 +296,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         v_lse = INFINITY;
         v_delta = 0.f;
         v_seg = -1;
+      }
+    };
+    // dQt tile of `it`: lane = head-dim index (within this CTA's half), column = query
+    auto drain_dq = [&](int it) {
+      int n, qbase;
+      tile_of(it, n, qbase);
+      uint32_t t0[32], t1[32];
+      tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)), t0);
+      tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)) + 32, t1);
+      tmem_ld_wait();
+      if (r < HO) {
+        float* dq = a.dQ + ((long long)b * a.Tq + qbase) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
+        const long long ld = (long long)a.N * H;
+        if (qbase + 64 <= a.Tq) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) atomicAdd(dq + i * ld, __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (qbase + i < a.Tq) atomicAdd(dq + i * ld, __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]));
+        }
       }
     };
     if (nit > 0) {
@@ -247,43 +330,55 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     for (int it = 0; it < nit && ok; ++it) {
-      // stats of tile `it` visible to every row thread; previous tile fully consumed
+      // stats of tile `it` visible to every row thread; previous tile's stats fully consumed
       mbar_arrive(barSync);
-      if (!mbar_wait_bounded(barSync, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      BWD_WAIT(barSync, it & 1, ST_TIMEOUT_EPILOGUE);
       float nx_lse = INFINITY, nx_delta = 0.f;
       int nx_seg = -1;
       if (it + 1 < nit) fetch_stats(it + 1, nx_lse, nx_delta, nx_seg);
-      const int g = it / nq, qt = qt0 + it % nq;
-      const int n = kvh * G + g;
-      const int qbase = qt * BQ_;
+      int n, qbase;
+      tile_of(it, n, qbase);
       const float* st_lse = stat_ptr(it & 1, 0);
       const float* st_delta = stat_ptr(it & 1, 1);
       const int* st_seg = reinterpret_cast<const int*>(stat_ptr(it & 1, 2));
+      const int pb = PIPE ? (it & 1) : 0;
+      // does any (key, query) pair of this tile need masking?
+      const int qpos_lo = qbase + a.q_off, qpos_hi = qbase + BQ_ - 1 + a.q_off;
+      const bool need_mask = (k0 + BK_ > a.Tk) || (qbase + BQ_ > a.Tq) || (a.seg_k != nullptr) ||
+                             (a.causal && (k0 + BK_ - 1 > qpos_lo)) ||
+                             (a.window > 0 && (k0 <= qpos_hi - a.window));
 
-      if (!mbar_wait_bounded(barSt, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      BWD_WAIT(barSt0 + 8 * sbuf(it), spar(it), ST_TIMEOUT_EPILOGUE);
       tc_fence_after();
       float p[64];
       {
         uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_ST, t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_ST + 32, t1);
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)), t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + 32, t1);
         tmem_ld_wait();
+        const float sc2 = a.scale * LOG2E;
+        if (!need_mask && a.softcap <= 0.f) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float s = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
-          const int qpos = qbase + i + a.q_off;
-          float z;
-          if (a.softcap > 0.f) z = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
-          else z = s * a.scale * LOG2E;
-          bool keep = key_valid && (qbase + i < a.Tq);
-          if (a.causal) keep = keep && (kp <= qpos);
-          if (a.window > 0) keep = keep && (kp > qpos - a.window);
-          if (a.seg_k) keep = keep && (st_seg[i] == my_seg);
-          p[i] = keep ? exp2f(z - st_lse[i]) : 0.f;
+          for (int i = 0; i < 64; ++i)
+            p[i] = exp2f(__uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]) * sc2 - st_lse[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const float s = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
+            const int qpos = qbase + i + a.q_off;
+            float z;
+            if (a.softcap > 0.f) z = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
+            else z = s * sc2;
+            bool keep = key_valid && (qbase + i < a.Tq);
+            if (a.causal) keep = keep && (kp <= qpos);
+            if (a.window > 0) keep = keep && (kp > qpos - a.window);
+            if (a.seg_k) keep = keep && (st_seg[i] == my_seg);
+            p[i] = keep ? exp2f(z - st_lse[i]) : 0.f;
+          }
         }
       }
       {
-        uint8_t* prow = sptr + C_::OFF_PT + r * 128;
+        uint8_t* prow = sptr + C_::OFF_PT + pb * C_::P_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 v;
@@ -297,17 +392,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
         mbar_arrive(barPt);
       }
-      if (!mbar_wait_bounded(bardPt, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      if (PIPE && it >= 1) {
+        // drain dQt of the previous tile while the tensor core works on dV of this one
+        BWD_WAIT(bardQ, (it - 1) & 1, ST_TIMEOUT_EPILOGUE);
+        tc_fence_after();
+        drain_dq(it - 1);
+        tc_fence_before();
+        mbar_arrive(barDQfree);
+      }
+      BWD_WAIT(bardPt0 + 8 * sbuf(it), spar(it), ST_TIMEOUT_EPILOGUE);
       tc_fence_after();
       {
         uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_DPT, t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_DPT + 32, t1);
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_dpt(sbuf(it)), t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_dpt(sbuf(it)) + 32, t1);
         tmem_ld_wait();
         if (a.softcap > 0.f) {
           uint32_t s0[32], s1[32];
-          tmem_ld_32x32(tmem + lane_addr + C_::TM_ST, s0);
-          tmem_ld_32x32(tmem + lane_addr + C_::TM_ST + 32, s1);
+          tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)), s0);
+          tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + 32, s1);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 64; ++i) {
@@ -316,7 +419,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             p[i] *= (1.f - t * t);
           }
         }
-        uint8_t* drow = sptr + C_::OFF_DST + r * 128;
+        uint8_t* drow = sptr + C_::OFF_DST + pb * C_::P_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           float d[8];
@@ -337,34 +440,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_before();
         mbar_arrive(bardSt);
       }
-      // dQt tile: lane = head-dim index (within this CTA's half), column = query
-      if (!mbar_wait_bounded(bardQ, it & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_DQT, t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::TM_DQT + 32, t1);
-        tmem_ld_wait();
-        if (r < HO) {
-          float* dq = a.dQ + ((long long)b * a.Tq + qbase) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
-#pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            if (qbase + i < a.Tq) {
-              const float v = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
-              atomicAdd(dq + (long long)i * a.N * H, v);
-            }
-          }
-        }
+      if (!PIPE) {
+        BWD_WAIT(bardQ, it & 1, ST_TIMEOUT_EPILOGUE);
+        tc_fence_after();
+        drain_dq(it);
+        tc_fence_before();
       }
-      tc_fence_before();
       if (it + 1 < nit && r < 64) {
         stat_ptr((it + 1) & 1, 0)[r] = nx_lse;
         stat_ptr((it + 1) & 1, 1)[r] = nx_delta;
         reinterpret_cast<int*>(stat_ptr((it + 1) & 1, 2))[r] = nx_seg;
       }
     }
+    if (PIPE && nit > 0 && ok) {
+      // last tile's dQt; its completion also means every dV / dK MMA has retired
+      ok = mbar_wait_bounded(bardQ, (nit - 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE);
+      tc_fence_after();
+      if (ok) drain_dq(nit - 1);
+    }
+#undef BWD_WAIT
     // ------------------------------------------------------------- dK / dV
-    // All MMAs retired when the last bardQ phase completed (waited above).
     tc_fence_after();
     __nv_bfloat16* dkrow = a.dK + ((long long)b * a.Tk + kp) * a.lddk + (long long)kvh * H + half * HO;
     __nv_bfloat16* dvrow = a.dV + ((long long)b * a.Tk + kp) * a.lddv + (long long)kvh * H + half * HO;

@@ -202,19 +202,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float z[64];
       float mx = -INFINITY;
       const int* segk = a.seg_k ? a.seg_k + (long long)b * a.Tk + k0 : nullptr;
+      // most key blocks of a causal tile lie fully below the diagonal: skip the per-element mask there
+      const bool need_mask = (k0 + BKV > a.Tk) || (segk != nullptr) ||
+                             (a.causal && (k0 + BKV - 1 > q0 + a.q_off)) ||
+                             (a.window > 0 && (k0 <= q0 + BQ - 1 + a.q_off - a.window));
+      if (!need_mask && a.softcap <= 0.f) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int kp = k0 + i;
-        float s = __uint_as_float(sraw[i]);
-        if (a.softcap > 0.f) s = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
-        else s *= sc2;
-        bool keep = kp < a.Tk;
-        if (a.causal) keep = keep && (kp <= qpos);
-        if (a.window > 0) keep = keep && (kp > qpos - a.window);
-        if (segk) keep = keep && (kp < a.Tk) && (__ldg(segk + (kp < a.Tk ? i : 0)) == my_seg);
-        s = keep ? s : -INFINITY;
-        z[i] = s;
-        mx = fmaxf(mx, s);
+        for (int i = 0; i < 64; ++i) {
+          z[i] = __uint_as_float(sraw[i]) * sc2;
+          mx = fmaxf(mx, z[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int kp = k0 + i;
+          float s = __uint_as_float(sraw[i]);
+          if (a.softcap > 0.f) s = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
+          else s *= sc2;
+          bool keep = kp < a.Tk;
+          if (a.causal) keep = keep && (kp <= qpos);
+          if (a.window > 0) keep = keep && (kp > qpos - a.window);
+          if (segk) keep = keep && (kp < a.Tk) && (__ldg(segk + (kp < a.Tk ? i : 0)) == my_seg);
+          s = keep ? s : -INFINITY;
+          z[i] = s;
+          mx = fmaxf(mx, s);
+        }
       }
       float alpha = 1.f;
       bool need = false;
