@@ -1,0 +1,138 @@
+"""Kernel micro-benchmarks: `python -m tunix_b200.ops.bench_kernels <kernel> [--shape flags]`.
+
+Each run does warm-up launches, then times `--iters` launches with CUDA events on the launching stream,
+flushing L2 (a 256 MiB memset) between iterations, and prints one JSON line with the median time, the
+achieved TFLOP/s or GB/s and its fraction of the measured peak (MEASURED_PEAKS.json at the repository
+root when present, else the fallback 1590 TFLOP/s / 6650 GB/s). The same entry point is what the ncu
+captures in `profiles/` run (small shapes, few iterations).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters: int, warmup: int = 3, flush: bool = True):
+    for _ in range(warmup):
+        fn()
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    times = []
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "adamw", "logsoftmax", "sample",
+                                       "glu", "rs_pull"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--dim", type=int, default=4096)
+    ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+    from tunix_b200 import _lib
+    from tunix_b200.ops import kernels as K
+    peak_tf, peak_gb, src = _peaks()
+    dev = "cuda"
+    bf = torch.bfloat16
+    out = {"kernel": args.kernel, "peaks": src}
+    if args.kernel == "gemm":
+        M, N, Kd = args.m, args.n, args.k
+        A = torch.randn((Kd, M) if args.a_mn else (M, Kd), device=dev, dtype=bf)
+        B = torch.randn((Kd, N) if args.b_mn else (N, Kd), device=dev, dtype=bf)
+        C = torch.empty(M, N, device=dev, dtype=bf)
+        ms = _time(lambda: K.gemm(A, B, a_mn=args.a_mn, b_mn=args.b_mn, out=C), args.iters, args.warmup)
+        tf = 2.0 * M * N * Kd / ms / 1e9
+        out.update(shape=[M, N, Kd], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf)
+    elif args.kernel in ("attn_fwd", "attn_bwd"):
+        B_, T, N, KH, H = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+        q = torch.randn(B_, T, N, H, device=dev, dtype=bf)
+        k = torch.randn(B_, T, KH, H, device=dev, dtype=bf)
+        v = torch.randn_like(k)
+        sc = 1.0 / math.sqrt(H)
+        fl = 4.0 * B_ * N * T * T * H / 2
+        if args.kernel == "attn_fwd":
+            ms = _time(lambda: K.attn_fwd(q, k, v, scale=sc), args.iters, args.warmup)
+        else:
+            o, lse = K.attn_fwd(q, k, v, scale=sc)
+            do = torch.randn_like(q)
+            ms = _time(lambda: K.attn_bwd(do, q, k, v, o, lse, scale=sc), args.iters, args.warmup)
+            fl *= 2.5
+        tf = fl / ms / 1e9
+        out.update(shape=[B_, T, N, KH, H], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf)
+    elif args.kernel == "rmsnorm":
+        x = torch.randn(args.rows, args.dim, device=dev, dtype=bf)
+        w = torch.ones(args.dim, device=dev, dtype=bf)
+        ms = _time(lambda: K.rmsnorm_fwd(x, w, 1e-6), args.iters, args.warmup)
+        gb = 2.0 * x.numel() * 2 / ms / 1e6
+        out.update(shape=[args.rows, args.dim], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "glu":
+        g = torch.randn(args.rows, args.dim, device=dev, dtype=bf)
+        u = torch.randn_like(g)
+        ms = _time(lambda: K.glu_fwd(g, u, 0), args.iters, args.warmup)
+        gb = 3.0 * g.numel() * 2 / ms / 1e6
+        out.update(shape=[args.rows, args.dim], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "adamw":
+        n = args.numel
+        p32, m, v = (torch.zeros(n, device=dev) for _ in range(3))
+        g = torch.randn(n, device=dev, dtype=bf)
+        p16 = torch.empty(n, device=dev, dtype=bf)
+        ss = torch.ones(1, device=dev)
+        ms = _time(lambda: K.adamw(p32, m, v, g, p16, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0, step=3,
+                                   max_norm=1.0, sumsq_buf=ss), args.iters, args.warmup, flush=False)
+        gb = n * (3 * 4 * 2 + 2 + 2) / ms / 1e6
+        out.update(numel=n, ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "logsoftmax":
+        z = torch.randn(args.rows, args.vocab, device=dev)
+        tg = torch.randint(0, args.vocab, (args.rows,), device=dev, dtype=torch.int32)
+        ms = _time(lambda: K.logsoftmax_gather(z, tg), args.iters, args.warmup)
+        gb = z.numel() * 4 / ms / 1e6
+        out.update(shape=[args.rows, args.vocab], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "sample":
+        from tunix_b200.ops import sampling_kernels as S
+        z = torch.randn(args.rows, args.vocab, device=dev)
+        ms = _time(lambda: S.sample(z, 1.0, None, None, 1, 0, want_logprob=True), args.iters, args.warmup)
+        gb = 3.0 * z.numel() * 4 / ms / 1e6
+        out.update(shape=[args.rows, args.vocab], ms=ms, gbs_3pass=gb, frac_of_peak=gb / peak_gb)
+    _lib.raise_if_kernel_error()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
