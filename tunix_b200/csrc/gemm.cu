@@ -54,8 +54,9 @@ struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int TMEM_COLS = 2 * BN;  // two accumulator stages
+  // fill ~200 KiB of shared memory: deeper rings for the narrow tiles that stream weights at small M
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -417,10 +418,17 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
   const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
-  // Narrow outputs use the 128-wide tile so more CTAs stream the weights.
+  // Tile width: the widest N tile that still gives every SM work. Large problems use 128x256; skinny
+  // ones (decode: M <= 128) fall to 128x64 / 128x32 so that >= 100 CTAs stream the weight matrix.
   const int num_m = (M + BM - 1) / BM;
-  const bool bn256 = (N >= 256) && ((long long)num_m * ((N + 255) / 256) >= g_sm_count / 2);
-  const int BN = bn256 ? 256 : 128;
+  int BN = 32;
+  for (int cand : {256, 128, 64, 32}) {
+    if (cand > 128 && N < 256) continue;
+    if (cand < 64 && b_mn) continue;          // MN-major B is loaded in 64-wide swizzled boxes
+    BN = cand;
+    if ((long long)num_m * ((N + cand - 1) / cand) >= (g_sm_count * 3) / 5) break;
+  }
+  if (b_mn && BN < 64) BN = 64;
   CUtensorMap tmA, tmB;
   int r;
   if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
@@ -445,11 +453,17 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
                          Cfg<256>::SMEM_BYTES);
     cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          Cfg<128>::SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<64>::SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<32>::SMEM_BYTES);
     attr_set = true;
   }
-  if (bn256)
-    gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args);
-  else
-    gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  switch (BN) {
+    case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 64: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    default: gemm_bf16_kernel<32><<<ctas, 192, Cfg<32>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

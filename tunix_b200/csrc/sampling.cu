@@ -43,8 +43,9 @@ __device__ __forceinline__ ArgMax amax(ArgMax a, ArgMax b) { return (b.v > a.v |
 
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, float inv_temp, int top_k, float top_p,
-              unsigned long long seed, int step, int greedy, long long* __restrict__ tokens,
-              float* __restrict__ logprobs) {
+              unsigned long long seed, int step_host, const int* __restrict__ step_dev, int greedy,
+              long long* __restrict__ tokens, float* __restrict__ logprobs) {
+  const int step = step_dev ? *step_dev : step_host;  // device-resident step keeps the launch graph-capturable
   __shared__ float red[33];
   __shared__ float s_a[32];
   __shared__ int s_i[32];
@@ -145,10 +146,12 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, float inv_t
 // logits fp32 [B, V] (row stride ld). tokens int64 [B]; logprobs fp32 [B] or null.
 // temperature <= 0 selects greedy decoding. top_k <= 0 and top_p >= 1 disable the filters.
 TB_API int tb_sample(const float* logits, long long ld, int B, int V, float temperature, int top_k, float top_p,
-                     unsigned long long seed, int step, long long* tokens, float* logprobs, cudaStream_t stream) {
+                     unsigned long long seed, int step, const int* step_dev, long long* tokens, float* logprobs,
+                     cudaStream_t stream) {
   if (B <= 0) return 0;
   const int greedy = temperature <= 0.f;
   const float inv_temp = greedy ? 1.f : 1.f / temperature;
-  sample_kernel<<<B, 1024, 0, stream>>>(logits, ld, V, inv_temp, top_k, top_p, seed, step, greedy, tokens, logprobs);
+  sample_kernel<<<B, 1024, 0, stream>>>(logits, ld, V, inv_temp, top_k, top_p, seed, step, step_dev, greedy, tokens,
+                                        logprobs);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

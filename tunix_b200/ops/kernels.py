@@ -301,3 +301,44 @@ def attn_bwd(dout, q, k, v, o, lse, *, scale: float, causal: bool = True, window
     _lib.check(rc, "tb_cast_f32_bf16")
     _count(4)
     return dq, dk, dv
+
+
+_lib.register_cuda_sigs({
+    "tb_kv_write": [_lib.P, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P],
+    "tb_paged_decode": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I,
+                        _lib.I, _lib.I, _lib.F, _lib.F, _lib.I, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P],
+})
+
+DECODE_SPLIT_TOKENS = 256
+
+
+def kv_write(k_new, v_new, seq_ids, positions, page_table, page_size: int, k_pool, v_pool) -> None:
+    """Scatter rows k_new / v_new [n_tok, KH*H] into the paged pools [num_pages, page_size, KH*H].
+
+    seq_ids / positions int32 [n_tok] (position < 0 = padding, skipped); page_table int32 [slots, max_pages]."""
+    n_tok, row = k_new.shape
+    rc = _lib.cuda().tb_kv_write(k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), seq_ids.data_ptr(),
+                                 positions.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size,
+                                 k_pool.data_ptr(), v_pool.data_ptr(), n_tok, row, _lib.stream_ptr())
+    _lib.check(rc, "tb_kv_write")
+    _count()
+
+
+def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_heads: int, page_size: int, max_ctx: int,
+                 scale: float, softcap: float = 0.0, window: int = 0, workspace=None, out=None):
+    """Single-token attention over a paged KV cache. q [B, N, H] bf16 -> out [B, N, H] bf16."""
+    B, N, H = q.shape
+    splits = (max_ctx + DECODE_SPLIT_TOKENS - 1) // DECODE_SPLIT_TOKENS
+    if workspace is None:
+        workspace = (torch.empty(B * N * splits * H, dtype=torch.float32, device=q.device),
+                     torch.empty(B * N * splits * 2, dtype=torch.float32, device=q.device))
+    if out is None:
+        out = torch.empty_like(q)
+    rc = _lib.cuda().tb_paged_decode(q.data_ptr(), N * H, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
+                                     page_table.shape[1], page_size, seq_ids.data_ptr(), seq_lens.data_ptr(), B, N,
+                                     num_kv_heads, H, max_ctx, float(scale), float(softcap), int(window),
+                                     workspace[0].data_ptr(), workspace[1].data_ptr(), out.data_ptr(), N * H,
+                                     _lib.stream_ptr())
+    _lib.check(rc, "tb_paged_decode")
+    _count(2)
+    return out

@@ -11,7 +11,7 @@ from . import kernels as K
 
 _lib.register_cuda_sigs({
     "tb_sample": [_lib.P, _lib.LL, _lib.I, _lib.I, _lib.F, _lib.I, _lib.F, ctypes.c_ulonglong, _lib.I, _lib.P, _lib.P,
-                  _lib.P],
+                  _lib.P, _lib.P],
 })
 
 
@@ -21,7 +21,7 @@ def available() -> bool:
 
 def sample(logits: torch.Tensor, temperature: float, top_p: Optional[float], top_k: Optional[int], seed: int, step: int,
            want_logprob: bool = False, out_tokens: Optional[torch.Tensor] = None,
-           out_logprobs: Optional[torch.Tensor] = None):
+           out_logprobs: Optional[torch.Tensor] = None, step_tensor: Optional[torch.Tensor] = None):
     """logits fp32 [B, V] on CUDA -> (tokens int64 [B], logprobs fp32 [B] | None)."""
     assert logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
     B, V = logits.shape
@@ -30,7 +30,7 @@ def sample(logits: torch.Tensor, temperature: float, top_p: Optional[float], top
         torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None)
     rc = _lib.cuda().tb_sample(logits.data_ptr(), logits.stride(0), B, V, float(temperature or 0.0), int(top_k or 0),
                                float(top_p if top_p is not None else 1.0), int(seed) & 0xFFFFFFFFFFFFFFFF, int(step),
-                               tok.data_ptr(), _lib.ptr(lp), _lib.stream_ptr())
+                               _lib.ptr(step_tensor), tok.data_ptr(), _lib.ptr(lp), _lib.stream_ptr())
     _lib.check(rc, "tb_sample")
     K._count()
     return tok, lp
