@@ -1,0 +1,121 @@
+"""Agentic RL: tools, parsers, environments, queue, sync lock, trajectory engine, end-to-end learner (CPU)."""
+import asyncio
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from tunix_b200.rl.agentic.agents.agent_types import TrajectoryStatus
+from tunix_b200.rl.agentic.agents.model_agent import ModelAgent
+from tunix_b200.rl.agentic.agents.tool_agent import ToolAgent
+from tunix_b200.rl.agentic.environments.task_environment import TaskEnvironment
+from tunix_b200.rl.agentic.environments.tool_environment import ToolEnvironment
+from tunix_b200.rl.agentic.parser.chat_template_parser import get_parser
+from tunix_b200.rl.agentic.parser.tool_parser import GeminiToolParser, QwenToolParser
+from tunix_b200.rl.agentic.queue_manager.group_queue_manager import GroupQueueManager
+from tunix_b200.rl.agentic.tools.calculator_tool import CalculatorTool
+from tunix_b200.rl.agentic.tools.tool_manager import ToolManager
+from tunix_b200.rl.agentic.trajectory.trajectory_collect_engine import TrajectoryCollectEngine
+from tunix_b200.rl.agentic.utils import RolloutSyncLock
+from tests.test_sampler_cpu import CharTok
+
+
+def test_tools_and_parsers():
+    calc = CalculatorTool()
+    assert calc.apply(expression="2*(3+4)").output == 14
+    assert calc.apply(expression="__import__('os')").error
+    tm = ToolManager([calc])
+    out = tm.execute_calls([{"id": "a", "name": "calculator", "arguments": {"expression": "1+1"}},
+                            {"id": "b", "name": "nope", "arguments": {}}])
+    assert out["a"].output == 2 and out["b"].error
+    q = QwenToolParser().parse('x <tool_call>{"name": "calculator", "arguments": {"expression": "3*3"}}</tool_call>')
+    assert q == [{"name": "calculator", "arguments": {"expression": "3*3"}}]
+    g = GeminiToolParser().parse('```tool_code\n{"name": "f", "args": {"a": 1}}\n```')
+    assert g == [{"name": "f", "arguments": {"a": 1}}]
+    msgs = [{"role": "user", "content": "hi"}]
+    assert get_parser("qwen").parse(msgs, add_generation_prompt=True).endswith("<|im_start|>assistant\n")
+    assert get_parser("gemma").parse(msgs).startswith("<bos><start_of_turn>user")
+    assert "<|eot_id|>" in get_parser("llama").parse(msgs)
+
+
+def test_group_queue_and_sync_lock():
+    async def run():
+        q = GroupQueueManager(group_size=2)
+        await q.put("a0", "a")
+        await q.put("b0", "b")
+        await q.put("a1", "a")
+        got = await q.get_batch(1)
+        assert got == [["a0", "a1"]] and q.open_buckets == 1
+        await q.put_exception(ValueError("boom"))
+        with pytest.raises(ValueError):
+            await q.get_batch(1)
+    asyncio.run(run())
+    lock, order = RolloutSyncLock(), []
+
+    def rollout():
+        with lock.acquire_rollout():
+            order.append("r+")
+            time.sleep(0.05)
+            order.append("r-")
+    t = threading.Thread(target=rollout)
+    t.start()
+    time.sleep(0.01)
+    with lock.acquire_weight_sync():
+        order.append("sync")
+    t.join()
+    assert order == ["r+", "r-", "sync"]
+
+
+def test_multi_turn_tool_episode_records_tokens_and_masks():
+    tok = CharTok()
+    script = iter(['<tool_call>{"name": "calculator", "arguments": {"expression": "6*7"}}</tool_call>',
+                   '<tool_call>{"name": "finish", "arguments": {"response": "42"}}</tool_call>'])
+
+    async def model_call(chat_completions=None, prompt_token_ids=None, max_tokens=None):
+        text = next(script)
+        ids = tok.encode(text)
+        return {"text": text, "tokens": ids, "logprobs": [-0.5] * len(ids)}
+    env = ToolEnvironment(task={"question": "6*7?", "answer": "42"}, tools=[CalculatorTool()], reward_fn="exact_match", max_steps=4)
+    eng = TrajectoryCollectEngine(ToolAgent(tools={"calculator": CalculatorTool()}), env, model_call=model_call, tokenizer=tok,
+                                  chat_parser=get_parser("qwen"), max_steps=4)
+    out = asyncio.run(eng.collect("Token"))
+    assert out["status"] == TrajectoryStatus.SUCCEEDED and out["trajectory_reward"] == 1.0 and out["num_turns"] == 2
+    m = out["conversation_masks"]
+    assert m.sum() > 0 and (m == 0).sum() > 0                       # assistant and environment tokens both present
+    assert np.all(out["old_logprobs"][m == 1] == -0.5) and np.all(out["old_logprobs"][m == 0] == 0)
+
+
+def test_failed_episode_is_marked_not_raised():
+    async def model_call(**kw):
+        raise RuntimeError("engine down")
+    eng = TrajectoryCollectEngine(ModelAgent(), TaskEnvironment(task={"question": "q"}), model_call=model_call, tokenizer=CharTok())
+    traj = asyncio.run(eng.collect("Trajectory"))
+    assert traj.status == TrajectoryStatus.FAILED
+
+
+def test_agentic_grpo_learner_end_to_end():
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
+    from tunix_b200.rl.algorithm_config import GRPOConfig
+    from tunix_b200.rl.rl_cluster import RLCluster
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
+    actor, ref = create_model(cfg, seed=0), create_model(cfg, seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
+                          train_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=5, max_prompt_length=16, temperature=1.0, seed=1, kv_cache_size=64, eos_tokens=[63])
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(), cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    before = torch.cat([p.detach().reshape(-1).clone() for p in actor.parameters()])
+
+    def length_reward(prompts, completions, completion_lengths=None, **kw):
+        return [float(n % 3) for n in completion_lengths]
+    learner = AgenticGRPOLearner(cl, [length_reward], GRPOConfig(num_generations=2, beta=0.04), max_concurrency=4,
+                                 chat_parser=get_parser("raw"))
+    learner.train([{"prompts": ["ab", "cd"]}, {"prompts": ["ef", "gh"]}])
+    assert cl.global_steps == 2 and learner.policy_version == 2
+    after = torch.cat([p.detach().reshape(-1) for p in actor.parameters()])
+    assert cl.metrics_logger.metric_exists("", "trajectory/valid_frac", "train")
