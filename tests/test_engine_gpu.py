@@ -34,18 +34,22 @@ def _model(**kw):
     return create_model(ModelConfig(**base), device=torch.device("cuda"), seed=0)
 
 
-def test_paged_decode_kernel_matches_reference():
+@pytest.mark.parametrize("N,KH,H,window,softcap", [(8, 2, 128, 0, 0.0), (4, 4, 64, 0, 0.0), (16, 2, 256, 0, 30.0),
+                                                   (8, 1, 128, 100, 0.0), (32, 2, 128, 0, 0.0)])
+def test_paged_decode_kernel_matches_reference(N, KH, H, window, softcap):
     from tunix_b200.ops import kernels as K
     torch.manual_seed(0)
-    B, N, KH, H, page, max_pages = 5, 8, 2, 128, 16, 40
+    B, page, max_pages = 5, 16, 40
     lens = torch.tensor([1, 17, 300, 600, 255], device="cuda", dtype=torch.int32)
     num_pages = B * max_pages
     kp = torch.randn(num_pages, page, KH * H, device="cuda", dtype=torch.bfloat16)
     vp = torch.randn_like(kp)
     perm = torch.randperm(num_pages, device="cuda").int().view(B, max_pages)
-    q = torch.randn(B, N, H, device="cuda", dtype=torch.bfloat16)
+    big = torch.randn(B, N * H + 64, device="cuda", dtype=torch.bfloat16)      # q rows with a stride, as the engine passes them
+    q = big[:, :N * H].view(B, N, H)
     slots = torch.arange(B, device="cuda", dtype=torch.int32)
-    out = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640, scale=1 / math.sqrt(H))
+    out = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640, scale=1 / math.sqrt(H),
+                         window=window, softcap=softcap)
     for b in range(B):
         L = int(lens[b])
         idx = torch.arange(L, device="cuda")
@@ -55,8 +59,48 @@ def test_paged_decode_kernel_matches_reference():
         kk = k.repeat_interleave(N // KH, dim=1)
         vv = v.repeat_interleave(N // KH, dim=1)
         s = torch.einsum("nh,lnh->nl", q[b].float(), kk) / math.sqrt(H)
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if window:
+            s = s.masked_fill(idx[None] < L - window, float("-inf"))
         ref = torch.einsum("nl,lnh->nh", torch.softmax(s, -1), vv)
         assert torch.allclose(out[b].float(), ref, atol=2e-2, rtol=2e-2), b
+
+
+@pytest.mark.parametrize("H,qk_norm", [(128, True), (64, False), (256, True)])
+def test_qkv_post_matches_separate_kernels(H, qk_norm):
+    from tunix_b200.ops import kernels as K
+    torch.manual_seed(1)
+    n_tok, N, KH, page, max_pages = 7, 4, 2, 16, 8
+    qkv = torch.randn(n_tok, (N + 2 * KH) * H, device="cuda", dtype=torch.bfloat16)
+    ref = qkv.clone()
+    pos = torch.tensor([0, 5, 17, -1, 33, 100, 2], device="cuda", dtype=torch.int32)
+    slots = torch.arange(n_tok, device="cuda", dtype=torch.int32)
+    table = torch.randperm(n_tok * max_pages, device="cuda").int().view(n_tok, max_pages)
+    kp = torch.zeros(n_tok * max_pages, page, KH * H, device="cuda", dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    kp2, vp2 = kp.clone(), vp.clone()
+    qw = torch.randn(H, device="cuda", dtype=torch.bfloat16) if qk_norm else None
+    kw = torch.randn(H, device="cuda", dtype=torch.bfloat16) if qk_norm else None
+    inv = 1.0 / (10000.0 ** (torch.arange(0, H // 2, device="cuda").float() / (H // 2)))
+    ang = torch.arange(128, device="cuda").float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    K.qkv_post(qkv, slots, pos, qw, kw, 1e-6, False, cos, sin, table, page, kp, vp, N, KH, H)
+    q = ref[:, :N * H].reshape(n_tok * N, H)
+    k = ref[:, N * H:(N + KH) * H].reshape(n_tok * KH, H)
+    v = ref[:, (N + KH) * H:].contiguous()
+    if qk_norm:
+        q, _ = K.rmsnorm_fwd(q.contiguous(), qw, 1e-6, want_rstd=False)
+        k, _ = K.rmsnorm_fwd(k.contiguous(), kw, 1e-6, want_rstd=False)
+    q, k = q.reshape(n_tok, N, H).contiguous(), k.reshape(n_tok, KH, H).contiguous()
+    cpos = pos.clamp(min=0)
+    K.rope_(q, cpos, cos, sin)
+    K.rope_(k, cpos, cos, sin)
+    K.kv_write(k.view(n_tok, -1), v, slots, pos, table, page, kp2, vp2)
+    valid = pos >= 0
+    assert torch.allclose(qkv[:, :N * H].view(n_tok, N, H)[valid].float(), q[valid].float(), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(kp.float(), kp2.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(vp, vp2)
 
 
 @pytest.mark.parametrize("M,N,K_", [(8, 4096, 512), (64, 1024, 4096), (100, 12288, 256)])
@@ -70,6 +114,32 @@ def test_small_m_gemm_tiles(M, N, K_):
     _lib.raise_if_kernel_error()
     ref = A.float() @ B.float().t()
     assert ((out - ref).norm() / ref.norm()).item() < 2e-3
+
+
+@pytest.mark.parametrize("M,N,K_", [(64, 4096, 4096), (64, 4096, 12288), (200, 6144, 4096), (17, 1000, 2048), (256, 24576, 1024),
+                                    (300, 512, 8192)])
+def test_splitk_gemm_with_epilogue(M, N, K_):
+    """Skinny problems take the cluster split-K kernel; bias, residual, alpha, fp32 accumulate and ragged edges."""
+    from tunix_b200 import _lib
+    from tunix_b200.ops import kernels as K
+    torch.manual_seed(2)
+    A = torch.randn(M, K_, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K_, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    out = K.gemm(A, B, bias=bias, residual=res, alpha=0.5)
+    _lib.raise_if_kernel_error()
+    want = 0.5 * ref + bias.float() + res.float()
+    assert ((out.float() - want).norm() / want.norm()).item() < 6e-3
+    acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    K.gemm(A, B, out=acc, accumulate=True)
+    _lib.raise_if_kernel_error()
+    assert ((acc - (ref + 1)).norm() / (ref + 1).norm()).item() < 2e-3
+    strided = torch.zeros(M, N + 8, device="cuda", dtype=torch.bfloat16)
+    K.gemm(A, B, out=strided[:, 8:])
+    _lib.raise_if_kernel_error()
+    assert ((strided[:, 8:].float() - ref).norm() / ref.norm()).item() < 6e-3 and float(strided[:, :8].abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize("graph", [False, True])

@@ -62,7 +62,8 @@ def test_gemm_epilogues():
     _check_status()
 
 
-@pytest.mark.parametrize("rows,D,add_one", [(37, 256, False), (1024, 4096, False), (300, 3584, True), (4096, 128, False)])
+@pytest.mark.parametrize("rows,D,add_one", [(37, 256, False), (1024, 4096, False), (300, 3584, True), (4096, 128, False),
+                                             (64, 8192, False), (5, 1536, True)])
 def test_rmsnorm(rows, D, add_one):
     k = _k()
     torch.manual_seed(2)

@@ -3,10 +3,13 @@
 //  * kv_write      : scatter new K / V rows of a step (decode) or of a whole prompt (prefill) into the pages
 //                    named by the page table; sequence ids and positions are read from device memory, so
 //                    the launch is identical every step and can live in a CUDA graph.
+//  * qkv_post      : what sits between the fused q/k/v projection and attention in a decode step, in one
+//                    launch: per-head RMS norm of q and k (when the model has it), RoPE of q and k, q back in
+//                    place, k and v rows straight into their pages.
 //  * paged_decode  : single-query attention over a paged cache with GQA: one CTA per (sequence, kv head,
-//                    context split). A warp streams 4 keys per iteration (8 lanes per key, 16 head dims per
-//                    lane, 16-byte loads), keeps running max / sum per query head and accumulates P*V in
-//                    registers; partial results of the splits are merged by `paged_decode_combine`.
+//                    context split). The query heads of a kv head are the rows of a 16-row mma.sync tile, K / V
+//                    stream through a double-buffered cp.async stage and are read with ldmatrix; running
+//                    max / sum per query head, partial results of the splits merged by `paged_decode_combine`.
 //                    Sliding window and logit soft-cap supported. Memory-bound by construction: every K / V
 //                    byte of the sequence is read exactly once per kv head.
 //
@@ -19,7 +22,7 @@ using namespace tb;
 
 namespace {
 
-constexpr int MAX_G = 8;        // query heads per kv head handled by one CTA
+constexpr int MAX_G = 16;       // query heads per kv head handled by one CTA (rows of one mma tile)
 constexpr int SPLIT_TOKENS = 256;
 
 // k_new/v_new: [n_tok, KH*H] rows. seq_ids[n_tok] = row of page_table, pos[n_tok] = position in the sequence
@@ -44,122 +47,254 @@ __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ k_new, const _
   }
 }
 
-template <int H, int G>
+// qkv: [n_tok, (N + 2 KH) * H] rows (q heads, then k heads, then v heads). One warp per (token, head).
+template <int H>
+__global__ void __launch_bounds__(256)
+qkv_post_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, const int* __restrict__ seq_ids,
+                const int* __restrict__ pos, const __nv_bfloat16* __restrict__ qw,
+                const __nv_bfloat16* __restrict__ kw, float eps, float add_one, const float* __restrict__ cos_t,
+                const float* __restrict__ sin_t, const int* __restrict__ page_table, int max_pages, int page_size,
+                __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int n_tok, int N, int KH) {
+  constexpr int HALF = H / 2, E = H / 64;          // elements per lane in each half
+  const int heads = N + 2 * KH;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long long)n_tok * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = (int)(wid / heads), hh = (int)(wid - (long long)t * heads);
+  const int p = pos[t];
+  __nv_bfloat16* src = qkv + (long long)t * ld + (long long)hh * H;
+  __nv_bfloat16* dst = src;
+  if (hh >= N) {
+    if (p < 0) return;
+    const int page = page_table[(long long)seq_ids[t] * max_pages + p / page_size];
+    if (page < 0) return;
+    const bool is_k = hh < N + KH;
+    const int kvh = is_k ? hh - N : hh - N - KH;
+    dst = (is_k ? k_pool : v_pool) + ((long long)page * page_size + p % page_size) * ((long long)KH * H) + (long long)kvh * H;
+    if (!is_k) {
+      for (int c = lane * 8; c < H; c += 256)
+        *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+      return;
+    }
+  }
+  float a[E], b[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    a[e] = __bfloat162float(src[lane * E + e]);
+    b[e] = __bfloat162float(src[HALF + lane * E + e]);
+  }
+  const __nv_bfloat16* w = hh < N ? qw : kw;
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {   // rounded to bf16 like the stand-alone norm kernel, so both paths agree
+      a[e] = __bfloat162float(__float2bfloat16(a[e] * rstd * (__bfloat162float(w[lane * E + e]) + add_one)));
+      b[e] = __bfloat162float(__float2bfloat16(b[e] * rstd * (__bfloat162float(w[HALF + lane * E + e]) + add_one)));
+    }
+  }
+  const int pp = p < 0 ? 0 : p;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float c = cos_t[(long long)pp * HALF + lane * E + e], sn = sin_t[(long long)pp * HALF + lane * E + e];
+    dst[lane * E + e] = __float2bfloat16(a[e] * c - b[e] * sn);
+    dst[HALF + lane * E + e] = __float2bfloat16(b[e] * c + a[e] * sn);
+  }
+}
+
+// ---- tensor-core fragments (warp-level mma.sync: with at most 16 query rows per kv head there is no 64/128-row
+// tile to give to tcgen05, and the kernel is bound by the K/V stream, not by math) --------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int TILE_KEYS = 64;   // keys staged per pipeline stage; 16 per warp
+
+// byte offset of 16-byte chunk c of row r in a [rows, H] bf16 tile whose 128-byte groups are XOR-swizzled by row
+template <int H>
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)(r * (H * 2) + (((c & ~7) | ((c ^ r) & 7)) << 4));
+}
+
+// One CTA per (sequence, kv head, context split): the G (<= 16) query heads of the kv head are the 16 rows of the
+// A operand, a warp owns 16 keys of each 64-key stage, S = Q K^T and O += P V run on mma.sync with K / V staged by
+// cp.async (double buffered) and read with ldmatrix; every K / V byte is read once.
+template <int H>
 __global__ void __launch_bounds__(128)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        // [B, N*H]
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ page_table, int max_pages, int page_size,
-                    const int* __restrict__ seq_ids, const int* __restrict__ seq_lens, int KH, float scale,
+                    const int* __restrict__ seq_ids, const int* __restrict__ seq_lens, int KH, int G, float scale,
                     float softcap, int window, int num_splits, float* __restrict__ part_acc,  // [B, N, splits, H]
                     float* __restrict__ part_ml) {                                              // [B, N, splits, 2]
-  constexpr int DPL = H / 8;                     // head dims per lane (8 lanes share a key)
+  constexpr int CPR = H / 8;                       // 16-byte chunks per row
+  constexpr int TILE_BYTES = TILE_KEYS * H * 2;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(128) uint8_t q_s[16 * H * 2];
   const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane >> 3, l8 = lane & 7;      // which of the 4 keys of this warp iteration; lane within the key
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = KH * G;
   const int len = seq_lens[b];
-  int lo = split * SPLIT_TOKENS, hi = min(len, lo + SPLIT_TOKENS);
+  int lo = split * SPLIT_TOKENS;
+  const int hi = min(len, lo + SPLIT_TOKENS);
   if (window > 0) lo = max(lo, len - window);
   const int* pt = page_table + (long long)seq_ids[b] * max_pages;
-  const long long row = (long long)KH * H;
+  const long long row_elems = (long long)KH * H;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t q_base = smem_u32(q_s);
 
-  float qf[G][DPL];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + (long long)b * ldq + (long long)(kh * G + g) * H + l8 * DPL;
-#pragma unroll
-    for (int d = 0; d < DPL; d += 8) {
-      const uint4 u = *reinterpret_cast<const uint4*>(qp + d);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        qf[g][d + 2 * j] = bf16_lo(w[j]) * scale;
-        qf[g][d + 2 * j + 1] = bf16_hi(w[j]) * scale;
+  // queries -> shared (rows >= G are zero)
+  for (int idx = tid; idx < 16 * CPR; idx += 128) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (r < G) u = *reinterpret_cast<const uint4*>(q + (long long)b * ldq + (long long)(kh * G + r) * H + c * 8);
+    *reinterpret_cast<uint4*>(q_s + swz<H>(r, c)) = u;
+  }
+
+  const int t_first = split * SPLIT_TOKENS + ((max(lo - split * SPLIT_TOKENS, 0)) / TILE_KEYS) * TILE_KEYS;
+  const int n_tiles = hi > t_first ? (hi - t_first + TILE_KEYS - 1) / TILE_KEYS : 0;
+
+  auto issue = [&](int tile, int buf) {
+    const int t0 = t_first + tile * TILE_KEYS;
+    const uint32_t kb = smem_base + buf * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    for (int idx = tid; idx < TILE_KEYS * CPR; idx += 128) {
+      const int r = idx / CPR, c = idx - r * CPR;
+      const int t = t0 + r;
+      const bool ok = t >= lo && t < hi;
+      long long off = 0;
+      if (ok) {
+        const int page = pt[t / page_size];
+        off = ((long long)page * page_size + t % page_size) * row_elems + (long long)kh * H + c * 8;
       }
+      const uint32_t d = swz<H>(r, c);
+      cp_async16(kb + d, k_pool + off, ok ? 16 : 0);
+      cp_async16(vb + d, v_pool + off, ok ? 16 : 0);
     }
-  }
-  float m[G], l[G], acc[G][DPL];
+    cp_async_commit();
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[H / 8][4];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
+  for (int i = 0; i < H / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  if (n_tiles > 0) issue(0, 0);
+  const int li = lane >> 3, lr = lane & 7;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int buf = tile & 1;
+    if (tile + 1 < n_tiles) {
+      issue(tile + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t kb = smem_base + buf * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    const int kr0 = warp * 16;
+    const int tw = t_first + tile * TILE_KEYS + kr0;      // first key of this warp's slice
+    if (tw < hi) {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
-  }
-  for (int t0 = lo + warp * 4; t0 < hi; t0 += 16) {
-    const int t = t0 + sub;
-    const bool valid = t < hi;
-    float kf[DPL], vf[DPL];
-    if (valid) {
-      const int page = pt[t / page_size];
-      const long long off = ((long long)page * page_size + t % page_size) * row + (long long)kh * H + l8 * DPL;
+      for (int ks = 0; ks < H / 16; ++ks) {
+        uint32_t a[4], kf[4];
+        ldsm_x4(a, q_base + swz<H>((li & 1) * 8 + lr, ks * 2 + (li >> 1)));
+        ldsm_x4(kf, kb + swz<H>(kr0 + (li >> 1) * 8 + lr, ks * 2 + (li & 1)));
+        mma_16816(s[0], a, kf[0], kf[1]);
+        mma_16816(s[1], a, kf[2], kf[3]);
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int d = 0; d < DPL; d += 8) {
-        const uint4 ku = *reinterpret_cast<const uint4*>(k_pool + off + d);
-        const uint4 vu = *reinterpret_cast<const uint4*>(v_pool + off + d);
-        const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+      for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          kf[d + 2 * j] = bf16_lo(kw[j]);
-          kf[d + 2 * j + 1] = bf16_hi(kw[j]);
-          vf[d + 2 * j] = bf16_lo(vw[j]);
-          vf[d + 2 * j + 1] = bf16_hi(vw[j]);
+          const int t = tw + nb * 8 + 2 * (lane & 3) + (j & 1);
+          float v = s[nb][j] * scale;
+          if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+          if (t < lo || t >= hi) v = -INFINITY;
+          s[nb][j] = v;
+          if (j < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
         }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float c0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - mn0);
+      const float c1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mn1);
+      m0 = mn0;
+      m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        s[nb][0] = (s[nb][0] == -INFINITY) ? 0.f : __expf(s[nb][0] - mn0);
+        s[nb][1] = (s[nb][1] == -INFINITY) ? 0.f : __expf(s[nb][1] - mn0);
+        s[nb][2] = (s[nb][2] == -INFINITY) ? 0.f : __expf(s[nb][2] - mn1);
+        s[nb][3] = (s[nb][3] == -INFINITY) ? 0.f : __expf(s[nb][3] - mn1);
+        ps0 += s[nb][0] + s[nb][1];
+        ps1 += s[nb][2] + s[nb][3];
       }
-    } else {
+      l0 = l0 * c0 + ps0;
+      l1 = l1 * c1 + ps1;
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[0][0], s[0][1]);
+      pa[1] = pack_bf16(s[0][2], s[0][3]);
+      pa[2] = pack_bf16(s[1][0], s[1][1]);
+      pa[3] = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) kf[d] = vf[d] = 0.f;
+      for (int d2 = 0; d2 < H / 16; ++d2) {
+        uint32_t vf[4];
+        ldsm_x4_t(vf, vb + swz<H>(kr0 + (li & 1) * 8 + lr, d2 * 2 + (li >> 1)));
+        float* oa = o[2 * d2];
+        float* ob = o[2 * d2 + 1];
+        oa[0] *= c0; oa[1] *= c0; oa[2] *= c1; oa[3] *= c1;
+        ob[0] *= c0; ob[1] *= c0; ob[2] *= c1; ob[3] *= c1;
+        mma_16816(o[2 * d2], pa, vf[0], vf[1]);
+        mma_16816(o[2 * d2 + 1], pa, vf[2], vf[3]);
+      }
     }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.f;
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) s += qf[g][d] * kf[d];
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-      if (!valid) s = -INFINITY;
-      const float mn = fmaxf(m[g], s);
-      const float corr = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mn);
-      const float p = (s == -INFINITY) ? 0.f : __expf(s - mn);
-      l[g] = l[g] * corr + p;
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) acc[g][d] = acc[g][d] * corr + p * vf[d];
-      m[g] = mn;
-    }
+    __syncthreads();
   }
-  // merge the 4 key groups of the warp, then the 4 warps through shared memory
-  __shared__ float sm_m[4][MAX_G], sm_l[4][MAX_G];
-  __shared__ float sm_acc[4][MAX_G][H];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // merge the four warps' partial states through shared memory (the stage buffers are free now)
+  float* sm_acc = reinterpret_cast<float*>(smem);             // [4][16][H]
+  __shared__ float sm_m[4][16], sm_l[4][16];
+  const int r0 = lane >> 2, r1 = r0 + 8, cq = 2 * (lane & 3);
+  if ((lane & 3) == 0) {
+    sm_m[warp][r0] = m0; sm_l[warp][r0] = l0;
+    sm_m[warp][r1] = m1; sm_l[warp][r1] = l1;
+  }
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-#pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
-      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
-      const float lo_ = __shfl_xor_sync(0xffffffffu, l[g], o);
-      const float mn = fmaxf(m[g], mo);
-      const float ca = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mn);
-      const float cb = (mo == -INFINITY) ? 0.f : __expf(mo - mn);
-      l[g] = l[g] * ca + lo_ * cb;
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) {
-        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][d], o);
-        acc[g][d] = acc[g][d] * ca + ao * cb;
-      }
-      m[g] = mn;
-    }
-    if (sub == 0) {
-      if (l8 == 0) {
-        sm_m[warp][g] = m[g];
-        sm_l[warp][g] = l[g];
-      }
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) sm_acc[warp][g][l8 * DPL + d] = acc[g][d];
-    }
+  for (int db = 0; db < H / 8; ++db) {
+    float* a0 = sm_acc + ((warp * 16 + r0) * H + db * 8 + cq);
+    float* a1 = sm_acc + ((warp * 16 + r1) * H + db * 8 + cq);
+    a0[0] = o[db][0]; a0[1] = o[db][1];
+    a1[0] = o[db][2]; a1[1] = o[db][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * H; idx += blockDim.x) {
+  for (int idx = tid; idx < G * H; idx += 128) {
     const int g = idx / H, d = idx - g * H;
     float mm = -INFINITY;
 #pragma unroll
@@ -169,13 +304,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
     for (int w = 0; w < 4; ++w) {
       const float c = (sm_m[w][g] == -INFINITY) ? 0.f : __expf(sm_m[w][g] - mm);
       ll += sm_l[w][g] * c;
-      aa += sm_acc[w][g][d] * c;
+      aa += sm_acc[(w * 16 + g) * H + d] * c;
     }
-    const long long o = (((long long)b * N + kh * G + g) * num_splits + split);
-    part_acc[o * H + d] = aa;
+    const long long oidx = (((long long)b * N + kh * G + g) * num_splits + split);
+    part_acc[oidx * H + d] = aa;
     if (d == 0) {
-      part_ml[o * 2] = mm;
-      part_ml[o * 2 + 1] = ll;
+      part_ml[oidx * 2] = mm;
+      part_ml[oidx * 2 + 1] = ll;
     }
   }
 }
@@ -211,18 +346,16 @@ int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q,
                   const __nv_bfloat16* kp, const __nv_bfloat16* vp, const int* pt, int max_pages, int page_size,
                   const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap, int window, int splits,
                   float* pa, float* pml) {
-#define LAUNCH(GV)                                                                                              \
-  paged_decode_kernel<H, GV><<<grid, 128, 0, stream>>>(q, ldq, kp, vp, pt, max_pages, page_size, seq_ids,      \
-                                                       seq_lens, KH, scale, softcap, window, splits, pa, pml); \
-  return 0;
-  switch (G) {
-    case 1: LAUNCH(1)
-    case 2: LAUNCH(2)
-    case 4: LAUNCH(4)
-    case 8: LAUNCH(8)
-    default: return -2;
+  constexpr int SMEM = 2 * 2 * TILE_KEYS * H * 2;     // two stages of K and V
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(paged_decode_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return -5;
+    attr_set = true;
   }
-#undef LAUNCH
+  paged_decode_kernel<H><<<grid, 128, SMEM, stream>>>(q, ldq, kp, vp, pt, max_pages, page_size, seq_ids, seq_lens, KH,
+                                                      G, scale, softcap, window, splits, pa, pml);
+  return 0;
 }
 
 }  // namespace
@@ -241,6 +374,30 @@ TB_API int tb_kv_write(const void* k_new, const void* v_new, long long ld_new, c
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+// Fused decode-side epilogue of the q/k/v projection (see qkv_post_kernel). qw / kw null = no QK norm.
+TB_API int tb_qkv_post(void* qkv, long long ld, const int* seq_ids, const int* pos, const void* qw, const void* kw,
+                       float eps, float add_one, const float* cos_t, const float* sin_t, const int* page_table,
+                       int max_pages, int page_size, void* k_pool, void* v_pool, int n_tok, int N, int KH, int H,
+                       cudaStream_t stream) {
+  if (n_tok <= 0) return 0;
+  if (ld % 8) return -2;
+  const long long warps = (long long)n_tok * (N + 2 * KH);
+  const int grid = (int)((warps + 7) / 8);
+#define QP(HV)                                                                                                     \
+  qkv_post_kernel<HV><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, seq_ids, pos, (const __nv_bfloat16*)qw,   \
+                                                (const __nv_bfloat16*)kw, eps, add_one, cos_t, sin_t, page_table,  \
+                                                max_pages, page_size, (__nv_bfloat16*)k_pool,                      \
+                                                (__nv_bfloat16*)v_pool, n_tok, N, KH)
+  switch (H) {
+    case 64: QP(64); break;
+    case 128: QP(128); break;
+    case 256: QP(256); break;
+    default: return -2;
+  }
+#undef QP
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 // q [B, N*H]; pools [num_pages, page_size, KH*H]; page_table [*, max_pages]; seq_ids [B]; seq_lens [B];
 // workspace: part_acc fp32 [B*N*splits*H], part_ml fp32 [B*N*splits*2] with splits = ceil(max_ctx / 256).
 TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, const void* v_pool,
@@ -251,6 +408,7 @@ TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, con
   if (B <= 0) return 0;
   if (KH <= 0 || N % KH || (ldq % 8)) return -2;
   const int G = N / KH;
+  if (G > MAX_G) return -2;
   const int splits = (max_ctx + SPLIT_TOKENS - 1) / SPLIT_TOKENS;
   dim3 grid(B, KH, splits);
   int rc;

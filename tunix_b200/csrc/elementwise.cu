@@ -63,6 +63,44 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, long lon
   }
 }
 
+// Same, one CTA per row: with few rows (decode) the warp-per-row kernel is a handful of warps each walking a
+// whole row twice, and latency, not bandwidth, sets its time. The row is held in registers between the passes.
+template <int VPT>   // 8-element vectors per thread
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ y, long long ldy, float* __restrict__ rstd_out, int D, float eps,
+                       float add_one) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ldx;
+  float v[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c = (threadIdx.x + j * 128) * 8;
+    if (c < D) {
+      load8(xr + c, v[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[j][i] * v[j][i];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  __nv_bfloat16* yr = y + row * ldy;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c = (threadIdx.x + j * 128) * 8;
+    if (c < D) {
+      float g[8];
+      load8(w + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j][i] = v[j][i] * rstd * (g[i] + add_one);
+      store8(yr + c, v[j]);
+    }
+  }
+}
+
 // dx = rstd * (dy*w' - xhat * mean(dy*w'*xhat)), xhat = x*rstd, w' = w + add_one.
 // If accumulate != 0, dx += (used when the residual stream's gradient is folded in).
 __global__ void rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, long long lddy,
@@ -294,6 +332,15 @@ TB_API int tb_rmsnorm_fwd(const void* x, long long ldx, const void* w, void* y, 
                           cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D % 8) return -2;
+  if (rows <= 2048 && D >= 1024 && D <= 8192) {
+    auto xx = (const __nv_bfloat16*)x;
+    auto ww = (const __nv_bfloat16*)w;
+    auto yy = (__nv_bfloat16*)y;
+    if (D <= 2048) rmsnorm_fwd_row_kernel<2><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    else if (D <= 4096) rmsnorm_fwd_row_kernel<4><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    else rmsnorm_fwd_row_kernel<8><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  }
   const int block = 256;
   rmsnorm_fwd_kernel<<<grid_for((long long)rows * 32, block), block, 0, stream>>>(
       (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, ldy, rstd, rows, D,

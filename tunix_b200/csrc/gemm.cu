@@ -18,6 +18,7 @@
 #include <unordered_map>
 #include <cstring>
 #include <cstdio>
+#include <cstdlib>
 
 using namespace tb;
 
@@ -210,6 +211,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool has_bias = args.flags & GF_BIAS;
     const bool has_res = args.flags & GF_RESIDUAL;
     const float alpha = args.alpha;
+    const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;      // vector paths need aligned bases
+    const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mt, nt;
@@ -242,7 +245,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (has_res) {
             const __nv_bfloat16* rp = args.resid + (long long)row * args.ldr + col0;
-            if (full && (args.ldr % 8 == 0)) {
+            if (full && (args.ldr % 8 == 0) && r_al16) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 uint4 u = reinterpret_cast<const uint4*>(rp)[g];
@@ -260,7 +263,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (out_f32) {
             float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col0;
-            if (full && (args.ldc % 4 == 0)) {
+            if (full && (args.ldc % 4 == 0) && c_al16) {
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 float4 o = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
@@ -277,7 +280,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* cp =
                 reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col0;
-            if (full && (args.ldc % 8 == 0)) {
+            if (full && (args.ldc % 8 == 0) && c_al16) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 if (accum) {
@@ -351,6 +354,10 @@ int g_sm_count = 0;
 
 }  // namespace
 
+int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                       int* status, cudaStream_t stream);
+
 tb_encode_tiled_fn tb_get_encode_tiled() {
   static tb_encode_tiled_fn fn = nullptr;
   static std::once_flag once;
@@ -418,6 +425,12 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
   const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  static const bool no_splitk = getenv("TUNIX_B200_NO_SPLITK") != nullptr;
+  if (max_ctas <= 0 && !no_splitk) {
+    // skinny problems: 128x256 tiles with the K range split over a cluster (gemm_splitk.cu)
+    const int sk = tb_gemm_splitk_try(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream);
+    if (sk != 0) return sk < 0 ? sk : 0;
+  }
   // Tile width: the widest N tile that still gives every SM work. Large problems use 128x256; skinny
   // ones (decode: M <= 128) fall to 128x64 / 128x32 so that >= 100 CTAs stream the weight matrix.
   const int num_m = (M + BM - 1) / BM;

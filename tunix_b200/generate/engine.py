@@ -130,6 +130,47 @@ class PagedEngine(BaseSampler):
                                  self.dtype)
 
     # ---------------------------------------------------------------- the model
+    @staticmethod
+    def _fused_weight(mods):
+        """One [sum(out_i), in] view over the weights of `mods`, so that projections sharing an input run as a
+        single GEMM. Weights already back to back in one storage (the optimizer's flat buffer lays q/k/v and
+        gate/up out that way) are viewed in place; weights that own their storage are moved, once, into a joint
+        tensor and stay views of it. Anything else (bias, LoRA, quantised base, foreign layout) returns None and
+        the caller runs the projections one by one."""
+        if any(m.quant is not None or m.bias is not None or (m.lora_a is not None and m.lora_enabled) for m in mods):
+            return None
+        ws = [m.weight for m in mods]
+        cols = ws[0].shape[1]
+        if any(w.shape[1] != cols or not w.is_contiguous() for w in ws):
+            return None
+        rows = sum(w.shape[0] for w in ws)
+        base = ws[0].data
+        off, adjacent = base.storage_offset(), True
+        for w in ws:
+            if w.untyped_storage().data_ptr() != base.untyped_storage().data_ptr() or w.storage_offset() != off:
+                adjacent = False
+                break
+            off += w.numel()
+        if adjacent:
+            return base.as_strided((rows, cols), (cols, 1), base.storage_offset())
+        esz = base.element_size()
+        if any(w.untyped_storage().nbytes() != w.numel() * esz for w in ws):
+            return None     # views of someone else's buffer: leave them where they are
+        joint = torch.empty((rows, cols), dtype=base.dtype, device=base.device)
+        r = 0
+        for w in ws:
+            joint[r:r + w.shape[0]].copy_(w.data)
+            w.data = joint[r:r + w.shape[0]]
+            r += w.shape[0]
+        return joint
+
+    def _fuse_all(self):
+        self._wqkv, self._wgu = [], []
+        for layer in self._model.layers:
+            at = layer.self_attn
+            self._wqkv.append(self._fused_weight([at.q_proj, at.k_proj, at.v_proj]))
+            self._wgu.append(self._fused_weight([layer.mlp.gate_proj, layer.mlp.up_proj]))
+
     def _rope(self, i):
         return self._model._rope(self.cfg.layer_type(i) == "local", self.device)
 
@@ -160,14 +201,23 @@ class PagedEngine(BaseSampler):
     def _lin(self, mod, x, residual=None):
         return mod(x, residual=residual)   # Linear.forward handles LoRA; no autograd under no_grad
 
-    def _mlp_and_norms(self, layer, x, attn_out):
+    def _mlp(self, layer, i, h, residual=None):
+        wgu = self._wgu[i]
+        if wgu is None:
+            return layer.mlp(h, residual=residual)
+        Fd = wgu.shape[0] // 2
+        gu = F.linear(h.reshape(-1, h.shape[-1]), wgu)
+        a = K.glu_fwd(gu[:, :Fd], gu[:, Fd:], K.GLU_SILU if layer.mlp.kind == "silu" else K.GLU_GELU)
+        return layer.mlp.down_proj(a.view(*h.shape[:-1], Fd), residual=residual)
+
+    def _mlp_and_norms(self, layer, i, x, attn_out):
         cfg = self.cfg
         if cfg.post_norms:
             x = x + layer.post_attn_norm(attn_out)
-            m = layer.mlp(layer.post_attention_layernorm(x))
+            m = self._mlp(layer, i, layer.post_attention_layernorm(x))
             return x + layer.post_ffw_norm(m)
         x = attn_out          # o_proj already added the residual
-        return layer.mlp(layer.post_attention_layernorm(x), residual=x)
+        return self._mlp(layer, i, layer.post_attention_layernorm(x), residual=x)
 
     def _prefill(self, toks, positions, seg, slots):
         """toks [B,P] left padded. Writes K/V pages, returns hidden state of the last position [B, D]."""
@@ -187,7 +237,7 @@ class PagedEngine(BaseSampler):
                             softcap=cfg.attn_logit_softcap, seg_q=seg, seg_k=seg)
             o = o.reshape(B, P, -1)
             a = at.o_proj(o, residual=None if cfg.post_norms else x)
-            x = self._mlp_and_norms(layer, x, a)
+            x = self._mlp_and_norms(layer, i, x, a)
         return self._model.norm(x[:, -1])
 
     def _decode_step(self, st) -> None:
@@ -200,14 +250,23 @@ class PagedEngine(BaseSampler):
         lens = st["seq_lens"]           # length including that token
         for i, layer in enumerate(self._model.layers):
             h = layer.input_layernorm(x)
-            q, k, v = self._attn_in(layer, h, pos, i)
-            K.kv_write(k.view(B, -1), v, st["slots"], pos, pool.table, pool.page_size, pool.k[i], pool.v[i])
             at = layer.self_attn
+            if self._wqkv[i] is not None:
+                qkv = F.linear(h, self._wqkv[i])
+                cos, sin = self._rope(i)
+                qn, kn = (at.q_norm, at.k_norm) if cfg.qk_norm else (None, None)
+                K.qkv_post(qkv, st["slots"], pos, qn.weight if qn is not None else None,
+                           kn.weight if kn is not None else None, cfg.norm_eps, cfg.norm_add_one, cos, sin, pool.table,
+                           pool.page_size, pool.k[i], pool.v[i], N, KH, H)
+                q = qkv[:, :N * H].view(B, N, H)
+            else:
+                q, k, v = self._attn_in(layer, h, pos, i)
+                K.kv_write(k.view(B, -1), v, st["slots"], pos, pool.table, pool.page_size, pool.k[i], pool.v[i])
             o = K.paged_decode(q, pool.k[i], pool.v[i], pool.table, st["slots"], lens, num_kv_heads=KH,
                                page_size=pool.page_size, max_ctx=self.cache_size, scale=at.scale,
                                softcap=cfg.attn_logit_softcap, window=at.window, workspace=st["ws"])
             a = at.o_proj(o.view(B, N * H), residual=None if cfg.post_norms else x)
-            x = self._mlp_and_norms(layer, x, a)
+            x = self._mlp_and_norms(layer, i, x, a)
         hlast = self._model.norm(x)
         self._sample_into(hlast, st, advance=True)
 
@@ -287,6 +346,7 @@ class PagedEngine(BaseSampler):
         dev = self.device
         B, P = toks_np.shape
         self._ensure_pool(B)
+        self._fuse_all()
         pool = self.pool
         for s in range(B):
             pool.release(s)

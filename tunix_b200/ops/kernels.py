@@ -307,6 +307,8 @@ _lib.register_cuda_sigs({
     "tb_kv_write": [_lib.P, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P],
     "tb_paged_decode": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I,
                         _lib.I, _lib.I, _lib.F, _lib.F, _lib.I, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P],
+    "tb_qkv_post": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P, _lib.I,
+                    _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P],
 })
 
 DECODE_SPLIT_TOKENS = 256
@@ -324,17 +326,34 @@ def kv_write(k_new, v_new, seq_ids, positions, page_table, page_size: int, k_poo
     _count()
 
 
+def qkv_post(qkv, seq_ids, positions, q_norm_w, k_norm_w, eps: float, add_one: bool, cos, sin, page_table,
+             page_size: int, k_pool, v_pool, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Fused epilogue of the decode-step q/k/v projection: per-head RMS norm of q and k (weights None = no norm),
+    RoPE of q and k, q rewritten in place in `qkv` [n_tok, (N + 2 KH) * H], k and v rows written to their pages."""
+    n_tok = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim
+    assert cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2 and positions.dtype == torch.int32
+    rc = _lib.cuda().tb_qkv_post(qkv.data_ptr(), qkv.stride(0), seq_ids.data_ptr(), positions.data_ptr(),
+                                 _lib.ptr(q_norm_w), _lib.ptr(k_norm_w), float(eps), 1.0 if add_one else 0.0,
+                                 cos.data_ptr(), sin.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size,
+                                 k_pool.data_ptr(), v_pool.data_ptr(), n_tok, num_heads, num_kv_heads, head_dim,
+                                 _lib.stream_ptr())
+    _lib.check(rc, "tb_qkv_post")
+    _count()
+
+
 def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_heads: int, page_size: int, max_ctx: int,
                  scale: float, softcap: float = 0.0, window: int = 0, workspace=None, out=None):
-    """Single-token attention over a paged KV cache. q [B, N, H] bf16 -> out [B, N, H] bf16."""
+    """Single-token attention over a paged KV cache. q [B, N, H] bf16 (row stride free) -> out [B, N, H] bf16."""
     B, N, H = q.shape
+    assert q.stride(2) == 1 and q.stride(1) == H
     splits = (max_ctx + DECODE_SPLIT_TOKENS - 1) // DECODE_SPLIT_TOKENS
     if workspace is None:
         workspace = (torch.empty(B * N * splits * H, dtype=torch.float32, device=q.device),
                      torch.empty(B * N * splits * 2, dtype=torch.float32, device=q.device))
     if out is None:
-        out = torch.empty_like(q)
-    rc = _lib.cuda().tb_paged_decode(q.data_ptr(), N * H, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
+        out = torch.empty((B, N, H), dtype=q.dtype, device=q.device)
+    rc = _lib.cuda().tb_paged_decode(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
                                      page_table.shape[1], page_size, seq_ids.data_ptr(), seq_lens.data_ptr(), B, N,
                                      num_kv_heads, H, max_ctx, float(scale), float(softcap), int(window),
                                      workspace[0].data_ptr(), workspace[1].data_ptr(), out.data_ptr(), N * H,
