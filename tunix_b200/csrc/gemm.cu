@@ -38,9 +38,23 @@ enum GemmFlags : int {
   GF_RESIDUAL = 32,    // + R[M,N] (bf16, row stride ldr)
 };
 
+// Grouped mode (mixture-of-experts): the tile list lives in device memory, built by a planning kernel from
+// per-expert token counts that the host never sees. A tile names its output block, its k-block range, a row
+// offset into B (the expert's slice of the stacked weights) and an element offset into C (the expert's slice of
+// a stacked weight gradient).
+struct TileDesc {
+  int m0, n0;          // output block origin
+  int m_end;           // rows >= m_end are not written
+  int kb0, kb1;        // k-block range [kb0, kb1)
+  int b_row0;          // added to the row coordinate of every B load
+  long long c_off;     // added (in elements) to C
+};
+
 struct GemmArgs {
   int M, N, K;
   int flags;
+  const TileDesc* tiles;      // null = dense problem
+  const int* num_tiles_dev;
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
@@ -112,14 +126,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  auto tile_coords = [&](int t, int& mt, int& nt) {
+  const bool grouped = args.tiles != nullptr;
+  const int total_tiles = grouped ? *args.num_tiles_dev : num_tiles;
+  auto tile_info = [&](int t) -> TileDesc {
+    if (grouped) return args.tiles[t];
     const int per_group = GROUP_M * num_n;
     const int g = t / per_group;
     const int first_m = g * GROUP_M;
     const int gsz = min(GROUP_M, num_m - first_m);
     const int r = t - g * per_group;
-    mt = first_m + (r % gsz);
-    nt = r / gsz;
+    TileDesc d;
+    d.m0 = (first_m + (r % gsz)) * BM;
+    d.n0 = (r / gsz) * BN;
+    d.m_end = M;
+    d.kb0 = 0;
+    d.kb1 = num_kb;
+    d.b_row0 = 0;
+    d.c_off = 0;
+    return d;
   };
 
   if (warp == 0) {
@@ -128,11 +152,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int mt, nt;
-        tile_coords(t, mt, nt);
-        const int m0 = mt * BM, n0 = nt * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileDesc td = tile_info(t);
+        const int m0 = td.m0, n0 = td.n0;
+        for (int kb = td.kb0; kb < td.kb1; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, args.status,
                                  ST_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -150,11 +173,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(sa + j * 8192, &tmA, full_bar(stage), m0 + 64 * j, k0);
           }
           if (!b_mn) {
-            tma_load_2d(sb, &tmB, full_bar(stage), k0, n0);
+            tma_load_2d(sb, &tmB, full_bar(stage), k0, n0 + td.b_row0);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * 8192, &tmB, full_bar(stage), n0 + 64 * j, k0);
+              tma_load_2d(sb + j * 8192, &tmB, full_bar(stage), n0 + 64 * j, k0 + td.b_row0);
           }
           if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -171,7 +194,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int kb0 = 0, kb1 = num_kb;
+        if (grouped) {
+          kb0 = args.tiles[t].kb0;
+          kb1 = args.tiles[t].kb1;
+          if (kb1 <= kb0) continue;                 // empty contraction: the epilogue writes zeros on its own
+        }
         if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag, args.status,
                                ST_TIMEOUT_MMA)) {
           ok = false;
@@ -179,7 +208,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -191,7 +220,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bd = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-            umma_f16_ss(tmem_d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // frees the smem slot when these MMAs retire
           if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
@@ -214,13 +243,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;      // vector paths need aligned bases
     const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int mt, nt;
-      tile_coords(t, mt, nt);
-      const int row = mt * BM + q * 32 + lane;
-      const int n0 = nt * BN;
-      if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status,
-                             ST_TIMEOUT_EPILOGUE)) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileDesc td = tile_info(t);
+      const int row = td.m0 + q * 32 + lane;
+      const int n0 = td.n0;
+      const int M = td.m_end;                       // shadows the problem's M: rows of this tile that exist
+      const long long c_off = td.c_off;
+      const bool empty_k = td.kb1 <= td.kb0;        // nothing was accumulated: the tile's value is zero
+      if (!empty_k && !mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status,
+                                         ST_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
       }
@@ -231,8 +262,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col0 = n0 + c * 32;
         if (col0 >= N) break;  // warp-uniform
         uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
+        if (!empty_k) {
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
         if (row < M) {
           float v[32];
 #pragma unroll
@@ -262,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
           if (out_f32) {
-            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col0;
+            float* cp = reinterpret_cast<float*>(args.C) + c_off + (long long)row * args.ldc + col0;
             if (full && (args.ldc % 4 == 0) && c_al16) {
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
@@ -279,7 +315,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           } else {
             __nv_bfloat16* cp =
-                reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col0;
+                reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + (long long)row * args.ldc + col0;
             if (full && (args.ldc % 8 == 0) && c_al16) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
@@ -311,6 +347,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
+      if (empty_k) continue;                        // the MMA warp skipped this tile too: no accumulator used
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -351,6 +388,7 @@ struct TmapKeyHash {
 std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
 int g_sm_count = 0;
+void set_gemm_attrs();
 
 }  // namespace
 
@@ -456,10 +494,65 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   args.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   args.ldr = ldr; args.alpha = alpha; args.status = status;
+  args.tiles = nullptr; args.num_tiles_dev = nullptr;
   const int tiles = num_m * ((N + BN - 1) / BN);
   int ctas = g_sm_count;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
+  set_gemm_attrs();
+  switch (BN) {
+    case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 64: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    default: gemm_bf16_kernel<32><<<ctas, 192, Cfg<32>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Grouped GEMM over a device-resident tile list (see TileDesc). The arrays are described by their full
+// extents: A is [a_rows, a_cols], B is [b_rows, b_cols] (row-major, leading strides lda / ldb); which of the
+// two dimensions is contracted follows from the MN-major flags exactly as in tb_gemm_bf16. N is the column
+// limit of one group's output, `bn` the tile width the list was planned for (256, 128 or 64).
+TB_API int tb_gemm_grouped_bf16(const void* A, long long a_rows, long long a_cols, long long lda, const void* B,
+                                long long b_rows, long long b_cols, long long ldb, void* C, long long ldc, int N,
+                                int flags, int bn, const void* tiles, const int* num_tiles_dev, int max_tiles,
+                                float alpha, int* status, cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  if (bn != 256 && bn != 128 && bn != 64) return -2;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, a_rows, a_cols, lda, BM, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmA, A, a_rows, a_cols, lda, BK, 64, 1);
+  if (r) return -3;
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, b_rows, b_cols, ldb, bn, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmB, B, b_rows, b_cols, ldb, BK, 64, 1);
+  if (r) return -4;
+  GemmArgs args;
+  args.M = 0; args.N = N; args.K = 0; args.flags = flags;
+  args.C = C; args.ldc = ldc; args.bias = nullptr; args.resid = nullptr; args.ldr = 0;
+  args.alpha = alpha; args.status = status;
+  args.tiles = reinterpret_cast<const TileDesc*>(tiles);
+  args.num_tiles_dev = num_tiles_dev;
+  const int ctas = max_tiles < g_sm_count ? max_tiles : g_sm_count;
+  set_gemm_attrs();
+  switch (bn) {
+    case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    default: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+namespace {
+void set_gemm_attrs() {
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -472,11 +565,5 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
                          Cfg<32>::SMEM_BYTES);
     attr_set = true;
   }
-  switch (BN) {
-    case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    case 64: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    default: gemm_bf16_kernel<32><<<ctas, 192, Cfg<32>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+}  // namespace

@@ -178,7 +178,7 @@ class MoELayer(nn.Module):
             frac = frac / max(idx.numel(), 1)
             self.last_aux_loss = cfg.router_aux_loss_coef * E * (frac * probs.mean(0)).sum()
         from ..parallel import moe_dispatch
-        y = moe_dispatch.expert_forward(self, xt, w.to(x.dtype), idx)
+        y = moe_dispatch.expert_forward(self, xt, w, idx)
         y = y.view(B, T, D)
         return y if residual is None else y + residual
 

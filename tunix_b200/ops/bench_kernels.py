@@ -47,7 +47,7 @@ def _time(fn, iters: int, warmup: int = 3, flush: bool = True):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "adamw", "logsoftmax", "sample",
-                                       "glu", "rs_pull"])
+                                       "glu", "moe"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -62,6 +62,9 @@ def main(argv=None) -> int:
     ap.add_argument("--dim", type=int, default=4096)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--ffn", type=int, default=768)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
@@ -129,6 +132,24 @@ def main(argv=None) -> int:
         ms = _time(lambda: S.sample(z, 1.0, None, None, 1, 0, want_logprob=True), args.iters, args.warmup)
         gb = 3.0 * z.numel() * 4 / ms / 1e6
         out.update(shape=[args.rows, args.vocab], ms=ms, gbs_3pass=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "moe":
+        from tunix_b200.ops import moe
+        T, E, k, D, Fd = args.rows, args.experts, args.topk, args.dim, args.ffn
+        x = (torch.randn(T, D, device=dev) * 0.5).to(bf).requires_grad_()
+        ws = [(torch.randn(E, Fd, D, device=dev) * 0.02).to(bf).requires_grad_() for _ in range(2)]
+        ws.append((torch.randn(E, D, Fd, device=dev) * 0.02).to(bf).requires_grad_())
+        for w in ws:
+            w.main_grad = torch.zeros(w.shape, dtype=torch.float32, device=dev)
+        wt, idx = torch.topk(torch.softmax(torch.randn(T, E, device=dev), -1), k, -1)
+        dout = torch.randn(T, D, device=dev).to(bf)
+        ms_f = _time(lambda: moe.experts(x, wt, idx, *ws), args.iters, args.warmup)
+
+        def fb():
+            moe.experts(x, wt, idx, *ws).backward(dout)
+        ms = _time(fb, args.iters, args.warmup)
+        fl_f = 2.0 * T * k * D * Fd * 3
+        out.update(shape=[T, E, k, D, Fd], fwd_ms=ms_f, fwd_bwd_ms=ms, fwd_tflops=fl_f / ms_f / 1e9,
+                   fwd_bwd_tflops=3 * fl_f / ms / 1e9, frac_of_peak=3 * fl_f / ms / 1e9 / peak_tf)
     _lib.raise_if_kernel_error()
     print(json.dumps(out))
     return 0

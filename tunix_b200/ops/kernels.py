@@ -361,3 +361,115 @@ def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_hea
     _lib.check(rc, "tb_paged_decode")
     _count(2)
     return out
+
+
+# ------------------------------------------------------------------ mixture of experts
+_lib.register_cuda_sigs({
+    "tb_gemm_grouped_bf16": [_lib.P, _lib.LL, _lib.LL, _lib.LL, _lib.P, _lib.LL, _lib.LL, _lib.LL, _lib.P, _lib.LL, _lib.I,
+                             _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.F, _lib.P, _lib.P],
+    "tb_moe_zero_pad": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P],
+    "tb_moe_scatter_rows": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.LL, _lib.I, _lib.I, _lib.P],
+    "tb_moe_gather_sum": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.LL, _lib.LL, _lib.I, _lib.I, _lib.P],
+    "tb_moe_dot_rows": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.P],
+    "tb_moe_tiles_rows": [_lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P],
+    "tb_moe_tiles_expert": [_lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.LL, _lib.P, _lib.P, _lib.P],
+})
+
+TILE_DESC_BYTES = 32
+
+
+class TileList:
+    """Device-resident tile list of a grouped GEMM: descriptors, their count (device int32) and a host bound."""
+
+    def __init__(self, max_tiles: int, bn: int, device):
+        self.desc = torch.empty(max(max_tiles, 1) * TILE_DESC_BYTES, dtype=torch.uint8, device=device)
+        self.count = torch.zeros(1, dtype=torch.int32, device=device)
+        self.max_tiles, self.bn = max_tiles, bn
+
+
+def _grouped_bn(n: int) -> int:
+    return 256 if n >= 256 else (128 if n >= 128 else 64)
+
+
+def moe_tiles_rows(seg_off: torch.Tensor, max_rows: int, n_out: int, k_contract: int, b_rows_per_expert: int) -> TileList:
+    """Tiles of a GEMM whose output rows are the permuted token rows: [max_rows, n_out] with the contraction
+    (k_contract, a multiple of 64) over the feature dimension and B = the stacked expert weights."""
+    assert k_contract % 64 == 0
+    E = seg_off.numel() - 1
+    bn = _grouped_bn(n_out)
+    num_n = (n_out + bn - 1) // bn
+    tl = TileList((max_rows // 128) * num_n, bn, seg_off.device)
+    rc = _lib.cuda().tb_moe_tiles_rows(seg_off.data_ptr(), E, num_n, bn, k_contract // 64, b_rows_per_expert,
+                                       tl.desc.data_ptr(), tl.count.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_tiles_rows")
+    _count()
+    return tl
+
+
+def moe_tiles_expert(seg_off: torch.Tensor, m_out: int, n_out: int) -> TileList:
+    """Tiles of a GEMM with one [m_out, n_out] output per expert, contracted over the expert's row segment."""
+    E = seg_off.numel() - 1
+    bn = _grouped_bn(n_out)
+    tl = TileList(E * ((m_out + 127) // 128) * ((n_out + bn - 1) // bn), bn, seg_off.device)
+    rc = _lib.cuda().tb_moe_tiles_expert(seg_off.data_ptr(), E, m_out, n_out, bn, m_out * n_out, tl.desc.data_ptr(),
+                                         tl.count.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_tiles_expert")
+    _count()
+    return tl
+
+
+def gemm_grouped(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, n_limit: int, tiles: TileList, *,
+                 a_mn: bool = False, b_mn: bool = False, accumulate: bool = False) -> torch.Tensor:
+    """Grouped GEMM over `tiles`. a, b: 2-D row-major arrays (b = stacked expert matrices viewed 2-D); which
+    dimension is contracted follows a_mn / b_mn as in `gemm`. out: bf16 or fp32, 2-D (per-expert outputs are
+    addressed through the tile's element offset). n_limit: number of valid output columns per group."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and _is2d_rowmajor(a) and _is2d_rowmajor(b)
+    flags = (GF_A_MN if a_mn else 0) | (GF_B_MN if b_mn else 0) | (GF_OUT_F32 if out.dtype == torch.float32 else 0) | \
+        (GF_ACCUM if accumulate else 0)
+    rc = _lib.cuda().tb_gemm_grouped_bf16(a.data_ptr(), a.shape[0], a.shape[1], a.stride(0), b.data_ptr(), b.shape[0],
+                                          b.shape[1], b.stride(0), out.data_ptr(), out.stride(-2), n_limit, flags,
+                                          tiles.bn, tiles.desc.data_ptr(), tiles.count.data_ptr(), tiles.max_tiles, 1.0,
+                                          _lib.status_buffer().data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_gemm_grouped_bf16")
+    _count()
+    return out
+
+
+def moe_zero_pad(buf: torch.Tensor, seg_off: torch.Tensor, counts: torch.Tensor) -> None:
+    rc = _lib.cuda().tb_moe_zero_pad(buf.data_ptr(), buf.stride(0), seg_off.data_ptr(), counts.data_ptr(),
+                                     counts.numel(), buf.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_zero_pad")
+    _count()
+
+
+def moe_scatter_rows(src: torch.Tensor, pos: torch.Tensor, scale, dst: torch.Tensor) -> None:
+    """dst[pos[t, j]] = scale[t, j] * src[t] (scale None = 1); pos int32 [T, k], negative = skip."""
+    T, k = pos.shape
+    rc = _lib.cuda().tb_moe_scatter_rows(src.data_ptr(), src.stride(0), pos.data_ptr(), _lib.ptr(scale), dst.data_ptr(),
+                                         dst.stride(0), T, k, src.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_scatter_rows")
+    _count()
+
+
+def moe_gather_sum(src: torch.Tensor, pos: torch.Tensor, wts, residual=None) -> torch.Tensor:
+    """out[t] = sum_j wts[t, j] * src[pos[t, j]] (+ residual[t]); wts fp32 [T, k] or None."""
+    T, k = pos.shape
+    D = src.shape[1]
+    out = torch.empty((T, D), dtype=torch.bfloat16, device=src.device)
+    rc = _lib.cuda().tb_moe_gather_sum(src.data_ptr(), src.stride(0), pos.data_ptr(), _lib.ptr(wts), _lib.ptr(residual),
+                                       residual.stride(0) if residual is not None else 0, out.data_ptr(), out.stride(0),
+                                       T, k, D, _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_gather_sum")
+    _count()
+    return out
+
+
+def moe_dot_rows(a: torch.Tensor, b: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """out[t, j] = <a[t], b[pos[t, j]]> in fp32."""
+    T, k = pos.shape
+    out = torch.empty((T, k), dtype=torch.float32, device=a.device)
+    rc = _lib.cuda().tb_moe_dot_rows(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), pos.data_ptr(), out.data_ptr(),
+                                     T, k, a.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_dot_rows")
+    _count()
+    return out

@@ -40,6 +40,10 @@ def expert_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Ten
     T, D = x.shape
     k = idx.shape[1]
     E = layer.cfg.num_experts
+    if x.is_cuda and x.dtype == torch.bfloat16 and D % 64 == 0 and layer.cfg.moe_hidden_dim % 64 == 0 and E <= 1024:
+        from ..ops import moe as moe_ops
+        return moe_ops.experts(x, weights, idx, layer.gate_proj, layer.up_proj, layer.down_proj, None,
+                               layer.cfg.activation)
     flat = idx.reshape(-1)
     order = torch.argsort(flat, stable=True)
     token_of = torch.div(order, k, rounding_mode="floor")
