@@ -23,6 +23,7 @@ P = c_void_p
 LL = c_longlong
 I = c_int
 F = c_float
+U = ctypes.c_uint
 
 _CUDA_SIGS = {
     "tb_gemm_bf16": [P, P, P, I, I, I, LL, LL, LL, I, P, P, LL, F, P, I, P],

@@ -50,11 +50,56 @@ struct TileDesc {
   long long c_off;     // added (in elements) to C
 };
 
+constexpr int MAX_RANKS = 8;
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+// Fused all-gather: CTAs past `gemm_ctas` pull the peers' row blocks of the gathered operand into the local
+// copy (TMA bulk loads from peer memory into shared memory, bulk stores from there to local memory) and
+// publish one flag per 128-row block; GEMM tiles wait for the flags of the rows they read.
+struct CopyArgs {
+  PeerPtrs src;               // every rank's gathered buffer (symmetric); rank p owns rows [p, p+1) * rows/world
+  char* dst;                  // this rank's gathered buffer
+  long long rank_bytes;       // bytes owned by one rank
+  long long job_bytes;        // bytes of one 128-row block
+  int jobs_per_rank;
+  int piece_bytes;            // bulk copy granularity (divides job_bytes, multiple of 16, <= 32 KiB)
+  unsigned* flags;            // [world * jobs_per_rank], local
+  unsigned epoch;
+};
+// Fused reduce-scatter: every rank leaves its partial product in its own symmetric buffer and counts finished
+// tiles per 128-row block; CTAs past `gemm_ctas` wait for the blocks of this rank's rows on every peer, pull
+// them (TMA bulk loads), add them up in fp32 and write the reduced rows.
+struct ReduceArgs {
+  PeerPtrs part;              // every rank's partial C [M, N] bf16, contiguous
+  PeerPtrs done;              // every rank's per-block counters
+  __nv_bfloat16* out;         // [M / world, N] contiguous
+  const __nv_bfloat16* resid; // optional, same layout as out
+  int tiles_per_rank;
+  unsigned target;            // counter value that marks a finished block in this call
+  int* work;                  // local counter handing out row blocks to reducer CTAs (zero at launch)
+};
+
 struct GemmArgs {
   int M, N, K;
   int flags;
   const TileDesc* tiles;      // null = dense problem
   const int* num_tiles_dev;
+  // --- fused collectives (all zero for a plain GEMM)
+  int gemm_ctas;              // CTAs that run GEMM tiles; the rest of the grid runs the aux role
+  int aux_kind;               // 0 none, 1 copier (all-gather), 2 reducer (reduce-scatter)
+  int rank, world;
+  int rot_m, rot_n;           // tile order starts at this m / n tile (own rows first, or own rows last)
+  int wait_mode;              // 0 none; a tile waits for the flags of 1: its A rows, 2: its B rows,
+                              // 3: each 128 rows of the contraction (gathered dimension = K, both operands MN-major)
+  int rot_k;                  // mode 3: k blocks start here (own rows first)
+  int own_lo, own_hi;         // flag range that is local and needs no wait
+  const unsigned* wait_flags;
+  unsigned wait_epoch;
+  unsigned* done_flags;       // per m tile, += 1 per epilogue warp and tile
+  CopyArgs copy;
+  ReduceArgs red;
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
@@ -74,6 +119,230 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
+
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long gtimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
+}
+constexpr long long FLAG_WAIT_NS = 4000000000ll;   // a flag another CTA or rank sets: give up after 4 s
+
+// Bounded wait for *flag to reach `target` (wrap-safe). `sys` = the flag lives in a peer's memory.
+__device__ __forceinline__ bool flag_wait_bounded(const unsigned* flag, unsigned target, bool sys,
+                                                  volatile int* abort_flag, int* status) {
+  const unsigned long long t0 = gtimer_ns();
+  int polls = 0;
+  while (true) {
+    const unsigned v = sys ? ld_acquire_sys_u32(flag) : ld_acquire_gpu_u32(flag);
+    if ((int)(v - target) >= 0) return true;
+    if ((++polls & 15) == 0) {
+      if (*abort_flag) return false;
+      if ((long long)(gtimer_ns() - t0) > FLAG_WAIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+        return false;
+      }
+    }
+    __nanosleep(sys ? 500 : 100);
+  }
+}
+
+// All-gather copier (one elected thread): peers' 128-row blocks, nearest ring neighbour first.
+__device__ void copier_role(const CopyArgs& ca, int rank, int world, int aux_id, int n_aux, uint32_t smem_base,
+                            uint32_t bar_base, int ring_bytes, volatile int* abort_flag, int* status) {
+  const int piece = ca.piece_bytes;
+  int nbuf = ring_bytes / piece;
+  if (nbuf > 6) nbuf = 6;
+  uint32_t phase_bits = 0;                                   // parity per buffer
+  const int total_jobs = (world - 1) * ca.jobs_per_rank;
+  for (int j = aux_id; j < total_jobs; j += n_aux) {
+    const int step = j / ca.jobs_per_rank, within = j - step * ca.jobs_per_rank;
+    const int peer = (rank + 1 + step) % world;
+    const long long off = (long long)peer * ca.rank_bytes + (long long)within * ca.job_bytes;
+    const char* src = reinterpret_cast<const char*>(ca.src.p[peer]) + off;
+    char* dst = ca.dst + off;
+    const int np = (int)(ca.job_bytes / piece);
+    for (int i = 0; i < np && i < nbuf; ++i) {
+      mbar_expect_tx(bar_base + 8u * i, piece);
+      bulk_load(smem_base + i * piece, src + (long long)i * piece, piece, bar_base + 8u * i);
+    }
+    bool ok = true;
+    for (int i = 0; i < np; ++i) {
+      const int b = i % nbuf;
+      if (!mbar_wait_bounded(bar_base + 8u * b, (phase_bits >> b) & 1u, abort_flag, status, ST_TIMEOUT_PRODUCER)) {
+        ok = false;
+        break;
+      }
+      phase_bits ^= 1u << b;
+      bulk_store(dst + (long long)i * piece, smem_base + b * piece, piece);
+      tma_store_commit();
+      if (i + nbuf < np) {
+        tma_store_wait_read<0>();                            // the buffer may be overwritten
+        mbar_expect_tx(bar_base + 8u * b, piece);
+        bulk_load(smem_base + b * piece, src + (long long)(i + nbuf) * piece, piece, bar_base + 8u * b);
+      }
+    }
+    if (!ok) return;
+    tma_store_wait<0>();
+    fence_proxy_async_all();
+    __threadfence();
+    st_release_gpu_u32(ca.flags + peer * ca.jobs_per_rank + within, ca.epoch);
+  }
+}
+
+// Reduce-scatter reducer (whole CTA): this rank's row blocks, summed over all ranks' partial products.
+// A block (128 rows x N) is walked in 16 KiB chunks; for each chunk the `world` source pieces stream through a
+// ring of 11 shared-memory buffers (TMA bulk loads, peers over NVLink) and every thread keeps the fp32 sums of
+// its vectors in registers until the last source has arrived. full / empty mbarriers per buffer, no CTA-wide
+// barrier inside the stream.
+__device__ void reducer_role(const ReduceArgs& ra, int rank, int world, int N, int aux_id, int n_aux,
+                             uint8_t* smem_al, uint32_t smem_base, uint32_t bar_base, volatile int* abort_flag,
+                             int* status) {
+  constexpr int PIECE = 16384, NBUF = 11, VEC = PIECE / 16, MAXV = (VEC + 191) / 192;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const long long block_bytes = 128ll * N * 2;
+  const int nchunk = (int)(block_bytes / PIECE);
+  // 11 buffers (176 KiB in flight per CTA against NVLink latency); their barriers sit behind them in the ring,
+  // which every tile configuration sizes at 192 KiB or more
+  (void)bar_base;
+  const uint32_t rbar = smem_base + NBUF * PIECE;
+  auto full = [&](int b) { return rbar + 8u * b; };
+  auto empty = [&](int b) { return rbar + 8u * (NBUF + b); };
+  __syncthreads();
+  if (tid == 0) {
+    for (int b = 0; b < NBUF; ++b) {
+      mbar_init(full(b), 1);
+      mbar_init(empty(b), nthr >> 5);                          // one arrival per warp
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  uint32_t ph_full = 0u, ph_empty = 0u;                      // parity bits per buffer (ph_empty: thread 0 only)
+  long long issued = 0;                                      // pieces issued so far (thread 0), over all blocks
+  long long consumed = 0;
+  volatile int* s_blk = reinterpret_cast<volatile int*>(smem_al + NBUF * PIECE + 8 * (2 * NBUF));
+  const int parts = (nchunk % 4 == 0) ? 4 : 1;               // work unit: a quarter of a block's chunks
+  (void)aux_id; (void)n_aux;
+  while (true) {
+    // row blocks are handed out by a counter: dedicated reducer CTAs start while the tiles still run, the tile
+    // CTAs join when their tiles are done
+    __syncthreads();
+    if (tid == 0) *s_blk = atomicAdd(ra.work, 1);
+    __syncthreads();
+    const int unit = *s_blk;                                 // (row block, part of its chunks)
+    if (unit >= ra.tiles_per_rank * parts) break;
+    const int blk = unit / parts, part = unit - blk * parts;
+    const int c_first = part * (nchunk / parts);
+    const int gmt = rank * ra.tiles_per_rank + blk;
+    if (tid == 0) {
+      for (int s = 0; s < world; ++s) {
+        const int p = (rank - 1 - s + 2 * world) % world;    // the peer that computes this rank's rows first
+        const unsigned* f = reinterpret_cast<const unsigned*>(ra.done.p[p]) + gmt;
+        if (!flag_wait_bounded(f, ra.target, p != rank, abort_flag, status)) break;
+      }
+      fence_proxy_async_all();
+    }
+    __syncthreads();
+    if (*abort_flag) return;
+    const int npieces = (nchunk / parts) * world;
+    int next = 0;                                            // next piece of this block to issue (thread 0)
+    auto issue_upto = [&](int limit) {
+      while (next < npieces && next < limit) {
+        const int b = (int)(issued % NBUF);
+        if (issued >= NBUF) {
+          if (!mbar_wait_bounded(empty(b), (ph_empty >> b) & 1u, abort_flag, status, ST_TIMEOUT_PRODUCER)) return;
+          ph_empty ^= 1u << b;
+        }
+        const int c = c_first + next / world, s = next % world;
+        const int p = (rank + 1 + s) % world;                // own partial product last
+        const char* src = reinterpret_cast<const char*>(ra.part.p[p]) + (long long)gmt * block_bytes + (long long)c * PIECE;
+        mbar_expect_tx(full(b), PIECE);
+        bulk_load(smem_base + b * PIECE, src, PIECE, full(b));
+        ++issued;
+        ++next;
+      }
+    };
+    if (tid == 0) issue_upto(NBUF - 1);
+    float acc[MAXV][8];
+    for (int q = 0; q < npieces; ++q) {
+      const int c = c_first + q / world, s = q % world;
+      if (tid == 0) issue_upto(q + NBUF);
+      const int b = (int)(consumed % NBUF);
+      if (!mbar_wait_bounded(full(b), (ph_full >> b) & 1u, abort_flag, status, ST_TIMEOUT_EPILOGUE)) return;
+      ph_full ^= 1u << b;
+      ++consumed;
+      const uint8_t* buf = smem_al + b * PIECE;
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int v = tid + j * 192;
+        if (v < VEC) {
+          const uint4 u = *reinterpret_cast<const uint4*>(buf + v * 16);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+          if (s == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              acc[j][2 * k] = bf16_lo(w[k]);
+              acc[j][2 * k + 1] = bf16_hi(w[k]);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              acc[j][2 * k] += bf16_lo(w[k]);
+              acc[j][2 * k + 1] += bf16_hi(w[k]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(empty(b));
+      if (s == world - 1) {
+        const long long out_off = ((long long)blk * block_bytes + (long long)c * PIECE) >> 1;   // elements
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int v = tid + j * 192;
+          if (v < VEC) {
+            if (ra.resid != nullptr) {
+              const uint4 u = *reinterpret_cast<const uint4*>(ra.resid + out_off + v * 8);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                acc[j][2 * k] += bf16_lo(w[k]);
+                acc[j][2 * k + 1] += bf16_hi(w[k]);
+              }
+            }
+            *reinterpret_cast<uint4*>(ra.out + out_off + v * 8) =
+                make_uint4(pack_bf16(acc[j][0], acc[j][1]), pack_bf16(acc[j][2], acc[j][3]),
+                           pack_bf16(acc[j][4], acc[j][5]), pack_bf16(acc[j][6], acc[j][7]));
+          }
+        }
+      }
+    }
+  }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(192, 1)
@@ -128,6 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const bool grouped = args.tiles != nullptr;
   const int total_tiles = grouped ? *args.num_tiles_dev : num_tiles;
+  const int n_gemm = args.gemm_ctas > 0 ? args.gemm_ctas : (int)gridDim.x;   // CTAs that walk the tile list
   auto tile_info = [&](int t) -> TileDesc {
     if (grouped) return args.tiles[t];
     const int per_group = GROUP_M * num_n;
@@ -136,8 +406,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int gsz = min(GROUP_M, num_m - first_m);
     const int r = t - g * per_group;
     TileDesc d;
-    d.m0 = (first_m + (r % gsz)) * BM;
-    d.n0 = (r / gsz) * BN;
+    d.m0 = ((first_m + (r % gsz) + args.rot_m) % num_m) * BM;
+    d.n0 = ((r / gsz + args.rot_n) % num_n) * BN;
     d.m_end = M;
     d.kb0 = 0;
     d.kb1 = num_kb;
@@ -146,16 +416,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     return d;
   };
 
-  if (warp == 0) {
+  if ((int)blockIdx.x >= n_gemm) {
+    // ------------------------------------------------ aux role of a fused collective (no tiles, no TMEM use)
+    const int aux_id = (int)blockIdx.x - n_gemm, n_aux = (int)gridDim.x - n_gemm;
+    if (args.aux_kind == 1) {
+      if (warp == 0 && elect_one())
+        copier_role(args.copy, args.rank, args.world, aux_id, n_aux, smem_base, bar_base, C_::STAGES * C_::STAGE_BYTES,
+                    abort_flag, args.status);
+    } else if (args.aux_kind == 2) {
+      reducer_role(args.red, args.rank, args.world, N, aux_id, n_aux, smem_al, smem_base, bar_base, abort_flag,
+                   args.status);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm) {
         const TileDesc td = tile_info(t);
         const int m0 = td.m0, n0 = td.n0;
-        for (int kb = td.kb0; kb < td.kb1; ++kb) {
+        if (args.wait_mode == 1 || args.wait_mode == 2) {
+          // rows this tile reads from the gathered operand must have landed (copier CTAs of this kernel)
+          const int f_lo = (args.wait_mode == 1 ? m0 : n0) >> 7;
+          const int ext = args.wait_mode == 1 ? min(BM, M - m0) : min(BN, N - n0);
+          const int f_hi = f_lo + ((ext + 127) >> 7);
+          for (int f = f_lo; f < f_hi && ok; ++f) {
+            if (f >= args.own_lo && f < args.own_hi) continue;
+            ok = flag_wait_bounded(args.wait_flags + f, args.wait_epoch, false, abort_flag, args.status);
+          }
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
+        for (int kbi = td.kb0; kbi < td.kb1; ++kbi) {
+          int kb = kbi;
+          if (args.wait_mode == 3) {
+            kb = (kbi + args.rot_k) % num_kb;
+            const int f = (kb * BK) >> 7;
+            if ((kbi == td.kb0 || (kb & 1) == 0) && !(f >= args.own_lo && f < args.own_hi)) {
+              if (!flag_wait_bounded(args.wait_flags + f, args.wait_epoch, false, abort_flag, args.status)) {
+                ok = false;
+                break;
+              }
+              fence_proxy_async_all();
+            }
+          }
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, args.status,
                                  ST_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -194,7 +499,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm) {
         int kb0 = 0, kb1 = num_kb;
         if (grouped) {
           kb0 = args.tiles[t].kb0;
@@ -243,7 +548,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;      // vector paths need aligned bases
     const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += n_gemm) {
       const TileDesc td = tile_info(t);
       const int row = td.m0 + q * 32 + lane;
       const int n0 = td.n0;
@@ -345,12 +650,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      if (args.done_flags != nullptr) {
+        __threadfence_system();                     // this tile's rows are visible to peers before the count moves
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(args.done_flags + (td.m0 >> 7), 1u);
+      }
       tc_fence_before();
       __syncwarp();
       if (empty_k) continue;                        // the MMA warp skipped this tile too: no accumulator used
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+  }
+
+  if (args.aux_kind == 2 && (int)blockIdx.x < n_gemm) {
+    // reduce-scatter: tile CTAs whose tiles are done help the reducer CTAs with the remaining row blocks
+    tc_fence_before();
+    __syncthreads();
+    if (!*abort_flag)
+      reducer_role(args.red, args.rank, args.world, N, 0, 1, smem_al, smem_base, bar_base, abort_flag, args.status);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -389,6 +707,21 @@ std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
 int g_sm_count = 0;
 void set_gemm_attrs();
+// CTAs to give to the copier / reducer role: enough to move `bytes` while the tiles compute `flops`, assuming
+// about 30 GB/s per CTA (measured: bulk copies with ~190 KiB in flight per CTA over NVLink) and 1.3 PFLOP/s for the tiles.
+int aux_ctas_for(double bytes, double flops) {
+  const double t = flops / 1.3e15;
+  int n = (int)(bytes / (t * 30e9) + 0.999);
+  if (n < 2) n = 2;
+  if (n > 32) n = 32;
+  return n;
+}
+void clear_fused(GemmArgs& a) {
+  a.gemm_ctas = 0; a.aux_kind = 0; a.rank = 0; a.world = 1; a.rot_m = 0; a.rot_n = 0; a.wait_mode = 0;
+  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
+  memset(&a.copy, 0, sizeof(a.copy));
+  memset(&a.red, 0, sizeof(a.red));
+}
 
 }  // namespace
 
@@ -495,6 +828,7 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   args.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   args.ldr = ldr; args.alpha = alpha; args.status = status;
   args.tiles = nullptr; args.num_tiles_dev = nullptr;
+  clear_fused(args);
   const int tiles = num_m * ((N + BN - 1) / BN);
   int ctas = g_sm_count;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
@@ -541,12 +875,172 @@ TB_API int tb_gemm_grouped_bf16(const void* A, long long a_rows, long long a_col
   args.alpha = alpha; args.status = status;
   args.tiles = reinterpret_cast<const TileDesc*>(tiles);
   args.num_tiles_dev = num_tiles_dev;
+  clear_fused(args);
   const int ctas = max_tiles < g_sm_count ? max_tiles : g_sm_count;
   set_gemm_attrs();
   switch (bn) {
     case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
     case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
     default: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// ------------------------------------------------------------------ fused collectives
+// C = epilogue(A * B^T) where one operand (or the contraction) is all-gathered from the peers inside the kernel.
+//   gathered: `world` pointers (host array) to every rank's copy of the gathered array [rows, cols], contiguous
+//   bf16, symmetric memory; rank r has already written rows [r, r+1) * rows / world of its own copy, and a
+//   cross-rank barrier has run since. The local copy is complete when the kernel ends.
+//   mode 1: gathered array is A [M, K] (K-major);  mode 2: gathered array is B [N, K] (K-major);
+//   mode 3: gathered array is B [K, N] (MN-major, gathered along the contraction), A [K, M] is MN-major too and
+//           local in full (weight gradient of a sequence-parallel layer).
+//   other / ld_other: the operand that is not gathered. flags: GF_* epilogue bits (operand layout bits are
+//   implied by the mode). ready: unsigned [rows / 128], local scratch that persists between calls; epoch: a
+//   value that grows by one per call on this buffer.
+TB_API int tb_gemm_ag_bf16(const void* const* gathered, int rank, int world, int mode, long long rows, long long cols,
+                           const void* other, long long ld_other, void* C, long long ldc, int M, int N, int K,
+                           int flags, const void* bias, const void* resid, long long ldr, unsigned* ready,
+                           unsigned epoch, int n_aux, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || mode < 1 || mode > 3) return -2;
+  if (rows % (128ll * world) || (cols % 8) || (ld_other % 8)) return -2;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  // the gathered operand's layout is fixed by the mode; the other operand keeps the caller's layout bit
+  if (mode == 1) flags &= ~GF_A_MN;
+  if (mode == 2) flags &= ~GF_B_MN;
+  if (mode == 3) flags |= GF_A_MN | GF_B_MN;
+  const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  const void* local = gathered[rank];
+  const void* A = mode == 1 ? local : other;
+  const void* B = mode == 1 ? other : local;
+  const long long lda = mode == 1 ? cols : ld_other, ldb = mode == 1 ? ld_other : cols;
+  const int num_m = (M + BM - 1) / BM;
+  if (world == 1) n_aux = 0;
+  else if (n_aux <= 0) n_aux = aux_ctas_for((double)(rows - rows / world) * cols * 2.0, 2.0 * M * N * K);
+  if (n_aux > g_sm_count / 2) n_aux = g_sm_count / 2;
+  const int avail = g_sm_count - n_aux;
+  int BN = 64;
+  for (int cand : {256, 128, 64}) {
+    if (cand > 128 && N < 256) continue;
+    BN = cand;
+    if ((long long)num_m * ((N + cand - 1) / cand) >= (avail * 3) / 5) break;
+  }
+  const int num_n = (N + BN - 1) / BN;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
+  if (r) return -3;
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
+  if (r) return -4;
+  GemmArgs a;
+  a.M = M; a.N = N; a.K = K; a.flags = flags; a.C = C; a.ldc = ldc;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  a.ldr = ldr; a.alpha = 1.f; a.status = status; a.tiles = nullptr; a.num_tiles_dev = nullptr;
+  clear_fused(a);
+  const int tiles = num_m * num_n;
+  int n_gemm = tiles < avail ? tiles : avail;
+  a.rank = rank; a.world = world;
+  if (world > 1) {
+    const int jpr = (int)(rows / world / 128);
+    a.gemm_ctas = n_gemm; a.aux_kind = 1; a.wait_mode = mode; a.wait_flags = ready; a.wait_epoch = epoch;
+    a.own_lo = rank * jpr; a.own_hi = (rank + 1) * jpr;
+    if (mode == 1) a.rot_m = (rank * jpr) % num_m;
+    if (mode == 2) a.rot_n = (int)((rank * (rows / world)) / BN) % num_n;
+    if (mode == 3) a.rot_k = (int)((rank * (rows / world)) / BK);
+    for (int p = 0; p < world; ++p) a.copy.src.p[p] = const_cast<void*>(gathered[p]);
+    a.copy.dst = reinterpret_cast<char*>(const_cast<void*>(local));
+    a.copy.rank_bytes = (rows / world) * cols * 2;
+    a.copy.job_bytes = 128 * cols * 2;
+    a.copy.jobs_per_rank = jpr;
+    int piece = 32768;
+    while (a.copy.job_bytes % piece) piece >>= 1;
+    a.copy.piece_bytes = piece;
+    a.copy.flags = ready;
+    a.copy.epoch = epoch;
+  }
+  set_gemm_attrs();
+  const int grid = n_gemm + (world > 1 ? n_aux : 0);
+  switch (BN) {
+    case 256: gemm_bf16_kernel<256><<<grid, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
+    case 128: gemm_bf16_kernel<128><<<grid, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
+    default: gemm_bf16_kernel<64><<<grid, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// out[M / world, N] = sum over ranks of (A_r * B_r^T)[this rank's rows] (+ resid), the reduce-scatter of a
+// row-parallel product, in one kernel. part / done: `world` pointers (host arrays) to every rank's partial
+// product buffer ([M, N] bf16 contiguous) and per-block counters (unsigned [M / 128]); both symmetric, a
+// cross-rank barrier has run since the previous use of `part`. *total (host) carries the counter target from
+// call to call and must evolve identically on all ranks (same shapes in the same order). work: one local int.
+TB_API int tb_gemm_rs_bf16(const void* A, long long lda, const void* B, long long ldb, int M, int N, int K, int flags,
+                           const void* const* part, const void* const* done, void* out, const void* resid, int rank,
+                           int world, unsigned* total, int* work, int n_aux, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -2;
+  if (M % (128 * world) || (N % 64) || (lda % 8) || (ldb % 8) || K <= 0) return -2;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  flags &= (GF_A_MN | GF_B_MN);
+  const int num_m = M / BM;
+  if (n_aux <= 0) n_aux = 4;     // a few dedicated reducers overlap with the tiles; all CTAs reduce once tiles end
+  if (n_aux > g_sm_count / 2) n_aux = g_sm_count / 2;
+  const int avail = g_sm_count - n_aux;
+  int BN = 64;
+  for (int cand : {256, 128, 64}) {
+    if (cand > 128 && N < 256) continue;
+    BN = cand;
+    if ((long long)num_m * ((N + cand - 1) / cand) >= (avail * 3) / 5) break;
+  }
+  const int num_n = (N + BN - 1) / BN;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
+  if (r) return -3;
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
+  if (r) return -4;
+  GemmArgs a;
+  a.M = M; a.N = N; a.K = K; a.flags = flags;
+  a.C = const_cast<void*>(part[rank]); a.ldc = N;
+  a.bias = nullptr; a.resid = nullptr; a.ldr = 0; a.alpha = 1.f; a.status = status;
+  a.tiles = nullptr; a.num_tiles_dev = nullptr;
+  clear_fused(a);
+  const int tiles = num_m * num_n;
+  const int n_gemm = tiles < avail ? tiles : avail;
+  const int tpr = num_m / world;
+  *total += 4u * (unsigned)num_n;
+  a.gemm_ctas = n_gemm; a.aux_kind = 2; a.rank = rank; a.world = world;
+  a.rot_m = (((rank + 1) % world) * tpr) % num_m;
+  a.done_flags = reinterpret_cast<unsigned*>(const_cast<void*>(done[rank]));
+  for (int p = 0; p < world; ++p) {
+    a.red.part.p[p] = const_cast<void*>(part[p]);
+    a.red.done.p[p] = const_cast<void*>(done[p]);
+  }
+  a.red.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.red.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  a.red.tiles_per_rank = tpr;
+  a.red.target = *total;
+  a.red.work = work;
+  if (cudaMemsetAsync(work, 0, sizeof(int), stream) != cudaSuccess) return -5;
+  set_gemm_attrs();
+  const int grid = n_gemm + n_aux;
+  switch (BN) {
+    case 256: gemm_bf16_kernel<256><<<grid, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
+    case 128: gemm_bf16_kernel<128><<<grid, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
+    default: gemm_bf16_kernel<64><<<grid, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, a); break;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

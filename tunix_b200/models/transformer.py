@@ -87,9 +87,23 @@ class Attention(nn.Module):
         cfg = self.cfg
         B, T, _ = x.shape
         N, K, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
-        q = self.q_proj(x).view(B, T, N, H)
-        k = self.k_proj(x).view(B, T, K, H)
-        v = self.v_proj(x).view(B, T, K, H)
+        tp = getattr(self.q_proj, "tp", None)
+        if tp is not None:
+            # sequence-parallel input [B/tp, T, D]: one all-gather feeds q, k and v of this rank's heads
+            from ..parallel import tp as tp_lib
+            projs = (self.q_proj, self.k_proj, self.v_proj)
+            if any(p.lora_a is not None or p.quant is not None for p in projs) or cache is not None:
+                raise NotImplementedError("tensor parallelism covers full-weight training without a KV cache")
+            w = torch.cat([p.weight for p in projs], 0)
+            b = torch.cat([p.bias for p in projs], 0) if self.q_proj.bias is not None else None
+            qkv = tp_lib.column_parallel_linear(x, w, b, tp)
+            B, N, K = qkv.shape[0], N // tp.world, K // tp.world
+            q, k, v = qkv.split([N * H, K * H, K * H], dim=-1)
+            q, k, v = (t.contiguous().view(B, T, -1, H) for t in (q, k, v))
+        else:
+            q = self.q_proj(x).view(B, T, N, H)
+            k = self.k_proj(x).view(B, T, K, H)
+            v = self.v_proj(x).view(B, T, K, H)
         if cfg.qk_norm:
             q = self.q_norm(q)
             k = self.k_norm(k)
@@ -121,6 +135,8 @@ class Attention(nn.Module):
             o = F.attention(q, k, v, scale=self.scale, causal=True, window=self.window,
                             softcap=cfg.attn_logit_softcap, q_off=q_off, seg_q=seg_q, seg_k=seg_k)
         o = o.reshape(B, T, N * H)
+        if tp is not None:
+            return tp_lib.row_parallel_linear(o, self.o_proj.weight, residual, tp), new_cache
         return self.o_proj(o, residual=residual), new_cache
 
 
@@ -134,6 +150,15 @@ class MLP(nn.Module):
         self.kind = cfg.activation
 
     def forward(self, x, residual=None):
+        tp = getattr(self.gate_proj, "tp", None)
+        if tp is not None:
+            from ..parallel import tp as tp_lib
+            if any(p.lora_a is not None or p.quant is not None for p in (self.gate_proj, self.up_proj, self.down_proj)):
+                raise NotImplementedError("tensor parallelism covers full-weight training")
+            gu = tp_lib.column_parallel_linear(x, torch.cat([self.gate_proj.weight, self.up_proj.weight], 0), None, tp)
+            g, u = gu.split(gu.shape[-1] // 2, dim=-1)
+            h = F.glu(g.contiguous(), u.contiguous(), self.kind)
+            return tp_lib.row_parallel_linear(h, self.down_proj.weight, residual, tp)
         h = F.glu(self.gate_proj(x), self.up_proj(x), self.kind)
         return self.down_proj(h, residual=residual)
 
@@ -237,6 +262,7 @@ class Transformer(nn.Module):
         self.lm_head = None if cfg.weight_tying else nn.Parameter(
             torch.empty(cfg.vocab_size, cfg.embed_dim, dtype=dt, device=device))
         self._rope_cache: dict = {}
+        self.tp = None  # parallel.tp.TPContext once apply_tensor_parallel has sliced the weights
 
     # ------------------------------------------------------------------ weights
     @torch.no_grad()
@@ -282,7 +308,14 @@ class Transformer(nn.Module):
             start = 0 if cache is None else cache[0]["end"]
             positions = torch.arange(start, start + T, device=dev, dtype=torch.int32)[None].expand(B, T)
         positions = positions.to(torch.int32).contiguous()
-        x = F.embedding(input_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
+        emb_tokens = input_tokens
+        if self.tp is not None and self.tp.world > 1:
+            # sequence-parallel residual stream: this rank embeds its B/tp sequences; attention sees all of them
+            if B % self.tp.world or cache is not None:
+                raise ValueError("tensor parallelism needs the batch divisible by tp and no KV cache")
+            n = B // self.tp.world
+            emb_tokens = input_tokens[self.tp.rank * n:(self.tp.rank + 1) * n]
+        x = F.embedding(emb_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         new_cache = [] if cache is not None else None
         use_remat = cfg.remat_config != RematConfig.NONE and torch.is_grad_enabled() and cache is None
         hook = self.layer_grad_hook if (torch.is_grad_enabled() and cache is None) else None

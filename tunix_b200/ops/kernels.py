@@ -473,3 +473,53 @@ def moe_dot_rows(a: torch.Tensor, b: torch.Tensor, pos: torch.Tensor) -> torch.T
     _lib.check(rc, "tb_moe_dot_rows")
     _count()
     return out
+
+
+# ------------------------------------------------------------------ GEMMs fused with a collective
+_lib.register_cuda_sigs({
+    "tb_gemm_ag_bf16": [_lib.P, _lib.I, _lib.I, _lib.I, _lib.LL, _lib.LL, _lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.I,
+                        _lib.I, _lib.I, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.U, _lib.I, _lib.P, _lib.P],
+    "tb_gemm_rs_bf16": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.P,
+                        _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.P, _lib.P],
+})
+
+
+def gemm_ag(gathered_ptrs, rank: int, world: int, mode: int, rows: int, cols: int, other: torch.Tensor, out: torch.Tensor,
+            M: int, N: int, K: int, ready: torch.Tensor, epoch: int, *, other_mn: bool = False, accumulate: bool = False,
+            bias=None, residual=None, n_aux: int = 0) -> torch.Tensor:
+    """GEMM whose gathered operand is pulled from the peers inside the kernel (see tb_gemm_ag_bf16 in gemm.cu).
+
+    gathered_ptrs / part_ptrs / done_ptrs below are `SymmBuffer.c_ptrs` pointer tables.
+    mode 1: A = gathered [M, K]; mode 2: B = gathered [N, K]; mode 3: B = gathered [K, N] and A = other [K, M]."""
+    flags = (GF_OUT_F32 if out.dtype == torch.float32 else 0) | (GF_ACCUM if accumulate else 0)
+    if other_mn and mode in (1, 2):
+        flags |= GF_B_MN if mode == 1 else GF_A_MN
+    if bias is not None:
+        flags |= GF_BIAS
+    ldr = 0
+    if residual is not None:
+        flags |= GF_RESIDUAL
+        ldr = residual.stride(0)
+    rc = _lib.cuda().tb_gemm_ag_bf16(gathered_ptrs, rank, world, mode, rows, cols, other.data_ptr(), other.stride(0), out.data_ptr(),
+                                     out.stride(0), M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), ldr,
+                                     ready.data_ptr(), epoch & 0xFFFFFFFF, n_aux, _lib.status_buffer().data_ptr(),
+                                     _lib.stream_ptr())
+    _lib.check(rc, "tb_gemm_ag_bf16")
+    _count()
+    return out
+
+
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, part_ptrs, done_ptrs, out: torch.Tensor, total, work: torch.Tensor,
+            rank: int, world: int, M: int, N: int, K: int, *, a_mn: bool = False, b_mn: bool = False, residual=None, n_aux: int = 0) -> torch.Tensor:
+    """Row-parallel GEMM with the reduce-scatter of its partial products fused in (tb_gemm_rs_bf16 in gemm.cu).
+    `total` is a ctypes.c_uint that carries the counter target of this workspace from call to call."""
+    import ctypes
+    flags = (GF_A_MN if a_mn else 0) | (GF_B_MN if b_mn else 0)
+    assert out.is_contiguous() and (residual is None or residual.is_contiguous())
+    rc = _lib.cuda().tb_gemm_rs_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), M, N, K, flags,
+                                     part_ptrs, done_ptrs, out.data_ptr(), _lib.ptr(residual), rank,
+                                     world, ctypes.byref(total), work.data_ptr(), n_aux, _lib.status_buffer().data_ptr(),
+                                     _lib.stream_ptr())
+    _lib.check(rc, "tb_gemm_rs_bf16")
+    _count()
+    return out

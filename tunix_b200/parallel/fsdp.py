@@ -37,7 +37,6 @@ from . import symm
 
 P, LL, I, F = _lib.P, _lib.LL, _lib.I, _lib.F
 _lib.register_cuda_sigs({
-    "tb_symm_barrier": [P, I, I, I, ctypes.c_uint, LL, P, P],
     "tb_reduce_scatter_pull": [P, I, P, I, I, I, P, F, P, I, P],
     "tb_allgather_pull": [P, P, I, I, I, P, I, P],
     "tb_gather_shard": [P, P, I, I, P, P, P],

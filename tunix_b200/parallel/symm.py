@@ -18,6 +18,12 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from .. import _lib
+
+_lib.register_cuda_sigs({
+    "tb_symm_barrier": [_lib.P, _lib.I, _lib.I, _lib.I, ctypes.c_uint, _lib.LL, _lib.P, _lib.P],
+})
+
 
 class SymmBuffer:
     def __init__(self, tensor: torch.Tensor, ptrs: list[int], rank: int, world: int, handle=None):
@@ -84,7 +90,6 @@ class SymmBarrier:
         self.timeout_ms = timeout_ms
 
     def wait(self, slot: int = 0, timeout_ms: Optional[int] = None) -> None:
-        from .. import _lib
         b = self.buf
         if b.world == 1:
             return

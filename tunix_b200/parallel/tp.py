@@ -1,0 +1,307 @@
+"""Tensor parallelism with sequence-parallel activations, on GEMMs that carry their collective.
+
+Between tensor-parallel regions the residual stream is sharded over the tp ranks along the flattened token
+dimension (rank r holds rows [r, r+1) * M / tp). A column-parallel projection all-gathers its input and a
+row-parallel projection reduce-scatters its output; both collectives run INSIDE the GEMM kernel
+(`csrc/gemm.cu`: copier / reducer CTAs next to the tcgen05 tile CTAs, data over NVLink peer memory):
+
+    column forward   y[M, N/tp]   = gather(x_s) @ W_c^T            all-gather -> GEMM   (mode 1)
+    column backward  dx_s         = scatter_sum(dy @ W_c)          GEMM -> reduce-scatter
+                     dW_c         = dy^T @ gather(x_s)             all-gather (contraction) -> GEMM (mode 3)
+    row forward      y_s[M/tp, N] = scatter_sum(x @ W_r^T) + res_s GEMM -> reduce-scatter
+    row backward     dx           = gather(dy_s) @ W_r             all-gather -> GEMM   (mode 1)
+                     dW_r         = gather(dy_s)^T @ x             plain GEMM on the buffer just gathered
+
+Every fused call is preceded by the device-side flag barrier of `symm.SymmBarrier`: it makes the peers'
+shards (or the previous reader's end) visible before remote memory is touched. Without symmetric memory
+(CPU / gloo, one rank) the same functions run `torch.distributed` collectives around plain matmuls, which is
+what the CPU tests exercise.
+
+Reference: the reference expresses this through GSPMD sharding annotations (`act_btd = (fsdp, None, tp)`,
+`ffw_weight_df = (fsdp, tp)`, tunix/models/llama3/model.py:47-82) and lets XLA insert the collectives.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import symm
+
+
+class TPContext:
+    """Process group + symmetric workspaces of one tensor-parallel group."""
+
+    def __init__(self, group=None, device=None, n_aux: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.n_aux = n_aux
+        self.fused = self.world > 1 and self.device.type == "cuda" and symm.symm_available(group)
+        self.barrier = symm.SymmBarrier(self.device, group) if self.fused else None
+        self._gather: dict = {}
+        self._partial: dict = {}
+
+    # ------------------------------------------------------------ workspaces (collective on first use)
+    def gather_ws(self, rows: int, cols: int):
+        key = (rows, cols)
+        ws = self._gather.get(key)
+        if ws is None:
+            buf = symm.symm_empty(rows * cols, torch.bfloat16, self.device, self.group, zero=True)
+            ws = {"buf": buf, "ready": torch.zeros(rows // 128 + 1, dtype=torch.int32, device=self.device), "epoch": 0}
+            self._gather[key] = ws
+        return ws
+
+    def partial_ws(self, M: int, N: int):
+        key = (M, N)
+        ws = self._partial.get(key)
+        if ws is None:
+            ws = {"part": symm.symm_empty(M * N, torch.bfloat16, self.device, self.group, zero=True),
+                  "done": symm.symm_empty(M // 128 + 1, torch.int32, self.device, self.group, zero=True),
+                  "total": ctypes.c_uint(0), "work": torch.zeros(1, dtype=torch.int32, device=self.device)}
+            self._partial[key] = ws
+        return ws
+
+    def fusable(self, M: int, *dims: int) -> bool:
+        return self.fused and M % (128 * self.world) == 0 and all(d % 64 == 0 for d in dims)
+
+    # ----------------------------------------------------------------------------------- primitives
+    def all_gather_rows(self, x_s: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x_s
+        out = torch.empty((x_s.shape[0] * self.world, *x_s.shape[1:]), dtype=x_s.dtype, device=x_s.device)
+        dist.all_gather_into_tensor(out, x_s.contiguous(), group=self.group)
+        return out
+
+    def reduce_scatter_rows(self, y: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return y
+        m = y.shape[0] // self.world
+        if "nccl" in str(dist.get_backend(self.group)):
+            out = torch.empty((m, *y.shape[1:]), dtype=y.dtype, device=y.device)
+            dist.reduce_scatter_tensor(out, y.contiguous(), group=self.group)
+            return out
+        y = y.float().contiguous()       # gloo has no reduce-scatter
+        dist.all_reduce(y, group=self.group)
+        return y[self.rank * m:(self.rank + 1) * m]
+
+    def ag_gemm(self, x_s: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False, bias=None):
+        """gather(x_s) @ op(w)^T. x_s [M/tp, K]; w [N, K] (or [K, N] when w_mn). Returns (y [M, N], gathered x)."""
+        from ..ops import kernels as K
+        m, Kd = x_s.shape
+        M = m * self.world
+        N = w.shape[1] if w_mn else w.shape[0]
+        if not self.fusable(M, Kd):
+            xg = self.all_gather_rows(x_s)
+            y = xg @ (w if w_mn else w.t())
+            return (y if bias is None else y + bias), xg
+        ws = self.gather_ws(M, Kd)
+        buf = ws["buf"]
+        xg = buf.tensor.view(M, Kd)
+        xg[self.rank * m:(self.rank + 1) * m].copy_(x_s)
+        self.barrier.wait()
+        ws["epoch"] += 1
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x_s.device)
+        K.gemm_ag(buf.c_ptrs, self.rank, self.world, 1, M, Kd, w, y, M, N, Kd, ws["ready"], ws["epoch"], other_mn=w_mn,
+                  bias=bias, n_aux=self.n_aux)
+        return y, xg
+
+    def ag_wgrad(self, dy: torch.Tensor, x_s: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False):
+        """dy^T @ gather(x_s): dy [M, N] local in full, x_s [M/tp, K] -> [N, K] (bf16, or into `out`)."""
+        from ..ops import kernels as K
+        m, Kd = x_s.shape
+        M, N = dy.shape
+        if not self.fusable(M, Kd, N):
+            xg = self.all_gather_rows(x_s)
+            g = dy.t().float() @ xg.float()
+            if out is None:
+                return g.to(dy.dtype)
+            return out.add_(g.to(out.dtype)) if accumulate else out.copy_(g)
+        ws = self.gather_ws(M, Kd)
+        buf = ws["buf"]
+        buf.tensor.view(M, Kd)[self.rank * m:(self.rank + 1) * m].copy_(x_s)
+        self.barrier.wait()
+        ws["epoch"] += 1
+        if out is None:
+            out = torch.empty((N, Kd), dtype=torch.bfloat16, device=dy.device)
+        K.gemm_ag(buf.c_ptrs, self.rank, self.world, 3, M, Kd, dy, out, N, Kd, M, ws["ready"], ws["epoch"],
+                  accumulate=accumulate, n_aux=self.n_aux)
+        return out
+
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False, residual_s=None) -> torch.Tensor:
+        """scatter_sum(x @ op(w)^T) (+ residual_s). x [M, K_local]; returns [M/tp, N]."""
+        from ..ops import kernels as K
+        M, Kd = x.shape
+        N = w.shape[1] if w_mn else w.shape[0]
+        if not self.fusable(M, N) or Kd % 8:
+            y = self.reduce_scatter_rows(x @ (w if w_mn else w.t())).to(x.dtype)
+            return y if residual_s is None else y + residual_s
+        ws = self.partial_ws(M, N)
+        self.barrier.wait()
+        out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=x.device)
+        K.gemm_rs(x, w, ws["part"].c_ptrs, ws["done"].c_ptrs, out, ws["total"], ws["work"], self.rank, self.world, M, N, Kd, b_mn=w_mn,
+                  residual=residual_s.contiguous() if residual_s is not None else None, n_aux=self.n_aux)
+        return out
+
+
+def _wgrad_into(w_ref, compute):
+    """Weight gradient either accumulated into `w_ref.main_grad` (fp32 flat buffer) or returned."""
+    mg = getattr(w_ref, "main_grad", None)
+    if mg is not None:
+        compute(mg, True)
+        w_ref.grad_added_to_main_grad = True
+        return None
+    return compute(None, False)
+
+
+class _ColumnSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_s, w, bias, tp: TPContext):
+        y, _ = tp.ag_gemm(x_s, w, bias=bias)
+        ctx.save_for_backward(x_s, w)
+        ctx.tp, ctx.w_ref, ctx.has_bias = tp, w, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_s, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        dx = tp.gemm_rs(dy, w, w_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = _wgrad_into(ctx.w_ref, lambda out, acc: tp.ag_wgrad(dy, x_s, out, acc))
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db, None
+
+
+class _RowSP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, residual_s, tp: TPContext):
+        y_s = tp.gemm_rs(x, w, residual_s=residual_s)
+        ctx.save_for_backward(x, w)
+        ctx.tp, ctx.w_ref, ctx.has_res = tp, w, residual_s is not None
+        return y_s
+
+    @staticmethod
+    def backward(ctx, dy_s):
+        from ..ops import kernels as K
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy_s = dy_s.contiguous()
+        dx, dyg = tp.ag_gemm(dy_s, w, w_mn=True)            # [M, K_local]; dyg = gathered dy [M, N]
+        dw = None
+        if ctx.needs_input_grad[1]:
+            def compute(out, acc):
+                if x.is_cuda and x.dtype == torch.bfloat16:
+                    return K.gemm(dyg, x, a_mn=True, b_mn=True, out=out, accumulate=acc) if out is not None else \
+                        K.gemm(dyg, x, a_mn=True, b_mn=True)
+                g = dyg.t().float() @ x.float()
+                if out is None:
+                    return g.to(x.dtype)
+                return out.add_(g.to(out.dtype)) if acc else out.copy_(g)
+            dw = _wgrad_into(ctx.w_ref, compute)
+        return dx, dw, (dy_s if ctx.has_res else None), None
+
+
+def column_parallel_linear(x_s, w, bias, tp: TPContext):
+    """x_s [..., K] sharded over tokens -> [tp * rows, N_local] for all tokens, this rank's output features."""
+    lead = x_s.shape[:-1]
+    y = _ColumnSP.apply(x_s.reshape(-1, x_s.shape[-1]), w, bias, tp)
+    return y.view(lead[0] * tp.world, *lead[1:], w.shape[0]) if len(lead) > 1 else y
+
+
+def row_parallel_linear(x, w, residual_s, tp: TPContext):
+    """x [..., K_local] for all tokens -> [rows / tp, N] token shard, summed over ranks (+ residual shard)."""
+    lead = x.shape[:-1]
+    r2 = residual_s.reshape(-1, residual_s.shape[-1]) if residual_s is not None else None
+    y = _RowSP.apply(x.reshape(-1, x.shape[-1]), w, r2, tp)
+    return y.view(lead[0] // tp.world, *lead[1:], w.shape[0]) if len(lead) > 1 else y
+
+
+# ------------------------------------------------------------------------------------ model surgery
+def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[0] // world
+    return t[rank * n:(rank + 1) * n].clone()
+
+
+def shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[1] // world
+    return t[:, rank * n:(rank + 1) * n].clone()
+
+
+def apply_tensor_parallel(model, tp: TPContext):
+    """Slice a Transformer's attention and MLP weights for `tp` in place and switch it to the sequence-parallel
+    forward (`Transformer.forward` consults `model.tp`). Heads and the MLP hidden dimension are split over the
+    ranks (kv heads too: num_kv_heads must be divisible by tp); embeddings, norms and lm_head stay replicated
+    and see this rank's token shard only, so their gradients are summed over the group by
+    `allreduce_replicated_grads` before the optimizer step."""
+    cfg = model.config
+    W, r = tp.world, tp.rank
+    if cfg.num_heads % W or cfg.num_kv_heads % W or cfg.hidden_dim % W:
+        raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} and hidden {cfg.hidden_dim} must divide by tp={W}")
+    if cfg.is_moe:
+        raise NotImplementedError("MoE layers use expert parallelism (parallel/ep.py), not tensor parallelism")
+    with torch.no_grad():
+        for layer in model.layers:
+            at, mlp = layer.self_attn, layer.mlp
+            for lin in (at.q_proj, at.k_proj, at.v_proj, mlp.gate_proj, mlp.up_proj):
+                lin.weight = nn.Parameter(shard_rows(lin.weight.data, r, W), requires_grad=lin.weight.requires_grad)
+                if lin.bias is not None:
+                    lin.bias = nn.Parameter(shard_rows(lin.bias.data, r, W), requires_grad=lin.bias.requires_grad)
+                lin.tp, lin.tp_mode = tp, "column"
+            for lin in (at.o_proj, mlp.down_proj):
+                lin.weight = nn.Parameter(shard_cols(lin.weight.data, r, W), requires_grad=lin.weight.requires_grad)
+                lin.tp, lin.tp_mode = tp, "row"
+    model.tp = tp
+    for n, p in model.named_parameters():
+        p.tp_sharded = any(k in n for k in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))
+    return model
+
+
+def allreduce_replicated_grads(model, tp: TPContext) -> None:
+    """Sum over the tp group the gradients of parameters every rank holds in full (they saw different tokens)."""
+    if tp.world == 1:
+        return
+    for p in model.parameters():
+        if getattr(p, "tp_sharded", False):
+            continue
+        g = getattr(p, "main_grad", None)
+        g = g if g is not None else p.grad
+        if g is not None:
+            dist.all_reduce(g, group=tp.group)
+
+
+def grad_sumsq(model, tp: TPContext) -> torch.Tensor:
+    """Squared global gradient norm: sliced parameters contribute once per rank (summed over the group),
+    replicated ones once (their gradients are already identical on all ranks)."""
+    dev = next(model.parameters()).device
+    sharded = torch.zeros((), dtype=torch.float32, device=dev)
+    repl = torch.zeros((), dtype=torch.float32, device=dev)
+    for p in model.parameters():
+        g = getattr(p, "main_grad", None)
+        g = g if g is not None else p.grad
+        if g is None:
+            continue
+        s = g.float().pow(2).sum()
+        if getattr(p, "tp_sharded", False):
+            sharded += s
+        else:
+            repl += s
+    if tp.world > 1:
+        dist.all_reduce(sharded, group=tp.group)
+    return (sharded + repl).reshape(1)
+
+
+def local_batch(model, t: Optional[torch.Tensor]):
+    """This rank's slice of a batch-major tensor under sequence-parallel TP (identity without TP)."""
+    tp = getattr(model, "tp", None)
+    if tp is None or t is None or tp.world == 1:
+        return t
+    n = t.shape[0] // tp.world
+    return t[tp.rank * n:(tp.rank + 1) * n]

@@ -66,8 +66,9 @@ def _default_loss_fn(model, input_tokens, input_mask, positions=None, attention_
     Uses the fused lm_head log-prob path, so [B,T,V] logits are never materialised."""
     hidden, _ = model(input_tokens, positions=positions, attention_mask=attention_mask, segment_ids=segment_ids,
                       skip_lm_head=True)
-    targets = input_tokens[:, 1:]
-    mask = input_mask[:, 1:].to(torch.float32)
+    from ..parallel.tp import local_batch   # under tensor parallelism `hidden` covers this rank's sequences only
+    targets = local_batch(model, input_tokens)[:, 1:]
+    mask = local_batch(model, input_mask)[:, 1:].to(torch.float32)
     logp, _ = model.token_logprobs(hidden[:, :-1], targets)
     nll_sum = -(logp * mask).sum()
     aux = model.aux_loss() if hasattr(model, "aux_loss") else None
@@ -220,9 +221,18 @@ class PeftTrainer:
         import torch.distributed as dist
         if dist.is_initialized() and dist.get_world_size() > 1 and getattr(self.optimizer, "is_sharded", False):
             dist.all_reduce(total)
+        tp = getattr(self.model, "tp", None)
+        if tp is not None and tp.world > 1:
+            dist.all_reduce(total, group=tp.group)      # every tp rank scored its own sequences
         return float(max(total.item(), 1e-8))
 
     def _optimizer_step(self, denominator: float):
+        tp = getattr(self.model, "tp", None)
+        if tp is not None and tp.world > 1:
+            from ..parallel import tp as tp_lib
+            self.optimizer.buffers.collect_autograd_grads()
+            tp_lib.allreduce_replicated_grads(self.model, tp)
+            return self.optimizer.step(denominator, sumsq=tp_lib.grad_sumsq(self.model, tp))
         return self.optimizer.step(denominator)
 
     @torch.no_grad()
@@ -323,7 +333,8 @@ class PeftTrainer:
         return None if buf is None else buf.loss
 
     def _shard_and_move(self, batch):
-        batch = sharding_utils.shard_input(batch, self.config.data_sharding_axis)
+        tp = getattr(self.model, "tp", None)
+        batch = sharding_utils.shard_input(batch, self.config.data_sharding_axis, model_parallel=tp.world if tp else 1)
         if dataclasses.is_dataclass(batch) and not isinstance(batch, type):
             return dataclasses.replace(batch, **{f.name: _to_device(getattr(batch, f.name), self.device)
                                                  for f in dataclasses.fields(batch)})

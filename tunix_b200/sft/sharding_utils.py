@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 
-def _dp_info(axes) -> tuple[int, int]:
+def _dp_info(axes, model_parallel: int = 1) -> tuple[int, int]:
     try:
         from ..parallel import mesh as mesh_lib
         m = mesh_lib.current_mesh()
@@ -25,7 +25,8 @@ def _dp_info(axes) -> tuple[int, int]:
     try:
         import torch.distributed as dist
         if dist.is_initialized():
-            return dist.get_rank(), dist.get_world_size()
+            # without a mesh, ranks of one model-parallel (tensor-parallel) group are adjacent and share a batch
+            return dist.get_rank() // model_parallel, dist.get_world_size() // model_parallel
     except Exception:
         pass
     return 0, 1
@@ -38,8 +39,8 @@ def _shard_leaf(x, rank: int, size: int):
     return x
 
 
-def shard_input(batch: Any, data_sharding_axis=("fsdp",), already_local: bool = False) -> Any:
-    rank, size = _dp_info(data_sharding_axis)
+def shard_input(batch: Any, data_sharding_axis=("fsdp",), already_local: bool = False, model_parallel: int = 1) -> Any:
+    rank, size = _dp_info(data_sharding_axis, model_parallel)
     if size == 1 or already_local or getattr(batch, "_is_local_shard", False):
         return batch
     if isinstance(batch, dict):
