@@ -408,6 +408,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     TileDesc d;
     d.m0 = ((first_m + (r % gsz) + args.rot_m) % num_m) * BM;
     d.n0 = ((r / gsz + args.rot_n) % num_n) * BN;
+    if (args.wait_mode == 2) {
+      // gathered B rows: walk N in groups of 8 tiles (own rows first), all of M inside a group, so that the
+      // tiles of a peer's rows come up only after everything that needs no transfer
+      constexpr int GROUP_N = 8;
+      const int per_gn = GROUP_N * num_m;
+      const int gn = t / per_gn;
+      const int first_n = gn * GROUP_N;
+      const int gszn = min(GROUP_N, num_n - first_n);
+      const int rn = t - gn * per_gn;
+      d.m0 = (rn / gszn) * BM;
+      d.n0 = ((first_n + (rn % gszn) + args.rot_n) % num_n) * BN;
+    }
     d.m_end = M;
     d.kb0 = 0;
     d.kb1 = num_kb;
@@ -707,13 +719,13 @@ std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
 int g_sm_count = 0;
 void set_gemm_attrs();
-// CTAs to give to the copier / reducer role: enough to move `bytes` while the tiles compute `flops`, assuming
+// CTAs to give to the copier role: enough to move `bytes` while the local share of `flops` is computed, assuming
 // about 30 GB/s per CTA (measured: bulk copies with ~190 KiB in flight per CTA over NVLink) and 1.3 PFLOP/s for the tiles.
-int aux_ctas_for(double bytes, double flops) {
-  const double t = flops / 1.3e15;
+int aux_ctas_for(double bytes, double flops, int world) {
+  const double t = flops / 1.3e15 / world;      // the transfer should be over when the local tiles are
   int n = (int)(bytes / (t * 30e9) + 0.999);
   if (n < 2) n = 2;
-  if (n > 32) n = 32;
+  if (n > 24) n = 24;
   return n;
 }
 void clear_fused(GemmArgs& a) {
@@ -892,8 +904,9 @@ TB_API int tb_gemm_grouped_bf16(const void* A, long long a_rows, long long a_col
 //   bf16, symmetric memory; rank r has already written rows [r, r+1) * rows / world of its own copy, and a
 //   cross-rank barrier has run since. The local copy is complete when the kernel ends.
 //   mode 1: gathered array is A [M, K] (K-major);  mode 2: gathered array is B [N, K] (K-major);
-//   mode 3: gathered array is B [K, N] (MN-major, gathered along the contraction), A [K, M] is MN-major too and
-//           local in full (weight gradient of a sequence-parallel layer).
+//   mode 3: gathered array is B [K, N] (MN-major, gathered along the contraction); A is local in full, [K, M]
+//           with GF_A_MN (weight gradient of a sequence-parallel layer) or [M, K] without (input gradient
+//           through row-sharded weights).
 //   other / ld_other: the operand that is not gathered. flags: GF_* epilogue bits (operand layout bits are
 //   implied by the mode). ready: unsigned [rows / 128], local scratch that persists between calls; epoch: a
 //   value that grows by one per call on this buffer.
@@ -912,7 +925,7 @@ TB_API int tb_gemm_ag_bf16(const void* const* gathered, int rank, int world, int
   // the gathered operand's layout is fixed by the mode; the other operand keeps the caller's layout bit
   if (mode == 1) flags &= ~GF_A_MN;
   if (mode == 2) flags &= ~GF_B_MN;
-  if (mode == 3) flags |= GF_A_MN | GF_B_MN;
+  if (mode == 3) flags |= GF_B_MN;       // A keeps the caller's layout: [K, M] (wgrad) or [M, K] (dgrad)
   const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
   const void* local = gathered[rank];
   const void* A = mode == 1 ? local : other;
@@ -920,7 +933,7 @@ TB_API int tb_gemm_ag_bf16(const void* const* gathered, int rank, int world, int
   const long long lda = mode == 1 ? cols : ld_other, ldb = mode == 1 ? ld_other : cols;
   const int num_m = (M + BM - 1) / BM;
   if (world == 1) n_aux = 0;
-  else if (n_aux <= 0) n_aux = aux_ctas_for((double)(rows - rows / world) * cols * 2.0, 2.0 * M * N * K);
+  else if (n_aux <= 0) n_aux = aux_ctas_for((double)(rows - rows / world) * cols * 2.0, 2.0 * M * N * K, world);
   if (n_aux > g_sm_count / 2) n_aux = g_sm_count / 2;
   const int avail = g_sm_count - n_aux;
   int BN = 64;

@@ -46,6 +46,15 @@ class Linear(nn.Module):
         return self.weight
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        comm = getattr(self, "dp_shard", None)
+        if comm is not None:
+            # the weight is this rank's block of rows; the GEMM gathers the rest from the peers as it runs
+            from ..parallel import fsdp3
+            y = fsdp3.sharded_linear(x, self.weight, self.bias, None if self.lora_a is not None else residual, comm)
+            if self.lora_a is not None and self.lora_enabled:
+                y = F.lora_delta(x, self.lora_a, self.lora_b, y, self.lora_scale)
+                return y if residual is None else y + residual
+            return y
         w = self.base_weight()
         if self.lora_a is not None and self.lora_enabled:
             y = F.linear(x, w, self.bias)

@@ -492,7 +492,7 @@ def gemm_ag(gathered_ptrs, rank: int, world: int, mode: int, rows: int, cols: in
     gathered_ptrs / part_ptrs / done_ptrs below are `SymmBuffer.c_ptrs` pointer tables.
     mode 1: A = gathered [M, K]; mode 2: B = gathered [N, K]; mode 3: B = gathered [K, N] and A = other [K, M]."""
     flags = (GF_OUT_F32 if out.dtype == torch.float32 else 0) | (GF_ACCUM if accumulate else 0)
-    if other_mn and mode in (1, 2):
+    if other_mn:
         flags |= GF_B_MN if mode == 1 else GF_A_MN
     if bias is not None:
         flags |= GF_BIAS

@@ -49,13 +49,20 @@ class TPContext:
 
     # ------------------------------------------------------------ workspaces (collective on first use)
     def gather_ws(self, rows: int, cols: int):
+        """Two symmetric buffers per shape, used alternately: a rank refills its rows of buffer i while a slower
+        peer may still be reading buffer i-1; by the time buffer i comes round again every peer has passed the
+        barrier of the call in between, so nobody reads it any more."""
         key = (rows, cols)
-        ws = self._gather.get(key)
-        if ws is None:
-            buf = symm.symm_empty(rows * cols, torch.bfloat16, self.device, self.group, zero=True)
-            ws = {"buf": buf, "ready": torch.zeros(rows // 128 + 1, dtype=torch.int32, device=self.device), "epoch": 0}
-            self._gather[key] = ws
-        return ws
+        pair = self._gather.get(key)
+        if pair is None:
+            pair = {"n": 0, "ws": []}
+            for _ in range(2):
+                buf = symm.symm_empty(rows * cols, torch.bfloat16, self.device, self.group, zero=True)
+                pair["ws"].append({"buf": buf, "epoch": 0,
+                                   "ready": torch.zeros(rows // 128 + 1, dtype=torch.int32, device=self.device)})
+            self._gather[key] = pair
+        pair["n"] += 1
+        return pair["ws"][pair["n"] & 1]
 
     def partial_ws(self, M: int, N: int):
         key = (M, N)
@@ -130,7 +137,57 @@ class TPContext:
         if out is None:
             out = torch.empty((N, Kd), dtype=torch.bfloat16, device=dy.device)
         K.gemm_ag(buf.c_ptrs, self.rank, self.world, 3, M, Kd, dy, out, N, Kd, M, ws["ready"], ws["epoch"],
-                  accumulate=accumulate, n_aux=self.n_aux)
+                  other_mn=True, accumulate=accumulate, n_aux=self.n_aux)
+        return out
+
+    # ---- weights sharded by rows over the group (ZeRO-3 style data parallelism, parallel/fsdp3.py)
+    def gemm_gather_w(self, x: torch.Tensor, w_s: torch.Tensor, bias=None, residual=None) -> torch.Tensor:
+        """x @ gather_rows(w_s)^T: x [M, K] local, w_s [N/W, K] this rank's rows of the weight (mode 2)."""
+        from ..ops import kernels as K
+        n, Kd = w_s.shape
+        N, M = n * self.world, x.shape[0]
+        if not self.fusable(N, Kd):
+            y = x @ self.all_gather_rows(w_s).t()
+            y = y if bias is None else y + bias
+            return y if residual is None else y + residual
+        ws = self.gather_ws(N, Kd)
+        buf = ws["buf"]
+        buf.tensor.view(N, Kd)[self.rank * n:(self.rank + 1) * n].copy_(w_s)
+        self.barrier.wait()
+        ws["epoch"] += 1
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        K.gemm_ag(buf.c_ptrs, self.rank, self.world, 2, N, Kd, x, y, M, N, Kd, ws["ready"], ws["epoch"], bias=bias,
+                  residual=residual, n_aux=self.n_aux)
+        return y
+
+    def gemm_gather_w_t(self, dy: torch.Tensor, w_s: torch.Tensor) -> torch.Tensor:
+        """dy @ gather_rows(w_s): dy [M, N], w_s [N/W, K] -> [M, K]; the gathered rows are the contraction (mode 3)."""
+        from ..ops import kernels as K
+        n, Kd = w_s.shape
+        N, M = n * self.world, dy.shape[0]
+        if not self.fusable(N, Kd):
+            return dy @ self.all_gather_rows(w_s)
+        ws = self.gather_ws(N, Kd)
+        buf = ws["buf"]
+        buf.tensor.view(N, Kd)[self.rank * n:(self.rank + 1) * n].copy_(w_s)
+        self.barrier.wait()
+        ws["epoch"] += 1
+        dx = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy.device)
+        K.gemm_ag(buf.c_ptrs, self.rank, self.world, 3, N, Kd, dy, dx, M, Kd, N, ws["ready"], ws["epoch"], n_aux=self.n_aux)
+        return dx
+
+    def wgrad_scatter(self, dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """scatter_sum_rows(dy^T @ x): dy [M, N], x [M, K] (this rank's tokens) -> [N/W, K] summed over ranks."""
+        from ..ops import kernels as K
+        M, N = dy.shape
+        Kd = x.shape[1]
+        if not self.fusable(N, Kd) or M % 8:
+            return self.reduce_scatter_rows((dy.t().float() @ x.float()).to(dy.dtype)).to(dy.dtype)
+        ws = self.partial_ws(N, Kd)
+        self.barrier.wait()
+        out = torch.empty((N // self.world, Kd), dtype=torch.bfloat16, device=dy.device)
+        K.gemm_rs(dy, x, ws["part"].c_ptrs, ws["done"].c_ptrs, out, ws["total"], ws["work"], self.rank, self.world, N, Kd, M,
+                  a_mn=True, b_mn=True, n_aux=self.n_aux)
         return out
 
     def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False, residual_s=None) -> torch.Tensor:

@@ -224,6 +224,9 @@ class PeftTrainer:
         tp = getattr(self.model, "tp", None)
         if tp is not None and tp.world > 1:
             dist.all_reduce(total, group=tp.group)      # every tp rank scored its own sequences
+        dps = getattr(self.model, "dp_shard", None)
+        if dps is not None and dps.world > 1 and not getattr(self.optimizer, "is_sharded", False):
+            dist.all_reduce(total, group=dps.group)
         return float(max(total.item(), 1e-8))
 
     def _optimizer_step(self, denominator: float):
@@ -233,6 +236,12 @@ class PeftTrainer:
             self.optimizer.buffers.collect_autograd_grads()
             tp_lib.allreduce_replicated_grads(self.model, tp)
             return self.optimizer.step(denominator, sumsq=tp_lib.grad_sumsq(self.model, tp))
+        dps = getattr(self.model, "dp_shard", None)
+        if dps is not None and dps.world > 1:
+            from ..parallel import fsdp3
+            self.optimizer.buffers.collect_autograd_grads()
+            fsdp3.sync_replicated_grads(self.model, dps)
+            return self.optimizer.step(denominator, sumsq=fsdp3.grad_sumsq(self.model, dps))
         return self.optimizer.step(denominator)
 
     @torch.no_grad()
