@@ -1,0 +1,48 @@
+"""Expert parallelism on CPU ranks (gloo): 2 ranks with half the experts and half the batch each == 1 rank."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.parallel import ep as ep_lib
+    from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig.tiny_llama().replace(num_layers=2, vocab_size=256, embed_dim=64, hidden_dim=128, num_heads=4, head_dim=16,
+                                           num_kv_heads=2, num_experts=4, num_experts_per_tok=2, moe_hidden_dim=32)
+    model = create_model(cfg, seed=0)
+    if world > 1:
+        ep_lib.shard_experts(model, ep_lib.EPContext(device="cpu"))
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, 256, (4, 24), generator=g)
+    mask = torch.ones(4, 24)
+    mask[2, :5] = 0
+    tr = PeftTrainer(model, optim.AdamW(1e-2, weight_decay=0.01, max_grad_norm=0.5),
+                     TrainingConfig(eval_every_n_steps=1000, max_steps=3, pbar_description=None))
+    tr.train([TrainingInput(toks, mask)] * 3)
+    torch.save({n: p.detach().clone() for n, p in model.named_parameters()}, f"{out}.{rank}")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_training_matches_single_process(tmp_path):
+    _run(0, 1, 0, str(tmp_path / "one"))
+    mp.spawn(_run, args=(2, 29745, str(tmp_path / "two")), nprocs=2, join=True)
+    one = torch.load(str(tmp_path / "one") + ".0")
+    parts = [torch.load(str(tmp_path / "two") + f".{r}") for r in range(2)]
+    for n, w in one.items():
+        got = torch.cat([p[n] for p in parts], 0) if parts[0][n].shape != w.shape else parts[0][n]
+        assert torch.allclose(got, w, atol=5e-5, rtol=2e-4), (n, (got - w).abs().max())

@@ -9,6 +9,9 @@
 //   moe_scatter_rows  : dst[pos[t, j]] = scale[t, j] * src[t]          (dispatch; combine backward)
 //   moe_gather_sum    : out[t] = sum_j w[t, j] * src[pos[t, j]] (+ res) (combine; dispatch backward with w = 1)
 //   moe_dot_rows      : dw[t, j] = <a[t], b[pos[t, j]]>                 (gradient of the routing weights)
+//   moe_pull_rows     : dst[r] = peer[src_rank[r]][src_row[r]]        (expert-parallel dispatch over NVLink, P2P loads)
+//   moe_gather_sum_peer: out[t] = sum_j peer[dst_rank[t, j]][pos[t, j]] (expert-parallel combine, P2P loads)
+//   moe_row_scale / moe_row_dot : per-row routing weight applied on the expert's side, and its gradient
 //   moe_tiles_rows    : tile list for GEMMs whose output rows are the permuted rows (forward, dgrad)
 //   moe_tiles_expert  : tile list for GEMMs with one output matrix per expert (wgrad), k range = the segment
 //
@@ -122,6 +125,94 @@ __global__ void moe_dot_rows_kernel(const __nv_bfloat16* __restrict__ a, long lo
   if (lane == 0) out[w] = s;
 }
 
+constexpr int MAX_RANKS = 8;
+struct PeerPtrs {
+  const void* p[MAX_RANKS];
+};
+
+// one warp per destination row; rows whose source rank is negative are left alone
+__global__ void moe_pull_rows_kernel(PeerPtrs src, long long lds, const int* __restrict__ src_rank,
+                                     const int* __restrict__ src_row, __nv_bfloat16* __restrict__ dst, long long ldd,
+                                     long long n_rows, int D) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const int r = src_rank[w];
+  if (r < 0) return;
+  const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + (long long)src_row[w] * lds;
+  __nv_bfloat16* d = dst + w * ldd;
+  for (int c = lane * 8; c < D; c += 256) *reinterpret_cast<uint4*>(d + c) = *reinterpret_cast<const uint4*>(s + c);
+}
+
+__global__ void __launch_bounds__(128)
+moe_gather_sum_peer_kernel(PeerPtrs src, long long lds, const int* __restrict__ dst_rank, const int* __restrict__ pos,
+                           const __nv_bfloat16* __restrict__ res, long long ldr, __nv_bfloat16* __restrict__ out,
+                           long long ldo, int k, int D) {
+  const long long t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < D; c += 128 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    if (res != nullptr) {
+      const uint4 u = *reinterpret_cast<const uint4*>(res + t * ldr + c);
+      const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = bf16_lo(in[j]);
+        acc[2 * j + 1] = bf16_hi(in[j]);
+      }
+    }
+    for (int j = 0; j < k; ++j) {
+      const int r = dst_rank[t * k + j];
+      if (r < 0) continue;
+      const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + (long long)pos[t * k + j] * lds;
+      const uint4 u = *reinterpret_cast<const uint4*>(row + c);
+      const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += bf16_lo(in[q]);
+        acc[2 * q + 1] += bf16_hi(in[q]);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + t * ldo + c) =
+        make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
+}
+
+// one warp per row: buf[r] *= scale[r] (out of place when dst != buf)
+__global__ void moe_row_scale_kernel(const __nv_bfloat16* __restrict__ src, long long lds, const float* __restrict__ scale,
+                                     __nv_bfloat16* __restrict__ dst, long long ldd, long long n_rows, int D) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const float f = scale[w];
+  for (int c = lane * 8; c < D; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src + w * lds + c);
+    const uint32_t in[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16(bf16_lo(in[j]) * f, bf16_hi(in[j]) * f);
+    *reinterpret_cast<uint4*>(dst + w * ldd + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// one warp per row: out[r] = <a[r], b[r]>
+__global__ void moe_row_dot_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const __nv_bfloat16* __restrict__ b,
+                                   long long ldb, float* __restrict__ out, long long n_rows, int D) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  float s = 0.f;
+  for (int c = lane * 8; c < D; c += 256) {
+    const uint4 ua = *reinterpret_cast<const uint4*>(a + w * lda + c), ub = *reinterpret_cast<const uint4*>(b + w * ldb + c);
+    const uint32_t x[4] = {ua.x, ua.y, ua.z, ua.w}, y[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s += bf16_lo(x[j]) * bf16_lo(y[j]) + bf16_hi(x[j]) * bf16_hi(y[j]);
+  }
+  s = warp_sum(s);
+  if (lane == 0) out[w] = s;
+}
+
 // single CTA: tiles [expert][m tile of its segment][n tile]
 __global__ void moe_tiles_rows_kernel(const int* __restrict__ seg_off, int E, int num_n, int bn, int kblocks,
                                       int b_rows_per_expert, TileDesc* __restrict__ tiles, int* __restrict__ num_tiles) {
@@ -211,6 +302,51 @@ TB_API int tb_moe_dot_rows(const void* a, long long lda, const void* b, long lon
   if (D % 8 || lda % 8 || ldb % 8) return -2;
   moe_dot_rows_kernel<<<(unsigned)((n + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)a, lda,
                                                                     (const __nv_bfloat16*)b, ldb, pos, out, n, k, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+static PeerPtrs make_peer_ptrs(const void* const* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < MAX_RANKS; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return pp;
+}
+
+// dst[r, :D] = peer[src_rank[r]][src_row[r], :D]; src_ptrs: `world` device pointers (host array), row stride lds.
+TB_API int tb_moe_pull_rows(const void* const* src_ptrs, int world, long long lds, const int* src_rank,
+                            const int* src_row, void* dst, long long ldd, long long n_rows, int D, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || D % 8 || lds % 8 || ldd % 8) return -2;
+  moe_pull_rows_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, stream>>>(make_peer_ptrs(src_ptrs, world), lds, src_rank,
+                                                                          src_row, (__nv_bfloat16*)dst, ldd, n_rows, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_moe_gather_sum_peer(const void* const* src_ptrs, int world, long long lds, const int* dst_rank,
+                                  const int* pos, const void* res, long long ldr, void* out, long long ldo,
+                                  long long n_tokens, int k, int D, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || D % 8 || lds % 8 || ldo % 8 || (res && ldr % 8)) return -2;
+  moe_gather_sum_peer_kernel<<<(unsigned)n_tokens, 128, 0, stream>>>(make_peer_ptrs(src_ptrs, world), lds, dst_rank, pos,
+                                                                     (const __nv_bfloat16*)res, ldr, (__nv_bfloat16*)out,
+                                                                     ldo, k, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_moe_row_scale(const void* src, long long lds, const float* scale, void* dst, long long ldd,
+                            long long n_rows, int D, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (D % 8 || lds % 8 || ldd % 8) return -2;
+  moe_row_scale_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)src, lds, scale,
+                                                                          (__nv_bfloat16*)dst, ldd, n_rows, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+TB_API int tb_moe_row_dot(const void* a, long long lda, const void* b, long long ldb, float* out, long long n_rows,
+                          int D, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (D % 8 || lda % 8 || ldb % 8) return -2;
+  moe_row_dot_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)a, lda,
+                                                                        (const __nv_bfloat16*)b, ldb, out, n_rows, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -190,7 +190,8 @@ class MoELayer(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(E, D, Fd, dtype=dt, device=device))
         self.last_aux_loss: Optional[torch.Tensor] = None
         self.last_routed_experts: Optional[torch.Tensor] = None
-        self.ep_group = None  # set by parallel.ep.shard_experts
+        self.ep = None        # parallel.ep.EPContext once shard_experts has kept this rank's experts
+        self.ep_group = None
 
     def forward(self, x, residual=None, forced_experts: Optional[torch.Tensor] = None):
         cfg = self.cfg

@@ -523,3 +523,52 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, part_ptrs, done_ptrs, out: torch.T
     _lib.check(rc, "tb_gemm_rs_bf16")
     _count()
     return out
+
+
+# ------------------------------------------------------------------ expert-parallel row exchange
+_lib.register_cuda_sigs({
+    "tb_moe_pull_rows": [_lib.P, _lib.I, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.LL, _lib.I, _lib.P],
+    "tb_moe_gather_sum_peer": [_lib.P, _lib.I, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.LL, _lib.LL, _lib.I,
+                               _lib.I, _lib.P],
+    "tb_moe_row_scale": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.LL, _lib.LL, _lib.I, _lib.P],
+    "tb_moe_row_dot": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.P],
+})
+
+
+def moe_pull_rows(src_ptrs, world: int, lds: int, src_rank: torch.Tensor, src_row: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[r] = peer[src_rank[r]][src_row[r]] (src_rank < 0: row left as is). src_ptrs: SymmBuffer.c_ptrs."""
+    rc = _lib.cuda().tb_moe_pull_rows(src_ptrs, world, lds, src_rank.data_ptr(), src_row.data_ptr(), dst.data_ptr(),
+                                      dst.stride(0), src_rank.numel(), dst.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_pull_rows")
+    _count()
+
+
+def moe_gather_sum_peer(src_ptrs, world: int, lds: int, dst_rank: torch.Tensor, pos: torch.Tensor, D: int,
+                        residual=None) -> torch.Tensor:
+    """out[t] = sum_j peer[dst_rank[t, j]][pos[t, j]] (+ residual[t]); dst_rank < 0 skips the slot."""
+    T, k = pos.shape
+    out = torch.empty((T, D), dtype=torch.bfloat16, device=pos.device)
+    rc = _lib.cuda().tb_moe_gather_sum_peer(src_ptrs, world, lds, dst_rank.data_ptr(), pos.data_ptr(), _lib.ptr(residual),
+                                            residual.stride(0) if residual is not None else 0, out.data_ptr(),
+                                            out.stride(0), T, k, D, _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_gather_sum_peer")
+    _count()
+    return out
+
+
+def moe_row_scale(src: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    out = torch.empty_like(src) if out is None else out
+    rc = _lib.cuda().tb_moe_row_scale(src.data_ptr(), src.stride(0), scale.data_ptr(), out.data_ptr(), out.stride(0),
+                                      src.shape[0], src.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_row_scale")
+    _count()
+    return out
+
+
+def moe_row_dot(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(a.shape[0], dtype=torch.float32, device=a.device)
+    rc = _lib.cuda().tb_moe_row_dot(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), a.shape[0],
+                                    a.shape[1], _lib.stream_ptr())
+    _lib.check(rc, "tb_moe_row_dot")
+    _count()
+    return out

@@ -115,3 +115,73 @@ def experts(x, wts, idx, gate_w, up_w, down_w, residual=None, kind: str = "silu"
     counts, seg_off, pos, max_rows = route_positions(idx, E)
     return _ExpertsFn.apply(x.contiguous(), wts.float().contiguous(), pos, seg_off, counts, max_rows, gate_w, up_w,
                             down_w, residual, K.GLU_SILU if kind == "silu" else K.GLU_GELU)
+
+
+class _LocalExpertsFn(torch.autograd.Function):
+    """Experts of one rank on rows that are already in expert order (expert parallelism): the routing weight
+    arrives per row and is applied to the activation before the down projection, so the rows that travel back
+    are ready to be summed, and its gradient <dy, y> is formed here as <dy W_down, h> without keeping y."""
+
+    @staticmethod
+    def forward(ctx, xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind):
+        R, D = xp.shape
+        E, Fd, _ = gate_w.shape
+        dev = xp.device
+        t_up = K.moe_tiles_rows(seg_off, R, Fd, D, Fd)
+        t_down = K.moe_tiles_rows(seg_off, R, D, Fd, D)
+        g = torch.empty((R, Fd), dtype=torch.bfloat16, device=dev)
+        u = torch.empty_like(g)
+        K.gemm_grouped(xp, gate_w.view(E * Fd, D), g, Fd, t_up)
+        K.gemm_grouped(xp, up_w.view(E * Fd, D), u, Fd, t_up)
+        hs = K.moe_row_scale(K.glu_fwd(g, u, kind), wrow)
+        y = torch.empty((R, D), dtype=torch.bfloat16, device=dev)
+        K.gemm_grouped(hs, down_w.view(E * D, Fd), y, D, t_down)
+        ctx.save_for_backward(xp, g, u, wrow, seg_off, gate_w, up_w, down_w)
+        ctx.kind = kind
+        ctx.w_refs = (gate_w, up_w, down_w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xp, g, u, wrow, seg_off, gate_w, up_w, down_w = ctx.saved_tensors
+        E, Fd, D = gate_w.shape
+        R, dev = xp.shape[0], dy.device
+        dy = dy.contiguous()
+        h = K.glu_fwd(g, u, ctx.kind)
+
+        def wgrad(a, b, w_ref, m_out, n_out):
+            tl = K.moe_tiles_expert(seg_off, m_out, n_out)
+            mg = getattr(w_ref, "main_grad", None)
+            if mg is not None:
+                K.gemm_grouped(a, b, mg.view(E, m_out, n_out), n_out, tl, a_mn=True, b_mn=True, accumulate=True)
+                w_ref.grad_added_to_main_grad = True
+                return None
+            dw = torch.empty((E, m_out, n_out), dtype=torch.bfloat16, device=dev)
+            K.gemm_grouped(a, b, dw, n_out, tl, a_mn=True, b_mn=True)
+            return dw
+
+        gw_ref, uw_ref, dw_ref = ctx.w_refs
+        dhp = torch.empty((R, Fd), dtype=torch.bfloat16, device=dev)
+        K.gemm_grouped(dy, down_w.view(E * D, Fd), dhp, Fd, K.moe_tiles_rows(seg_off, R, Fd, D, D), b_mn=True)
+        dwrow = K.moe_row_dot(dhp, h) if ctx.needs_input_grad[1] else None
+        d_down = None
+        if ctx.needs_input_grad[6]:
+            hs = K.moe_row_scale(h, wrow)
+            d_down = wgrad(dy, hs, dw_ref, D, Fd)
+        dh = K.moe_row_scale(dhp, wrow, out=dhp)
+        dg, du = K.glu_bwd(dh, g, u, ctx.kind, inplace=True)
+        d_gate = wgrad(dg, xp, gw_ref, Fd, D) if ctx.needs_input_grad[4] else None
+        d_up = wgrad(du, xp, uw_ref, Fd, D) if ctx.needs_input_grad[5] else None
+        dxp = None
+        if ctx.needs_input_grad[0]:
+            t_dx = K.moe_tiles_rows(seg_off, R, D, Fd, Fd)
+            dxp = xp
+            K.gemm_grouped(dg, gate_w.view(E * Fd, D), dxp, D, t_dx, b_mn=True)
+            K.gemm_grouped(du, up_w.view(E * Fd, D), dxp, D, t_dx, b_mn=True, accumulate=True)
+        return dxp, dwrow, None, None, d_gate, d_up, d_down, None
+
+
+def local_experts(xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind: str = "silu"):
+    """y[r] = wrow[r] * expert_of_segment(r)(xp[r]) for rows laid out in this rank's expert segments."""
+    return _LocalExpertsFn.apply(xp, wrow.float().contiguous(), seg_off, counts, gate_w, up_w, down_w,
+                                 K.GLU_SILU if kind == "silu" else K.GLU_GELU)

@@ -34,7 +34,7 @@ def _experts_on_rows(layer, xs: torch.Tensor, counts, first_expert: int = 0) -> 
 
 def expert_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     """x [T, D]; weights, idx [T, k]. Returns sum_k w * expert_{idx}(x)  [T, D]."""
-    if getattr(layer, "ep_group", None) is not None:
+    if getattr(layer, "ep", None) is not None and layer.ep.world > 1:
         from . import ep
         return ep.expert_parallel_forward(layer, x, weights, idx)
     T, D = x.shape
