@@ -8,6 +8,7 @@
 //  * reduce_scatter_pull: out32[shard] = scale * sum_p grad_p[shard]  + sum of squares, in one pass
 //                         (gradient reduce-scatter fused with cast/scale and the grad-norm partial)
 //  * allgather_pull     : full_params[all shards] = peers' updated bf16 shards
+//  * pull_blocks        : dst block = a peer's block, for a table of 2-D blocks (trainer -> rollout weight reshard)
 //
 // Parameters are sharded per tensor along dim 0: a tensor of `len` elements at `full_off` in the
 // flat buffer is owned in W contiguous pieces of `rank_stride = len / W`; rank r keeps piece r at
@@ -164,6 +165,46 @@ __global__ void gather_shard_kernel(const __nv_bfloat16* __restrict__ full, cons
   }
 }
 
+// One 2-D block of a weight transfer: `rows` runs of `cols` bf16 elements (cols % 8 == 0), read from rank
+// `src_rank`'s staging buffer at element offset src_off (row stride src_ld) and written to the local
+// destination at dst_off (row stride dst_ld). A contiguous slice is a block with one row.
+struct Block2D {
+  long long src_off, dst_off, src_ld, dst_ld;
+  int src_rank, rows, cols, pad;
+};
+
+__global__ void __launch_bounds__(512)
+pull_blocks_kernel(PeerPtrs src, const Block2D* __restrict__ blocks, int nblocks, __nv_bfloat16* __restrict__ dst) {
+  // the whole grid walks every block: NVLink latency is covered by the bytes in flight (4 vectors per thread)
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int b = 0; b < nblocks; ++b) {
+    const Block2D bl = blocks[b];
+    const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.p[bl.src_rank]) + bl.src_off;
+    __nv_bfloat16* d = dst + bl.dst_off;
+    const int vpr = bl.cols >> 3;
+    const long long total = (long long)bl.rows * vpr;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long i = i0 + j * stride;
+        if (i < total) {
+          const long long r = i / vpr;
+          v[j] = *reinterpret_cast<const uint4*>(s + r * bl.src_ld + ((int)(i - r * vpr) << 3));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long i = i0 + j * stride;
+        if (i < total) {
+          const long long r = i / vpr;
+          *reinterpret_cast<uint4*>(d + r * bl.dst_ld + ((int)(i - r * vpr) << 3)) = v[j];
+        }
+      }
+    }
+  }
+}
+
 PeerPtrs make_ptrs(const void* const* ptrs, int world) {
   PeerPtrs pp;
   for (int i = 0; i < MAX_RANKS; ++i) pp.p[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
@@ -217,5 +258,15 @@ TB_API int tb_gather_shard(const void* full, const void* chunks, int nchunks, in
   gather_shard_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(full),
                                                 reinterpret_cast<const Chunk*>(chunks), nchunks, rank,
                                                 shard32, reinterpret_cast<__nv_bfloat16*>(shard16));
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// dst[block] = peer[block.src_rank][block] for a device-resident table of Block2D (48 bytes each).
+TB_API int tb_pull_blocks(const void* const* src_ptrs, int world, const void* blocks, int nblocks, void* dst,
+                          cudaStream_t stream) {
+  if (nblocks <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS) return -2;
+  pull_blocks_kernel<<<296, 512, 0, stream>>>(make_ptrs(src_ptrs, world), reinterpret_cast<const Block2D*>(blocks),
+                                               nblocks, reinterpret_cast<__nv_bfloat16*>(dst));
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
