@@ -184,3 +184,28 @@ def test_adamw_matches_torch():
     ss = torch.zeros(1, device="cuda")
     k.sumsq(g, ss)
     assert abs(ss.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+
+
+@pytest.mark.parametrize("M,N,K_,a_mn,b_mn", [(2048, 2048, 512, False, False), (4096, 1536, 1024, False, True),
+                                              (2304, 2048, 768, True, True), (2000, 2100, 320, False, False),
+                                              (8192, 4096, 4096, False, False)])
+def test_gemm_cta_pair_tiles(M, N, K_, a_mn, b_mn):
+    """Problems with a wave of 256 x 256 tiles run on CTA pairs (tcgen05.mma.cta_group::2): layouts, ragged edges,
+    bias / residual / alpha, fp32 accumulation into an existing buffer."""
+    k = _k()
+    torch.manual_seed(5)
+    A = torch.randn((K_, M) if a_mn else (M, K_), device="cuda", dtype=torch.bfloat16)
+    B = (torch.randn((K_, N) if b_mn else (N, K_), device="cuda") * 0.05).to(torch.bfloat16)
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    out = k.gemm(A, B, a_mn=a_mn, b_mn=b_mn)
+    _check_status()
+    assert _rel_err(out, ref) < 5e-3
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out2 = k.gemm(A, B, a_mn=a_mn, b_mn=b_mn, bias=bias, residual=res, alpha=0.25)
+    _check_status()
+    assert _rel_err(out2, 0.25 * ref + bias.float() + res.float()) < 5e-3
+    acc = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+    k.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
+    _check_status()
+    assert _rel_err(acc, ref + 2.0) < 2e-3

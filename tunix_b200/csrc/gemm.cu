@@ -741,6 +741,10 @@ int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int 
                        long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
                        int* status, cudaStream_t stream);
 
+int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                     int* status, cudaStream_t stream);
+
 tb_encode_tiled_fn tb_get_encode_tiled() {
   static tb_encode_tiled_fn fn = nullptr;
   static std::once_flag once;
@@ -813,6 +817,11 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
     // skinny problems: 128x256 tiles with the K range split over a cluster (gemm_splitk.cu)
     const int sk = tb_gemm_splitk_try(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream);
     if (sk != 0) return sk < 0 ? sk : 0;
+  }
+  if (max_ctas <= 0) {
+    // large problems: 256x256 tiles on CTA pairs (gemm_2cta.cu)
+    const int tc = tb_gemm_2cta_try(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream);
+    if (tc != 0) return tc < 0 ? tc : 0;
   }
   // Tile width: the widest N tile that still gives every SM work. Large problems use 128x256; skinny
   // ones (decode: M <= 128) fall to 128x64 / 128x32 so that >= 100 CTAs stream the weight matrix.

@@ -1,0 +1,398 @@
+// Two-SM bf16 GEMM for sm_100a: a pair of CTAs (a 2-CTA cluster) computes one 256 x 256 output tile with
+// `tcgen05.mma.cta_group::2`.
+//
+//   C[M,N] = epilogue( A[M,K] * B[N,K]^T )            fp32 accumulation in TMEM
+//
+// Why: with one CTA per tile a 128 x 256 tile has to pull 48 KiB of operands through the SM's L2 port for every
+// 512 tensor-core cycles, more than the port delivers, and the tensor pipe idles a quarter of the time (ncu:
+// 74 % active on the single-CTA kernel). In a CTA pair each CTA stages its own 128 rows of A and only HALF of
+// the B tile (128 of its 256 rows); the pair's MMA reads both halves, so every CTA moves 32 KiB per 512 cycles
+// for the same math. No TMA multicast is involved: each CTA loads its own halves.
+//
+//   * cluster (2,1,1); CTA rank 0 is the leader and issues every MMA, rank 1 contributes shared memory and TMEM
+//   * warp 0 (both CTAs): TMA producer for the CTA's own A / B halves; the loads carry `.cta_group::2` so that
+//     their transaction bytes complete on the LEADER's full barrier, which the leader's producer arms with the
+//     bytes of both CTAs
+//   * warp 1 (leader): one thread issues 4 MMAs (M 256, N 256, K 16) per stage, then commits the stage's empty
+//     barrier in both CTAs (two plain commits, own and peer address) and, per tile, the accumulator-full barrier
+//     in both CTAs
+//   * warps 2..5 (both CTAs): epilogue for the CTA's 128 rows, TMEM double-buffered; "accumulator free" arrives
+//     on the leader's barrier from all eight epilogue warps (remote mbarrier arrive for the peer)
+//   * 6 stages x 32 KiB, TMEM 2 x 256 columns per CTA, every wait bounded, cluster barrier before teardown
+//
+// Operand layouts (K-major / MN-major) and epilogue flags are those of gemm.cu.
+#include "common.cuh"
+#include <cstdlib>
+
+using namespace tb;
+
+namespace {
+
+constexpr int BM = 256, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int HM = 128, HN = 128;                  // rows of A and of B staged by one CTA
+constexpr int STAGES = 6;
+constexpr int A_BYTES = HM * BK * 2, B_BYTES = HN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GROUP_M = 8;
+
+enum { GF_A_MN = 1, GF_B_MN = 2, GF_OUT_F32 = 4, GF_ACCUM = 8, GF_BIAS = 16, GF_RESIDUAL = 32 };
+
+struct Args2 {
+  int M, N, K, flags;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* resid;
+  long long ldr;
+  float alpha;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on a barrier (own or peer, cluster address) when the MMAs issued so far by this thread have retired
+__device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// TMA tile load into this CTA's shared memory whose bytes complete on a barrier given by cluster address
+__device__ __forceinline__ void tma2_load_2d(uint32_t smem_dst, const CUtensorMap* tm, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args2 args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // used in the leader only
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };           // one per CTA
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };       // one per CTA
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };  // used in the leader only
+  volatile uint32_t* tmem_ptr_smem =
+      reinterpret_cast<volatile uint32_t*>(smem_al + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int M = args.M, N = args.N, K = args.K;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_kb = (K + BK - 1) / BK;
+  const int num_tiles = num_m * num_n;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const bool a_mn = args.flags & GF_A_MN, b_mn = args.flags & GF_B_MN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 8);       // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(smem_u32((const void*)tmem_ptr_smem), 2 * BN);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  cluster_sync_all();                    // barriers of both CTAs exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  auto tile_coords = [&](int t, int& mt, int& nt) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(GROUP_M, num_m - first_m);
+    const int r = t - g * per_group;
+    mt = first_m + (r % gsz);
+    nt = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (own halves of A and B)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int mt, nt;
+        tile_coords(t, mt, nt);
+        const int m0 = mt * BM + (int)rank * HM, n0 = nt * BN + (int)rank * HN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, args.status, ST_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t fb = mapa_u32(full_bar(stage), 0);           // the leader's barrier for this stage
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!a_mn) {
+            tma2_load_2d(sa, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HM / 64; ++j) tma2_load_2d(sa + j * 8192, &tmA, fb, m0 + 64 * j, k0);
+          }
+          if (!b_mn) {
+            tma2_load_2d(sb, &tmB, fb, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HN / 64; ++j) tma2_load_2d(sb + j * 8192, &tmB, fb, n0 + 64 * j, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (leader && elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
+      const uint32_t a_lbo = a_mn ? 8192u : 16u, b_lbo = b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = a_mn ? 2048u : 32u, b_kstep = b_mn ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1, abort_flag, args.status, ST_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, args.status, ST_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            umma2_f16_ss(tmem_d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit(empty_bar(stage));                              // frees the stage here ...
+          umma2_commit(mapa_u32(empty_bar(stage), 1));                 // ... and in the peer
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma2_commit(tfull_bar(acc));
+        umma2_commit(mapa_u32(tfull_bar(acc), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (own 128 rows)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = args.flags & GF_OUT_F32, accum = args.flags & GF_ACCUM;
+    const bool has_bias = args.flags & GF_BIAS, has_res = args.flags & GF_RESIDUAL;
+    const float alpha = args.alpha;
+    const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;
+    const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
+    const uint32_t tempty_leader0 = mapa_u32(tempty_bar(0), 0), tempty_leader1 = mapa_u32(tempty_bar(1), 0);
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int mt, nt;
+      tile_coords(t, mt, nt);
+      const int row = mt * BM + (int)rank * HM + q * 32 + lane;
+      const int n0 = nt * BN;
+      if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < M) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+          const bool full = (col0 + 32 <= N);
+          if (has_bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (full || col0 + i < N) v[i] += __bfloat162float(args.bias[col0 + i]);
+          }
+          if (has_res) {
+            const __nv_bfloat16* rp = args.resid + (long long)row * args.ldr + col0;
+            if (full && (args.ldr % 8 == 0) && r_al16) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const uint4 u = reinterpret_cast<const uint4*>(rp)[g];
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  v[g * 8 + 2 * j] += bf16_lo(w[j]);
+                  v[g * 8 + 2 * j + 1] += bf16_hi(w[j]);
+                }
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) v[i] += __bfloat162float(rp[i]);
+            }
+          }
+          if (out_f32) {
+            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col0;
+            if (full && (args.ldc % 4 == 0) && c_al16) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                float4 o = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                if (accum) {
+                  const float4 p = reinterpret_cast<float4*>(cp)[g];
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                reinterpret_cast<float4*>(cp)[g] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) cp[i] = accum ? cp[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col0;
+            if (full && (args.ldc % 8 == 0) && c_al16) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (accum) {
+                  const uint4 u = reinterpret_cast<uint4*>(cp)[g];
+                  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    v[g * 8 + 2 * j] += bf16_lo(w[j]);
+                    v[g * 8 + 2 * j + 1] += bf16_hi(w[j]);
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+                o.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+                o.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+                o.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+                reinterpret_cast<uint4*>(cp)[g] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) cp[i] = __float2bfloat16(v[i] + (accum ? __bfloat162float(cp[i]) : 0.f));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc == 0 ? tempty_leader0 : tempty_leader1);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let TMA copies that may still be in flight land
+  }
+  cluster_sync_all();                    // the peer may still read this CTA's shared memory / write its TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 2 * BN);
+  }
+}
+
+int g_sms2 = 0;
+
+}  // namespace
+
+// Returns 1 when the problem was launched here, 0 when it is left to the single-CTA kernel, negative on error.
+int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                     int* status, cudaStream_t stream) {
+  static const bool off = getenv("TUNIX_B200_NO_2CTA") != nullptr;
+  if (off) return 0;
+  if (g_sms2 == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms2, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaFuncSetAttribute(gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return -5;
+  }
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+  const int pairs = g_sms2 / 2;
+  // worth it when the pairs have at least a wave of 256 x 256 tiles and the K loop amortises the prologue
+  if (N < 256 || M < 256 || K < 256 || (long long)num_m * num_n < (pairs * 3) / 5) return 0;
+  const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, HM, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
+  if (r) return -3;
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, HN, BK, 1);
+  else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
+  if (r) return -4;
+  Args2 a;
+  a.M = M; a.N = N; a.K = K; a.flags = flags; a.C = C; a.ldc = ldc;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  a.ldr = ldr; a.alpha = alpha; a.status = status;
+  const int tiles = num_m * num_n;
+  const int use_pairs = tiles < pairs ? tiles : pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * use_pairs, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm2_kernel, tmA, tmB, a) != cudaSuccess) return -5;
+  return 1;
+}
