@@ -47,7 +47,7 @@ def _time(fn, iters: int, warmup: int = 3, flush: bool = True):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "adamw", "logsoftmax", "sample",
-                                       "glu", "moe"])
+                                       "glu", "moe", "paged_decode"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -132,6 +132,19 @@ def main(argv=None) -> int:
         ms = _time(lambda: S.sample(z, 1.0, None, None, 1, 0, want_logprob=True), args.iters, args.warmup)
         gb = 3.0 * z.numel() * 4 / ms / 1e6
         out.update(shape=[args.rows, args.vocab], ms=ms, gbs_3pass=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "paged_decode":
+        Bn, ctx, N, KH, H, page = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim, 64
+        max_pages = (ctx + page - 1) // page
+        kp = torch.randn(Bn * max_pages, page, KH * H, device=dev, dtype=bf)
+        vp = torch.randn_like(kp)
+        table = torch.randperm(Bn * max_pages, device=dev).int().view(Bn, max_pages)
+        lens = torch.full((Bn,), ctx, device=dev, dtype=torch.int32)
+        slots = torch.arange(Bn, device=dev, dtype=torch.int32)
+        q = torch.randn(Bn, N, H, device=dev, dtype=bf)
+        ms = _time(lambda: K.paged_decode(q, kp, vp, table, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=ctx,
+                                          scale=1.0 / math.sqrt(H)), args.iters, args.warmup)
+        gb = 2.0 * Bn * ctx * KH * H * 2 / ms / 1e6
+        out.update(shape=[Bn, ctx, N, KH, H], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
     elif args.kernel == "moe":
         from tunix_b200.ops import moe
         T, E, k, D, Fd = args.rows, args.experts, args.topk, args.dim, args.ffn
