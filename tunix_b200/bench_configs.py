@@ -1,0 +1,274 @@
+"""Runners for the benchmark configurations other than the headline SFT one (which is `bench.py`):
+
+    python -m tunix_b200.bench_configs tiny_lora_cpu
+    python -m tunix_b200.bench_configs grpo  [--layers L] [--prompts P] [--steps S]      (torchrun for > 1 GPU)
+    python -m tunix_b200.bench_configs dpo   [--layers L] [--pairs N]
+    python -m tunix_b200.bench_configs moe   [--layers L]                                (torchrun; experts over ranks)
+
+All use synthetic uniform token ids and random-init weights. `--layers` shrinks a model so that a configuration
+fits fewer GPUs than it was specified for; the JSON line names the layer count that actually ran, so a reduced
+run cannot be mistaken for the full one. Times are CUDA-event times, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+class IdTokenizer:
+    """Token ids written as space-separated integers: lets string-based APIs carry synthetic ids."""
+
+    def __init__(self, vocab: int, eos: int = -1, pad: int = 0, bos=None):
+        self.vocab, self._eos, self._pad, self._bos = vocab, eos, pad, bos
+
+    def encode(self, s, **_):
+        return [int(t) for t in s.split()] if isinstance(s, str) else list(s)
+
+    def decode(self, ids, **_):
+        return " ".join(str(int(i)) for i in ids)
+
+    def bos_id(self):
+        return self._bos
+
+    def eos_id(self):
+        return self._eos
+
+    def pad_id(self):
+        return self._pad
+
+
+def _dist():
+    if "RANK" in os.environ and not dist.is_initialized():
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        dist.init_process_group("nccl")
+    return (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
+
+
+def _max_over_ranks(x: float, dev) -> float:
+    if not dist.is_initialized():
+        return x
+    t = torch.tensor([x], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def tiny_lora_cpu(args) -> dict:
+    """Config 1: tiny Llama-style decoder, fp32, LoRA r=8 on q/v, 20 AdamW steps, against a plain PyTorch oracle."""
+    from . import lora, optim
+    from .common.configs import TrainingConfig
+    from .models.config import ModelConfig
+    from .models.transformer import create_model
+    from .sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig(family="llama3", num_layers=2, vocab_size=1024, embed_dim=256, hidden_dim=1024, num_heads=4, head_dim=64,
+                      num_kv_heads=2, norm_eps=1e-6, rope_theta=10000.0, dtype=torch.float32, max_position=128)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, 1024, (4, 128), generator=g)
+    mask = torch.zeros(4, 128)
+    mask[:, 64:] = 1
+
+    def run(native: bool):
+        model = create_model(cfg, seed=0)
+        lora.apply_lora_to_model(model, lora.LoraProvider(module_path=r".*(q_proj|v_proj)", rank=8, alpha=16.0), seed=0)
+        if native:
+            tr = PeftTrainer(model, optim.AdamW(1e-3, weight_decay=0.0), TrainingConfig(eval_every_n_steps=10 ** 9, max_steps=20,
+                                                                                         pbar_description=None))
+            tr.train([TrainingInput(toks, mask)] * 20)
+            return tr.metrics_logger.get_metric_history("", "loss", "train")
+        params = [p for n, p in model.named_parameters() if "lora_" in n]
+        for n, p in model.named_parameters():
+            p.requires_grad_("lora_" in n)
+        opt = torch.optim.AdamW(params, lr=1e-3, weight_decay=0.0, betas=(0.9, 0.999), eps=1e-8)
+        losses = []
+        for _ in range(20):
+            logits = model(toks)[0].float()
+            lp = torch.log_softmax(logits[:, :-1], -1).gather(-1, toks[:, 1:, None].long()).squeeze(-1)
+            loss = -(lp * mask[:, 1:]).sum() / mask[:, 1:].sum()
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        return losses
+    ours, oracle = run(True), run(False)
+    return {"config": "tiny_lora_cpu", "steps": 20, "loss_first": ours[0], "loss_last": ours[-1],
+            "max_abs_diff_vs_pytorch_fp32": float(np.max(np.abs(np.asarray(ours) - np.asarray(oracle))))}
+
+
+def grpo(args) -> dict:
+    """Config 3: Qwen3-8B GRPO, colocated sampler, 64 prompts x 8 generations, prompt 256, up to 768 sampled tokens."""
+    from . import optim
+    from .common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+    from .models.config import get_config
+    from .models.transformer import create_model
+    from .parallel import fsdp
+    from .rl.algorithm_config import GRPOConfig
+    from .rl.grpo.grpo_learner import GRPOLearner
+    from .rl.rl_cluster import RLCluster
+    rank, world = _dist()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = get_config("qwen3_8b").replace(dtype=torch.bfloat16, max_position=1032)
+    if args.layers:
+        cfg = cfg.replace(num_layers=args.layers)
+    actor = create_model(cfg, device=dev, seed=0)
+    ref = create_model(cfg, device=dev, seed=0)
+    for p in ref.parameters():
+        p.requires_grad_(False)
+    tok = IdTokenizer(cfg.vocab_size)
+    G = 8
+    per_rank = max(args.prompts // world, 1)
+    opt = fsdp.ShardedAdamW(1e-6, max_grad_norm=1.0) if world > 1 else optim.AdamW(1e-6, max_grad_norm=1.0)
+    tcfg = RLTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, actor_optimizer=opt, mini_batch_size=per_rank * G,
+                            train_micro_batch_size=args.micro, rollout_micro_batch_size=per_rank * G,
+                            compute_logps_micro_batch_size=args.micro * 2, pbar_description=None)
+    rc = RolloutConfig(max_tokens_to_generate=768, max_prompt_length=256, temperature=1.0, top_p=1.0, seed=2,
+                       kv_cache_size=1032, eos_tokens=[-1])
+    cluster = RLCluster(actor=actor, reference=ref, tokenizer=tok,
+                        cluster_config=ClusterConfig(role_to_mesh={}, training_config=tcfg, rollout_config=rc, rollout_engine="paged"))
+
+    def reward(prompts, completions, completion_ids=None, completion_lengths=None, **_):
+        out = []
+        for ids, n in zip(completion_ids, completion_lengths):
+            ids = np.asarray(ids[:int(n)])
+            out.append(float((ids % 7 == 0).mean() if len(ids) else 0.0) - 0.001 * float(n))
+        return out
+    learner = GRPOLearner(cluster, GRPOConfig(num_generations=G, beta=0.04, epsilon=0.2), [reward])
+    rng = np.random.default_rng(2 + rank)
+    data = [{"prompts": [" ".join(map(str, rng.integers(3, cfg.vocab_size, 256))) for _ in range(per_rank)]}
+            for _ in range(args.steps)]
+    times = []
+    orig = learner._generate_and_compute_advantage
+    roll_t = []
+
+    def timed(*a, **kw):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        r = orig(*a, **kw)
+        torch.cuda.synchronize()
+        roll_t.append(time.perf_counter() - t0)
+        return r
+    learner._generate_and_compute_advantage = timed
+    for step, batch in enumerate(data):
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()
+        t0 = time.perf_counter()
+        cluster.cluster_config.training_config.max_steps = step + 1
+        learner.tcfg.max_steps = step + 1
+        learner.train([batch])
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    step_s = _max_over_ranks(times[-1], dev)
+    gen_tokens = per_rank * G * 768 * world
+    return {"config": "grpo_qwen3_8b", "n_gpus": world, "layers": cfg.num_layers, "prompts": per_rank * world, "generations": G,
+            "step_seconds": step_s, "first_step_seconds": _max_over_ranks(times[0], dev),
+            "rollout_and_scoring_seconds": _max_over_ranks(roll_t[-1], dev) if roll_t else None,
+            "rollout_tokens_per_step": gen_tokens, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}
+
+
+def dpo(args) -> dict:
+    """Config 4: Gemma-2-9B DPO with LoRA r=16 on all linear layers, 32 pairs of 512 + 512 tokens per step."""
+    from . import lora, optim
+    from .models.config import get_config
+    from .models.transformer import create_model
+    from .sft.dpo.dpo_trainer import DPOTrainer, DPOTrainingConfig, TrainingInput
+    rank, world = _dist()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = get_config("gemma2_9b").replace(dtype=torch.bfloat16, max_position=1024)
+    if args.layers:
+        cfg = cfg.replace(num_layers=args.layers)
+    model = create_model(cfg, device=dev, seed=0)
+    lora.apply_lora_to_model(model, lora.LoraProvider(rank=16, alpha=32.0), seed=0)
+    pairs = max(args.pairs // world, 1)
+    tc = DPOTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, beta=0.1, max_prompt_length=512, max_response_length=512,
+                           pbar_description=None, gradient_accumulation_steps=max(pairs // args.micro, 1))
+    tr = DPOTrainer(model, None, optim.AdamW(5e-6), tc)
+    g = torch.Generator().manual_seed(3 + rank)
+    mb = min(args.micro, pairs)
+
+    def batch():
+        def ids(n):
+            return torch.randint(3, cfg.vocab_size, (mb, n), generator=g)
+        ones = torch.ones(mb, 512)
+        return TrainingInput(prompt_ids=ids(512), prompt_mask=ones, chosen_ids=ids(512), chosen_mask=ones, rejected_ids=ids(512),
+                             rejected_mask=ones)
+    accum = max(pairs // mb, 1)
+    times = []
+    for step in range(args.steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tr.config.max_steps = step + 1
+        tr.train([batch() for _ in range(accum)])
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / 1e3)
+    return {"config": "dpo_gemma2_9b_lora", "n_gpus": world, "layers": cfg.num_layers, "pairs_per_step": pairs * world,
+            "step_seconds": _max_over_ranks(float(np.median(times[1:] or times)), dev),
+            "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}
+
+
+def moe(args) -> dict:
+    """Config 5: Qwen3-30B-A3B SFT with the experts spread over the ranks, global batch 32 x 4096."""
+    from . import optim
+    from .common.configs import TrainingConfig
+    from .models.config import get_config
+    from .models.transformer import create_model
+    from .parallel import ep as ep_lib
+    from .sft.peft_trainer import PeftTrainer, TrainingInput
+    rank, world = _dist()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = get_config("qwen3_30b_a3b").replace(dtype=torch.bfloat16, max_position=4096, router_aux_loss_coef=0.001)
+    if args.layers:
+        cfg = cfg.replace(num_layers=args.layers)
+    model = create_model(cfg, device=dev, seed=0)
+    if world > 1:
+        ep_lib.shard_experts(model, ep_lib.EPContext(device=dev))
+    seqs = max(32 // world, 1)
+    mb = min(args.micro, seqs)
+    tr = PeftTrainer(model, optim.AdamW(2e-5, max_grad_norm=1.0),
+                     TrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, pbar_description=None,
+                                    gradient_accumulation_steps=seqs // mb))
+    g = torch.Generator().manual_seed(4 + rank)
+    times = []
+    for step in range(args.steps):
+        batches = [{"input_tokens": torch.randint(0, cfg.vocab_size, (mb, 4096), generator=g).to(dev, torch.int32),
+                    "input_mask": torch.ones(mb, 4096, device=dev), "_is_local_shard": True} for _ in range(seqs // mb)]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tr.config.max_steps = step + 1
+        tr.train(batches)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / 1e3)
+    sec = _max_over_ranks(float(np.median(times[1:] or times)), dev)
+    return {"config": "moe_qwen3_30b_a3b_sft", "n_gpus": world, "layers": cfg.num_layers, "global_batch": seqs * world, "seq_len": 4096,
+            "step_seconds": sec, "tokens_per_sec": seqs * world * 4096 / sec, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("config", choices=["tiny_lora_cpu", "grpo", "dpo", "moe"])
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--prompts", type=int, default=64)
+    ap.add_argument("--pairs", type=int, default=32)
+    ap.add_argument("--micro", type=int, default=4)
+    args = ap.parse_args(argv)
+    res = {"tiny_lora_cpu": tiny_lora_cpu, "grpo": grpo, "dpo": dpo, "moe": moe}[args.config](args)
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        print(json.dumps(res))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
