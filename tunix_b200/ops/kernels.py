@@ -572,3 +572,45 @@ def moe_row_dot(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     _lib.check(rc, "tb_moe_row_dot")
     _count()
     return out
+
+
+# ------------------------------------------------------------------ RL token math
+_lib.register_cuda_sigs({
+    "tb_policy_loss": [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.F, _lib.F, _lib.F, _lib.I,
+                       _lib.F, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P],
+    "tb_gae_scan": [_lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P],
+})
+
+KL_MODES = {"kl": 0, "mse_kl": 1, "low_var_kl": 2}
+
+
+def policy_loss(logp, old_logp, ref_logp, adv, mask, is_w, eps_lo: float, eps_hi: float, eps_c, kl_mode: str, kl_clamp):
+    """Clipped policy objective and KL per token with their derivatives w.r.t. logp (see csrc/rl_loss.cu).
+    Returns (pg, dpg, kl, dkl, flags[2]); kl / dkl are None without a reference."""
+    B, T = logp.shape
+    f = lambda t: None if t is None else t.detach().float().contiguous()  # noqa: E731
+    logp_, old_, ref_, adv_, mask_, isw_ = f(logp), f(old_logp), f(ref_logp), f(adv), f(mask), f(is_w)
+    pg, dpg = torch.empty_like(logp_), torch.empty_like(logp_)
+    kl = torch.empty_like(logp_) if ref_ is not None else None
+    dkl = torch.empty_like(logp_) if ref_ is not None else None
+    flags = torch.empty((2, B, T), dtype=torch.float32, device=logp.device)
+    rc = _lib.cuda().tb_policy_loss(logp_.data_ptr(), _lib.ptr(old_), _lib.ptr(ref_), adv_.data_ptr(), 1 if adv_.dim() == 2 else 0,
+                                    mask_.data_ptr(), _lib.ptr(isw_), B, T, float(eps_lo), float(eps_hi),
+                                    float(eps_c) if eps_c else 0.0, KL_MODES[kl_mode], float(kl_clamp) if kl_clamp else 0.0,
+                                    pg.data_ptr(), dpg.data_ptr(), _lib.ptr(kl), _lib.ptr(dkl), flags.data_ptr(),
+                                    _lib.stream_ptr())
+    _lib.check(rc, "tb_policy_loss")
+    _count()
+    return pg, dpg, kl, dkl, flags
+
+
+def gae_scan(rewards, values, mask, gamma: float, lam: float):
+    """Reverse GAE scan over [B, T] fp32 tensors; returns (advantages before masking, returns)."""
+    r, v = rewards.float().contiguous(), values.float().contiguous()
+    m = None if mask is None else mask.float().contiguous()
+    adv, ret = torch.empty_like(r), torch.empty_like(r)
+    rc = _lib.cuda().tb_gae_scan(r.data_ptr(), v.data_ptr(), _lib.ptr(m), r.shape[0], r.shape[1], float(gamma), float(lam),
+                                 adv.data_ptr(), ret.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_gae_scan")
+    _count()
+    return adv, ret

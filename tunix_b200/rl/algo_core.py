@@ -45,6 +45,12 @@ def compute_gae_advantages(rewards, values, mask, gamma: float = 1.0, gae_lambda
     Masked steps pass the running state through unchanged. Returns (advantages, returns)."""
     r, v, m = rewards.float(), values.float(), mask.float()
     B, T = r.shape
+    if r.is_cuda:
+        from ..ops import kernels as K
+        adv, returns = K.gae_scan(r, v, m, gamma, gae_lambda)        # one thread per sequence walks T backwards
+        if whiten:
+            adv = masked_whiten(adv, m)
+        return adv * m, returns
     adv = torch.zeros_like(r)
     next_v = torch.zeros(B, device=r.device)
     last = torch.zeros(B, device=r.device)
@@ -121,6 +127,30 @@ def ppo_value_loss_fn(model, train_example, algo_config, pad_id, eos_id, **kwarg
 
 
 # ------------------------------------------------------------------- GRPO loss
+class _PolicyLossFn(torch.autograd.Function):
+    """Token-level clipped objective (+ KL) from `csrc/rl_loss.cu`; backward applies the kernel's derivatives."""
+
+    @staticmethod
+    def forward(ctx, logp, old, ref, adv, mask, is_w, eps, eps_high, eps_c, kl_mode, kl_clamp):
+        from ..ops import kernels as K
+        pg, dpg, kl, dkl, flags = K.policy_loss(logp, old, ref, adv, mask, is_w, eps, eps_high, eps_c, kl_mode, kl_clamp)
+        ctx.save_for_backward(dpg, dkl if dkl is not None else dpg)
+        ctx.has_kl = kl is not None
+        ctx.mark_non_differentiable(flags)
+        if kl is None:
+            kl = torch.zeros((), device=logp.device)
+            ctx.mark_non_differentiable(kl)
+        return pg, kl, flags
+
+    @staticmethod
+    def backward(ctx, g_pg, g_kl, _g_flags):
+        dpg, dkl = ctx.saved_tensors
+        g = g_pg * dpg
+        if ctx.has_kl and g_kl is not None:
+            g = g + g_kl * dkl
+        return (g,) + (None,) * 10
+
+
 @function_registry.register_policy_loss_fn("grpo")
 def grpo_loss_fn(model, train_example, algo_config, pad_id, eos_id, **kwargs) -> LossOutput:
     beta, eps = algo_config.beta, algo_config.epsilon
@@ -180,34 +210,52 @@ def grpo_loss_fn(model, train_example, algo_config, pad_id, eos_id, **kwargs) ->
             scnt = common.segment_sum(maskf, comp_seg, S)
             s = (ssum / scnt.clamp(min=1.0)).gather(1, comp_seg.long().clamp(0, S - 1))
         lr = (safe_new - safe_new.detach() + s.detach()).clamp(-10.0, 10.0)
-    ratio = torch.exp(lr)
-    if adv.dim() == 1:
-        adv = adv[:, None].expand_as(ratio)
-    adv = torch.where(active & torch.isfinite(adv), adv, torch.zeros_like(adv))
-    l1 = -adv * ratio
-    l2 = -adv * ratio.clamp(1.0 - eps, 1.0 + eps_high)
-    loss = torch.maximum(l1, l2)
-    clipfrac = ((l2 > l1).float() * maskf).sum() / token_denom.clamp(min=1.0)
+    fused_tokens = logp.is_cuda and loss_algo == "grpo"
     aux = {}
-    if eps_c is not None:
-        l3 = -eps_c * adv
-        lower = (loss > l3) & (adv < 0)
-        loss = torch.where(adv < 0, torch.minimum(l3, loss), loss)
-        lo = common.aggregate_loss(lower.float(), maskf, mode, comp_seg, num_segments)
-        aux["pg_clipfrac_lower"] = (lo.sum / lo.denominator.clamp(min=lo.min_denominator or 1e-8)).detach()
-    if is_w is not None:
-        wts = torch.where(active, is_w.float().detach(), torch.zeros_like(loss))
-        loss = loss * wts
-        aux["sampler_is/weight_mean"] = ((wts * maskf).sum() / token_denom.clamp(min=1.0)).detach()
+    kl_fused = None
+    if fused_tokens:
+        # ratio, clipping, dual clip, importance weight and KL in one kernel; gradients come from its derivatives
+        loss, kl_fused, flags = _PolicyLossFn.apply(
+            logp, None if on_policy else old, train_example.ref_per_token_logps, adv, completion_mask.float(),
+            None if is_w is None else is_w.float(), eps, eps_high, eps_c, algo_config.kl_loss_mode, algo_config.kl_clamp_value)
+        clipfrac = (flags[0] * maskf).sum() / token_denom.clamp(min=1.0)
+        if eps_c is not None:
+            lo = common.aggregate_loss(flags[1], maskf, mode, comp_seg, num_segments)
+            aux["pg_clipfrac_lower"] = (lo.sum / lo.denominator.clamp(min=lo.min_denominator or 1e-8)).detach()
+        if is_w is not None:
+            wts = torch.where(active, is_w.float().detach(), torch.zeros_like(loss))
+            aux["sampler_is/weight_mean"] = ((wts * maskf).sum() / token_denom.clamp(min=1.0)).detach()
+    else:
+        ratio = torch.exp(lr)
+        if adv.dim() == 1:
+            adv = adv[:, None].expand_as(ratio)
+        adv = torch.where(active & torch.isfinite(adv), adv, torch.zeros_like(adv))
+        l1 = -adv * ratio
+        l2 = -adv * ratio.clamp(1.0 - eps, 1.0 + eps_high)
+        loss = torch.maximum(l1, l2)
+        clipfrac = ((l2 > l1).float() * maskf).sum() / token_denom.clamp(min=1.0)
+        if eps_c is not None:
+            l3 = -eps_c * adv
+            lower = (loss > l3) & (adv < 0)
+            loss = torch.where(adv < 0, torch.minimum(l3, loss), loss)
+            lo = common.aggregate_loss(lower.float(), maskf, mode, comp_seg, num_segments)
+            aux["pg_clipfrac_lower"] = (lo.sum / lo.denominator.clamp(min=lo.min_denominator or 1e-8)).detach()
+        if is_w is not None:
+            wts = torch.where(active, is_w.float().detach(), torch.zeros_like(loss))
+            loss = loss * wts
+            aux["sampler_is/weight_mean"] = ((wts * maskf).sum() / token_denom.clamp(min=1.0)).detach()
     norm = kwargs.get("loss_norm")
     pg = common.aggregate_loss(loss, maskf, mode, comp_seg, num_segments, norm=norm)
     total_sum = pg.sum
     aux["reduced_pg_loss"] = common.reduced_loss_agg(loss, maskf, mode, comp_seg, num_segments, norm=norm)
     aux["unreduced_pg_loss"] = (pg.sum / pg.denominator.clamp(min=pg.min_denominator or 1e-8)).detach()
     if train_example.ref_per_token_logps is not None:
-        kl = common.compute_kl_divergence(logp, train_example.ref_per_token_logps, algo_config.kl_loss_mode,
-                                          algo_config.kl_clamp_value)
-        kl = torch.where(active, kl, torch.zeros_like(kl))
+        if kl_fused is not None:
+            kl = kl_fused
+        else:
+            kl = common.compute_kl_divergence(logp, train_example.ref_per_token_logps, algo_config.kl_loss_mode,
+                                              algo_config.kl_clamp_value)
+            kl = torch.where(active, kl, torch.zeros_like(kl))
         klagg = common.aggregate_loss(kl, maskf, mode, comp_seg, num_segments, norm=norm)
         aux["kl"] = ((kl * maskf).sum() / token_denom.clamp(min=1.0)).detach()
         aux["kl_loss"] = (klagg.sum / klagg.denominator.clamp(min=klagg.min_denominator or 1e-8)).detach()
