@@ -137,32 +137,31 @@ def grpo(args) -> dict:
             ids = np.asarray(ids[:int(n)])
             out.append(float((ids % 7 == 0).mean() if len(ids) else 0.0) - 0.001 * float(n))
         return out
-    learner = GRPOLearner(cluster, GRPOConfig(num_generations=G, beta=0.04, epsilon=0.2), [reward])
+    learner = GRPOLearner(cluster, [reward], GRPOConfig(num_generations=G, beta=0.04, epsilon=0.2))
     rng = np.random.default_rng(2 + rank)
     data = [{"prompts": [" ".join(map(str, rng.integers(3, cfg.vocab_size, 256))) for _ in range(per_rank)]}
             for _ in range(args.steps)]
-    times = []
     orig = learner._generate_and_compute_advantage
-    roll_t = []
+    roll_t, starts = [], []
 
     def timed(*a, **kw):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
+        starts.append(t0)
         r = orig(*a, **kw)
         torch.cuda.synchronize()
         roll_t.append(time.perf_counter() - t0)
         return r
     learner._generate_and_compute_advantage = timed
-    for step, batch in enumerate(data):
-        torch.cuda.synchronize()
-        if dist.is_initialized():
-            dist.barrier()
-        t0 = time.perf_counter()
-        cluster.cluster_config.training_config.max_steps = step + 1
-        learner.tcfg.max_steps = step + 1
-        learner.train([batch])
-        torch.cuda.synchronize()
-        times.append(time.perf_counter() - t0)
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    t_begin = time.perf_counter()
+    learner.train(data)                      # a step = rollout + scoring + reference log-probs + update + weight sync
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    bounds = starts + [t_end]
+    times = [bounds[i + 1] - bounds[i] for i in range(len(starts))] or [t_end - t_begin]
     step_s = _max_over_ranks(times[-1], dev)
     gen_tokens = per_rank * G * 768 * world
     return {"config": "grpo_qwen3_8b", "n_gpus": world, "layers": cfg.num_layers, "prompts": per_rank * world, "generations": G,
@@ -203,8 +202,8 @@ def dpo(args) -> dict:
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        tr.config.max_steps = step + 1
-        tr.train([batch() for _ in range(accum)])
+        for i in range(accum):
+            tr._train_step(tr._prepare_inputs(batch()), i == accum - 1)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) / 1e3)
@@ -242,8 +241,8 @@ def moe(args) -> dict:
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        tr.config.max_steps = step + 1
-        tr.train(batches)
+        for i, b in enumerate(batches):
+            tr._train_step(b, i == len(batches) - 1)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) / 1e3)

@@ -84,11 +84,14 @@ class _LoraDeltaFn(torch.autograd.Function):
     def forward(ctx, x, a, b, base, scale):
         x2 = _flat2d(x)
         t = K.gemm(x2, a)                                   # [M, r]
-        y = K.gemm(t, b, residual=_flat2d(base), alpha=scale)
+        # allocated with its final shape: a consumer (the in-place RoPE) may overwrite the output, which autograd
+        # forbids for a view made inside this Function
+        y = torch.empty(base.shape, dtype=torch.bfloat16, device=x.device)
+        K.gemm(t, b, residual=_flat2d(base), alpha=scale, out=y.view(-1, base.shape[-1]))
         ctx.save_for_backward(x2, a, b, t)
         ctx.scale = scale
         ctx.x_shape = x.shape
-        return y.view(base.shape)
+        return y
 
     @staticmethod
     def backward(ctx, dy):

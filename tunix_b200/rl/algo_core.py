@@ -219,6 +219,13 @@ def grpo_loss_fn(model, train_example, algo_config, pad_id, eos_id, **kwargs) ->
             logp, None if on_policy else old, train_example.ref_per_token_logps, adv, completion_mask.float(),
             None if is_w is None else is_w.float(), eps, eps_high, eps_c, algo_config.kl_loss_mode, algo_config.kl_clamp_value)
         clipfrac = (flags[0] * maskf).sum() / token_denom.clamp(min=1.0)
+        with torch.no_grad():       # diagnostics below want the ratio and both branches of the objective
+            ratio = torch.exp(lr.detach())
+            if adv.dim() == 1:
+                adv = adv[:, None].expand_as(ratio)
+            adv = torch.where(active & torch.isfinite(adv), adv, torch.zeros_like(adv))
+            l1 = -adv * ratio
+            l2 = -adv * ratio.clamp(1.0 - eps, 1.0 + eps_high)
         if eps_c is not None:
             lo = common.aggregate_loss(flags[1], maskf, mode, comp_seg, num_segments)
             aux["pg_clipfrac_lower"] = (lo.sum / lo.denominator.clamp(min=lo.min_denominator or 1e-8)).detach()
