@@ -89,7 +89,20 @@ def has_gpu() -> bool:
     return torch.cuda.is_available()
 
 
+_home_device = None
+
+
 def stream_ptr() -> int:
+    """Stream of the calling thread on this process's GPU. One process drives one GPU; a helper thread (rollout
+    producer, agentic loop, engine group) starts with CUDA device 0 current, so its launches would go to the
+    wrong GPU on every rank but the first: such a thread is moved to the process's device on its first launch."""
+    global _home_device
+    cur = torch.cuda.current_device()
+    if _home_device is None:
+        if threading.current_thread() is threading.main_thread():
+            _home_device = cur
+    elif cur != _home_device and threading.current_thread() is not threading.main_thread():
+        torch.cuda.set_device(_home_device)
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -127,7 +127,7 @@ def grpo(args) -> dict:
                             train_micro_batch_size=args.micro, rollout_micro_batch_size=per_rank * G,
                             compute_logps_micro_batch_size=args.micro * 2, pbar_description=None)
     rc = RolloutConfig(max_tokens_to_generate=768, max_prompt_length=256, temperature=1.0, top_p=1.0, seed=2,
-                       kv_cache_size=1032, eos_tokens=[-1])
+                       kv_cache_size=1032, eos_tokens=[-1], max_running_requests=args.max_running)
     cluster = RLCluster(actor=actor, reference=ref, tokenizer=tok,
                         cluster_config=ClusterConfig(role_to_mesh={}, training_config=tcfg, rollout_config=rc, rollout_engine="paged"))
 
@@ -259,6 +259,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=64)
     ap.add_argument("--pairs", type=int, default=32)
     ap.add_argument("--micro", type=int, default=4)
+    ap.add_argument("--max-running", type=int, default=256, help="sequences decoded together by the rollout engine")
     args = ap.parse_args(argv)
     res = {"tiny_lora_cpu": tiny_lora_cpu, "grpo": grpo, "dpo": dpo, "moe": moe}[args.config](args)
     if not dist.is_initialized() or dist.get_rank() == 0:
