@@ -313,11 +313,6 @@ class Transformer(nn.Module):
                 skip_lm_head: bool = False, output_hidden_states: bool = False):
         cfg = self.config
         B, T = input_tokens.shape
-        dev = input_tokens.device
-        if positions is None:
-            start = 0 if cache is None else cache[0]["end"]
-            positions = torch.arange(start, start + T, device=dev, dtype=torch.int32)[None].expand(B, T)
-        positions = positions.to(torch.int32).contiguous()
         emb_tokens = input_tokens
         if self.tp is not None and self.tp.world > 1:
             # sequence-parallel residual stream: this rank embeds its B/tp sequences; attention sees all of them
@@ -326,6 +321,22 @@ class Transformer(nn.Module):
             n = B // self.tp.world
             emb_tokens = input_tokens[self.tp.rank * n:(self.tp.rank + 1) * n]
         x = F.embedding(emb_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
+        return self.forward_embeddings(x, positions=positions, cache=cache, attention_mask=attention_mask,
+                                       segment_ids=segment_ids, skip_lm_head=skip_lm_head,
+                                       output_hidden_states=output_hidden_states, batch_shape=(B, T))
+
+    def forward_embeddings(self, x, positions=None, cache=None, attention_mask=None, segment_ids=None,
+                           skip_lm_head: bool = False, output_hidden_states: bool = False, batch_shape=None):
+        """The decoder stack on input embeddings `x` (what `forward` runs after the token lookup; multimodal front
+        ends call it with image soft tokens spliced in). `batch_shape` = (B, T) of the full batch when `x` is this
+        rank's shard of it."""
+        cfg = self.config
+        B, T = batch_shape if batch_shape is not None else x.shape[:2]
+        dev = x.device
+        if positions is None:
+            start = 0 if cache is None else cache[0]["end"]
+            positions = torch.arange(start, start + T, device=dev, dtype=torch.int32)[None].expand(B, T)
+        positions = positions.to(torch.int32).contiguous()
         new_cache = [] if cache is not None else None
         use_remat = cfg.remat_config != RematConfig.NONE and torch.is_grad_enabled() and cache is None
         hook = self.layer_grad_hook if (torch.is_grad_enabled() and cache is None) else None
