@@ -222,7 +222,10 @@ def moe(args) -> dict:
     from .sft.peft_trainer import PeftTrainer, TrainingInput
     rank, world = _dist()
     dev = torch.device("cuda", torch.cuda.current_device())
-    cfg = get_config("qwen3_30b_a3b").replace(dtype=torch.bfloat16, max_position=4096, router_aux_loss_coef=0.001)
+    from .models.config import RematConfig
+    # per-layer recompute: the permuted expert activations of 48 layers do not fit next to the optimizer state
+    cfg = get_config("qwen3_30b_a3b").replace(dtype=torch.bfloat16, max_position=4096, router_aux_loss_coef=0.001,
+                                              remat_config=RematConfig.DECODER)
     if args.layers:
         cfg = cfg.replace(num_layers=args.layers)
     model = create_model(cfg, device=dev, seed=0)
