@@ -209,3 +209,16 @@ def test_gemm_cta_pair_tiles(M, N, K_, a_mn, b_mn):
     k.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
     _check_status()
     assert _rel_err(acc, ref + 2.0) < 2e-3
+
+
+@pytest.mark.parametrize("shape,block", [((256, 512), 64), ((100, 72), 32), ((3, 50), 64)])
+def test_nf4_dequant_kernel_matches_reference(shape, block):
+    from tunix_b200.lora import NF4Weight
+    torch.manual_seed(3)
+    w = torch.randn(*shape, device="cuda", dtype=torch.bfloat16)
+    q = NF4Weight(w, block)
+    got = q.dequantize()
+    _check_status()
+    cpu = NF4Weight(w.cpu(), block).dequantize()
+    assert got.shape == w.shape and torch.allclose(got.float().cpu(), cpu.float(), atol=1e-2, rtol=1e-2)
+    assert (got.float() - w.float()).abs().mean() < 0.15

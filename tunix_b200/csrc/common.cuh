@@ -134,6 +134,15 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with `launch_pdl` may start while its predecessor in the stream is still running: its
+// prologue (barrier init, TMEM allocation, tensor-map prefetch, index arithmetic) overlaps the predecessor's
+// tail. `pdl_wait()` blocks until every prerequisite grid has completed and its writes are visible; it must come
+// before the first read of anything a predecessor wrote and before any global write. `pdl_trigger()` lets the
+// NEXT kernel start launching. Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -298,5 +307,25 @@ typedef CUresult (*tb_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint
                                        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 tb_encode_tiled_fn tb_get_encode_tiled();
 // 2-D bf16 row-major tensor [rows, cols] with row stride ld (elements); box = [box_rows, box_cols].
+// Host side: whether launches of PDL-aware kernels carry the programmatic-serialization attribute
+// (tb_set_pdl, off by default), and the launcher that applies it.
+bool tb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = tb_pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int tb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                          uint64_t ld, uint32_t box_rows, uint32_t box_cols, int swizzle128);

@@ -56,6 +56,8 @@ qkv_post_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, const int* __rest
                 const float* __restrict__ sin_t, const int* __restrict__ page_table, int max_pages, int page_size,
                 __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, int n_tok, int N, int KH) {
   constexpr int HALF = H / 2, E = H / 64;          // elements per lane in each half
+  pdl_trigger();
+  pdl_wait();
   const int heads = N + 2 * KH;
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= (long long)n_tok * heads) return;
@@ -150,6 +152,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
   constexpr int TILE_BYTES = TILE_KEYS * H * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(128) uint8_t q_s[16 * H * 2];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = KH * G;
@@ -319,6 +323,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                             const int* __restrict__ seq_lens, int N, int H, int num_splits, int window,
                                             __nv_bfloat16* __restrict__ out, long long ldo) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x, n = blockIdx.y;
   const int len = seq_lens[b];
   const int used = min(num_splits, (len + SPLIT_TOKENS - 1) / SPLIT_TOKENS);
@@ -353,9 +359,8 @@ int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q,
       return -5;
     attr_set = true;
   }
-  paged_decode_kernel<H><<<grid, 128, SMEM, stream>>>(q, ldq, kp, vp, pt, max_pages, page_size, seq_ids, seq_lens, KH,
-                                                      G, scale, softcap, window, splits, pa, pml);
-  return 0;
+  return launch_pdl(paged_decode_kernel<H>, grid, dim3(128), SMEM, stream, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids,
+                    seq_lens, KH, G, scale, softcap, window, splits, pa, pml) == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace
@@ -383,11 +388,11 @@ TB_API int tb_qkv_post(void* qkv, long long ld, const int* seq_ids, const int* p
   if (ld % 8) return -2;
   const long long warps = (long long)n_tok * (N + 2 * KH);
   const int grid = (int)((warps + 7) / 8);
+  cudaError_t err = cudaSuccess;
 #define QP(HV)                                                                                                     \
-  qkv_post_kernel<HV><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, seq_ids, pos, (const __nv_bfloat16*)qw,   \
-                                                (const __nv_bfloat16*)kw, eps, add_one, cos_t, sin_t, page_table,  \
-                                                max_pages, page_size, (__nv_bfloat16*)k_pool,                      \
-                                                (__nv_bfloat16*)v_pool, n_tok, N, KH)
+  err = launch_pdl(qkv_post_kernel<HV>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, ld, seq_ids, pos,     \
+                   (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, eps, add_one, cos_t, sin_t, page_table,       \
+                   max_pages, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_tok, N, KH)
   switch (H) {
     case 64: QP(64); break;
     case 128: QP(128); break;
@@ -395,7 +400,7 @@ TB_API int tb_qkv_post(void* qkv, long long ld, const int* seq_ids, const int* p
     default: return -2;
   }
 #undef QP
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return err == cudaSuccess ? 0 : -5;
 }
 
 // q [B, N*H]; pools [num_pages, page_size, KH*H]; page_table [*, max_pages]; seq_ids [B]; seq_lens [B];
@@ -422,7 +427,6 @@ TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, con
     default: return -2;
   }
   if (rc) return rc;
-  paged_decode_combine_kernel<<<dim3(B, N), 128, 0, stream>>>(part_acc, part_ml, seq_lens, N, H, splits, window,
-                                                               (__nv_bfloat16*)out, ldo);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_pdl(paged_decode_combine_kernel, dim3(B, N), dim3(128), 0, stream, (const float*)part_acc,
+                    (const float*)part_ml, seq_lens, N, H, splits, window, (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : -5;
 }

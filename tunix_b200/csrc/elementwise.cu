@@ -71,6 +71,8 @@ rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const
                        __nv_bfloat16* __restrict__ y, long long ldy, float* __restrict__ rstd_out, int D, float eps,
                        float add_one) {
   __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * ldx;
   float v[VPT][8];
@@ -224,6 +226,8 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ g, long long ld
                                const __nv_bfloat16* __restrict__ u, long long ldu,
                                __nv_bfloat16* __restrict__ h, long long ldh, long long rows, int F,
                                int kind) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_row = F >> 3;
   const long long total = rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -269,6 +273,8 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids,
                                      const __nv_bfloat16* __restrict__ table, long long ldt,
                                      __nv_bfloat16* __restrict__ out, long long ldo,
                                      long long tokens, int D, int vocab, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_row = D >> 3;
   const long long total = tokens * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -336,10 +342,11 @@ TB_API int tb_rmsnorm_fwd(const void* x, long long ldx, const void* w, void* y, 
     auto xx = (const __nv_bfloat16*)x;
     auto ww = (const __nv_bfloat16*)w;
     auto yy = (__nv_bfloat16*)y;
-    if (D <= 2048) rmsnorm_fwd_row_kernel<2><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
-    else if (D <= 4096) rmsnorm_fwd_row_kernel<4><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
-    else rmsnorm_fwd_row_kernel<8><<<rows, 128, 0, stream>>>(xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
-    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+    cudaError_t e;
+    if (D <= 2048) e = launch_pdl(rmsnorm_fwd_row_kernel<2>, dim3(rows), dim3(128), 0, stream, xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    else if (D <= 4096) e = launch_pdl(rmsnorm_fwd_row_kernel<4>, dim3(rows), dim3(128), 0, stream, xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    else e = launch_pdl(rmsnorm_fwd_row_kernel<8>, dim3(rows), dim3(128), 0, stream, xx, ldx, ww, yy, ldy, rstd, D, eps, add_one);
+    return e == cudaSuccess ? 0 : -5;
   }
   const int block = 256;
   rmsnorm_fwd_kernel<<<grid_for((long long)rows * 32, block), block, 0, stream>>>(
@@ -380,10 +387,8 @@ TB_API int tb_glu_fwd(const void* g, long long ldg, const void* u, long long ldu
                       long long ldh, long long rows, int F, int kind, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F % 8) return -2;
-  glu_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, stream>>>(
-      (const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)h, ldh, rows, F,
-      kind);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_pdl(glu_fwd_kernel, dim3(grid_for(rows * (F / 8), 256)), dim3(256), 0, stream, (const __nv_bfloat16*)g, ldg,
+                    (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)h, ldh, rows, F, kind) == cudaSuccess ? 0 : -5;
 }
 
 TB_API int tb_glu_bwd(const void* dh, long long lddh, const void* g, long long ldg, const void* u,
@@ -402,9 +407,8 @@ TB_API int tb_embedding_fwd(const int* ids, const void* table, long long ldt, vo
                             cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (D % 8) return -2;
-  embedding_fwd_kernel<<<grid_for(tokens * (D / 8), 256), 256, 0, stream>>>(
-      ids, (const __nv_bfloat16*)table, ldt, (__nv_bfloat16*)out, ldo, tokens, D, vocab, scale);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_pdl(embedding_fwd_kernel, dim3(grid_for(tokens * (D / 8), 256)), dim3(256), 0, stream, ids,
+                    (const __nv_bfloat16*)table, ldt, (__nv_bfloat16*)out, ldo, tokens, D, vocab, scale) == cudaSuccess ? 0 : -5;
 }
 
 TB_API int tb_embedding_bwd(const int* ids, const void* dout, long long ldo, void* dtable,

@@ -390,10 +390,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_alloc(smem_u32((const void*)tmem_ptr_smem), C_::TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  pdl_wait();            // everything above overlapped the previous kernel's tail; from here on memory is read
 
   const bool grouped = args.tiles != nullptr;
   const int total_tiles = grouped ? *args.num_tiles_dev : num_tiles;
@@ -787,6 +789,13 @@ int tb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint
   return 0;
 }
 
+namespace {
+bool g_pdl = false;
+}
+bool tb_pdl_enabled() { return g_pdl; }
+// Programmatic dependent launch for the kernels that support it (decode path): 1 = on.
+TB_API void tb_set_pdl(int on) { g_pdl = on != 0; }
+
 // Forget cached tensor maps (call when device memory is released back to the driver).
 TB_API void tb_tmap_cache_clear() {
   std::lock_guard<std::mutex> lk(g_tmap_mu);
@@ -855,13 +864,14 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
   set_gemm_attrs();
+  cudaError_t err;
   switch (BN) {
-    case 256: gemm_bf16_kernel<256><<<ctas, 192, Cfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    case 128: gemm_bf16_kernel<128><<<ctas, 192, Cfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    case 64: gemm_bf16_kernel<64><<<ctas, 192, Cfg<64>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
-    default: gemm_bf16_kernel<32><<<ctas, 192, Cfg<32>::SMEM_BYTES, stream>>>(tmA, tmB, args); break;
+    case 256: err = launch_pdl(gemm_bf16_kernel<256>, dim3(ctas), dim3(192), Cfg<256>::SMEM_BYTES, stream, tmA, tmB, args); break;
+    case 128: err = launch_pdl(gemm_bf16_kernel<128>, dim3(ctas), dim3(192), Cfg<128>::SMEM_BYTES, stream, tmA, tmB, args); break;
+    case 64: err = launch_pdl(gemm_bf16_kernel<64>, dim3(ctas), dim3(192), Cfg<64>::SMEM_BYTES, stream, tmA, tmB, args); break;
+    default: err = launch_pdl(gemm_bf16_kernel<32>, dim3(ctas), dim3(192), Cfg<32>::SMEM_BYTES, stream, tmA, tmB, args); break;
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return err == cudaSuccess ? 0 : -5;
 }
 
 // Grouped GEMM over a device-resident tile list (see TileDesc). The arrays are described by their full

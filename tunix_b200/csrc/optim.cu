@@ -206,3 +206,55 @@ TB_API int tb_cast_bf16_f32(const void* in, float* out, long long n, float scale
                                                                 scale, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+
+// ------------------------------------------------------------------ NF4 dequantisation (QLoRA base weights)
+// packed: two 4-bit codes per byte (high nibble first), absmax: one fp32 per `block` values. Writes bf16.
+// One thread expands 8 bytes = 16 values and writes two 16-byte vectors; the 16-entry codebook sits in registers
+// through a constant table. The frozen base weight is expanded once per use into a scratch tensor that the GEMM
+// reads; nothing else of the 4-bit weight is ever materialised.
+namespace {
+__constant__ float kNf4Code[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                   -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                   0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                   0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+
+__global__ void nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmax, int block,
+                                   __nv_bfloat16* __restrict__ out, long long numel) {
+  const long long n16 = (numel + 15) / 16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) {
+    const long long base = i * 16;
+    const uint2 bytes = *reinterpret_cast<const uint2*>(packed + i * 8);
+    const uint32_t w[2] = {bytes.x, bytes.y};
+    float v[16];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const uint32_t byte = (w[b >> 2] >> ((b & 3) * 8)) & 0xFFu;
+      v[2 * b] = kNf4Code[byte >> 4];
+      v[2 * b + 1] = kNf4Code[byte & 0xF];
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] *= absmax[(base + j) / block];
+    if (base + 16 <= numel) {
+      uint4 o0, o1;
+      o0.x = pack_bf16(v[0], v[1]); o0.y = pack_bf16(v[2], v[3]); o0.z = pack_bf16(v[4], v[5]); o0.w = pack_bf16(v[6], v[7]);
+      o1.x = pack_bf16(v[8], v[9]); o1.y = pack_bf16(v[10], v[11]); o1.z = pack_bf16(v[12], v[13]); o1.w = pack_bf16(v[14], v[15]);
+      reinterpret_cast<uint4*>(out + base)[0] = o0;
+      reinterpret_cast<uint4*>(out + base)[1] = o1;
+    } else {
+      for (int j = 0; j < 16 && base + j < numel; ++j) out[base + j] = __float2bfloat16(v[j]);
+    }
+  }
+}
+}  // namespace
+
+// packed holds ceil(numel / 2) bytes padded to a multiple of 8; any block size works (absmax is looked up per value).
+TB_API int tb_nf4_dequant(const void* packed, const float* absmax, int block, void* out, long long numel,
+                          cudaStream_t stream) {
+  if (numel <= 0) return 0;
+  if (block <= 0 || (reinterpret_cast<uintptr_t>(packed) & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  const long long n16 = (numel + 15) / 16;
+  int grid = (int)((n16 + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  nf4_dequant_kernel<<<grid, 256, 0, stream>>>((const uint8_t*)packed, absmax, block, (__nv_bfloat16*)out, numel);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

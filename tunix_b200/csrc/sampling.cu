@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, float inv_temp, int top_k, float top_p,
               unsigned long long seed, int step_host, const int* __restrict__ step_dev, int greedy,
               long long* __restrict__ tokens, float* __restrict__ logprobs) {
+  pdl_trigger();
+  pdl_wait();
   const int step = step_dev ? *step_dev : step_host;  // device-resident step keeps the launch graph-capturable
   __shared__ float red[33];
   __shared__ float s_a[32];
@@ -151,7 +153,6 @@ TB_API int tb_sample(const float* logits, long long ld, int B, int V, float temp
   if (B <= 0) return 0;
   const int greedy = temperature <= 0.f;
   const float inv_temp = greedy ? 1.f : 1.f / temperature;
-  sample_kernel<<<B, 1024, 0, stream>>>(logits, ld, V, inv_temp, top_k, top_p, seed, step, step_dev, greedy, tokens,
-                                        logprobs);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_pdl(sample_kernel, dim3(B), dim3(1024), 0, stream, logits, ld, V, inv_temp, top_k, top_p, seed, step, step_dev,
+                    greedy, tokens, logprobs) == cudaSuccess ? 0 : -5;
 }

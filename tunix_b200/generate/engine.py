@@ -77,7 +77,8 @@ class PagePool:
 
 class PagedEngine(BaseSampler):
     def __init__(self, transformer, tokenizer, cache_config: CacheConfig, page_size: int = 64,
-                 max_running_requests: int = 64, use_cuda_graph: bool = True, check_every: int = 16):
+                 max_running_requests: int = 64, use_cuda_graph: bool = True, check_every: int = 16,
+                 use_pdl: bool = True):
         self._model = transformer
         self.tokenizer = tokenizer
         self.cfg = transformer.config
@@ -91,6 +92,7 @@ class PagedEngine(BaseSampler):
         self.page_size = page_size
         self.max_running = max_running_requests
         self.use_graph = use_cuda_graph
+        self.use_pdl = use_pdl      # programmatic dependent launch between the kernels of a decode step
         self.check_every = check_every
         self.max_pages_per_seq = (self.cache_size + page_size - 1) // page_size
         self.pool: Optional[PagePool] = None
@@ -380,6 +382,15 @@ class PagedEngine(BaseSampler):
             return st["out_tokens"][:, :0].cpu().numpy(), st["out_lp"][:, :0].cpu().numpy()
         # token 0 comes from the prefill's last hidden state; it will sit at position `len`
         self._sample_into(hlast, st, advance=False)
+        from .. import _lib
+        _lib.register_cuda_sigs({"tb_set_pdl": [_lib.I]})
+        _lib.cuda().tb_set_pdl(1 if self.use_pdl else 0)
+        try:
+            return self._decode_loop(st, max_steps, pool, B)
+        finally:
+            _lib.cuda().tb_set_pdl(0)
+
+    def _decode_loop(self, st, max_steps, pool, B):
         graph = None
         if self.use_graph and max_steps > 2:
             # warm the decode path once outside capture (lazy kernel attribute setup, tensor-map cache), then

@@ -60,6 +60,17 @@ class NF4Weight:
         self.numel = w.numel()
 
     def dequantize(self) -> torch.Tensor:
+        if self.packed.is_cuda and self.dtype == torch.bfloat16:
+            # one kernel: codebook lookup, block scale, bf16 store (csrc/optim.cu)
+            from . import _lib
+            _lib.register_cuda_sigs({"tb_nf4_dequant": [_lib.P, _lib.P, _lib.I, _lib.P, _lib.LL, _lib.P]})
+            if self.packed.numel() % 8:
+                self.packed = torch.cat([self.packed, self.packed.new_zeros(8 - self.packed.numel() % 8)])
+            out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.packed.device)
+            rc = _lib.cuda().tb_nf4_dequant(self.packed.data_ptr(), self.absmax.data_ptr(), self.block, out.data_ptr(),
+                                            self.numel, _lib.stream_ptr())
+            _lib.check(rc, "tb_nf4_dequant")
+            return out
         code = torch.tensor(_NF4_CODE, device=self.packed.device)
         idx = torch.stack([(self.packed >> 4) & 0xF, self.packed & 0xF], dim=1).view(-1).long()
         vals = code[idx].view(-1, self.block) * self.absmax[:, None]
