@@ -1,0 +1,88 @@
+"""Architecture parity with the Hugging Face implementations: same random weights, same tokens, same logits.
+
+A tiny model of each family is built with `transformers`, its weights are written as safetensors, loaded through
+this framework's loader into the generic decoder, and the fp32 logits are compared on CPU."""
+import json
+import os
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _save(model, path):
+    from safetensors.torch import save_file
+    os.makedirs(path, exist_ok=True)
+    sd = {k: v.detach().clone().contiguous() for k, v in model.state_dict().items()}
+    save_file(sd, os.path.join(path, "model.safetensors"))
+    json.dump(model.config.to_dict(), open(os.path.join(path, "config.json"), "w"), default=str)
+
+
+def _ours(cfg, path):
+    from tunix_b200.models import safetensors_loader
+    from tunix_b200.models.transformer import create_model
+    model = create_model(cfg, seed=1)
+    safetensors_loader.load_safetensors_into(model, path)
+    return model.eval()
+
+
+CASES = {
+    "llama3": lambda t: (t.LlamaForCausalLM(t.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                                          num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-5,
+                                                          rope_theta=500000.0, tie_word_embeddings=False, max_position_embeddings=64)),
+                         dict(family="llama3", norm_eps=1e-5, rope_theta=500000.0)),
+    "qwen2": lambda t: (t.Qwen2ForCausalLM(t.Qwen2Config(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                                         num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6,
+                                                         rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=64)),
+                        dict(family="qwen2", norm_eps=1e-6, rope_theta=1000000.0, qkv_bias=True)),
+    "qwen3": lambda t: (t.Qwen3ForCausalLM(t.Qwen3Config(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6,
+                                                         rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=64)),
+                        dict(family="qwen3", norm_eps=1e-6, rope_theta=1000000.0, qk_norm=True)),
+    "gemma2": lambda t: (t.Gemma2ForCausalLM(t.Gemma2Config(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                                            num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                                            rms_norm_eps=1e-6, rope_theta=10000.0, query_pre_attn_scalar=16,
+                                                            sliding_window=8, attn_logit_softcapping=50.0,
+                                                            final_logit_softcapping=30.0, max_position_embeddings=64,
+                                                            attn_implementation="eager")),
+                         None),
+    "gemma3": lambda t: (t.Gemma3ForCausalLM(t.Gemma3TextConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=6,
+                                                                num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                                                rms_norm_eps=1e-6, rope_theta=1000000.0, rope_local_base_freq=10000.0,
+                                                                query_pre_attn_scalar=16, sliding_window=8, sliding_window_pattern=6,
+                                                                max_position_embeddings=64, attn_implementation="eager")),
+                         None),
+}
+
+
+@pytest.mark.parametrize("family", sorted(CASES))
+def test_logits_match_huggingface(family, tmp_path):
+    from tunix_b200.models.config import ModelConfig
+    torch.manual_seed(0)
+    hf, extra = CASES[family](transformers)
+    hf = hf.eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    _save(hf, str(tmp_path))
+    c = hf.config
+    if family in ("gemma2", "gemma3"):
+        from tunix_b200.models.config import get_config
+        cfg = get_config("gemma2_2b" if family == "gemma2" else "gemma3_1b").replace(num_layers=c.num_hidden_layers, vocab_size=128, embed_dim=64, hidden_dim=96, num_heads=4, head_dim=16,
+                                              num_kv_heads=2, dtype=torch.float32, max_position=64, sliding_window=8,
+                                              query_pre_attn_scalar=16.0)
+        ours = _ours(cfg, str(tmp_path))
+        toks = torch.randint(0, 128, (2, 17))
+        with torch.no_grad():
+            want, got = hf(toks).logits.float(), ours(toks)[0].float()
+        assert torch.allclose(got, want, atol=5e-4, rtol=2e-3), float((got - want).abs().max())
+        return
+    cfg = ModelConfig(num_layers=2, vocab_size=128, embed_dim=64, hidden_dim=96, num_heads=4, head_dim=16, num_kv_heads=2,
+                      dtype=torch.float32, max_position=64, weight_tying=False, **extra)
+    ours = _ours(cfg, str(tmp_path))
+    toks = torch.randint(0, 128, (2, 17))
+    with torch.no_grad():
+        want = hf(toks).logits.float()
+        got = ours(toks)[0].float()
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
