@@ -56,6 +56,35 @@ def prompt_dataset(hp, tokenizer, vocab_size):
     return data_lib.jsonl_prompts(path, c["batch_size"], tpl, c["num_train_epochs"])
 
 
+def agentic_kwargs(hp) -> dict:
+    """Constructor arguments of the agentic learner from the `agentic_config` section (all optional)."""
+    try:
+        a = dict(hp["agentic_config"] or {})
+    except KeyError:
+        return {}
+    from ..rl.agentic.agents.model_agent import ModelAgent
+    from ..rl.agentic.agents.tool_agent import ToolAgent
+    from ..rl.agentic.environments.task_environment import TaskEnvironment
+    from ..rl.agentic.environments.tool_environment import ToolEnvironment
+    from ..rl.agentic.parser.chat_template_parser import get_parser
+    from ..rl.agentic.tools.calculator_tool import CalculatorTool
+    tools = {"calculator": CalculatorTool}
+    chosen = [tools[t]() for t in a.get("tools", []) if t in tools]
+    kw = {"max_turns": int(a.get("max_turns", 1)), "max_concurrency": int(a.get("max_concurrency", 16)),
+          "off_policy_steps": int(a.get("off_policy_steps", 0)), "episode_timeout": float(a.get("episode_timeout", 600.0)),
+          "chat_parser": get_parser(a.get("chat_parser", "default"))}
+    if a.get("agent", "model") == "tool":
+        kw["agent_class"], kw["agent_kwargs"] = ToolAgent, {"tools": {t.name: t for t in chosen}}
+    else:
+        kw["agent_class"] = ModelAgent
+    if a.get("environment", "task") == "tool":
+        kw["env_class"], kw["env_kwargs"] = ToolEnvironment, {"tools": chosen, "reward_fn": a.get("reward_fn", "exact_match"),
+                                                              "max_steps": kw["max_turns"]}
+    else:
+        kw["env_class"], kw["env_kwargs"] = TaskEnvironment, {"reward_fn": a.get("reward_fn", "exact_match")}
+    return kw
+
+
 def main(argv=None):
     hp = config_lib.HyperParameters(sys.argv if argv is None else argv)
     dev = init_distributed()
@@ -68,7 +97,7 @@ def main(argv=None):
     rewards = hp.obtain_reward_fns()
     if hp["training_mode"] == "agentic_grpo":
         from ..rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
-        learner = AgenticGRPOLearner(cluster, rewards, algo)
+        learner = AgenticGRPOLearner(cluster, rewards, algo, **agentic_kwargs(hp))
     else:
         learner = learner_cls(cluster, rewards, algo)
     learner.train(prompt_dataset(hp, cluster.tokenizer, cluster.train_actor.config.vocab_size))
