@@ -78,7 +78,7 @@ class PagePool:
 class PagedEngine(BaseSampler):
     def __init__(self, transformer, tokenizer, cache_config: CacheConfig, page_size: int = 64,
                  max_running_requests: int = 64, use_cuda_graph: bool = True, check_every: int = 16,
-                 use_pdl: bool = True):
+                 use_pdl: bool = False):
         self._model = transformer
         self.tokenizer = tokenizer
         self.cfg = transformer.config
