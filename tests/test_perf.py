@@ -47,3 +47,25 @@ def test_threads_have_separate_stacks_and_noop():
     with n.span("x") as s:
         assert s is None
     assert n.spans() == []
+
+
+def test_tagged_tracer_query_sequence_and_lanes(tmp_path):
+    import json
+    from tunix_b200.perf.experimental import constants as C
+    from tunix_b200.perf.experimental.tracer import TaggedTracer, assign_lanes, sequentialize, write_chrome_trace
+    now = [0.0]
+    tr = TaggedTracer(clock=lambda: now[0])
+    with tr.tags(**{C.STEP: 3}):
+        with tr.span("rollout", timeline="engine", **{C.ROLE: C.ROLLOUT}):
+            now[0] = 2.0
+        with tr.span("update", timeline="trainer", **{C.ROLE: C.ACTOR, C.MICRO_BATCH: 0}):
+            now[0] = 3.0
+    tr.add("update", "trainer", 2.5, 4.0, **{C.STEP: 3, C.ROLE: C.ACTOR, C.MICRO_BATCH: 1})
+    assert len(tr.query(**{C.STEP: 3})) == 3 and tr.total("update", **{C.ROLE: C.ACTOR}) == 2.5
+    seq = sequentialize(tr.query(timeline="trainer"))
+    assert [(s.begin, s.end) for s in seq] == [(2.0, 3.0), (3.0, 4.5)]
+    lanes = assign_lanes(tr.query(timeline="trainer"))
+    assert sorted(lanes.values()) == [0, 1]                      # the two overlapping updates sit on different lanes
+    write_chrome_trace(tr.query(), str(tmp_path / "t.json"))
+    ev = json.load(open(tmp_path / "t.json"))["traceEvents"]
+    assert sum(e["ph"] == "X" for e in ev) == 3
