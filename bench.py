@@ -103,6 +103,9 @@ def main() -> int:
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
+                    help="gradient / parameter collectives of the sharded optimizer: our peer-memory kernels, or NCCL "
+                         "reduce-scatter + all-gather (the in-repo baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -143,7 +146,7 @@ def main() -> int:
     opt = optim.AdamW(2e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.0, max_grad_norm=1.0)
     if world > 1:
         from tunix_b200.parallel import fsdp
-        opt = fsdp.ShardedAdamW(2e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.0, max_grad_norm=1.0)
+        opt = fsdp.ShardedAdamW(2e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.0, max_grad_norm=1.0, comm=args.comm)
     tc = TrainingConfig(eval_every_n_steps=10 ** 9, max_steps=None, gradient_accumulation_steps=accum,
                         pbar_description=None, resume_from_checkpoint_on_init=False, max_inflight_computations=2)
     trainer = PeftTrainer(model, opt, tc)
@@ -235,7 +238,7 @@ def main() -> int:
                        "optimizer": "AdamW lr 2e-5, fp32 master+moments, clip 1.0",
                        "loss_mask": f"positions >= {PROMPT_LEN}",
                        "l2": "no flush: each step streams >100 GB of weights/optimizer state (>> 126 MB L2)"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "impl": "ours",
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "impl": "ours" if args.comm == "p2p" else "ours-nccl-baseline",
             "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out))
