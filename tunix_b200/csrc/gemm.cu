@@ -86,6 +86,8 @@ struct GemmArgs {
   int flags;
   const TileDesc* tiles;      // null = dense problem
   const int* num_tiles_dev;
+  int bn_rt;                  // dense problems only: tile width actually used (multiple of 16, <= BN; 0 = BN). A width
+                              // picked at run time lets a skinny problem cover the SMs in whole waves.
   // --- fused collectives (all zero for a plain GEMM)
   int gemm_ctas;              // CTAs that run GEMM tiles; the rest of the grid runs the aux role
   int aux_kind;               // 0 none, 1 copier (all-gather), 2 reducer (reduce-scatter)
@@ -366,7 +368,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int M = args.M, N = args.N, K = args.K;
   const int num_m = (M + BM - 1) / BM;
-  const int num_n = (N + BN - 1) / BN;
+  const int bn = args.bn_rt > 0 ? args.bn_rt : BN;        // tile width in use
+  const int num_n = (N + bn - 1) / bn;
   const int num_kb = (K + BK - 1) / BK;
   const int num_tiles = num_m * num_n;
   const bool a_mn = args.flags & GF_A_MN;
@@ -409,7 +412,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int r = t - g * per_group;
     TileDesc d;
     d.m0 = ((first_m + (r % gsz) + args.rot_m) % num_m) * BM;
-    d.n0 = ((r / gsz + args.rot_n) % num_n) * BN;
+    d.n0 = ((r / gsz + args.rot_n) % num_n) * bn;
     if (args.wait_mode == 2) {
       // gathered B rows: walk N in groups of 8 tiles (own rows first), all of M inside a group, so that the
       // tiles of a peer's rows come up only after everything that needs no transfer
@@ -482,7 +485,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           const uint32_t sa = smem_base + stage * C_::STAGE_BYTES;
           const uint32_t sb = sa + C_::A_BYTES;
-          mbar_expect_tx(full_bar(stage), C_::STAGE_BYTES);
+          mbar_expect_tx(full_bar(stage), C_::A_BYTES + (b_mn ? C_::B_BYTES : bn * BK * 2));
           const int k0 = kb * BK;
           if (!a_mn) {
             tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
@@ -505,7 +508,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
+      const uint32_t idesc = make_idesc_bf16(BM, bn, a_mn ? 1 : 0, b_mn ? 1 : 0);
       const uint32_t a_lbo = a_mn ? 8192u : 16u, b_lbo = b_mn ? 8192u : 16u;
       const uint32_t a_kstep = a_mn ? 2048u : 32u, b_kstep = b_mn ? 2048u : 32u;
       int stage = 0;
@@ -566,6 +569,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const TileDesc td = tile_info(t);
       const int row = td.m0 + q * 32 + lane;
       const int n0 = td.n0;
+      const int N = min(args.N, n0 + bn);           // shadows the problem's N: columns of this tile that exist
       const int M = td.m_end;                       // shadows the problem's M: rows of this tile that exist
       const long long c_off = td.c_off;
       const bool empty_k = td.kb1 <= td.kb0;        // nothing was accumulated: the tile's value is zero
@@ -732,7 +736,7 @@ int aux_ctas_for(double bytes, double flops, int world) {
 }
 void clear_fused(GemmArgs& a) {
   a.gemm_ctas = 0; a.aux_kind = 0; a.rank = 0; a.world = 1; a.rot_m = 0; a.rot_n = 0; a.wait_mode = 0;
-  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
+  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.bn_rt = 0; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
   memset(&a.copy, 0, sizeof(a.copy));
   memset(&a.red, 0, sizeof(a.red));
 }
@@ -843,12 +847,28 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
     if ((long long)num_m * ((N + cand - 1) / cand) >= (g_sm_count * 3) / 5) break;
   }
   if (b_mn && BN < 64) BN = 64;
+  // Skinny problems (one row of tiles, K-major B): a run-time tile width, a multiple of 16, chosen so that the
+  // tiles fill the SMs in whole waves (24576 columns: 140 tiles of 176 instead of 96 of 256).
+  int bn_rt = 0;
+  static const bool fixed_bn = getenv("TUNIX_B200_FIXED_BN") != nullptr;
+  if (num_m == 1 && !b_mn && N >= 1024 && max_ctas <= 0 && !fixed_bn) {
+    double best = 0.0;
+    for (int w = 32; w <= 256; w += 16) {
+      const int tiles = (N + w - 1) / w;
+      const int waves = (tiles + g_sm_count - 1) / g_sm_count;
+      // wave efficiency, with a mild preference for wide tiles (fewer re-reads of A)
+      const double eff = (double)tiles / (waves * g_sm_count) * (1.0 + 0.0004 * w) * ((double)N / ((double)tiles * w));
+      if (eff > best) { best = eff; bn_rt = w; }
+    }
+    BN = bn_rt > 128 ? 256 : bn_rt > 64 ? 128 : bn_rt > 32 ? 64 : 32;
+    if (bn_rt == BN) bn_rt = 0;
+  }
   CUtensorMap tmA, tmB;
   int r;
   if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
   else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
   if (r) return -3;
-  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1);
+  if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, bn_rt > 0 ? bn_rt : BN, BK, 1);
   else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
   if (r) return -4;
   GemmArgs args;
@@ -859,7 +879,8 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   args.ldr = ldr; args.alpha = alpha; args.status = status;
   args.tiles = nullptr; args.num_tiles_dev = nullptr;
   clear_fused(args);
-  const int tiles = num_m * ((N + BN - 1) / BN);
+  args.bn_rt = bn_rt;
+  const int tiles = num_m * ((N + (bn_rt > 0 ? bn_rt : BN) - 1) / (bn_rt > 0 ? bn_rt : BN));
   int ctas = g_sm_count;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
