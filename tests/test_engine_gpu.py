@@ -103,7 +103,8 @@ def test_qkv_post_matches_separate_kernels(H, qk_norm):
     assert torch.equal(vp, vp2)
 
 
-@pytest.mark.parametrize("M,N,K_", [(8, 4096, 512), (64, 1024, 4096), (100, 12288, 256)])
+@pytest.mark.parametrize("M,N,K_", [(8, 4096, 512), (64, 1024, 4096), (100, 12288, 256), (64, 24576, 512), (32, 151936, 256),
+                                    (128, 6144, 1024), (17, 5000, 320)])
 def test_small_m_gemm_tiles(M, N, K_):
     from tunix_b200 import _lib
     from tunix_b200.ops import kernels as K
@@ -114,6 +115,13 @@ def test_small_m_gemm_tiles(M, N, K_):
     _lib.raise_if_kernel_error()
     ref = A.float() @ B.float().t()
     assert ((out - ref).norm() / ref.norm()).item() < 2e-3
+    # tile widths picked at run time (176, 208, 48, ...) must respect the epilogue options and the tile's column limit
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out2 = K.gemm(A, B, bias=bias, residual=res)
+    _lib.raise_if_kernel_error()
+    want = ref + bias.float() + res.float()
+    assert ((out2.float() - want).norm() / want.norm()).item() < 6e-3
 
 
 @pytest.mark.parametrize("M,N,K_", [(64, 4096, 4096), (64, 4096, 12288), (200, 6144, 4096), (17, 1000, 2048), (256, 24576, 1024),
