@@ -222,3 +222,37 @@ def test_nf4_dequant_kernel_matches_reference(shape, block):
     cpu = NF4Weight(w.cpu(), block).dequantize()
     assert got.shape == w.shape and torch.allclose(got.float().cpu(), cpu.float(), atol=1e-2, rtol=1e-2)
     assert (got.float() - w.float()).abs().mean() < 0.15
+
+
+@pytest.mark.parametrize("rows,V,D,softcap,temp", [(512, 5000, 256, 0.0, 1.0), (1024, 33000, 512, 30.0, 0.7), (300, 128256, 128, 0.0, 1.0)])
+def test_fused_lm_head_logprobs_match_reference(rows, V, D, softcap, temp):
+    """The log-softmax epilogue of the two-SM GEMM (no logits in memory) against fp32 PyTorch, forward and backward."""
+    from tunix_b200.ops import functional as F
+    torch.manual_seed(9)
+    h = (torch.randn(rows, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, D, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    tg = torch.randint(0, V, (rows,), device="cuda")
+    tg[::17] = -1                                                  # ignored positions
+    logp, ent = F.lm_head_logprobs(h, w, tg, softcap=softcap, temperature=temp, want_entropy=True)
+    _check_status()
+    z = h.detach().float() @ w.detach().float().t()
+    if softcap:
+        z = softcap * torch.tanh(z / softcap)
+    z = z / temp
+    ref_lp = torch.log_softmax(z, -1).gather(-1, tg.clamp(min=0)[:, None]).squeeze(-1)
+    ref_lp = torch.where(tg >= 0, ref_lp, torch.zeros_like(ref_lp))
+    p = torch.softmax(z, -1)
+    ref_ent = -(p * torch.log_softmax(z, -1)).sum(-1)
+    assert torch.allclose(logp, ref_lp, atol=3e-2, rtol=2e-2), float((logp - ref_lp).abs().max())
+    assert torch.allclose(ent, ref_ent, atol=3e-2, rtol=2e-2)
+    g = torch.randn(rows, device="cuda")
+    (logp * g).sum().backward()
+    _check_status()
+    hr = h.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    zr = hr @ wr.t()
+    if softcap:
+        zr = softcap * torch.tanh(zr / softcap)
+    lp2 = torch.log_softmax(zr / temp, -1).gather(-1, tg.clamp(min=0)[:, None]).squeeze(-1)
+    (torch.where(tg >= 0, lp2, torch.zeros_like(lp2)) * g).sum().backward()
+    assert _rel_err(h.grad, hr.grad) < 3e-2 and _rel_err(w.grad, wr.grad) < 3e-2

@@ -46,6 +46,12 @@ struct Args2 {
   long long ldr;
   float alpha;
   int* status;
+  // log-softmax epilogue (lm_head): instead of writing C, every tile leaves per row the online-softmax state of its
+  // 256 columns and the target column's value, so logits never reach memory. partial: fp32 [M, num_n, 4] =
+  // (max, sum exp(z - max), sum exp(z - max) z, z[target] or -inf when the target is in another tile).
+  const int* targets;
+  float* partial;
+  float inv_temp, softcap;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -237,6 +243,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;
     const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
     const uint32_t tempty_leader0 = mapa_u32(tempty_bar(0), 0), tempty_leader1 = mapa_u32(tempty_bar(1), 0);
+    const bool lse_mode = args.partial != nullptr;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mt, nt;
       tile_coords(t, mt, nt);
@@ -245,6 +252,53 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      if (lse_mode) {
+        // one thread owns one row of the tile: the softmax statistics of its 256 columns need no communication
+        float mx = -INFINITY, sm = 0.f, sz = 0.f, zt = -INFINITY;
+        const int tgt = row < M ? args.targets[row] : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float cm = -INFINITY;
+          float z[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(r[i]) * alpha;
+            if (args.softcap > 0.f) v = args.softcap * tanhf(v / args.softcap);
+            v *= args.inv_temp;
+            z[i] = (col0 + i < N) ? v : -INFINITY;
+            cm = fmaxf(cm, z[i]);
+          }
+          if (tgt >= col0 && tgt < col0 + 32) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i == tgt) zt = z[i];
+          }
+          const float nm = fmaxf(mx, cm);
+          const float corr = (mx == -INFINITY) ? 0.f : __expf(mx - nm);
+          float s2 = 0.f, z2 = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float e = (z[i] == -INFINITY) ? 0.f : __expf(z[i] - nm);
+            s2 += e;
+            z2 += e * (z[i] == -INFINITY ? 0.f : z[i]);
+          }
+          sm = sm * corr + s2;
+          sz = sz * corr + z2;
+          mx = nm;
+        }
+        if (row < M)
+          *reinterpret_cast<float4*>(args.partial + ((long long)row * num_n + nt) * 4) = make_float4(mx, sm, sz, zt);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc == 0 ? tempty_leader0 : tempty_leader1);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -345,6 +399,46 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 }
 
 int g_sms2 = 0;
+// set for the duration of one tb_lm_head_lse call (host side, same thread)
+thread_local const int* g_lse_targets = nullptr;
+thread_local float* g_lse_partial = nullptr;
+thread_local float g_lse_inv_temp = 1.f, g_lse_softcap = 0.f;
+
+// partial [M, num_n, 4] -> logp[row] = z[target] - lse (0 for targets outside [0, V)), lse, entropy = lse - E[z]
+__global__ void lse_combine_kernel(const float* __restrict__ partial, const int* __restrict__ targets, int M, int num_n,
+                                   int V, float* __restrict__ logp, float* __restrict__ lse_out, float* __restrict__ ent_out) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int lane = threadIdx.x & 31;
+  float mx = -INFINITY, sm = 0.f, sz = 0.f, zt = -INFINITY;
+  for (int j = lane; j < num_n; j += 32) {
+    const float4 p = *reinterpret_cast<const float4*>(partial + ((long long)row * num_n + j) * 4);
+    const float nm = fmaxf(mx, p.x);
+    const float a = (mx == -INFINITY) ? 0.f : __expf(mx - nm), b = (p.x == -INFINITY) ? 0.f : __expf(p.x - nm);
+    sm = sm * a + p.y * b;
+    sz = sz * a + p.z * b;
+    mx = nm;
+    zt = fmaxf(zt, p.w);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx, o), os = __shfl_xor_sync(0xffffffffu, sm, o);
+    const float oz = __shfl_xor_sync(0xffffffffu, sz, o), ot = __shfl_xor_sync(0xffffffffu, zt, o);
+    const float nm = fmaxf(mx, om);
+    const float a = (mx == -INFINITY) ? 0.f : __expf(mx - nm), b = (om == -INFINITY) ? 0.f : __expf(om - nm);
+    sm = sm * a + os * b;
+    sz = sz * a + oz * b;
+    mx = nm;
+    zt = fmaxf(zt, ot);
+  }
+  if (lane == 0) {
+    const float lse = mx + logf(sm);
+    const int t = targets[row];
+    if (logp) logp[row] = (t >= 0 && t < V) ? zt - lse : 0.f;
+    if (lse_out) lse_out[row] = lse;
+    if (ent_out) ent_out[row] = lse - sz / sm;
+  }
+}
 
 }  // namespace
 
@@ -379,6 +473,7 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   a.ldr = ldr; a.alpha = alpha; a.status = status;
+  a.targets = g_lse_targets; a.partial = g_lse_partial; a.inv_temp = g_lse_inv_temp; a.softcap = g_lse_softcap;
   const int tiles = num_m * num_n;
   const int use_pairs = tiles < pairs ? tiles : pairs;
   cudaLaunchConfig_t cfg = {};
@@ -395,4 +490,21 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, gemm2_kernel, tmA, tmB, a) != cudaSuccess) return -5;
   return 1;
+}
+
+// log p(target) (and optionally lse / entropy) of z = softcap(h W^T) / temperature without materialising z:
+// the two-SM GEMM's epilogue leaves per-tile softmax statistics, a small kernel merges them.
+// h [M, K] bf16 (row stride ldh), w [V, K] bf16 (row stride ldw), targets int32 [M] (negative = ignored),
+// partial: fp32 scratch of M * ceil(V / 256) * 4 elements. Returns 1 when run here, 0 when the problem does not
+// qualify for the two-SM kernel (the caller uses its chunked path), negative on error.
+TB_API int tb_lm_head_lse(const void* h, long long ldh, const void* w, long long ldw, int M, int V, int K,
+                          const int* targets, float inv_temp, float softcap, float* partial, float* logp, float* lse,
+                          float* entropy, int* status, cudaStream_t stream) {
+  g_lse_targets = targets; g_lse_partial = partial; g_lse_inv_temp = inv_temp; g_lse_softcap = softcap;
+  const int rc = tb_gemm_2cta_try(h, w, nullptr, M, V, K, ldh, ldw, 0, 0, nullptr, nullptr, 0, 1.0f, status, stream);
+  g_lse_targets = nullptr; g_lse_partial = nullptr; g_lse_inv_temp = 1.f; g_lse_softcap = 0.f;
+  if (rc != 1) return rc;
+  const int num_n = (V + BN - 1) / BN;
+  lse_combine_kernel<<<(M + 7) / 8, 256, 0, stream>>>(partial, targets, M, num_n, V, logp, lse, entropy);
+  return cudaGetLastError() == cudaSuccess ? 1 : -5;
 }

@@ -47,7 +47,7 @@ def _time(fn, iters: int, warmup: int = 3, flush: bool = True):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "adamw", "logsoftmax", "sample",
-                                       "glu", "moe", "paged_decode"])
+                                       "glu", "moe", "paged_decode", "lm_head"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -132,6 +132,17 @@ def main(argv=None) -> int:
         ms = _time(lambda: S.sample(z, 1.0, None, None, 1, 0, want_logprob=True), args.iters, args.warmup)
         gb = 3.0 * z.numel() * 4 / ms / 1e6
         out.update(shape=[args.rows, args.vocab], ms=ms, gbs_3pass=gb, frac_of_peak=gb / peak_gb)
+    elif args.kernel == "lm_head":
+        from tunix_b200.ops import functional as F
+        rows, V, D = args.rows, args.vocab, args.dim
+        h = (torch.randn(rows, D, device=dev) * 0.5).to(bf)
+        w = (torch.randn(V, D, device=dev) * 0.02).to(bf)
+        tg = torch.randint(0, V, (rows,), device=dev)
+        with torch.no_grad():
+            ms = _time(lambda: F.lm_head_logprobs(h, w, tg, chunk=4096), args.iters, args.warmup)
+        tf = 2.0 * rows * V * D / ms / 1e9
+        out.update(shape=[rows, V, D], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf,
+                   fused=not bool(os.environ.get("TUNIX_B200_NO_FUSED_LSE")))
     elif args.kernel == "paged_decode":
         Bn, ctx, N, KH, H, page = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim, 64
         max_pages = (ctx + page - 1) // page

@@ -288,8 +288,10 @@ class _LmHeadLogprobFn(torch.autograd.Function):
         logp = torch.empty(rows, dtype=torch.float32, device=h.device)
         lse = torch.empty_like(logp)
         ent = torch.empty_like(logp) if want_entropy else None
-        buf = torch.empty((min(chunk, max(rows, 1)), V), dtype=torch.float32, device=h.device)
-        for s0 in range(0, rows, chunk):
+        # fused path: the two-SM GEMM's epilogue reduces each 256-column tile to softmax statistics, no logits in memory
+        fused = K.lm_head_lse(h2, w, tg, softcap=softcap, temperature=temperature, logp=logp, lse=lse, entropy=ent)
+        buf = None if fused else torch.empty((min(chunk, max(rows, 1)), V), dtype=torch.float32, device=h.device)
+        for s0 in range(0, rows if not fused else 0, chunk):
             n = min(chunk, rows - s0)
             z = buf[:n]
             K.gemm(h2[s0:s0 + n], w, out=z)

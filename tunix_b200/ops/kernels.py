@@ -614,3 +614,34 @@ def gae_scan(rewards, values, mask, gamma: float, lam: float):
     _lib.check(rc, "tb_gae_scan")
     _count()
     return adv, ret
+
+
+# ------------------------------------------------------------------ fused lm_head -> log-softmax statistics
+_lib.register_cuda_sigs({
+    "tb_lm_head_lse": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P,
+                       _lib.P, _lib.P, _lib.P],
+})
+
+
+def lm_head_lse(h2: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, *, softcap: float, temperature: float,
+                logp: torch.Tensor, lse: torch.Tensor, entropy) -> bool:
+    """log p(target), log-sum-exp and (optionally) entropy of softcap(h W^T) / temperature, written into the given
+    fp32 [rows] tensors, without materialising logits (csrc/gemm_2cta.cu). Returns False when the problem is too
+    small for the two-SM kernel; the caller then runs its chunked path."""
+    import os
+    if os.environ.get("TUNIX_B200_NO_FUSED_LSE"):
+        return False
+    rows, Kd = h2.shape
+    V = w.shape[0]
+    if rows < 256 or not (_is2d_rowmajor(h2) and _is2d_rowmajor(w)) or h2.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    num_n = (V + 255) // 256
+    partial = torch.empty(rows * num_n * 4, dtype=torch.float32, device=h2.device)
+    rc = _lib.cuda().tb_lm_head_lse(h2.data_ptr(), h2.stride(0), w.data_ptr(), w.stride(0), rows, V, Kd, targets.data_ptr(),
+                                    1.0 / float(temperature), float(softcap or 0.0), partial.data_ptr(), logp.data_ptr(),
+                                    lse.data_ptr(), _lib.ptr(entropy), _lib.status_buffer().data_ptr(), _lib.stream_ptr())
+    if rc < 0:
+        _lib.check(rc, "tb_lm_head_lse")
+    if rc == 1:
+        _count(2)
+    return rc == 1
