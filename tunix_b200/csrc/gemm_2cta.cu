@@ -399,10 +399,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 }
 
 int g_sms2 = 0;
-// set for the duration of one tb_lm_head_lse call (host side, same thread)
-thread_local const int* g_lse_targets = nullptr;
-thread_local float* g_lse_partial = nullptr;
-thread_local float g_lse_inv_temp = 1.f, g_lse_softcap = 0.f;
+struct LseArgs {           // log-softmax epilogue request; partial == nullptr for a plain GEMM
+  const int* targets = nullptr;
+  float* partial = nullptr;
+  float inv_temp = 1.f, softcap = 0.f;
+};
 
 // partial [M, num_n, 4] -> logp[row] = z[target] - lse (0 for targets outside [0, V)), lse, entropy = lse - E[z]
 __global__ void lse_combine_kernel(const float* __restrict__ partial, const int* __restrict__ targets, int M, int num_n,
@@ -442,10 +443,10 @@ __global__ void lse_combine_kernel(const float* __restrict__ partial, const int*
 
 }  // namespace
 
-// Returns 1 when the problem was launched here, 0 when it is left to the single-CTA kernel, negative on error.
-int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                     long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
-                     int* status, cudaStream_t stream) {
+namespace {
+int launch_2cta(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                int flags, const void* bias, const void* resid, long long ldr, float alpha, int* status,
+                cudaStream_t stream, const LseArgs& lse) {
   static const bool off = getenv("TUNIX_B200_NO_2CTA") != nullptr;
   if (off) return 0;
   if (g_sms2 == 0) {
@@ -473,7 +474,7 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   a.ldr = ldr; a.alpha = alpha; a.status = status;
-  a.targets = g_lse_targets; a.partial = g_lse_partial; a.inv_temp = g_lse_inv_temp; a.softcap = g_lse_softcap;
+  a.targets = lse.targets; a.partial = lse.partial; a.inv_temp = lse.inv_temp; a.softcap = lse.softcap;
   const int tiles = num_m * num_n;
   const int use_pairs = tiles < pairs ? tiles : pairs;
   cudaLaunchConfig_t cfg = {};
@@ -491,6 +492,14 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
   if (cudaLaunchKernelEx(&cfg, gemm2_kernel, tmA, tmB, a) != cudaSuccess) return -5;
   return 1;
 }
+}  // namespace
+
+// Returns 1 when the problem was launched here, 0 when it is left to the single-CTA kernel, negative on error.
+int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                     int* status, cudaStream_t stream) {
+  return launch_2cta(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream, LseArgs{});
+}
 
 // log p(target) (and optionally lse / entropy) of z = softcap(h W^T) / temperature without materialising z:
 // the two-SM GEMM's epilogue leaves per-tile softmax statistics, a small kernel merges them.
@@ -500,9 +509,9 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
 TB_API int tb_lm_head_lse(const void* h, long long ldh, const void* w, long long ldw, int M, int V, int K,
                           const int* targets, float inv_temp, float softcap, float* partial, float* logp, float* lse,
                           float* entropy, int* status, cudaStream_t stream) {
-  g_lse_targets = targets; g_lse_partial = partial; g_lse_inv_temp = inv_temp; g_lse_softcap = softcap;
-  const int rc = tb_gemm_2cta_try(h, w, nullptr, M, V, K, ldh, ldw, 0, 0, nullptr, nullptr, 0, 1.0f, status, stream);
-  g_lse_targets = nullptr; g_lse_partial = nullptr; g_lse_inv_temp = 1.f; g_lse_softcap = 0.f;
+  LseArgs lse_args;
+  lse_args.targets = targets; lse_args.partial = partial; lse_args.inv_temp = inv_temp; lse_args.softcap = softcap;
+  const int rc = launch_2cta(h, w, nullptr, M, V, K, ldh, ldw, 0, 0, nullptr, nullptr, 0, 1.0f, status, stream, lse_args);
   if (rc != 1) return rc;
   const int num_n = (V + BN - 1) / BN;
   lse_combine_kernel<<<(M + 7) / 8, 256, 0, stream>>>(partial, targets, M, num_n, V, logp, lse, entropy);

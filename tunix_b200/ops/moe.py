@@ -64,6 +64,7 @@ class _ExpertsFn(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable      # the saved buffers are overwritten below: one backward per forward
     def backward(ctx, dout):
         xp, g, u, y, wts, pos, seg_off, counts, gate_w, up_w, down_w = ctx.saved_tensors
         E, Fd, D = gate_w.shape
@@ -142,6 +143,7 @@ class _LocalExpertsFn(torch.autograd.Function):
         return y
 
     @staticmethod
+    @torch.autograd.function.once_differentiable      # the saved buffers are overwritten below: one backward per forward
     def backward(ctx, dy):
         xp, g, u, wrow, seg_off, gate_w, up_w, down_w = ctx.saved_tensors
         E, Fd, D = gate_w.shape
