@@ -88,6 +88,8 @@ struct GemmArgs {
   const int* num_tiles_dev;
   int bn_rt;                  // dense problems only: tile width actually used (multiple of 16, <= BN; 0 = BN). A width
                               // picked at run time lets a skinny problem cover the SMs in whole waves.
+  const uint8_t* b_packed;    // dense problems only: B pre-tiled by tb_pack_weight (one contiguous, pre-swizzled
+                              // block per n tile and k block, fetched with one bulk copy); null = B through tmB
   // --- fused collectives (all zero for a plain GEMM)
   int gemm_ctas;              // CTAs that run GEMM tiles; the rest of the grid runs the aux role
   int aux_kind;               // 0 none, 1 copier (all-gather), 2 reducer (reduce-scatter)
@@ -494,7 +496,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < BM / 64; ++j)
               tma_load_2d(sa + j * 8192, &tmA, full_bar(stage), m0 + 64 * j, k0);
           }
-          if (!b_mn) {
+          if (args.b_packed != nullptr) {
+            const size_t blk = (size_t)(n0 / bn) * num_kb + kb;
+            bulk_load(sb, args.b_packed + blk * (size_t)(bn * BK * 2), bn * BK * 2, full_bar(stage));
+          } else if (!b_mn) {
             tma_load_2d(sb, &tmB, full_bar(stage), k0, n0 + td.b_row0);
           } else {
 #pragma unroll
@@ -736,7 +741,7 @@ int aux_ctas_for(double bytes, double flops, int world) {
 }
 void clear_fused(GemmArgs& a) {
   a.gemm_ctas = 0; a.aux_kind = 0; a.rank = 0; a.world = 1; a.rot_m = 0; a.rot_n = 0; a.wait_mode = 0;
-  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.bn_rt = 0; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
+  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.bn_rt = 0; a.b_packed = nullptr; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
   memset(&a.copy, 0, sizeof(a.copy));
   memset(&a.red, 0, sizeof(a.red));
 }
@@ -745,7 +750,7 @@ void clear_fused(GemmArgs& a) {
 
 int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
-                       int* status, cudaStream_t stream);
+                       int* status, cudaStream_t stream, const void* b_packed = nullptr);
 
 int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                      long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
@@ -891,6 +896,109 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
     case 128: err = launch_pdl(gemm_bf16_kernel<128>, dim3(ctas), dim3(192), Cfg<128>::SMEM_BYTES, stream, tmA, tmB, args); break;
     case 64: err = launch_pdl(gemm_bf16_kernel<64>, dim3(ctas), dim3(192), Cfg<64>::SMEM_BYTES, stream, tmA, tmB, args); break;
     default: err = launch_pdl(gemm_bf16_kernel<32>, dim3(ctas), dim3(192), Cfg<32>::SMEM_BYTES, stream, tmA, tmB, args); break;
+  }
+  return err == cudaSuccess ? 0 : -5;
+}
+
+// ------------------------------------------------------------------ pre-tiled weights for skinny GEMMs
+// A K-major weight [N, K] read through a 2-D tensor map arrives as 128-byte row pieces that lie K*2 bytes apart:
+// at decode sizes (M <= 128) the kernel is a pure weight stream, and that access pattern reaches about half of
+// the copy bandwidth. tb_pack_weight re-tiles the weight once: block (n tile, k block) holds `w` rows x 64
+// columns contiguously, already in the 128-byte-swizzled order the MMA descriptors expect, and the blocks of
+// one n tile follow each other, so a CTA streams one contiguous range with one bulk copy per pipeline stage.
+__global__ void pack_weight_kernel(const __nv_bfloat16* __restrict__ W, long long ldw, int N, int K, int w, int num_kb,
+                                   uint4* __restrict__ P, long long total) {
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(idx & 7);
+    const long long rr = idx >> 3;
+    const int r = (int)(rr % w);
+    const long long blk = rr / w;
+    const int kb = (int)(blk % num_kb);
+    const long long nt = blk / num_kb;
+    const long long n = nt * w + r;
+    const int k = kb * BK + c * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (n < N && k < K) v = *reinterpret_cast<const uint4*>(W + n * ldw + k);
+    P[blk * (long long)w * 8 + (long long)r * 8 + (c ^ (r & 7))] = v;
+  }
+}
+
+// Tile width a weight [N, K] is packed with: 256 where the cluster split-K kernel takes the problem (long
+// contraction, few tiles), otherwise the multiple of 16 that fills the SMs in whole waves.
+TB_API int tb_packed_width(int N, int K) {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (K >= 8192 && N >= 256 && ((N + 255) / 256) * 2 <= g_sm_count) return 256;
+  double best = 0.0;
+  int bw = 32;
+  for (int w = 32; w <= 256; w += 16) {
+    const int tiles = (N + w - 1) / w;
+    const int waves = (tiles + g_sm_count - 1) / g_sm_count;
+    const double eff = (double)tiles / (waves * g_sm_count) * (1.0 + 0.0004 * w) * ((double)N / ((double)tiles * w));
+    if (eff > best) { best = eff; bw = w; }
+  }
+  return bw;
+}
+
+// P must hold ceil(N/w) * ceil(K/64) * w * 128 bytes. W: [N, K] bf16, 16-byte aligned, ldw and K multiples of 8.
+TB_API int tb_pack_weight(const void* W, long long ldw, int N, int K, int w, void* P, cudaStream_t stream) {
+  if (N <= 0 || K <= 0 || w < 16 || w > 256 || (w % 16) || (ldw % 8) || (K % 8) ||
+      (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(P) & 127))
+    return -2;
+  const int num_kb = (K + BK - 1) / BK;
+  const long long total = (long long)((N + w - 1) / w) * num_kb * w * 8;
+  const int threads = 256;
+  const long long want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  pack_weight_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(W), ldw, N, K, w, num_kb,
+                                                     reinterpret_cast<uint4*>(P), total);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// C[M,N] = alpha * A[M,K] * W^T (+bias)(+resid)(+C) with W given as the packed copy P of width w.
+TB_API int tb_gemm_packed_bf16(const void* A, long long lda, const void* P, int w, void* C, long long ldc, int M, int N,
+                               int K, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                               int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (lda % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(P) & 127) ||
+      w < 16 || w > 256 || (w % 16) || (flags & (GF_A_MN | GF_B_MN)))
+    return -2;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  static const bool no_splitk = getenv("TUNIX_B200_NO_SPLITK") != nullptr;
+  if (w == 256 && !no_splitk) {
+    const int sk = tb_gemm_splitk_try(A, nullptr, C, M, N, K, lda, 8, ldc, flags, bias, resid, ldr, alpha, status, stream, P);
+    if (sk != 0) return sk < 0 ? sk : 0;
+  }
+  const int BN = w > 128 ? 256 : w > 64 ? 128 : w > 32 ? 64 : 32;
+  CUtensorMap tmA;
+  if (tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1)) return -3;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K; args.flags = flags;
+  args.C = C; args.ldc = ldc;
+  args.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  args.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
+  args.ldr = ldr; args.alpha = alpha; args.status = status;
+  args.tiles = nullptr; args.num_tiles_dev = nullptr;
+  clear_fused(args);
+  args.bn_rt = w == BN ? 0 : w;
+  args.b_packed = reinterpret_cast<const uint8_t*>(P);
+  const int tiles = ((M + BM - 1) / BM) * ((N + w - 1) / w);
+  const int ctas = tiles < g_sm_count ? tiles : g_sm_count;
+  set_gemm_attrs();
+  cudaError_t err;
+  switch (BN) {
+    case 256: err = launch_pdl(gemm_bf16_kernel<256>, dim3(ctas), dim3(192), Cfg<256>::SMEM_BYTES, stream, tmA, tmA, args); break;
+    case 128: err = launch_pdl(gemm_bf16_kernel<128>, dim3(ctas), dim3(192), Cfg<128>::SMEM_BYTES, stream, tmA, tmA, args); break;
+    case 64: err = launch_pdl(gemm_bf16_kernel<64>, dim3(ctas), dim3(192), Cfg<64>::SMEM_BYTES, stream, tmA, tmA, args); break;
+    default: err = launch_pdl(gemm_bf16_kernel<32>, dim3(ctas), dim3(192), Cfg<32>::SMEM_BYTES, stream, tmA, tmA, args); break;
   }
   return err == cudaSuccess ? 0 : -5;
 }

@@ -40,8 +40,13 @@ struct SkArgs {
   long long ldr;
   float alpha;
   int* status;
+  const uint8_t* b_packed;   // B pre-tiled in 256-row blocks by tb_pack_weight (null: B through tmB)
 };
 
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -107,7 +112,10 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t sa = smem_base + stage * STAGE_BYTES;
         mbar_expect_tx(full_bar(stage), STAGE_BYTES);
         tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, m0);
-        tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, n0);
+        if (args.b_packed != nullptr)
+          bulk_load(sa + A_BYTES, args.b_packed + ((size_t)blockIdx.x * num_kb + kb) * (size_t)B_BYTES, B_BYTES, full_bar(stage));
+        else
+          tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, n0);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
@@ -232,7 +240,7 @@ int g_sk_sms = 0;
 // kernel), a negative code on error. A and B K-major, same conventions as tb_gemm_bf16.
 int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
-                       int* status, cudaStream_t stream) {
+                       int* status, cudaStream_t stream, const void* b_packed) {
   if (flags & 3) return 0;                              // MN-major operands stay on the persistent kernel
   // Measured on B200 against the persistent kernel's narrow tiles: the split pays once the K loop is long
   // (down projections, K >= 8192: 40 -> 28 us at 64 x 4096 x 12288) and loses a few us below that.
@@ -285,8 +293,10 @@ int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int 
   if (S == 1 && tiles >= g_sk_sms) return 0;            // enough tiles for the persistent kernel
   CUtensorMap tmA, tmB;
   if (tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1)) return -3;
-  if (tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1)) return -4;
+  if (b_packed != nullptr) tmB = tmA;                  // unused by the kernel
+  else if (tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, BN, BK, 1)) return -4;
   SkArgs a;
+  a.b_packed = reinterpret_cast<const uint8_t*>(b_packed);
   a.M = M; a.N = N; a.K = K; a.flags = flags; a.S = S; a.C = C; a.ldc = ldc;
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);

@@ -53,6 +53,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--packed", action="store_true", help="gemm: B as a pre-tiled PackedWeight (decode-size M)")
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
@@ -79,9 +80,15 @@ def main(argv=None) -> int:
         A = torch.randn((Kd, M) if args.a_mn else (M, Kd), device=dev, dtype=bf)
         B = torch.randn((Kd, N) if args.b_mn else (N, Kd), device=dev, dtype=bf)
         C = torch.empty(M, N, device=dev, dtype=bf)
-        ms = _time(lambda: K.gemm(A, B, a_mn=args.a_mn, b_mn=args.b_mn, out=C), args.iters, args.warmup)
+        if args.packed:
+            pw = K.PackedWeight(B)
+            ms = _time(lambda: K.gemm_packed(A, pw, out=C), args.iters, args.warmup)
+            out.update(packed_width=pw.width)
+        else:
+            ms = _time(lambda: K.gemm(A, B, a_mn=args.a_mn, b_mn=args.b_mn, out=C), args.iters, args.warmup)
         tf = 2.0 * M * N * Kd / ms / 1e9
-        out.update(shape=[M, N, Kd], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf)
+        gb = (M * Kd + N * Kd + M * N) * 2 / ms / 1e6
+        out.update(shape=[M, N, Kd], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf, gbs=gb, frac_of_copy_bw=gb / peak_gb)
     elif args.kernel in ("attn_fwd", "attn_bwd"):
         B_, T, N, KH, H = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
         q = torch.randn(B_, T, N, H, device=dev, dtype=bf)

@@ -645,3 +645,69 @@ def lm_head_lse(h2: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, *, sof
     if rc == 1:
         _count(2)
     return rc == 1
+
+
+# ------------------------------------------------------------------ pre-tiled weights for decode-size GEMMs
+_lib.register_cuda_sigs({
+    "tb_packed_width": [_lib.I, _lib.I],
+    "tb_pack_weight": [_lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P],
+    "tb_gemm_packed_bf16": [_lib.P, _lib.LL, _lib.P, _lib.I, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P,
+                            _lib.LL, _lib.F, _lib.P, _lib.P],
+})
+
+
+class PackedWeight:
+    """A K-major weight [N, K] re-tiled for streaming (csrc/gemm.cu, tb_pack_weight): per (n tile of `width` rows,
+    64-column k block) one contiguous, pre-swizzled block. `refresh` re-packs after the source changed."""
+
+    def __init__(self, weight: torch.Tensor, width: int | None = None):
+        assert weight.dtype == torch.bfloat16 and _is2d_rowmajor(weight)
+        self.N, self.K = weight.shape
+        self.width = int(width) if width else int(_lib.cuda().tb_packed_width(self.N, self.K))
+        nbytes = -(-self.N // self.width) * -(-self.K // 64) * self.width * 128
+        self.data = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
+        self.refresh(weight)
+
+    def refresh(self, weight: torch.Tensor) -> None:
+        assert weight.shape == (self.N, self.K) and weight.dtype == torch.bfloat16 and _is2d_rowmajor(weight)
+        rc = _lib.cuda().tb_pack_weight(weight.data_ptr(), weight.stride(0), self.N, self.K, self.width, self.data.data_ptr(),
+                                        _lib.stream_ptr())
+        _lib.check(rc, "tb_pack_weight")
+        _count()
+
+
+def gemm_packed(a: torch.Tensor, pw: PackedWeight, *, out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+                accumulate: bool = False, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                alpha: float = 1.0) -> torch.Tensor:
+    """C = alpha * A @ W^T with W given as a PackedWeight; same epilogue options as `gemm`."""
+    assert a.dtype == torch.bfloat16 and _is2d_rowmajor(a)
+    M, K = a.shape
+    assert K == pw.K, f"contraction mismatch {K} vs {pw.K}"
+    N = pw.N
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        assert not accumulate
+    assert out.shape == (M, N) and out.stride(1) == 1
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= GF_OUT_F32
+    else:
+        assert out.dtype == torch.bfloat16
+    if accumulate:
+        flags |= GF_ACCUM
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+        flags |= GF_BIAS
+    ldr = 0
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+        flags |= GF_RESIDUAL
+        ldr = residual.stride(0)
+    if M == 0:
+        return out
+    rc = _lib.cuda().tb_gemm_packed_bf16(a.data_ptr(), a.stride(0), pw.data.data_ptr(), pw.width, out.data_ptr(), out.stride(0),
+                                         M, N, K, flags, _lib.ptr(bias), _lib.ptr(residual), ldr, float(alpha),
+                                         _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "tb_gemm_packed_bf16")
+    _count()
+    return out
