@@ -243,3 +243,39 @@ def test_engine_packed_weights_match_unpacked():
     b2 = packed(prompt_token_ids=prompts, max_generation_steps=8, return_logprobs=True, eos_tokens=[2])
     for la, lb in zip(a2.logprobs, b2.logprobs):
         assert abs(la[0] - lb[0]) < 5e-2
+
+
+def test_engine_continuous_batching_matches_single_batch():
+    """More requests than slots: finished sequences hand their slot to waiting ones; greedy results equal those of
+    an engine that runs all requests side by side, and every page returns to the pool."""
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import PagedEngine
+    model = _model()
+    cc = CacheConfig(cache_size=128, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(0)
+    prompts = [[1] + rng.integers(3, 500, size=int(n)).tolist() for n in (4, 9, 2, 17, 6, 30, 3, 12, 5)]
+    wide = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=16, check_every=4)
+    ref = wide(prompt_token_ids=prompts, max_generation_steps=24, return_logprobs=True, eos_tokens=[2])
+    # end-of-sequence ids taken from what the model actually emits, so that sequences stop at different steps
+    eos = sorted({2, int(ref.tokens[0][3]), int(ref.tokens[4][9]), int(ref.tokens[7][1])})
+    ref = wide(prompt_token_ids=prompts, max_generation_steps=24, return_logprobs=True, eos_tokens=eos)
+    lens = [len(t) for t in ref.tokens]
+    assert min(lens) < 24 and max(lens) > min(lens)
+    for graph in (True, False):
+        narrow = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=3, check_every=4, use_cuda_graph=graph)
+        out = narrow(prompt_token_ids=prompts, max_generation_steps=24, return_logprobs=True, eos_tokens=eos)
+        _lib.raise_if_kernel_error()
+        same = total = 0
+        for a, b, la, lb in zip(ref.tokens, out.tokens, ref.logprobs, out.logprobs):
+            n = min(len(a), len(b))
+            same += int((np.asarray(a[:n]) == np.asarray(b[:n])).sum())
+            total += max(len(a), len(b))
+            assert abs(la[0] - lb[0]) < 5e-2
+        assert same / total > 0.9, (same, total)
+        assert narrow.pool.free_pages == narrow.pool.num_pages
+    # a single generated token per request never enters the decode loop
+    one = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=2)(prompt_token_ids=prompts, max_generation_steps=1,
+                                                                               eos_tokens=[2])
+    assert [len(t) for t in one.tokens] == [1] * len(prompts)
+    assert [int(t[0]) for t in one.tokens] == [int(t[0]) for t in ref.tokens]

@@ -41,6 +41,8 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0, help="override layer count (0 = preset)")
     ap.add_argument("--engine", default="paged", choices=["paged", "dense"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pack", action="store_true", help="decode GEMMs read the weights in place (no pre-tiled copy)")
+    ap.add_argument("--check-every", type=int, default=10 ** 9, help="decode steps between looks at the done flags")
     ap.add_argument("--pdl", action="store_true", help="launch decode kernels with programmatic dependent launch")
     args = ap.parse_args(argv)
     from tunix_b200 import _lib
@@ -60,7 +62,8 @@ def main(argv=None) -> int:
     prompts = rng.integers(3, cfg.vocab_size, (args.seqs, args.prompt)).tolist()
     if args.engine == "paged":
         eng = PagedEngine(model, _Tok(), cc, page_size=64, max_running_requests=args.max_running,
-                          use_cuda_graph=not args.no_graph, check_every=10 ** 9, use_pdl=args.pdl)
+                          use_cuda_graph=not args.no_graph, check_every=args.check_every, use_pdl=args.pdl,
+                          pack_weights=not args.no_pack)
     else:
         eng = Sampler(model, _Tok(), cc)
     kw = dict(prompt_token_ids=prompts, max_generation_steps=args.gen, max_prompt_length=args.prompt, temperature=1.0,
@@ -80,7 +83,7 @@ def main(argv=None) -> int:
     print(json.dumps({"metric": "rollout_decode_tokens_per_sec", "value": n_tok / wall, "unit": "tokens/s",
                       "device_ms": e0.elapsed_time(e1), "wall_s": wall, "generated_tokens": n_tok, "model": args.model,
                       "layers": cfg.num_layers, "seqs": args.seqs, "prompt": args.prompt, "gen": args.gen,
-                      "engine": args.engine, "cuda_graph": not args.no_graph, "pdl": args.pdl,
+                      "engine": args.engine, "cuda_graph": not args.no_graph, "pdl": args.pdl, "packed": not args.no_pack,
                       "ms_per_decode_step": 1e3 * wall / (args.gen * max(1, -(-args.seqs // args.max_running))),
                       "native_launches_outside_graph": kernels.launch_count - l0,
                       "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))

@@ -5,14 +5,15 @@ sglang_jax_sampler.py) and follows the page-table conventions of its host-side p
 (tunix/experimental/generate/single_type_kv_cache_manager.py, tiered_page_pool.py): fixed-size pages, a
 free list, one page table row per running sequence.
 
-Per wave of at most `max_running_requests` sequences:
-  prefill  one pass over the left-padded prompts with the tcgen05 flash-attention kernel; K / V of every
-           layer are scattered into the pages by `kv_write` (padding is skipped);
+Requests are batched continuously over `max_running_requests` slots (`_run`): a finished sequence frees its
+slot and pages at the next check point and the next waiting request is prefilled into it.
+  prefill  one pass over the left-padded prompts of the admitted requests with the tcgen05 flash-attention
+           kernel; K / V of every layer are scattered into the pages by `kv_write` (padding is skipped);
   decode   every step is the same fixed sequence of kernel launches (embedding -> per layer RMSNorm, tcgen05
            GEMMs with narrow tiles, RoPE at device-resident positions, `kv_write`, `paged_decode` attention,
            GLU -> final norm -> lm_head GEMM in fp32 -> fused sampling kernel), all reading sequence lengths,
            the step counter and the page table from device memory, so the whole step is captured once in a
-           CUDA graph and replayed; the host only checks every `check_every` steps whether all sequences hit EOS.
+           CUDA graph and replayed; the host looks at the slots' done flags only every `check_every` steps.
 Outputs match `Sampler` (`SamplerOutput` with ragged tokens, optional per-token log-probs).
 """
 from __future__ import annotations
@@ -99,6 +100,7 @@ class PagedEngine(BaseSampler):
         # below ~16k weight rows a GEMM is bound by its fixed costs and the packed form does not pay.
         self.pack_weights = pack_weights
         self.pack_min_rows = 16384
+        self._packed_on = False     # per call: the packed form wins up to 128 running sequences (one row of tiles)
         self._packed = None
         self.check_every = check_every
         self.max_pages_per_seq = (self.cache_size + page_size - 1) // page_size
@@ -218,7 +220,7 @@ class PagedEngine(BaseSampler):
                     have[name].refresh(w)
 
     def _pk(self, i, name):
-        return self._packed[i].get(name) if self._packed is not None else None
+        return self._packed[i].get(name) if self._packed is not None and self._packed_on else None
 
     def _rope(self, i):
         return self._model._rope(self.cfg.layer_type(i) == "local", self.device)
@@ -328,31 +330,39 @@ class PagedEngine(BaseSampler):
                 a = at.o_proj(o.view(B, N * H), residual=None if cfg.post_norms else x)
             x = self._mlp_and_norms(layer, i, x, a, decode=True)
         hlast = self._model.norm(x)
-        self._sample_into(hlast, st, advance=True)
+        self._sample_into(hlast, st)
 
-    def _sample_into(self, hlast, st, advance: bool) -> None:
+    def _logits(self, hlast, out=None):
         ph = self._pk(len(self._model.layers), "head")
         if ph is not None:
-            logits = K.gemm_packed(hlast, ph, out=st["logits"])
+            logits = K.gemm_packed(hlast, ph, out=out, out_dtype=torch.float32)
         else:
-            logits = K.gemm(hlast, self._model.head_weight(), out=st["logits"])
+            logits = K.gemm(hlast, self._model.head_weight(), out=out, out_dtype=torch.float32)
         if self.cfg.final_logit_softcap:
             c = self.cfg.final_logit_softcap
             logits.copy_(c * torch.tanh(logits / c))
+        return logits
+
+    def _sample_into(self, hlast, st) -> None:
+        """Sample one token per slot of the running batch and advance the slots that are still generating. A
+        finished (or empty) slot idles: position -1 and length 0 make the next step write no K/V and attend to
+        nothing, and its output goes to the spare last column."""
+        logits = self._logits(hlast, out=st["logits"])
         p = st["params"]
         S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
                  out_tokens=st["next"], out_logprobs=st["next_lp"], step_tensor=st["step"])
         done = st["done"]
         tok = torch.where(done, st["pad"], st["next"])
-        idx = st["step"].to(torch.int64).view(1, 1).expand(tok.shape[0], 1)
+        idx = torch.where(done, st["dump_col"], st["out_pos"])[:, None]
         st["out_tokens"].scatter_(1, idx, tok[:, None])
-        st["out_lp"].scatter_(1, idx, torch.where(done, torch.zeros_like(st["next_lp"]), st["next_lp"])[:, None])
-        st["done"].copy_(done | (tok[:, None] == st["eos"]).any(-1))
-        # the sampled token is fed at the next decode step; a decode step also moves the write position on
+        st["out_lp"].scatter_(1, idx, st["next_lp"][:, None])
+        st["out_pos"].add_((~done).to(torch.int64))
+        st["done"].copy_(done | (tok[:, None] == st["eos"]).any(-1) | (st["out_pos"] >= st["dump_col"]))
+        # the sampled token is fed at the next decode step, at the position one past the current length
         st["tokens"].copy_(tok)
-        if advance:
-            st["positions"].copy_(st["seq_lens"])
-            st["seq_lens"].add_(1)
+        live = ~st["done"]
+        st["positions"].copy_(torch.where(live, st["seq_lens"], st["neg1"]))
+        st["seq_lens"].copy_(torch.where(live, st["seq_lens"] + 1, st["zero"]))
         st["step"].add_(1)
 
     # --------------------------------------------------------------------- call
@@ -377,19 +387,18 @@ class PagedEngine(BaseSampler):
             raise ValueError("prompt + generation exceeds the configured cache size")
         was_training = self._model.training
         self._model.eval()
-        all_tokens, all_lps = [], []
         prompts_all, plens_all = pad_prompts_left(rows, plen, pad_id)
         self._fuse_all()
         self._pack_all()
-        for w0 in range(0, len(rows), self.max_running):
-            toks_np, lens_np = prompts_all[w0:w0 + self.max_running], plens_all[w0:w0 + self.max_running]
-            gen, lps = self._run_wave(toks_np, lens_np, max_generation_steps, eos_ids, pad_id, temperature, top_p, top_k,
-                                      (seed or 0) + w0)
-            all_tokens.append(gen)
-            all_lps.append(lps)
-        self._model.train(was_training)
-        gen = np.concatenate(all_tokens)
-        lps = np.concatenate(all_lps)
+        from .. import _lib
+        _lib.register_cuda_sigs({"tb_set_pdl": [_lib.I]})
+        _lib.cuda().tb_set_pdl(1 if self.use_pdl else 0)
+        try:
+            gen, lps = self._run(prompts_all, plens_all, max_generation_steps, eos_ids, pad_id, temperature, top_p, top_k,
+                                 seed or 0)
+        finally:
+            _lib.cuda().tb_set_pdl(0)
+            self._model.train(was_training)
         tokens, texts, lp_out = [], [], []
         for b in range(gen.shape[0]):
             row = gen[b]
@@ -408,74 +417,142 @@ class PagedEngine(BaseSampler):
                              padded_prompt_tokens=prompts_all, logprobs=lp_out if return_logprobs else None,
                              prompt_lengths=np.asarray(plens_all))
 
-    def _run_wave(self, toks_np, lens_np, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
+    def _run(self, toks_np, lens_np, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
+        """Continuous batching over `max_running_requests` slots. All requests wait in a queue; a slot whose
+        sequence has finished (end-of-sequence token or `max_steps` tokens) is harvested at the next check point
+        (every `check_every` decode steps), its pages go back to the pool, and the next waiting request is
+        prefilled into it while the other slots keep their state. The decode step always runs over all slots
+        (one captured graph); idle slots cost a row of the GEMMs and no attention work.
+
+        toks_np [n, P] left-padded prompts, lens_np [n]. Returns (tokens [n, max_steps], logprobs [n, max_steps])."""
         dev = self.device
-        B, P = toks_np.shape
+        n_req, P = toks_np.shape
+        out_tok = np.full((n_req, max_steps), pad_id, np.int64)
+        out_lp = np.zeros((n_req, max_steps), np.float32)
+        if max_steps == 0 or n_req == 0:
+            return out_tok, out_lp
+        B = min(self.max_running, n_req)
+        self._packed_on = B <= 128
         self._ensure_pool(B)
-        self._fuse_all()
         pool = self.pool
-        for s in range(B):
+        for s in range(self.max_running):
             pool.release(s)
-            pool.reserve(s, int(lens_np[s]) + max_steps + 1)
-        pool.sync_table()
-        toks = torch.from_numpy(toks_np).to(dev)
-        lens = torch.from_numpy(lens_np).to(dev)
-        seg = (torch.arange(P, device=dev)[None] >= (P - lens)[:, None]).to(torch.int32)
-        positions = torch.clamp(torch.cumsum(seg, -1) - 1, min=0).to(torch.int32)
-        slots = torch.arange(B, device=dev, dtype=torch.int32)
-        hlast = self._prefill(toks, positions, seg, slots)
         splits = (self.cache_size + K.DECODE_SPLIT_TOKENS - 1) // K.DECODE_SPLIT_TOKENS
         N, H, V = self.cfg.num_heads, self.cfg.head_dim, self.cfg.vocab_size
+        i64 = dict(dtype=torch.int64, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
         st = {
-            "tokens": torch.zeros(B, dtype=torch.int64, device=dev),
-            "positions": lens.to(torch.int32).clone(),            # first generated token sits at position len
-            "seq_lens": (lens + 1).to(torch.int32),
-            "slots": slots, "done": torch.zeros(B, dtype=torch.bool, device=dev),
-            "next": torch.zeros(B, dtype=torch.int64, device=dev), "next_lp": torch.zeros(B, device=dev),
-            "out_tokens": torch.full((B, max(max_steps, 1)), pad_id, dtype=torch.int64, device=dev),
-            "out_lp": torch.zeros((B, max(max_steps, 1)), device=dev),
+            "tokens": torch.zeros(B, **i64),
+            "positions": torch.full((B,), -1, **i32),             # -1 / 0: an empty slot
+            "seq_lens": torch.zeros(B, **i32),
+            "slots": torch.arange(B, **i32), "done": torch.ones(B, dtype=torch.bool, device=dev),
+            "next": torch.zeros(B, **i64), "next_lp": torch.zeros(B, device=dev),
+            "out_tokens": torch.full((B, max_steps + 1), pad_id, **i64),      # last column: writes of idle slots
+            "out_lp": torch.zeros((B, max_steps + 1), device=dev),
+            "out_pos": torch.zeros(B, **i64),
+            "dump_col": torch.full((B,), max_steps, **i64),
+            "neg1": torch.full((B,), -1, **i32), "zero": torch.zeros(B, **i32),
             "logits": torch.empty(B, V, dtype=torch.float32, device=dev),
-            "step": torch.zeros(1, dtype=torch.int32, device=dev),
-            "pad": torch.full((B,), pad_id, dtype=torch.int64, device=dev),
-            "eos": torch.as_tensor(eos_ids, device=dev, dtype=torch.int64),
+            "step": torch.zeros(1, **i32),
+            "pad": torch.full((B,), pad_id, **i64),
+            "eos": torch.as_tensor(eos_ids, **i64),
             "ws": (torch.empty(B * N * splits * H, dtype=torch.float32, device=dev),
                    torch.empty(B * N * splits * 2, dtype=torch.float32, device=dev)),
             "params": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed},
         }
-        if max_steps == 0:
-            return st["out_tokens"][:, :0].cpu().numpy(), st["out_lp"][:, :0].cpu().numpy()
-        # token 0 comes from the prefill's last hidden state; it will sit at position `len`
-        self._sample_into(hlast, st, advance=False)
-        from .. import _lib
-        _lib.register_cuda_sigs({"tb_set_pdl": [_lib.I]})
-        _lib.cuda().tb_set_pdl(1 if self.use_pdl else 0)
-        try:
-            return self._decode_loop(st, max_steps, pool, B)
-        finally:
-            _lib.cuda().tb_set_pdl(0)
-
-    def _decode_loop(self, st, max_steps, pool, B):
+        waiting = list(range(n_req))[::-1]          # pop() takes the next request in order
+        slot_req = [-1] * B
+        slot_cnt = [0] * B                          # tokens a slot's request has produced at most (host-side bound)
         graph = None
-        if self.use_graph and max_steps > 2:
-            # warm the decode path once outside capture (lazy kernel attribute setup, tensor-map cache), then
-            # capture one step and replay it
-            snap = {k: st[k].clone() for k in ("tokens", "positions", "seq_lens", "done", "out_tokens", "out_lp", "step")}
-            self._decode_step(st)
-            for k, v in snap.items():
-                st[k].copy_(v)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._decode_step(st)
-            for k, v in snap.items():
-                st[k].copy_(v)
-        for step in range(1, max_steps):
-            if graph is not None:
-                graph.replay()
-            else:
-                self._decode_step(st)
-            if step % self.check_every == 0 and bool(st["done"].all()):
+        while True:
+            # ---- check point: harvest finished slots, admit waiting requests (repeats while an admitted request
+            # finishes with its very first token)
+            while True:
+                done_h = st["done"].cpu().numpy()
+                fin = [s for s in range(B) if slot_req[s] >= 0 and done_h[s]]
+                if fin:
+                    ix = torch.as_tensor(fin, **i64)
+                    toks_h = st["out_tokens"][ix, :max_steps].cpu().numpy()
+                    lps_h = st["out_lp"][ix, :max_steps].cpu().numpy()
+                    cnt_h = st["out_pos"][ix].cpu().numpy()
+                    for j, s in enumerate(fin):
+                        c = int(cnt_h[j])
+                        out_tok[slot_req[s], :c] = toks_h[j, :c]
+                        out_lp[slot_req[s], :c] = lps_h[j, :c]
+                        slot_req[s] = -1
+                        pool.release(s)
+                free = [s for s in range(B) if slot_req[s] < 0]
+                if not waiting or not free:
+                    break
+                take = free[:len(waiting)]
+                reqs = [waiting.pop() for _ in take]
+                for s, r in zip(take, reqs):
+                    slot_req[s] = r
+                    slot_cnt[s] = 1
+                    pool.reserve(s, int(lens_np[r]) + max_steps + 1)
+                pool.sync_table()
+                self._admit(st, take, toks_np[reqs], lens_np[reqs], pad_id)
+            if all(r < 0 for r in slot_req):
                 break
-        for s in range(B):
-            pool.release(s)
-        return st["out_tokens"].cpu().numpy(), st["out_lp"].cpu().numpy()
+            # ---- decode until the next check point
+            if graph is None and self.use_graph and max_steps > 2:
+                graph = self._capture(st)
+            # no slot can run past max_steps tokens: that bounds the steps to the next look at the done flags
+            left = [max_steps - slot_cnt[s] for s in range(B) if slot_req[s] >= 0]
+            n_steps = max(1, min(self.check_every, min(left) if waiting else max(left)))
+            for _ in range(n_steps):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    self._decode_step(st)
+            for s in range(B):
+                slot_cnt[s] += n_steps
+        return out_tok, out_lp
+
+    def _admit(self, st, slots_list, toks_np, lens_np, pad_id) -> None:
+        """Prefill the given prompts into their slots, sample each one's first token and set the slot state."""
+        dev = self.device
+        P = toks_np.shape[1]
+        toks = torch.from_numpy(np.ascontiguousarray(toks_np)).to(dev)
+        lens = torch.from_numpy(np.ascontiguousarray(lens_np)).to(dev)
+        seg = (torch.arange(P, device=dev)[None] >= (P - lens)[:, None]).to(torch.int32)
+        positions = torch.clamp(torch.cumsum(seg, -1) - 1, min=0).to(torch.int32)
+        slots = torch.as_tensor(slots_list, dtype=torch.int32, device=dev)
+        hlast = self._prefill(toks, positions, seg, slots)
+        logits = self._logits(hlast)
+        p = st["params"]
+        g = len(slots_list)
+        nxt = torch.zeros(g, dtype=torch.int64, device=dev)
+        nlp = torch.zeros(g, device=dev)
+        S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
+                 out_tokens=nxt, out_logprobs=nlp, step_tensor=st["step"])
+        ix = slots.to(torch.int64)
+        max_steps = st["out_tokens"].shape[1] - 1
+        st["out_tokens"][ix] = pad_id
+        st["out_tokens"][ix, 0] = nxt
+        st["out_lp"][ix, 0] = nlp
+        st["out_pos"][ix] = 1
+        done = (nxt[:, None] == st["eos"]).any(-1)
+        if max_steps <= 1:
+            done = torch.ones_like(done)
+        st["done"][ix] = done
+        st["tokens"][ix] = nxt
+        # token 0 came from the prefill's last hidden state; it is fed at position `len`
+        st["positions"][ix] = torch.where(done, st["neg1"][ix], lens.to(torch.int32))
+        st["seq_lens"][ix] = torch.where(done, st["zero"][ix], (lens + 1).to(torch.int32))
+
+    def _capture(self, st):
+        """Warm the decode path once outside capture (lazy kernel attribute setup, tensor-map cache), then capture
+        one step; the state the warm-up and the capture touched is put back."""
+        keys = ("tokens", "positions", "seq_lens", "done", "out_tokens", "out_lp", "out_pos", "step")
+        snap = {k: st[k].clone() for k in keys}
+        self._decode_step(st)
+        for k, v in snap.items():
+            st[k].copy_(v)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._decode_step(st)
+        for k, v in snap.items():
+            st[k].copy_(v)
+        return graph
