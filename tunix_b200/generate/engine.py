@@ -389,7 +389,9 @@ class PagedEngine(BaseSampler):
         self._model.eval()
         prompts_all, plens_all = pad_prompts_left(rows, plen, pad_id)
         self._fuse_all()
-        self._pack_all()
+        self._packed_on = self.pack_weights and min(self.max_running, len(rows)) <= 128
+        if self._packed_on:
+            self._pack_all()
         from .. import _lib
         _lib.register_cuda_sigs({"tb_set_pdl": [_lib.I]})
         _lib.cuda().tb_set_pdl(1 if self.use_pdl else 0)
@@ -432,7 +434,6 @@ class PagedEngine(BaseSampler):
         if max_steps == 0 or n_req == 0:
             return out_tok, out_lp
         B = min(self.max_running, n_req)
-        self._packed_on = B <= 128
         self._ensure_pool(B)
         pool = self.pool
         for s in range(self.max_running):
