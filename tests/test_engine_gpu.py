@@ -279,3 +279,45 @@ def test_engine_continuous_batching_matches_single_batch():
                                                                                eos_tokens=[2])
     assert [len(t) for t in one.tokens] == [1] * len(prompts)
     assert [int(t[0]) for t in one.tokens] == [int(t[0]) for t in ref.tokens]
+
+
+def test_engine_server_mode_joins_requests_and_pauses_for_weight_updates():
+    from concurrent.futures import ThreadPoolExecutor
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import EngineServer, PagedEngine
+    model = _model()
+    cc = CacheConfig(cache_size=128, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(1)
+    prompts = [[1] + rng.integers(3, 500, size=int(n)).tolist() for n in (4, 9, 2, 17, 6, 30, 3, 12)]
+    limits = [20, 5, 12, 20, 1, 8, 20, 3]
+    ref = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=8)(
+        prompt_token_ids=prompts, max_generation_steps=20, max_prompt_length=32, return_logprobs=True, eos_tokens=[2])
+    eng = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=3, check_every=4)
+    with EngineServer(eng, max_new_tokens=20, max_prompt_length=32, eos_tokens=[2]) as srv:
+        with ThreadPoolExecutor(4) as ex:            # one prompt per call, from several threads at once
+            res = list(ex.map(lambda a: srv.generate(a[0], a[1], timeout=120), zip(prompts, limits)))
+        same = total = 0
+        for (toks, lps), want, wlp, lim in zip(res, ref.tokens, ref.logprobs, limits):
+            n = min(lim, len(want))
+            assert len(toks) == n and len(lps) == n
+            same += int((toks == np.asarray(want[:n])).sum())
+            total += n
+            assert abs(float(lps[0]) - wlp[0]) < 5e-2
+        assert same / total > 0.9, (same, total)
+        assert srv.admitted == len(prompts)
+        # weight update between requests: drain, change the weights in place, resume
+        assert srv.pause(timeout=60)
+        with torch.no_grad():
+            for p in model.parameters():
+                p.mul_(0.5)
+        torch.cuda.synchronize()
+        srv.resume()
+        toks, lps = srv.generate(prompts[3], 6, timeout=120)
+        want = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=2)(
+            prompt_token_ids=[prompts[3]], max_generation_steps=6, max_prompt_length=32, return_logprobs=True, eos_tokens=[2])
+        assert abs(float(lps[0]) - want.logprobs[0][0]) < 5e-2 and int(toks[0]) == int(want.tokens[0][0])
+    _lib.raise_if_kernel_error()
+    assert eng.pool.free_pages == eng.pool.num_pages
+    with pytest.raises(RuntimeError):
+        srv.submit([1, 2, 3])

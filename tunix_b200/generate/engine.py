@@ -357,7 +357,7 @@ class PagedEngine(BaseSampler):
         st["out_tokens"].scatter_(1, idx, tok[:, None])
         st["out_lp"].scatter_(1, idx, st["next_lp"][:, None])
         st["out_pos"].add_((~done).to(torch.int64))
-        st["done"].copy_(done | (tok[:, None] == st["eos"]).any(-1) | (st["out_pos"] >= st["dump_col"]))
+        st["done"].copy_(done | (tok[:, None] == st["eos"]).any(-1) | (st["out_pos"] >= st["limit"]))
         # the sampled token is fed at the next decode step, at the position one past the current length
         st["tokens"].copy_(tok)
         live = ~st["done"]
@@ -419,30 +419,13 @@ class PagedEngine(BaseSampler):
                              padded_prompt_tokens=prompts_all, logprobs=lp_out if return_logprobs else None,
                              prompt_lengths=np.asarray(plens_all))
 
-    def _run(self, toks_np, lens_np, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
-        """Continuous batching over `max_running_requests` slots. All requests wait in a queue; a slot whose
-        sequence has finished (end-of-sequence token or `max_steps` tokens) is harvested at the next check point
-        (every `check_every` decode steps), its pages go back to the pool, and the next waiting request is
-        prefilled into it while the other slots keep their state. The decode step always runs over all slots
-        (one captured graph); idle slots cost a row of the GEMMs and no attention work.
-
-        toks_np [n, P] left-padded prompts, lens_np [n]. Returns (tokens [n, max_steps], logprobs [n, max_steps])."""
+    def _new_state(self, B, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
         dev = self.device
-        n_req, P = toks_np.shape
-        out_tok = np.full((n_req, max_steps), pad_id, np.int64)
-        out_lp = np.zeros((n_req, max_steps), np.float32)
-        if max_steps == 0 or n_req == 0:
-            return out_tok, out_lp
-        B = min(self.max_running, n_req)
-        self._ensure_pool(B)
-        pool = self.pool
-        for s in range(self.max_running):
-            pool.release(s)
         splits = (self.cache_size + K.DECODE_SPLIT_TOKENS - 1) // K.DECODE_SPLIT_TOKENS
         N, H, V = self.cfg.num_heads, self.cfg.head_dim, self.cfg.vocab_size
         i64 = dict(dtype=torch.int64, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
-        st = {
+        return {
             "tokens": torch.zeros(B, **i64),
             "positions": torch.full((B,), -1, **i32),             # -1 / 0: an empty slot
             "seq_lens": torch.zeros(B, **i32),
@@ -451,6 +434,7 @@ class PagedEngine(BaseSampler):
             "out_tokens": torch.full((B, max_steps + 1), pad_id, **i64),      # last column: writes of idle slots
             "out_lp": torch.zeros((B, max_steps + 1), device=dev),
             "out_pos": torch.zeros(B, **i64),
+            "limit": torch.full((B,), max_steps, **i64),          # tokens the slot's request may generate
             "dump_col": torch.full((B,), max_steps, **i64),
             "neg1": torch.full((B,), -1, **i32), "zero": torch.zeros(B, **i32),
             "logits": torch.empty(B, V, dtype=torch.float32, device=dev),
@@ -461,16 +445,63 @@ class PagedEngine(BaseSampler):
                    torch.empty(B * N * splits * 2, dtype=torch.float32, device=dev)),
             "params": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed},
         }
+
+    def _run(self, toks_np, lens_np, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
+        """All requests of one call through the continuous-batching loop. toks_np [n, P] left-padded prompts,
+        lens_np [n]. Returns (tokens [n, max_steps], logprobs [n, max_steps])."""
+        n_req = toks_np.shape[0]
+        out_tok = np.full((n_req, max_steps), pad_id, np.int64)
+        out_lp = np.zeros((n_req, max_steps), np.float32)
+        if max_steps == 0 or n_req == 0:
+            return out_tok, out_lp
+        B = min(self.max_running, n_req)
+        st = self._new_state(B, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed)
         waiting = list(range(n_req))[::-1]          # pop() takes the next request in order
-        slot_req = [-1] * B
+
+        class Source:
+            def take(self, n_free):
+                reqs = [waiting.pop() for _ in range(min(n_free, len(waiting)))]
+                return [(r, toks_np[r], int(lens_np[r]), max_steps) for r in reqs]
+
+            def more_waiting(self):
+                return bool(waiting)
+
+            def deliver(self, r, toks, lps):
+                out_tok[r, :len(toks)] = toks
+                out_lp[r, :len(lps)] = lps
+
+            def idle(self):
+                return False                        # nothing running and nothing waiting: the call is over
+
+        self._loop(st, B, max_steps, pad_id, Source())
+        return out_tok, out_lp
+
+    def _loop(self, st, B, max_steps, pad_id, source) -> None:
+        """Continuous batching over B slots. A slot whose sequence has finished (end-of-sequence token or its
+        token limit) is harvested at the next check point (every `check_every` decode steps at most), its pages go
+        back to the pool, and the next waiting request is prefilled into it while the other slots keep their
+        state. The decode step always runs over all slots (one captured graph); idle slots cost a row of the
+        GEMMs and no attention work.
+
+        `source` hands out requests and takes results: take(n_free) -> [(id, padded prompt row, prompt length,
+        token limit)], more_waiting(), deliver(id, tokens, logprobs), and idle(), called when no slot is busy and
+        take() returned nothing: it may block for new work and returns False to end the loop."""
+        dev = self.device
+        self._ensure_pool(B)
+        pool = self.pool
+        for s in range(self.max_running):
+            pool.release(s)
+        i64 = dict(dtype=torch.int64, device=dev)
+        slot_req = [None] * B
         slot_cnt = [0] * B                          # tokens a slot's request has produced at most (host-side bound)
+        slot_lim = [0] * B
         graph = None
         while True:
             # ---- check point: harvest finished slots, admit waiting requests (repeats while an admitted request
             # finishes with its very first token)
             while True:
                 done_h = st["done"].cpu().numpy()
-                fin = [s for s in range(B) if slot_req[s] >= 0 and done_h[s]]
+                fin = [s for s in range(B) if slot_req[s] is not None and done_h[s]]
                 if fin:
                     ix = torch.as_tensor(fin, **i64)
                     toks_h = st["out_tokens"][ix, :max_steps].cpu().numpy()
@@ -478,29 +509,32 @@ class PagedEngine(BaseSampler):
                     cnt_h = st["out_pos"][ix].cpu().numpy()
                     for j, s in enumerate(fin):
                         c = int(cnt_h[j])
-                        out_tok[slot_req[s], :c] = toks_h[j, :c]
-                        out_lp[slot_req[s], :c] = lps_h[j, :c]
-                        slot_req[s] = -1
+                        source.deliver(slot_req[s], toks_h[j, :c], lps_h[j, :c])
+                        slot_req[s] = None
                         pool.release(s)
-                free = [s for s in range(B) if slot_req[s] < 0]
-                if not waiting or not free:
+                free = [s for s in range(B) if slot_req[s] is None]
+                new = source.take(len(free)) if free else []
+                if not new:
                     break
-                take = free[:len(waiting)]
-                reqs = [waiting.pop() for _ in take]
-                for s, r in zip(take, reqs):
-                    slot_req[s] = r
+                take = free[:len(new)]
+                for s, (rid, _row, ln, lim) in zip(take, new):
+                    slot_req[s] = rid
                     slot_cnt[s] = 1
-                    pool.reserve(s, int(lens_np[r]) + max_steps + 1)
+                    slot_lim[s] = max(1, min(int(lim), max_steps))
+                    pool.reserve(s, ln + slot_lim[s] + 1)
                 pool.sync_table()
-                self._admit(st, take, toks_np[reqs], lens_np[reqs], pad_id)
-            if all(r < 0 for r in slot_req):
+                self._admit(st, take, np.stack([row for _, row, _, _ in new]), np.asarray([ln for _, _, ln, _ in new]),
+                            pad_id, [slot_lim[s] for s in take])
+            if all(r is None for r in slot_req):
+                if source.idle():
+                    continue
                 break
-            # ---- decode until the next check point
+            # ---- decode until the next check point; no slot can run past its token limit, which bounds the steps
+            # to the next look at the done flags
             if graph is None and self.use_graph and max_steps > 2:
                 graph = self._capture(st)
-            # no slot can run past max_steps tokens: that bounds the steps to the next look at the done flags
-            left = [max_steps - slot_cnt[s] for s in range(B) if slot_req[s] >= 0]
-            n_steps = max(1, min(self.check_every, min(left) if waiting else max(left)))
+            left = [slot_lim[s] - slot_cnt[s] for s in range(B) if slot_req[s] is not None]
+            n_steps = max(1, min(self.check_every, min(left) if source.more_waiting() else max(left)))
             for _ in range(n_steps):
                 if graph is not None:
                     graph.replay()
@@ -508,9 +542,8 @@ class PagedEngine(BaseSampler):
                     self._decode_step(st)
             for s in range(B):
                 slot_cnt[s] += n_steps
-        return out_tok, out_lp
 
-    def _admit(self, st, slots_list, toks_np, lens_np, pad_id) -> None:
+    def _admit(self, st, slots_list, toks_np, lens_np, pad_id, limits) -> None:
         """Prefill the given prompts into their slots, sample each one's first token and set the slot state."""
         dev = self.device
         P = toks_np.shape[1]
@@ -528,14 +561,13 @@ class PagedEngine(BaseSampler):
         S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
                  out_tokens=nxt, out_logprobs=nlp, step_tensor=st["step"])
         ix = slots.to(torch.int64)
-        max_steps = st["out_tokens"].shape[1] - 1
+        lim = torch.as_tensor(limits, dtype=torch.int64, device=dev)
         st["out_tokens"][ix] = pad_id
         st["out_tokens"][ix, 0] = nxt
         st["out_lp"][ix, 0] = nlp
         st["out_pos"][ix] = 1
-        done = (nxt[:, None] == st["eos"]).any(-1)
-        if max_steps <= 1:
-            done = torch.ones_like(done)
+        st["limit"][ix] = lim
+        done = (nxt[:, None] == st["eos"]).any(-1) | (lim <= 1)
         st["done"][ix] = done
         st["tokens"][ix] = nxt
         # token 0 came from the prefill's last hidden state; it is fed at position `len`
@@ -552,8 +584,153 @@ class PagedEngine(BaseSampler):
             st[k].copy_(v)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread-local capture: other threads of the process (a trainer, another engine) keep using CUDA meanwhile
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self._decode_step(st)
         for k, v in snap.items():
             st[k].copy_(v)
         return graph
+
+
+class EngineServer:
+    """Server mode of `PagedEngine`: any thread submits single requests, which join the running batch at the next
+    check point instead of waiting for a batch to be assembled (the role of the reference's vLLM server mode,
+    tunix/generate/vllm_sampler.py:281-355, that agentic rollouts depend on: one prompt per call,
+    tunix/rl/agentic/agentic_rl_learner.py:441-500).
+
+    One loop thread owns the engine. Sampling parameters, the prompt window and the token limit's upper bound are
+    fixed per server (they shape the captured decode step); `max_tokens` is per request. `pause()` stops admission
+    and returns once the running requests have been delivered, so that weights can be updated in place;
+    `resume()` re-reads them (fused views, packed copies) and admits again."""
+
+    def __init__(self, engine: PagedEngine, *, max_new_tokens: int, max_prompt_length: int, temperature: float = 0.0,
+                 top_p: Optional[float] = None, top_k: Optional[int] = None, seed: int = 0,
+                 eos_tokens: Optional[Sequence[int]] = None):
+        import collections
+        import threading
+        if max_prompt_length + max_new_tokens > engine.cache_size:
+            raise ValueError("prompt + generation exceeds the configured cache size")
+        self.engine = engine
+        self.max_new_tokens = int(max_new_tokens)
+        self.P = int(max_prompt_length)
+        self.pad_id = engine.tokenizer.pad_id()
+        self._eos = list(eos_tokens) if eos_tokens else [engine.tokenizer.eos_id()]
+        self._sampling = (temperature, top_p, top_k, seed)
+        self._cv = threading.Condition()
+        self._queue = collections.deque()
+        self._futures: dict = {}
+        self._next_id = 0
+        self._paused = False
+        self._closed = False
+        self._drained = threading.Event()
+        self._error: Optional[BaseException] = None
+        self.admitted = 0
+        self._thread = threading.Thread(target=self._serve, name="tunix-b200-engine-server", daemon=True)
+        self._thread.start()
+
+    # ------------------------------------------------------------------ client side
+    def submit(self, prompt_token_ids, max_tokens: Optional[int] = None):
+        """Queue one request; the returned future resolves to (tokens int64 [n], logprobs float32 [n])."""
+        from concurrent.futures import Future
+        ids = list(prompt_token_ids)[-self.P:]
+        if not ids:
+            raise ValueError("empty prompt")
+        fut = Future()
+        with self._cv:
+            if self._closed or self._error is not None:
+                raise RuntimeError("engine server is closed") from self._error
+            rid = self._next_id
+            self._next_id += 1
+            self._futures[rid] = fut
+            self._queue.append((rid, ids, min(int(max_tokens or self.max_new_tokens), self.max_new_tokens)))
+            self._cv.notify_all()
+        return fut
+
+    def generate(self, prompt_token_ids, max_tokens: Optional[int] = None, timeout: Optional[float] = None):
+        return self.submit(prompt_token_ids, max_tokens).result(timeout)
+
+    def pause(self, timeout: Optional[float] = None) -> bool:
+        """Stop admitting requests and wait until the running ones are delivered. True when drained in time."""
+        with self._cv:
+            self._drained.clear()
+            self._paused = True
+            self._cv.notify_all()
+        return self._drained.wait(timeout)
+
+    def resume(self) -> None:
+        with self._cv:
+            self._paused = False
+            self._cv.notify_all()
+
+    def close(self, timeout: Optional[float] = 60.0) -> None:
+        with self._cv:
+            self._closed = True
+            self._cv.notify_all()
+        self._thread.join(timeout)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ------------------------------------------------------------------ request source of PagedEngine._loop
+    def take(self, n_free):
+        out = []
+        with self._cv:
+            while not self._paused and self._queue and len(out) < n_free:
+                rid, ids, lim = self._queue.popleft()
+                row = np.full(self.P, self.pad_id, np.int64)
+                row[self.P - len(ids):] = ids
+                out.append((rid, row, len(ids), lim))
+            self.admitted += len(out)
+        return out
+
+    def more_waiting(self):
+        with self._cv:
+            return bool(self._queue) and not self._paused
+
+    def deliver(self, rid, toks, lps):
+        with self._cv:
+            fut = self._futures.pop(rid)
+        fut.set_result((np.array(toks, np.int64), np.array(lps, np.float32)))
+
+    def idle(self):
+        refresh = False
+        with self._cv:
+            while True:
+                if self._closed:
+                    return False
+                if self._paused:
+                    self._drained.set()
+                    refresh = True
+                elif self._queue:
+                    break
+                self._cv.wait(0.05)
+        if refresh:                                   # weights may have been updated while the server was paused
+            self.engine._fuse_all()
+            if self.engine._packed_on:
+                self.engine._pack_all()
+        return True
+
+    def _serve(self):
+        eng = self.engine
+        try:
+            torch.cuda.set_device(eng.device)
+            with torch.no_grad():
+                eng._fuse_all()
+                eng._packed_on = eng.pack_weights and eng.max_running <= 128
+                if eng._packed_on:
+                    eng._pack_all()
+                t, p, k, seed = self._sampling
+                st = eng._new_state(eng.max_running, self.max_new_tokens, self._eos, self.pad_id, t, p, k, seed)
+                eng._loop(st, eng.max_running, self.max_new_tokens, self.pad_id, self)
+        except BaseException as e:                    # hand the failure to every waiting client
+            with self._cv:
+                self._error = e
+                self._closed = True
+                futs = list(self._futures.values())
+                self._futures.clear()
+            for f in futs:
+                f.set_exception(e)
+            self._drained.set()
