@@ -55,3 +55,42 @@ def test_gae_scan_matches_cpu_loop():
     a_cpu, ret_cpu = compute_gae_advantages(r, v, m, 0.99, 0.95, whiten=False)
     a_gpu, ret_gpu = compute_gae_advantages(r.cuda(), v.cuda(), m.cuda(), 0.99, 0.95, whiten=False)
     assert torch.allclose(a_gpu.cpu(), a_cpu, atol=1e-4, rtol=1e-4) and torch.allclose(ret_gpu.cpu(), ret_cpu, atol=1e-4, rtol=1e-4)
+
+
+def test_agentic_grpo_with_engine_server_mode():
+    """Agentic GRPO on the paged engine in server mode: every model call is its own request to the engine's
+    server; weights are synchronised between steps with the server paused."""
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200 import _lib, optim
+    from tunix_b200.common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
+    from tunix_b200.rl.agentic.parser.chat_template_parser import get_parser
+    from tunix_b200.rl.algorithm_config import GRPOConfig
+    from tunix_b200.rl.rl_cluster import RLCluster
+    cfg = ModelConfig(family="qwen3", num_layers=2, vocab_size=256, embed_dim=128, hidden_dim=256, num_heads=2, head_dim=64,
+                      num_kv_heads=1, qk_norm=True, dtype=torch.bfloat16, max_position=128)
+    dev = torch.device("cuda")
+    actor, ref = create_model(cfg, device=dev, seed=0), create_model(cfg, device=dev, seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
+                          train_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=16, temperature=1.0, seed=1, kv_cache_size=64, eos_tokens=[255])
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(), cluster_config=ClusterConfig(
+        role_to_mesh={}, training_config=tc, rollout_config=rc, rollout_engine="paged"))
+
+    def length_reward(prompts, completions, completion_lengths=None, **kw):
+        return [float(n % 3) for n in completion_lengths]
+    learner = AgenticGRPOLearner(cl, [length_reward], GRPOConfig(num_generations=2, beta=0.04), max_concurrency=4,
+                                 chat_parser=get_parser("raw"), server_mode=True)
+    served = []
+    orig = learner._server_call
+
+    def counting(ids, mt):
+        served.append(len(ids))
+        return orig(ids, mt)
+    learner._server_call = counting
+    learner.train([{"prompts": ["ab", "cd"]}, {"prompts": ["ef", "gh"]}])
+    _lib.raise_if_kernel_error()
+    assert cl.global_steps == 2 and learner.policy_version == 2
+    assert len(served) == 8                  # 2 steps x 2 prompts x 2 generations, one request each

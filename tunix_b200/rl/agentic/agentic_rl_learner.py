@@ -75,13 +75,19 @@ class _ModelCallBatcher:
 class AgenticRLLearner(abc.ABC):
     def __init__(self, rl_cluster: RLCluster, reward_fns, algo_config, *, agent_class=ModelAgent, agent_kwargs=None,
                  env_class=TaskEnvironment, env_kwargs=None, chat_parser=None, max_concurrency: int = 16,
-                 off_policy_steps: int = 0, max_turns: int = 1, episode_timeout: float = 600.0, metric_fns=None):
+                 off_policy_steps: int = 0, max_turns: int = 1, episode_timeout: float = 600.0, metric_fns=None,
+                 server_mode: bool = False):
         self.rl_cluster, self.algo_config = rl_cluster, algo_config
         self.tcfg = rl_cluster.cluster_config.training_config
         self.agent_class, self.agent_kwargs = agent_class, dict(agent_kwargs or {})
         self.env_class, self.env_kwargs = env_class, dict(env_kwargs or {})
         self.chat_parser = chat_parser
         self.max_concurrency, self.off_policy_steps = max_concurrency, off_policy_steps
+        # server mode: every model call is submitted on its own to the paged engine's server and joins the running
+        # batch there; otherwise concurrent calls are collected for a short window into one engine call
+        self.server_mode = server_mode
+        self._server = None
+        self._server_pool = None
         self.max_turns, self.episode_timeout = max_turns, episode_timeout
         self.metric_fns = list(metric_fns or [])
         self.reward_manager = None
@@ -114,7 +120,19 @@ class AgenticRLLearner(abc.ABC):
                         "policy_version": self.policy_version})
         return res
 
+    def _server_call(self, prompt_token_ids, max_tokens) -> dict:
+        with self.sync_lock.acquire_rollout():
+            toks, lps = self._server.generate(prompt_token_ids, max_tokens)
+            version = self.policy_version
+        tk = self.rl_cluster.tokenizer
+        stop = {tk.eos_id(), tk.pad_id()}
+        return {"text": tk.decode([int(t) for t in toks if int(t) not in stop]), "tokens": toks, "logprobs": lps,
+                "policy_version": version}
+
     async def _model_call(self, chat_completions=None, prompt_token_ids=None, max_tokens=None) -> dict:
+        if self._server is not None:
+            return await asyncio.get_running_loop().run_in_executor(self._server_pool, self._server_call,
+                                                                   list(prompt_token_ids), max_tokens)
         return await self._batcher.call(prompt_token_ids, max_tokens)
 
     # ------------------------------------------------------------- producer
@@ -137,6 +155,11 @@ class AgenticRLLearner(abc.ABC):
 
     async def _produce(self, batches: Iterable[dict], out_q: queue.Queue, permits: threading.Semaphore):
         self._batcher = _ModelCallBatcher(self._generate_batch, max_batch=self.max_concurrency)
+        start = getattr(self.rl_cluster.rollout, "start_server", None) if self.server_mode else None
+        if start is not None:
+            self._server = start(self.rl_cluster._rollout_config(Mode.TRAIN))
+            if self._server is not None:
+                self._server_pool = cf.ThreadPoolExecutor(max_workers=self.max_concurrency, thread_name_prefix="agentic-call")
         try:
             for bi, batch in enumerate(batches):
                 await asyncio.get_running_loop().run_in_executor(None, permits.acquire)
@@ -152,6 +175,10 @@ class AgenticRLLearner(abc.ABC):
             out_q.put(("error", -1, e))
         finally:
             self._batcher.close()
+            if self._server is not None:
+                self._server_pool.shutdown(wait=False, cancel_futures=True)
+                self._server.close()
+                self._server = None
             out_q.put(("done", -1, None))
 
     # ------------------------------------------------------------- consumer
@@ -186,8 +213,13 @@ class AgenticRLLearner(abc.ABC):
                     self.rl_cluster.update_actor(list(pending), None)
                 pending = []
                 with self.sync_lock.acquire_weight_sync():
+                    srv = self._server
+                    if srv is not None:
+                        srv.pause()             # no request is in flight under the lock; the server parks its loop
                     self.rl_cluster.sync_weights()
                     self.policy_version += 1
+                    if srv is not None:
+                        srv.resume()            # re-reads the updated weights before the next admission
                 self.rl_cluster.flush_metrics()
                 permits.release()
                 if max_steps is not None and self.rl_cluster.global_steps >= max_steps:

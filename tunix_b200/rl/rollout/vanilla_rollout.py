@@ -36,6 +36,18 @@ class VanillaRollout(BaseRollout):
                              left_padded_prompt_tokens=out.padded_prompt_tokens, logprobs=lps,
                              routed_experts=out.routed_experts, prompt_lengths=out.prompt_lengths)
 
+    def start_server(self, rollout_config: RolloutConfig):
+        """Server mode of the paged engine (single requests join the running batch): the continuous-batching
+        server the reference requires of vLLM for agentic rollouts (tunix/rl/agentic/agentic_rl_learner.py:293-301).
+        None on the dense sampler."""
+        if self._engine is None:
+            return None
+        from ...generate.engine import EngineServer
+        rc = rollout_config
+        return EngineServer(self._engine, max_new_tokens=rc.max_tokens_to_generate, max_prompt_length=rc.max_prompt_length,
+                            temperature=rc.temperature, top_p=rc.top_p, top_k=rc.top_k, seed=rc.seed or 0,
+                            eos_tokens=rc.eos_tokens)
+
     def get_per_token_logps(self, prompt_tokens, completion_tokens, completion_mask=None):
         return common.compute_per_token_logps(self.model(), prompt_tokens, completion_tokens, self.pad_id(), self.eos_id(),
                                               completion_mask=completion_mask, stop_gradient=True)
