@@ -86,3 +86,72 @@ def test_logits_match_huggingface(family, tmp_path):
         got = ours(toks)[0].float()
     assert got.shape == want.shape
     assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
+
+
+GEMMA4_CASES = {
+    # per-layer inputs, kv sharing over the last 4 layers, double-wide MLP in the sharing layers
+    "ple_shared": dict(hf=dict(num_hidden_layers=8, hidden_size_per_layer_input=8, vocab_size_per_layer_input=128,
+                               num_kv_shared_layers=4, use_double_wide_mlp=True, num_key_value_heads=1),
+                       ours=dict(num_layers=8, per_layer_input_dim=8, num_kv_shared_layers=4, kv_shared_hidden_dim=192,
+                                 num_kv_heads=1, layer_pattern=("local", "local", "local", "global"))),
+    # keys double as values on the global layers, fewer global kv heads
+    "k_eq_v": dict(hf=dict(num_hidden_layers=4, hidden_size_per_layer_input=0, attention_k_eq_v=True,
+                           num_global_key_value_heads=1, num_key_value_heads=2),
+                   ours=dict(num_layers=4, k_eq_v_global=True, num_global_kv_heads=1, num_kv_heads=2,
+                             layer_pattern=("local", "local", "local", "global"))),
+    # MoE block beside the dense MLP
+    "moe": dict(hf=dict(num_hidden_layers=4, hidden_size_per_layer_input=0, enable_moe_block=True, num_experts=4,
+                        top_k_experts=2, moe_intermediate_size=32, num_key_value_heads=2),
+                ours=dict(num_layers=4, num_experts=4, num_experts_per_tok=2, moe_hidden_dim=32, num_kv_heads=2,
+                          layer_pattern=("local", "local", "local", "global"))),
+}
+
+
+@pytest.mark.parametrize("case", sorted(GEMMA4_CASES))
+def test_gemma4_logits_match_huggingface(case, tmp_path):
+    from tunix_b200.models import safetensors_loader
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.transformer import create_model
+    t = transformers
+    if not hasattr(t, "Gemma4ForCausalLM"):
+        pytest.skip("transformers without Gemma 4")
+    spec = GEMMA4_CASES[case]
+    torch.manual_seed(0)
+    L = spec["hf"]["num_hidden_layers"]
+    hcfg = t.Gemma4TextConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_attention_heads=4, head_dim=16,
+                              global_head_dim=32, rms_norm_eps=1e-6, sliding_window=8, max_position_embeddings=64,
+                              final_logit_softcapping=30.0, attn_implementation="eager",
+                              layer_types=["sliding_attention" if (i + 1) % 4 else "full_attention" for i in range(L)],
+                              **spec["hf"])
+    hf = t.Gemma4ForCausalLM(hcfg).eval().float()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.05)
+        if "norm" in n or n.endswith("scale"):
+            p.data.add_(1.0)
+    for n, b in hf.named_buffers():
+        if n.endswith("layer_scalar"):
+            b.fill_(0.5 + 0.1 * int(n.split(".")[2]))
+    _save(hf, str(tmp_path))
+    cfg = Gemma4Config._base(vocab_size=128, embed_dim=64, hidden_dim=96, num_heads=4, head_dim=16, global_head_dim=32,
+                             sliding_window=8, max_position=64, dtype=torch.float32, **spec["ours"])
+    ours = create_model(cfg, seed=1)
+    unused = safetensors_loader.load_safetensors_into(ours, str(tmp_path))
+    # the only checkpoint tensors without a home are the k/v weights HF keeps for the kv-sharing layers
+    assert all(".self_attn.k_" in k or ".self_attn.v_" in k for k in unused), unused
+    ours.eval()
+    toks = torch.randint(1, 128, (2, 19))
+    with torch.no_grad():
+        want = hf(toks, use_cache=True).logits.float()
+        got = ours(toks)[0].float()
+    assert torch.allclose(got, want, atol=5e-4, rtol=2e-3), float((got - want).abs().max())
+    # prefill + one decode step through the dense cache (kv-sharing layers read their source layer's cache)
+    with torch.no_grad():
+        cache = ours.init_cache(2, 32)
+        _, cache = ours(toks[:, :18], cache=cache)
+        step, _ = ours(toks[:, 18:19], positions=torch.full((2, 1), 18, dtype=torch.int32), cache=cache)
+    assert torch.allclose(step[:, 0].float(), want[:, 18], atol=5e-4, rtol=2e-3)
+    # gradients reach every parameter
+    ours.train()
+    loss = ours(toks)[0].float().logsumexp(-1).mean()
+    loss.backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in ours.parameters())

@@ -282,6 +282,11 @@ PRESETS = {name: getattr(ModelConfig, name) for name in dir(ModelConfig)
 def get_config(name: str) -> ModelConfig:
     """Look up a preset by config id (e.g. `llama3p1_8b`, `qwen3_8b`, `gemma2_9b`)."""
     key = name.lower().replace("-", "_").replace(".", "p")
+    if key.startswith("gemma4") and key not in PRESETS:
+        from .gemma4 import Gemma4Config          # registered on first use: gemma4 imports this module
+        for n in ("gemma4_e2b", "gemma4_e4b", "gemma4_12b", "gemma4_31b", "gemma4_26b_a4b"):
+            PRESETS[n] = getattr(Gemma4Config, n)
+            PRESETS[n + "_it"] = getattr(Gemma4Config, n)
     if key not in PRESETS:
         raise KeyError(f"unknown model config '{name}'; known: {sorted(PRESETS)}")
     return PRESETS[key]()

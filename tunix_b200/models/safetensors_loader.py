@@ -37,10 +37,27 @@ _KEY_MAPS = {
         (r"model\.layers\.(\d+)\.pre_feedforward_layernorm\.weight", r"layers.\1.post_attention_layernorm.weight"),
         (r"model\.layers\.(\d+)\.post_feedforward_layernorm\.weight", r"layers.\1.post_ffw_norm.weight"),
     ],
+    # Gemma-4 keeps the HF norm names; "a|b" = the tensor is split in equal parts along its second-to-last axis
+    "gemma4": _COMMON + [
+        (r"model\.embed_tokens_per_layer\.weight", "embed_tokens_per_layer"),
+        (r"model\.per_layer_(model_projection|projection_norm)\.weight", r"per_layer_\1.weight"),
+        (r"model\.layers\.(\d+)\.(post_attention|pre_feedforward|post_feedforward)_layernorm\.weight", r"layers.\1.\2_layernorm.weight"),
+        (r"model\.layers\.(\d+)\.(post_feedforward_layernorm_1|post_feedforward_layernorm_2|pre_feedforward_layernorm_2)\.weight",
+         r"layers.\1.\2.weight"),
+        (r"model\.layers\.(\d+)\.(per_layer_input_gate|per_layer_projection|post_per_layer_input_norm)\.weight", r"layers.\1.\2.weight"),
+        (r"model\.layers\.(\d+)\.layer_scalar", r"layers.\1.layer_scalar"),
+        (r"model\.layers\.(\d+)\.router\.proj\.weight", r"layers.\1.moe.router.weight"),
+        (r"model\.layers\.(\d+)\.router\.scale", r"layers.\1.moe.router_scale"),
+        (r"model\.layers\.(\d+)\.router\.per_expert_scale", r"layers.\1.moe.per_expert_scale"),
+        (r"model\.layers\.(\d+)\.experts\.gate_up_proj", r"layers.\1.moe.gate_proj|layers.\1.moe.up_proj"),
+        (r"model\.layers\.(\d+)\.experts\.down_proj", r"layers.\1.moe.down_proj"),
+    ],
 }
 
 
 def key_map_for(cfg) -> list:
+    if cfg.family == "gemma4":
+        return _KEY_MAPS["gemma4"]
     return _KEY_MAPS["gemma_post_norms" if cfg.post_norms else "default"]
 
 
@@ -79,6 +96,7 @@ def load_safetensors_into(model, path: str, dtype: Optional[torch.dtype] = None,
         raise FileNotFoundError(f"no safetensors files under {path}")
     table = key_map_for(model.config)
     params = dict(model.named_parameters())
+    params.update({n: b for n, b in model.named_buffers() if n.endswith("layer_scalar")})
     seen, unused = set(), []
     with torch.no_grad():
         for f in files:
@@ -91,6 +109,12 @@ def load_safetensors_into(model, path: str, dtype: Optional[torch.dtype] = None,
                     t = sf.get_tensor(key)
                     if preprocess_fn is not None:
                         t = preprocess_fn(name, t)
+                    if "|" in name:
+                        names = name.split("|")
+                        for nm, part in zip(names, t.chunk(len(names), dim=-2)):
+                            params[nm].copy_(part.to(params[nm].device, dtype or params[nm].dtype))
+                            seen.add((nm, None))
+                        continue
                     expert = None
                     if "#" in name:
                         name, e = name.split("#")
@@ -109,7 +133,7 @@ def load_safetensors_into(model, path: str, dtype: Optional[torch.dtype] = None,
     if strict:
         missing = []
         for n, p in params.items():
-            if "lora_" in n:
+            if "lora_" in n or (n, None) in seen:
                 continue
             if p.dim() == 3 and n.endswith(("gate_proj", "up_proj", "down_proj")) and model.config.is_moe:
                 missing += [f"{n}#{e}" for e in range(p.shape[0]) if (n, e) not in seen]
@@ -122,9 +146,9 @@ def load_safetensors_into(model, path: str, dtype: Optional[torch.dtype] = None,
 
 def create_model_from_safe_tensors(path: str, config, device=None, dtype: Optional[torch.dtype] = None):
     """Build the model of `config` and fill it from the checkpoint at `path`."""
-    from .transformer import Transformer
+    from .transformer import create_model
     if dtype is not None:
         config = config.replace(dtype=dtype)
-    model = Transformer(config, device=device)
+    model = create_model(config, device=device, init=False)
     load_safetensors_into(model, path)
     return model

@@ -397,7 +397,11 @@ class Transformer(nn.Module):
 def create_model(cfg: ModelConfig, device=None, seed: int = 0, init: bool = True) -> Transformer:
     """Random-init model of the given architecture (dummy-model creator of the reference:
     tunix/models/dummy_model_creator.py:29-92)."""
-    model = Transformer(cfg, device=device)
+    if cfg.family == "gemma4":
+        from .gemma4 import Gemma4Transformer
+        model = Gemma4Transformer(cfg, device=device)
+    else:
+        model = Transformer(cfg, device=device)
     if init:
         model.init_weights(seed)
     return model
