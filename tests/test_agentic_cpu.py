@@ -38,6 +38,15 @@ def test_tools_and_parsers():
     assert get_parser("qwen").parse(msgs, add_generation_prompt=True).endswith("<|im_start|>assistant\n")
     assert get_parser("gemma").parse(msgs).startswith("<bos><start_of_turn>user")
     assert "<|eot_id|>" in get_parser("llama").parse(msgs)
+    g4 = get_parser("gemma4")
+    assert g4.parse(msgs, add_generation_prompt=True) == "<bos><|turn>system\n<|think|><turn|>\n<|turn>user\nhi<turn|>\n<|turn>model\n"
+    assert g4.parse([{"role": "assistant", "content": "ok<turn|>"}, {"role": "tool", "content": "42"}], is_first_msg=False) == \
+        "<|turn>model\nok<turn|>\n<|tool_response>42<tool_response|>"
+    from tunix_b200.rl.agentic.parser.chat_template_parser import Gemma4ChatTemplateParser
+    quiet = Gemma4ChatTemplateParser(CharTok(), enable_thinking=False)
+    assert quiet.parse(msgs, add_generation_prompt=True).endswith("<|turn>model\n<|channel>thought\n<channel|>")
+    toks, n = quiet.update_assistant_end_tokens(np.asarray([5, 6]))
+    assert n == 1 and len(toks) == 3
 
 
 def test_group_queue_and_sync_lock():

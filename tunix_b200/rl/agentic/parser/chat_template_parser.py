@@ -76,13 +76,64 @@ class GemmaChatTemplateParser(ChatTemplateParser):
         return f"<start_of_turn>{role}\n{m['content']}<end_of_turn>\n"
 
 
+class Gemma4ChatTemplateParser(ChatTemplateParser):
+    """Gemma 4 turns (`<|turn>role\\n ... <turn|>\\n`), with the thinking switch of the family: thinking on puts
+    `<|think|>` into the system turn (one is made up when the conversation has none); thinking off opens the model
+    turn with an empty thought channel (tunix/rl/agentic/parser/chat_template_parser/parser.py:436-540)."""
+    assistant_end = "<turn|>"
+
+    def __init__(self, tokenizer=None, enable_thinking: bool = True):
+        super().__init__(tokenizer)
+        self.enable_thinking = enable_thinking
+        self.generation_prompt = "<|turn>model\n" + ("" if enable_thinking else "<|channel>thought\n<channel|>")
+
+    def parse(self, messages, add_generation_prompt: bool = False, is_first_msg: bool = True) -> str:
+        out = ""
+        if is_first_msg:
+            out = "<bos>"
+            if messages and messages[0]["role"] not in ("system", "developer") and self.enable_thinking:
+                out += "<|turn>system\n<|think|><turn|>\n"
+        for m in messages:
+            out += self.render_message(m)
+        if add_generation_prompt:
+            out += self.generation_prompt
+        return out
+
+    def render_message(self, m):
+        role, content = m["role"], str(m["content"]).replace("<turn|>\n", "").strip()
+        if role in ("system", "developer"):
+            return "<|turn>system\n" + ("<|think|>" if self.enable_thinking else "") + content + "<turn|>\n"
+        if role == "tool":
+            return "<|tool_response>" + str(m["content"]) + "<tool_response|>"
+        if role == "assistant":
+            body = str(m["content"]).strip()
+            prefix = "<|turn>model\n" if self.enable_thinking else self.generation_prompt
+            return prefix + body + ("\n" if body.endswith("<turn|>") else "<turn|>\n")
+        return "<|turn>user\n" + content.replace("<turn|>", "") + "<turn|>\n"
+
+    def update_assistant_end_tokens(self, tokens):
+        """An assistant turn is rendered with a newline after its end token, so the sampled tokens get the same
+        suffix (otherwise rollout and trainer log-probs disagree). Returns (tokens, number appended)."""
+        import numpy as np
+        try:
+            nl = self.tokenizer.encode("\n", add_special_tokens=False)
+        except TypeError:
+            nl = self.tokenizer.encode("\n")
+        special = set()
+        for name in ("bos_id", "eos_id"):
+            v = getattr(self.tokenizer, name, None)
+            special.add(v() if callable(v) else v)
+        nl = [t for t in nl if t not in special]
+        return np.concatenate([np.asarray(tokens), np.asarray(nl, dtype=np.int32)]), len(nl)
+
+
 class RawTextParser(ChatTemplateParser):
     def render_message(self, m):
         return str(m["content"])
 
 
 _PARSERS = {"default": DefaultChatTemplateParser, "qwen": QwenChatTemplateParser, "llama": LlamaChatTemplateParser,
-            "gemma": GemmaChatTemplateParser, "raw": RawTextParser}
+            "gemma": GemmaChatTemplateParser, "gemma4": Gemma4ChatTemplateParser, "raw": RawTextParser}
 
 
 def get_parser(kind: str = "default", tokenizer=None) -> ChatTemplateParser:
