@@ -1,4 +1,5 @@
 """Vision tower, soft-token splice and bidirectional image spans (CPU, tiny sizes)."""
+import pytest
 import torch
 
 from tunix_b200.models import vision as V
@@ -44,3 +45,103 @@ def test_multimodal_forward_backward_and_bidirectional_mask():
     assert not torch.allclose(a[0, 1], b[0, 1])
     text_only = mm(toks[:, 5:])[0]
     assert text_only.shape == (1, 3, 128)
+
+
+@pytest.mark.parametrize("clipped,standardize", [(False, False), (True, True)])
+def test_gemma4_vision_tower_matches_huggingface(clipped, standardize):
+    t = pytest.importorskip("transformers")
+    if not hasattr(t, "Gemma4VisionConfig"):
+        pytest.skip("transformers without Gemma 4")
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4VisionModel
+    from tunix_b200.models.gemma4_vision import Gemma4VisionConfig, Gemma4VisionTower
+    torch.manual_seed(0)
+    hcfg = t.Gemma4VisionConfig(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=4, head_dim=16, patch_size=4, position_embedding_size=32,
+                                pooling_kernel_size=2, use_clipped_linears=clipped, standardize=standardize,
+                                attn_implementation="eager")
+    hf = Gemma4VisionModel(hcfg).eval().float()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.1)
+        if "norm" in n:
+            p.data.add_(1.0)
+    for n, b in hf.named_buffers():
+        if n.endswith("_min"):
+            b.fill_(-1.5)
+        elif n.endswith("_max"):
+            b.fill_(1.5)
+        elif n.endswith("std_bias"):
+            b.copy_(torch.randn_like(b) * 0.1)
+        elif n.endswith("std_scale"):
+            b.copy_(1.0 + torch.rand_like(b))
+    ours = Gemma4VisionTower(Gemma4VisionConfig(hidden_size=64, intermediate_size=96, num_layers=2, num_heads=4, num_kv_heads=4,
+                                                head_dim=16, patch_size=4, position_embedding_size=32, pooling_kernel_size=2,
+                                                use_clipped_linears=clipped, standardize=standardize, dtype=torch.float32))
+    missing, unexpected = ours.load_state_dict({k: v for k, v in hf.state_dict().items() if "rotary" not in k}, strict=False)
+    assert not unexpected and all("_unit" in m for m in missing), (missing, unexpected)
+    # image 0: 6 x 4 patches; image 1: 4 x 4 patches and 8 padding entries
+    P = 24
+    pos = torch.full((2, P, 2), -1, dtype=torch.long)
+    pos[0] = torch.tensor([[x, y] for y in range(4) for x in range(6)])
+    pos[1, :16] = torch.tensor([[x, y] for y in range(4) for x in range(4)])
+    pix = torch.rand(2, P, 48)
+    pix[1, 16:] = 0
+    with torch.no_grad():
+        want = hf(pix, pos).last_hidden_state
+        soft, valid = ours(pix, pos)
+    assert valid.sum().item() == 6 + 4 and want.shape[0] == 10
+    assert torch.allclose(soft[valid], want, atol=2e-4, rtol=2e-3), float((soft[valid] - want).abs().max())
+
+
+def test_gemma4_multimodal_matches_huggingface(tmp_path):
+    t = pytest.importorskip("transformers")
+    if not hasattr(t, "Gemma4VisionConfig"):
+        pytest.skip("transformers without Gemma 4")
+    from safetensors.torch import save_file
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4Model
+    from tunix_b200.models import safetensors_loader
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.gemma4_vision import Gemma4Multimodal, Gemma4VisionConfig
+    from tunix_b200.models.transformer import create_model
+    torch.manual_seed(0)
+    IMG = 120
+    tcfg = t.Gemma4TextConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4,
+                              num_key_value_heads=2, head_dim=16, global_head_dim=32, rms_norm_eps=1e-6, sliding_window=8,
+                              max_position_embeddings=64, hidden_size_per_layer_input=8, vocab_size_per_layer_input=128,
+                              layer_types=["sliding_attention"] * 3 + ["full_attention"], attn_implementation="eager")
+    vcfg = t.Gemma4VisionConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                                num_key_value_heads=2, head_dim=16, patch_size=4, position_embedding_size=32,
+                                pooling_kernel_size=2, attn_implementation="eager")
+    hf = Gemma4Model(t.Gemma4Config(text_config=tcfg, vision_config=vcfg, audio_config=None, image_token_id=IMG)).eval().float()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.08)
+        if "norm" in n:
+            p.data.add_(1.0)
+    sd = hf.state_dict()
+    # key names of a Gemma4ForConditionalGeneration checkpoint: model.language_model.*
+    save_file({"model." + k: v.clone().contiguous() for k, v in sd.items() if k.startswith("language_model.")
+               and "rotary" not in k}, str(tmp_path / "model.safetensors"))
+    lm = create_model(Gemma4Config._base(vocab_size=128, embed_dim=64, hidden_dim=96, num_layers=4, num_heads=4, num_kv_heads=2,
+                                         head_dim=16, global_head_dim=32, sliding_window=8, max_position=64,
+                                         per_layer_input_dim=8, layer_pattern=("local", "local", "local", "global"),
+                                         dtype=torch.float32), seed=3)
+    safetensors_loader.load_safetensors_into(lm, str(tmp_path))
+    ours = Gemma4Multimodal(lm, Gemma4VisionConfig(hidden_size=32, intermediate_size=48, num_layers=1, num_heads=2, num_kv_heads=2,
+                                                   head_dim=16, patch_size=4, position_embedding_size=32, pooling_kernel_size=2,
+                                                   image_token_id=IMG, dtype=torch.float32),
+                            pad_token_id=tcfg.pad_token_id).eval()
+    ours.vision_tower.load_state_dict({k[len("vision_tower."):]: v for k, v in sd.items()
+                                       if k.startswith("vision_tower.") and "rotary" not in k}, strict=False)
+    ours.embed_vision.load_state_dict({k[len("embed_vision."):]: v for k, v in sd.items() if k.startswith("embed_vision.")},
+                                      strict=False)
+    P = 24
+    pos = torch.full((2, P, 2), -1, dtype=torch.long)
+    pos[0] = torch.tensor([[x, y] for y in range(4) for x in range(6)])
+    pos[1, :16] = torch.tensor([[x, y] for y in range(4) for x in range(4)])
+    pix = torch.rand(2, P, 48)
+    toks = torch.randint(1, 100, (2, 20))
+    toks[0, 3:9] = IMG          # 6 soft tokens
+    toks[1, 5:9] = IMG          # 4 soft tokens
+    with torch.no_grad():
+        want = hf(input_ids=toks, pixel_values=pix, image_position_ids=pos, use_cache=True).last_hidden_state
+        got = ours(toks, pixel_values=pix, pixel_position_ids=pos, skip_lm_head=True)[0]
+    assert torch.allclose(got, want, atol=5e-4, rtol=2e-3), float((got - want).abs().max())

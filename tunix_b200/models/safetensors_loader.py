@@ -62,7 +62,8 @@ def key_map_for(cfg) -> list:
 
 
 def map_key(hf_key: str, table: list) -> Optional[str]:
-    hf_key = re.sub(r"^language_model\.", "", hf_key)
+    hf_key = re.sub(r"^language_model\.", "", hf_key)                 # language_model.model.layers... (Gemma 3)
+    hf_key = re.sub(r"^model\.language_model\.", "model.", hf_key)    # model.language_model.layers... (Gemma 4)
     for pat, repl in table:
         m = re.fullmatch(pat, hf_key)
         if m:
