@@ -145,3 +145,42 @@ def test_gemma4_multimodal_matches_huggingface(tmp_path):
         want = hf(input_ids=toks, pixel_values=pix, image_position_ids=pos, use_cache=True).last_hidden_state
         got = ours(toks, pixel_values=pix, pixel_position_ids=pos, skip_lm_head=True)[0]
     assert torch.allclose(got, want, atol=5e-4, rtol=2e-3), float((got - want).abs().max())
+
+
+def test_gemma4_audio_tower_matches_huggingface():
+    t = pytest.importorskip("transformers")
+    if not hasattr(t, "Gemma4AudioConfig"):
+        pytest.skip("transformers without Gemma 4")
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4AudioModel
+    from tunix_b200.models.gemma4_audio import Gemma4AudioConfig, Gemma4AudioTower
+    torch.manual_seed(0)
+    # "sdpa" makes the reference build boolean masks; with "eager" it builds additive ones, which its local attention
+    # (written for booleans) reads the wrong way round
+    hcfg = t.Gemma4AudioConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=4, subsampling_conv_channels=[16, 8],
+                               conv_kernel_size=5, attention_chunk_size=4, attention_context_left=13, attention_context_right=0,
+                               output_proj_dims=24, use_clipped_linears=True, attn_implementation="sdpa")
+    hf = Gemma4AudioModel(hcfg).eval().float()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.15)
+        if "norm" in n:
+            p.data.add_(1.0)
+    for n, b in hf.named_buffers():
+        if n.endswith("_min"):
+            b.fill_(-2.0)
+        elif n.endswith("_max"):
+            b.fill_(2.0)
+    ours = Gemma4AudioTower(Gemma4AudioConfig(hidden_size=32, num_layers=2, num_heads=4, subsampling_conv_channels=(16, 8),
+                                              conv_kernel_size=5, attention_chunk_size=4, output_proj_dims=24,
+                                              use_clipped_linears=True, dtype=torch.float32))
+    missing, unexpected = ours.load_state_dict({k: v for k, v in hf.state_dict().items()
+                                                if "rel_pos_enc" not in k and not k.endswith("softcap")}, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    feats = torch.randn(2, 40, 16)
+    mask = torch.ones(2, 40, dtype=torch.bool)
+    mask[1, 28:] = False
+    with torch.no_grad():
+        out = hf(feats, mask)
+        got, valid = ours(feats, mask)
+    assert torch.equal(valid, out.attention_mask.bool())
+    want = out.last_hidden_state
+    assert torch.allclose(got[valid], want[valid], atol=3e-4, rtol=2e-3), float((got[valid] - want[valid]).abs().max())

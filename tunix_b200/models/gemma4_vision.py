@@ -203,21 +203,38 @@ class Gemma4MultimodalEmbedder(nn.Module):
         return self.embedding_projection(F.rmsnorm(soft, self._unit, self.eps, False))
 
 
+def splice_soft_tokens(emb: torch.Tensor, is_slot: torch.Tensor, soft: torch.Tensor, valid: torch.Tensor) -> torch.Tensor:
+    """emb [B, T, D]; is_slot [B, T] true at placeholder tokens; soft [B, S, D] with validity [B, S]. The k-th
+    placeholder of a row receives the k-th valid soft token of that row."""
+    B, T, D = emb.shape
+    order = torch.argsort((~valid).to(torch.int8), dim=1, stable=True)                  # valid ones first, in order
+    rank = (torch.cumsum(is_slot.long(), 1) - 1).clamp(min=0, max=soft.shape[1] - 1)
+    picked = soft.gather(1, order.gather(1, rank)[..., None].expand(B, T, D))
+    return torch.where(is_slot[..., None], picked.to(emb.dtype), emb)
+
+
 class Gemma4Multimodal(nn.Module):
-    """Gemma 4 decoder with the vision encoder in front. `forward(tokens, pixel_values=..., pixel_position_ids=...)`
-    puts the k-th valid soft token of a row over its k-th image placeholder token; per-layer inputs of those
+    """Gemma 4 decoder with the vision (and optionally the audio) encoder in front.
+    `forward(tokens, pixel_values=..., pixel_position_ids=..., input_features=..., input_features_mask=...)` puts
+    the k-th valid soft token of a row over its k-th placeholder token of that modality; per-layer inputs of those
     positions come from the padding token, as in the reference. With `bidirectional_images` the tokens of one
     image attend to each other in both directions (the 31B / 26B-A4B checkpoints)."""
 
     def __init__(self, language_model, vision_config: Gemma4VisionConfig, bidirectional_images: bool = False,
-                 pad_token_id: int = 0, device=None):
+                 pad_token_id: int = 0, audio_config=None, device=None):
         super().__init__()
         self.language_model = language_model
         self.vision_config = vision_config
+        self.audio_config = audio_config
         self.vision_tower = Gemma4VisionTower(vision_config, device)
         lm_cfg = language_model.config
         self.embed_vision = Gemma4MultimodalEmbedder(vision_config.hidden_size, lm_cfg.embed_dim, vision_config.norm_eps,
                                                      lm_cfg.dtype, device)
+        if audio_config is not None:
+            from .gemma4_audio import Gemma4AudioTower
+            self.audio_tower = Gemma4AudioTower(audio_config, device)
+            self.embed_audio = Gemma4MultimodalEmbedder(audio_config.output_proj_dims, lm_cfg.embed_dim, audio_config.norm_eps,
+                                                        lm_cfg.dtype, device)
         self.bidirectional_images = bidirectional_images
         self.pad_token_id = pad_token_id
         self.config = lm_cfg
@@ -226,32 +243,33 @@ class Gemma4Multimodal(nn.Module):
         soft, valid = self.vision_tower(pixel_values, pixel_position_ids)
         return self.embed_vision(soft), valid
 
-    def forward(self, input_tokens, pixel_values=None, pixel_position_ids=None, positions=None, segment_ids=None,
-                skip_lm_head: bool = False, **kw):
-        lm, vc = self.language_model, self.vision_config
-        if pixel_values is None:
+    def encode_audio(self, input_features, input_features_mask=None):
+        frames, valid = self.audio_tower(input_features, input_features_mask)
+        return self.embed_audio(frames), valid
+
+    def forward(self, input_tokens, pixel_values=None, pixel_position_ids=None, input_features=None,
+                input_features_mask=None, positions=None, segment_ids=None, skip_lm_head: bool = False, **kw):
+        lm, vc, ac = self.language_model, self.vision_config, self.audio_config
+        if pixel_values is None and input_features is None:
             return lm(input_tokens, positions=positions, segment_ids=segment_ids, skip_lm_head=skip_lm_head, **kw)
         cfg = lm.config
+        B, T = input_tokens.shape
         is_img = input_tokens == vc.image_token_id
-        safe = torch.where(is_img, torch.full_like(input_tokens, self.pad_token_id), input_tokens)
+        is_aud = (input_tokens == ac.audio_token_id) if ac is not None else torch.zeros_like(is_img)
+        safe = torch.where(is_img | is_aud, torch.full_like(input_tokens, self.pad_token_id), input_tokens)
         emb = F.embedding(safe, lm.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
-        soft, valid = self.encode_images(pixel_values, pixel_position_ids)
-        B, T, D = emb.shape
-        n_img = soft.shape[0] // B
-        soft = soft.reshape(B, n_img * soft.shape[1], D)
-        valid = valid.reshape(B, -1)
-        # k-th placeholder of a row <- k-th valid soft token of that row
-        order = torch.argsort((~valid).to(torch.int8), dim=1, stable=True)              # valid ones first, in order
-        rank = (torch.cumsum(is_img.long(), 1) - 1).clamp(min=0, max=soft.shape[1] - 1)
-        src = order.gather(1, rank)
-        picked = soft.gather(1, src[..., None].expand(B, T, D))
-        emb = torch.where(is_img[..., None], picked.to(emb.dtype), emb)
+        if pixel_values is not None:
+            soft, valid = self.encode_images(pixel_values, pixel_position_ids)
+            emb = splice_soft_tokens(emb, is_img, soft.reshape(B, -1, soft.shape[-1]), valid.reshape(B, -1))
+        if input_features is not None:
+            soft, valid = self.encode_audio(input_features, input_features_mask)
+            emb = splice_soft_tokens(emb, is_aud, soft.reshape(B, -1, soft.shape[-1]), valid.reshape(B, -1))
         ple = lm.per_layer_inputs(safe, emb) if cfg.per_layer_input_dim else None
         mask = None
-        if self.bidirectional_images:
+        if self.bidirectional_images and pixel_values is not None:
             from . import cache_utils
             start = is_img & ~torch.nn.functional.pad(is_img, (1, 0))[:, :-1]
-            spans = torch.where(is_img, torch.cumsum(start.long(), 1), torch.zeros_like(rank))
+            spans = torch.where(is_img, torch.cumsum(start.long(), 1), torch.zeros_like(input_tokens, dtype=torch.long))
             pos = torch.arange(T, device=input_tokens.device)
             mask = torch.stack([cache_utils.prefill_mask(pos, pos, bidirectional_span=spans[b]) for b in range(B)])
         return lm.forward_embeddings(emb, positions=positions, attention_mask=mask, segment_ids=segment_ids,
