@@ -8,7 +8,7 @@ from .config import PRESETS, ModelConfig, get_config
 
 _FAMILY_PATTERNS = [
     (r"llama[-_]?3", "llama3"), (r"qwen[-_]?3", "qwen3"), (r"qwen[-_]?2", "qwen2"), (r"deepseek[-_]?r1[-_]?distill[-_]?qwen", "qwen2"),
-    (r"gemma[-_]?3", "gemma3"), (r"gemma[-_]?2", "gemma2"), (r"gemma", "gemma"),
+    (r"gemma[-_]?4", "gemma4"), (r"gemma[-_]?3", "gemma3"), (r"gemma[-_]?2", "gemma2"), (r"gemma", "gemma"),
 ]
 
 
@@ -39,6 +39,8 @@ def get_model_config_id(model_name: str) -> str:
     n = n.replace("meta-", "")
     n = re.sub(r"^(llama|qwen|gemma)[-_]?(\d+)(?:\.(\d+))?", lambda m: f"{m.group(1)}{m.group(2)}" + (f"p{m.group(3)}" if m.group(3) else ""), n)
     n = n.replace("-", "_").replace(".", "p")
+    if n.startswith("gemma4"):
+        get_config("gemma4_e2b")          # Gemma-4 presets register on first use
     if n in PRESETS:
         return n
     # tolerate size suffix variants ("8b" vs "8B") and missing minor versions

@@ -49,5 +49,6 @@ for _fam, _pref, _tmpl in (("llama3", ("llama-3", "meta-llama-3", "llama3"), "ll
                            ("qwen3", ("qwen3",), "qwen"),
                            ("gemma", ("gemma-2b", "gemma-7b", "gemma-1.1"), "gemma"),
                            ("gemma2", ("gemma-2-",), "gemma"),
-                           ("gemma3", ("gemma-3-",), "gemma")):
+                           ("gemma3", ("gemma-3-",), "gemma"),
+                           ("gemma4", ("gemma-4-",), "gemma4")):
     register_family(FamilyEntry(_fam, config_lib.get_config, _pref, _tmpl))
