@@ -155,3 +155,29 @@ def test_gemma4_logits_match_huggingface(case, tmp_path):
     loss = ours(toks)[0].float().logsumexp(-1).mean()
     loss.backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in ours.parameters())
+
+
+def test_gemma4_export_round_trip(tmp_path):
+    """Saver -> loader round trip of a Gemma-4 model with every special tensor (per-layer inputs, experts, router,
+    layer scalars), and the exported names are the ones `transformers` uses."""
+    from tunix_b200.models import safetensors_loader, safetensors_saver
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.transformer import create_model
+    cfg = Gemma4Config._base(vocab_size=64, embed_dim=32, hidden_dim=48, num_layers=4, num_heads=2, num_kv_heads=1, head_dim=16,
+                             global_head_dim=32, sliding_window=8, max_position=32, per_layer_input_dim=8, num_experts=4,
+                             num_experts_per_tok=2, moe_hidden_dim=16, layer_pattern=("local", "global"), dtype=torch.float32)
+    a = create_model(cfg, seed=5)
+    with torch.no_grad():
+        for i, layer in enumerate(a.layers):
+            layer.layer_scalar.fill_(0.5 + i)
+    safetensors_saver.save_lora_merged_model_as_safetensors(a, str(tmp_path))
+    from safetensors import safe_open
+    with safe_open(str(tmp_path / "model.safetensors"), "pt") as f:
+        keys = set(f.keys())
+    assert {"model.embed_tokens_per_layer.weight", "model.layers.0.experts.gate_up_proj", "model.layers.1.router.proj.weight",
+            "model.layers.2.router.per_expert_scale", "model.layers.3.layer_scalar"} <= keys
+    b = create_model(cfg, seed=6)
+    assert safetensors_loader.load_safetensors_into(b, str(tmp_path)) == []
+    toks = torch.randint(1, 64, (2, 9))
+    with torch.no_grad():
+        assert torch.equal(a(toks)[0], b(toks)[0])
