@@ -90,6 +90,8 @@ class PagedEngine(BaseSampler):
             raise ValueError("PagedEngine runs bf16 models on CUDA; use Sampler elsewhere")
         if self.cfg.is_moe:
             raise NotImplementedError("MoE decode goes through Sampler")
+        if self.cfg.family == "gemma4":
+            raise NotImplementedError("Gemma-4 decode (per-layer inputs, shared KV, 512-wide heads) goes through Sampler")
         self.page_size = page_size
         self.max_running = max_running_requests
         self.use_graph = use_cuda_graph
