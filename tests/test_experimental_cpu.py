@@ -167,3 +167,162 @@ def test_watchdog_names_the_silent_rank(tmp_path):
     out = str(tmp_path / "seen.pt")
     mp.spawn(_wd_rank, args=(2, 29749, out), nprocs=2, join=True)
     assert torch.load(out) == [1]
+
+
+def test_traffic_controller_gates_tasks_around_weight_sync():
+    import asyncio
+    from tunix_b200.experimental.common.datatypes import WorkerState
+    from tunix_b200.experimental.worker.traffic_controller import TrafficController
+
+    async def run():
+        tc = TrafficController()
+        gate = asyncio.Event()
+
+        async def work():
+            await gate.wait()
+            return 1
+        t1 = asyncio.ensure_future(work())
+        assert tc.try_admit(t1) and tc.active_tasks() == [t1]
+        tc.close_for_sync()
+        assert tc.state == WorkerState.SYNCING and not tc.is_admission_open()
+        t2 = asyncio.ensure_future(work())
+        assert not tc.try_admit(t2)                  # rejected and cancelled
+        waiter = asyncio.ensure_future(tc.wait_for_admission())
+        await asyncio.sleep(0)
+        assert t2.cancelled() or t2.cancelling() and not waiter.done()
+        assert not await tc.drain(timeout_s=0.01)    # t1 still runs
+        gate.set()
+        assert await tc.drain(timeout_s=1.0) and t1.result() == 1
+        assert tc.reopen()
+        await asyncio.wait_for(waiter, 1.0)
+        t3 = asyncio.ensure_future(asyncio.sleep(10))
+        assert tc.try_admit(t3)
+        assert tc.stop() == [t3]
+        await asyncio.sleep(0)
+        assert t3.cancelled() and tc.state == WorkerState.STOPPED and not tc.reopen()
+        import pytest
+        with pytest.raises(RuntimeError):
+            tc.close_for_sync()
+    asyncio.run(run())
+
+
+def test_worker_registry_lineage_and_dispatch_window():
+    import asyncio
+    import numpy as np
+    import pytest
+    from tunix_b200.experimental.common.dispatch_window import DispatchWindow
+    from tunix_b200.experimental.common.lineage import LineageContext, map_in_chunks
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerInfo, WorkerRegistry
+
+    class W:
+        def __init__(self, wid, roles):
+            self._i = WorkerInfo(wid, tuple(roles))
+
+        def info(self):
+            return self._i
+    reg = WorkerRegistry()
+    a, b, c = W("r1", ["rollout"]), W("r0", ["rollout", "inference"]), W("t0", ["trainer"])
+    for w in (a, b, c):
+        reg.register(w)
+    assert [w.info().worker_id for w in reg.group("rollout")] == ["r0", "r1"] and len(reg.group("critic")) == 0
+    assert reg.roles() == {"rollout", "inference", "trainer"} and "t0" in reg and len(reg) == 3
+    with pytest.raises(ValueError):
+        reg.register(W("r1", ["rollout"]))
+    with pytest.raises(ValueError):
+        reg.register(W("x", []))
+    reg.register(W("r1", ["inference"]), override=True)
+    assert [w.info().worker_id for w in reg.group("rollout")] == ["r0"]
+    reg.unregister("t0")
+    assert reg.worker_ids() == ["r0", "r1"]
+
+    t0, t1 = LineageContext(tracking_id="traj_0"), LineageContext(tracking_id="traj_1")
+    t0.add_event("worker.rollout", "generate", {"tokens": 5})
+    batch = LineageContext.merge("batch_0", [t0, None, t1, t0], "orchestrator.assembler", "pack", {"rows": 2})
+    assert batch.parent_tracking_ids == ["traj_0", "traj_1"] and batch.events[0].operation == "pack"
+    out = map_in_chunks(lambda x, y: x.sum(-1) + y, 2, np.arange(10).reshape(5, 2), np.ones(5))
+    assert out.tolist() == [2, 6, 10, 14, 18]
+
+    async def run():
+        consumed = [0]
+        win = DispatchWindow(1, lambda: consumed[0], full_batch_size=2, out_of_order_resume=True)
+        await asyncio.wait_for(win.wait_for(1), 0.1)             # within next_batch + staleness
+        parked = asyncio.ensure_future(win.wait_for(2))
+        await asyncio.sleep(0.01)
+        assert not parked.done()
+        consumed[0] = 1
+        win.release()
+        await asyncio.wait_for(parked, 0.5)
+        # two filtered groups (= one full batch) move the window by one
+        win.on_group_filtered([{"prompt_id": "p7"}])
+        assert win.next_batch == 2
+        win.on_group_filtered([{"prompt_id": "p9"}])
+        assert win.next_batch == 2 and win.skipped_prompt_ids == {"p7", "p9"}
+        win.record_committed_groups([[{"prompt_id": "p1"}], [{"prompt_id": "p2"}]])
+        meta = win.checkpoint_metadata(pending_groups=[[{"prompt_id": "p3"}]])
+        assert meta == {"committed_prompt_ids": ["p1", "p2", "p3"], "skipped_prompt_ids": ["p7", "p9"]}
+        fresh = DispatchWindow(1, lambda: 0, full_batch_size=2, out_of_order_resume=True)
+        assert fresh.dataset_skip_count == 0 and fresh.admit({"prompt_id": "p1"})
+        assert fresh.restore_checkpoint_metadata(meta) and fresh.uses_prompt_id_resume
+        assert not fresh.admit({"prompt_id": "p1"}) and not fresh.admit({"prompt_id": "p9"}) and fresh.admit({"prompt_id": "p4"})
+    asyncio.run(run())
+
+
+def test_workers_and_split_step_trainer():
+    import numpy as np
+    import torch
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import CacheConfig, TrainingConfig
+    from tunix_b200.experimental.common.datatypes import RolloutRequest, WorkerState
+    from tunix_b200.experimental.common.lineage import LineageContext
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.train.peft_trainer_v2 import TrainerV2
+    from tunix_b200.experimental.worker.rollout_worker import InferenceWorker, RolloutWorker, TrainerWorker
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+    sampler = Sampler(model, CharTok(), CacheConfig(64, 1, 1, 16))
+    synced = []
+    rw = RolloutWorker("rollout-0", sampler, apply_weights=lambda v, p: synced.append((v, p)), eos_tokens=[2])
+    trainer = PeftTrainer(model, optim.AdamW(1e-2), TrainingConfig(eval_every_n_steps=10 ** 9, pbar_description=None,
+                                                                   resume_from_checkpoint_on_init=False))
+    tw = TrainerWorker("trainer-0", TrainerV2(trainer))
+    iw = InferenceWorker("ref-0", {"sum": lambda x: np.asarray(x).sum(-1)})
+    reg = WorkerRegistry()
+    for w in (rw, tw, iw):
+        w.start()
+        reg.register(w)
+    assert [w.worker_id for w in reg.group("rollout")] == ["rollout-0"] and rw.state == WorkerState.READY
+    lin = LineageContext(tracking_id="traj_0")
+    resp = rw.submit(RolloutRequest("q0", [1, 5, 6, 7], group_id="g", max_tokens=6, temperature=0.0, metadata={"lineage": lin}))
+    assert resp.request_id == "q0" and 1 <= len(resp.tokens) <= 6 and len(resp.logprobs) == len(resp.tokens)
+    assert resp.finish_reason in ("stop", "length") and lin.events[0].component == "worker.rollout"
+    rw.sync_weights(3, {"w": 1})
+    assert synced == [(3, {"w": 1})] and rw.policy_version == 3 and rw.state == WorkerState.READY
+    assert iw.submit({"op": "sum", "x": [[1, 2], [3, 4]]}).tolist() == [3, 7]
+    # split-step training: three micro-batches of different sizes, one optimizer step
+    before = torch.cat([p.detach().reshape(-1).clone() for p in model.parameters()])
+    losses = []
+    for n in (2, 1, 3):
+        toks = torch.randint(3, 60, (n, 12))
+        r = tw.submit({"op": "fwd_bwd", "batch": {"input_tokens": toks, "input_mask": torch.ones(n, 12)}})
+        losses.append(r["loss"])
+    assert r["pending_microbatches"] == 3 and all(np.isfinite(losses))
+    up = tw.submit({"op": "update"})
+    assert up["step"] == 1 and up["microbatches"] == 3 and tw.policy_version == 1
+    after = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    assert not torch.equal(before, after)
+    ev = tw.submit({"op": "eval_step", "batch": {"input_tokens": toks, "input_mask": torch.ones(3, 12)}})
+    assert np.isfinite(ev["loss"])
+    logits = tw.submit({"op": "fwd_only", "batch": {"input_tokens": toks, "input_mask": torch.ones(3, 12)}})
+    assert logits.shape == (3, 12, 64)
+    import pytest
+    with pytest.raises(RuntimeError):
+        tw.trainer.update()
+    for w in (rw, tw, iw):
+        w.stop()
+        assert w.state == WorkerState.STOPPED
