@@ -326,3 +326,61 @@ def test_workers_and_split_step_trainer():
     for w in (rw, tw, iw):
         w.stop()
         assert w.state == WorkerState.STOPPED
+
+
+def test_rollout_manager_streams_episodes_and_syncs_between_them():
+    import asyncio
+    import time
+    from tunix_b200.experimental.rollout.manager import RolloutManager
+    from tunix_b200.experimental.worker.traffic_controller import AdmissionClosedError
+    weights = {"v": 0}
+
+    def generate(prompt, max_tokens):              # a blocking engine: echoes the weight version it ran with
+        time.sleep(0.01 * len(prompt))
+        return [weights["v"]] * (max_tokens or 1), [0.0] * (max_tokens or 1)
+
+    async def episode(model_call, item):
+        turns = []
+        for _ in range(item["turns"]):
+            out = await model_call(item["prompt"], 2)
+            turns.append((out["tokens"][0], out["policy_version"]))
+        if item.get("boom"):
+            raise ValueError("environment failed")
+        return turns
+
+    async def run():
+        mgr = RolloutManager(generate, episode, max_concurrency=2,
+                             apply_weights=lambda v, p: weights.__setitem__("v", v), partial_rollout=False)
+        items = [{"prompt": [1] * n, "turns": 1} for n in (5, 1, 3)] + [{"prompt": [1], "turns": 1, "boom": True}]
+        got = [o async for o in mgr.as_completed(items)]
+        assert len(got) == 4 and sum(o["error"] is not None for o in got) == 1
+        assert [len(o["item"]["prompt"]) for o in got if o["error"] is None][0] == 1        # shortest finishes first
+        # a sync round with an episode in flight: it drains first, new episodes are refused meanwhile
+        mgr.start_episode({"prompt": [1] * 4, "turns": 2})
+        await asyncio.sleep(0.005)
+        pre = asyncio.ensure_future(mgr.pre_weight_sync())
+        await asyncio.sleep(0.005)
+        import pytest
+        with pytest.raises(AdmissionClosedError):
+            mgr.start_episode({"prompt": [1], "turns": 1})
+        info = await pre
+        assert info["in_flight_before"] == 1 and info["in_flight_after"] == 0 and info["drained"]
+        assert (await mgr.pop_next_completed())["result"] == [(0, 0), (0, 0)]
+        await mgr.weight_sync(7, None)
+        assert await mgr.post_weight_sync() and mgr.policy_version == 7
+        out = [o async for o in mgr.as_completed([{"prompt": [1], "turns": 1}])]
+        assert out[0]["result"] == [(7, 7)]
+        assert mgr.stats["episodes"] == 5 and mgr.stats["failed"] == 1
+        # partial rollouts: the episode in flight is not drained; its next request waits for the new weights
+        part = RolloutManager(generate, episode, max_concurrency=2,
+                              apply_weights=lambda v, p: weights.__setitem__("v", v), partial_rollout=True)
+        part.policy_version = 7
+        part.start_episode({"prompt": [1] * 3, "turns": 2})
+        await asyncio.sleep(0.005)
+        info = await part.pre_weight_sync()
+        assert info["in_flight_after"] == 1
+        await asyncio.sleep(0.06)                    # first turn done, second one parked at the gate
+        await part.weight_sync(8, None)
+        await part.post_weight_sync()
+        assert (await part.pop_next_completed())["result"] == [(7, 7), (8, 8)]
+    asyncio.run(run())
