@@ -1,5 +1,6 @@
 """Vanilla sampler behaviour on CPU with a tiny model and a character tokenizer."""
 import numpy as np
+import pytest
 import torch
 
 from tunix_b200.common.configs import CacheConfig
@@ -97,3 +98,79 @@ def test_update_params_copies_lora_only():
     name, p = next(iter(model.named_parameters()))
     s.update_params({name: torch.zeros_like(p)})
     assert float(dict(model.named_parameters())[name].abs().sum()) == 0.0
+
+
+class _FakeEngine:
+    """Stands in for PagedEngine under EngineServer: `_loop` serves the request source with a scripted model
+    (token = last prompt token + step), one request per slot and step, so the server's queueing, token limits,
+    pause / resume and failure hand-off run on the CPU."""
+
+    def __init__(self, slots=2, fail_on=None):
+        import torch
+        self.cache_size, self.max_running, self.pack_weights, self._packed_on = 64, slots, False, False
+        self.tokenizer, self.device = CharTok(), torch.device("cpu")
+        self.refreshed, self.fail_on = 0, fail_on
+
+    def _fuse_all(self):
+        self.refreshed += 1
+
+    def _pack_all(self):
+        pass
+
+    def _new_state(self, *a):
+        return {}
+
+    def _loop(self, st, B, max_steps, pad_id, source):
+        import time
+        running = {}
+        while True:
+            for rid, row, ln, lim in source.take(B - len(running)):
+                if self.fail_on is not None and int(row[-1]) == self.fail_on:
+                    raise RuntimeError("device fault")
+                running[rid] = (int(row[-1]), lim, [])
+            if not running:
+                if source.idle():
+                    continue
+                return
+            time.sleep(0.002)
+            for rid in list(running):
+                last, lim, out = running[rid]
+                out.append(last + len(out) + 1)
+                if len(out) >= lim:
+                    source.deliver(rid, out, [0.0] * len(out))
+                    del running[rid]
+
+
+def test_engine_server_protocol_on_cpu():
+    from concurrent.futures import ThreadPoolExecutor
+    from tunix_b200.generate.engine import EngineServer
+    eng = _FakeEngine(slots=2)
+    with EngineServer(eng, max_new_tokens=5, max_prompt_length=8, eos_tokens=[2]) as srv:
+        with ThreadPoolExecutor(6) as ex:
+            outs = list(ex.map(lambda i: srv.generate([1, 10 * i], max_tokens=1 + i % 5, timeout=10), range(1, 9)))
+        for i, (toks, lps) in zip(range(1, 9), outs):
+            assert toks.tolist() == [10 * i + k + 1 for k in range(1 + i % 5)] and len(lps) == len(toks)
+        assert srv.generate(list(range(100, 120)), 2, timeout=10)[0].tolist() == [120, 121]   # prompt cut to its tail
+        assert srv.generate([1, 7], max_tokens=99, timeout=10)[0].shape == (5,)               # capped at the server's limit
+        before = eng.refreshed
+        assert srv.pause(timeout=5)
+        fut = srv.submit([1, 3], 2)
+        import time
+        time.sleep(0.05)
+        assert not fut.done()                       # queued, not admitted while paused
+        srv.resume()
+        assert fut.result(10)[0].tolist() == [4, 5] and eng.refreshed == before + 1          # weights re-read once
+    with pytest.raises(RuntimeError):
+        srv.submit([1])
+    # a failure of the engine loop reaches every waiting client and closes the server
+    bad = EngineServer(_FakeEngine(slots=1, fail_on=13), max_new_tokens=4, max_prompt_length=8, eos_tokens=[2])
+    ok = bad.submit([1, 5], 2)
+    assert ok.result(10)[0].tolist() == [6, 7]
+    f1, f2 = bad.submit([1, 13], 2), bad.submit([1, 6], 2)
+    with pytest.raises(RuntimeError, match="device fault"):
+        f1.result(10)
+    with pytest.raises(RuntimeError):
+        f2.result(10)
+    with pytest.raises(RuntimeError):
+        bad.submit([1, 2])
+    bad.close()

@@ -718,7 +718,8 @@ class EngineServer:
     def _serve(self):
         eng = self.engine
         try:
-            torch.cuda.set_device(eng.device)
+            if eng.device.type == "cuda":
+                torch.cuda.set_device(eng.device)
             with torch.no_grad():
                 eng._fuse_all()
                 eng._packed_on = eng.pack_weights and eng.max_running <= 128
