@@ -384,3 +384,44 @@ def test_rollout_manager_streams_episodes_and_syncs_between_them():
         await part.post_weight_sync()
         assert (await part.pop_next_completed())["result"] == [(7, 7), (8, 8)]
     asyncio.run(run())
+
+
+def test_batch_assemblers_pad_and_pack():
+    import numpy as np
+    from tunix_b200.experimental.common.datatypes import RLTrainerPayload
+    from tunix_b200.experimental.common.lineage import LineageContext
+    from tunix_b200.experimental.orchestrator.batch_assembly import (BatchConfig, PaddingStats, create_batch_assembler,
+                                                                    summarize_padding_stats)
+    rng = np.random.default_rng(0)
+
+    def traj(i, p, c):
+        return RLTrainerPayload({"prompt_ids": rng.integers(3, 50, p), "completion_ids": rng.integers(3, 50, c),
+                                 "old_per_token_logps": -np.ones(c, np.float32), "lineage": LineageContext(tracking_id=f"traj_{i}")},
+                                policy_version=2, group_id=f"g{i // 2}", reward=float(i))
+    items = [traj(i, p, c) for i, (p, c) in enumerate([(4, 6), (8, 3), (2, 9), (5, 5), (3, 2)])]
+    pad = create_batch_assembler(BatchConfig(rows_per_microbatch=2, max_prompt_length=8, max_response_length=8), packed=False)
+    out = list(pad.feed(items))
+    assert [b.batch_id for b in out] == ["batch_0", "batch_1"] and out[0].arrays["input_tokens"].shape == (2, 16)
+    b0 = out[0]
+    assert b0.arrays["prompt_mask"][0].tolist() == [0] * 4 + [1] * 4 + [0] * 8          # left-padded prompt
+    assert b0.arrays["completion_mask"][0].tolist() == [0] * 8 + [1] * 6 + [0] * 2      # right-padded completion
+    assert b0.arrays["advantages"][1, 8:11].tolist() == [1.0] * 3 and b0.arrays["old_per_token_logps"][0, 8] == -1
+    assert b0.stats.row_valid_tokens.tolist() == [10, 11] and b0.lineage.parent_tracking_ids == ["traj_0", "traj_1"]
+    tail = list(pad.flush())
+    assert len(tail) == 1 and tail[0].num_trajectories == 1 and tail[0].stats.row_num_sequences.tolist() == [1, 0]
+    # packing: all five fit two rows of 24 tokens
+    pk = create_batch_assembler(BatchConfig(rows_per_microbatch=2, max_packed_len=24), packed=True)
+    assert list(pk.feed(items[:2])) == []                       # 21 tokens: below a full micro-batch, keeps buffering
+    got = list(pk.feed(items[2:])) + list(pk.flush())
+    assert sum(b.num_trajectories for b in got) == 5
+    b = got[0]
+    seg = b.arrays["segment_ids"]
+    assert seg.shape == (2, 24) and b.stats.valid_tokens == int((seg > 0).sum()) and b.stats.row_capacity == 24
+    row0 = b.arrays["positions"][0][seg[0] == 1]
+    assert row0.tolist() == list(range(len(row0)))              # positions restart per segment
+    assert set(b.lineage.parent_tracking_ids) <= {f"traj_{i}" for i in range(5)}
+    summary = summarize_padding_stats([x.stats for x in got])
+    assert summary["valid_tokens"] == 47 and summary["sequences"] == 5 and 0 <= summary["padding_ratio"] < 1
+    import pytest
+    with pytest.raises(ValueError):
+        PaddingStats(row_valid_tokens=np.asarray([30]), row_num_sequences=np.asarray([1]), row_capacity=24)
