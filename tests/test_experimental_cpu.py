@@ -425,3 +425,91 @@ def test_batch_assemblers_pad_and_pack():
     import pytest
     with pytest.raises(ValueError):
         PaddingStats(row_valid_tokens=np.asarray([30]), row_num_sequences=np.asarray([1]), row_capacity=24)
+
+
+def test_orchestrator_end_to_end_with_worker_failover():
+    """Prompts -> rollout workers -> group advantages -> packed micro-batches -> split-step trainer -> weight sync, on
+    a tiny CPU model; one of two rollout workers dies mid-run and the other takes over."""
+    import numpy as np
+    import torch
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import CacheConfig, TrainingConfig
+    from tunix_b200.experimental.common.datatypes import WorkerState
+    from tunix_b200.experimental.common.dispatch_window import DispatchWindow
+    from tunix_b200.experimental.orchestrator.batch_assembly import BatchConfig, create_batch_assembler
+    from tunix_b200.experimental.orchestrator.orchestrator import AlgorithmAdapter, Orchestrator
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.train.peft_trainer_v2 import TrainerV2
+    from tunix_b200.experimental.worker.rollout_worker import RolloutWorker, TrainerWorker
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer
+    from tunix_b200.sft.utils import LossOutput, WeightedMetric
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+    cc = CacheConfig(64, 1, 1, 16)
+
+    def pg_loss(model, input_tokens, completion_mask, advantages, segment_ids=None, positions=None, **_):
+        hidden, _ = model(input_tokens[:, :-1], positions=None if positions is None else positions[:, :-1],
+                          segment_ids=None if segment_ids is None else segment_ids[:, :-1], skip_lm_head=True)
+        lp = model.token_logprobs(hidden.reshape(-1, hidden.shape[-1]), input_tokens[:, 1:].reshape(-1).long())[0]
+        lp = lp.view(input_tokens.shape[0], -1)
+        m = completion_mask[:, 1:]
+        loss_sum = -(lp * advantages[:, 1:] * m).sum()
+        return LossOutput(loss=WeightedMetric(loss_sum, m.sum()))
+
+    def to_inputs(batch):
+        out = {k: torch.as_tensor(v) for k, v in batch.items()}
+        out["input_tokens"] = out["input_tokens"].long()
+        return out
+    trainer = PeftTrainer(model, optim.AdamW(5e-3), TrainingConfig(eval_every_n_steps=10 ** 9, pbar_description=None,
+                                                                   resume_from_checkpoint_on_init=False))
+    trainer.with_loss_fn(pg_loss).with_gen_model_input_fn(to_inputs)
+
+    class Flaky:
+        """A sampler that breaks after a number of calls (a host-side stand-in for a lost rollout worker)."""
+        def __init__(self, inner, die_after):
+            self.inner, self.left = inner, die_after
+
+        def __call__(self, **kw):
+            self.left -= 1
+            if self.left < 0:
+                raise ConnectionError("rollout worker lost")
+            return self.inner(**kw)
+    synced = []
+    reg = WorkerRegistry()
+    workers = [RolloutWorker("rollout-0", Flaky(Sampler(model, CharTok(), cc), die_after=5), eos_tokens=[2],
+                             apply_weights=lambda v, p: synced.append(("rollout-0", v))),
+               RolloutWorker("rollout-1", Sampler(model, CharTok(), cc), eos_tokens=[2],
+                             apply_weights=lambda v, p: synced.append(("rollout-1", v))),
+               TrainerWorker("trainer-0", TrainerV2(trainer))]
+    for w in workers:
+        w.start()
+        reg.register(w)
+    consumed = [0]
+    window = DispatchWindow(0, lambda: consumed[0], full_batch_size=2, out_of_order_resume=True)
+    orch = Orchestrator(reg, create_batch_assembler(BatchConfig(rows_per_microbatch=2, max_packed_len=48), packed=True),
+                        AlgorithmAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens)), drop_uniform_groups=True),
+                        group_size=4, window=window, rollout_params={"max_tokens": 6, "temperature": 1.0, "seed": None},
+                        export_weights=lambda: {"version_of": "actor"})
+    before = torch.cat([p.detach().reshape(-1).clone() for p in model.parameters()])
+    rng = np.random.default_rng(0)
+    batches = [[{"prompt_id": f"p{s}_{i}", "prompt_ids": [1] + rng.integers(3, 60, 4).tolist()} for i in range(2)] for s in range(3)]
+    for s, b in enumerate(batches):
+        rec = orch.step(s, b)
+        consumed[0] += 1
+        assert rec["trajectories"] + 4 * rec["filtered_groups"] == 8
+    hist = orch.history
+    assert [h["policy_version"] for h in hist] == [1, 2, 3] and hist[-1]["train_step"] == 3
+    assert all(np.isfinite(h["loss"]) and 0 <= h["padding_ratio"] < 1 for h in hist)
+    after = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    assert not torch.equal(before, after)
+    # rollout-0 died during the first step: marked FAILED, excluded, and only rollout-1 keeps receiving weights
+    assert workers[0].state == WorkerState.FAILED and orch.excluded == {"rollout-0"}
+    assert [s for s in synced if s[0] == "rollout-1"] == [("rollout-1", 1), ("rollout-1", 2), ("rollout-1", 3)]
+    assert window.committed_prompt_ids | window.skipped_prompt_ids == {f"p{s}_{i}" for s in range(3) for i in range(2)}
+    assert workers[1].served >= 19
+    orch.close()
