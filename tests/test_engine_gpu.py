@@ -50,6 +50,10 @@ def test_paged_decode_kernel_matches_reference(N, KH, H, window, softcap):
     slots = torch.arange(B, device="cuda", dtype=torch.int32)
     out = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640, scale=1 / math.sqrt(H),
                          window=window, softcap=softcap)
+    for split in (64, 128, 256):        # the context split per CTA only changes the schedule
+        again = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640,
+                               scale=1 / math.sqrt(H), window=window, softcap=softcap, split_tokens=split)
+        assert torch.allclose(again.float(), out.float(), atol=2e-2, rtol=2e-2), split
     for b in range(B):
         L = int(lens[b])
         idx = torch.arange(L, device="cuda")

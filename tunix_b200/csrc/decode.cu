@@ -23,7 +23,7 @@ using namespace tb;
 namespace {
 
 constexpr int MAX_G = 16;       // query heads per kv head handled by one CTA (rows of one mma tile)
-constexpr int SPLIT_TOKENS = 256;
+constexpr int MAX_SPLIT_TOKENS = 2048;  // context tokens per CTA: a multiple of 64 up to this, chosen by the caller
 
 // k_new/v_new: [n_tok, KH*H] rows. seq_ids[n_tok] = row of page_table, pos[n_tok] = position in the sequence
 // (negative = padding, skipped). Pools: [num_pages, page_size, KH*H].
@@ -146,7 +146,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ page_table, int max_pages, int page_size,
                     const int* __restrict__ seq_ids, const int* __restrict__ seq_lens, int KH, int G, float scale,
-                    float softcap, int window, int num_splits, float* __restrict__ part_acc,  // [B, N, splits, H]
+                    float softcap, int window, int num_splits, int split_tokens,
+                    float* __restrict__ part_acc,                                               // [B, N, splits, H]
                     float* __restrict__ part_ml) {                                              // [B, N, splits, 2]
   constexpr int CPR = H / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = TILE_KEYS * H * 2;
@@ -158,8 +159,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int N = KH * G;
   const int len = seq_lens[b];
-  int lo = split * SPLIT_TOKENS;
-  const int hi = min(len, lo + SPLIT_TOKENS);
+  int lo = split * split_tokens;
+  if (lo >= len) return;          // past the end of this sequence: the combine kernel never reads this split
+  const int hi = min(len, lo + split_tokens);
   if (window > 0) lo = max(lo, len - window);
   const int* pt = page_table + (long long)seq_ids[b] * max_pages;
   const long long row_elems = (long long)KH * H;
@@ -174,7 +176,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
     *reinterpret_cast<uint4*>(q_s + swz<H>(r, c)) = u;
   }
 
-  const int t_first = split * SPLIT_TOKENS + ((max(lo - split * SPLIT_TOKENS, 0)) / TILE_KEYS) * TILE_KEYS;
+  const int t_first = split * split_tokens + ((max(lo - split * split_tokens, 0)) / TILE_KEYS) * TILE_KEYS;
   const int n_tiles = hi > t_first ? (hi - t_first + TILE_KEYS - 1) / TILE_KEYS : 0;
 
   auto issue = [&](int tile, int buf) {
@@ -321,13 +323,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
 
 // out[b, n, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
 __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                            const int* __restrict__ seq_lens, int N, int H, int num_splits, int window,
-                                            __nv_bfloat16* __restrict__ out, long long ldo) {
+                                            const int* __restrict__ seq_lens, int N, int H, int num_splits, int split_tokens,
+                                            int window, __nv_bfloat16* __restrict__ out, long long ldo) {
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x, n = blockIdx.y;
   const int len = seq_lens[b];
-  const int used = min(num_splits, (len + SPLIT_TOKENS - 1) / SPLIT_TOKENS);
+  const int used = min(num_splits, (len + split_tokens - 1) / split_tokens);
   const long long base = ((long long)b * N + n) * num_splits;
   float M = -INFINITY;
   for (int s = 0; s < used; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
@@ -351,7 +353,7 @@ template <int H>
 int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, long long ldq,
                   const __nv_bfloat16* kp, const __nv_bfloat16* vp, const int* pt, int max_pages, int page_size,
                   const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap, int window, int splits,
-                  float* pa, float* pml) {
+                  int split_tokens, float* pa, float* pml) {
   constexpr int SMEM = 2 * 2 * TILE_KEYS * H * 2;     // two stages of K and V
   static bool attr_set = false;
   if (!attr_set) {
@@ -359,8 +361,10 @@ int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q,
       return -5;
     attr_set = true;
   }
-  return launch_pdl(paged_decode_kernel<H>, grid, dim3(128), SMEM, stream, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids,
-                    seq_lens, KH, G, scale, softcap, window, splits, pa, pml) == cudaSuccess ? 0 : -5;
+  // a split of one 64-key tile needs one stage only: more CTAs fit on an SM
+  const int smem = split_tokens > TILE_KEYS ? SMEM : SMEM / 2;
+  return launch_pdl(paged_decode_kernel<H>, grid, dim3(128), smem, stream, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids,
+                    seq_lens, KH, G, scale, softcap, window, splits, split_tokens, pa, pml) == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace
@@ -404,29 +408,33 @@ TB_API int tb_qkv_post(void* qkv, long long ld, const int* seq_ids, const int* p
 }
 
 // q [B, N*H]; pools [num_pages, page_size, KH*H]; page_table [*, max_pages]; seq_ids [B]; seq_lens [B];
-// workspace: part_acc fp32 [B*N*splits*H], part_ml fp32 [B*N*splits*2] with splits = ceil(max_ctx / 256).
+// workspace: part_acc fp32 [B*N*splits*H], part_ml fp32 [B*N*splits*2] with splits = ceil(max_ctx / split_tokens);
+// split_tokens = context tokens per CTA, a multiple of 64 in [64, 2048] (0 = 256). CTAs of splits that lie past the
+// end of their sequence return at once.
 TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, const void* v_pool,
                            const int* page_table, int max_pages, int page_size, const int* seq_ids,
                            const int* seq_lens, int B, int N, int KH, int H, int max_ctx, float scale, float softcap,
-                           int window, float* part_acc, float* part_ml, void* out, long long ldo,
+                           int window, int split_tokens, float* part_acc, float* part_ml, void* out, long long ldo,
                            cudaStream_t stream) {
   if (B <= 0) return 0;
   if (KH <= 0 || N % KH || (ldq % 8)) return -2;
   const int G = N / KH;
   if (G > MAX_G) return -2;
-  const int splits = (max_ctx + SPLIT_TOKENS - 1) / SPLIT_TOKENS;
+  if (split_tokens <= 0) split_tokens = 256;
+  if (split_tokens % TILE_KEYS || split_tokens > MAX_SPLIT_TOKENS) return -2;
+  const int splits = (max_ctx + split_tokens - 1) / split_tokens;
   dim3 grid(B, KH, splits);
   int rc;
   auto qq = (const __nv_bfloat16*)q;
   auto kp = (const __nv_bfloat16*)k_pool;
   auto vp = (const __nv_bfloat16*)v_pool;
   switch (H) {
-    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, part_acc, part_ml); break;
-    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, part_acc, part_ml); break;
-    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, part_acc, part_ml); break;
+    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
+    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
+    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
     default: return -2;
   }
   if (rc) return rc;
   return launch_pdl(paged_decode_combine_kernel, dim3(B, N), dim3(128), 0, stream, (const float*)part_acc,
-                    (const float*)part_ml, seq_lens, N, H, splits, window, (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : -5;
+                    (const float*)part_ml, seq_lens, N, H, splits, split_tokens, window, (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : -5;
 }

@@ -324,7 +324,7 @@ class PagedEngine(BaseSampler):
                 K.kv_write(k.view(B, -1), v, st["slots"], pos, pool.table, pool.page_size, pool.k[i], pool.v[i])
             o = K.paged_decode(q, pool.k[i], pool.v[i], pool.table, st["slots"], lens, num_kv_heads=KH,
                                page_size=pool.page_size, max_ctx=self.cache_size, scale=at.scale,
-                               softcap=cfg.attn_logit_softcap, window=at.window, workspace=st["ws"])
+                               softcap=cfg.attn_logit_softcap, window=at.window, workspace=st["ws"], split_tokens=st["split"])
             po = self._pk(i, "o")
             if po is not None:
                 a = K.gemm_packed(o.view(B, N * H), po, residual=None if cfg.post_norms else x)
@@ -423,7 +423,8 @@ class PagedEngine(BaseSampler):
 
     def _new_state(self, B, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
         dev = self.device
-        splits = (self.cache_size + K.DECODE_SPLIT_TOKENS - 1) // K.DECODE_SPLIT_TOKENS
+        split = K.decode_split_tokens(B, self.cfg.num_kv_heads)
+        splits = (self.cache_size + split - 1) // split
         N, H, V = self.cfg.num_heads, self.cfg.head_dim, self.cfg.vocab_size
         i64 = dict(dtype=torch.int64, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -446,6 +447,7 @@ class PagedEngine(BaseSampler):
             "ws": (torch.empty(B * N * splits * H, dtype=torch.float32, device=dev),
                    torch.empty(B * N * splits * 2, dtype=torch.float32, device=dev)),
             "params": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed},
+            "split": split,
         }
 
     def _run(self, toks_np, lens_np, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):

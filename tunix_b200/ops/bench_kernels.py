@@ -53,6 +53,8 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--split", type=int, default=0, help="paged_decode: context tokens per CTA (0 = chosen from the batch)")
+    ap.add_argument("--max-ctx", type=int, default=0, help="paged_decode: size the grid for this context (0 = --seq)")
     ap.add_argument("--packed", action="store_true", help="gemm: B as a pre-tiled PackedWeight (decode-size M)")
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=2048)
@@ -159,10 +161,12 @@ def main(argv=None) -> int:
         lens = torch.full((Bn,), ctx, device=dev, dtype=torch.int32)
         slots = torch.arange(Bn, device=dev, dtype=torch.int32)
         q = torch.randn(Bn, N, H, device=dev, dtype=bf)
-        ms = _time(lambda: K.paged_decode(q, kp, vp, table, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=ctx,
-                                          scale=1.0 / math.sqrt(H)), args.iters, args.warmup)
+        ms = _time(lambda: K.paged_decode(q, kp, vp, table, slots, lens, num_kv_heads=KH, page_size=page,
+                                          max_ctx=args.max_ctx or ctx, scale=1.0 / math.sqrt(H), split_tokens=args.split),
+                   args.iters, args.warmup)
         gb = 2.0 * Bn * ctx * KH * H * 2 / ms / 1e6
-        out.update(shape=[Bn, ctx, N, KH, H], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb)
+        out.update(shape=[Bn, ctx, N, KH, H], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb,
+                   split_tokens=args.split or K.decode_split_tokens(Bn, KH))
     elif args.kernel == "moe":
         from tunix_b200.ops import moe
         T, E, k, D, Fd = args.rows, args.experts, args.topk, args.dim, args.ffn
