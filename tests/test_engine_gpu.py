@@ -34,12 +34,14 @@ def _model(**kw):
     return create_model(ModelConfig(**base), device=torch.device("cuda"), seed=0)
 
 
+@pytest.mark.parametrize("page", [16, 64])          # 64-token pages are staged by TMA, smaller ones gathered by cp.async
 @pytest.mark.parametrize("N,KH,H,window,softcap", [(8, 2, 128, 0, 0.0), (4, 4, 64, 0, 0.0), (16, 2, 256, 0, 30.0),
                                                    (8, 1, 128, 100, 0.0), (32, 2, 128, 0, 0.0)])
-def test_paged_decode_kernel_matches_reference(N, KH, H, window, softcap):
+def test_paged_decode_kernel_matches_reference(N, KH, H, window, softcap, page):
+    from tunix_b200 import _lib
     from tunix_b200.ops import kernels as K
     torch.manual_seed(0)
-    B, page, max_pages = 5, 16, 40
+    B, max_pages = 5, 640 // page
     lens = torch.tensor([1, 17, 300, 600, 255], device="cuda", dtype=torch.int32)
     num_pages = B * max_pages
     kp = torch.randn(num_pages, page, KH * H, device="cuda", dtype=torch.bfloat16)
@@ -50,10 +52,11 @@ def test_paged_decode_kernel_matches_reference(N, KH, H, window, softcap):
     slots = torch.arange(B, device="cuda", dtype=torch.int32)
     out = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640, scale=1 / math.sqrt(H),
                          window=window, softcap=softcap)
-    for split in (64, 128, 256):        # the context split per CTA only changes the schedule
+    for split in (64, 128, 256, 512):        # the context split per CTA only changes the schedule
         again = K.paged_decode(q, kp, vp, perm, slots, lens, num_kv_heads=KH, page_size=page, max_ctx=640,
                                scale=1 / math.sqrt(H), window=window, softcap=softcap, split_tokens=split)
         assert torch.allclose(again.float(), out.float(), atol=2e-2, rtol=2e-2), split
+    _lib.raise_if_kernel_error()
     for b in range(B):
         L = int(lens[b])
         idx = torch.arange(L, device="cuda")

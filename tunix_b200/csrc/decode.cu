@@ -137,22 +137,38 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * (H * 2) + (((c & ~7) | ((c ^ r) & 7)) << 4));
 }
 
+// byte offset of chunk c of key row r inside a staged K or V tile. TMA stages a tile as H/64 slabs of [64 rows x
+// 128 bytes] with the hardware's 128-byte swizzle; the cp.async path keeps whole rows together.
+template <int H, bool TMA>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  if (TMA) return (uint32_t)((c >> 3) * (TILE_KEYS * 128) + r * 128 + (((c ^ r) & 7) << 4));
+  return swz<H>(r, c);
+}
+
 // One CTA per (sequence, kv head, context split): the G (<= 16) query heads of the kv head are the 16 rows of the
-// A operand, a warp owns 16 keys of each 64-key stage, S = Q K^T and O += P V run on mma.sync with K / V staged by
-// cp.async (double buffered) and read with ldmatrix; every K / V byte is read once.
-template <int H>
+// A operand, a warp owns 16 keys of each 64-key stage, S = Q K^T and O += P V run on mma.sync and read K / V with
+// ldmatrix; every K / V byte is read once. Staging: with pages of a multiple of 64 tokens a tile lies in one page
+// and one thread fetches it with TMA (two tensor-map boxes per 64 head dims, STAGES deep, mbarrier completion);
+// otherwise all threads gather rows with cp.async (double buffered). The TMA path reads whole 64-token tiles, so
+// the unused tail of a page must hold finite values (pages start zeroed and only ever receive K / V rows).
+template <int H, bool TMA, int STAGES>
 __global__ void __launch_bounds__(128)
-paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        // [B, N*H]
+paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const __nv_bfloat16* __restrict__ q, long long ldq,        // [B, N*H]
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ page_table, int max_pages, int page_size,
                     const int* __restrict__ seq_ids, const int* __restrict__ seq_lens, int KH, int G, float scale,
                     float softcap, int window, int num_splits, int split_tokens,
                     float* __restrict__ part_acc,                                               // [B, N, splits, H]
-                    float* __restrict__ part_ml) {                                              // [B, N, splits, 2]
+                    float* __restrict__ part_ml, int* __restrict__ status) {                    // [B, N, splits, 2]
   constexpr int CPR = H / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = TILE_KEYS * H * 2;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(128) uint8_t q_s[16 * H * 2];
+  __shared__ __align__(8) unsigned long long full_bars[STAGES];
+  __shared__ int abort_flag;
+  // TMA tiles are 1024-byte aligned (the launch adds the slack for it)
+  uint8_t* smem = smem_raw + (TMA ? ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u) : 0u);
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
@@ -179,6 +195,27 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
   const int t_first = split * split_tokens + ((max(lo - split * split_tokens, 0)) / TILE_KEYS) * TILE_KEYS;
   const int n_tiles = hi > t_first ? (hi - t_first + TILE_KEYS - 1) / TILE_KEYS : 0;
 
+  if (TMA) {
+    if (tid == 0) {
+      for (int i = 0; i < STAGES; ++i) mbar_init(smem_u32(&full_bars[i]), 1);
+      abort_flag = 0;
+      mbar_fence_init();
+    }
+    __syncthreads();
+  }
+  // one thread, one tile: the tile's 64 tokens lie in one page
+  auto issue_tma = [&](int tile, int buf) {
+    const int t0 = t_first + tile * TILE_KEYS;
+    const int row = pt[t0 / page_size] * page_size + t0 % page_size;
+    const uint32_t kb = smem_base + buf * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
+    const uint32_t bar = smem_u32(&full_bars[buf]);
+    mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+    for (int j = 0; j < H / 64; ++j) {
+      tma_load_2d(kb + j * (TILE_KEYS * 128), &tmK, bar, kh * H + j * 64, row);
+      tma_load_2d(vb + j * (TILE_KEYS * 128), &tmV, bar, kh * H + j * 64, row);
+    }
+  };
   auto issue = [&](int tile, int buf) {
     const int t0 = t_first + tile * TILE_KEYS;
     const uint32_t kb = smem_base + buf * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
@@ -203,17 +240,28 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
 #pragma unroll
   for (int i = 0; i < H / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-  if (n_tiles > 0) issue(0, 0);
+  if (TMA) {
+    if (tid == 0)
+      for (int i = 0; i < STAGES - 1 && i < n_tiles; ++i) issue_tma(i, i);
+  } else if (n_tiles > 0) {
+    issue(0, 0);
+  }
   const int li = lane >> 3, lr = lane & 7;
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int buf = tile & 1;
-    if (tile + 1 < n_tiles) {
-      issue(tile + 1, buf ^ 1);
-      cp_async_wait<1>();
+    const int buf = TMA ? tile % STAGES : (tile & 1);
+    if (TMA) {
+      // the buffer of tile + STAGES - 1 was read in the previous iteration, which ended with a barrier
+      if (tid == 0 && tile + STAGES - 1 < n_tiles) issue_tma(tile + STAGES - 1, (tile + STAGES - 1) % STAGES);
+      if (!mbar_wait_bounded(smem_u32(&full_bars[buf]), (tile / STAGES) & 1, &abort_flag, status, ST_TIMEOUT_PRODUCER)) break;
     } else {
-      cp_async_wait<0>();
+      if (tile + 1 < n_tiles) {
+        issue(tile + 1, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
     }
-    __syncthreads();
     const uint32_t kb = smem_base + buf * 2 * TILE_BYTES, vb = kb + TILE_BYTES;
     const int kr0 = warp * 16;
     const int tw = t_first + tile * TILE_KEYS + kr0;      // first key of this warp's slice
@@ -223,7 +271,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
       for (int ks = 0; ks < H / 16; ++ks) {
         uint32_t a[4], kf[4];
         ldsm_x4(a, q_base + swz<H>((li & 1) * 8 + lr, ks * 2 + (li >> 1)));
-        ldsm_x4(kf, kb + swz<H>(kr0 + (li >> 1) * 8 + lr, ks * 2 + (li & 1)));
+        ldsm_x4(kf, kb + tile_off<H, TMA>(kr0 + (li >> 1) * 8 + lr, ks * 2 + (li & 1)));
         mma_16816(s[0], a, kf[0], kf[1]);
         mma_16816(s[1], a, kf[2], kf[3]);
       }
@@ -268,7 +316,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq,        /
 #pragma unroll
       for (int d2 = 0; d2 < H / 16; ++d2) {
         uint32_t vf[4];
-        ldsm_x4_t(vf, vb + swz<H>(kr0 + (li & 1) * 8 + lr, d2 * 2 + (li >> 1)));
+        ldsm_x4_t(vf, vb + tile_off<H, TMA>(kr0 + (li & 1) * 8 + lr, d2 * 2 + (li >> 1)));
         float* oa = o[2 * d2];
         float* ob = o[2 * d2 + 1];
         oa[0] *= c0; oa[1] *= c0; oa[2] *= c1; oa[3] *= c1;
@@ -349,22 +397,49 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_acc, 
   }
 }
 
-template <int H>
-int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, long long ldq,
-                  const __nv_bfloat16* kp, const __nv_bfloat16* vp, const int* pt, int max_pages, int page_size,
-                  const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap, int window, int splits,
-                  int split_tokens, float* pa, float* pml) {
-  constexpr int SMEM = 2 * 2 * TILE_KEYS * H * 2;     // two stages of K and V
+template <int H, bool TMA, int STAGES>
+int launch_decode_v(int G, dim3 grid, cudaStream_t stream, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                    const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* kp, const __nv_bfloat16* vp, const int* pt,
+                    int max_pages, int page_size, const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap,
+                    int window, int splits, int split_tokens, float* pa, float* pml, int* status) {
+  constexpr int TILE2 = 2 * TILE_KEYS * H * 2;                       // one stage: a K tile and a V tile
+  constexpr int SMEM = STAGES * TILE2 + (TMA ? 1024 : 0);
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_decode_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(paged_decode_kernel<H, TMA, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return -5;
     attr_set = true;
   }
   // a split of one 64-key tile needs one stage only: more CTAs fit on an SM
-  const int smem = split_tokens > TILE_KEYS ? SMEM : SMEM / 2;
-  return launch_pdl(paged_decode_kernel<H>, grid, dim3(128), smem, stream, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids,
-                    seq_lens, KH, G, scale, softcap, window, splits, split_tokens, pa, pml) == cudaSuccess ? 0 : -5;
+  const int smem = split_tokens > TILE_KEYS ? SMEM : TILE2 + (TMA ? 1024 : 0);
+  return launch_pdl(paged_decode_kernel<H, TMA, STAGES>, grid, dim3(128), smem, stream, tmK, tmV, q, ldq, kp, vp, pt, max_pages,
+                    page_size, seq_ids, seq_lens, KH, G, scale, softcap, window, splits, split_tokens, pa, pml, status) == cudaSuccess ? 0 : -5;
+}
+
+// TMA staging needs tiles that lie inside one page.
+template <int H>
+int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, long long ldq,
+                  const __nv_bfloat16* kp, const __nv_bfloat16* vp, long long pool_rows, const int* pt, int max_pages,
+                  int page_size, const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap, int window,
+                  int splits, int split_tokens, float* pa, float* pml, int* status) {
+  static const bool no_tma = getenv("TUNIX_B200_DECODE_NO_TMA") != nullptr;
+  static const char* stages_env = getenv("TUNIX_B200_DECODE_STAGES");
+  CUtensorMap tmK, tmV;
+  memset(&tmK, 0, sizeof(tmK));
+  memset(&tmV, 0, sizeof(tmV));
+  const bool tma = !no_tma && page_size % TILE_KEYS == 0 && pool_rows > 0 &&
+                   tb_make_tmap_2d_bf16(&tmK, kp, (uint64_t)pool_rows, (uint64_t)KH * H, (uint64_t)KH * H, TILE_KEYS, 64, 1) == 0 &&
+                   tb_make_tmap_2d_bf16(&tmV, vp, (uint64_t)pool_rows, (uint64_t)KH * H, (uint64_t)KH * H, TILE_KEYS, 64, 1) == 0;
+#define LD(T, S) launch_decode_v<H, T, S>(G, grid, stream, tmK, tmV, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids, seq_lens, \
+                                         KH, scale, softcap, window, splits, split_tokens, pa, pml, status)
+  if (!tma) return LD(false, 2);
+  // measured at head dim 128 (8 kv heads, 256 sequences x 768 tokens): 2 / 3 / 4 stages take 157 / 161 / 194 us,
+  // cp.async staging 190 us: three CTAs per SM with two stages each beat deeper rings on fewer CTAs
+  const int want = stages_env ? atoi(stages_env) : 2;
+  if (want <= 2) return LD(true, 2);
+  if (want == 3 || H >= 256) return LD(true, 3);
+  return LD(true, 4);
+#undef LD
 }
 
 }  // namespace
@@ -410,12 +485,13 @@ TB_API int tb_qkv_post(void* qkv, long long ld, const int* seq_ids, const int* p
 // q [B, N*H]; pools [num_pages, page_size, KH*H]; page_table [*, max_pages]; seq_ids [B]; seq_lens [B];
 // workspace: part_acc fp32 [B*N*splits*H], part_ml fp32 [B*N*splits*2] with splits = ceil(max_ctx / split_tokens);
 // split_tokens = context tokens per CTA, a multiple of 64 in [64, 2048] (0 = 256). CTAs of splits that lie past the
-// end of their sequence return at once.
+// end of their sequence return at once. pool_rows = num_pages * page_size (rows of the pools, for the tensor maps;
+// 0 = no TMA staging). status: word that a bounded mbarrier wait writes its code to.
 TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, const void* v_pool,
                            const int* page_table, int max_pages, int page_size, const int* seq_ids,
                            const int* seq_lens, int B, int N, int KH, int H, int max_ctx, float scale, float softcap,
-                           int window, int split_tokens, float* part_acc, float* part_ml, void* out, long long ldo,
-                           cudaStream_t stream) {
+                           int window, int split_tokens, long long pool_rows, float* part_acc, float* part_ml, void* out,
+                           long long ldo, int* status, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (KH <= 0 || N % KH || (ldq % 8)) return -2;
   const int G = N / KH;
@@ -429,9 +505,9 @@ TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, con
   auto kp = (const __nv_bfloat16*)k_pool;
   auto vp = (const __nv_bfloat16*)v_pool;
   switch (H) {
-    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
-    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
-    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml); break;
+    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
+    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
+    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
     default: return -2;
   }
   if (rc) return rc;

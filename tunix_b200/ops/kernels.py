@@ -306,12 +306,12 @@ def attn_bwd(dout, q, k, v, o, lse, *, scale: float, causal: bool = True, window
 _lib.register_cuda_sigs({
     "tb_kv_write": [_lib.P, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P],
     "tb_paged_decode": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I,
-                        _lib.I, _lib.I, _lib.F, _lib.F, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P],
+                        _lib.I, _lib.I, _lib.F, _lib.F, _lib.I, _lib.I, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.P],
     "tb_qkv_post": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P, _lib.I,
                     _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P],
 })
 
-DECODE_SPLIT_TOKENS = 256
+DECODE_SPLIT_TOKENS = 512
 
 
 def kv_write(k_new, v_new, seq_ids, positions, page_table, page_size: int, k_pool, v_pool) -> None:
@@ -344,9 +344,13 @@ def qkv_post(qkv, seq_ids, positions, q_norm_w, k_norm_w, eps: float, add_one: b
 
 def decode_split_tokens(batch: int, num_kv_heads: int) -> int:
     """Context tokens per CTA of `paged_decode` (grid = batch x kv heads x splits). Measured on B200 with 8 kv heads,
-    head dim 128: at 64 sequences 64 / 128 / 256 / 512 tokens per CTA take 122 / 101 / 83 / 83 us at context 1000
-    (52 / 44 / 40 / 40 us at context 290): the per-CTA costs (query load, merge of the warps' states, partial write,
-    combine) outweigh a finer balance; at 256 sequences x 768 tokens 256 / 512 / 1024 take 220 / 202 / 189 us."""
+    head dim 128, TMA staging: at 64 sequences x 640 tokens 128 / 256 / 512 tokens per CTA take 58 / 56 / 52 us, at
+    256 sequences x 768 tokens 512 / 1024 take 161 / 157 us: the per-CTA costs (query load, merge of the warps'
+    states, partial write, combine) outweigh a finer balance, so the split is coarse."""
+    import os
+    forced = os.environ.get("TUNIX_B200_DECODE_SPLIT")
+    if forced:
+        return int(forced)
     return 1024 if batch * num_kv_heads >= 2048 else DECODE_SPLIT_TOKENS
 
 
@@ -358,6 +362,9 @@ def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_hea
     assert q.stride(2) == 1 and q.stride(1) == H
     split_tokens = split_tokens or decode_split_tokens(B, num_kv_heads)
     splits = (max_ctx + split_tokens - 1) // split_tokens
+    # contiguous pools [pages, page_size, KH * H] can be staged by TMA (one tensor map per pool)
+    pool_rows = k_pool.shape[0] * k_pool.shape[1] if (k_pool.is_contiguous() and v_pool.is_contiguous()
+                                                      and k_pool.shape == v_pool.shape) else 0
     if workspace is None:
         workspace = (torch.empty(B * N * splits * H, dtype=torch.float32, device=q.device),
                      torch.empty(B * N * splits * 2, dtype=torch.float32, device=q.device))
@@ -366,8 +373,8 @@ def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_hea
     rc = _lib.cuda().tb_paged_decode(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
                                      page_table.shape[1], page_size, seq_ids.data_ptr(), seq_lens.data_ptr(), B, N,
                                      num_kv_heads, H, max_ctx, float(scale), float(softcap), int(window), int(split_tokens),
-                                     workspace[0].data_ptr(), workspace[1].data_ptr(), out.data_ptr(), N * H,
-                                     _lib.stream_ptr())
+                                     pool_rows, workspace[0].data_ptr(), workspace[1].data_ptr(), out.data_ptr(), N * H,
+                                     _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "tb_paged_decode")
     _count(2)
     return out
