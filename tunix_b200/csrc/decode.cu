@@ -160,7 +160,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                     const int* __restrict__ seq_ids, const int* __restrict__ seq_lens, int KH, int G, float scale,
                     float softcap, int window, int num_splits, int split_tokens,
                     float* __restrict__ part_acc,                                               // [B, N, splits, H]
-                    float* __restrict__ part_ml, int* __restrict__ status) {                    // [B, N, splits, 2]
+                    float* __restrict__ part_ml,                                                // [B, N, splits, 2]
+                    __nv_bfloat16* __restrict__ out, long long ldo,   // written directly when there is one split
+                    int* __restrict__ status) {
   constexpr int CPR = H / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = TILE_KEYS * H * 2;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -176,7 +178,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
   const int N = KH * G;
   const int len = seq_lens[b];
   int lo = split * split_tokens;
-  if (lo >= len) return;          // past the end of this sequence: the combine kernel never reads this split
+  if (lo >= len) {                // past the end of this sequence: the combine kernel never reads this split
+    if (num_splits == 1)          // (an empty slot with a single split: its output row is zero)
+      for (int idx = threadIdx.x; idx < G * H; idx += 128)
+        out[(long long)b * ldo + (long long)(kh * G) * H + idx] = __float2bfloat16(0.f);
+    return;
+  }
   const int hi = min(len, lo + split_tokens);
   if (window > 0) lo = max(lo, len - window);
   const int* pt = page_table + (long long)seq_ids[b] * max_pages;
@@ -360,6 +367,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       ll += sm_l[w][g] * c;
       aa += sm_acc[(w * 16 + g) * H + d] * c;
     }
+    if (num_splits == 1) {                 // the whole context in this CTA: no partial state, no combine kernel
+      out[(long long)b * ldo + (long long)(kh * G + g) * H + d] = __float2bfloat16(ll > 0.f ? aa / ll : 0.f);
+      continue;
+    }
     const long long oidx = (((long long)b * N + kh * G + g) * num_splits + split);
     part_acc[oidx * H + d] = aa;
     if (d == 0) {
@@ -401,7 +412,8 @@ template <int H, bool TMA, int STAGES>
 int launch_decode_v(int G, dim3 grid, cudaStream_t stream, const CUtensorMap& tmK, const CUtensorMap& tmV,
                     const __nv_bfloat16* q, long long ldq, const __nv_bfloat16* kp, const __nv_bfloat16* vp, const int* pt,
                     int max_pages, int page_size, const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap,
-                    int window, int splits, int split_tokens, float* pa, float* pml, int* status) {
+                    int window, int splits, int split_tokens, float* pa, float* pml, __nv_bfloat16* out, long long ldo,
+                    int* status) {
   constexpr int TILE2 = 2 * TILE_KEYS * H * 2;                       // one stage: a K tile and a V tile
   constexpr int SMEM = STAGES * TILE2 + (TMA ? 1024 : 0);
   static bool attr_set = false;
@@ -413,7 +425,8 @@ int launch_decode_v(int G, dim3 grid, cudaStream_t stream, const CUtensorMap& tm
   // a split of one 64-key tile needs one stage only: more CTAs fit on an SM
   const int smem = split_tokens > TILE_KEYS ? SMEM : TILE2 + (TMA ? 1024 : 0);
   return launch_pdl(paged_decode_kernel<H, TMA, STAGES>, grid, dim3(128), smem, stream, tmK, tmV, q, ldq, kp, vp, pt, max_pages,
-                    page_size, seq_ids, seq_lens, KH, G, scale, softcap, window, splits, split_tokens, pa, pml, status) == cudaSuccess ? 0 : -5;
+                    page_size, seq_ids, seq_lens, KH, G, scale, softcap, window, splits, split_tokens, pa, pml, out, ldo,
+                    status) == cudaSuccess ? 0 : -5;
 }
 
 // TMA staging needs tiles that lie inside one page.
@@ -421,7 +434,7 @@ template <int H>
 int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, long long ldq,
                   const __nv_bfloat16* kp, const __nv_bfloat16* vp, long long pool_rows, const int* pt, int max_pages,
                   int page_size, const int* seq_ids, const int* seq_lens, int KH, float scale, float softcap, int window,
-                  int splits, int split_tokens, float* pa, float* pml, int* status) {
+                  int splits, int split_tokens, float* pa, float* pml, __nv_bfloat16* out, long long ldo, int* status) {
   static const bool no_tma = getenv("TUNIX_B200_DECODE_NO_TMA") != nullptr;
   static const char* stages_env = getenv("TUNIX_B200_DECODE_STAGES");
   CUtensorMap tmK, tmV;
@@ -431,7 +444,7 @@ int launch_decode(int G, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q,
                    tb_make_tmap_2d_bf16(&tmK, kp, (uint64_t)pool_rows, (uint64_t)KH * H, (uint64_t)KH * H, TILE_KEYS, 64, 1) == 0 &&
                    tb_make_tmap_2d_bf16(&tmV, vp, (uint64_t)pool_rows, (uint64_t)KH * H, (uint64_t)KH * H, TILE_KEYS, 64, 1) == 0;
 #define LD(T, S) launch_decode_v<H, T, S>(G, grid, stream, tmK, tmV, q, ldq, kp, vp, pt, max_pages, page_size, seq_ids, seq_lens, \
-                                         KH, scale, softcap, window, splits, split_tokens, pa, pml, status)
+                                         KH, scale, softcap, window, splits, split_tokens, pa, pml, out, ldo, status)
   if (!tma) return LD(false, 2);
   // measured at head dim 128 (8 kv heads, 256 sequences x 768 tokens): 2 / 3 / 4 stages take 157 / 161 / 194 us,
   // cp.async staging 190 us: three CTAs per SM with two stages each beat deeper rings on fewer CTAs
@@ -505,12 +518,13 @@ TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, con
   auto kp = (const __nv_bfloat16*)k_pool;
   auto vp = (const __nv_bfloat16*)v_pool;
   switch (H) {
-    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
-    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
-    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, status); break;
+    case 64: rc = launch_decode<64>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, (__nv_bfloat16*)out, ldo, status); break;
+    case 128: rc = launch_decode<128>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, (__nv_bfloat16*)out, ldo, status); break;
+    case 256: rc = launch_decode<256>(G, grid, stream, qq, ldq, kp, vp, pool_rows, page_table, max_pages, page_size, seq_ids, seq_lens, KH, scale, softcap, window, splits, split_tokens, part_acc, part_ml, (__nv_bfloat16*)out, ldo, status); break;
     default: return -2;
   }
   if (rc) return rc;
+  if (splits == 1) return 0;
   return launch_pdl(paged_decode_combine_kernel, dim3(B, N), dim3(128), 0, stream, (const float*)part_acc,
                     (const float*)part_ml, seq_lens, N, H, splits, split_tokens, window, (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : -5;
 }

@@ -423,7 +423,7 @@ class PagedEngine(BaseSampler):
 
     def _new_state(self, B, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
         dev = self.device
-        split = K.decode_split_tokens(B, self.cfg.num_kv_heads)
+        split = K.decode_split_tokens(B, self.cfg.num_kv_heads, self.cache_size)
         splits = (self.cache_size + split - 1) // split
         N, H, V = self.cfg.num_heads, self.cfg.head_dim, self.cfg.vocab_size
         i64 = dict(dtype=torch.int64, device=dev)

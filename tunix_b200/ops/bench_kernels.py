@@ -166,7 +166,7 @@ def main(argv=None) -> int:
                    args.iters, args.warmup)
         gb = 2.0 * Bn * ctx * KH * H * 2 / ms / 1e6
         out.update(shape=[Bn, ctx, N, KH, H], ms=ms, gbs=gb, frac_of_peak=gb / peak_gb,
-                   split_tokens=args.split or K.decode_split_tokens(Bn, KH))
+                   split_tokens=args.split or K.decode_split_tokens(Bn, KH, args.max_ctx or ctx))
     elif args.kernel == "moe":
         from tunix_b200.ops import moe
         T, E, k, D, Fd = args.rows, args.experts, args.topk, args.dim, args.ffn

@@ -342,16 +342,20 @@ def qkv_post(qkv, seq_ids, positions, q_norm_w, k_norm_w, eps: float, add_one: b
     _count()
 
 
-def decode_split_tokens(batch: int, num_kv_heads: int) -> int:
+def decode_split_tokens(batch: int, num_kv_heads: int, max_ctx: int = 0) -> int:
     """Context tokens per CTA of `paged_decode` (grid = batch x kv heads x splits). Measured on B200 with 8 kv heads,
     head dim 128, TMA staging: at 64 sequences x 640 tokens 128 / 256 / 512 tokens per CTA take 58 / 56 / 52 us, at
     256 sequences x 768 tokens 512 / 1024 take 161 / 157 us: the per-CTA costs (query load, merge of the warps'
-    states, partial write, combine) outweigh a finer balance, so the split is coarse."""
+    states, partial write, combine) outweigh a finer balance, so the split is coarse. A context that fits one split
+    needs no combine kernel at all (the CTA writes the output row itself)."""
     import os
     forced = os.environ.get("TUNIX_B200_DECODE_SPLIT")
     if forced:
         return int(forced)
-    return 1024 if batch * num_kv_heads >= 2048 else DECODE_SPLIT_TOKENS
+    if batch * num_kv_heads >= 512:
+        whole = -(-max_ctx // 64) * 64
+        return whole if 0 < whole <= 2048 else 1024      # one split per sequence when the context allows
+    return DECODE_SPLIT_TOKENS
 
 
 def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_heads: int, page_size: int, max_ctx: int,
@@ -360,7 +364,7 @@ def paged_decode(q, k_pool, v_pool, page_table, seq_ids, seq_lens, *, num_kv_hea
     `workspace` (two fp32 buffers) must be sized for ceil(max_ctx / split_tokens) splits."""
     B, N, H = q.shape
     assert q.stride(2) == 1 and q.stride(1) == H
-    split_tokens = split_tokens or decode_split_tokens(B, num_kv_heads)
+    split_tokens = split_tokens or decode_split_tokens(B, num_kv_heads, max_ctx)
     splits = (max_ctx + split_tokens - 1) // split_tokens
     # contiguous pools [pages, page_size, KH * H] can be staged by TMA (one tensor map per pool)
     pool_rows = k_pool.shape[0] * k_pool.shape[1] if (k_pool.is_contiguous() and v_pool.is_contiguous()
