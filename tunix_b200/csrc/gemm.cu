@@ -86,6 +86,8 @@ struct GemmArgs {
   int flags;
   const TileDesc* tiles;      // null = dense problem
   const int* num_tiles_dev;
+  int a_rows_rt;              // K-major A, one tile high, no MN-major B: rows of A that are loaded (16 / 32 / 64; 0 = all
+                              // 128) and the ring is packed tightly, see the kernel
   int bn_rt;                  // dense problems only: tile width actually used (multiple of 16, <= BN; 0 = BN). A width
                               // picked at run time lets a skinny problem cover the SMs in whole waves.
   const uint8_t* b_packed;    // dense problems only: B pre-tiled by tb_pack_weight (one contiguous, pre-swizzled
@@ -113,6 +115,8 @@ struct GemmArgs {
   int* status;
 };
 
+constexpr int MAX_STAGES = 16;   // barrier slots per kind; the compact ring of skinny problems (GemmArgs::a_rows_rt) uses up to this many
+
 template <int BN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -121,7 +125,7 @@ struct Cfg {
   // fill ~200 KiB of shared memory: deeper rings for the narrow tiles that stream weights at small M
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : (BN == 64) ? 8 : 10;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator stages
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -359,11 +363,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t bar_base = smem_base + C_::STAGES * C_::STAGE_BYTES;
   // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2], then tmem ptr, abort
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (C_::STAGES + s); };
-  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * C_::STAGES + s); };
-  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * C_::STAGES + 2 + s); };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * MAX_STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * MAX_STAGES + 2 + s); };
   volatile uint32_t* tmem_ptr_smem =
-      reinterpret_cast<volatile uint32_t*>(smem_al + C_::STAGES * C_::STAGE_BYTES + 8 * (2 * C_::STAGES + 4));
+      reinterpret_cast<volatile uint32_t*>(smem_al + C_::STAGES * C_::STAGE_BYTES + 8 * (2 * MAX_STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -378,7 +382,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool b_mn = args.flags & GF_B_MN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C_::STAGES; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -403,6 +407,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   pdl_wait();            // everything above overlapped the previous kernel's tail; from here on memory is read
 
   const bool grouped = args.tiles != nullptr;
+  // Ring geometry. Normally STAGES slots of a 128-row A tile and a BN-row B tile. A one-tile-high problem with
+  // M <= 64 (a_rows_rt) loads only the rows of A that exist and packs the slots tightly (a_rows_rt * 128 bytes of
+  // A, then bn rows of B): the same shared memory holds more stages, which is what a kernel that only streams
+  // weights is short of. The MMA still reads 128 rows of A; rows past a_rows_rt are whatever follows in the ring
+  // (the slot's B tile, the next slot), and the accumulator rows they produce are never stored.
+  const int a_bytes = args.a_rows_rt > 0 ? args.a_rows_rt * BK * 2 : C_::A_BYTES;
+  const int stage_bytes = args.a_rows_rt > 0 ? a_bytes + bn * BK * 2 : C_::STAGE_BYTES;
+  int nstages = C_::STAGES;
+  if (args.a_rows_rt > 0) {
+    // the last slot's 128-row A read must end inside the ring
+    nstages = (C_::STAGES * C_::STAGE_BYTES - C_::A_BYTES) / stage_bytes + 1;
+    if (nstages * stage_bytes > C_::STAGES * C_::STAGE_BYTES) --nstages;
+    nstages = max(1, min(nstages, MAX_STAGES));
+  }
   const int total_tiles = grouped ? *args.num_tiles_dev : num_tiles;
   const int n_gemm = args.gemm_ctas > 0 ? args.gemm_ctas : (int)gridDim.x;   // CTAs that walk the tile list
   auto tile_info = [&](int t) -> TileDesc {
@@ -485,9 +503,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + stage * C_::STAGE_BYTES;
-          const uint32_t sb = sa + C_::A_BYTES;
-          mbar_expect_tx(full_bar(stage), C_::A_BYTES + (b_mn ? C_::B_BYTES : bn * BK * 2));
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + a_bytes;
+          mbar_expect_tx(full_bar(stage), a_bytes + (b_mn ? C_::B_BYTES : bn * BK * 2));
           const int k0 = kb * BK;
           if (!a_mn) {
             tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
@@ -506,7 +524,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(sb + j * 8192, &tmB, full_bar(stage), n0 + 64 * j, k0 + td.b_row0);
           }
-          if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -541,8 +559,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + stage * C_::STAGE_BYTES;
-          const uint32_t sb = sa + C_::A_BYTES;
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + a_bytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
@@ -550,7 +568,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma_f16_ss(tmem_d, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // frees the smem slot when these MMAs retire
-          if (++stage == C_::STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == nstages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(tfull_bar(acc));
@@ -741,7 +759,7 @@ int aux_ctas_for(double bytes, double flops, int world) {
 }
 void clear_fused(GemmArgs& a) {
   a.gemm_ctas = 0; a.aux_kind = 0; a.rank = 0; a.world = 1; a.rot_m = 0; a.rot_n = 0; a.wait_mode = 0;
-  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.bn_rt = 0; a.b_packed = nullptr; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
+  a.own_lo = 0; a.own_hi = 0; a.rot_k = 0; a.a_rows_rt = 0; a.bn_rt = 0; a.b_packed = nullptr; a.wait_flags = nullptr; a.wait_epoch = 0; a.done_flags = nullptr;
   memset(&a.copy, 0, sizeof(a.copy));
   memset(&a.red, 0, sizeof(a.red));
 }
@@ -870,7 +888,9 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   }
   CUtensorMap tmA, tmB;
   int r;
-  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1);
+  static const bool no_compact = getenv("TUNIX_B200_NO_COMPACT_RING") != nullptr;
+  const int a_rows = (num_m == 1 && M <= 64 && !a_mn && !b_mn && max_ctas <= 0 && !no_compact) ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 0;
+  if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, a_rows > 0 ? a_rows : BM, BK, 1);
   else       r = tb_make_tmap_2d_bf16(&tmA, A, K, M, lda, BK, 64, 1);
   if (r) return -3;
   if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, bn_rt > 0 ? bn_rt : BN, BK, 1);
@@ -885,6 +905,7 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   args.tiles = nullptr; args.num_tiles_dev = nullptr;
   clear_fused(args);
   args.bn_rt = bn_rt;
+  args.a_rows_rt = a_rows;
   const int tiles = num_m * ((N + (bn_rt > 0 ? bn_rt : BN) - 1) / (bn_rt > 0 ? bn_rt : BN));
   int ctas = g_sm_count;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
@@ -979,7 +1000,9 @@ TB_API int tb_gemm_packed_bf16(const void* A, long long lda, const void* P, int 
   }
   const int BN = w > 128 ? 256 : w > 64 ? 128 : w > 32 ? 64 : 32;
   CUtensorMap tmA;
-  if (tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, BM, BK, 1)) return -3;
+  static const bool no_compact = getenv("TUNIX_B200_NO_COMPACT_RING") != nullptr;
+  const int a_rows = (M <= 64 && !no_compact) ? (M <= 16 ? 16 : M <= 32 ? 32 : 64) : 0;
+  if (tb_make_tmap_2d_bf16(&tmA, A, M, K, lda, a_rows > 0 ? a_rows : BM, BK, 1)) return -3;
   GemmArgs args;
   args.M = M; args.N = N; args.K = K; args.flags = flags;
   args.C = C; args.ldc = ldc;
@@ -989,6 +1012,7 @@ TB_API int tb_gemm_packed_bf16(const void* A, long long lda, const void* P, int 
   args.tiles = nullptr; args.num_tiles_dev = nullptr;
   clear_fused(args);
   args.bn_rt = w == BN ? 0 : w;
+  args.a_rows_rt = a_rows;
   args.b_packed = reinterpret_cast<const uint8_t*>(P);
   const int tiles = ((M + BM - 1) / BM) * ((N + w - 1) / w);
   const int ctas = tiles < g_sm_count ? tiles : g_sm_count;
