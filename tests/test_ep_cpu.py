@@ -46,3 +46,26 @@ def test_expert_parallel_training_matches_single_process(tmp_path):
     for n, w in one.items():
         got = torch.cat([p[n] for p in parts], 0) if parts[0][n].shape != w.shape else parts[0][n]
         assert torch.allclose(got, w, atol=5e-5, rtol=2e-4), (n, (got - w).abs().max())
+
+
+def test_plan_sizes_buffers_by_received_rows():
+    """The routing plan bounds what a rank receives by its actual (128-padded) row count, not by the worst case."""
+    import torch
+    from tunix_b200.parallel.ep import _Plan
+
+    class Ctx:
+        def __init__(self, world, rank):
+            self.world, self.rank = world, rank
+    W, T, k, E = 4, 50, 2, 8
+    g = torch.Generator().manual_seed(0)
+    idx_all = torch.randint(0, E, (W * T, k), generator=g, dtype=torch.int32)
+    total = 0
+    for r in range(W):
+        p = _Plan(idx_all, E, Ctx(W, r))
+        counts = torch.bincount(idx_all.reshape(-1).long(), minlength=E).view(W, E // W)[r]
+        want = int(((counts + 127) // 128 * 128).sum())
+        assert p.rows == max(128, want) and p.rows <= p.max_rows and p.src_rank.numel() == p.rows
+        assert int((p.src_rank >= 0).sum()) == int(counts.sum()) and int(p.seg_off[-1]) == want
+        assert int(p.own_pos.max()) < p.rows
+        total += int(counts.sum())
+    assert total == W * T * k

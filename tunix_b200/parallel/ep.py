@@ -115,15 +115,20 @@ class _Plan:
         pos = torch.empty_like(flat)
         pos[order] = seg_start[sorted_e] + rank_in
         owner = flat // E_loc
+        # worst case (every slot of every rank routed here): the size of the symmetric row workspace, which must be
+        # the same on all ranks. What this rank actually receives is read back once (the plan synchronises with the
+        # host anyway, for `nonzero` below) so that buffers and element-wise kernels cover those rows only: with 8
+        # ranks the worst case is 8 times the expected row count.
         self.max_rows = ((W * T * k + E_loc * 127 + 127) // 128) * 128
+        self.rows = max(128, int(pad2[r].sum().item()))
         # this rank as a source: where its slots live
         mine = slice(r * T * k, (r + 1) * T * k)
         self.dst_rank = owner[mine].int().view(T, k).contiguous()
         self.dst_pos = pos[mine].int().view(T, k).contiguous()
         # this rank as an owner: which (source, token) fills each of its rows, and the slot's global index
         own = (owner == r).nonzero(as_tuple=True)[0]
-        self.src_rank = torch.full((self.max_rows,), -1, dtype=torch.int32, device=flat.device)
-        self.src_row = torch.zeros((self.max_rows,), dtype=torch.int32, device=flat.device)
+        self.src_rank = torch.full((self.rows,), -1, dtype=torch.int32, device=flat.device)
+        self.src_row = torch.zeros((self.rows,), dtype=torch.int32, device=flat.device)
         self.src_rank[pos[own]] = (own // (T * k)).int()
         self.src_row[pos[own]] = ((own // k) % T).int()
         self.own_slots, self.own_pos = own, pos[own]
@@ -142,7 +147,7 @@ class _Dispatch(torch.autograd.Function):
         ws = ep.workspace("tok", T, D)
         ws.tensor.view(T, D).copy_(x)
         ep.barrier.wait()
-        xp = torch.empty((plan.max_rows, D), dtype=torch.bfloat16, device=x.device)
+        xp = torch.empty((plan.rows, D), dtype=torch.bfloat16, device=x.device)
         K.moe_zero_pad(xp, plan.seg_off, plan.counts)
         K.moe_pull_rows(ws.c_ptrs, ep.world, D, plan.src_rank, plan.src_row, xp)
         ep.barrier.wait()
@@ -154,7 +159,7 @@ class _Dispatch(torch.autograd.Function):
         from ..ops import kernels as K
         plan, ep, D = ctx.plan, ctx.ep, ctx.D
         ws = ep.workspace("rows", plan.max_rows, D)
-        ws.tensor.view(plan.max_rows, D).copy_(dxp)
+        ws.tensor.view(plan.max_rows, D)[:plan.rows].copy_(dxp)
         ep.barrier.wait()
         dx = K.moe_gather_sum_peer(ws.c_ptrs, ep.world, D, plan.dst_rank, plan.dst_pos, D)
         ep.barrier.wait()
@@ -167,7 +172,7 @@ class _Combine(torch.autograd.Function):
         from ..ops import kernels as K
         D = y.shape[1]
         ws = ep.workspace("rows", plan.max_rows, D)
-        ws.tensor.view(plan.max_rows, D).copy_(y)
+        ws.tensor.view(plan.max_rows, D)[:plan.rows].copy_(y)
         ep.barrier.wait()
         out = K.moe_gather_sum_peer(ws.c_ptrs, ep.world, D, plan.dst_rank, plan.dst_pos, D, residual)
         ep.barrier.wait()
@@ -182,7 +187,7 @@ class _Combine(torch.autograd.Function):
         ws = ep.workspace("tok", T, D)
         ws.tensor.view(T, D).copy_(dout)
         ep.barrier.wait()
-        dy = torch.empty((plan.max_rows, D), dtype=torch.bfloat16, device=dout.device)
+        dy = torch.empty((plan.rows, D), dtype=torch.bfloat16, device=dout.device)
         K.moe_zero_pad(dy, plan.seg_off, plan.counts)
         K.moe_pull_rows(ws.c_ptrs, ep.world, D, plan.src_rank, plan.src_row, dy)
         ep.barrier.wait()
@@ -224,7 +229,7 @@ def expert_parallel_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: 
     from ..ops import moe as moe_ops
     plan = _Plan(idx_all, E, ep)
     xp = _Dispatch.apply(x.contiguous(), plan, ep)
-    wrow = torch.zeros(plan.max_rows, dtype=torch.float32, device=x.device).index_put((plan.own_pos,),
+    wrow = torch.zeros(plan.rows, dtype=torch.float32, device=x.device).index_put((plan.own_pos,),
                                                                                      w_all.reshape(-1)[plan.own_slots])
     y = moe_ops.local_experts(xp, wrow, plan.seg_off, plan.counts, layer.gate_proj, layer.up_proj, layer.down_proj,
                               layer.cfg.activation)
