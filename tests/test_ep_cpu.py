@@ -66,6 +66,11 @@ def test_plan_sizes_buffers_by_received_rows():
         want = int(((counts + 127) // 128 * 128).sum())
         assert p.rows == max(128, want) and p.rows <= p.max_rows and p.src_rank.numel() == p.rows
         assert int((p.src_rank >= 0).sum()) == int(counts.sum()) and int(p.seg_off[-1]) == want
-        assert int(p.own_pos.max()) < p.rows
+        mine = p.own_dest < p.rows
+        assert int(mine.sum()) == int(counts.sum()) and int(p.own_dest.max()) <= p.rows
+        # every owned slot is the row the plan says it is: (source rank, token) recovered from the slot index
+        slot = torch.arange(W * T * k)[mine]
+        assert torch.equal(p.src_rank[p.own_dest[mine]].long(), slot // (T * k))
+        assert torch.equal(p.src_row[p.own_dest[mine]].long(), (slot // k) % T)
         total += int(counts.sum())
     assert total == W * T * k

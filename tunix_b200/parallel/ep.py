@@ -116,22 +116,24 @@ class _Plan:
         pos[order] = seg_start[sorted_e] + rank_in
         owner = flat // E_loc
         # worst case (every slot of every rank routed here): the size of the symmetric row workspace, which must be
-        # the same on all ranks. What this rank actually receives is read back once (the plan synchronises with the
-        # host anyway, for `nonzero` below) so that buffers and element-wise kernels cover those rows only: with 8
-        # ranks the worst case is 8 times the expected row count.
+        # the same on all ranks. What this rank actually receives is read back (the plan's one host synchronisation)
+        # so that buffers and element-wise kernels cover those rows only: with 8 ranks the worst case is 8 times
+        # the expected row count.
         self.max_rows = ((W * T * k + E_loc * 127 + 127) // 128) * 128
         self.rows = max(128, int(pad2[r].sum().item()))
         # this rank as a source: where its slots live
         mine = slice(r * T * k, (r + 1) * T * k)
         self.dst_rank = owner[mine].int().view(T, k).contiguous()
         self.dst_pos = pos[mine].int().view(T, k).contiguous()
-        # this rank as an owner: which (source, token) fills each of its rows, and the slot's global index
-        own = (owner == r).nonzero(as_tuple=True)[0]
-        self.src_rank = torch.full((self.rows,), -1, dtype=torch.int32, device=flat.device)
-        self.src_row = torch.zeros((self.rows,), dtype=torch.int32, device=flat.device)
-        self.src_rank[pos[own]] = (own // (T * k)).int()
-        self.src_row[pos[own]] = ((own // k) % T).int()
-        self.own_slots, self.own_pos = own, pos[own]
+        # this rank as an owner: which (source, token) fills each of its rows. Slots owned elsewhere are sent to a
+        # spare last entry instead of being compacted away (no `nonzero`, so no second host synchronisation).
+        slots = torch.arange(flat.numel(), device=flat.device)
+        self.own_dest = torch.where(owner == r, pos, torch.full_like(pos, self.rows))      # [W*T*k] row or `rows`
+        self.src_rank = torch.full((self.rows + 1,), -1, dtype=torch.int32, device=flat.device).scatter_(
+            0, self.own_dest, torch.div(slots, T * k, rounding_mode="floor").int())[:self.rows]
+        self.src_rank = self.src_rank.contiguous()
+        self.src_row = torch.zeros((self.rows + 1,), dtype=torch.int32, device=flat.device).scatter_(
+            0, self.own_dest, (torch.div(slots, k, rounding_mode="floor") % T).int())[:self.rows].contiguous()
         seg = torch.zeros(E_loc + 1, dtype=torch.int64, device=flat.device)
         seg[1:] = torch.cumsum(pad2[r], 0)
         self.seg_off = seg.int()
@@ -229,8 +231,9 @@ def expert_parallel_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: 
     from ..ops import moe as moe_ops
     plan = _Plan(idx_all, E, ep)
     xp = _Dispatch.apply(x.contiguous(), plan, ep)
-    wrow = torch.zeros(plan.rows, dtype=torch.float32, device=x.device).index_put((plan.own_pos,),
-                                                                                     w_all.reshape(-1)[plan.own_slots])
+    # routing weight of every row this rank owns (slots owned elsewhere land in the spare entry, cut off again)
+    wrow = torch.zeros(plan.rows + 1, dtype=torch.float32, device=x.device).index_put((plan.own_dest,),
+                                                                                         w_all.reshape(-1))[:plan.rows]
     y = moe_ops.local_experts(xp, wrow, plan.seg_off, plan.counts, layer.gate_proj, layer.up_proj, layer.down_proj,
                               layer.cfg.activation)
     return _Combine.apply(y, residual, plan, ep)
