@@ -56,3 +56,44 @@ def test_tp2_training_matches_single_process(tmp_path):
             assert torch.allclose(parts[0][n], parts[1][n], atol=1e-6), n   # replicated parameters stay in step
             got = parts[0][n]
         assert torch.allclose(got, w, atol=3e-5, rtol=1e-4), (n, (got - w).abs().max())
+
+
+def _vocab_parallel(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200.ops import reference as R
+    from tunix_b200.parallel import tp as tp_lib
+    tp = tp_lib.TPContext(device="cpu")
+    g = torch.Generator().manual_seed(3)                      # the same tensors on every rank
+    rows, D, V = 37, 32, 96
+    h = torch.randn(rows, D, generator=g).requires_grad_()
+    w = (torch.randn(V, D, generator=g) * 0.3)
+    t = torch.randint(0, V, (rows,), generator=g)
+    t[5] = -1
+    gout = torch.randn(rows, generator=g)
+    res = {}
+    for softcap, temp in ((0.0, 1.0), (5.0, 0.7)):
+        ws = w[rank * V // world:(rank + 1) * V // world].clone().requires_grad_()
+        lp, ent = tp_lib.vocab_parallel_logprobs(h, ws, t, tp, softcap=softcap, temperature=temp, want_entropy=True, chunk=16)
+        (lp * gout).sum().backward()
+        wf = w.clone().requires_grad_()
+        hf = h.detach().clone().requires_grad_()
+        lp_ref, ent_ref = R.lm_head_logprobs_ref(hf, wf, t, softcap=softcap, temperature=temp, want_entropy=True)
+        (lp_ref * gout).sum().backward()
+        key = f"{softcap}_{temp}"
+        res[key] = [float((lp - lp_ref).abs().max()), float((ent - ent_ref).abs().max()),
+                    float((h.grad - hf.grad).abs().max()),
+                    float((ws.grad - wf.grad[rank * V // world:(rank + 1) * V // world]).abs().max())]
+        h.grad = None
+    torch.save(res, f"{out}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_logprobs_match_full_head(tmp_path):
+    mp.spawn(_vocab_parallel, args=(2, 29747, str(tmp_path / "vp")), nprocs=2, join=True)
+    for rank in range(2):
+        res = torch.load(str(tmp_path / "vp") + f".{rank}")
+        for key, errs in res.items():
+            assert max(errs) < 2e-4, (rank, key, errs)

@@ -365,3 +365,85 @@ def local_batch(model, t: Optional[torch.Tensor]):
         return t
     n = t.shape[0] // tp.world
     return t[tp.rank * n:(tp.rank + 1) * n]
+
+
+# ---------------------------------------------------------------------------------- vocab-parallel lm_head
+class _VocabParallelLogprobs(torch.autograd.Function):
+    """log p(target) (and entropy) with the vocabulary rows of the head sharded over the group: every rank scores
+    its slice in row chunks (fp32 logits of `chunk x V/tp` at a time), and the ranks exchange three numbers per
+    token: the running maximum (all-reduce max), then sum exp(z - max), the target's logit and, for the entropy,
+    sum exp(z - max) * z (all-reduce sum). The backward pass recomputes the chunk's logits and forms
+    dz = (softmax - onehot) * g locally; dh is summed over the group, dW stays with the shard.
+    (tunix/models/*: lm_head sharded `(fsdp, tp)`, tunix/models/llama3/model.py:47-82)."""
+
+    @staticmethod
+    def forward(ctx, h, w_shard, targets, tp, softcap, temperature, want_entropy, chunk):
+        rows, D = h.shape
+        Vs = w_shard.shape[0]
+        lo = tp.rank * Vs
+        t = targets.reshape(-1).long()
+        local = (t >= lo) & (t < lo + Vs)
+        m = torch.empty(rows, dtype=torch.float32, device=h.device)
+        stats = torch.zeros(rows, 3, dtype=torch.float32, device=h.device)          # sumexp, target logit, sum exp*z
+
+        def logits(s0, s1):
+            z = (h[s0:s1].to(w_shard.dtype) @ w_shard.t()).float()
+            if softcap > 0:
+                z = softcap * torch.tanh(z / softcap)
+            return z / temperature
+        for s0 in range(0, rows, chunk):
+            m[s0:s0 + chunk] = logits(s0, min(s0 + chunk, rows)).max(-1).values
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=tp.group)
+        for s0 in range(0, rows, chunk):
+            s1 = min(s0 + chunk, rows)
+            z = logits(s0, s1)
+            e = torch.exp(z - m[s0:s1, None])
+            stats[s0:s1, 0] = e.sum(-1)
+            idx = (t[s0:s1] - lo).clamp(0, Vs - 1)
+            stats[s0:s1, 1] = torch.where(local[s0:s1], z.gather(1, idx[:, None])[:, 0], torch.zeros_like(m[s0:s1]))
+            if want_entropy:
+                stats[s0:s1, 2] = (e * z).sum(-1)
+        dist.all_reduce(stats, group=tp.group)
+        lse = m + torch.log(stats[:, 0])
+        valid = t >= 0
+        logp = torch.where(valid, stats[:, 1] - lse, torch.zeros_like(lse))
+        ent = (lse - stats[:, 2] / stats[:, 0]) if want_entropy else None
+        ctx.save_for_backward(h, w_shard, t, lse)
+        ctx.tp, ctx.softcap, ctx.temperature, ctx.chunk, ctx.lo = tp, softcap, temperature, chunk, lo
+        ctx.mark_non_differentiable(*([ent] if ent is not None else []))
+        return (logp, ent) if want_entropy else (logp, None)
+
+    @staticmethod
+    def backward(ctx, g_logp, _g_ent):
+        h, w, t, lse = ctx.saved_tensors
+        tp, softcap, temp, chunk, lo = ctx.tp, ctx.softcap, ctx.temperature, ctx.chunk, ctx.lo
+        rows, Vs = h.shape[0], w.shape[0]
+        g = torch.where(t >= 0, g_logp.reshape(-1).float(), torch.zeros_like(lse))
+        dh = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=h.device)
+        local = (t >= lo) & (t < lo + Vs)
+        for s0 in range(0, rows, chunk):
+            s1 = min(s0 + chunk, rows)
+            raw = (h[s0:s1].to(w.dtype) @ w.t()).float()
+            z = (softcap * torch.tanh(raw / softcap) if softcap > 0 else raw) / temp
+            dz = -torch.exp(z - lse[s0:s1, None])                                     # d logp / dz = onehot - softmax
+            idx = (t[s0:s1] - lo).clamp(0, Vs - 1)
+            dz.scatter_add_(1, idx[:, None], local[s0:s1, None].float())
+            dz = dz * (g[s0:s1, None] / temp)
+            if softcap > 0:
+                dz = dz * (1.0 - torch.tanh(raw / softcap) ** 2)
+            dh[s0:s1] = dz @ w.float()
+            dw += dz.t() @ h[s0:s1].float()
+        dist.all_reduce(dh, group=tp.group)
+        return dh.to(h.dtype), dw.to(w.dtype), None, None, None, None, None, None
+
+
+def vocab_parallel_logprobs(h, w_shard, targets, tp: TPContext, *, softcap: float = 0.0, temperature: float = 1.0,
+                            want_entropy: bool = False, chunk: int = 2048):
+    """Per-token log p(target) with the head's vocabulary rows sharded over `tp` (rank r holds rows
+    [r * V/tp, (r+1) * V/tp)). `h` [..., D] and `targets` [...] are the same on every rank of the group; negative
+    targets are ignored (log-prob 0). Returns (logp fp32, entropy fp32 | None), identical on all ranks."""
+    h2 = h.reshape(-1, h.shape[-1])
+    logp, ent = _VocabParallelLogprobs.apply(h2, w_shard, targets, tp, float(softcap or 0.0), float(temperature),
+                                             bool(want_entropy), int(chunk) if chunk and chunk > 0 else 2048)
+    return logp.view(targets.shape), (ent.view(targets.shape) if ent is not None else None)
