@@ -68,6 +68,21 @@ def main():
         res[f"dw_{rep}"] = rel(ws_.grad, wr.grad[sl])
         res[f"dgate_{rep}"] = rel(part.gate_proj.grad, full.gate_proj.grad[rank * n:(rank + 1) * n])
         res[f"ddown_{rep}"] = rel(part.down_proj.grad, full.down_proj.grad[rank * n:(rank + 1) * n])
+    # the same with fixed-capacity receive buffers (no read-back in the routing plan): identical results while the
+    # capacity is not exceeded, and the overflow flag stays clear
+    part.ep.capacity_factor = 4.0
+    for p in part.parameters():
+        p.grad = None
+    xs = x_all[sl].clone().requires_grad_()
+    ws_ = w_all[sl].clone().requires_grad_()
+    out = ep_lib.expert_parallel_forward(part, xs, ws_, idx_all[sl])
+    out.backward(dout_all[sl])
+    _lib.raise_if_kernel_error()
+    part.ep.raise_if_overflow()
+    res["out_cap"] = rel(out, ref[sl])
+    res["dx_cap"] = rel(xs.grad, xr.grad[sl])
+    res["dgate_cap"] = rel(part.gate_proj.grad, full.gate_proj.grad[rank * n:(rank + 1) * n])
+    part.ep.capacity_factor = None
     allres = [None] * world
     dist.all_gather_object(allres, res)
     if rank == 0:

@@ -74,3 +74,43 @@ def test_plan_sizes_buffers_by_received_rows():
         assert torch.equal(p.src_row[p.own_dest[mine]].long(), (slot // k) % T)
         total += int(counts.sum())
     assert total == W * T * k
+
+
+def test_plan_with_fixed_capacity_drops_overflow_and_flags_it():
+    """Fixed-capacity plans need no read-back: with room to spare they equal the exact plan; when an owner would
+    receive more rows than the capacity, the slots past it are dropped on both sides and the overflow flag is set."""
+    import pytest
+    import torch
+    from tunix_b200.parallel.ep import EPContext, _Plan
+
+    def ctx(world, rank, cf=None):
+        c = EPContext.__new__(EPContext)
+        c.world, c.rank, c.capacity_factor, c.overflow = world, rank, cf, None
+        return c
+    W, T, k, E = 2, 96, 2, 4
+    g = torch.Generator().manual_seed(1)
+    idx_all = torch.randint(0, E, (W * T, k), generator=g, dtype=torch.int32)
+    for r in range(W):
+        exact = _Plan(idx_all, E, ctx(W, r))
+        roomy_ctx = ctx(W, r, cf=4.0)
+        roomy = _Plan(idx_all, E, roomy_ctx)
+        assert roomy.rows >= exact.rows and not bool(roomy_ctx.overflow)
+        assert torch.equal(roomy.dst_rank, exact.dst_rank) and torch.equal(roomy.dst_pos, exact.dst_pos)
+        assert torch.equal(roomy.seg_off, exact.seg_off) and torch.equal(roomy.counts, exact.counts)
+        assert torch.equal(roomy.src_rank[:exact.rows], exact.src_rank) and int((roomy.src_rank[exact.rows:] >= 0).sum()) == 0
+    # everything routed to expert 0 (rank 0): 2048 rows wanted, capacity 0.5 * 1024 + 2 * 128 = 768
+    T2 = 512
+    skew = torch.zeros(W * T2, k, dtype=torch.int32)
+    c0 = ctx(W, 0, cf=0.5)
+    p0 = _Plan(skew, E, c0)
+    assert p0.rows == 768 and bool(c0.overflow)
+    assert p0.seg_off.tolist() == [0, 768, 768] and p0.counts.tolist() == [768, 0]
+    assert int((p0.src_rank >= 0).sum()) == 768                       # the owner fills exactly its capacity
+    kept = (p0.dst_rank >= 0)
+    c1 = ctx(W, 1, cf=0.5)
+    p1 = _Plan(skew, E, c1)
+    assert int(kept.sum()) + int((p1.dst_rank >= 0).sum()) == 768      # the sources agree on which slots survive
+    assert int(p0.dst_pos[kept].max()) < 768
+    with pytest.raises(RuntimeError):
+        c0.raise_if_overflow()
+    c0.raise_if_overflow()                                             # cleared after it was reported

@@ -230,7 +230,7 @@ def moe(args) -> dict:
         cfg = cfg.replace(num_layers=args.layers)
     model = create_model(cfg, device=dev, seed=0)
     if world > 1:
-        ep_lib.shard_experts(model, ep_lib.EPContext(device=dev))
+        ep_lib.shard_experts(model, ep_lib.EPContext(device=dev, capacity_factor=args.ep_capacity or None))
     seqs = max(32 // world, 1)
     mb = min(args.micro, seqs)
     tr = PeftTrainer(model, optim.AdamW(2e-5, max_grad_norm=1.0),
@@ -248,6 +248,8 @@ def moe(args) -> dict:
             tr._train_step(b, i == len(batches) - 1)
         e1.record()
         torch.cuda.synchronize()
+        if world > 1:
+            model.dp_shard.raise_if_overflow()
         times.append(e0.elapsed_time(e1) / 1e3)
     sec = _max_over_ranks(float(np.median(times[1:] or times)), dev)
     return {"config": "moe_qwen3_30b_a3b_sft", "n_gpus": world, "layers": cfg.num_layers, "global_batch": seqs * world, "seq_len": 4096,
@@ -262,6 +264,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=64)
     ap.add_argument("--pairs", type=int, default=32)
     ap.add_argument("--micro", type=int, default=4)
+    ap.add_argument("--ep-capacity", type=float, default=0.0, help="moe: fixed-capacity expert-parallel buffers (0 = exact)")
     ap.add_argument("--max-running", type=int, default=256, help="sequences decoded together by the rollout engine")
     args = ap.parse_args(argv)
     res = {"tiny_lora_cpu": tiny_lora_cpu, "grpo": grpo, "dpo": dpo, "moe": moe}[args.config](args)

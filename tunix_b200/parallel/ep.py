@@ -30,8 +30,16 @@ from . import symm
 
 
 class EPContext:
-    def __init__(self, group=None, device=None):
+    """`capacity_factor` (optional): receive buffers hold `capacity_factor x tokens x k` rows (plus one 128-row
+    pad per local expert) instead of the exact count, so the routing plan needs no read-back from the device: no
+    host synchronisation inside the layer. Slots that would land past the capacity are dropped (they contribute
+    nothing, as in capacity-based MoE training) and `overflow` records that it happened; `raise_if_overflow()`
+    reads it (one synchronisation, e.g. once per step)."""
+
+    def __init__(self, group=None, device=None, capacity_factor=None):
         self.group = group
+        self.capacity_factor = capacity_factor
+        self.overflow = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = torch.device(device) if device is not None else (
@@ -39,6 +47,11 @@ class EPContext:
         self.fused = self.world > 1 and self.device.type == "cuda" and symm.symm_available(group)
         self.barrier = symm.SymmBarrier(self.device, group) if self.fused else None
         self._ws: dict = {}
+
+    def raise_if_overflow(self) -> None:
+        if self.overflow is not None and bool(self.overflow.item()):
+            self.overflow = None
+            raise RuntimeError("expert-parallel capacity exceeded: tokens were dropped; raise capacity_factor")
 
     def workspace(self, kind: str, rows: int, D: int) -> symm.SymmBuffer:
         key = (kind, rows, D)
@@ -120,7 +133,15 @@ class _Plan:
         # so that buffers and element-wise kernels cover those rows only: with 8 ranks the worst case is 8 times
         # the expected row count.
         self.max_rows = ((W * T * k + E_loc * 127 + 127) // 128) * 128
-        self.rows = max(128, int(pad2[r].sum().item()))
+        if getattr(ep, "capacity_factor", None):
+            # fixed capacity: nothing is read back. Segments are cut at the capacity, slots past it are dropped.
+            self.rows = min(self.max_rows, ((int(ep.capacity_factor * T * k) + E_loc * 128 + 127) // 128) * 128)
+            over = (pad2.sum(1) > self.rows).any()
+            ep.overflow = over if ep.overflow is None else (ep.overflow | over)
+            kept = pos < self.rows
+            owner = torch.where(kept, owner, torch.full_like(owner, -1))      # dropped slots belong to nobody
+        else:
+            self.rows = max(128, int(pad2[r].sum().item()))
         # this rank as a source: where its slots live
         mine = slice(r * T * k, (r + 1) * T * k)
         self.dst_rank = owner[mine].int().view(T, k).contiguous()
@@ -136,8 +157,9 @@ class _Plan:
             0, self.own_dest, (torch.div(slots, k, rounding_mode="floor") % T).int())[:self.rows].contiguous()
         seg = torch.zeros(E_loc + 1, dtype=torch.int64, device=flat.device)
         seg[1:] = torch.cumsum(pad2[r], 0)
+        seg = seg.clamp(max=self.rows)                                        # (a no-op without a capacity)
         self.seg_off = seg.int()
-        self.counts = counts.view(W, E_loc)[r].int().contiguous()
+        self.counts = torch.minimum(counts.view(W, E_loc)[r], seg[1:] - seg[:-1]).int().contiguous()
         self.T, self.k = T, k
 
 
