@@ -513,3 +513,49 @@ def test_orchestrator_end_to_end_with_worker_failover():
     assert window.committed_prompt_ids | window.skipped_prompt_ids == {f"p{s}_{i}" for s in range(3) for i in range(2)}
     assert workers[1].served >= 19
     orch.close()
+
+
+def test_remote_worker_over_grpc_loopback():
+    """A worker served on 127.0.0.1 behaves like the local object: requests, weight sync with a payload larger
+    than one chunk, remote exceptions, the token check, and registration in the worker registry."""
+    import numpy as np
+    import pytest
+    pytest.importorskip("grpc")
+    from tunix_b200.experimental.common.datatypes import RolloutRequest, WorkerState
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.worker.remote_execution import RemoteError, RemoteWorker, serve_worker
+    from tunix_b200.experimental.worker.rollout_worker import RolloutWorker
+
+    class Out:
+        def __init__(self, toks):
+            self.tokens, self.logprobs, self.text = [toks], [[-0.5] * len(toks)], ["x"]
+    seen = {}
+
+    def engine(prompt_token_ids, max_generation_steps, **kw):
+        if prompt_token_ids[0][0] == 99:
+            raise ValueError("bad prompt")
+        return Out([t + 1 for t in prompt_token_ids[0]][:max_generation_steps])
+    local = RolloutWorker("rollout-7", engine, apply_weights=lambda v, p: seen.update(version=v, nbytes=p["w"].nbytes), eos_tokens=[2])
+    with serve_worker(local, "127.0.0.1:0", token="s3cret") as srv:
+        remote = RemoteWorker(srv.address, token="s3cret")
+        remote.start()
+        assert remote.state == WorkerState.READY and remote.worker_id == "rollout-7" and remote.info().roles == ("rollout",)
+        resp = remote.submit(RolloutRequest("q", [5, 6, 7], max_tokens=2))
+        assert resp.tokens == [6, 7] and resp.request_id == "q" and local.served == 1
+        big = {"w": np.zeros(3 << 20, np.float32)}                    # 12 MB: goes over the chunked call
+        remote.sync_weights(4, big)
+        assert seen == {"version": 4, "nbytes": 12 << 20} and remote.policy_version == 4
+        reg = WorkerRegistry()
+        reg.register(remote)
+        assert [w.worker_id for w in reg.group("rollout")] == ["rollout-7"]
+        with pytest.raises(RemoteError) as ei:
+            remote.submit(RolloutRequest("bad", [99], max_tokens=1))
+        assert isinstance(ei.value.__cause__, ValueError) and remote.state == WorkerState.FAILED
+        with pytest.raises(RemoteError):
+            remote._invoke("_fail", None)                                 # private names are not callable remotely
+        intruder = RemoteWorker(srv.address, token="guess")
+        with pytest.raises(RemoteError) as ei:
+            intruder.info()
+        assert isinstance(ei.value.__cause__, PermissionError)
+        remote.close()
+        intruder.close()

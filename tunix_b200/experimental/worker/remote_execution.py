@@ -1,0 +1,157 @@
+"""Workers behind a gRPC endpoint (tunix/experimental/worker/remote_execution.py, network.py, in miniature).
+
+`serve_worker(worker, address)` exposes a worker object's public methods over one generic unary RPC
+(`/tunix_b200.Worker/Call`); `RemoteWorker(address)` is the proxy the orchestrator registers instead of the
+object itself: `submit`, `sync_weights`, `start`, `stop`, `info`, `state` and any other public method go over the
+wire. Payloads are cloudpickle frames (method name, args, kwargs -> ("ok", value) | ("err", exception)), large
+ones are split into chunks on a client-streaming RPC (`/tunix_b200.Worker/CallChunked`), so a weight payload does
+not have to fit one message.
+
+Unpickling executes code: the endpoint is meant for the private network of one training job. It binds to the
+loopback interface unless told otherwise and takes an optional shared token that every call must carry.
+grpcio and cloudpickle are optional dependencies; importing this module without them raises ImportError."""
+from __future__ import annotations
+
+import hmac
+import threading
+from concurrent import futures
+from typing import Any, Iterator, Optional
+
+import cloudpickle
+import grpc
+
+from ..common.datatypes import WorkerState
+
+_SERVICE = "tunix_b200.Worker"
+_CHUNK = 4 << 20
+_MAX_MSG = 64 << 20
+_OPTS = [("grpc.max_send_message_length", _MAX_MSG), ("grpc.max_receive_message_length", _MAX_MSG)]
+_PRIVATE = ("_",)
+
+
+class RemoteError(RuntimeError):
+    """The remote method raised; `__cause__` is the original exception when it could be pickled."""
+
+
+def _ident(b: bytes) -> bytes:
+    return b
+
+
+class _Servicer:
+    def __init__(self, worker, token: Optional[str]):
+        self.worker, self.token = worker, token
+        self._lock = threading.Lock()
+
+    def _dispatch(self, blob: bytes) -> bytes:
+        try:
+            token, name, args, kwargs = cloudpickle.loads(blob)
+            if self.token is not None and not hmac.compare_digest(str(token or ""), self.token):
+                raise PermissionError("bad or missing token")
+            if name.startswith(_PRIVATE):
+                raise AttributeError(f"{name!r} is not a remote method")
+            attr = getattr(self.worker, name)
+            value = attr(*args, **kwargs) if callable(attr) else attr
+            return cloudpickle.dumps(("ok", value))
+        except BaseException as e:                      # the failure travels back; the server keeps serving
+            try:
+                return cloudpickle.dumps(("err", e))
+            except Exception:
+                return cloudpickle.dumps(("err", RuntimeError(repr(e))))
+
+    def call(self, request: bytes, context) -> bytes:
+        return self._dispatch(request)
+
+    def call_chunked(self, request_iterator: Iterator[bytes], context) -> bytes:
+        return self._dispatch(b"".join(request_iterator))
+
+
+class WorkerServer:
+    def __init__(self, worker, address: str = "127.0.0.1:0", token: Optional[str] = None, max_threads: int = 16):
+        svc = _Servicer(worker, token)
+        self._server = grpc.server(futures.ThreadPoolExecutor(max_workers=max_threads), options=_OPTS)
+        handlers = {
+            "Call": grpc.unary_unary_rpc_method_handler(svc.call, request_deserializer=_ident, response_serializer=_ident),
+            "CallChunked": grpc.stream_unary_rpc_method_handler(svc.call_chunked, request_deserializer=_ident,
+                                                                response_serializer=_ident),
+        }
+        self._server.add_generic_rpc_handlers((grpc.method_handlers_generic_handler(_SERVICE, handlers),))
+        host = address.rsplit(":", 1)[0]
+        self.port = self._server.add_insecure_port(address)
+        if self.port == 0:
+            raise OSError(f"could not bind {address}")
+        self.address = f"{host}:{self.port}"
+        self._server.start()
+
+    def stop(self, grace: float = 1.0) -> None:
+        self._server.stop(grace).wait()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.stop()
+
+
+def serve_worker(worker, address: str = "127.0.0.1:0", token: Optional[str] = None) -> WorkerServer:
+    return WorkerServer(worker, address, token)
+
+
+class RemoteWorker:
+    """Client-side stand-in for a worker served by `serve_worker`. Unknown attributes become remote calls."""
+
+    def __init__(self, address: str, token: Optional[str] = None, timeout: Optional[float] = 600.0):
+        self.address, self._token, self._timeout = address, token, timeout
+        self._channel = grpc.insecure_channel(address, options=_OPTS)
+        self._call = self._channel.unary_unary(f"/{_SERVICE}/Call", request_serializer=_ident, response_deserializer=_ident)
+        self._call_chunked = self._channel.stream_unary(f"/{_SERVICE}/CallChunked", request_serializer=_ident,
+                                                        response_deserializer=_ident)
+        self._info = None
+
+    def _invoke(self, name: str, *args, **kwargs) -> Any:
+        blob = cloudpickle.dumps((self._token, name, args, kwargs))
+        if len(blob) > _CHUNK:
+            reply = self._call_chunked((blob[i:i + _CHUNK] for i in range(0, len(blob), _CHUNK)), timeout=self._timeout)
+        else:
+            reply = self._call(blob, timeout=self._timeout)
+        kind, value = cloudpickle.loads(reply)
+        if kind == "err":
+            raise RemoteError(f"{name} failed on {self.address}: {value!r}") from (value if isinstance(value, BaseException) else None)
+        return value
+
+    # the methods the orchestrator and the registry use, spelled out so that they show up in completion and docs
+    def info(self):
+        if self._info is None:
+            self._info = self._invoke("info")
+        return self._info
+
+    @property
+    def worker_id(self) -> str:
+        return self.info().worker_id
+
+    @property
+    def state(self) -> WorkerState:
+        return self._invoke("state")
+
+    @property
+    def policy_version(self) -> int:
+        return self._invoke("policy_version")
+
+    def start(self) -> None:
+        return self._invoke("start")
+
+    def stop(self) -> None:
+        return self._invoke("stop")
+
+    def submit(self, request: Any) -> Any:
+        return self._invoke("submit", request)
+
+    def sync_weights(self, version: int, payload: Any = None) -> None:
+        return self._invoke("sync_weights", version, payload)
+
+    def __getattr__(self, name: str):
+        if name.startswith("_"):
+            raise AttributeError(name)
+        return lambda *a, **kw: self._invoke(name, *a, **kw)
+
+    def close(self) -> None:
+        self._channel.close()
