@@ -559,3 +559,59 @@ def test_remote_worker_over_grpc_loopback():
         assert isinstance(ei.value.__cause__, PermissionError)
         remote.close()
         intruder.close()
+
+
+def test_orchestrator_with_a_remote_rollout_worker():
+    """The orchestrator drives a rollout worker through its gRPC endpoint exactly as it drives a local one."""
+    import numpy as np
+    import pytest
+    pytest.importorskip("grpc")
+    import torch
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import CacheConfig, TrainingConfig
+    from tunix_b200.experimental.orchestrator.batch_assembly import BatchConfig, create_batch_assembler
+    from tunix_b200.experimental.orchestrator.orchestrator import AlgorithmAdapter, Orchestrator
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.train.peft_trainer_v2 import TrainerV2
+    from tunix_b200.experimental.worker.remote_execution import RemoteWorker, serve_worker
+    from tunix_b200.experimental.worker.rollout_worker import RolloutWorker, TrainerWorker
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer
+    from tunix_b200.sft.utils import LossOutput, WeightedMetric
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+
+    def loss(model, input_tokens, completion_mask, advantages, **_):
+        hidden, _ = model(input_tokens[:, :-1], skip_lm_head=True)
+        lp = model.token_logprobs(hidden.reshape(-1, hidden.shape[-1]), input_tokens[:, 1:].reshape(-1).long())[0]
+        m = completion_mask[:, 1:]
+        return LossOutput(loss=WeightedMetric(-(lp.view(m.shape) * advantages[:, 1:] * m).sum(), m.sum()))
+    trainer = PeftTrainer(model, optim.AdamW(5e-3), TrainingConfig(eval_every_n_steps=10 ** 9, pbar_description=None,
+                                                                   resume_from_checkpoint_on_init=False))
+    trainer.with_loss_fn(loss).with_gen_model_input_fn(
+        lambda b: {k: (torch.as_tensor(v).long() if k == "input_tokens" else torch.as_tensor(v)) for k, v in b.items()})
+    versions = []
+    served = RolloutWorker("rollout-r", Sampler(model, CharTok(), CacheConfig(64, 1, 1, 16)), eos_tokens=[2],
+                           apply_weights=lambda v, p: versions.append(v))
+    with serve_worker(served) as srv:
+        remote = RemoteWorker(srv.address)
+        tw = TrainerWorker("trainer-0", TrainerV2(trainer))
+        remote.start()
+        tw.start()
+        reg = WorkerRegistry()
+        reg.register(remote)
+        reg.register(tw)
+        orch = Orchestrator(reg, create_batch_assembler(BatchConfig(rows_per_microbatch=2, max_prompt_length=8,
+                                                                    max_response_length=8), packed=False),
+                            AlgorithmAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens))), group_size=4,
+                            rollout_params={"max_tokens": 6, "temperature": 1.0})
+        rng = np.random.default_rng(1)
+        rec = orch.step(0, [{"prompt_id": f"p{i}", "prompt_ids": [1] + rng.integers(3, 60, 4).tolist()} for i in range(2)])
+        assert rec["trajectories"] + 4 * rec["filtered_groups"] == 8 and rec["policy_version"] == (1 if rec["microbatches"] else 0)
+        assert served.served == 8 and versions == ([1] if rec["microbatches"] else [])
+        orch.close()
+        remote.close()
