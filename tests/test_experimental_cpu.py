@@ -615,3 +615,31 @@ def test_orchestrator_with_a_remote_rollout_worker():
         assert served.served == 8 and versions == ([1] if rec["microbatches"] else [])
         orch.close()
         remote.close()
+
+
+def test_launcher_starts_worker_processes_and_discovers_them():
+    """Two worker processes come up, announce themselves to the controller's directory, serve requests through
+    their own gRPC endpoints and leave when the controller shuts down."""
+    import pytest
+    pytest.importorskip("grpc")
+    from tunix_b200.experimental.common.datatypes import WorkerState
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.runtime.launcher import Launcher
+    lau = Launcher(token="t0k")
+    try:
+        factory = "tunix_b200.experimental.worker.mock_worker:make_echo_worker"
+        procs = [lau.launch(factory, "rollout-0", scale=2), lau.launch(factory, "trainer-0", role="trainer", scale=3)]
+        entries = lau.wait_for(["rollout-0", "trainer-0"], timeout=120)
+        assert entries["trainer-0"]["roles"] == ("trainer",) and entries["rollout-0"]["address"].startswith("127.0.0.1:")
+        workers = lau.workers()
+        reg = WorkerRegistry()
+        for w in workers.values():
+            reg.register(w)
+        assert [w.worker_id for w in reg.group("rollout")] == ["rollout-0"]
+        assert workers["rollout-0"].submit(21) == 42 and workers["trainer-0"].submit(5) == 15
+        assert workers["rollout-0"].state == WorkerState.READY
+        workers["rollout-0"].sync_weights(3, None)
+        assert workers["rollout-0"].policy_version == 3
+    finally:
+        lau.shutdown()
+    assert all(p.poll() is not None for p in procs)

@@ -29,3 +29,14 @@ class MockWorker(AbstractWorker):
     def _sync_weights(self, version, payload):
         if self.fail_on_sync:
             raise RuntimeError("scripted weight-sync failure")
+
+    def info(self):
+        from ..orchestrator.worker_registry import WorkerInfo
+        return WorkerInfo(self.worker_id, (getattr(self, "role", "mock"),))
+
+
+def make_echo_worker(worker_id: str, role: str = "rollout", scale: int = 1, latency_s: float = 0.0) -> MockWorker:
+    """Factory for process-launch tests and demos: answers a request `x` with `x * scale`."""
+    w = MockWorker(worker_id, handler=lambda r: r * scale, latency_s=latency_s)
+    w.role = role
+    return w
