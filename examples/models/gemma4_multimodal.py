@@ -26,10 +26,7 @@ def main():
                              patch_size=4, position_embedding_size=64, pooling_kernel_size=2, image_token_id=IMG, dtype=dt)
     aud = Gemma4AudioConfig(hidden_size=64, num_layers=2, num_heads=4, subsampling_conv_channels=(16, 8), output_proj_dims=48,
                             audio_token_id=AUD, dtype=dt)
-    model = Gemma4Multimodal(lm, vis, audio_config=aud, device=dev).to(dev)
-    for p in model.parameters():
-        if p.dim() >= 2:
-            torch.nn.init.normal_(p, std=0.05)
+    model = Gemma4Multimodal(lm, vis, audio_config=aud, device=dev).to(dev).init_encoder_weights(seed=0, std=0.05)
     # one 8 x 8-patch image -> 16 soft tokens; 64 mel frames -> 16 audio frames
     pos = torch.tensor([[x, y] for y in range(8) for x in range(8)], device=dev)[None]
     pixels = torch.rand(1, 64, 3 * 4 * 4, device=dev)

@@ -184,3 +184,44 @@ def test_gemma4_audio_tower_matches_huggingface():
     assert torch.equal(valid, out.attention_mask.bool())
     want = out.last_hidden_state
     assert torch.allclose(got[valid], want[valid], atol=3e-4, rtol=2e-3), float((got[valid] - want[valid]).abs().max())
+
+
+def test_gemma4_image_processing_feeds_the_vision_tower():
+    """Aspect-ratio-preserving resize to a patch budget, patch grid positions, padding, placeholder expansion; the
+    processed batch goes through the Gemma-4 multimodal model and the number of soft tokens matches the slots."""
+    import numpy as np
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.gemma4_vision import Gemma4Multimodal, Gemma4VisionConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.processors import image_processor as IP
+    assert IP.get_target_dimensions(480, 640, 16, 10080, 3) == (1344, 1824)          # 84 x 114 = 9576 patches <= 10080
+    assert IP.get_target_dimensions(10, 4000, 16, 90, 3) == (48, 480)                 # the short side keeps one cell
+    assert IP.get_target_dimensions(0, 0, 16, 90, 3) == (48, 48)
+    p, xy = IP.patchify(np.arange(8 * 12 * 3, dtype=np.float32).reshape(8, 12, 3), 4)
+    assert p.shape == (6, 48) and xy.tolist() == [[0, 0], [1, 0], [2, 0], [0, 1], [1, 1], [2, 1]]
+    assert p[4, :3].tolist() == [4 * 12 * 3 + 4 * 3, 4 * 12 * 3 + 4 * 3 + 1, 4 * 12 * 3 + 4 * 3 + 2]   # patch (x=1, y=1) starts at pixel (4, 4)
+    IMG = 120
+    rng = np.random.default_rng(0)
+    wide = (rng.random((40, 90, 3)) * 255).astype(np.uint8)
+    tall = (rng.random((70, 30)) * 255).astype(np.uint8)                                 # grey-scale input
+    toks = [np.asarray([2, 5, IMG, 6, IMG, 7]), np.asarray([2, IMG, 9])]
+    vis, out = IP.process_gemma4_inputs([[wide, tall], [tall]], toks, patch_size=4, max_soft_tokens=16, pooling_kernel_size=2,
+                                        placeholder_token=IMG, start_token=121, end_token=122, double_new_line_token=123)
+    assert vis.patches.shape == (4, 64, 48) and vis.images_per_row == 2 and len(vis.soft_token_counts) == 2
+    assert (vis.positions_xy[3] == -1).all() and float(np.abs(vis.patches[3]).sum()) == 0.0      # the missing image of row 1
+    for cnt, row in zip(vis.soft_token_counts, out):
+        assert int((row == IMG).sum()) == sum(cnt) and int((row == 121).sum()) == len(cnt)
+    real = (vis.positions_xy[..., 0] >= 0).sum(1)
+    assert [int(r) // 4 for r in real[:3]] == list(vis.soft_token_counts[0]) + list(vis.soft_token_counts[1])
+    lm = create_model(Gemma4Config._base(vocab_size=128, embed_dim=64, hidden_dim=96, num_layers=2, num_heads=2, num_kv_heads=1,
+                                         head_dim=16, global_head_dim=32, sliding_window=8, max_position=128,
+                                         layer_pattern=("local", "global"), dtype=torch.float32), seed=0)
+    mm = Gemma4Multimodal(lm, Gemma4VisionConfig(hidden_size=32, intermediate_size=48, num_layers=1, num_heads=2, num_kv_heads=2,
+                                                 head_dim=16, patch_size=4, position_embedding_size=64, pooling_kernel_size=2,
+                                                 image_token_id=IMG, dtype=torch.float32))
+    mm.init_encoder_weights(seed=1, std=0.05)
+    width = max(len(r) for r in out)
+    batch = torch.as_tensor(np.stack([np.pad(r, (0, width - len(r))) for r in out]))
+    with torch.no_grad():
+        logits, _ = mm(batch, pixel_values=torch.as_tensor(vis.patches), pixel_position_ids=torch.as_tensor(vis.positions_xy))
+    assert logits.shape == (2, width, 128) and torch.isfinite(logits).all()

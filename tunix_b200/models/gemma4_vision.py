@@ -239,6 +239,21 @@ class Gemma4Multimodal(nn.Module):
         self.pad_token_id = pad_token_id
         self.config = lm_cfg
 
+    @torch.no_grad()
+    def init_encoder_weights(self, seed: int = 0, std: float = 0.02) -> "Gemma4Multimodal":
+        """Random normal(0, std) matrices for the encoders and their embedders (the decoder has its own
+        `init_weights`); norm scales and position tables keep their constructor values."""
+        mods = [self.vision_tower, self.embed_vision] + ([self.audio_tower, self.embed_audio] if self.audio_config is not None else [])
+        dev = next(self.vision_tower.parameters()).device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        for m in mods:
+            for name, p in m.named_parameters():
+                if p.dim() >= 2 and "position_embedding_table" not in name:
+                    p.normal_(0.0, std, generator=gen)
+                elif name.endswith("bias"):
+                    p.zero_()
+        return self
+
     def encode_images(self, pixel_values, pixel_position_ids):
         soft, valid = self.vision_tower(pixel_values, pixel_position_ids)
         return self.embed_vision(soft), valid
