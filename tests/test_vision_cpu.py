@@ -225,3 +225,35 @@ def test_gemma4_image_processing_feeds_the_vision_tower():
     with torch.no_grad():
         logits, _ = mm(batch, pixel_values=torch.as_tensor(vis.patches), pixel_position_ids=torch.as_tensor(vis.positions_xy))
     assert logits.shape == (2, width, 128) and torch.isfinite(logits).all()
+
+
+def test_sampler_prefills_a_multimodal_prompt():
+    """The dense Sampler passes image inputs to the prefill of a Gemma-4 multimodal model: the first sampled token
+    equals the argmax of a direct forward pass, and changing the image changes the continuation's log-probs."""
+    import numpy as np
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.gemma4_vision import Gemma4Multimodal, Gemma4VisionConfig
+    from tunix_b200.models.transformer import create_model
+    IMG = 120
+    lm = create_model(Gemma4Config._base(vocab_size=128, embed_dim=64, hidden_dim=96, num_layers=4, num_heads=2, num_kv_heads=1,
+                                         head_dim=16, global_head_dim=32, sliding_window=8, max_position=128, per_layer_input_dim=8,
+                                         num_kv_shared_layers=2, layer_pattern=("local", "global"), dtype=torch.float32), seed=0)
+    mm = Gemma4Multimodal(lm, Gemma4VisionConfig(hidden_size=32, intermediate_size=48, num_layers=1, num_heads=2, num_kv_heads=2,
+                                                 head_dim=16, patch_size=4, position_embedding_size=64, pooling_kernel_size=2,
+                                                 image_token_id=IMG, dtype=torch.float32)).init_encoder_weights(seed=2, std=0.2).eval()
+    pos = torch.tensor([[x, y] for y in range(4) for x in range(4)])[None]              # 16 patches -> 4 soft tokens
+    pix = torch.rand(1, 16, 48, generator=torch.Generator().manual_seed(0))
+    prompt = [1, 7, 8] + [IMG] * 4 + [9, 10]
+    toks = torch.tensor([prompt])
+    with torch.no_grad():
+        want = int(mm(toks, pixel_values=pix, pixel_position_ids=pos)[0][0, -1].argmax())
+    sampler = Sampler(mm, CharTok(), CacheConfig(64, 4, 1, 16))
+    out = sampler(prompt_token_ids=[prompt], max_generation_steps=5, max_prompt_length=len(prompt), return_logprobs=True, eos_tokens=[127],
+                  model_inputs={"pixel_values": pix, "pixel_position_ids": pos})
+    assert int(out.tokens[0][0]) == want and len(out.tokens[0]) == 5
+    other = sampler(prompt_token_ids=[prompt], max_generation_steps=5, max_prompt_length=len(prompt), return_logprobs=True, eos_tokens=[127],
+                    model_inputs={"pixel_values": 1.0 - pix, "pixel_position_ids": pos})
+    assert not np.allclose(out.logprobs[0], other.logprobs[0])

@@ -78,7 +78,11 @@ class Sampler(BaseSampler):
                  eos_tokens: Optional[Sequence[int]] = None, forbidden_tokens: Optional[Iterable[int]] = None,
                  temperature: float = 0.0, top_p: Optional[float] = None, top_k: Optional[int] = None,
                  beam_size: Optional[int] = None, seed: Optional[int] = None, pad_output: bool = False, *,
-                 prompt_token_ids: Optional[Sequence[Sequence[int]]] = None) -> SamplerOutput:
+                 prompt_token_ids: Optional[Sequence[Sequence[int]]] = None,
+                 model_inputs: Optional[dict] = None) -> SamplerOutput:
+        """`model_inputs`: extra keyword tensors for the prefill pass of a multimodal model (e.g. `pixel_values`,
+        `pixel_position_ids`, `input_features`): the prompts carry the placeholder tokens, the decode steps are
+        text only (tunix/generate/sampler.py: images / audio hooks)."""
         if (input_strings is None) == (prompt_token_ids is None):
             raise ValueError("give exactly one of input_strings / prompt_token_ids")
         if isinstance(input_strings, str):
@@ -106,7 +110,8 @@ class Sampler(BaseSampler):
         cache = self._model.init_cache(B, total, self.dtype, dev)
         was_training = self._model.training
         self._model.eval()
-        hidden, cache = self._model(toks, positions=positions, cache=cache, segment_ids=seg, skip_lm_head=True)
+        extra = {k: (v.to(dev) if hasattr(v, "to") else v) for k, v in (model_inputs or {}).items()}
+        hidden, cache = self._model(toks, positions=positions, cache=cache, segment_ids=seg, skip_lm_head=True, **extra)
         last_h = hidden[:, -1:]
         next_pos = positions[:, -1:] + 1
         forbidden = torch.as_tensor(sorted(set(forbidden_tokens)), device=dev) if forbidden_tokens else None

@@ -262,11 +262,18 @@ class Gemma4Multimodal(nn.Module):
         frames, valid = self.audio_tower(input_features, input_features_mask)
         return self.embed_audio(frames), valid
 
+    # what the dense `Sampler` asks of its model besides `forward`
+    def init_cache(self, *a, **kw):
+        return self.language_model.init_cache(*a, **kw)
+
+    def compute_final_logits(self, hidden):
+        return self.language_model.compute_final_logits(hidden)
+
     def forward(self, input_tokens, pixel_values=None, pixel_position_ids=None, input_features=None,
-                input_features_mask=None, positions=None, segment_ids=None, skip_lm_head: bool = False, **kw):
+                input_features_mask=None, positions=None, segment_ids=None, skip_lm_head: bool = False, cache=None, **kw):
         lm, vc, ac = self.language_model, self.vision_config, self.audio_config
         if pixel_values is None and input_features is None:
-            return lm(input_tokens, positions=positions, segment_ids=segment_ids, skip_lm_head=skip_lm_head, **kw)
+            return lm(input_tokens, positions=positions, segment_ids=segment_ids, skip_lm_head=skip_lm_head, cache=cache, **kw)
         cfg = lm.config
         B, T = input_tokens.shape
         is_img = input_tokens == vc.image_token_id
@@ -287,7 +294,7 @@ class Gemma4Multimodal(nn.Module):
             spans = torch.where(is_img, torch.cumsum(start.long(), 1), torch.zeros_like(input_tokens, dtype=torch.long))
             pos = torch.arange(T, device=input_tokens.device)
             mask = torch.stack([cache_utils.prefill_mask(pos, pos, bidirectional_span=spans[b]) for b in range(B)])
-        return lm.forward_embeddings(emb, positions=positions, attention_mask=mask, segment_ids=segment_ids,
+        return lm.forward_embeddings(emb, positions=positions, cache=cache, attention_mask=mask, segment_ids=segment_ids,
                                      skip_lm_head=skip_lm_head, per_layer_inputs=ple)
 
     def token_logprobs(self, *a, **kw):
