@@ -257,3 +257,33 @@ def test_sampler_prefills_a_multimodal_prompt():
     other = sampler(prompt_token_ids=[prompt], max_generation_steps=5, max_prompt_length=len(prompt), return_logprobs=True, eos_tokens=[127],
                     model_inputs={"pixel_values": 1.0 - pix, "pixel_position_ids": pos})
     assert not np.allclose(out.logprobs[0], other.logprobs[0])
+
+
+def test_sft_step_on_a_multimodal_batch():
+    """The default SFT loss forwards the image arrays of a batch to a multimodal model; gradients reach the vision
+    encoder and the step changes its weights."""
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.gemma4 import Gemma4Config
+    from tunix_b200.models.gemma4_vision import Gemma4Multimodal, Gemma4VisionConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer
+    IMG = 120
+    lm = create_model(Gemma4Config._base(vocab_size=128, embed_dim=64, hidden_dim=96, num_layers=2, num_heads=2, num_kv_heads=1,
+                                         head_dim=16, global_head_dim=32, sliding_window=8, max_position=64,
+                                         layer_pattern=("local", "global"), dtype=torch.float32), seed=0)
+    mm = Gemma4Multimodal(lm, Gemma4VisionConfig(hidden_size=32, intermediate_size=48, num_layers=1, num_heads=2, num_kv_heads=2,
+                                                 head_dim=16, patch_size=4, position_embedding_size=64, pooling_kernel_size=2,
+                                                 image_token_id=IMG, dtype=torch.float32)).init_encoder_weights(seed=2, std=0.1)
+    tr = PeftTrainer(mm, optim.AdamW(1e-2), TrainingConfig(eval_every_n_steps=10 ** 9, pbar_description=None,
+                                                           resume_from_checkpoint_on_init=False))
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(1, 100, (2, 16), generator=g)
+    toks[:, 2:6] = IMG
+    batch = {"input_tokens": toks, "input_mask": (toks != IMG).float(),
+             "pixel_values": torch.rand(2, 16, 48, generator=g),
+             "pixel_position_ids": torch.tensor([[x, y] for y in range(4) for x in range(4)])[None].expand(2, 16, 2)}
+    before = mm.vision_tower.patch_embedder.input_proj.weight.detach().clone()
+    metric, _, gnorm = tr._train_step(batch, True)
+    assert torch.isfinite(metric.value()) and float(gnorm) > 0
+    assert not torch.equal(before, mm.vision_tower.patch_embedder.input_proj.weight.detach())

@@ -59,13 +59,22 @@ class MetricsBuffer:
         return float(np.mean([float(l) for l in self.losses])) if self.losses else 0.0
 
 
+_MULTIMODAL_KEYS = ("images", "pixel_values", "pixel_position_ids", "input_features", "input_features_mask")
+
+
 def _default_loss_fn(model, input_tokens, input_mask, positions=None, attention_mask=None, segment_ids=None,
-                     **_unused) -> LossOutput:
+                     **extra) -> LossOutput:
     """Next-token NLL: sum_t -log p(x_{t+1}) * mask_{t+1} over sum_t mask_{t+1} (:1197-1230).
 
-    Uses the fused lm_head log-prob path, so [B,T,V] logits are never materialised."""
-    hidden, _ = model(input_tokens, positions=positions, attention_mask=attention_mask, segment_ids=segment_ids,
-                      skip_lm_head=True)
+    Uses the fused lm_head log-prob path, so [B,T,V] logits are never materialised. Image / audio inputs of a
+    batch (`images` of `TrainingInput`, or the Gemma-4 patch and feature arrays) go to a multimodal model's
+    forward; other extra fields are ignored."""
+    mm = {k: v for k, v in extra.items() if k in _MULTIMODAL_KEYS and v is not None}
+    if mm:
+        hidden, _ = model(input_tokens, positions=positions, segment_ids=segment_ids, skip_lm_head=True, **mm)
+    else:
+        hidden, _ = model(input_tokens, positions=positions, attention_mask=attention_mask, segment_ids=segment_ids,
+                          skip_lm_head=True)
     from ..parallel.tp import local_batch   # under tensor parallelism `hidden` covers this rank's sequences only
     targets = local_batch(model, input_tokens)[:, 1:]
     mask = local_batch(model, input_mask)[:, 1:].to(torch.float32)
@@ -109,7 +118,8 @@ class PeftTrainer:
         self.loss_fn: Callable = _default_loss_fn
         self.eval_loss_fn: Callable = _default_loss_fn
         self.gen_model_input_fn: Callable = lambda x: x if isinstance(x, dict) else {
-            "input_tokens": x.input_tokens, "input_mask": x.input_mask}
+            "input_tokens": x.input_tokens, "input_mask": x.input_mask,
+            **({"images": x.images} if getattr(x, "images", None) is not None else {})}
         self._has_aux = False
         self.checkpoint_manager = ckpt_lib.CheckpointManager(training_config.checkpoint_root_directory,
                                                              training_config.checkpointing_options)
