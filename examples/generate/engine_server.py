@@ -3,7 +3,12 @@
     python examples/generate/engine_server.py            (one B200; random-init Qwen3-style model, synthetic prompts)
 
 Every `generate` call is one request with its own token limit; requests join the running batch at the next
-check point (continuous batching). `pause()` / `resume()` bracket an in-place weight update."""
+check point (continuous batching). `pause()` / `resume()` bracket an in-place weight update. With `--http PORT` the
+same server is then put behind the OpenAI-style HTTP front end (`/v1/completions`, `/v1/chat/completions`) until
+interrupted:
+
+    curl -s 127.0.0.1:8000/v1/completions -d '{"prompt": "hello", "max_tokens": 16}'"""
+import argparse
 import time
 from concurrent.futures import ThreadPoolExecutor
 
@@ -34,6 +39,9 @@ class Tok:                      # the engine needs ids for bos / eos / pad and a
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--http", type=int, default=None, help="serve the OpenAI-style routes on this port afterwards")
+    args = ap.parse_args()
     cfg = ModelConfig(family="qwen3", num_layers=4, vocab_size=4096, embed_dim=1024, hidden_dim=3072, num_heads=8, head_dim=128,
                       num_kv_heads=2, qk_norm=True, dtype=torch.bfloat16, max_position=1024)
     model = create_model(cfg, device=torch.device("cuda"), seed=0)
@@ -56,6 +64,15 @@ def main():
         srv.resume()
         toks, lps = srv.generate(prompts[0], 8)
         print("after the weight update:", toks.tolist(), [round(float(x), 3) for x in lps])
+        if args.http is not None:
+            from tunix_b200.generate.openai_server import serve
+            with serve(srv, Tok(), model_name="qwen3-random-init", port=args.http) as http:
+                print("serving on", http.url)
+                try:
+                    while True:
+                        time.sleep(1.0)
+                except KeyboardInterrupt:
+                    pass
 
 
 if __name__ == "__main__":

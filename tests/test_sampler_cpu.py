@@ -174,3 +174,69 @@ def test_engine_server_protocol_on_cpu():
     with pytest.raises(RuntimeError):
         bad.submit([1, 2])
     bad.close()
+
+
+def _http(url, body=None):
+    import json
+    import urllib.error
+    import urllib.request
+    req = urllib.request.Request(url, data=None if body is None else json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=20) as r:
+            return r.status, r.headers.get("Content-Type"), r.read()
+    except urllib.error.HTTPError as e:
+        return e.code, e.headers.get("Content-Type"), e.read()
+
+
+def test_openai_style_http_front_end_over_the_engine_server():
+    """Completions, chat, several prompts in one request, streaming and the error codes, over a real socket on the
+    loop-back interface; the back end is the engine server driven by the scripted engine."""
+    import json
+    from concurrent.futures import ThreadPoolExecutor
+    from tunix_b200.generate.engine import EngineServer
+    from tunix_b200.generate.openai_server import serve
+    tok = CharTok()
+    with EngineServer(_FakeEngine(slots=4), max_new_tokens=6, max_prompt_length=32, eos_tokens=[2]) as eng:
+        with serve(eng, tok, model_name="toy") as http:
+            st, _, raw = _http(http.url + "/health")
+            assert st == 200 and json.loads(raw)["data"][0]["id"] == "toy"
+            last = tok.encode("hello")[-1]
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": "hello", "max_tokens": 3, "logprobs": True})
+            out = json.loads(raw)
+            want = [last + 1, last + 2, last + 3]
+            assert st == 200 and out["object"] == "text_completion"
+            assert out["choices"][0]["text"] == tok.decode(want) and out["choices"][0]["finish_reason"] == "length"
+            assert out["choices"][0]["logprobs"]["tokens"] == want
+            assert out["usage"] == {"prompt_tokens": 5, "completion_tokens": 3, "total_tokens": 8}
+            assert out["sampling"]["temperature"] == 0.0
+            # a list of prompts: one choice each, generated side by side
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": ["ab", "abc", "abcd"], "max_tokens": 2})
+            ch = json.loads(raw)["choices"]
+            assert [c["index"] for c in ch] == [0, 1, 2]
+            assert [c["text"] for c in ch] == [tok.decode([tok.encode(p)[-1] + 1, tok.encode(p)[-1] + 2]) for p in ("ab", "abc", "abcd")]
+            # chat: rendered by the template parser, answered as an assistant message
+            msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+            st, _, raw = _http(http.url + "/v1/chat/completions", {"messages": msgs, "max_tokens": 4})
+            out = json.loads(raw)
+            prompt = http.chat_parser.parse(msgs, add_generation_prompt=True, is_first_msg=True)
+            # the engine keeps the last 32 prompt tokens; the scripted model continues from the last one
+            pl = tok.encode(prompt)[-1]
+            assert st == 200 and out["choices"][0]["message"] == {"role": "assistant", "content": tok.decode([pl + k for k in range(1, 5)])}
+            # streaming: server-sent events ending with [DONE]
+            st, ctype, raw = _http(http.url + "/v1/chat/completions", {"messages": msgs, "max_tokens": 2, "stream": True})
+            events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
+            assert st == 200 and ctype == "text/event-stream" and events[-1] == "[DONE]"
+            assert json.loads(events[0])["choices"][0]["delta"]["content"] == tok.decode([pl + 1, pl + 2])
+            assert json.loads(events[1])["choices"][0]["finish_reason"] == "length"
+            # concurrency on the wire becomes batch width in the engine
+            with ThreadPoolExecutor(8) as ex:
+                res = list(ex.map(lambda i: _http(http.url + "/v1/completions", {"prompt": "x" * (i + 1), "max_tokens": 2}), range(8)))
+            assert all(r[0] == 200 for r in res) and http.requests_served >= 8
+            # errors
+            assert _http(http.url + "/v1/completions", {"prompt": 5})[0] == 400
+            assert _http(http.url + "/v1/completions", {"prompt": "a", "max_tokens": 0})[0] == 400
+            assert _http(http.url + "/v1/chat/completions", {"messages": []})[0] == 400
+            assert _http(http.url + "/v1/nothing", {})[0] == 404 and _http(http.url + "/nothing")[0] == 404
+            eng.close()
+            assert _http(http.url + "/v1/completions", {"prompt": "a"})[0] == 503    # engine gone: unavailable, not a hang

@@ -1,0 +1,217 @@
+"""OpenAI-style HTTP front end of the continuous-batching engine server
+(the role of tunix/experimental/rollout/serve_vllm_sampler.py:54-360 in the reference, which puts FastAPI in front of
+a vLLM sampler).
+
+Routes:
+
+    GET  /health, /v1/models        liveness and the served model's name
+    POST /v1/completions            {"prompt": str | [str], "max_tokens", "stream"}
+    POST /v1/chat/completions       {"messages": [{"role", "content"}], "max_tokens", "stream"}
+
+Every HTTP request becomes one `submit()` on the engine server and joins the running batch at its next check point;
+one handler thread per connection waits for its own future, so concurrency on the wire turns directly into batch
+width on the GPU. Sampling parameters are fixed per engine server (they shape its captured decode step): a request
+whose `temperature` / `top_p` differ from the server's is answered with the server's values, reported back under
+`"sampling"`. `stream: true` answers as server-sent events; the engine delivers a request when it finishes, so the
+stream carries one content chunk, a finish chunk and `[DONE]`.
+
+The back end is anything with `generate(prompt_token_ids, max_tokens) -> (tokens, logprobs)`, i.e.
+`generate.engine.EngineServer`; chat prompts are rendered by a `ChatTemplateParser`. The server is the standard
+library's threaded HTTP server: nothing here needs an event loop."""
+from __future__ import annotations
+
+import json
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Any, Optional, Sequence
+
+
+class _BadRequest(ValueError):
+    pass
+
+
+class OpenAIServer:
+    def __init__(self, backend, tokenizer, *, model_name: str = "tunix-b200", chat_parser=None,
+                 host: str = "127.0.0.1", port: int = 0, request_timeout: Optional[float] = 600.0,
+                 sampling: Optional[dict] = None):
+        """`port=0` picks a free port (read it back from `.port`). `sampling` is echoed to clients."""
+        if chat_parser is None:
+            from ..rl.agentic.parser.chat_template_parser import get_parser
+            chat_parser = get_parser("default", tokenizer)
+        self.backend, self.tokenizer, self.chat_parser = backend, tokenizer, chat_parser
+        self.model_name, self.request_timeout = model_name, request_timeout
+        self.sampling = dict(sampling or {})
+        self.requests_served = 0
+        self._lock = threading.Lock()
+        outer = self
+
+        class Handler(BaseHTTPRequestHandler):
+            protocol_version = "HTTP/1.1"
+
+            def log_message(self, *a):                      # quiet: the engine's own metrics are the record
+                pass
+
+            def do_GET(self):
+                if self.path in ("/health", "/v1/models"):
+                    outer._send_json(self, 200, outer._models())
+                else:
+                    outer._send_json(self, 404, {"error": {"message": f"no route {self.path}", "type": "not_found"}})
+
+            def do_POST(self):
+                try:
+                    n = int(self.headers.get("Content-Length") or 0)
+                    body = json.loads(self.rfile.read(n) or b"{}")
+                    if not isinstance(body, dict):
+                        raise _BadRequest("the request body must be a JSON object")
+                    if self.path == "/v1/completions":
+                        outer._completions(self, body)
+                    elif self.path == "/v1/chat/completions":
+                        outer._chat(self, body)
+                    else:
+                        outer._send_json(self, 404, {"error": {"message": f"no route {self.path}", "type": "not_found"}})
+                except (_BadRequest, json.JSONDecodeError) as e:
+                    outer._send_json(self, 400, {"error": {"message": str(e), "type": "invalid_request_error"}})
+                except TimeoutError as e:
+                    outer._send_json(self, 504, {"error": {"message": f"generation timed out: {e}", "type": "timeout"}})
+                except RuntimeError as e:                   # the engine server is closed or failed
+                    outer._send_json(self, 503, {"error": {"message": str(e), "type": "unavailable"}})
+
+        self._httpd = ThreadingHTTPServer((host, port), Handler)
+        self._httpd.daemon_threads = True
+        self.host, self.port = self._httpd.server_address[:2]
+        self._thread = threading.Thread(target=self._httpd.serve_forever, name="tunix-b200-openai-server", daemon=True)
+        self._thread.start()
+
+    # ------------------------------------------------------------------ plumbing
+    @property
+    def url(self) -> str:
+        return f"http://{self.host}:{self.port}"
+
+    def close(self) -> None:
+        self._httpd.shutdown()
+        self._httpd.server_close()
+        self._thread.join(5.0)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    @staticmethod
+    def _send_json(h, code: int, payload: dict) -> None:
+        data = json.dumps(payload).encode()
+        h.send_response(code)
+        h.send_header("Content-Type", "application/json")
+        h.send_header("Content-Length", str(len(data)))
+        h.end_headers()
+        h.wfile.write(data)
+
+    @staticmethod
+    def _send_sse(h, chunks: Sequence[dict]) -> None:
+        data = b"".join(b"data: " + json.dumps(c).encode() + b"\n\n" for c in chunks) + b"data: [DONE]\n\n"
+        h.send_response(200)
+        h.send_header("Content-Type", "text/event-stream")
+        h.send_header("Cache-Control", "no-cache")
+        h.send_header("Content-Length", str(len(data)))
+        h.end_headers()
+        h.wfile.write(data)
+
+    def _models(self) -> dict:
+        return {"status": "ok", "model": self.model_name, "object": "list",
+                "data": [{"id": self.model_name, "object": "model"}]}
+
+    # ------------------------------------------------------------------ generation
+    def _generate(self, prompt: str, body: dict) -> dict:
+        ids = self.tokenizer.encode(prompt)
+        if not ids:
+            raise _BadRequest("empty prompt")
+        max_tokens = body.get("max_tokens")
+        if max_tokens is not None and (not isinstance(max_tokens, int) or max_tokens < 1):
+            raise _BadRequest("max_tokens must be a positive integer")
+        limit = getattr(self.backend, "max_new_tokens", None)
+        try:
+            toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout)
+        except TypeError:                                   # a back end without the timeout argument
+            toks, lps = self.backend.generate(ids, max_tokens)
+        toks = [int(t) for t in toks]
+        asked = min(max_tokens or limit or len(toks), limit or len(toks))
+        with self._lock:
+            self.requests_served += 1
+        return {"text": self.tokenizer.decode(toks), "tokens": toks, "prompt_tokens": len(ids),
+                "logprobs": [float(x) for x in lps] if body.get("logprobs") and lps is not None else None,
+                "finish_reason": "length" if len(toks) >= asked else "stop"}
+
+    def _usage(self, results: Sequence[dict]) -> dict:
+        p, c = sum(r["prompt_tokens"] for r in results), sum(len(r["tokens"]) for r in results)
+        return {"prompt_tokens": p, "completion_tokens": c, "total_tokens": p + c}
+
+    def _many(self, prompts: Sequence[str], body: dict) -> list:
+        if len(prompts) == 1:
+            return [self._generate(prompts[0], body)]
+        out: list = [None] * len(prompts)                   # several prompts of one request run side by side
+        errs: list = []
+
+        def run(i):
+            try:
+                out[i] = self._generate(prompts[i], body)
+            except BaseException as e:
+                errs.append(e)
+        threads = [threading.Thread(target=run, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errs:
+            raise errs[0]
+        return out
+
+    def _completions(self, h, body: dict) -> None:
+        prompt = body.get("prompt")
+        prompts = [prompt] if isinstance(prompt, str) else prompt
+        if not isinstance(prompts, list) or not prompts or not all(isinstance(p, str) for p in prompts):
+            raise _BadRequest("prompt must be a string or a list of strings")
+        results = self._many(prompts, body)
+        rid, now = "cmpl-" + uuid.uuid4().hex, int(time.time())
+        base = {"id": rid, "object": "text_completion", "created": now, "model": body.get("model") or self.model_name}
+        choices = [{"index": i, "text": r["text"], "finish_reason": r["finish_reason"],
+                    "logprobs": {"token_logprobs": r["logprobs"], "tokens": r["tokens"]} if r["logprobs"] else None}
+                   for i, r in enumerate(results)]
+        if body.get("stream"):
+            self._send_sse(h, [dict(base, choices=[c]) for c in choices])
+        else:
+            self._send_json(h, 200, dict(base, choices=choices, usage=self._usage(results), sampling=self.sampling))
+
+    def _chat(self, h, body: dict) -> None:
+        messages = body.get("messages")
+        if not isinstance(messages, list) or not messages:
+            raise _BadRequest("messages must be a non-empty list")
+        msgs = []
+        for m in messages:
+            if not isinstance(m, dict) or "content" not in m:
+                raise _BadRequest("every message needs a role and a content")
+            msgs.append({"role": m.get("role", "user"), "content": m["content"]})
+        prompt = self.chat_parser.parse(msgs, add_generation_prompt=True, is_first_msg=True)
+        r = self._generate(prompt, body)
+        rid, now = "chatcmpl-" + uuid.uuid4().hex, int(time.time())
+        model = body.get("model") or self.model_name
+        if body.get("stream"):
+            base = {"id": rid, "object": "chat.completion.chunk", "created": now, "model": model}
+            self._send_sse(h, [
+                dict(base, choices=[{"index": 0, "delta": {"role": "assistant", "content": r["text"]}, "finish_reason": None}]),
+                dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": r["finish_reason"]}])])
+            return
+        self._send_json(h, 200, {
+            "id": rid, "object": "chat.completion", "created": now, "model": model,
+            "choices": [{"index": 0, "message": {"role": "assistant", "content": r["text"]},
+                         "finish_reason": r["finish_reason"]}],
+            "usage": self._usage([r]), "sampling": self.sampling})
+
+
+def serve(engine_server, tokenizer, **kwargs: Any) -> OpenAIServer:
+    """Put the HTTP front end on a running `EngineServer`; its sampling parameters are the ones echoed to clients."""
+    t, p, k, seed = getattr(engine_server, "_sampling", (None, None, None, None))
+    kwargs.setdefault("sampling", {"temperature": t, "top_p": p, "top_k": k, "seed": seed})
+    return OpenAIServer(engine_server, tokenizer, **kwargs)
