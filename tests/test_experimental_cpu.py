@@ -643,3 +643,54 @@ def test_launcher_starts_worker_processes_and_discovers_them():
     finally:
         lau.shutdown()
     assert all(p.poll() is not None for p in procs)
+
+
+def test_sql_trajectory_store_converter_and_explorer(tmp_path):
+    import io
+    import numpy as np
+    from tunix_b200.experimental.trajectory import explorer
+    from tunix_b200.experimental.trajectory.store import (FileTrajectoryStore, SqliteTrajectoryStore, new_record,
+                                                          record_from_trajectory)
+    from tunix_b200.rl.agentic.agents.agent_types import Action, Step, Trajectory, TrajectoryStatus
+    db = str(tmp_path / "runs" / "traj.db")
+    st = SqliteTrajectoryStore(db)
+    ids = st.put_many([new_record([{"model_response": f"answer {i}", "reward": i / 4}], reward=i / 4, group_id=f"g{i % 2}",
+                                  policy_version=i // 2) for i in range(6)])
+    assert len(st) == 6 and st.get(ids[3])["steps"][0]["model_response"] == "answer 3"
+    assert [r["reward"] for r in st.query(group_id="g1")] == [0.25, 0.75, 1.25]
+    assert [r["reward"] for r in st.query(min_policy_version=1, min_reward=0.6, max_reward=1.1)] == [0.75, 1.0]
+    assert len(list(st.query(limit=2))) == 2 and next(st.query(newest_first=True, limit=1))["reward"] in (1.25,)
+    assert [r["reward"] for r in st.query(predicate=lambda r: r["reward"] > 1.0)] == [1.25]
+    stats = st.stats()
+    assert stats[0]["count"] == 2 and abs(stats[2]["reward_mean"] - 1.125) < 1e-9 and stats[1]["steps_mean"] == 1.0
+    with pytest.raises(KeyError):
+        st.get("nope")
+    # an agent trajectory with token arrays converts to a record that survives the JSON round trip
+    traj = Trajectory(task={"question": "2+2"}, reward=1.0, status=TrajectoryStatus.SUCCEEDED, steps=[
+        Step(model_response="<think>easy</think> 4", thought="easy", action=Action(action="4"), observation="2+2", reward=1.0,
+             done=True, assistant_tokens=np.array([5, 6, 7]), assistant_masks=np.array([1, 1, 1]), logprobs=np.array([-0.1, -0.2, -0.3]))])
+    rec = record_from_trajectory(traj, group_id="g9", policy_version=3, env="math")
+    tid = st.put(rec)
+    back = st.get(tid)
+    assert back["steps"][0]["assistant_tokens"] == [5, 6, 7] and back["steps"][0]["action"] == "4"
+    assert back["metadata"]["status"] == "SUCCEEDED" and back["metadata"]["env"] == "math" and back["policy_version"] == 3
+    st.close()
+    # the explorer on the SQL store, then exported to JSON lines and explored again
+    out = io.StringIO()
+    assert explorer.main([db, "stats"], out) == 0 and out.getvalue().count("\n") == 5           # header + versions 0, 1, 2, 3
+    out = io.StringIO()
+    assert explorer.main([db, "list", "--min-reward", "1.0"], out) == 0
+    assert out.getvalue().count("\n") == 3 and "answer 5" in out.getvalue()
+    out = io.StringIO()
+    assert explorer.main([db, "show", tid], out) == 0 and "model_response: <think>easy</think> 4" in out.getvalue()
+    assert explorer.main([db, "show", "missing"], io.StringIO()) == 1
+    jl = str(tmp_path / "copy.jsonl")
+    assert explorer.main([db, "export", jl], io.StringIO()) == 0
+    fs = FileTrajectoryStore(jl)
+    assert len(list(fs.read())) == 7
+    fs.close()
+    out = io.StringIO()
+    assert explorer.main([jl, "list", "--group", "g9"], out) == 0 and out.getvalue().count("\n") == 1
+    out1, out2 = io.StringIO(), io.StringIO()
+    explorer.main([jl, "stats"], out1), explorer.main([db, "stats"], out2)
+    assert out1.getvalue() == out2.getvalue()

@@ -124,3 +124,115 @@ def _to_jsonable(o):
     if hasattr(o, "__dict__"):
         return o.__dict__
     return str(o)
+
+
+class SqliteTrajectoryStore:
+    """SQL store (tunix/experimental/trajectory/: the SQL back end): one row per trajectory with the fields that
+    queries filter on as indexed columns and the whole record as JSON. Safe to use from several threads (one
+    connection, one lock); a path of ":memory:" keeps it in RAM."""
+
+    _SCHEMA = ("CREATE TABLE IF NOT EXISTS trajectories (trajectory_id TEXT PRIMARY KEY, group_id TEXT, policy_version INTEGER,"
+               " reward REAL, num_steps INTEGER, created_at REAL, record TEXT NOT NULL);"
+               "CREATE INDEX IF NOT EXISTS idx_group ON trajectories (group_id);"
+               "CREATE INDEX IF NOT EXISTS idx_version ON trajectories (policy_version);")
+
+    def __init__(self, path: str, default=None):
+        import sqlite3
+        if path != ":memory:":
+            os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        self.path = path
+        self._default = default or _to_jsonable
+        self._lock = threading.Lock()
+        self._db = sqlite3.connect(path, check_same_thread=False)
+        self._db.executescript(self._SCHEMA)
+        self._db.commit()
+
+    def put(self, record: dict) -> str:
+        return self.put_many([record])[0]
+
+    def put_many(self, records) -> list:
+        rows = [(r["trajectory_id"], None if r.get("group_id") is None else str(r["group_id"]), int(r.get("policy_version", 0)),
+                 float(r.get("reward", 0.0)), len(r.get("steps") or ()), float(r.get("created_at", time.time())),
+                 json.dumps(r, default=self._default)) for r in records]
+        with self._lock:
+            self._db.executemany("INSERT OR REPLACE INTO trajectories VALUES (?, ?, ?, ?, ?, ?, ?)", rows)
+            self._db.commit()
+        return [r[0] for r in rows]
+
+    def get(self, trajectory_id: str) -> dict:
+        with self._lock:
+            row = self._db.execute("SELECT record FROM trajectories WHERE trajectory_id = ?", (trajectory_id,)).fetchone()
+        if row is None:
+            raise KeyError(trajectory_id)
+        return json.loads(row[0])
+
+    def query(self, predicate: Optional[Callable[[dict], bool]] = None, group_id: Optional[str] = None,
+              min_policy_version: Optional[int] = None, min_reward: Optional[float] = None,
+              max_reward: Optional[float] = None, limit: Optional[int] = None, newest_first: bool = False) -> Iterator[dict]:
+        where, args = [], []
+        for clause, v in (("group_id = ?", None if group_id is None else str(group_id)), ("policy_version >= ?", min_policy_version),
+                          ("reward >= ?", min_reward), ("reward <= ?", max_reward)):
+            if v is not None:
+                where.append(clause)
+                args.append(v)
+        sql = "SELECT record FROM trajectories" + (" WHERE " + " AND ".join(where) if where else "") + \
+              " ORDER BY created_at " + ("DESC" if newest_first else "ASC") + ", rowid"
+        if limit is not None and predicate is None:
+            sql += f" LIMIT {int(limit)}"
+        with self._lock:
+            rows = self._db.execute(sql, args).fetchall()
+        n = 0
+        for (raw,) in rows:
+            r = json.loads(raw)
+            if predicate is None or predicate(r):
+                yield r
+                n += 1
+                if limit is not None and n >= limit:
+                    return
+
+    def stats(self) -> dict:
+        """Per policy version: count, mean / min / max reward, mean number of steps."""
+        with self._lock:
+            rows = self._db.execute("SELECT policy_version, COUNT(*), AVG(reward), MIN(reward), MAX(reward), AVG(num_steps)"
+                                    " FROM trajectories GROUP BY policy_version ORDER BY policy_version").fetchall()
+        return {int(v): {"count": int(c), "reward_mean": a, "reward_min": lo, "reward_max": hi, "steps_mean": s}
+                for v, c, a, lo, hi, s in rows}
+
+    def __len__(self) -> int:
+        with self._lock:
+            return int(self._db.execute("SELECT COUNT(*) FROM trajectories").fetchone()[0])
+
+    def flush(self) -> None:
+        with self._lock:
+            self._db.commit()
+
+    def close(self) -> None:
+        with self._lock:
+            self._db.commit()
+            self._db.close()
+
+
+def record_from_trajectory(traj, group_id=None, policy_version: int = 0, **metadata) -> dict:
+    """Convert an agent `Trajectory` (rl/agentic/agents/agent_types.py) to a store record: per step the model's
+    response, the parsed action, the observation, reward and the token-level arrays when they were kept."""
+    steps = []
+    for s in getattr(traj, "steps", ()):
+        act = getattr(s, "action", None)
+        step = {"model_response": getattr(s, "model_response", ""), "thought": getattr(s, "thought", ""),
+                "action": getattr(act, "action", act), "observation": getattr(s, "observation", None),
+                "reward": float(getattr(s, "reward", 0.0)), "done": bool(getattr(s, "done", False)),
+                "mc_return": float(getattr(s, "mc_return", 0.0))}
+        for k in ("assistant_tokens", "assistant_masks", "env_tokens", "env_masks", "logprobs"):
+            v = getattr(s, k, None)
+            if v is not None:
+                step[k] = v
+        steps.append(step)
+    status = getattr(traj, "status", None)
+    rec = new_record(steps, reward=float(getattr(traj, "reward", 0.0)), group_id=group_id, policy_version=policy_version,
+                     status=getattr(status, "name", status), task=getattr(traj, "task", None), **metadata)
+    return rec
+
+
+def open_store(path: str):
+    """Open a store by file type: `.db` / `.sqlite` -> SQL, anything else -> JSON lines."""
+    return SqliteTrajectoryStore(path) if path.endswith((".db", ".sqlite", ".sqlite3")) else FileTrajectoryStore(path)
