@@ -694,3 +694,54 @@ def test_sql_trajectory_store_converter_and_explorer(tmp_path):
     out1, out2 = io.StringIO(), io.StringIO()
     explorer.main([jl, "stats"], out1), explorer.main([db, "stats"], out2)
     assert out1.getvalue() == out2.getvalue()
+
+
+def test_routing_pool_sticky_keys_failover_and_round_robin():
+    import subprocess
+    import sys
+    from concurrent.futures import ThreadPoolExecutor
+    from tunix_b200.experimental.worker.routing import NoWorkerAvailable, RoutingPool, stable_route_hash
+
+    class W:
+        def __init__(self, name):
+            self.name, self.fail, self.seen = name, False, []
+
+        def submit(self, req):
+            if self.fail:
+                raise ConnectionError(self.name)
+            self.seen.append(req.get("route_key"))
+            return self.name
+
+    ws = {f"w{i}": W(f"w{i}") for i in range(4)}
+    pool = RoutingPool(ws)
+    keys = [f"conv-{i}" for i in range(200)]
+    first = {k: pool.submit({"route_key": k}) for k in keys}
+    assert all(pool.submit({"route_key": k}) == first[k] for k in keys)                    # sticky
+    assert min(sum(v == n for v in first.values()) for n in ws) >= 25                      # and spread (50 each expected)
+    # the digest does not depend on the process (Python's hash() does)
+    other = subprocess.run([sys.executable, "-c", "from tunix_b200.experimental.worker.routing import stable_route_hash as h;"
+                            "print(h('conv-7', 'w1'))"], capture_output=True, text=True, check=True).stdout.strip()
+    assert int(other) == stable_route_hash("conv-7", "w1")
+    # a worker fails: its keys move, nobody else's do
+    ws["w2"].fail = True
+    second = {k: pool.submit({"route_key": k}) for k in keys}
+    assert all(second[k] == first[k] for k in keys if first[k] != "w2") and "w2" not in second.values()
+    assert pool.stats()["w2"]["down"] and pool.live() == ["w0", "w1", "w3"]
+    ws["w2"].fail = False
+    pool.mark_up("w2")
+    assert all(pool.submit({"route_key": k}) == first[k] for k in keys)                    # and come back
+    # no key: round robin over the live workers
+    before = {n: s["served"] for n, s in pool.stats().items()}
+    with ThreadPoolExecutor(4) as ex:
+        list(ex.map(lambda i: pool.submit({"i": i}), range(40)))
+    gained = {n: pool.stats()[n]["served"] - before[n] for n in ws}
+    assert sum(gained.values()) == 40 and min(gained.values()) >= 5
+    # a custom router wins over the key; everything down is an error, not a hang
+    routed = RoutingPool(ws, router=lambda req, names: "w3" if req.get("big") else None)
+    assert routed.submit({"big": True, "route_key": "conv-1"}) == "w3"
+    for w in ws.values():
+        w.fail = True
+    with pytest.raises(NoWorkerAvailable):
+        pool.submit({"route_key": "x"})
+    with pytest.raises(NoWorkerAvailable):
+        pool.submit({"route_key": "x"})                                                    # now nobody is live

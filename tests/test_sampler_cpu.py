@@ -240,3 +240,30 @@ def test_openai_style_http_front_end_over_the_engine_server():
             assert _http(http.url + "/v1/nothing", {})[0] == 404 and _http(http.url + "/nothing")[0] == 404
             eng.close()
             assert _http(http.url + "/v1/completions", {"prompt": "a"})[0] == 503    # engine gone: unavailable, not a hang
+
+
+def test_openai_front_end_routes_conversations_over_several_engines():
+    import json
+    from tunix_b200.generate.engine import EngineServer
+    from tunix_b200.generate.openai_server import OpenAIServer, PooledBackend
+    tok = CharTok()
+    engines = {f"gpu{i}": EngineServer(_FakeEngine(slots=2), max_new_tokens=4, max_prompt_length=16, eos_tokens=[2]) for i in range(3)}
+    try:
+        back = PooledBackend(engines)
+        with OpenAIServer(back, tok, model_name="toy") as http:
+            for conv in ("a", "b", "c", "d", "e"):
+                owner = back.pool.owner(conv)
+                before = engines[owner].admitted
+                for turn in range(3):
+                    st, _, raw = _http(http.url + "/v1/completions", {"prompt": "hi" * (turn + 1), "max_tokens": 2, "route_key": conv})
+                    assert st == 200 and len(json.loads(raw)["choices"][0]["text"]) == 2
+                assert engines[owner].admitted == before + 3                     # every turn reached the same engine
+            for _ in range(6):                                                   # no key: spread over the engines
+                assert _http(http.url + "/v1/completions", {"prompt": "x", "max_tokens": 1})[0] == 200
+            assert all(s["served"] >= 2 for s in back.pool.stats().values())
+            for e in engines.values():
+                e.close()
+            assert _http(http.url + "/v1/completions", {"prompt": "x"})[0] == 503
+    finally:
+        for e in engines.values():
+            e.close()

@@ -65,6 +65,8 @@ class OpenAIServer:
                     body = json.loads(self.rfile.read(n) or b"{}")
                     if not isinstance(body, dict):
                         raise _BadRequest("the request body must be a JSON object")
+                    if body.get("route_key") is None and self.headers.get("x-route-key"):
+                        body["route_key"] = self.headers.get("x-route-key")
                     if self.path == "/v1/completions":
                         outer._completions(self, body)
                     elif self.path == "/v1/chat/completions":
@@ -132,10 +134,13 @@ class OpenAIServer:
         if max_tokens is not None and (not isinstance(max_tokens, int) or max_tokens < 1):
             raise _BadRequest("max_tokens must be a positive integer")
         limit = getattr(self.backend, "max_new_tokens", None)
-        try:
-            toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout)
-        except TypeError:                                   # a back end without the timeout argument
-            toks, lps = self.backend.generate(ids, max_tokens)
+        if getattr(self.backend, "routes", False):          # several engines: the key keeps a conversation on one of them
+            toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout, route_key=body.get("route_key"))
+        else:
+            try:
+                toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout)
+            except TypeError:                               # a back end without the timeout argument
+                toks, lps = self.backend.generate(ids, max_tokens)
         toks = [int(t) for t in toks]
         asked = min(max_tokens or limit or len(toks), limit or len(toks))
         with self._lock:
@@ -208,6 +213,26 @@ class OpenAIServer:
             "choices": [{"index": 0, "message": {"role": "assistant", "content": r["text"]},
                          "finish_reason": r["finish_reason"]}],
             "usage": self._usage([r]), "sampling": self.sampling})
+
+
+class PooledBackend:
+    """Several engine servers (one per GPU or per replica) behind one front end. A request's `route_key` (JSON field
+    or `x-route-key` header; the reference's server takes the same two, serve_vllm_sampler.py:229) pins it to one
+    engine through `experimental.worker.routing.RoutingPool`; requests without a key go to the least loaded engine."""
+    routes = True
+
+    def __init__(self, engines: dict):
+        from ..experimental.worker.routing import RoutingPool
+        self.engines = dict(engines)
+        self.pool = RoutingPool(self.engines, call=lambda e, r: e.generate(r["ids"], r["max_tokens"], timeout=r["timeout"]))
+        limits = [getattr(e, "max_new_tokens", None) for e in self.engines.values()]
+        self.max_new_tokens = min(x for x in limits if x is not None) if any(x is not None for x in limits) else None
+
+    def generate(self, ids, max_tokens=None, timeout=None, route_key=None):
+        try:
+            return self.pool.submit({"ids": ids, "max_tokens": max_tokens, "timeout": timeout, "route_key": route_key})
+        except Exception as e:
+            raise RuntimeError(str(e)) from e
 
 
 def serve(engine_server, tokenizer, **kwargs: Any) -> OpenAIServer:
