@@ -328,3 +328,28 @@ def test_engine_server_mode_joins_requests_and_pauses_for_weight_updates():
     assert eng.pool.free_pages == eng.pool.num_pages
     with pytest.raises(RuntimeError):
         srv.submit([1, 2, 3])
+
+
+def test_tiered_page_pool_round_trip_on_device():
+    """Pages offloaded to pinned host memory and loaded back keep their contents, on the pool's own stream, while
+    the pools adopted are plain device tensors like the engine's K / V page pools."""
+    from tunix_b200.experimental.generate.tiered_page_pool import PageLocation, TieredPagePool
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pools = {n: torch.randn(16, 64, 2, 128, device=dev, generator=g).to(torch.bfloat16) for n in ("k", "v")}
+    pool = TieredPagePool(["k", "v"], (64, 2, 128), torch.bfloat16, 16, 8, device=dev, device_pages=pools)
+    ids = pool.allocate_device_pages(16)
+    want = {n: {p: pools[n][pool.page_idx(p)].clone() for p in ids} for n in pools}
+    out = ids[2:10]
+    pool.offload(out)
+    assert pool.num_free_device_pages == 8 and all(pool.page_location(p) is PageLocation.HOST for p in out)
+    assert pool.host["k"].is_pinned()
+    for n in pools:                                         # the freed slots get overwritten before the pages return
+        pools[n][torch.tensor([i for i in range(16) if i not in pool.device_indices([p for p in ids if p not in out])],
+                              device=dev)] = 0
+    pool.load(out[::-1])
+    torch.cuda.synchronize()
+    for n in pools:
+        for p in ids:
+            assert torch.equal(pools[n][pool.page_idx(p)], want[n][p]), (n, p)
+    assert pool.bytes_offloaded == pool.bytes_loaded == 8 * 2 * 64 * 2 * 128 * 2

@@ -745,3 +745,49 @@ def test_routing_pool_sticky_keys_failover_and_round_robin():
         pool.submit({"route_key": "x"})
     with pytest.raises(NoWorkerAvailable):
         pool.submit({"route_key": "x"})                                                    # now nobody is live
+
+
+def test_tiered_page_pool_moves_pages_between_device_and_host():
+    import torch
+    from tunix_b200.experimental.generate.tiered_page_pool import PageLocation, TieredPagePool, TieredPoolError
+    pool = TieredPagePool(["k", "v"], page_shape=(4, 2, 8), dtype=torch.float32, num_device_pages=4, num_host_pages=3)
+    ids = pool.allocate_device_pages(4)
+    assert pool.num_free_device_pages == 0 and sorted(pool.device_indices(ids)) == [0, 1, 2, 3]
+    for p in ids:                                           # a recognisable pattern per logical page and partition
+        pool.dev["k"][pool.page_idx(p)] = float(p + 1)
+        pool.dev["v"][pool.page_idx(p)] = -float(p + 1)
+    with pytest.raises(TieredPoolError):
+        pool.allocate_device_pages(1)
+    pool.offload([ids[1], ids[3]])
+    assert pool.page_location(ids[1]) is PageLocation.HOST and pool.num_free_device_pages == 2 and pool.num_free_host_pages == 1
+    assert float(pool.host["k"][pool.page_idx(ids[3])].mean()) == ids[3] + 1
+    with pytest.raises(TieredPoolError, match="load it first"):
+        pool.device_indices(ids)
+    more = pool.allocate_device_pages(2)                    # the freed device slots are reused...
+    for p in more:
+        pool.dev["k"][pool.page_idx(p)] = 100.0 + p
+        pool.dev["v"][pool.page_idx(p)] = -100.0 - p
+    with pytest.raises(TieredPoolError):                    # ...so nothing fits until something else leaves
+        pool.load([ids[1]])
+    assert pool.page_location(ids[1]) is PageLocation.HOST  # a refused move changes nothing
+    pool.offload([more[0]])
+    with pytest.raises(TieredPoolError):                    # the host tier is full now: 3 pages
+        pool.offload([more[1]])
+    pool.free([more[1]])
+    pool.load([ids[1]])
+    assert pool.page_location(ids[1]) is PageLocation.DEVICE
+    assert float(pool.dev["k"][pool.page_idx(ids[1])].mean()) == ids[1] + 1 and float(pool.dev["v"][pool.page_idx(ids[1])].mean()) == -(ids[1] + 1)
+    assert float(pool.dev["k"][pool.page_idx(ids[0])].mean()) == ids[0] + 1                 # untouched neighbours
+    page_bytes = 4 * 2 * 8 * 4 * 2
+    assert pool.bytes_offloaded == 3 * page_bytes and pool.bytes_loaded == page_bytes
+    with pytest.raises(TieredPoolError):
+        pool.offload([ids[3]])                              # already on the host
+    with pytest.raises(TieredPoolError):
+        pool.free([ids[0], ids[0]])
+    with pytest.raises(TieredPoolError):
+        pool.free([12345])
+    pool.free([ids[0], ids[1], ids[2], ids[3], more[0]])
+    assert pool.num_free_device_pages == 4 and pool.num_free_host_pages == 3
+    # adopting existing pools checks their geometry
+    with pytest.raises(ValueError):
+        TieredPagePool(["k"], (4, 2, 8), torch.float32, 4, 2, device_pages={"k": torch.zeros(3, 4, 2, 8)})
