@@ -791,3 +791,61 @@ def test_tiered_page_pool_moves_pages_between_device_and_host():
     # adopting existing pools checks their geometry
     with pytest.raises(ValueError):
         TieredPagePool(["k"], (4, 2, 8), torch.float32, 4, 2, device_pages={"k": torch.zeros(3, 4, 2, 8)})
+
+
+def test_lifecycle_driver_and_startup_validation():
+    import types
+    from tunix_b200.experimental.common.datatypes import WorkerState
+    from tunix_b200.experimental.orchestrator.lifecycle import LifecycleDriver, LifecycleError
+    from tunix_b200.experimental.orchestrator.startup_validation import (RegistryValidator, StartupValidationError,
+                                                                         validate_startup)
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.worker.mock_worker import MockWorker, make_echo_worker
+
+    def registry(*workers):
+        reg = WorkerRegistry()
+        for w in workers:
+            reg.register(w)
+        return reg
+
+    good = [make_echo_worker("r0"), make_echo_worker("r1"), make_echo_worker("t0", role="trainer")]
+    reg = registry(*good)
+    drv = LifecycleDriver(reg)
+    drv.bring_up()
+    assert all(w.state == WorkerState.READY for w in good)
+    drv.shutdown()
+    assert all(w.state == WorkerState.STOPPED for w in good)
+    # one worker fails to initialise: the others are stopped again and the error names the failure
+    ok1, ok2 = make_echo_worker("a"), make_echo_worker("c")
+    bad = MockWorker("b", fail_on_init=True)
+    bad.role = "rollout"
+    with pytest.raises(LifecycleError, match="b: RuntimeError") as ei:
+        LifecycleDriver(registry(ok1, bad, ok2)).bring_up()
+    assert [wid for wid, _ in ei.value.failures] == ["b"] and ei.value.phase == "bring_up"
+    assert ok1.state == WorkerState.STOPPED and ok2.state == WorkerState.STOPPED and bad.state == WorkerState.FAILED
+    # shutdown is best effort and reports every worker that could not be stopped
+    s1, s2 = make_echo_worker("s1"), make_echo_worker("s2")
+    reg2 = registry(s1, s2)
+    LifecycleDriver(reg2).bring_up()
+    s1._drain = lambda: (_ for _ in ()).throw(OSError("stuck"))
+    with pytest.raises(LifecycleError, match="shutdown failed on 1 worker") as ei:
+        LifecycleDriver(reg2).shutdown()
+    assert ei.value.failures[0][0] == "s1" and s2.state == WorkerState.STOPPED
+    # startup validation gathers every problem in one error
+    alg = types.SimpleNamespace(num_generations=4, algo_variant="grpo", max_response_length=256)
+    tc = types.SimpleNamespace(mini_batch_size=16, train_micro_batch_size=4, rollout_micro_batch_size=8, compute_logps_micro_batch_size=None)
+    validate_startup(reg, alg, tc)
+    alg_bad = types.SimpleNamespace(num_generations=1, algo_variant="grpo", max_response_length=0)
+    tc_bad = types.SimpleNamespace(mini_batch_size=10, train_micro_batch_size=4, rollout_micro_batch_size=True, compute_logps_micro_batch_size=5)
+    with pytest.raises(StartupValidationError) as ei:
+        validate_startup(registry(make_echo_worker("only")), alg_bad, tc_bad)
+    msgs = "\n".join(ei.value.errors)
+    for part in ("max_response_length must be a positive integer", "not divisible by train_micro_batch_size 4",
+                 "rollout_micro_batch_size must be a positive integer", "num_generations must be > 1 for 'grpo'",
+                 "role 'trainer': 0 worker(s) registered, 1 needed"):
+        assert part in msgs, part
+    assert "compute_logps_micro_batch_size 5" not in msgs                    # 10 % 5 == 0
+    tc_pack = types.SimpleNamespace(mini_batch_size=16, train_micro_batch_size=3, sequence_packing=True)
+    validate_startup(reg, alg, tc_pack)                                       # token-sized micro-batches need not divide
+    with pytest.raises(StartupValidationError, match="2 needed"):
+        validate_startup(reg, alg, tc, validators=[RegistryValidator(min_counts={"trainer": 2})])
