@@ -849,3 +849,47 @@ def test_lifecycle_driver_and_startup_validation():
     validate_startup(reg, alg, tc_pack)                                       # token-sized micro-batches need not divide
     with pytest.raises(StartupValidationError, match="2 needed"):
         validate_startup(reg, alg, tc, validators=[RegistryValidator(min_counts={"trainer": 2})])
+
+
+def test_algorithm_adapters_grpo_variants_and_ppo_gae():
+    import numpy as np
+    import torch
+    from tunix_b200.experimental.common.datatypes import RolloutResponse
+    from tunix_b200.experimental.orchestrator.algorithm_adapter import GRPOAdapter, PPOAdapter
+    from tunix_b200.experimental.orchestrator.batch_assembly import BatchConfig, create_batch_assembler
+    item = {"prompt_ids": [1, 5, 6], "prompt_id": "p0"}
+    resp = [RolloutResponse(f"p0/{i}", tokens=list(range(10, 10 + n)), logprobs=[-0.5] * n, group_id="p0", policy_version=2)
+            for i, n in enumerate((2, 4, 3, 1))]
+    reward = lambda it, r: float(len(r.tokens))
+    r = np.array([2, 4, 3, 1], np.float32)
+    g = GRPOAdapter(reward).create_payloads(item, resp)
+    np.testing.assert_allclose([p.example["advantages"][0] for p in g], (r - r.mean()) / (r.std() + 1e-6), rtol=1e-5)
+    assert all(len(p.example["advantages"]) == len(p.example["completion_ids"]) for p in g) and g[1].policy_version == 2
+    d = GRPOAdapter(reward, estimator="drgrpo").create_payloads(item, resp)
+    np.testing.assert_allclose([p.example["advantages"][0] for p in d], r - r.mean(), rtol=1e-6)
+    l = GRPOAdapter(reward, estimator="rloo").create_payloads(item, resp)
+    np.testing.assert_allclose([p.example["advantages"][0] for p in l], r - (r.sum() - r) / 3, rtol=1e-6)
+    assert GRPOAdapter(lambda it, rr: 1.0).create_payloads(item, resp) == []            # uniform group: nothing to learn
+    # PPO: reward on the last token, KL charged per token, GAE over the response; compare with the recurrence
+    values = lambda p, c: [0.1 * (k + 1) for k in range(len(c))]
+    ref = lambda p, c: [-0.7] * len(c)
+    ppo = PPOAdapter(reward, values, ref_logps_fn=ref, gamma=0.9, gae_lambda=0.8, kl_coef=0.5, whiten=False)
+    out = ppo.create_payloads(item, resp)
+    for p, rr in zip(out, resp):
+        n = len(rr.tokens)
+        rew = np.full(n, -0.5 * (-0.5 + 0.7), np.float32)
+        rew[-1] += n
+        v = np.array(values(None, rr.tokens), np.float32)
+        adv, last = np.zeros(n, np.float32), 0.0
+        for t in range(n - 1, -1, -1):
+            nv = v[t + 1] if t + 1 < n else 0.0
+            last = rew[t] + 0.9 * nv - v[t] + 0.9 * 0.8 * last
+            adv[t] = last
+        np.testing.assert_allclose(p.example["advantages"], adv, rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(p.example["returns"], adv + v, rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(p.example["values"], v)
+    # the assembler carries the per-token PPO fields into the micro-batch
+    asm = create_batch_assembler(BatchConfig(rows_per_microbatch=4, max_prompt_length=4, max_response_length=4), packed=False)
+    batches = list(asm.feed(out)) + list(asm.flush())
+    assert len(batches) == 1 and {"returns", "values", "old_per_token_logps"} <= set(batches[0].arrays)
+    assert batches[0].arrays["returns"].shape == batches[0].arrays["advantages"].shape

@@ -84,6 +84,8 @@ class Orchestrator:
         return list(self._pool.map(self._one_rollout, reqs))
 
     def _payloads(self, item: dict, responses: Sequence) -> list:
+        if hasattr(self.adapter, "create_payloads"):        # algorithm_adapter.GRPOAdapter / PPOAdapter
+            return self.adapter.create_payloads(item, responses)
         rewards = np.asarray([self.adapter.reward_fn(item, r) for r in responses], np.float32)
         if self.adapter.drop_uniform_groups and float(rewards.std()) == 0.0:
             return []
