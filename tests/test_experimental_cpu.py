@@ -893,3 +893,63 @@ def test_algorithm_adapters_grpo_variants_and_ppo_gae():
     batches = list(asm.feed(out)) + list(asm.flush())
     assert len(batches) == 1 and {"returns", "values", "old_per_token_logps"} <= set(batches[0].arrays)
     assert batches[0].arrays["returns"].shape == batches[0].arrays["advantages"].shape
+
+
+def test_deployments_local_processes_and_jobset_manifest():
+    """The same role specs start local worker processes or render a Kubernetes JobSet; a pod-style worker (own
+    bind / advertised address, no parent pipe) runs until it is terminated and withdraws from the directory."""
+    import signal
+    import subprocess
+    import sys
+    import time
+    import yaml
+    pytest.importorskip("grpc")
+    from tunix_b200.experimental.runtime.deployment import LocalDeployment, RoleSpec, jobset_manifest, to_yaml
+    from tunix_b200.experimental.runtime.launcher import Launcher
+    factory = "tunix_b200.experimental.worker.mock_worker:make_echo_worker"
+    roles = [RoleSpec("rollout", factory, replicas=2, gpus_per_worker=1, args={"scale": 2}),
+             RoleSpec("trainer", factory, replicas=1, gpus_per_worker=8, args={"scale": 5}, env={"NCCL_NVLS_ENABLE": 0})]
+    dep = LocalDeployment(roles, token="s3")
+    try:
+        workers = dep.start(timeout=120)
+        assert sorted(workers) == ["rollout-0", "rollout-1", "trainer-0"]
+        assert workers["rollout-1"].submit(4) == 8 and workers["trainer-0"].submit(4) == 20
+        assert workers["trainer-0"].info().roles == ("trainer",)
+    finally:
+        dep.shutdown()
+    man = yaml.safe_load(to_yaml(jobset_manifest("grpo-run", "registry.local/tunix-b200:1", roles,
+                                                 directory_address="controller.default.svc:4000", token_secret="run-token",
+                                                 node_selector={"gpu": "b200"})))
+    assert man["kind"] == "JobSet" and [j["name"] for j in man["spec"]["replicatedJobs"]] == ["rollout", "trainer"]
+    rj, tj = (j["template"]["spec"] for j in man["spec"]["replicatedJobs"])
+    assert rj["parallelism"] == rj["completions"] == 2 and rj["completionMode"] == "Indexed"
+    tc = tj["template"]["spec"]["containers"][0]
+    assert tc["resources"]["limits"]["nvidia.com/gpu"] == 8 and tj["template"]["spec"]["nodeSelector"] == {"gpu": "b200"}
+    cmd = tc["command"]
+    assert cmd[cmd.index("--worker-id") + 1] == "trainer-$(JOB_COMPLETION_INDEX)" and "--stay" in cmd
+    assert cmd[cmd.index("--advertise") + 1] == "$(POD_IP):50051" and cmd[cmd.index("--token") + 1] == "$(TUNIX_B200_TOKEN)"
+    assert {"name": "NCCL_NVLS_ENABLE", "value": "0"} in tc["env"] and "scale=5" in cmd
+    assert any(e.get("valueFrom", {}).get("secretKeyRef", {}).get("name") == "run-token" for e in tc["env"])
+    with pytest.raises(ValueError, match="DNS label"):
+        jobset_manifest("Bad_Name", "img", roles, directory_address="x:1")
+    # a pod-style worker: explicit bind and advertised addresses, leaves on SIGTERM
+    lau = Launcher(token="s3")
+    proc = None
+    try:
+        proc = subprocess.Popen([sys.executable, "-m", "tunix_b200.experimental.runtime.launcher", "--factory", factory,
+                                 "--worker-id", "rollout-7", "--directory", lau.address, "--token", "s3", "--bind", "127.0.0.1:0",
+                                 "--stay", "--arg", "scale=3"], stdin=subprocess.DEVNULL)
+        lau._procs["rollout-7"] = proc
+        lau.wait_for(["rollout-7"], timeout=120)
+        assert lau.workers()["rollout-7"].submit(5) == 15               # stdin at end of file did not end it
+        proc.send_signal(signal.SIGTERM)
+        assert proc.wait(30) == 0
+        deadline = time.time() + 5
+        while "rollout-7" in lau.directory.entries() and time.time() < deadline:
+            time.sleep(0.05)
+        assert "rollout-7" not in lau.directory.entries()
+    finally:
+        if proc is not None and proc.poll() is None:
+            proc.kill()
+        lau._procs.clear()
+        lau.shutdown()

@@ -106,6 +106,10 @@ def _parse_args(argv):
     ap.add_argument("--directory", required=True)
     ap.add_argument("--token", default=None)
     ap.add_argument("--arg", action="append", default=[])
+    ap.add_argument("--bind", default="127.0.0.1:0", help="address the worker serves on (0.0.0.0:PORT inside a pod)")
+    ap.add_argument("--advertise", default=None, help="address announced to the directory (POD_IP:PORT inside a pod)")
+    ap.add_argument("--stay", action="store_true", help="run until SIGTERM / SIGINT instead of until stdin closes "
+                    "(a pod has no controlling parent holding a pipe)")
     return ap.parse_args(argv)
 
 
@@ -123,12 +127,19 @@ def main(argv=None) -> int:
     mod, fn = a.factory.split(":")
     factory = getattr(importlib.import_module(mod), fn)
     worker = factory(worker_id=a.worker_id, **{k: _coerce(v) for k, v in (kv.split("=", 1) for kv in a.arg)})
-    server = serve_worker(worker, "127.0.0.1:0", a.token)
+    server = serve_worker(worker, a.bind, a.token)
     worker.start()
     directory = RemoteWorker(a.directory, a.token)
-    directory.announce(a.worker_id, server.address, worker.info().roles)
+    directory.announce(a.worker_id, a.advertise or server.address, worker.info().roles)
     try:
-        sys.stdin.read()                            # returns when the controller closes the pipe or exits
+        if a.stay:
+            import signal
+            done = threading.Event()
+            for sig in (signal.SIGTERM, signal.SIGINT):
+                signal.signal(sig, lambda *_: done.set())
+            done.wait()
+        else:
+            sys.stdin.read()                        # returns when the controller closes the pipe or exits
     finally:
         try:
             directory.withdraw(a.worker_id)
