@@ -953,3 +953,72 @@ def test_deployments_local_processes_and_jobset_manifest():
             proc.kill()
         lau._procs.clear()
         lau.shutdown()
+
+
+def test_engine_participants_stage_commit_and_roll_back_weight_rounds():
+    """Two rollout engines behind a coordinator: a good round swaps both models while their servers are paused; a
+    round whose second transfer fails leaves BOTH on the old weights and serving again."""
+    import threading
+    import torch
+    from tunix_b200.experimental.weight_sync.participants import EngineParticipant
+    from tunix_b200.experimental.weight_sync.weight_sync_coordinator import RoundState, WeightSyncCoordinator
+
+    class Server:                                           # the pause / resume face of generate.engine.EngineServer
+        def __init__(self, drains=True):
+            self.paused, self.drains, self.log = False, drains, []
+
+        def pause(self, timeout=None):
+            self.paused = True
+            self.log.append("pause")
+            return self.drains
+
+        def resume(self):
+            self.paused = False
+            self.log.append("resume")
+
+    torch.manual_seed(0)
+    trainer = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    rollouts = [torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4)).to(torch.bfloat16) for _ in range(2)]
+    servers = [Server(), Server()]
+    seen_paused = []
+
+    def source():
+        seen_paused.append([s.paused for s in servers])
+        return trainer.named_parameters()
+
+    parts = [EngineParticipant(f"r{i}", m, source, s) for i, (m, s) in enumerate(zip(rollouts, servers))]
+    coord = WeightSyncCoordinator(parts)
+    addr = [p.data_ptr() for p in rollouts[0].parameters()]
+    assert coord.run_round(1) is RoundState.COMMITTED
+    for m in rollouts:
+        for (n, p), (_, q) in zip(m.named_parameters(), trainer.named_parameters()):
+            assert torch.equal(p, q.to(torch.bfloat16)), n                        # cast into the rollout dtype
+    assert [p.data_ptr() for p in rollouts[0].parameters()] == addr                # in place: captured graphs stay valid
+    assert all(all(row) for row in seen_paused) and [s.log for s in servers] == [["pause", "resume"]] * 2
+    assert parts[0].version == 1 and parts[0].bytes_last_round == sum(p.numel() * 2 for p in rollouts[0].parameters())
+    # second round: the trainer moved on, but the second engine's transfer fails on a shape -> nobody changes
+    before = [[p.clone() for p in m.parameters()] for m in rollouts]
+    with torch.no_grad():
+        for p in trainer.parameters():
+            p.add_(1.0)
+    parts[1].source = lambda: [("0.weight", torch.zeros(3, 3))]
+    assert coord.run_round(2) is RoundState.ABORTED and "shape" in coord.history[-1][2]
+    for m, old in zip(rollouts, before):
+        assert all(torch.equal(p, o) for p, o in zip(m.parameters(), old))
+    assert not any(s.paused for s in servers) and parts[0].version == 1 and parts[0]._staged is None
+    # a missing tensor is an error under strict, fine otherwise; a key map renames
+    parts[1].source = lambda: [(n, p) for n, p in trainer.named_parameters() if n != "1.bias"]
+    assert coord.run_round(3) is RoundState.ABORTED and "lacks" in coord.history[-1][2]
+    parts[1].strict = False
+    parts[1].source = lambda: [("model." + n, p) for n, p in trainer.named_parameters() if n != "1.bias"]
+    parts[1].key_map = lambda n: n[len("model."):]
+    assert coord.run_round(4) is RoundState.COMMITTED
+    assert torch.equal(rollouts[1][0].weight, trainer[0].weight.to(torch.bfloat16)) and torch.equal(rollouts[1][1].bias, before[1][3])
+    # requests that do not drain in time abort the round and the server is admitted again
+    stuck = EngineParticipant("r9", rollouts[0], trainer.named_parameters, Server(drains=False), pause_timeout=0.01)
+    c2 = WeightSyncCoordinator([stuck])
+    assert c2.run_round(1) is RoundState.ABORTED and stuck.server.log == ["pause", "resume"]
+    # without staging nothing is held between transfer and commit
+    direct = EngineParticipant("r8", rollouts[0], trainer.named_parameters, None, stage=False)
+    assert WeightSyncCoordinator([direct]).run_round(7) is RoundState.COMMITTED and direct.version == 7
+    assert torch.equal(rollouts[0][1].bias, trainer[1].bias.to(torch.bfloat16))

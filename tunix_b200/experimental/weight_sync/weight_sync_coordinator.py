@@ -83,7 +83,7 @@ class WeightSyncCoordinator:
             self._phase(RoundState.COMMITTING, lambda p: p.commit(version), committed)
         except BaseException as e:
             # some workers run the new version, some the old one, one of them possibly half-way
-            self.state = RoundState.UNKNOWN_TRANSFER_STATE if committed or True else RoundState.ABORTED
+            self.state = RoundState.UNKNOWN_TRANSFER_STATE
             self.history.append((version, self.state, repr(e)))
             return self.state
         self.state, self.version = RoundState.COMMITTED, version
