@@ -128,3 +128,45 @@ def test_agentic_grpo_learner_end_to_end():
     assert cl.global_steps == 2 and learner.policy_version == 2
     after = torch.cat([p.detach().reshape(-1) for p in actor.parameters()])
     assert cl.metrics_logger.metric_exists("", "trajectory/valid_frac", "train")
+
+
+def test_frozenlake_environment_and_multi_turn_episode():
+    from tunix_b200.rl.agentic.environments.frozenlake_environment import (FrozenLakeAgent, FrozenLakeEnv, generate_map,
+                                                                            parse_move, shortest_path)
+    assert parse_move("I think ```Left``` then ```Down```") == "down" and parse_move("go RIGHT now") == "right"
+    assert parse_move("no idea") is None
+    for seed in range(20):                                  # every generated map is solvable and reproducible
+        g = generate_map(5, 0.6, seed)
+        assert shortest_path(g) is not None and g == generate_map(5, 0.6, seed) and g[0][0] == "S" and g[-1][-1] == "G"
+    env = FrozenLakeEnv({"map": ["S_O", "__O", "O_G"]}, max_steps=6)
+    obs, _ = env.reset()
+    assert "P _ O" in obs and "6 moves" in obs
+    assert env.step("```Up```")[0].count("P") == 1 and env.pos == (0, 0)                   # walls clamp
+    obs, r, done, info = env.step("banana")
+    assert not done and info["valid"] is False and "not a move" in obs
+    assert env.step("```Right```")[3]["moved"] == "right" and env.pos == (0, 1)
+    obs, r, done, info = env.step("```Right```")
+    assert done and r == 0.0 and "X" in obs and info["won"] is False                        # a hole ends the episode
+    # a scripted model walks the shortest path through the collection engine: multi-turn, reward 1
+    task = {"seed": 3, "size": 4, "p": 0.7, "max_steps": 10}
+    env = FrozenLakeEnv(task)
+    path = shortest_path(env.grid)
+    tok = CharTok()
+    script = iter([f"The goal is below and to the right. ```{m.capitalize()}```" for m in path])
+
+    async def model_call(chat_completions=None, prompt_token_ids=None, max_tokens=None):
+        text = next(script)
+        ids = tok.encode(text)
+        return {"text": text, "tokens": ids, "logprobs": [-0.1] * len(ids)}
+    eng = TrajectoryCollectEngine(FrozenLakeAgent(), env, model_call=model_call, tokenizer=tok, chat_parser=get_parser("qwen"),
+                                  max_steps=10)
+    out = asyncio.run(eng.collect("Token"))
+    assert out["status"] == TrajectoryStatus.SUCCEEDED and out["trajectory_reward"] == 1.0 and out["num_turns"] == len(path)
+    assert (out["conversation_masks"] == 0).sum() > 0       # the maps the environment sent back are masked out of the loss
+    # slippery episodes are reproducible from the task
+    runs = []
+    for _ in range(2):
+        e = FrozenLakeEnv({"seed": 5, "size": 4, "is_slippery": True}, max_steps=5)
+        e.reset()
+        runs.append([e.step("```Down```")[3].get("moved") for _ in range(3) if e.step_count < 3])
+    assert runs[0] == runs[1]

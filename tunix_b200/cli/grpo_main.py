@@ -75,9 +75,16 @@ def agentic_kwargs(hp) -> dict:
           "chat_parser": get_parser(a.get("chat_parser", "default"))}
     if a.get("agent", "model") == "tool":
         kw["agent_class"], kw["agent_kwargs"] = ToolAgent, {"tools": {t.name: t for t in chosen}}
+    elif a.get("agent") == "frozenlake":
+        from ..rl.agentic.environments.frozenlake_environment import FrozenLakeAgent
+        kw["agent_class"] = FrozenLakeAgent
     else:
         kw["agent_class"] = ModelAgent
-    if a.get("environment", "task") == "tool":
+    if a.get("environment") == "frozenlake":
+        from ..rl.agentic.environments.frozenlake_environment import FrozenLakeEnv
+        kw["env_class"], kw["env_kwargs"] = FrozenLakeEnv, {"max_steps": kw["max_turns"],
+                                                            "is_slippery": bool(a.get("is_slippery", False))}
+    elif a.get("environment", "task") == "tool":
         kw["env_class"], kw["env_kwargs"] = ToolEnvironment, {"tools": chosen, "reward_fn": a.get("reward_fn", "exact_match"),
                                                               "max_steps": kw["max_turns"]}
     else:
