@@ -181,3 +181,65 @@ def test_gemma4_export_round_trip(tmp_path):
     toks = torch.randint(1, 64, (2, 9))
     with torch.no_grad():
         assert torch.equal(a(toks)[0], b(toks)[0])
+
+
+@pytest.mark.parametrize("family", sorted(CASES))
+def test_config_from_hf_and_logit_checker(family, tmp_path, capsys):
+    """The checkpoint directory alone (config.json + safetensors) is enough: the config is derived from the Hugging
+    Face one and the checker reports agreement with the Hugging Face forward pass."""
+    from tunix_b200.models import logit_checker
+    from tunix_b200.models.hf_config import config_from_hf
+    torch.manual_seed(0)
+    hf, _ = CASES[family](transformers)
+    hf = hf.eval().float()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    cfg = config_from_hf(str(tmp_path), dtype=torch.float32)
+    assert cfg.family == family and cfg.num_layers == hf.config.num_hidden_layers and cfg.head_dim == 16
+    if family == "gemma3":
+        assert cfg.layer_pattern == ("local",) * 5 + ("global",) and cfg.local_rope_theta == 10000.0 and cfg.qk_norm
+    if family == "gemma2":
+        assert cfg.layer_pattern == ("local", "global") and cfg.attn_logit_softcap == 50.0 and cfg.sliding_window == 8
+    if family == "qwen2":
+        assert cfg.qkv_bias
+    rc = logit_checker.main(["--model-path", str(tmp_path), "--tokens", "17", "--atol", "1e-3"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["ok"] and out["top1_agreement"] == 1.0 and out["kl_ref_to_ours"] < 1e-6, out
+    # a wrong architecture is caught, not waved through
+    bad = logit_checker.check(str(tmp_path), tokens=17, config_overrides={"norm_eps": 0.5})
+    assert bad["max_abs_diff"] > 1e-3
+
+
+def test_automodel_reads_an_unnamed_checkpoint_directory_and_moe_config(tmp_path):
+    from tunix_b200.models.automodel import AutoModel
+    from tunix_b200.models.hf_config import config_from_hf
+    torch.manual_seed(0)
+    hf, _ = CASES["qwen3"](transformers)
+    hf = hf.eval().float()
+    hf.save_pretrained(str(tmp_path / "my-finetune"), safe_serialization=True)
+    model, path = AutoModel.from_pretrained(str(tmp_path / "my-finetune"), dtype=torch.float32)
+    toks = torch.randint(0, 128, (1, 9))
+    with torch.no_grad():
+        assert torch.allclose(model.eval()(toks)[0].float(), hf(toks).logits, atol=2e-4, rtol=1e-3)
+    assert path == str(tmp_path / "my-finetune")
+    with pytest.raises((KeyError, ValueError)):
+        AutoModel.from_pretrained("no-such-model-anywhere")
+    moe = config_from_hf({"model_type": "qwen3_moe", "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 4,
+                          "head_dim": 128, "num_hidden_layers": 48, "vocab_size": 151936, "intermediate_size": 6144,
+                          "moe_intermediate_size": 768, "num_experts": 128, "num_experts_per_tok": 8, "norm_topk_prob": True,
+                          "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 40960, "torch_dtype": "bfloat16",
+                          "router_aux_loss_coef": 0.001})
+    from tunix_b200.models.config import ModelConfig
+    want = ModelConfig.qwen3_30b_a3b()
+    for f in ("num_layers", "embed_dim", "num_heads", "num_kv_heads", "head_dim", "num_experts", "num_experts_per_tok",
+              "moe_hidden_dim", "vocab_size", "qk_norm", "rope_theta", "router_aux_loss_coef"):
+        assert getattr(moe, f) == getattr(want, f), f
+    assert moe.dtype == torch.bfloat16
+    llama = config_from_hf({"model_type": "llama", "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+                            "num_hidden_layers": 32, "vocab_size": 128256, "intermediate_size": 14336, "rms_norm_eps": 1e-5,
+                            "rope_theta": 500000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}})
+    assert llama.head_dim == 128 and llama.rope_llama3_scaling["factor"] == 8.0 and llama.family == "llama3"
+    with pytest.raises(ValueError, match="model_type"):
+        config_from_hf({"model_type": "mamba", "hidden_size": 8, "num_attention_heads": 1, "num_hidden_layers": 1, "vocab_size": 8})

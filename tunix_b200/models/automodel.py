@@ -44,7 +44,16 @@ class AutoModel:
                         remat_config: Optional[str] = None, use_flash_attention: Optional[bool] = None,
                         seed: int = 0, **config_overrides):
         """Returns (model, model_path)."""
-        cfg: ModelConfig = naming.config_for(model_id)
+        try:
+            cfg: ModelConfig = naming.config_for(model_id)
+        except (KeyError, ValueError):
+            # no preset of that name: a checkpoint directory describes itself through its config.json
+            path = model_path or (model_id if os.path.isdir(model_id) else None)
+            if path is None or not os.path.exists(os.path.join(path, "config.json")):
+                raise
+            from .hf_config import config_from_hf
+            cfg = config_from_hf(path)
+            model_path = path
         over = dict(config_overrides)
         if dtype is not None:
             over["dtype"] = dtype
