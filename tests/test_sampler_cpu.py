@@ -240,6 +240,14 @@ def test_openai_style_http_front_end_over_the_engine_server():
             assert _http(http.url + "/v1/nothing", {})[0] == 404 and _http(http.url + "/nothing")[0] == 404
             eng.close()
             assert _http(http.url + "/v1/completions", {"prompt": "a"})[0] == 503    # engine gone: unavailable, not a hang
+            st, ctype, raw = _http(http.url + "/metrics")
+            text = raw.decode()
+            assert st == 200 and ctype.startswith("text/plain")
+            vals = {l.split(" ")[0]: float(l.split(" ")[1]) for l in text.splitlines() if l and not l.startswith("#")}
+            assert vals["tunix_b200_http_requests_total"] == http.requests_served >= 14
+            assert vals['tunix_b200_http_errors_total{status="400"}'] == 3 and vals['tunix_b200_http_errors_total{status="503"}'] == 1
+            assert vals["tunix_b200_http_completion_tokens_total"] >= 3 + 6 + 4 + 2 + 16 and vals["tunix_b200_http_requests_in_flight"] == 0
+            assert vals['tunix_b200_http_request_seconds_bucket{le="+Inf"}'] == vals["tunix_b200_http_request_seconds_count"] == http.requests_served
 
 
 def test_openai_front_end_routes_conversations_over_several_engines():

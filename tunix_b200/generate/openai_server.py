@@ -5,6 +5,8 @@ a vLLM sampler).
 Routes:
 
     GET  /health, /v1/models        liveness and the served model's name
+    GET  /metrics                   Prometheus text format: requests, errors by status, prompt / completion tokens,
+                                    request latency histogram, requests in flight
     POST /v1/completions            {"prompt": str | [str], "max_tokens", "stream"}
     POST /v1/chat/completions       {"messages": [{"role", "content"}], "max_tokens", "stream"}
 
@@ -32,6 +34,9 @@ class _BadRequest(ValueError):
     pass
 
 
+_LAT_BUCKETS = (0.05, 0.1, 0.25, 0.5, 1.0, 2.5, 5.0, 10.0, 30.0, 60.0, 120.0)
+
+
 class OpenAIServer:
     def __init__(self, backend, tokenizer, *, model_name: str = "tunix-b200", chat_parser=None,
                  host: str = "127.0.0.1", port: int = 0, request_timeout: Optional[float] = 600.0,
@@ -45,6 +50,8 @@ class OpenAIServer:
         self.sampling = dict(sampling or {})
         self.requests_served = 0
         self._lock = threading.Lock()
+        self._m = {"prompt_tokens": 0, "completion_tokens": 0, "inflight": 0, "errors": {}, "lat_sum": 0.0,
+                   "lat_buckets": [0] * (len(_LAT_BUCKETS) + 1)}
         outer = self
 
         class Handler(BaseHTTPRequestHandler):
@@ -56,6 +63,13 @@ class OpenAIServer:
             def do_GET(self):
                 if self.path in ("/health", "/v1/models"):
                     outer._send_json(self, 200, outer._models())
+                elif self.path == "/metrics":
+                    data = outer.metrics_text().encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/plain; version=0.0.4")
+                    self.send_header("Content-Length", str(len(data)))
+                    self.end_headers()
+                    self.wfile.write(data)
                 else:
                     outer._send_json(self, 404, {"error": {"message": f"no route {self.path}", "type": "not_found"}})
 
@@ -102,8 +116,31 @@ class OpenAIServer:
     def __exit__(self, *exc):
         self.close()
 
-    @staticmethod
-    def _send_json(h, code: int, payload: dict) -> None:
+    def metrics_text(self) -> str:
+        with self._lock:
+            m = {k: (dict(v) if isinstance(v, dict) else list(v) if isinstance(v, list) else v) for k, v in self._m.items()}
+            served = self.requests_served
+        p = "tunix_b200_http"
+        lines = [f"# TYPE {p}_requests_total counter", f"{p}_requests_total {served}",
+                 f"# TYPE {p}_errors_total counter"]
+        lines += [f'{p}_errors_total{{status="{code}"}} {n}' for code, n in sorted(m["errors"].items())] or [f"{p}_errors_total 0"]
+        lines += [f"# TYPE {p}_prompt_tokens_total counter", f"{p}_prompt_tokens_total {m['prompt_tokens']}",
+                  f"# TYPE {p}_completion_tokens_total counter", f"{p}_completion_tokens_total {m['completion_tokens']}",
+                  f"# TYPE {p}_requests_in_flight gauge", f"{p}_requests_in_flight {m['inflight']}",
+                  f"# TYPE {p}_request_seconds histogram"]
+        acc = 0
+        for le, n in zip(_LAT_BUCKETS, m["lat_buckets"]):
+            acc += n
+            lines.append(f'{p}_request_seconds_bucket{{le="{le}"}} {acc}')
+        acc += m["lat_buckets"][-1]
+        lines += [f'{p}_request_seconds_bucket{{le="+Inf"}} {acc}', f"{p}_request_seconds_sum {m['lat_sum']:.6f}",
+                  f"{p}_request_seconds_count {acc}"]
+        return "\n".join(lines) + "\n"
+
+    def _send_json(self, h, code: int, payload: dict) -> None:
+        if code >= 400:
+            with self._lock:
+                self._m["errors"][code] = self._m["errors"].get(code, 0) + 1
         data = json.dumps(payload).encode()
         h.send_response(code)
         h.send_header("Content-Type", "application/json")
@@ -134,20 +171,34 @@ class OpenAIServer:
         if max_tokens is not None and (not isinstance(max_tokens, int) or max_tokens < 1):
             raise _BadRequest("max_tokens must be a positive integer")
         limit = getattr(self.backend, "max_new_tokens", None)
-        if getattr(self.backend, "routes", False):          # several engines: the key keeps a conversation on one of them
-            toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout, route_key=body.get("route_key"))
-        else:
-            try:
-                toks, lps = self.backend.generate(ids, max_tokens, timeout=self.request_timeout)
-            except TypeError:                               # a back end without the timeout argument
-                toks, lps = self.backend.generate(ids, max_tokens)
+        t0 = time.perf_counter()
+        with self._lock:
+            self._m["inflight"] += 1
+        try:
+            toks, lps = self._call_backend(ids, max_tokens, body)
+        finally:
+            with self._lock:
+                self._m["inflight"] -= 1
+        dt = time.perf_counter() - t0
         toks = [int(t) for t in toks]
         asked = min(max_tokens or limit or len(toks), limit or len(toks))
         with self._lock:
             self.requests_served += 1
+            self._m["prompt_tokens"] += len(ids)
+            self._m["completion_tokens"] += len(toks)
+            self._m["lat_sum"] += dt
+            self._m["lat_buckets"][next((i for i, le in enumerate(_LAT_BUCKETS) if dt <= le), len(_LAT_BUCKETS))] += 1
         return {"text": self.tokenizer.decode(toks), "tokens": toks, "prompt_tokens": len(ids),
                 "logprobs": [float(x) for x in lps] if body.get("logprobs") and lps is not None else None,
                 "finish_reason": "length" if len(toks) >= asked else "stop"}
+
+    def _call_backend(self, ids, max_tokens, body):
+        if getattr(self.backend, "routes", False):          # several engines: the key keeps a conversation on one of them
+            return self.backend.generate(ids, max_tokens, timeout=self.request_timeout, route_key=body.get("route_key"))
+        try:
+            return self.backend.generate(ids, max_tokens, timeout=self.request_timeout)
+        except TypeError:                                   # a back end without the timeout argument
+            return self.backend.generate(ids, max_tokens)
 
     def _usage(self, results: Sequence[dict]) -> dict:
         p, c = sum(r["prompt_tokens"] for r in results), sum(len(r["tokens"]) for r in results)
