@@ -1052,3 +1052,70 @@ def test_distributed_grpo_example_runs_across_processes(capsys):
     assert mod.main(["--print-jobset"]) is None
     man = yaml.safe_load(capsys.readouterr().out)
     assert man["kind"] == "JobSet" and man["spec"]["replicatedJobs"][0]["template"]["spec"]["parallelism"] == 2
+
+
+def test_bulk_plane_striped_transfers_and_remote_weight_sync():
+    import os
+    import threading
+    import numpy as np
+    pytest.importorskip("grpc")
+    from tunix_b200.experimental.worker.network import (ArrayBundle, BulkReceiver, join_arrays, send_bulk, split_arrays)
+    from tunix_b200.experimental.worker.mock_worker import MockWorker
+    from tunix_b200.experimental.worker.remote_execution import RemoteWorker, serve_worker
+    rng = np.random.default_rng(0)
+    payload = {"layers": [{"w": rng.standard_normal((601, 301)).astype(np.float32), "b": rng.integers(-9, 9, 77).astype(np.int16)}],
+               "head": ("bf16", rng.integers(0, 2 ** 15, (1000, 33)).astype(np.int16)), "step": 7, "empty": np.zeros((0, 4), np.float64),
+               "tiny": np.arange(3)}
+    skeleton, arrays = split_arrays(payload, min_bytes=0)
+    assert len(arrays) == 5 and skeleton["step"] == 7
+    views = ArrayBundle.unpack(ArrayBundle.pack(arrays))
+    back = join_arrays(skeleton, views)
+    assert np.array_equal(back["layers"][0]["w"], payload["layers"][0]["w"]) and back["head"][0] == "bf16"
+    assert np.array_equal(back["head"][1], payload["head"][1]) and back["empty"].shape == (0, 4) and back["tiny"].dtype == np.arange(3).dtype
+    assert all((v.ctypes.data - views[0].ctypes.data) % 64 == 0 for v in views if v.nbytes)       # arrays start on 64-byte offsets
+    # raw transfers: several sizes and stripe counts, several at once, wrong token, incomplete transfer
+    rx = BulkReceiver(token="k3y")
+    try:
+        blobs = [os.urandom(n) for n in (0, 1, 300_000, 3_000_001)]
+        handles = [None] * len(blobs)
+
+        def send(i):
+            handles[i] = send_bulk(rx.address, blobs[i], stripes=1 + i * 2, token="k3y")
+        ts = [threading.Thread(target=send, args=(i,)) for i in range(len(blobs))]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        for h, blob in zip(handles, blobs):
+            assert h.nbytes == len(blob) and bytes(rx.take(h.transfer_id, timeout=10)) == blob
+        assert rx.bytes_received == sum(map(len, blobs))
+        with pytest.raises(ConnectionError):
+            send_bulk(rx.address, b"x" * 1000, token="wrong")
+        with pytest.raises(TimeoutError):
+            rx.take(b"\x00" * 16, timeout=0.05)
+    finally:
+        rx.close()
+    # a remote worker: the weight payload goes over the bulk plane, small payloads and servers without one use the RPC
+    got = {}
+
+    class W(MockWorker):
+        def _sync_weights(self, version, payload):
+            got[version] = payload
+    for bulk in (True, False):
+        w = W("w0")
+        with serve_worker(w, token="k3y") if bulk else __import__("tunix_b200.experimental.worker.remote_execution", fromlist=["WorkerServer"]).WorkerServer(w, token="k3y", bulk=False) as srv:
+            rw = RemoteWorker(srv.address, token="k3y")
+            rw.start()
+            rw.sync_weights(1, payload)
+            assert np.array_equal(got[1]["layers"][0]["w"], payload["layers"][0]["w"]) and got[1]["head"][0] == "bf16"
+            assert np.array_equal(got[1]["head"][1], payload["head"][1]) and got[1]["step"] == 7 and np.array_equal(got[1]["tiny"], np.arange(3))
+            assert (rw.bulk_bytes_sent > 700_000) == bulk                      # the arrays left the pickle, or could not
+            rw.sync_weights(2, {"small": np.ones(8)})
+            assert got[2]["small"].sum() == 8 and (rw.bulk_bytes_sent > 700_000) == bulk
+            if bulk:                                        # a worker that copies its payload hands the buffer back
+                w.releases_bulk_payloads = True
+                rw.sync_weights(4, payload)
+                rw.sync_weights(5, payload)
+                assert srv.bulk.buffers_reused == 1 and np.array_equal(got[5]["layers"][0]["w"], payload["layers"][0]["w"])
+            sent = rw.bulk_bytes_sent
+            rw.sync_weights(3, None)
+            assert got[3] is None and rw.bulk_bytes_sent == sent
+            rw.close()

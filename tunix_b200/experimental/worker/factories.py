@@ -89,4 +89,5 @@ def make_rollout_worker(worker_id: str, role: str = "rollout", model: str = "toy
     w = RolloutWorker(worker_id, eng, eos_tokens=[tok.eos_id()], apply_weights=lambda version, payload: install_state(net, payload))
     w.role = role
     w.model = net
+    w.releases_bulk_payloads = True                     # install_state copies into the parameters and keeps nothing
     return w

@@ -5,7 +5,9 @@
 object itself: `submit`, `sync_weights`, `start`, `stop`, `info`, `state` and any other public method go over the
 wire. Payloads are cloudpickle frames (method name, args, kwargs -> ("ok", value) | ("err", exception)), large
 ones are split into chunks on a client-streaming RPC (`/tunix_b200.Worker/CallChunked`), so a weight payload does
-not have to fit one message.
+not have to fit one message. Weight payloads whose numpy arrays add up to 512 KiB or more skip the pickle
+altogether: the arrays travel over the striped TCP bulk plane of `network.py` and only a handle and the payload's
+skeleton go through the RPC.
 
 Unpickling executes code: the endpoint is meant for the private network of one training job. It binds to the
 loopback interface unless told otherwise and takes an optional shared token that every call must carry.
@@ -38,19 +40,41 @@ def _ident(b: bytes) -> bytes:
 
 
 class _Servicer:
-    def __init__(self, worker, token: Optional[str]):
-        self.worker, self.token = worker, token
+    def __init__(self, worker, token: Optional[str], bulk=None):
+        self.worker, self.token, self.bulk = worker, token, bulk
         self._lock = threading.Lock()
+
+    def _resolve_bulk(self, args, kwargs):
+        """Arguments that arrived over the bulk plane: ("__bulk__", handle, skeleton) -> the payload with its arrays."""
+        from .network import ArrayBundle, BulkHandle, join_arrays
+
+        taken = []
+
+        def fix(a):
+            if isinstance(a, tuple) and len(a) == 3 and a[0] == "__bulk__" and isinstance(a[1], BulkHandle):
+                if self.bulk is None:
+                    raise RuntimeError("this server has no bulk plane")
+                taken.append(self.bulk.take(a[1].transfer_id))
+                return join_arrays(a[2], ArrayBundle.unpack(taken[-1]))
+            return a
+        return tuple(fix(a) for a in args), {k: fix(v) for k, v in kwargs.items()}, taken
 
     def _dispatch(self, blob: bytes) -> bytes:
         try:
             token, name, args, kwargs = cloudpickle.loads(blob)
             if self.token is not None and not hmac.compare_digest(str(token or ""), self.token):
                 raise PermissionError("bad or missing token")
+            if name == "__bulk_address__":
+                return cloudpickle.dumps(("ok", None if self.bulk is None else self.bulk.address))
             if name.startswith(_PRIVATE):
                 raise AttributeError(f"{name!r} is not a remote method")
+            args, kwargs, taken = self._resolve_bulk(args, kwargs)
             attr = getattr(self.worker, name)
             value = attr(*args, **kwargs) if callable(attr) else attr
+            if taken and getattr(self.worker, "releases_bulk_payloads", False):
+                del args, kwargs                            # the worker copied what it needs: the buffers serve the next round
+                for buf in taken:
+                    self.bulk.release(buf)
             return cloudpickle.dumps(("ok", value))
         except BaseException as e:                      # the failure travels back; the server keeps serving
             try:
@@ -66,8 +90,13 @@ class _Servicer:
 
 
 class WorkerServer:
-    def __init__(self, worker, address: str = "127.0.0.1:0", token: Optional[str] = None, max_threads: int = 16):
-        svc = _Servicer(worker, token)
+    def __init__(self, worker, address: str = "127.0.0.1:0", token: Optional[str] = None, max_threads: int = 16,
+                 bulk: bool = True):
+        self.bulk = None
+        if bulk:
+            from .network import BulkReceiver
+            self.bulk = BulkReceiver(address.rsplit(":", 1)[0], 0, token)
+        svc = _Servicer(worker, token, self.bulk)
         self._server = grpc.server(futures.ThreadPoolExecutor(max_workers=max_threads), options=_OPTS)
         handlers = {
             "Call": grpc.unary_unary_rpc_method_handler(svc.call, request_deserializer=_ident, response_serializer=_ident),
@@ -84,6 +113,8 @@ class WorkerServer:
 
     def stop(self, grace: float = 1.0) -> None:
         self._server.stop(grace).wait()
+        if self.bulk is not None:
+            self.bulk.close()
 
     def __enter__(self):
         return self
@@ -106,6 +137,29 @@ class RemoteWorker:
         self._call_chunked = self._channel.stream_unary(f"/{_SERVICE}/CallChunked", request_serializer=_ident,
                                                         response_deserializer=_ident)
         self._info = None
+        self._bulk_address: Any = False                     # False: not asked yet; None: the server has none
+        self.bulk_stripes = 4
+        self._pack_buf = None
+        self.bulk_bytes_sent = 0
+
+    def _via_bulk(self, payload: Any) -> Any:
+        """Large array payloads leave the pickle: arrays over striped TCP, the skeleton over the RPC."""
+        from .network import BULK_THRESHOLD, ArrayBundle, send_bulk, split_arrays
+        if not isinstance(payload, (dict, list, tuple)):
+            return payload
+        skeleton, arrays = split_arrays(payload, min_bytes=4096)
+        if sum(a.nbytes for a in arrays) < BULK_THRESHOLD:
+            return payload
+        if self._bulk_address is False:
+            self._bulk_address = self._invoke("__bulk_address__")
+        if self._bulk_address is None:
+            return payload
+        host = self.address.rsplit(":", 1)[0]
+        target = f"{host}:{self._bulk_address.rsplit(':', 1)[1]}"      # the host we reach it by, the port it listens on
+        self._pack_buf = ArrayBundle.pack(arrays, out=self._pack_buf)      # same size every round: the buffer is kept
+        handle = send_bulk(target, self._pack_buf, stripes=self.bulk_stripes, token=self._token, timeout=self._timeout)
+        self.bulk_bytes_sent += handle.nbytes
+        return ("__bulk__", handle, skeleton)
 
     def _invoke(self, name: str, *args, **kwargs) -> Any:
         blob = cloudpickle.dumps((self._token, name, args, kwargs))
@@ -146,7 +200,7 @@ class RemoteWorker:
         return self._invoke("submit", request)
 
     def sync_weights(self, version: int, payload: Any = None) -> None:
-        return self._invoke("sync_weights", version, payload)
+        return self._invoke("sync_weights", version, self._via_bulk(payload))
 
     def __getattr__(self, name: str):
         if name.startswith("_"):
