@@ -233,6 +233,9 @@ def test_openai_style_http_front_end_over_the_engine_server():
             with ThreadPoolExecutor(8) as ex:
                 res = list(ex.map(lambda i: _http(http.url + "/v1/completions", {"prompt": "x" * (i + 1), "max_tokens": 2}), range(8)))
             assert all(r[0] == 200 for r in res) and http.requests_served >= 8
+            with ThreadPoolExecutor(96) as ex:              # a burst of connections larger than a default listen backlog
+                res = list(ex.map(lambda i: _http(http.url + "/v1/completions", {"prompt": "y" * (1 + i % 7), "max_tokens": 1}), range(192)))
+            assert all(r[0] == 200 for r in res)
             # errors
             assert _http(http.url + "/v1/completions", {"prompt": 5})[0] == 400
             assert _http(http.url + "/v1/completions", {"prompt": "a", "max_tokens": 0})[0] == 400
@@ -244,7 +247,7 @@ def test_openai_style_http_front_end_over_the_engine_server():
             text = raw.decode()
             assert st == 200 and ctype.startswith("text/plain")
             vals = {l.split(" ")[0]: float(l.split(" ")[1]) for l in text.splitlines() if l and not l.startswith("#")}
-            assert vals["tunix_b200_http_requests_total"] == http.requests_served >= 14
+            assert vals["tunix_b200_http_requests_total"] == http.requests_served >= 14 + 192
             assert vals['tunix_b200_http_errors_total{status="400"}'] == 3 and vals['tunix_b200_http_errors_total{status="503"}'] == 1
             assert vals["tunix_b200_http_completion_tokens_total"] >= 3 + 6 + 4 + 2 + 16 and vals["tunix_b200_http_requests_in_flight"] == 0
             assert vals['tunix_b200_http_request_seconds_bucket{le="+Inf"}'] == vals["tunix_b200_http_request_seconds_count"] == http.requests_served

@@ -37,6 +37,11 @@ class _BadRequest(ValueError):
 _LAT_BUCKETS = (0.05, 0.1, 0.25, 0.5, 1.0, 2.5, 5.0, 10.0, 30.0, 60.0, 120.0)
 
 
+class _HTTPServer(ThreadingHTTPServer):
+    request_queue_size = 1024                               # the listen backlog: hundreds of clients connect at once
+    daemon_threads = True
+
+
 class OpenAIServer:
     def __init__(self, backend, tokenizer, *, model_name: str = "tunix-b200", chat_parser=None,
                  host: str = "127.0.0.1", port: int = 0, request_timeout: Optional[float] = 600.0,
@@ -94,8 +99,7 @@ class OpenAIServer:
                 except RuntimeError as e:                   # the engine server is closed or failed
                     outer._send_json(self, 503, {"error": {"message": str(e), "type": "unavailable"}})
 
-        self._httpd = ThreadingHTTPServer((host, port), Handler)
-        self._httpd.daemon_threads = True
+        self._httpd = _HTTPServer((host, port), Handler)
         self.host, self.port = self._httpd.server_address[:2]
         self._thread = threading.Thread(target=self._httpd.serve_forever, name="tunix-b200-openai-server", daemon=True)
         self._thread.start()
