@@ -1119,3 +1119,61 @@ def test_bulk_plane_striped_transfers_and_remote_weight_sync():
             rw.sync_weights(3, None)
             assert got[3] is None and rw.bulk_bytes_sent == sent
             rw.close()
+
+
+def test_async_sampler_adapter_over_server_and_batch_engines():
+    import asyncio
+    import torch
+    from tests.test_sampler_cpu import CharTok, _FakeEngine
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.experimental.rollout.sampler import EngineSamplerAdapter, SamplingParams, SamplingRequest, SamplingResponse
+    from tunix_b200.experimental.weight_sync.participants import EngineParticipant
+    from tunix_b200.generate.engine import EngineServer
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    with pytest.raises(ValueError):
+        SamplingResponse("r", [1, 2], [0.0])
+
+    async def server_case():
+        srv = EngineServer(_FakeEngine(slots=3, fail_on=13), max_new_tokens=5, max_prompt_length=8, eos_tokens=[2])
+        trainer, rollout = torch.nn.Linear(4, 4), torch.nn.Linear(4, 4)
+        ad = EngineSamplerAdapter(srv, tokenizer=CharTok(), participant=EngineParticipant("r0", rollout, trainer.named_parameters, srv))
+        await ad.start()
+        reqs = [SamplingRequest(f"q{i}", [1, 20 + i], SamplingParams(max_tokens=1 + i % 3)) for i in range(6)]
+        out = await ad.sample(reqs)
+        assert [r.request_id for r in out] == [f"q{i}" for i in range(6)] and all(r.error is None for r in out)
+        assert [r.token_ids for r in out] == [[20 + i + k + 1 for k in range(1 + i % 3)] for i in range(6)]
+        assert out[0].text == CharTok().decode(out[0].token_ids) and out[0].finish_reason == "length"
+        # a weight sync: sampling waits at the gate, then sees the new version
+        await ad.pre_weight_sync(1)
+        pending = asyncio.ensure_future(ad.sample([SamplingRequest("late", [1, 3], SamplingParams(max_tokens=1))]))
+        await asyncio.sleep(0.05)
+        assert not pending.done() and (await ad.get_load_info()).paused
+        await ad.weight_sync(1)
+        await ad.post_weight_sync(1)
+        late = (await pending)[0]
+        assert late.policy_version == 1 and torch.equal(rollout.weight, trainer.weight)
+        # an aborted sync reopens the gate on the old version
+        await ad.pre_weight_sync(2)
+        await ad.abort_weight_sync()
+        assert (await ad.sample([SamplingRequest("x", [1, 4], SamplingParams(max_tokens=1))]))[0].policy_version == 1
+        info = await ad.get_load_info()
+        assert info.served == 8 and info.inflight == 0 and not info.paused
+        # the engine fails on one request: that response carries the error
+        bad = await ad.sample([SamplingRequest("boom", [1, 13], SamplingParams(max_tokens=2))])
+        assert isinstance(bad[0].error, RuntimeError) and bad[0].finish_reason == "error"
+        await ad.stop()
+
+    async def batch_case():
+        cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
+        model = create_model(cfg, seed=0)
+        ad = EngineSamplerAdapter(Sampler(model, CharTok(), CacheConfig(32, 1, 1, 16)), tokenizer=CharTok(), eos_tokens=[2])
+        out = await ad.sample([SamplingRequest("a", [1, 5, 6], SamplingParams(max_tokens=4, temperature=0.0)),
+                               SamplingRequest("b", [1, 7], SamplingParams(max_tokens=3, temperature=0.0, return_logprobs=False))])
+        assert len(out[0].token_ids) <= 4 and len(out[0].logprobs) == len(out[0].token_ids) and out[1].logprobs is None
+        assert await ad.pause() and (await ad.get_load_info()).paused
+        await ad.resume()
+        await ad.stop()
+    asyncio.run(server_case())
+    asyncio.run(batch_case())
