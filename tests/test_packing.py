@@ -69,3 +69,30 @@ def test_router_replay_census():
     routed[0, 1, 0] = [3, 3]
     seg = np.array([[1, 1, 1, 0]], np.int32)
     assert P.count_router_replay_forced_tokens(routed, seg) == (3, 1)
+
+
+def test_native_packing_under_address_and_undefined_behaviour_sanitizers():
+    """The C++ host library is rebuilt with -fsanitize=address,undefined and this file's tests, plus the batch
+    assemblers', run against it in a child process with the sanitizer run-time preloaded: an out-of-bounds write,
+    a use after free or signed overflow in the packing code aborts the child."""
+    import os
+    import subprocess
+    import sys
+    import pytest
+    from tunix_b200 import _build
+    try:
+        _, asan = _build.sanitizer_toolchain()
+        lib = _build.build_host_sanitized()
+    except RuntimeError as e:
+        pytest.skip(str(e))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
+               TUNIX_B200_HOST_LIB=str(lib))
+    who = subprocess.run([sys.executable, "-c", "from tunix_b200 import _lib; print(_lib.host()._name)"], env=env, cwd=root,
+                         capture_output=True, text=True, timeout=300)
+    assert who.returncode == 0 and who.stdout.strip().endswith("libtunix_b200_host_asan.so"), who.stderr[-2000:]
+    run = subprocess.run([sys.executable, "-m", "pytest", "tests/test_packing.py", "tests/test_experimental_cpu.py", "-x", "-q",
+                          "-p", "no:cacheprovider", "-k", "not sanitizers and (packing or pack or batch_assemblers or ffd or fill)"],
+                         env=env, cwd=root, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-3000:]
+    assert " passed" in run.stdout and "failed" not in run.stdout

@@ -102,6 +102,38 @@ def build_host(force: bool = False) -> Path:
     return HOST_LIB
 
 
+def build_host_sanitized(force: bool = False) -> Path:
+    """The host extensions once more with AddressSanitizer and UndefinedBehaviorSanitizer, for the test that runs the
+    packing suite against them (the process that loads this library must have libasan preloaded)."""
+    sources = sorted((CSRC / "host").glob("*.cc"))
+    out = BUILD_DIR / "libtunix_b200_host_asan.so"
+    stamp = BUILD_DIR / "host_asan.stamp"
+    flags = ["-O1", "-g", "-std=c++17", "-fPIC", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+             "-fno-sanitize-recover=all"]
+    digest = _digest(sources, " ".join(flags))
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+        return out
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    cxx, _ = sanitizer_toolchain()
+    _run([cxx, *flags, "-shared", "-o", str(out), *map(str, sources)])
+    stamp.write_text(digest)
+    return out
+
+
+def sanitizer_toolchain():
+    """(compiler, path of its libasan.so): the first g++ that ships the sanitizer run-time."""
+    seen = []
+    for cxx in (os.environ.get("CXX"), "/usr/bin/g++", shutil.which("g++")):
+        if not cxx or cxx in seen or not os.path.exists(cxx):
+            continue
+        seen.append(cxx)
+        res = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True)
+        path = res.stdout.strip()
+        if res.returncode == 0 and os.path.isabs(path) and os.path.exists(path):
+            return cxx, path
+    raise RuntimeError("no g++ with libasan on this machine")
+
+
 TRAJJSON_LIB = PKG_DIR / "utils" / "_trajjson.so"
 
 

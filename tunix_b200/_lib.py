@@ -80,7 +80,8 @@ def host():
     if _host_lib is None:
         with _lock:
             if _host_lib is None:
-                path = _build.build_host()
+                import os
+                path = os.environ.get("TUNIX_B200_HOST_LIB") or _build.build_host()      # override: a sanitizer build
                 _host_lib = ctypes.CDLL(str(path))
     return _host_lib
 
