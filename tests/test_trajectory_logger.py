@@ -62,3 +62,28 @@ def test_csv_logger(tmp_path):
     T.log_item(p, {"a": 2, "arr": np.array([3, 4])}, "csv")
     rows = open(p).read().strip().split("\n")
     assert rows[0] == "a,arr" and rows[1] == '1,"[1, 2]"'
+
+
+def test_native_serializer_under_address_and_undefined_behaviour_sanitizers():
+    """`_trajjson` rebuilt with -fsanitize=address,undefined; this file's tests run against it in a child process
+    with the sanitizer run-time preloaded."""
+    import os
+    import subprocess
+    import sys
+    import pytest
+    from tunix_b200 import _build
+    try:
+        _, asan = _build.sanitizer_toolchain()
+        lib = _build.build_pyext_sanitized()
+    except RuntimeError as e:
+        pytest.skip(str(e))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
+               TUNIX_B200_TRAJJSON_LIB=str(lib))
+    who = subprocess.run([sys.executable, "-c", "from tunix_b200.utils import trajectory_logger as t; print(t._trajjson.__file__)"],
+                         env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert who.returncode == 0 and who.stdout.strip() == str(lib), who.stdout + who.stderr[-2000:]
+    run = subprocess.run([sys.executable, "-m", "pytest", "tests/test_trajectory_logger.py", "-x", "-q", "-p", "no:cacheprovider",
+                          "-k", "not sanitizers"], env=env, cwd=root, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stdout[-3000:] + run.stderr[-3000:]
+    assert " passed" in run.stdout and "failed" not in run.stdout

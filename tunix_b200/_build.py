@@ -155,6 +155,28 @@ def build_pyext(force: bool = False) -> Path:
     return TRAJJSON_LIB
 
 
+def build_pyext_sanitized(force: bool = False) -> Path:
+    """`_trajjson` with AddressSanitizer and UndefinedBehaviorSanitizer, beside the build products (not in the
+    package); `TUNIX_B200_TRAJJSON_LIB` makes `utils.trajectory_logger` load it."""
+    import sysconfig
+    src = CSRC / "pyext" / "trajjson.cc"
+    out = BUILD_DIR / "asan" / "_trajjson.so"
+    stamp = BUILD_DIR / "pyext_asan.stamp"
+    flags = ["-O1", "-g", "-std=c++17", "-fPIC", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+             "-fno-sanitize-recover=all", "-fvisibility=default"]
+    digest = _digest([src], " ".join(flags) + sys.version)
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+        return out
+    out.parent.mkdir(parents=True, exist_ok=True)
+    inc = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(inc, "Python.h")):
+        raise RuntimeError("Python.h not found")
+    cxx, _ = sanitizer_toolchain()
+    _run([cxx, *flags, "-shared", "-I", inc, "-o", str(out), str(src)])
+    stamp.write_text(digest)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_host(force)
     try:

@@ -23,7 +23,14 @@ from typing import Any, Literal, Optional
 import numpy as np
 
 try:  # native fast path
-    from . import _trajjson  # type: ignore
+    if os.environ.get("TUNIX_B200_TRAJJSON_LIB"):           # another build of the module (the sanitizer build of the tests)
+        import importlib.machinery
+        import importlib.util
+        _loader = importlib.machinery.ExtensionFileLoader(__package__ + "._trajjson", os.environ["TUNIX_B200_TRAJJSON_LIB"])
+        _trajjson = importlib.util.module_from_spec(importlib.util.spec_from_loader(_loader.name, _loader))
+        _loader.exec_module(_trajjson)
+    else:
+        from . import _trajjson  # type: ignore
 except Exception:  # pragma: no cover - exercised only without the built module
     _trajjson = None
 
