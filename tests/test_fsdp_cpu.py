@@ -48,3 +48,55 @@ def test_two_gloo_ranks_match_single_process(tmp_path):
     mp.spawn(_train, args=(2, 29731, double), nprocs=2, join=True)
     a, b = torch.load(single), torch.load(double)
     assert torch.allclose(a, b, atol=2e-5, rtol=1e-4), (a - b).abs().max()
+
+
+def test_flag_barrier_protocol_model_with_threads_as_ranks():
+    """The device barrier's protocol restated on the host: nobody leaves barrier k before everybody entered it,
+    under random schedules, with slots interleaved, across the 32-bit epoch wrap; a rank that stays away costs the
+    others a bounded wait and a status that names it."""
+    import random
+    import threading
+    import time
+    from tunix_b200.parallel.protocol_model import ST_TIMEOUT_FLAG, FlagBarrierModel, _not_older, run_ranks
+    assert _not_older(5, 5) and _not_older(6, 5) and not _not_older(4, 5)
+    assert _not_older(2, 0xFFFFFFFE) and not _not_older(0xFFFFFFFE, 2)           # across the wrap
+    for world, start in ((2, 0), (4, 0), (8, 0xFFFFFFF0)):
+        model = FlagBarrierModel(world, slots=3)
+        if start:
+            model.set_epoch(start)
+        rounds = 40
+        entered = [[0] * world for _ in range(rounds)]
+        lock = threading.Lock()
+
+        def body(rank, model=model, entered=entered, world=world):
+            rng = random.Random(rank)
+            jitter = lambda: time.sleep(rng.random() * 2e-4) if rng.random() < 0.3 else None
+            for k in range(rounds):
+                with lock:
+                    entered[k][rank] = 1
+                assert model.wait(rank, slot=k % 3, timeout_s=20.0, yield_fn=jitter)
+                with lock:
+                    assert sum(entered[k]) == world, (k, rank)        # everybody had entered before anyone left
+            return True
+        assert all(run_ranks(world, body))
+        assert not model.status.any()
+    # rank 2 never joins the second barrier: the others give up after the limit and name it
+    model = FlagBarrierModel(3)
+
+    def body(rank):
+        assert model.wait(rank, timeout_s=10.0)
+        if rank == 2:
+            return "left"
+        return model.wait(rank, timeout_s=0.2)
+    t0 = time.monotonic()
+    assert run_ranks(3, body) == [False, False, "left"] and time.monotonic() - t0 < 5
+    assert model.status[0].tolist() == [ST_TIMEOUT_FLAG, 2, 2] and model.status[1].tolist() == [ST_TIMEOUT_FLAG, 2, 2]
+    assert model.status[2, 0] == 0
+    # a late rank is not an absent one: the barrier completes once it shows up
+    model = FlagBarrierModel(2)
+
+    def late(rank):
+        if rank == 1:
+            time.sleep(0.15)
+        return model.wait(rank, timeout_s=5.0)
+    assert run_ranks(2, late) == [True, True]
