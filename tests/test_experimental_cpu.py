@@ -1177,3 +1177,68 @@ def test_async_sampler_adapter_over_server_and_batch_engines():
         await ad.stop()
     asyncio.run(server_case())
     asyncio.run(batch_case())
+
+
+def test_orchestrator_streaming_overlaps_training_with_rollout():
+    """With streaming, micro-batches reach the trainer while later prompts are still being generated; the set of
+    trajectories, the last-micro-batch flag and the update are the same as without."""
+    import threading
+    import time
+    import numpy as np
+    from tunix_b200.experimental.common.datatypes import RolloutResponse
+    from tunix_b200.experimental.orchestrator.algorithm_adapter import GRPOAdapter
+    from tunix_b200.experimental.orchestrator.batch_assembly import BatchConfig, create_batch_assembler
+    from tunix_b200.experimental.orchestrator.orchestrator import Orchestrator
+    from tunix_b200.experimental.orchestrator.worker_registry import WorkerRegistry
+    from tunix_b200.experimental.worker.mock_worker import MockWorker
+    busy = {"n": 0}
+    lock = threading.Lock()
+    log = []
+
+    def generate(req):
+        slow = int(req.group_id[1:]) >= 2                   # the later prompts take much longer
+        with lock:
+            busy["n"] += 1
+        time.sleep(0.25 if slow else 0.01)
+        with lock:
+            busy["n"] -= 1
+        n = 2 + req.seed % 3
+        return RolloutResponse(req.request_id, tokens=[10 + (req.seed + k) % 40 for k in range(n)], logprobs=[-0.3] * n,
+                               group_id=req.group_id, policy_version=req.policy_version, metadata=dict(req.metadata))
+
+    def train(req):
+        if req["op"] == "fwd_bwd":
+            log.append(("fwd_bwd", req["is_last_microbatch"], busy["n"], req["batch"]["input_tokens"].shape[0]))
+            return {"loss": 0.5}
+        log.append(("update",))
+        return {"grad_norm": 1.0, "step": sum(1 for e in log if e[0] == "update")}
+
+    def build(streaming):
+        reg = WorkerRegistry()
+        ws = [MockWorker(f"rollout-{i}", handler=generate, max_inflight=64) for i in range(2)] + [MockWorker("trainer-0", handler=train)]
+        for w in ws:
+            w.role = "trainer" if w.worker_id.startswith("trainer") else "rollout"
+            w.start()
+            reg.register(w)
+        return Orchestrator(reg, create_batch_assembler(BatchConfig(rows_per_microbatch=4, max_prompt_length=4, max_response_length=4),
+                                                        packed=False),
+                            GRPOAdapter(lambda item, r: float(sum(r.tokens) % 7)), group_size=4, streaming=streaming,
+                            rollout_params={"max_tokens": 4, "seed": 0})
+    prompts = [{"prompt_id": f"p{i}", "prompt_ids": [1, 5 + i]} for i in range(4)]
+    recs = {}
+    for streaming in (False, True):
+        log.clear()
+        orch = build(streaming)
+        recs[streaming] = orch.step(0, prompts)
+        orch.close()
+        steps = [e for e in log if e[0] == "fwd_bwd"]
+        assert [e[1] for e in steps] == [False] * (len(steps) - 1) + [True] and log[-1] == ("update",)
+        assert sum(e[3] for e in steps) == recs[streaming]["trajectories"]
+        if streaming:
+            assert any(e[2] > 0 for e in steps[:-1]), log            # a training pass ran while rollouts were in flight
+            assert recs[True]["microbatches_overlapped_with_rollout"] >= 1
+        else:
+            assert all(e[2] == 0 for e in steps)
+    for k in ("trajectories", "filtered_groups", "microbatches", "policy_version"):
+        assert recs[True][k] == recs[False][k], k
+    assert abs(recs[True]["reward_mean"] - recs[False]["reward_mean"]) < 1e-6

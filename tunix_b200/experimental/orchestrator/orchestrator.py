@@ -41,12 +41,14 @@ class AlgorithmAdapter:
 class Orchestrator:
     def __init__(self, registry, assembler, adapter: AlgorithmAdapter, *, group_size: int, window=None,
                  export_weights: Optional[Callable[[], Any]] = None, rollout_params: Optional[dict] = None,
-                 max_threads: int = 16):
+                 max_threads: int = 16, streaming: bool = False):
         self.registry, self.assembler, self.adapter = registry, assembler, adapter
         self.group_size, self.window = group_size, window
         self.export_weights = export_weights
         self.rollout_params = dict(rollout_params or {})
         self._pool = cf.ThreadPoolExecutor(max_workers=max_threads, thread_name_prefix="orchestrator")
+        self._group_pool = cf.ThreadPoolExecutor(max_workers=max(2, max_threads // 2), thread_name_prefix="orchestrator-group")
+        self.streaming = streaming
         self._rr = itertools.count()
         self._seed = itertools.count(int(self.rollout_params.pop("seed", None) or 0))     # every generation samples anew
         self.policy_version = 0
@@ -73,14 +75,15 @@ class Orchestrator:
                     self.excluded.add(w.worker_id)
         raise RuntimeError(f"rollout {req.request_id} failed on every worker") from last
 
-    def _group(self, step: int, item: dict) -> list:
+    def _group(self, step: int, item: dict, seeds: Optional[Sequence[int]] = None) -> list:
         pid = str(item.get("prompt_id", id(item)))
         reqs = []
+        seeds = list(seeds) if seeds is not None else [next(self._seed) for _ in range(self.group_size)]
         for g in range(self.group_size):
             lin = LineageContext(tracking_id=f"traj_{pid}_{g}")
             lin.add_event("engine.dispatch", "rollout", {"step": step, "policy_version": self.policy_version})
             reqs.append(RolloutRequest(f"{pid}/{g}", list(item["prompt_ids"]), group_id=pid, policy_version=self.policy_version,
-                                       metadata={"lineage": lin}, seed=next(self._seed), **self.rollout_params))
+                                       metadata={"lineage": lin}, seed=seeds[g], **self.rollout_params))
         return list(self._pool.map(self._one_rollout, reqs))
 
     def _payloads(self, item: dict, responses: Sequence) -> list:
@@ -108,34 +111,67 @@ class Orchestrator:
         for w in self._rollout_workers():
             w.sync_weights(self.policy_version, payload)
 
-    def step(self, step: int, prompts: Sequence[dict]) -> dict:
-        """One optimizer update from the given prompts (each rolled out `group_size` times)."""
+    def step(self, step: int, prompts: Sequence[dict], streaming: Optional[bool] = None) -> dict:
+        """One optimizer update from the given prompts (each rolled out `group_size` times).
+
+        With `streaming` (default: the constructor's setting) the trainer starts on the first micro-batch as soon as
+        enough groups have come back to fill it, while the remaining prompts are still being generated: rollout and
+        the training passes overlap instead of running one after the other (the reference's streaming gradient
+        accumulation, tunix/experimental/orchestrator/rl_program.py). One assembled micro-batch is always held
+        back so that the last one can be flagged for the sharded optimizer's gradient reduction."""
+        streaming = self.streaming if streaming is None else streaming
         trainer = self.registry.group("trainer").members()[0]
-        rewards, stats, losses, n_traj, filtered = [], [], [], 0, 0
-        batches = []
-        for item in prompts:
-            if self.window is not None and not self.window.admit(item):
-                continue
-            payloads = self._payloads(item, self._group(step, item))
+        rewards, stats, losses = [], [], []
+        count = {"traj": 0, "filtered": 0, "batches": 0, "overlapped": 0}
+        held: list = []
+
+        def train(batch, last: bool) -> None:
+            out = trainer.submit({"op": "fwd_bwd", "batch": batch.arrays, "is_last_microbatch": last})
+            batch.lineage.add_event("worker.trainer", "fwd_bwd", {"loss": out["loss"], "step": step})
+            losses.append(out["loss"])
+            stats.append(batch.stats)
+            count["batches"] += 1
+
+        def push(batches, rollouts_pending: bool) -> None:
+            for b in batches:
+                held.append(b)
+                if streaming and len(held) > 1:
+                    train(held.pop(0), False)
+                    count["overlapped"] += int(rollouts_pending)
+
+        def consume(item, responses, rollouts_pending: bool) -> None:
+            payloads = self._payloads(item, responses)
             if not payloads:
-                filtered += 1
+                count["filtered"] += 1
                 if self.window is not None:
                     self.window.on_group_filtered([item])
-                continue
-            rewards += [p.reward for p in payloads]
-            n_traj += len(payloads)
-            batches += list(self.assembler.feed(payloads))
+                return
+            rewards.extend(p.reward for p in payloads)
+            count["traj"] += len(payloads)
+            push(self.assembler.feed(payloads), rollouts_pending)
             if self.window is not None:
                 self.window.record_committed_groups([[item]])
-        batches += list(self.assembler.flush())
-        for i, b in enumerate(batches):
-            out = trainer.submit({"op": "fwd_bwd", "batch": b.arrays, "is_last_microbatch": i == len(batches) - 1})
-            b.lineage.add_event("worker.trainer", "fwd_bwd", {"loss": out["loss"], "step": step})
-            losses.append(out["loss"])
-            stats.append(b.stats)
-        rec = {"step": step, "trajectories": n_traj, "filtered_groups": filtered, "microbatches": len(batches),
+
+        admitted = [it for it in prompts if self.window is None or self.window.admit(it)]
+        if streaming:
+            # seeds are drawn here, in prompt order, so that a run does not depend on which group a thread picks up first
+            futs = {self._group_pool.submit(self._group, step, it, [next(self._seed) for _ in range(self.group_size)]): it
+                    for it in admitted}
+            left = len(futs)
+            for f in cf.as_completed(futs):
+                left -= 1
+                consume(futs[f], f.result(), left > 0)
+        else:
+            for it in admitted:
+                consume(it, self._group(step, it), False)
+        push(self.assembler.flush(), False)
+        while held:
+            train(held.pop(0), len(held) == 0)
+        rec = {"step": step, "trajectories": count["traj"], "filtered_groups": count["filtered"], "microbatches": count["batches"],
                "reward_mean": float(np.mean(rewards)) if rewards else 0.0, "loss": float(np.mean(losses)) if losses else None}
-        if batches:
+        if streaming:
+            rec["microbatches_overlapped_with_rollout"] = count["overlapped"]
+        if count["batches"]:
             up = trainer.submit({"op": "update"})
             rec.update(grad_norm=up["grad_norm"], train_step=up["step"], **summarize_padding_stats(stats))
             self._sync_weights()
@@ -154,3 +190,4 @@ class Orchestrator:
 
     def close(self) -> None:
         self._pool.shutdown(wait=False, cancel_futures=True)
+        self._group_pool.shutdown(wait=False, cancel_futures=True)
