@@ -1242,3 +1242,54 @@ def test_orchestrator_streaming_overlaps_training_with_rollout():
     for k in ("trajectories", "filtered_groups", "microbatches", "policy_version"):
         assert recs[True][k] == recs[False][k], k
     assert abs(recs[True]["reward_mean"] - recs[False]["reward_mean"]) < 1e-6
+
+
+def test_prompt_dataset_prefetch_skip_errors_and_early_close():
+    import asyncio
+    import threading
+    import time
+    from tunix_b200.experimental.orchestrator.dataset_utils import PrefetchIterator, iter_dataset_async, total_prompt_groups
+    assert total_prompt_groups(100, 8) == 800 and total_prompt_groups(100, 8, max_staleness=2) == (100 + 25) * 8
+    assert total_prompt_groups(8, 4, max_staleness=1) == (8 + 6) * 4
+    assert list(PrefetchIterator(["a", "b", "c"], skip_count=1)) == [(1, "b"), (2, "c")]
+    produced, closed = [], threading.Event()
+
+    def gen(n, fail_at=None):
+        try:
+            for i in range(n):
+                if i == fail_at:
+                    raise OSError("shard missing")
+                produced.append(i)
+                yield {"prompt": i}
+        finally:
+            closed.set()
+    assert [(i, d["prompt"]) for i, d in PrefetchIterator(gen(6), skip_count=2, prefetch_size=2)] == [(i, i) for i in range(2, 6)]
+    assert closed.is_set()
+    # bounded look-ahead: the producer stays at most prefetch_size (+ the one in hand) ahead of the consumer
+    produced.clear(); closed.clear()
+    it = PrefetchIterator(gen(100), prefetch_size=3)
+    assert next(it)[0] == 0
+    time.sleep(0.2)
+    assert len(produced) <= 1 + 3 + 1
+    it.close()                                              # stopping early closes the generator
+    assert closed.wait(2.0) and len(produced) < 100
+    # the dataset's failure arrives at its position
+    got = []
+    with pytest.raises(OSError, match="shard missing"):
+        for i, _ in PrefetchIterator(gen(10, fail_at=3)):
+            got.append(i)
+    assert got == [0, 1, 2]
+
+    async def consume():
+        out = []
+        async for i, d in iter_dataset_async(gen(5), skip_count=1, prefetch_size=2):
+            out.append(i)
+            if i == 3:
+                break
+        return out
+    closed.clear()
+    assert asyncio.run(consume()) == [1, 2, 3]
+
+    async def consume_list():
+        return [i async for i, _ in iter_dataset_async([10, 11, 12], skip_count=2)]
+    assert asyncio.run(consume_list()) == [2]
