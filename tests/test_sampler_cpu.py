@@ -236,6 +236,18 @@ def test_openai_style_http_front_end_over_the_engine_server():
             with ThreadPoolExecutor(96) as ex:              # a burst of connections larger than a default listen backlog
                 res = list(ex.map(lambda i: _http(http.url + "/v1/completions", {"prompt": "y" * (1 + i % 7), "max_tokens": 1}), range(192)))
             assert all(r[0] == 200 for r in res)
+            # n samples per prompt (a GRPO group in one request) and stop strings
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": ["ab", "abc"], "max_tokens": 3, "n": 3})
+            ch = json.loads(raw)["choices"]
+            assert st == 200 and [c["index"] for c in ch] == list(range(6)) and ch[0]["text"] == ch[2]["text"] != ch[3]["text"]
+            full = ch[0]["text"]
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": "ab", "max_tokens": 3, "stop": [full[1:], "zzzz"]})
+            c0 = json.loads(raw)["choices"][0]
+            assert c0["text"] == full[:1] and c0["finish_reason"] == "stop" and json.loads(raw)["usage"]["completion_tokens"] == 3
+            st, _, raw = _http(http.url + "/v1/chat/completions", {"messages": msgs, "max_tokens": 2, "n": 2})
+            assert st == 200 and len(json.loads(raw)["choices"]) == 2 and json.loads(raw)["usage"]["completion_tokens"] == 4
+            assert _http(http.url + "/v1/completions", {"prompt": "a", "n": 0})[0] == 400
+            assert _http(http.url + "/v1/completions", {"prompt": "a", "stop": [""]})[0] == 400
             # errors
             assert _http(http.url + "/v1/completions", {"prompt": 5})[0] == 400
             assert _http(http.url + "/v1/completions", {"prompt": "a", "max_tokens": 0})[0] == 400
@@ -248,7 +260,7 @@ def test_openai_style_http_front_end_over_the_engine_server():
             assert st == 200 and ctype.startswith("text/plain")
             vals = {l.split(" ")[0]: float(l.split(" ")[1]) for l in text.splitlines() if l and not l.startswith("#")}
             assert vals["tunix_b200_http_requests_total"] == http.requests_served >= 14 + 192
-            assert vals['tunix_b200_http_errors_total{status="400"}'] == 3 and vals['tunix_b200_http_errors_total{status="503"}'] == 1
+            assert vals['tunix_b200_http_errors_total{status="400"}'] == 5 and vals['tunix_b200_http_errors_total{status="503"}'] == 1
             assert vals["tunix_b200_http_completion_tokens_total"] >= 3 + 6 + 4 + 2 + 16 and vals["tunix_b200_http_requests_in_flight"] == 0
             assert vals['tunix_b200_http_request_seconds_bucket{le="+Inf"}'] == vals["tunix_b200_http_request_seconds_count"] == http.requests_served
 

@@ -7,8 +7,8 @@ Routes:
     GET  /health, /v1/models        liveness and the served model's name
     GET  /metrics                   Prometheus text format: requests, errors by status, prompt / completion tokens,
                                     request latency histogram, requests in flight
-    POST /v1/completions            {"prompt": str | [str], "max_tokens", "stream"}
-    POST /v1/chat/completions       {"messages": [{"role", "content"}], "max_tokens", "stream"}
+    POST /v1/completions            {"prompt": str | [str], "max_tokens", "n", "stop", "logprobs", "stream"}
+    POST /v1/chat/completions       {"messages": [{"role", "content"}], "max_tokens", "n", "stop", "stream"}
 
 Every HTTP request becomes one `submit()` on the engine server and joins the running batch at its next check point;
 one handler thread per connection waits for its own future, so concurrency on the wire turns directly into batch
@@ -228,12 +228,35 @@ class OpenAIServer:
             raise errs[0]
         return out
 
+    @staticmethod
+    def _n(body: dict) -> int:
+        n = body.get("n", 1)
+        if isinstance(n, bool) or not isinstance(n, int) or not 1 <= n <= 64:
+            raise _BadRequest("n must be an integer between 1 and 64")
+        return n
+
+    @staticmethod
+    def _apply_stop(result: dict, body: dict) -> dict:
+        """Cut the text at the first stop string (the tokens and their count stay what the engine produced)."""
+        stop = body.get("stop")
+        if stop is None:
+            return result
+        stops = [stop] if isinstance(stop, str) else stop
+        if not isinstance(stops, list) or not all(isinstance(x, str) and x for x in stops):
+            raise _BadRequest("stop must be a non-empty string or a list of them")
+        cut = min((i for i in (result["text"].find(x) for x in stops) if i >= 0), default=-1)
+        if cut >= 0:
+            result = dict(result, text=result["text"][:cut], finish_reason="stop")
+        return result
+
     def _completions(self, h, body: dict) -> None:
         prompt = body.get("prompt")
         prompts = [prompt] if isinstance(prompt, str) else prompt
         if not isinstance(prompts, list) or not prompts or not all(isinstance(p, str) for p in prompts):
             raise _BadRequest("prompt must be a string or a list of strings")
-        results = self._many(prompts, body)
+        n = self._n(body)
+        self._apply_stop({"text": ""}, body)                # validate before generating
+        results = [self._apply_stop(r, body) for r in self._many([p for p in prompts for _ in range(n)], body)]
         rid, now = "cmpl-" + uuid.uuid4().hex, int(time.time())
         base = {"id": rid, "object": "text_completion", "created": now, "model": body.get("model") or self.model_name}
         choices = [{"index": i, "text": r["text"], "finish_reason": r["finish_reason"],
@@ -254,7 +277,10 @@ class OpenAIServer:
                 raise _BadRequest("every message needs a role and a content")
             msgs.append({"role": m.get("role", "user"), "content": m["content"]})
         prompt = self.chat_parser.parse(msgs, add_generation_prompt=True, is_first_msg=True)
-        r = self._generate(prompt, body)
+        n = self._n(body)
+        self._apply_stop({"text": ""}, body)
+        results = [self._apply_stop(x, body) for x in self._many([prompt] * n, body)]
+        r = results[0]
         rid, now = "chatcmpl-" + uuid.uuid4().hex, int(time.time())
         model = body.get("model") or self.model_name
         if body.get("stream"):
@@ -265,9 +291,9 @@ class OpenAIServer:
             return
         self._send_json(h, 200, {
             "id": rid, "object": "chat.completion", "created": now, "model": model,
-            "choices": [{"index": 0, "message": {"role": "assistant", "content": r["text"]},
-                         "finish_reason": r["finish_reason"]}],
-            "usage": self._usage([r]), "sampling": self.sampling})
+            "choices": [{"index": i, "message": {"role": "assistant", "content": x["text"]}, "finish_reason": x["finish_reason"]}
+                        for i, x in enumerate(results)],
+            "usage": self._usage(results), "sampling": self.sampling})
 
 
 class PooledBackend:
