@@ -170,3 +170,37 @@ def test_frozenlake_environment_and_multi_turn_episode():
         e.reset()
         runs.append([e.step("```Down```")[3].get("moved") for _ in range(3) if e.step_count < 3])
     assert runs[0] == runs[1]
+
+
+def test_episode_over_http_against_a_remote_engine_server():
+    """A FrozenLake episode whose model calls go over HTTP to the OpenAI-style front end: prompts travel as token
+    ids, sampled ids and log-probs come back and are what the trajectory records."""
+    from tests.test_sampler_cpu import _FakeEngine
+    from tunix_b200.generate.engine import EngineServer
+    from tunix_b200.generate.openai_server import serve
+    from tunix_b200.rl.agentic.environments.frozenlake_environment import FrozenLakeAgent, FrozenLakeEnv
+    from tunix_b200.rl.agentic.http_model_client import HTTPModelClient, RemoteModelError
+    tok = CharTok()
+    fake = _FakeEngine(slots=4)
+    fake.cache_size = 8192
+    with EngineServer(fake, max_new_tokens=6, max_prompt_length=4096, eos_tokens=[2]) as eng, \
+            serve(eng, tok, model_name="toy") as http:
+        client = HTTPModelClient(http.url, route_key="episode-1")
+        out = client.generate([1, 30, 31], max_tokens=3)
+        assert out["tokens"] == [32, 33, 34] and out["logprobs"] == [0.0] * 3 and out["text"] == tok.decode([32, 33, 34])
+        env = FrozenLakeEnv({"map": ["S_", "_G"]}, max_steps=3)
+        engine = TrajectoryCollectEngine(FrozenLakeAgent(), env, model_call=client.with_route_key("episode-2"), tokenizer=tok,
+                                         chat_parser=get_parser("qwen"), max_steps=3)
+        res = asyncio.run(engine.collect("Token"))
+        # the scripted engine continues from the prompt's last token, which is no move: the environment reminds, three turns pass
+        assert res["num_turns"] == 3 and res["trajectory_reward"] == 0.0 and res["status"] != TrajectoryStatus.FAILED
+        assert (res["conversation_masks"] == 1).sum() == 3 * 6 and client.calls == 1 + 3
+        with pytest.raises(RemoteModelError, match="400"):
+            client.generate([], 2)
+        with pytest.raises(ValueError):
+            asyncio.run(client(chat_completions=[{"role": "user", "content": "hi"}]))
+        chat = HTTPModelClient(http.url, tokenizer=tok, chat_parser=get_parser("qwen"))
+        assert len(asyncio.run(chat(chat_completions=[{"role": "user", "content": "hi"}], max_tokens=2))["tokens"]) == 2
+    down = HTTPModelClient(http.url, retries=1, timeout=2.0)
+    with pytest.raises(RemoteModelError, match="no answer"):
+        down.generate([1, 2], 1)

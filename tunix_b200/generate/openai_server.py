@@ -7,7 +7,9 @@ Routes:
     GET  /health, /v1/models        liveness and the served model's name
     GET  /metrics                   Prometheus text format: requests, errors by status, prompt / completion tokens,
                                     request latency histogram, requests in flight
-    POST /v1/completions            {"prompt": str | [str], "max_tokens", "n", "stop", "logprobs", "stream"}
+    POST /v1/completions            {"prompt": str | [int] | [str | [int]], "max_tokens", "n", "stop", "logprobs", "stream"}
+                                    (token ids as a prompt reach the engine untouched; with "logprobs" the answer
+                                    carries the sampled token ids and their log-probs, which is what RL needs)
     POST /v1/chat/completions       {"messages": [{"role", "content"}], "max_tokens", "n", "stop", "stream"}
 
 Every HTTP request becomes one `submit()` on the engine server and joins the running batch at its next check point;
@@ -167,8 +169,9 @@ class OpenAIServer:
                 "data": [{"id": self.model_name, "object": "model"}]}
 
     # ------------------------------------------------------------------ generation
-    def _generate(self, prompt: str, body: dict) -> dict:
-        ids = self.tokenizer.encode(prompt)
+    def _generate(self, prompt, body: dict) -> dict:
+        """`prompt`: text, or token ids (then nothing is tokenised here and the caller's ids reach the engine as is)."""
+        ids = self.tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
         if not ids:
             raise _BadRequest("empty prompt")
         max_tokens = body.get("max_tokens")
@@ -251,9 +254,10 @@ class OpenAIServer:
 
     def _completions(self, h, body: dict) -> None:
         prompt = body.get("prompt")
-        prompts = [prompt] if isinstance(prompt, str) else prompt
-        if not isinstance(prompts, list) or not prompts or not all(isinstance(p, str) for p in prompts):
-            raise _BadRequest("prompt must be a string or a list of strings")
+        is_ids = lambda p: isinstance(p, list) and p and all(isinstance(t, int) and not isinstance(t, bool) for t in p)
+        prompts = [prompt] if isinstance(prompt, str) or is_ids(prompt) else prompt
+        if not isinstance(prompts, list) or not prompts or not all(isinstance(p, str) or is_ids(p) for p in prompts):
+            raise _BadRequest("prompt must be a string, a list of token ids, or a list of either")
         n = self._n(body)
         self._apply_stop({"text": ""}, body)                # validate before generating
         results = [self._apply_stop(r, body) for r in self._many([p for p in prompts for _ in range(n)], body)]
