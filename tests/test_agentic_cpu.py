@@ -114,7 +114,7 @@ def test_agentic_grpo_learner_end_to_end():
     from tunix_b200.rl.rl_cluster import RLCluster
     cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
     actor, ref = create_model(cfg, seed=0), create_model(cfg, seed=0)
-    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=3, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
                           train_micro_batch_size=2)
     rc = RolloutConfig(max_tokens_to_generate=5, max_prompt_length=16, temperature=1.0, seed=1, kv_cache_size=64, eos_tokens=[63])
     cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(), cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
@@ -128,6 +128,17 @@ def test_agentic_grpo_learner_end_to_end():
     assert cl.global_steps == 2 and learner.policy_version == 2
     after = torch.cat([p.detach().reshape(-1) for p in actor.parameters()])
     assert cl.metrics_logger.metric_exists("", "trajectory/valid_frac", "train")
+    # an external model client (e.g. the HTTP one) replaces the cluster's engine for the episodes' model calls
+    calls = []
+
+    async def client(chat_completions=None, prompt_token_ids=None, max_tokens=None):
+        calls.append(len(prompt_token_ids))
+        n = 2 + len(calls) % 3
+        return {"text": "x" * n, "tokens": [5 + (len(calls) + k) % 50 for k in range(n)], "logprobs": [-1.0] * n}
+    remote = AgenticGRPOLearner(cl, [length_reward], GRPOConfig(num_generations=2, beta=0.04), max_concurrency=4,
+                                chat_parser=get_parser("raw"), model_client=client)
+    remote.train([{"prompts": ["ab", "cd"]}, {"prompts": ["ef", "gh"]}, {"prompts": ["ij", "kl"]}])   # two consumed: resumed past
+    assert len(calls) == 4 and cl.global_steps == 3
 
 
 def test_frozenlake_environment_and_multi_turn_episode():

@@ -17,7 +17,7 @@ _EXPORTS = {
     "PPOLearner": "rl.ppo.ppo_learner", "PPOConfig": "rl.algorithm_config",
     "AgenticGRPOLearner": "rl.agentic.agentic_grpo_learner",
     # generation and models
-    "Sampler": "generate.sampler", "PagedEngine": "generate.engine", "EngineServer": "generate.engine",
+    "Sampler": "generate.sampler", "PagedEngine": "generate.engine", "EngineServer": "generate.engine", "OpenAIServer": "generate.openai_server",
     "CacheConfig": "common.configs", "Gemma4Config": "models.gemma4", "Gemma4Multimodal": "models.gemma4_vision",
     "TokenizerAdapter": "generate.tokenizer_adapter", "AutoModel": "models.automodel", "ModelConfig": "models.config",
     "Transformer": "models.transformer", "create_model": "models.transformer",

@@ -76,7 +76,12 @@ class AgenticRLLearner(abc.ABC):
     def __init__(self, rl_cluster: RLCluster, reward_fns, algo_config, *, agent_class=ModelAgent, agent_kwargs=None,
                  env_class=TaskEnvironment, env_kwargs=None, chat_parser=None, max_concurrency: int = 16,
                  off_policy_steps: int = 0, max_turns: int = 1, episode_timeout: float = 600.0, metric_fns=None,
-                 server_mode: bool = False):
+                 server_mode: bool = False, model_client=None):
+        """`model_client`: an `async (chat_completions, prompt_token_ids, max_tokens) -> {"text", "tokens",
+        "logprobs"}` that replaces the cluster's own rollout engine for the episodes' model calls, e.g.
+        `http_model_client.HTTPModelClient` in front of engines in another process. Keeping those engines' weights
+        current is then the deployment's job (`experimental.weight_sync`)."""
+        self.model_client = model_client
         self.rl_cluster, self.algo_config = rl_cluster, algo_config
         self.tcfg = rl_cluster.cluster_config.training_config
         self.agent_class, self.agent_kwargs = agent_class, dict(agent_kwargs or {})
@@ -130,6 +135,8 @@ class AgenticRLLearner(abc.ABC):
                 "policy_version": version}
 
     async def _model_call(self, chat_completions=None, prompt_token_ids=None, max_tokens=None) -> dict:
+        if self.model_client is not None:
+            return await self.model_client(chat_completions=chat_completions, prompt_token_ids=prompt_token_ids, max_tokens=max_tokens)
         if self._server is not None:
             return await asyncio.get_running_loop().run_in_executor(self._server_pool, self._server_call,
                                                                    list(prompt_token_ids), max_tokens)
