@@ -669,7 +669,11 @@ def test_sql_trajectory_store_converter_and_explorer(tmp_path):
     traj = Trajectory(task={"question": "2+2"}, reward=1.0, status=TrajectoryStatus.SUCCEEDED, steps=[
         Step(model_response="<think>easy</think> 4", thought="easy", action=Action(action="4"), observation="2+2", reward=1.0,
              done=True, assistant_tokens=np.array([5, 6, 7]), assistant_masks=np.array([1, 1, 1]), logprobs=np.array([-0.1, -0.2, -0.3]))])
+    traj.steps[0].chat_completions = [{"role": "user", "content": "2+2?"}]
     rec = record_from_trajectory(traj, group_id="g9", policy_version=3, env="math")
+    worse = record_from_trajectory(traj, group_id="g9", policy_version=3)
+    worse["reward"] = 0.25
+    st.put(worse)
     tid = st.put(rec)
     back = st.get(tid)
     assert back["steps"][0]["assistant_tokens"] == [5, 6, 7] and back["steps"][0]["action"] == "4"
@@ -678,6 +682,12 @@ def test_sql_trajectory_store_converter_and_explorer(tmp_path):
     # the explorer on the SQL store, then exported to JSON lines and explored again
     out = io.StringIO()
     assert explorer.main([db, "stats"], out) == 0 and out.getvalue().count("\n") == 5           # header + versions 0, 1, 2, 3
+    sft = str(tmp_path / "sft.jsonl")                       # good conversations as chat rows for SFT (rejection sampling)
+    assert explorer.main([db, "export-sft", sft, "--best-of-group"], io.StringIO()) == 0
+    rows = [__import__("json").loads(l) for l in open(sft)]
+    assert len(rows) == 1 and rows[0]["reward"] == 1.0 and rows[0]["trajectory_id"] == tid
+    assert rows[0]["messages"] == [{"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "<think>easy</think> 4"}]
+    assert explorer.main([db, "export-sft", sft, "--min-reward", "0.2"], io.StringIO()) == 0 and len(open(sft).readlines()) == 2
     out = io.StringIO()
     assert explorer.main([db, "list", "--min-reward", "1.0"], out) == 0
     assert out.getvalue().count("\n") == 3 and "answer 5" in out.getvalue()
@@ -687,10 +697,10 @@ def test_sql_trajectory_store_converter_and_explorer(tmp_path):
     jl = str(tmp_path / "copy.jsonl")
     assert explorer.main([db, "export", jl], io.StringIO()) == 0
     fs = FileTrajectoryStore(jl)
-    assert len(list(fs.read())) == 7
+    assert len(list(fs.read())) == 8
     fs.close()
     out = io.StringIO()
-    assert explorer.main([jl, "list", "--group", "g9"], out) == 0 and out.getvalue().count("\n") == 1
+    assert explorer.main([jl, "list", "--group", "g9"], out) == 0 and out.getvalue().count("\n") == 2
     out1, out2 = io.StringIO(), io.StringIO()
     explorer.main([jl, "stats"], out1), explorer.main([db, "stats"], out2)
     assert out1.getvalue() == out2.getvalue()

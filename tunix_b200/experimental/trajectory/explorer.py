@@ -5,6 +5,8 @@ tunix/experimental/trajectory/).
     python -m tunix_b200.experimental.trajectory.explorer runs/traj.db list --min-reward 0.5 --limit 20
     python -m tunix_b200.experimental.trajectory.explorer runs/traj.jsonl show <trajectory_id>
     python -m tunix_b200.experimental.trajectory.explorer runs/traj.jsonl export out.db        (JSON lines -> SQL or back)
+    python -m tunix_b200.experimental.trajectory.explorer runs/traj.db export-sft best.jsonl --min-reward 1.0 --best-of-group
+                                                      (conversations of good trajectories as {"messages": [...]} rows for SFT)
 
 Works on both store formats; a JSON-lines file is scanned, a SQL store is queried."""
 from __future__ import annotations
@@ -80,6 +82,10 @@ def main(argv: Optional[list] = None, out=None) -> int:
     sh.add_argument("--json", action="store_true")
     ex = sub.add_parser("export")
     ex.add_argument("dest")
+    sft = sub.add_parser("export-sft")
+    sft.add_argument("dest")
+    sft.add_argument("--min-reward", type=float, default=None)
+    sft.add_argument("--best-of-group", action="store_true", help="keep only the highest-reward trajectory of each group")
     a = ap.parse_args(argv)
 
     if a.cmd == "stats":
@@ -112,6 +118,21 @@ def main(argv: Optional[list] = None, out=None) -> int:
                 return 0
         print(f"no trajectory {a.trajectory_id}", file=sys.stderr)
         return 1
+    if a.cmd == "export-sft":
+        rows = [r for r in _records(a.path, min_reward=a.min_reward) if (r.get("metadata") or {}).get("conversation")]
+        if a.best_of_group:
+            best: dict = {}
+            for r in rows:
+                key = r.get("group_id") if r.get("group_id") is not None else r["trajectory_id"]
+                if key not in best or r.get("reward", 0.0) > best[key].get("reward", 0.0):
+                    best[key] = r
+            rows = list(best.values())
+        with open(a.dest, "w", encoding="utf-8") as f:
+            for r in rows:
+                f.write(json.dumps({"messages": r["metadata"]["conversation"], "reward": r.get("reward", 0.0),
+                                    "trajectory_id": r["trajectory_id"]}) + "\n")
+        print(f"{len(rows)} conversations -> {a.dest}", file=out)
+        return 0
     if a.cmd == "export":
         dest = open_store(a.dest)
         n = 0

@@ -228,6 +228,10 @@ def record_from_trajectory(traj, group_id=None, policy_version: int = 0, **metad
                 step[k] = v
         steps.append(step)
     status = getattr(traj, "status", None)
+    last = traj.steps[-1] if getattr(traj, "steps", None) else None
+    if last is not None and getattr(last, "chat_completions", None):
+        # the whole conversation as chat messages: what the last call saw plus its answer
+        metadata.setdefault("conversation", list(last.chat_completions) + [{"role": "assistant", "content": last.model_response}])
     rec = new_record(steps, reward=float(getattr(traj, "reward", 0.0)), group_id=group_id, policy_version=policy_version,
                      status=getattr(status, "name", status), task=getattr(traj, "task", None), **metadata)
     return rec
