@@ -53,3 +53,27 @@ def test_grpo_and_ppo_main_run(tmp_path):
     assert cl.global_steps == 1
     cl = ppo_main.main(["x", BASE, *common])
     assert cl.global_steps == 1
+
+
+def test_sft_loader_reads_chat_rows_with_assistant_only_loss(tmp_path):
+    import json
+    import numpy as np
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200.cli.utils.data import chat_row_tokens, jsonl_sft
+    from tunix_b200.rl.agentic.parser.chat_template_parser import get_parser
+    tok, parser = CharTok(), get_parser("qwen")
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"},
+            {"role": "user", "content": "sure?"}, {"role": "assistant", "content": "yes"}]
+    ids, mask = chat_row_tokens(msgs, tok, parser)
+    assert ids == tok.encode(parser.parse(msgs)) and len(mask) == len(ids)
+    # the loss covers exactly the assistant's words and their end markers
+    want = sum(len(tok.encode(parser.render_message(m))) - len(tok.encode(parser.generation_prompt)) for m in msgs if m["role"] == "assistant")
+    assert int(sum(mask)) == want and mask[0] == 0.0 and mask[-1] == 1.0
+    path = tmp_path / "sft.jsonl"
+    with open(path, "w") as f:
+        f.write(json.dumps({"messages": msgs, "reward": 1.0}) + "\n")
+        f.write(json.dumps({"text": "plain text row"}) + "\n")
+    batch = next(iter(jsonl_sft(str(path), tok, 2, 256)))
+    toks, m = np.asarray(batch.input_tokens), np.asarray(batch.input_mask)
+    assert toks.shape == (2, 256) and m[0].sum() == want and toks[0, :len(ids)].tolist() == ids
+    assert m[1].sum() == len("plain text row") + 1

@@ -33,14 +33,38 @@ def synthetic_sft(batch_size, seq_len, vocab_size, num_batches, seed=0, prompt_l
         yield TrainingInput(ids, mask)
 
 
-def jsonl_sft(path, tokenizer, batch_size, max_target_length, epochs=1) -> Iterator[TrainingInput]:
+def chat_row_tokens(messages, tokenizer, chat_parser):
+    """Token ids of a conversation and a loss mask that is 1 on the assistant's turns only (their end marker
+    included, the role header the template puts before them excluded)."""
+    ids = list(tokenizer.encode(chat_parser.bos())) if chat_parser.bos() else []
+    mask = [0.0] * len(ids)
+    header = tokenizer.encode(chat_parser.generation_prompt) if chat_parser.generation_prompt else []
+    for m in messages:
+        t = tokenizer.encode(chat_parser.render_message(m))
+        learn = m.get("role") == "assistant"
+        skip = len(header) if learn and t[:len(header)] == header else 0
+        ids += t
+        mask += [0.0] * skip + [1.0 if learn else 0.0] * (len(t) - skip)
+    return ids, mask
+
+
+def jsonl_sft(path, tokenizer, batch_size, max_target_length, epochs=1, chat_parser=None) -> Iterator[TrainingInput]:
+    """Rows are {"text"}, {"src", "dst"} or {"messages": [{"role", "content"}, ...]} (chat rows, e.g. the
+    trajectory explorer's `export-sft`; the loss covers the assistant's turns)."""
     recs = [json.loads(l) for l in open(path) if l.strip()]
     pad = tokenizer.pad_id()
+    if chat_parser is None and any("messages" in r for r in recs):
+        from ...rl.agentic.parser.chat_template_parser import get_parser
+        chat_parser = get_parser("qwen", tokenizer)
     for _ in range(epochs):
         for s0 in range(0, len(recs) - batch_size + 1, batch_size):
             rows, masks = [], []
             for r in recs[s0:s0 + batch_size]:
-                if "src" in r:
+                if "messages" in r:
+                    t, m = chat_row_tokens(r["messages"], tokenizer, chat_parser)
+                    rows.append(t[:max_target_length])
+                    masks.append(m[:max_target_length])
+                elif "src" in r:
                     p = tokenizer.encode(r["src"])
                     c = tokenizer.encode(r["dst"]) + [tokenizer.eos_id()]
                     rows.append(([tokenizer.bos_id()] if tokenizer.bos_id() is not None else []) + p + c)
