@@ -746,6 +746,22 @@ def test_routing_pool_sticky_keys_failover_and_round_robin():
         list(ex.map(lambda i: pool.submit({"i": i}), range(40)))
     gained = {n: pool.stats()[n]["served"] - before[n] for n in ws}
     assert sum(gained.values()) == 40 and min(gained.values()) >= 5
+    # the pool follows a health monitor: a silent worker leaves the rotation before a request fails on it
+    from tunix_b200.experimental.common.datatypes import HealthReport, WorkerState
+    from tunix_b200.experimental.orchestrator.health_monitor import HealthMonitor
+    now = [0.0]
+    mon = HealthMonitor(heartbeat_timeout_s=10.0, clock=lambda: now[0])
+    for n in ws:
+        mon.observe(HealthReport(n, WorkerState.READY))
+    assert pool.apply_health(mon) == ([], [])
+    now[0] = 8.0
+    for n in ("w0", "w1", "w3"):
+        mon.observe(HealthReport(n, WorkerState.READY))
+    now[0] = 12.0                                           # w2 has been silent for 12 s
+    assert pool.apply_health(mon) == (["w2"], []) and pool.live() == ["w0", "w1", "w3"]
+    assert all(pool.submit({"route_key": k}) != "w2" for k in keys[:50]) and not ws["w2"].seen[-1:] == ["never"]
+    mon.observe(HealthReport("w2", WorkerState.READY))
+    assert pool.apply_health(mon) == ([], ["w2"]) and pool.live() == ["w0", "w1", "w2", "w3"]
     # a custom router wins over the key; everything down is an error, not a hang
     routed = RoutingPool(ws, router=lambda req, names: "w3" if req.get("big") else None)
     assert routed.submit({"big": True, "route_key": "conv-1"}) == "w3"

@@ -125,6 +125,30 @@ class RoutingPool:
                     self._inflight[name] -= 1
         raise NoWorkerAvailable(f"request failed on {tried} worker(s)") from last
 
+    def follow(self, monitor, period_s: float = 1.0) -> "threading.Event":
+        """Keep this pool's rotation in step with a `HealthMonitor`: workers it reports unhealthy (silent, failed,
+        stuck in a transitional state) are marked down before a request has to fail on them, and marked up again
+        once their reports are healthy. Returns the event that stops the follower thread."""
+        stop = threading.Event()
+
+        def loop():
+            while not stop.wait(period_s):
+                self.apply_health(monitor)
+        threading.Thread(target=loop, name="routing-pool-health", daemon=True).start()
+        return stop
+
+    def apply_health(self, monitor) -> tuple:
+        """One pass of `follow`; returns (marked down, marked up)."""
+        bad = {u.worker_id for u in monitor.check()}
+        good = set(monitor.healthy_workers())
+        with self._lock:
+            names = set(self._workers)
+            down = sorted((bad & names) - self._down)
+            up = sorted(good & names & self._down)
+            self._down |= set(down)
+            self._down -= set(up)
+        return down, up
+
     def stats(self) -> dict:
         with self._lock:
             return {n: {"served": self._served.get(n, 0), "inflight": self._inflight.get(n, 0), "down": n in self._down}
