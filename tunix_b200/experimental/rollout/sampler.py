@@ -12,7 +12,7 @@ from __future__ import annotations
 import asyncio
 import dataclasses
 import time
-from typing import Any, Optional, Protocol, Sequence
+from typing import Optional, Protocol, Sequence
 
 import numpy as np
 

@@ -16,7 +16,7 @@ import json
 import sys
 from typing import Iterator, Optional
 
-from .store import FileTrajectoryStore, SqliteTrajectoryStore, open_store
+from .store import SqliteTrajectoryStore, open_store
 
 
 def _records(path: str, group_id=None, min_version=None, min_reward=None, max_reward=None, limit=None) -> Iterator[dict]:

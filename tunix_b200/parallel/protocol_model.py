@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import threading
 import time
-from typing import Optional
 
 import numpy as np
 
