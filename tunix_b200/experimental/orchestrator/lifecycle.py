@@ -38,8 +38,15 @@ class LifecycleDriver:
         return sorted(failures, key=lambda t: t[0])
 
     def bring_up(self) -> None:
+        """Workers that are already serving (launched processes start themselves before they announce) are left
+        alone; the others are started side by side."""
+        from ..common.datatypes import WorkerState
+
+        def start(w):
+            if w.state not in (WorkerState.READY, WorkerState.BUSY):
+                w.start()
         ids = self.registry.worker_ids()
-        failures = self._each(ids, lambda w: w.start())
+        failures = self._each(ids, start)
         if failures:
             failed = {wid for wid, _ in failures}
             self._each([i for i in ids if i not in failed], lambda w: w.stop())
