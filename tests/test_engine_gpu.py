@@ -353,3 +353,49 @@ def test_tiered_page_pool_round_trip_on_device():
         for p in ids:
             assert torch.equal(pools[n][pool.page_idx(p)], want[n][p]), (n, p)
     assert pool.bytes_offloaded == pool.bytes_loaded == 8 * 2 * 64 * 2 * 128 * 2
+
+
+def test_http_front_end_and_model_client_over_the_real_engine():
+    """The serving path end to end on the device: HTTP request -> engine server -> paged engine's captured decode
+    step -> answer, greedy, compared with the same prompts generated by the engine directly; token-id prompts and
+    log-probs through the model client; counters on /metrics."""
+    import asyncio
+    import json
+    import urllib.request
+    from concurrent.futures import ThreadPoolExecutor
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import EngineServer, PagedEngine
+    from tunix_b200.generate.openai_server import serve
+    from tunix_b200.rl.agentic.http_model_client import HTTPModelClient
+    model, tok = _model(), Tok()
+    cc = CacheConfig(cache_size=128, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(3)
+    prompts = [[1] + rng.integers(3, 200, size=int(n)).tolist() for n in (5, 11, 3, 20, 8, 14)]
+    ref = PagedEngine(model, tok, cc, page_size=16, max_running_requests=8)(
+        prompt_token_ids=prompts, max_generation_steps=10, max_prompt_length=32, return_logprobs=True, eos_tokens=[2])
+    eng = PagedEngine(model, tok, cc, page_size=16, max_running_requests=4, check_every=4)
+    with EngineServer(eng, max_new_tokens=10, max_prompt_length=32, eos_tokens=[2]) as srv, serve(srv, tok, model_name="tiny") as http:
+        def post(ids):
+            body = json.dumps({"prompt": ids, "max_tokens": 10, "logprobs": True}).encode()
+            with urllib.request.urlopen(urllib.request.Request(http.url + "/v1/completions", data=body), timeout=120) as r:
+                return json.loads(r.read())
+        with ThreadPoolExecutor(6) as ex:
+            answers = list(ex.map(post, prompts))
+        same = total = 0
+        for ans, want, wlp in zip(answers, ref.tokens, ref.logprobs):
+            got = ans["choices"][0]["logprobs"]["tokens"]
+            n = min(len(got), len(want))
+            assert n >= 1 and ans["choices"][0]["text"] == tok.decode(got)
+            same += sum(int(a == int(b)) for a, b in zip(got[:n], want[:n]))
+            total += n
+            assert abs(ans["choices"][0]["logprobs"]["token_logprobs"][0] - float(wlp[0])) < 5e-2
+        assert same / total > 0.9, (same, total)
+        client = HTTPModelClient(http.url, route_key="ep0")
+        out = asyncio.run(client(prompt_token_ids=prompts[1], max_tokens=4))
+        assert out["tokens"][0] == int(ref.tokens[1][0]) and len(out["logprobs"]) == len(out["tokens"]) <= 4
+        with urllib.request.urlopen(http.url + "/metrics", timeout=30) as r:
+            text = r.read().decode()
+        assert "tunix_b200_http_requests_total 7" in text
+    _lib.raise_if_kernel_error()
+    assert eng.pool.free_pages == eng.pool.num_pages
