@@ -40,7 +40,7 @@ def reference_arm(args) -> int:
         import jax  # noqa: F401
     except Exception as e:  # ModuleNotFoundError in practice
         why = (f"reference not installable offline: pip --no-index cannot resolve its dependencies "
-               f"(jax, flax, optax, orbax, qwix, datasets absent from /opt/wheelhouse) and --no-deps fails "
+               f"(jax, flax, optax, orbax, qwix, datasets absent from the offline wheel directory) and --no-deps fails "
                f"in CMake (nanobind missing); import error: {type(e).__name__}: {e}")
     if why is None:
         why = "reference imported but its SFT path needs a JAX GPU backend that is not present"

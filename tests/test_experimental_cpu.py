@@ -554,9 +554,21 @@ def test_remote_worker_over_grpc_loopback():
         with pytest.raises(RemoteError):
             remote._invoke("_fail", None)                                 # private names are not callable remotely
         intruder = RemoteWorker(srv.address, token="guess")
-        with pytest.raises(RemoteError) as ei:
+        with pytest.raises(RemoteError, match="token"):
             intruder.info()
-        assert isinstance(ei.value.__cause__, PermissionError)
+        # a frame without a valid tag is refused before any of it is unpickled: this payload would set the flag
+        import cloudpickle, grpc
+        from tunix_b200.experimental.worker import remote_execution as rex
+
+        class Boom:
+            def __reduce__(self):
+                return (seen.update, ({"pwned": True},))
+        for frame in (cloudpickle.dumps(("guess", "info", (Boom(),), {})),            # an untagged pickle
+                      rex._seal(cloudpickle.dumps(("info", (Boom(),), {})), "guess")):   # tagged under the wrong token
+            with pytest.raises(grpc.RpcError) as rpc:
+                intruder._call(frame, timeout=10)
+            assert rpc.value.code() == grpc.StatusCode.UNAUTHENTICATED
+        assert "pwned" not in seen
         remote.close()
         intruder.close()
 

@@ -10,7 +10,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _train(rank, world, port, out):
+def _train(rank, world, port, out, variant="full"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if world > 1:
@@ -23,8 +23,15 @@ def _train(rank, world, port, out):
     from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
     torch.manual_seed(0)
     cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=256, embed_dim=64, hidden_dim=128, num_heads=2,
-                                           head_dim=32, num_kv_heads=1)
+                                           head_dim=32, num_kv_heads=1, qkv_bias=variant != "full")
     model = create_model(cfg, seed=0)
+    if variant == "lora":
+        from tunix_b200.lora import LoraProvider, apply_lora_to_model
+        apply_lora_to_model(model, LoraProvider(rank=4, alpha=8.0))
+        with torch.no_grad():
+            for n_, p_ in model.named_parameters():
+                if n_.endswith("lora_b"):
+                    p_.normal_(0.0, 0.05, generator=torch.Generator().manual_seed(11))
     g = torch.Generator().manual_seed(5)
     toks = torch.randint(0, 256, (4, 24), generator=g)
     mask = torch.ones(4, 24)
@@ -34,7 +41,7 @@ def _train(rank, world, port, out):
     tc = TrainingConfig(eval_every_n_steps=1000, max_steps=3, pbar_description=None)
     tr = PeftTrainer(model, opt, tc)
     tr.train([TrainingInput(toks, mask)] * 3)
-    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters() if p.requires_grad])
     if rank == 0:
         torch.save(flat, out)
     if world > 1:
@@ -46,6 +53,16 @@ def test_two_gloo_ranks_match_single_process(tmp_path):
     single, double = str(tmp_path / "s.pt"), str(tmp_path / "d.pt")
     _train(0, 1, 0, single)
     mp.spawn(_train, args=(2, 29731, double), nprocs=2, join=True)
+    a, b = torch.load(single), torch.load(double)
+    assert torch.allclose(a, b, atol=2e-5, rtol=1e-4), (a - b).abs().max()
+
+
+@pytest.mark.parametrize("variant", ["bias", "lora"])
+def test_two_gloo_ranks_match_single_process_with_biases_and_adapters(tmp_path, variant):
+    """Bias and adapter gradients do not come from the wgrad epilogue; they must reach the sharded update too."""
+    single, double = str(tmp_path / "s.pt"), str(tmp_path / "d.pt")
+    _train(0, 1, 0, single, variant)
+    mp.spawn(_train, args=(2, 29733 if variant == "bias" else 29735, double, variant), nprocs=2, join=True)
     a, b = torch.load(single), torch.load(double)
     assert torch.allclose(a, b, atol=2e-5, rtol=1e-4), (a - b).abs().max()
 

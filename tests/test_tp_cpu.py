@@ -97,3 +97,57 @@ def test_vocab_parallel_logprobs_match_full_head(tmp_path):
         res = torch.load(str(tmp_path / "vp") + f".{rank}")
         for key, errs in res.items():
             assert max(errs) < 2e-4, (rank, key, errs)
+
+
+def _ckpt(rank, world, port, root, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.parallel import tp as tp_lib
+    from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=128, embed_dim=32, hidden_dim=64, num_heads=2,
+                                           head_dim=16, num_kv_heads=2)
+
+    def build(seed):
+        m = create_model(cfg, seed=seed)
+        return tp_lib.apply_tensor_parallel(m, tp_lib.TPContext(device="cpu"))
+
+    g = torch.Generator().manual_seed(5)
+    toks, mask = torch.randint(0, 128, (2, 16), generator=g), torch.ones(2, 16)
+    tc = TrainingConfig(eval_every_n_steps=1000, max_steps=2, pbar_description=None, checkpoint_root_directory=root,
+                        checkpointing_options={"save_interval_steps": 1, "enable_async_checkpointing": rank == 0})
+    tr = PeftTrainer(build(0), optim.AdamW(1e-2, weight_decay=0.0), tc)
+    tr.train([TrainingInput(toks, mask)] * 2)                      # every rank calls save(); one of them writes
+    trained = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    mu = {n: t.clone() for n, t in tr.optimizer.state_dict()["mu"].items()}
+    dist.barrier()
+    # a fresh, differently initialised model picks the state up on construction (resume_from_checkpoint_on_init)
+    tr2 = PeftTrainer(build(1), optim.AdamW(1e-2, weight_decay=0.0), tc)
+    ok = tr2.train_steps == 2
+    for n, p in tr2.model.named_parameters():
+        ok = ok and torch.equal(p.detach(), trained[n])
+    for n, t in tr2.optimizer.state_dict()["mu"].items():
+        ok = ok and torch.allclose(t, mu[n])
+    torch.save({"ok": bool(ok), "shapes": {n: tuple(p.shape) for n, p in trained.items()}}, f"{out}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_checkpoint_of_a_tp_sliced_model_holds_whole_tensors_and_restores_each_slice(tmp_path):
+    root, out = str(tmp_path / "ck"), str(tmp_path / "res")
+    mp.spawn(_ckpt, args=(2, 29745, root, out), nprocs=2, join=True)
+    res = [torch.load(f"{out}.{r}") for r in range(2)]
+    assert all(r["ok"] for r in res)
+    from tunix_b200.sft.checkpoint_manager import _load_item
+    import json
+    saved = _load_item(os.path.join(root, "2", "model_params"))
+    q = saved["layers"]["0"]["self_attn"]["q_proj"]["weight"]            # nested by name parts, whole rows
+    assert tuple(q.shape) == (32, 32) and res[0]["shapes"]["layers.0.self_attn.q_proj.weight"] == (16, 32)
+    assert tuple(saved["layers"]["0"]["mlp"]["down_proj"]["weight"].shape) == (32, 64)
+    md = json.load(open(os.path.join(root, "2", "model_params", "_METADATA")))["tree_metadata"]
+    assert "('layers', '0', 'self_attn', 'q_proj', 'weight')" in md
+    assert sorted(d for d in os.listdir(root) if not d.isdigit()) == []   # no temporary directory left behind

@@ -536,11 +536,10 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
   if (tb_make_tmap_2d_bf16(&tdo, dout, (uint64_t)a.B * a.Tq, (uint64_t)a.N * H, lddo, BQ_, 64, 1)) return -3;
   if (tb_make_tmap_2d_bf16(&tk, k, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldk, BK_, 64, 1)) return -3;
   if (tb_make_tmap_2d_bf16(&tv, v, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldv, BK_, 64, 1)) return -3;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(attn_bwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
-    attr = true;
-  }
+  static DeviceOnce once;
+  if (once.first() &&
+      cudaFuncSetAttribute(attn_bwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess)
+    return -5;
   dim3 grid((a.Tk + BK_ - 1) / BK_, a.KH * C_::NHALF, a.B);
   attn_bwd_kernel<H><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -593,6 +592,7 @@ TB_API int tb_attn_bwd(const void* q, const void* k, const void* v, const void* 
 // ---------------------------------------------------------------------------------------------
 #include "noalloc.h"
 #include <cstdio>
+#include <mutex>
 
 namespace {
 
@@ -603,7 +603,8 @@ static __device__ __align__(256) float g_noalloc_delta_scratch[TB_NOALLOC_MAX_RO
 constexpr int kMaxDevices = 64;
 float* g_noalloc_dq_ptr[kMaxDevices] = {nullptr};
 float* g_noalloc_delta_ptr[kMaxDevices] = {nullptr};
-char g_noalloc_error[256] = "";
+std::mutex g_noalloc_setup_mutex;          // two host threads may make the first call on a device at once
+thread_local char g_noalloc_error[256] = "";   // each host thread reads the message of its own last call
 
 __global__ void noalloc_zero_kernel(float* p, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -622,6 +623,7 @@ int noalloc_fail(int code, const char* msg) {
 // In host code the array names above are host-side stand-ins, not device addresses; the real
 // addresses are looked up once per device, with that device current.
 int noalloc_setup(int dev) {
+  std::lock_guard<std::mutex> lock(g_noalloc_setup_mutex);
   if (g_noalloc_dq_ptr[dev] && g_noalloc_delta_ptr[dev]) return 0;
   float* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_dq_scratch);

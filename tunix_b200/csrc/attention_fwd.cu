@@ -329,11 +329,10 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnArgs& a, l
   if (tb_make_tmap_2d_bf16(&tq, q, (uint64_t)a.B * a.Tq, (uint64_t)a.N * H, ldq, BQ, 64, 1)) return -3;
   if (tb_make_tmap_2d_bf16(&tk, k, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldk, BKV, 64, 1)) return -3;
   if (tb_make_tmap_2d_bf16(&tv, v, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldv, BKV, 64, 1)) return -3;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(attn_fwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES);
-    attr = true;
-  }
+  static DeviceOnce once;
+  if (once.first() &&
+      cudaFuncSetAttribute(attn_fwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess)
+    return -5;
   dim3 grid((a.Tq + BQ - 1) / BQ, a.N, a.B);
   attn_fwd_kernel<H><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -311,6 +311,21 @@ tb_encode_tiled_fn tb_get_encode_tiled();
 // (tb_set_pdl, off by default), and the launcher that applies it.
 bool tb_pdl_enabled();
 
+// Function attributes (the dynamic shared-memory limit) are per device. A launcher keeps one flag table per
+// kernel instance and sets the attribute the first time it launches on each device, so that a process which
+// drives several GPUs gets the opt-in on every one of them.
+struct DeviceOnce {
+  bool done[64] = {};
+  // true exactly once per device (the current one); devices past the table are reported every time
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {

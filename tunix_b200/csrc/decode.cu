@@ -416,12 +416,10 @@ int launch_decode_v(int G, dim3 grid, cudaStream_t stream, const CUtensorMap& tm
                     int* status) {
   constexpr int TILE2 = 2 * TILE_KEYS * H * 2;                       // one stage: a K tile and a V tile
   constexpr int SMEM = STAGES * TILE2 + (TMA ? 1024 : 0);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_decode_kernel<H, TMA, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-      return -5;
-    attr_set = true;
-  }
+  static DeviceOnce once;
+  if (once.first() &&
+      cudaFuncSetAttribute(paged_decode_kernel<H, TMA, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+    return -5;
   // a split of one 64-key tile needs one stage only: more CTAs fit on an SM
   const int smem = split_tokens > TILE_KEYS ? SMEM : TILE2 + (TMA ? 1024 : 0);
   return launch_pdl(paged_decode_kernel<H, TMA, STAGES>, grid, dim3(128), smem, stream, tmK, tmV, q, ldq, kp, vp, pt, max_pages,

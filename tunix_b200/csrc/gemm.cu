@@ -1232,8 +1232,8 @@ TB_API int tb_gemm_rs_bf16(const void* A, long long lda, const void* B, long lon
 
 namespace {
 void set_gemm_attrs() {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce once;
+  if (once.first()) {
     cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          Cfg<256>::SMEM_BYTES);
     cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1242,7 +1242,6 @@ void set_gemm_attrs() {
                          Cfg<64>::SMEM_BYTES);
     cudaFuncSetAttribute(gemm_bf16_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          Cfg<32>::SMEM_BYTES);
-    attr_set = true;
   }
 }
 }  // namespace

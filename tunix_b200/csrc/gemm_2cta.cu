@@ -449,7 +449,8 @@ int launch_2cta(const void* A, const void* B, void* C, int M, int N, int K, long
                 cudaStream_t stream, const LseArgs& lse) {
   static const bool off = getenv("TUNIX_B200_NO_2CTA") != nullptr;
   if (off) return 0;
-  if (g_sms2 == 0) {
+  static DeviceOnce once;
+  if (once.first()) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sms2, cudaDevAttrMultiProcessorCount, dev);

@@ -246,7 +246,8 @@ int tb_gemm_splitk_try(const void* A, const void* B, void* C, int M, int N, int 
   // (down projections, K >= 8192: 40 -> 28 us at 64 x 4096 x 12288); at K = 4096 it wins up to 64 rows
   // (64 x 4096 x 4096: 23.6 -> 20.5 us, 16 rows: 23.6 -> 18.5 us) and loses from 128 rows on.
   if (M > 512 || N < 256 || K < (M <= 64 ? 4096 : 8192)) return 0;
-  if (g_sk_sms == 0) {
+  static DeviceOnce once;
+  if (once.first()) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sk_sms, cudaDevAttrMultiProcessorCount, dev);

@@ -305,3 +305,6 @@ TB_HOST_API int tb_count_router_replay_forced(const int16_t* routed, const int32
   out[1] = forced;
   return 0;
 }
+
+// Version of this library's C ABI; bumped when an exported signature changes.
+extern "C" __attribute__((visibility("default"))) int tb_host_abi_version() { return 2; }

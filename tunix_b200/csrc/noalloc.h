@@ -26,6 +26,9 @@
 //     contiguous; lse is [B, N, Tq] fp32 from the forward pass; status is a device int that receives
 //     a non-zero code if a bounded wait inside the kernel gives up (may be null).
 //   * No segment ids; query i sits at key position i + (Tk - Tq).
+//   * Host threads: the one-time address lookup is guarded by a mutex, and tb_noalloc_last_error()
+//     returns the message of the calling thread's own last call (thread-local storage). The GPU-side
+//     rule above still holds: calls from different threads must not overlap on the device.
 // Returns 0 on success, a negative code otherwise.
 #pragma once
 #include <cuda_runtime.h>

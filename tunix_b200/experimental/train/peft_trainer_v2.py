@@ -56,11 +56,12 @@ class TrainerV2(AbstractTrainer):
         if getattr(tr.optimizer, "is_sharded", False) and not self._closed_last:
             raise RuntimeError("a sharded optimizer reduces gradients during the last backward pass: "
                                "call fwd_bwd(..., is_last_microbatch=True) before update()")
+        local = False
         if tr._denoms and tr._denoms[0] is not None:
-            denominator = tr._reduce_denominator(torch.stack([d.float() for d in tr._denoms]).sum())
+            denominator, local = tr._reduce_denominator(torch.stack([d.float() for d in tr._denoms]).sum())
         else:
             denominator = float(len(tr._denoms))
-        grad_norm = tr._optimizer_step(denominator)
+        grad_norm = tr._optimizer_step(denominator, local)
         tr.optimizer.zero_grad()
         tr._denoms = []
         n, self._pending = self._pending, 0

@@ -23,6 +23,19 @@ def _native(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16
 
 
+def _deliver_grad(param, g: torch.Tensor):
+    """Hand a parameter gradient to its owner: added into `param.main_grad` when the optimizer gave the parameter a
+    slot in its flat gradient buffer (then autograd sees None), returned for autograd otherwise. Optimizers that
+    reduce a layer's gradients while backward is still running rely on every gradient of the layer having arrived
+    this way by the time backward leaves the layer."""
+    mg = getattr(param, "main_grad", None)
+    if mg is None:
+        return g
+    mg.add_(g.reshape(mg.shape).to(mg.dtype))
+    param.grad_added_to_main_grad = True
+    return None
+
+
 def _flat2d(x: torch.Tensor) -> torch.Tensor:
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1:
@@ -45,6 +58,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         ctx.x_shape = x.shape
         ctx.w_ref = w
+        ctx.b_ref = bias
         return y
 
     @staticmethod
@@ -62,7 +76,7 @@ class _LinearFn(torch.autograd.Function):
             else:
                 dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy.dtype)
+            db = _deliver_grad(ctx.b_ref, dy2.float().sum(0).to(dy.dtype))
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres
@@ -91,6 +105,7 @@ class _LoraDeltaFn(torch.autograd.Function):
         ctx.save_for_backward(x2, a, b, t)
         ctx.scale = scale
         ctx.x_shape = x.shape
+        ctx.a_ref, ctx.b_ref = a, b
         return y
 
     @staticmethod
@@ -104,7 +119,7 @@ class _LoraDeltaFn(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[0]:
             dx = K.gemm(dt, a, b_mn=True).view(ctx.x_shape)
-        return dx, da, db, dy, None
+        return dx, _deliver_grad(ctx.a_ref, da), _deliver_grad(ctx.b_ref, db), dy, None
 
 
 def lora_delta(x, a, b, base, scale: float):

@@ -163,21 +163,30 @@ class Optimizer:
             self._sumsq += b.grad_flat.float().pow(2).sum()
         return self._sumsq
 
-    def step(self, denominator: float = 1.0, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, denominator: Union[float, torch.Tensor] = 1.0, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Apply one update with grads / denominator. Returns the (pre-clip) global grad norm, a device scalar.
 
-        `sumsq` may be passed in when it was already reduced across ranks."""
+        `sumsq` may be passed in when it was already reduced across ranks. `denominator` may be a one-element
+        tensor on the parameters' device: the update kernel then divides by it on the device and the host never
+        reads it (the reference trainer likewise keeps the accumulated denominator inside its jitted step,
+        tunix/sft/peft_trainer.py:517-548)."""
         b = self.buffers
         b.collect_autograd_grads()
         if sumsq is None:
             sumsq = self.grad_sumsq()
         self.step_count += 1
         lr = self.learning_rate_at(self.step_count - 1)
+        if isinstance(denominator, torch.Tensor) and self._native() and self._device_denominator:
+            den = denominator.reshape(1).to(torch.float32).clamp_min(1e-8)
+            self._apply(lr, 1.0, sumsq, den)
+            return sumsq.sqrt() / den
         inv = 1.0 / max(float(denominator), 1e-8)
         self._apply(lr, inv, sumsq)
         return sumsq.sqrt() * inv
 
-    def _apply(self, lr: float, grad_scale: float, sumsq: torch.Tensor) -> None:
+    _device_denominator = False   # subclasses whose kernels read the denominator from device memory set this
+
+    def _apply(self, lr: float, grad_scale: float, sumsq: torch.Tensor, denom: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
     def _clip_scale_cpu(self, grad_scale: float, sumsq: torch.Tensor) -> float:
@@ -233,14 +242,16 @@ class AdamW(Optimizer):
             d["master"] = self.buffers.master
         return d
 
-    def _apply(self, lr, grad_scale, sumsq):
+    _device_denominator = True
+
+    def _apply(self, lr, grad_scale, sumsq, denom=None):
         b = self.buffers
         t = self.step_count
         if self._native():
             from .ops import kernels as K
             K.adamw(b.master_flat(), self.m, self.v, b.grad_flat, b.param_flat if b.master is not None else None,
                     lr=lr, beta1=self.b1, beta2=self.b2, eps=self.eps, weight_decay=self.weight_decay, step=t,
-                    grad_scale=grad_scale, max_norm=self.max_grad_norm or 0.0, sumsq_buf=sumsq)
+                    grad_scale=grad_scale, max_norm=self.max_grad_norm or 0.0, sumsq_buf=sumsq, denom_buf=denom)
             return
         scale = self._clip_scale_cpu(grad_scale, sumsq)
         with torch.no_grad():
@@ -275,7 +286,7 @@ class SGD(Optimizer):
             d["master"] = self.buffers.master
         return d
 
-    def _apply(self, lr, grad_scale, sumsq):
+    def _apply(self, lr, grad_scale, sumsq, denom=None):
         b = self.buffers
         scale = self._clip_scale_cpu(grad_scale, sumsq) if (self.max_grad_norm or not self._native()) else grad_scale
         if self._native():

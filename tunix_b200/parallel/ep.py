@@ -279,6 +279,7 @@ def shard_experts(model, ep: EPContext):
                     q = nn.Parameter(p.data[r * n:(r + 1) * n].clone(), requires_grad=p.requires_grad)
                     q.dp_sharded = True
                     q.shard_spec = (0, r, W)
+                    q.shard_group = ep.group
                     setattr(mod, name, q)
                 mod.ep = ep
                 mod.ep_group = ep.group if ep.group is not None else True

@@ -61,9 +61,11 @@ class ShardedAdamW(AdamW):
     is_sharded = True
 
     def __init__(self, learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-4, max_grad_norm=None,
-                 group=None, comm: str = "p2p", overlap: bool = True, barrier_timeout_ms: int = 30000):
+                 group=None, comm: str = "p2p", overlap: bool = True, barrier_timeout_ms: int = 30000,
+                 defer_gather: bool = True, gather_ctas: int = 24):
         super().__init__(learning_rate, b1, b2, eps, weight_decay, max_grad_norm)
         self.group, self.comm, self.overlap = group, comm, overlap
+        self.defer_gather, self.gather_ctas = defer_gather, gather_ctas
         self.barrier_timeout_ms = barrier_timeout_ms
         self._update_pending = True
         self._reduced: set = set()
@@ -120,7 +122,9 @@ class ShardedAdamW(AdamW):
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
         self.red32 = torch.zeros_like(self.master)
-        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._stats = torch.zeros(2, dtype=torch.float32, device=dev)   # [sum g^2 of the shard, denominator]
+        self._sumsq = self._stats[:1]
+        self._param_events: dict = {}
         # chunk tables per bucket
         self.shard_offsets, soff = [], 0
         for ln in self.lens:
@@ -164,10 +168,38 @@ class ShardedAdamW(AdamW):
     # -------------------------------------------------------------- backward
     def prepare_backward(self, is_update_step: bool) -> None:
         self._update_pending = is_update_step
+        if is_update_step and self.is_sharded and getattr(self, "params", None) is not None:
+            # the flags now tell which gradients of THIS backward pass have reached the flat buffer
+            for p in self.params:
+                p.grad_added_to_main_grad = False
 
     def install_hooks(self, model) -> None:
         """Ask the model to report when backward leaves each decoder layer (see Transformer.layer_grad_hook)."""
         model.layer_grad_hook = self.on_layer_backward_done
+        if not (self.is_sharded and getattr(self, "_native_dev", False) and self.comm_stream is not None
+                and self.comm == "p2p" and self.defer_gather):
+            return
+        # the parameter pulls of the last update may still be in flight when the next forward starts: every
+        # part of the model waits for its own bucket, anything unrecognised waits for all of them
+        layers = getattr(model, "layers", None)
+        if layers is None:
+            self.defer_gather = False
+            return
+        model.register_forward_pre_hook(lambda m, a: self.wait_bucket(-1))
+        for i, layer in enumerate(layers):
+            layer.register_forward_pre_hook(lambda m, a, i=i: self.wait_bucket(i))
+        known = set(range(len(layers))) | {-1, 10 ** 6}
+        if not set(self.bucket_tables) <= known:
+            self.defer_gather = False
+        self._tail_hooks(model)
+
+    def _tail_hooks(self, model) -> None:
+        tail = lambda *a, **k: self.wait_bucket(10 ** 6)  # noqa: E731
+        norm = getattr(model, "norm", None)
+        if norm is not None:
+            norm.register_forward_pre_hook(tail)
+        else:
+            self.defer_gather = False
 
     def on_layer_backward_done(self, layer_idx: int) -> None:
         """Called from autograd when all gradients of buckets > layer_idx .. are complete.
@@ -175,9 +207,35 @@ class ShardedAdamW(AdamW):
         Boundary `i` sits at the input of decoder layer i, boundary L at the output of the last layer."""
         if not (self.is_sharded and self._update_pending and self.overlap and self._native_dev):
             return
-        ready = [b for b in self.bucket_order if b >= layer_idx and b not in self._reduced]
+        ready = [b for b in self.bucket_order if b >= layer_idx and b not in self._reduced
+                 and self._bucket_complete(b)]
         if ready:
             self._reduce_buckets(ready)
+
+    def _bucket_complete(self, b: int) -> bool:
+        """A bucket may be reduced during backward only if every trainable tensor in it has already put this pass's
+        gradient into the flat buffer. Gradients that autograd delivers through `.grad` (ops without a
+        `main_grad` epilogue) are folded in here when they have arrived; a bucket still missing one waits for
+        `step()`, which reduces it after `collect_autograd_grads()`."""
+        for i in self._bucket_param_idx_cached(b):
+            p = self.params[i]
+            if not p.requires_grad:
+                continue
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(self.grad_dtype))
+                p.grad = None
+                p.grad_added_to_main_grad = True
+            if not getattr(p, "grad_added_to_main_grad", False):
+                return False
+        return True
+
+    def _bucket_param_idx_cached(self, b: int) -> list:
+        cache = getattr(self, "_bucket_idx", None)
+        if cache is None:
+            cache = self._bucket_idx = {}
+        if b not in cache:
+            cache[b] = self._bucket_param_idx(b)
+        return cache[b]
 
     def _reduce_buckets(self, buckets: list) -> None:
         lib = _lib.cuda()
@@ -241,16 +299,23 @@ class ShardedAdamW(AdamW):
     def zero_grad(self) -> None:
         if not self.is_sharded or self.world == 1:
             return super().zero_grad()
-        # peers finished reading these gradients before the post-update barrier completed (see step)
+        # peers finished reading these gradients before the barrier that follows the update completed, and the
+        # current stream already waits for that barrier (see _gather_params)
         self.grad_flat.zero_()
         for p in self.params:
             p.grad = None
 
-    def step(self, denominator: float = 1.0, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    reduces_denominator = True   # step(..., denominator_is_local=True) sums the ranks' denominators itself
+
+    def step(self, denominator=1.0, sumsq: Optional[torch.Tensor] = None,
+             denominator_is_local: bool = False) -> torch.Tensor:
+        """One sharded update. `denominator` is a float, or a one-element device tensor that the host never reads;
+        with `denominator_is_local` it is this rank's part and is summed over the group in the same all-reduce as
+        the squared gradient norm."""
         if self.world == 1:
             return super().step(denominator, sumsq)
         if not self._native_dev:
-            return self._step_cpu(denominator)
+            return self._step_cpu(denominator, denominator_is_local)
         lib = _lib.cuda()
         self.collect_autograd_grads()
         rest = [b for b in self.bucket_order if b not in self._reduced]
@@ -258,44 +323,98 @@ class ShardedAdamW(AdamW):
             self._reduce_buckets(rest)
         main = torch.cuda.current_stream()
         if self.comm_stream is not None:
+            # also orders this update after the previous step's parameter pulls and its closing barrier
             main.wait_stream(self.comm_stream)
-        dist.all_reduce(self._sumsq, group=self.group)
+        self._param_events = {}
+        den = self._stats[1:2]
+        if isinstance(denominator, torch.Tensor):
+            den.copy_(denominator.reshape(1).to(torch.float32))
+        else:
+            den.fill_(float(denominator))
+        if denominator_is_local:
+            dist.all_reduce(self._stats, group=self.group)      # [sum g^2, sum of denominators] in one message
+        else:
+            dist.all_reduce(self._sumsq, group=self.group)
+        den.clamp_(min=1e-8)
         self.step_count += 1
         lr = self.learning_rate_at(self.step_count - 1)
-        inv = 1.0 / max(float(denominator), 1e-8)
         from ..ops import kernels as K
         K.adamw(self.master, self.m, self.v, self.red32, self.shard16, lr=lr, beta1=self.b1, beta2=self.b2,
-                eps=self.eps, weight_decay=self.weight_decay, step=self.step_count, grad_scale=inv,
-                max_norm=self.max_grad_norm or 0.0, sumsq_buf=self._sumsq)
-        grad_norm = self._sumsq.sqrt() * inv
-        # every rank's bf16 shard is final and every rank is done reading gradients once this barrier passes
+                eps=self.eps, weight_decay=self.weight_decay, step=self.step_count, grad_scale=1.0,
+                max_norm=self.max_grad_norm or 0.0, sumsq_buf=self._sumsq, denom_buf=den)
+        grad_norm = self._sumsq.sqrt() / den
         if self.comm == "nccl":
             gathered = torch.empty(self.world * self.shard_total, dtype=self.shard16.dtype, device=self.shard16.device)
             dist.all_gather_into_tensor(gathered, self.shard16, group=self.group)
             ptr_arr = (ctypes.c_void_p * 8)(*[gathered.data_ptr() + r * self.shard_total * 2 for r in range(self.world)],
                                             *([None] * (8 - self.world)))
             shard_ptrs = ctypes.cast(ptr_arr, ctypes.c_void_p)
+            for b in self.bucket_order:
+                tab, n = self.bucket_tables[b]
+                _lib.check(lib.tb_allgather_pull(shard_ptrs, tab.data_ptr(), n, self.rank, self.world,
+                                                 self.param_flat.data_ptr(), 0, _lib.stream_ptr()), "tb_allgather_pull")
+                self.comm_launches += 1
         else:
-            self.barrier.wait(slot=1)
-            shard_ptrs = self.shard16_buf.c_ptrs
-        for b in self.bucket_order:
-            tab, n = self.bucket_tables[b]
-            _lib.check(lib.tb_allgather_pull(shard_ptrs, tab.data_ptr(), n, self.rank, self.world,
-                                             self.param_flat.data_ptr(), 0, _lib.stream_ptr()), "tb_allgather_pull")
-            self.comm_launches += 1
-        if self.comm != "nccl":
-            # peers must finish pulling this rank's shard before the next update overwrites it, and finish
-            # reading gradients before they are zeroed: both hold once everyone passed this point.
-            self.barrier.wait(slot=2)
+            self._gather_params(main)
         self._reduced.clear()
-        self._sumsq.zero_()
+        self._stats.zero_()
         return grad_norm
 
-    def _step_cpu(self, denominator: float) -> torch.Tensor:
+    def _gather_params(self, main) -> None:
+        """Pull every peer's updated bf16 shard into the resident copy, bucket by bucket in the order the next
+        forward pass uses them. With `overlap` the pulls run on the side stream and the next forward waits per
+        layer (`wait_bucket`), so only the first bucket's transfer is exposed; otherwise they run in line."""
+        lib = _lib.cuda()
+        deferred = self.comm_stream is not None and self.defer_gather
+        stream = self.comm_stream if deferred else main
+        if deferred:
+            ev = torch.cuda.Event()
+            ev.record(main)
+            stream.wait_event(ev)
+        with torch.cuda.stream(stream):
+            # every rank's bf16 shard is final and every rank is done reading gradients once this barrier passes
+            self.barrier.wait(slot=1)
+            if deferred:
+                grads_free = torch.cuda.Event()
+                grads_free.record(stream)
+            for b in sorted(self.bucket_tables):         # -1 (embeddings), layers 0..L-1, then the head
+                tab, n = self.bucket_tables[b]
+                _lib.check(lib.tb_allgather_pull(self.shard16_buf.c_ptrs, tab.data_ptr(), n, self.rank, self.world,
+                                                 self.param_flat.data_ptr(), self.gather_ctas if deferred else 0,
+                                                 stream.cuda_stream), "tb_allgather_pull")
+                self.comm_launches += 1
+                if deferred:
+                    e = torch.cuda.Event()
+                    e.record(stream)
+                    self._param_events[b] = e
+            # peers must finish pulling this rank's shard before the next update overwrites it: holds once
+            # everyone passed this point (the next update waits for this stream)
+            self.barrier.wait(slot=2)
+        if deferred:
+            main.wait_event(grads_free)      # the gradient buffer may be zeroed from here on
+
+    def wait_bucket(self, b: int) -> None:
+        """Make the current stream wait until bucket `b` of the parameters holds the latest update."""
+        ev = self._param_events.pop(b, None) if self._param_events else None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def wait_params(self) -> None:
+        """Make the current stream wait for every outstanding parameter pull (evaluation, checkpoints, weight
+        sync and anything else that reads parameters outside the layer-by-layer forward)."""
+        if self._param_events:
+            self._param_events = {}
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def _step_cpu(self, denominator, denominator_is_local: bool = False) -> torch.Tensor:
         """gloo ranks: all-reduce gradients, update the local shard with the same math, all-gather."""
         self.collect_autograd_grads()
         g = self.grad_flat.float()
         dist.all_reduce(g, group=self.group)
+        if denominator_is_local:
+            d = torch.as_tensor(denominator, dtype=torch.float32).reshape(1).clone()
+            dist.all_reduce(d, group=self.group)
+            denominator = float(d)
         inv = 1.0 / max(float(denominator), 1e-8)
         W, r = self.world, self.rank
         shard_g = torch.cat([g[o + r * (ln // W): o + (r + 1) * (ln // W)] for o, ln in zip(self.offsets, self.lens)])

@@ -72,6 +72,7 @@ def apply_weight_sharding(model, comm: CommContext, min_rows: int = 1):
                 mod.weight = nn.Parameter(mod.weight.data[r * n:(r + 1) * n].clone(), requires_grad=mod.weight.requires_grad)
                 mod.weight.dp_sharded = True
                 mod.weight.shard_spec = (0, r, W)
+                mod.weight.shard_group = comm.group
                 mod.dp_shard = comm
     model.dp_shard = comm
     return model

@@ -3,9 +3,8 @@
 Allocation and handle exchange use `torch.distributed._symmetric_memory` (CUDA VMM allocations whose
 handles travel over the process group's store); what comes back is, per buffer, the list of device
 pointers under which THIS rank can address EVERY rank's copy. Our own kernels (csrc/comm.cu) take that
-pointer table and move data with peer loads over NVLink. NVLS multicast is deliberately not used by
-default (`TUNIX_B200_NVLS=1` opts in where a kernel supports it): a rank that dies while bound to a
-multicast object can fault its peers.
+pointer table and move data with peer loads over NVLink. NVLS multicast is deliberately not used by any
+kernel of this package: a rank that dies while bound to a multicast object can fault its peers.
 
 On CPU (gloo) or a single rank the "symmetric" buffer is an ordinary tensor and the pointer table has
 one entry, so the same call sites work everywhere.

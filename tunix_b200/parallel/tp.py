@@ -310,13 +310,16 @@ def apply_tensor_parallel(model, tp: TPContext):
             for lin in (at.q_proj, at.k_proj, at.v_proj, mlp.gate_proj, mlp.up_proj):
                 lin.weight = nn.Parameter(shard_rows(lin.weight.data, r, W), requires_grad=lin.weight.requires_grad)
                 lin.weight.shard_spec = (0, r, W)
+                lin.weight.shard_group = tp.group
                 if lin.bias is not None:
                     lin.bias = nn.Parameter(shard_rows(lin.bias.data, r, W), requires_grad=lin.bias.requires_grad)
                     lin.bias.shard_spec = (0, r, W)
+                    lin.bias.shard_group = tp.group
                 lin.tp, lin.tp_mode = tp, "column"
             for lin in (at.o_proj, mlp.down_proj):
                 lin.weight = nn.Parameter(shard_cols(lin.weight.data, r, W), requires_grad=lin.weight.requires_grad)
                 lin.weight.shard_spec = (1, r, W)
+                lin.weight.shard_group = tp.group
                 lin.tp, lin.tp_mode = tp, "row"
     model.tp = tp
     for n, p in model.named_parameters():

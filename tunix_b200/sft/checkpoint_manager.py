@@ -8,10 +8,18 @@ Layout (tunix/sft/checkpoint_manager.py:124-358, fixture tests/sft/test_data/che
     <root>/<step>/optimizer_state/...            same, keys ('mu'|'nu'|'master', <param name>)
 
 Arrays are written as plain (non-OCDBT) zarr-v2 chunk files; bfloat16 uses dtype string "bfloat16"
-with the raw 2-byte payload. LoRA models save / restore adapter parameters only (partial restore).
+with the raw 2-byte payload. A parameter `layers.0.weight` is recorded in `_METADATA` under the key tuple
+('layers', '0', 'weight') and stored in the directory `layers.0.weight`, which is how Orbax names the arrays
+of a nested tree. LoRA models save / restore adapter parameters only (partial restore).
 Saves run on a background thread after a device->host copy (async checkpointing); policies:
 fixed step interval or "at least N seconds since the last save", keep the latest `max_to_keep`.
 `maybe_restore` returns `(step, custom_metadata)`.
+
+Several ranks: the decision to save is taken on rank 0 and broadcast (a wall-clock policy would otherwise let
+ranks disagree and hang the collectives below); every rank then takes part in gathering sharded state (a
+sharded optimizer's `state_dict()`, parameters that carry `shard_spec = (dim, index, count)` from the tensor /
+weight / expert parallel modules) so that the arrays written are whole tensors under their full names; only
+rank 0 touches the file system. On restore every rank reads the whole array and keeps its own slice.
 """
 from __future__ import annotations
 
@@ -71,9 +79,56 @@ def _flatten(tree: Any, prefix=()) -> dict:
     return out
 
 
+def _split_keys(tree: Any) -> Any:
+    """{'a.b.c': t} -> {'a': {'b': {'c': t}}}: dotted parameter names become the nested tree Orbax would see."""
+    if not isinstance(tree, dict):
+        return tree
+    out: dict = {}
+    for k, v in tree.items():
+        parts = str(k).split(".")
+        d = out
+        for part in parts[:-1]:
+            d = d.setdefault(part, {})
+            if not isinstance(d, dict):
+                raise ValueError(f"checkpoint key {k!r} is both a leaf and a prefix of another key")
+        if isinstance(d.get(parts[-1]), dict):
+            raise ValueError(f"checkpoint key {k!r} is both a leaf and a prefix of another key")
+        d[parts[-1]] = _split_keys(v)
+    return out
+
+
+def _dist():
+    import torch.distributed as dist
+    return dist if (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1) else None
+
+
+def _gather_sharded(t: torch.Tensor, owner) -> torch.Tensor:
+    """Whole tensor from the slices that the ranks of `owner.shard_group` hold along `owner.shard_spec[0]`.
+    Collective over that group; a tensor without a `shard_spec` comes back as it is."""
+    spec = getattr(owner, "shard_spec", None)
+    dist = _dist()
+    if spec is None or dist is None or spec[2] <= 1:
+        return t
+    dim, _, count = spec
+    group = getattr(owner, "shard_group", None)
+    t = t.detach().contiguous()
+    parts = [torch.empty_like(t) for _ in range(count)]
+    dist.all_gather(parts, t, group=group)
+    return torch.cat(parts, dim=dim)
+
+
+def _slice_for(t: torch.Tensor, owner) -> torch.Tensor:
+    spec = getattr(owner, "shard_spec", None)
+    if spec is None or spec[2] <= 1 or tuple(t.shape) == tuple(owner.shape):
+        return t
+    dim, index, count = spec
+    n = t.shape[dim] // count
+    return t.narrow(dim, index * n, n)
+
+
 def _save_item(path: str, tree: dict) -> None:
     os.makedirs(path, exist_ok=True)
-    flat = _flatten(tree)
+    flat = _flatten(_split_keys(tree))
     md = {}
     for key, val in flat.items():
         name = ".".join(key)
@@ -112,6 +167,7 @@ class CheckpointManager:
         self._last_save_time = time.time()
         self._thread: Optional[threading.Thread] = None
         self._error: Optional[BaseException] = None
+        self._decisions: dict = {}
         if self._root:
             os.makedirs(self._root, exist_ok=True)
 
@@ -141,21 +197,61 @@ class CheckpointManager:
             return time.time() - self._last_save_time >= o.save_interval_secs
         return False
 
+    def should_save(self, step: int, force: bool = False) -> bool:
+        """The decision for `step`, the same on every rank: rank 0 decides (its clock, its view of the directory)
+        and the others are told, because the gathers inside `save` are collectives."""
+        if not self._root:
+            return False
+        cached = self._decisions.get((step, force))
+        if cached is not None:
+            return cached
+        dist = _dist()
+        if dist is None:
+            decision = self._should_save(step, force)
+        else:
+            box = [self._should_save(step, force) if dist.get_rank() == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            decision = bool(box[0])
+        self._decisions = {(step, force): decision}
+        return decision
+
     # --------------------------------------------------------------------- save
     def save(self, step: int, model, optimizer=None, save_only_lora_params: bool = False, force: bool = False,
              custom_metadata: Optional[dict] = None) -> bool:
-        if not self._should_save(step, force):
+        if not self.should_save(step, force):
             return False
+        self._decisions = {}
         self.wait_until_finished()
         from ..lora import is_lora_param_name
-        # Device -> host copies happen here (synchronously); file IO on the worker thread.
-        params = {n: p.detach().to("cpu", copy=True) for n, p in model.named_parameters()
-                  if (not save_only_lora_params) or is_lora_param_name(n)}
+        dist = _dist()
+        writer = dist is None or dist.get_rank() == 0
+        # Collective part (every rank): whole tensors out of sharded ones. Device -> host copies happen here
+        # (synchronously) on the rank that writes; file IO on its worker thread.
+        owners = dict(model.named_parameters())
+        params = {}
+        for n, p in owners.items():
+            if save_only_lora_params and not is_lora_param_name(n):
+                continue
+            full = _gather_sharded(p.detach(), p)
+            if writer:
+                params[n] = full.to("cpu", copy=True)
         opt_state = None
         if optimizer is not None:
-            sd = optimizer.state_dict()
-            opt_state = {k: ({n: t.detach().to("cpu", copy=True) for n, t in v.items()} if isinstance(v, dict) else v)
-                         for k, v in sd.items()}
+            sd = optimizer.state_dict()           # a sharded optimizer gathers here, on every rank
+            opt_state = {}
+            for k, v in sd.items():
+                if isinstance(v, dict):
+                    d = {}
+                    for n, t in v.items():
+                        full = _gather_sharded(t.detach(), owners.get(n))
+                        if writer:
+                            d[n] = full.to("cpu", copy=True)
+                    opt_state[k] = d
+                else:
+                    opt_state[k] = v
+        self._last_save_time = time.time()
+        if not writer:
+            return True
         meta = {"step": step, "custom_metadata": custom_metadata or {}, "init_timestamp_nsecs": time.time_ns(),
                 "item_handlers": {"model_params": "StandardCheckpointHandler",
                                   "optimizer_state": "StandardCheckpointHandler"}}
@@ -169,6 +265,7 @@ class CheckpointManager:
                 _save_item(os.path.join(tmp, "model_params"), params)
                 if opt_state is not None:
                     _save_item(os.path.join(tmp, "optimizer_state"), opt_state)
+                meta["commit_timestamp_nsecs"] = time.time_ns()
                 with open(os.path.join(tmp, "_CHECKPOINT_METADATA"), "w") as f:
                     json.dump(meta, f)
                 shutil.rmtree(final, ignore_errors=True)
@@ -177,7 +274,6 @@ class CheckpointManager:
             except BaseException as e:  # surfaced on the next wait
                 self._error = e
 
-        self._last_save_time = time.time()
         if self._opts.enable_async_checkpointing:
             self._thread = threading.Thread(target=work, name="ckpt-save", daemon=True)
             self._thread.start()
@@ -213,6 +309,13 @@ class CheckpointManager:
         if not self._root:
             return 0, {}
         self.wait_until_finished()
+        dist = _dist()
+        if dist is not None:
+            dist.barrier()              # the writing rank has finished its last save
+            if step is None:
+                box = [self.latest_step() if dist.get_rank() == 0 else None]
+                dist.broadcast_object_list(box, src=0)
+                step = box[0]
         step = self.latest_step() if step is None else step
         if step is None:
             return 0, {}
@@ -227,15 +330,19 @@ class CheckpointManager:
                 if restore_only_lora_params and not is_lora_param_name(n):
                     continue
                 if n in saved:
-                    p.copy_(saved[n].to(p.device, p.dtype))
+                    p.copy_(_slice_for(saved[n], p).to(p.device, p.dtype))
                 elif not restore_only_lora_params and not saved_is_partial(saved):
                     raise KeyError(f"parameter {n} missing from checkpoint {d}")
         if optimizer is not None and os.path.isdir(os.path.join(d, "optimizer_state")):
             sd = _load_item(os.path.join(d, "optimizer_state"))
             fixed = {}
+            owners = dict(model.named_parameters())
+            unsharded_state = getattr(optimizer, "is_sharded", False)   # it slices whole tensors itself
             for k, v in sd.items():
                 if isinstance(v, dict):
-                    fixed[k] = {".".join(kk): vv for kk, vv in _flatten(v).items()}
+                    fixed[k] = {".".join(kk): (vv if unsharded_state or ".".join(kk) not in owners
+                                               else _slice_for(vv, owners[".".join(kk)]))
+                                for kk, vv in _flatten(v).items()}
                 else:
                     fixed[k] = v
             optimizer.load_state_dict(fixed)

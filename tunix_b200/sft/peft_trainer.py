@@ -211,12 +211,13 @@ class PeftTrainer:
         self._denoms.append(denom.detach() if denom is not None else None)
         grad_norm = None
         if is_update_step:
+            local = False
             if self._denoms and self._denoms[0] is not None:
                 total = torch.stack([d.float() for d in self._denoms]).sum()
-                denominator = self._reduce_denominator(total)
+                denominator, local = self._reduce_denominator(total)
             else:
                 denominator = float(len(self._denoms))
-            grad_norm = self._optimizer_step(denominator)
+            grad_norm = self._optimizer_step(denominator, local)
             self.optimizer.zero_grad()
             self._denoms = []
         if isinstance(metric, WeightedMetric):
@@ -226,20 +227,34 @@ class PeftTrainer:
             metric = metric.detach()
         return metric, aux, grad_norm
 
-    def _reduce_denominator(self, total: torch.Tensor) -> float:
-        """Global denominator of the update (summed over data-parallel ranks)."""
+    def _reduce_denominator(self, total: torch.Tensor):
+        """Denominator of the update -> (value, is_local). On a CUDA device the value stays a device tensor that
+        the update kernel divides by, so no step waits for the host to read it (the reference's jitted step keeps
+        it on the device as well, tunix/sft/peft_trainer.py:517-548). A sharded optimizer that sums denominators
+        together with its gradient norm gets this rank's part (`is_local`); otherwise the sum over the
+        data-parallel ranks is taken here."""
         import torch.distributed as dist
-        if dist.is_initialized() and dist.get_world_size() > 1 and getattr(self.optimizer, "is_sharded", False):
-            dist.all_reduce(total)
+        multi = dist.is_initialized() and dist.get_world_size() > 1
+        sharded = getattr(self.optimizer, "is_sharded", False)
         tp = getattr(self.model, "tp", None)
+        dps = getattr(self.model, "dp_shard", None)
+        local = False
+        if multi and sharded:
+            if getattr(self.optimizer, "reduces_denominator", False) and not (tp is not None and tp.world > 1):
+                local = True
+            else:
+                dist.all_reduce(total)
         if tp is not None and tp.world > 1:
             dist.all_reduce(total, group=tp.group)      # every tp rank scored its own sequences
-        dps = getattr(self.model, "dp_shard", None)
-        if dps is not None and dps.world > 1 and not getattr(self.optimizer, "is_sharded", False):
+        if dps is not None and dps.world > 1 and not sharded:
             dist.all_reduce(total, group=dps.group)
-        return float(max(total.item(), 1e-8))
+        if total.is_cuda:
+            return total.reshape(1), local
+        return float(max(total.item(), 1e-8)), local
 
-    def _optimizer_step(self, denominator: float):
+    def _optimizer_step(self, denominator, denominator_is_local: bool = False):
+        if denominator_is_local:
+            return self.optimizer.step(denominator, denominator_is_local=True)
         tp = getattr(self.model, "tp", None)
         if tp is not None and tp.world > 1:
             from ..parallel import tp as tp_lib
@@ -425,6 +440,8 @@ class PeftTrainer:
                 self._buffered_train_metrics.grad_norm = grad_norm
                 self._train_steps += 1
                 self._write_train_metrics()
+                if self.checkpoint_manager.should_save(self._train_steps):
+                    self._params_ready()
                 self.checkpoint_manager.save(self._train_steps, self.model, self.optimizer,
                                              save_only_lora_params=self._lora,
                                              custom_metadata=self._checkpoint_metadata())
@@ -432,12 +449,20 @@ class PeftTrainer:
                     self._run_eval(eval_ds)
             prof.maybe_deactivate(self._train_steps)
         self._throttler.wait_for_all()
+        self._params_ready()
         if self.training_hooks:
             self.training_hooks.on_train_end(self)
         if not self.is_managed_externally:
             self.close()
 
     _resume_skip = True
+
+    def _params_ready(self) -> None:
+        """Order the current stream after any parameter transfer that the optimizer left running on a side stream
+        (a sharded optimizer pulls the updated shards while the next forward pass already runs)."""
+        wait = getattr(self.optimizer, "wait_params", None)
+        if wait is not None:
+            wait()
 
     def _aux_metrics(self, aux) -> Optional[dict]:
         """aux dict of scalars -> {name: (value, reducer)} for the metrics buffer."""
