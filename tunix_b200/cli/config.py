@@ -23,7 +23,17 @@ import yaml
 from .. import optim as optim_lib
 
 REPLACE_KEYS = ("lora_config", "reward_functions", "config_overrides", "vllm_config", "sglang_jax_config")
-ROLE_MODEL_KEYS = ("actor_model_config", "critic_model_config", "reference_model_config", "rollout_model_config")
+ROLE_MODEL_KEYS = ("actor_model_config", "critic_model_config", "reference_model_config", "rollout_model_config",
+                   "reward_model_config")
+
+
+def _unalias(obj: Any) -> Any:
+    """A copy in which no two places share a container (`<<: *anchor` merges reuse the anchor's nested objects)."""
+    if isinstance(obj, dict):
+        return {k: _unalias(v) for k, v in obj.items()}
+    if isinstance(obj, list):
+        return [_unalias(v) for v in obj]
+    return obj
 
 
 def _parse_scalar(text: str) -> Any:
@@ -75,7 +85,7 @@ class HyperParameters:
             cand = os.path.join(os.path.dirname(os.path.abspath(__file__)), base_path)
             base_path = cand if os.path.exists(cand) else base_path
         with open(base_path) as f:
-            base = yaml.safe_load(f)
+            base = _unalias(yaml.safe_load(f))       # YAML anchors make sections share nested dicts: give each its own
         self._schema = copy.deepcopy(base)
         cfg = base
         cli: dict = {}
@@ -136,10 +146,20 @@ class HyperParameters:
     def create_mesh(self, section: str = "model_config"):
         from ..parallel.mesh import create_mesh
         m = self.config[section]["mesh"]
+        import ast
+
+        import numpy as np
         import torch.distributed as dist
         if not dist.is_initialized():
             return None
-        return create_mesh(m["shape"], m["axis_names"])
+        shape = ast.literal_eval(m["shape"]) if isinstance(m["shape"], str) else m["shape"]
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        world = dist.get_world_size()
+        if int(np.prod(shape)) == 1 and world > 1 and len(shape) == 1:
+            shape = (world,)          # the default "(1,)" means "all ranks along the one axis"
+        if int(np.prod(shape)) != world:
+            raise ValueError(f"{section}.mesh.shape {shape} needs {int(np.prod(shape))} ranks, the job has {world}")
+        return create_mesh(shape, m["axis_names"])
 
     def obtain_reward_fns(self) -> list[Callable]:
         return [load_reward_fn(p) for p in (self.config.get("reward_functions") or [])]

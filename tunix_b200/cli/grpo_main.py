@@ -5,55 +5,22 @@ from __future__ import annotations
 
 import sys
 
-from ..common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
 from ..rl.algorithm_config import DAPOConfig, DrGRPOConfig, GRPOConfig
 from ..rl.grpo.grpo_learner import DAPOLearner, DrGRPOLearner, GRPOLearner
 from ..rl.rl_cluster import RLCluster
-from . import config as config_lib
-from .peft_main import init_distributed, training_config_from
-from .utils import data as data_lib, model as model_lib
+from .base_rl_pipeline import BasePipeline
 
 
-def rollout_config_from(hp) -> RolloutConfig:
-    rc = hp["rollout_config"]
-    return RolloutConfig(max_tokens_to_generate=rc["total_generation_steps"], max_prompt_length=rc["max_prompt_length"],
-                         temperature=rc["temperature"], top_p=rc.get("top_p"), top_k=rc.get("top_k"),
-                         kv_cache_size=rc["max_prompt_length"] + rc["total_generation_steps"] + 8)
-
-
-def create_rl_engine(hp, dev, need_critic: bool = False) -> RLCluster:
-    actor = model_lib.create_model(hp["actor_model_config"], device=dev)
-    tok = model_lib.create_tokenizer(hp["tokenizer_config"])
-    from ..lora import is_lora_enabled
-    reference = None
-    if not is_lora_enabled(actor):
-        reference = model_lib.create_model(hp["reference_model_config"], device=dev)
-        reference.load_state_dict(actor.state_dict())
-        for p in reference.parameters():
-            p.requires_grad_(False)
-    critic = None
-    if need_critic:
-        from ..rl.utils import create_critic_model
-        critic = create_critic_model(actor)
-    rt = dict(hp["rl_training_config"])
-    aoc, coc = rt.pop("actor_optimizer_config"), rt.pop("critic_optimizer_config", None)
-    max_steps = rt.get("max_steps")
-    tc = training_config_from(rt, RLTrainingConfig, actor_optimizer=config_lib.create_optimizer(aoc, max_steps),
-                              critic_optimizer=config_lib.create_optimizer(coc or aoc, max_steps) if need_critic else None)
-    cc = ClusterConfig(role_to_mesh={}, rollout_engine=hp["rollout_engine"], offload_to_cpu=hp["offload_to_cpu"],
-                       training_config=tc, rollout_config=rollout_config_from(hp))
-    return RLCluster(actor=actor, reference=reference, critic=critic, tokenizer=tok, cluster_config=cc)
+def create_rl_engine(hp, dev=None, need_critic: bool = False) -> RLCluster:
+    """Kept for callers that hold a `HyperParameters`: the pipeline's engine construction on the same config."""
+    pipe = hp if isinstance(hp, BasePipeline) else BasePipeline.__new__(BasePipeline)
+    if pipe is not hp:
+        pipe.__dict__.update(hp.__dict__)
+    return pipe.create_rl_engine(dev, need_critic)
 
 
 def prompt_dataset(hp, tokenizer, vocab_size):
-    c = hp.config
-    n = c["num_batches"] or (c["rl_training_config"].get("max_steps") or 10)
-    if c["data_source"] == "synthetic":
-        return data_lib.synthetic_prompts(c["batch_size"], min(c["rollout_config"]["max_prompt_length"], 32), vocab_size, n)
-    import os
-    path = os.path.join(c["data_directory"], c["dataset_name"] or "train.jsonl")
-    tpl = (lambda p: tokenizer.apply_chat_template([{"role": "user", "content": p}])) if c["apply_chat_template_to_dataset"] else None
-    return data_lib.jsonl_prompts(path, c["batch_size"], tpl, c["num_train_epochs"])
+    return BasePipeline.prompt_dataset(hp, tokenizer, vocab_size)
 
 
 def agentic_kwargs(hp) -> dict:
@@ -93,22 +60,22 @@ def agentic_kwargs(hp) -> dict:
 
 
 def main(argv=None):
-    hp = config_lib.HyperParameters(sys.argv if argv is None else argv)
-    dev = init_distributed()
-    cluster = create_rl_engine(hp, dev)
-    g = dict(hp["grpo_config"])
-    variant = g.pop("algo_variant", "grpo")
-    cfg_cls, learner_cls = {"dapo": (DAPOConfig, DAPOLearner), "drgrpo": (DrGRPOConfig, DrGRPOLearner)}.get(
-        variant, (GRPOConfig, GRPOLearner))
-    algo = cfg_cls(**g)
-    rewards = hp.obtain_reward_fns()
-    if hp["training_mode"] == "agentic_grpo":
-        from ..rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
-        learner = AgenticGRPOLearner(cluster, rewards, algo, **agentic_kwargs(hp))
-    else:
-        learner = learner_cls(cluster, rewards, algo)
-    learner.train(prompt_dataset(hp, cluster.tokenizer, cluster.train_actor.config.vocab_size))
-    return cluster
+    """Every rank runs this. Actor ranks train; ranks that only host the sampler or the reference serve them
+    (`actor_model_config.mesh`, `rollout_model_config.mesh`, `same_mesh_as` decide who is who)."""
+    hp = BasePipeline(sys.argv if argv is None else argv)
+
+    def build(cluster):
+        g = dict(hp["grpo_config"])
+        variant = g.pop("algo_variant", "grpo")
+        cfg_cls, learner_cls = {"dapo": (DAPOConfig, DAPOLearner), "drgrpo": (DrGRPOConfig, DrGRPOLearner)}.get(
+            variant, (GRPOConfig, GRPOLearner))
+        algo = cfg_cls(**g)
+        rewards = hp.obtain_reward_fns()
+        if hp["training_mode"] == "agentic_grpo":
+            from ..rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
+            return AgenticGRPOLearner(cluster, rewards, algo, **agentic_kwargs(hp))
+        return learner_cls(cluster, rewards, algo)
+    return hp.run(build)
 
 
 if __name__ == "__main__":

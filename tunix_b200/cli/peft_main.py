@@ -40,21 +40,19 @@ def init_distributed():
 
 
 def run_peft_trainer(hp: config_lib.HyperParameters):
-    import torch.distributed as dist
+    """The mesh of `model_config.mesh` picks the parallel strategy (`parallel/strategy.py`): an `fsdp` axis ->
+    sharded optimizer (or, with `model_config.shard_weights`, weights sharded too and gathered inside the GEMMs),
+    a `tp` axis -> tensor parallelism, both -> tensor-parallel groups that are data-parallel replicas."""
+    from ..parallel import strategy
     dev = init_distributed()
-    hp.create_mesh()
+    mesh = hp.create_mesh()
     model = model_lib.create_model(hp["model_config"], device=dev)
     tok = model_lib.create_tokenizer(hp["tokenizer_config"])
     tc = training_config_from(hp["training_config"])
-    if dist.is_initialized() and dist.get_world_size() > 1:
-        from ..parallel import fsdp
-        oc = hp["optimizer_config"]
-        base = hp.create_optimizer()
-        opt = fsdp.ShardedAdamW(base._lr, b1=oc.get("b1", 0.9), b2=oc.get("b2", 0.999), weight_decay=oc.get("weight_decay", 0.0),
-                                max_grad_norm=oc.get("max_grad_norm"), comm="p2p" if dev.type == "cuda" else "nccl")
-    else:
-        opt = hp.create_optimizer()
+    opt, plan = strategy.apply_parallelism(model, hp.create_optimizer(), mesh,
+                                           shard_weights=bool(hp["model_config"].get("shard_weights", False)), device=dev)
     trainer = PeftTrainer(model, opt, tc)
+    trainer.parallel_plan = plan
     train_ds, eval_ds = data_lib.create_datasets(hp, tok, model.config.vocab_size)
     trainer.train(train_ds, eval_ds)
     return trainer

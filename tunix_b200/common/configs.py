@@ -194,5 +194,6 @@ class ClusterConfig:
     rollout_engine: Any = "vanilla"
     offload_to_cpu: bool = False
     gc_collect_after_weight_sync: bool = True
+    shard_frozen_models: bool = True   # an `fsdp` axis on a frozen role's mesh stores it as gathered-on-use row blocks
     training_config: RLTrainingConfig = None
     rollout_config: Any = None   # RolloutConfig or {Mode: RolloutConfig}

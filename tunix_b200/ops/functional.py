@@ -13,14 +13,32 @@ accumulates into it in its epilogue and autograd sees no gradient for that param
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from . import kernels as K
 from . import reference as R
 
 
+_library_mode = False
+
+
+@contextlib.contextmanager
+def library_ops():
+    """Route every op of this module through stock PyTorch (cuBLAS GEMMs, the library's fused attention, unfused
+    element-wise ops) instead of this package's kernels, on any device. This is the in-repo baseline that
+    benchmarks measure the kernels against; nothing else uses it."""
+    global _library_mode
+    prev, _library_mode = _library_mode, True
+    try:
+        yield
+    finally:
+        _library_mode = prev
+
+
 def _native(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype == torch.bfloat16 and not _library_mode
 
 
 def _deliver_grad(param, g: torch.Tensor):
@@ -250,6 +268,11 @@ def attention(q, k, v, *, scale: float, causal: bool = True, window: int = 0, so
             seg_k = seg_k.to(torch.int32).contiguous()
         return _AttnFn.apply(q, k, v, float(scale), bool(causal), int(window or 0), float(softcap or 0.0), q_off,
                              seg_q, seg_k)
+    if _library_mode and q.is_cuda and causal and not window and not softcap and seg_q is None and q_off is None \
+            and q.shape[1] == k.shape[1]:
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                             is_causal=True, scale=scale, enable_gqa=True)
+        return o.transpose(1, 2).contiguous()
     return R.attention_ref(q, k, v, scale=scale, causal=causal, window=window or 0, softcap=softcap or 0.0,
                            q_off=q_off, seg_q=seg_q, seg_k=seg_k)
 
@@ -285,7 +308,7 @@ class _EmbeddingFn(torch.autograd.Function):
 
 
 def embedding(ids, table, scale: float = 1.0):
-    if table.is_cuda and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
+    if table.is_cuda and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0 and not _library_mode:
         return _EmbeddingFn.apply(ids, table, float(scale))
     out = torch.nn.functional.embedding(ids.long(), table)
     return out * scale if scale != 1.0 else out
@@ -369,6 +392,21 @@ def lm_head_logprobs(h, w, targets, *, softcap: float = 0.0, temperature: float 
         return _LmHeadLogprobFn.apply(h, w, targets, float(softcap or 0.0), float(temperature), bool(want_entropy),
                                       int(chunk) if chunk and chunk > 0 else 2048)
     h2 = h.reshape(-1, h.shape[-1])
+    if _library_mode and h.is_cuda and h.dtype == torch.bfloat16:
+        # what a stock PyTorch trainer does: bf16 logits from the library GEMM, fp32 log-softmax, row chunks
+        lps, ents = [], []
+        tg_all = targets.reshape(-1).long()
+        for s0 in range(0, h2.shape[0], chunk or h2.shape[0]):
+            z = torch.nn.functional.linear(h2[s0:s0 + chunk], w).float()
+            if softcap and softcap > 0:
+                z = softcap * torch.tanh(z / softcap)
+            lsm = torch.log_softmax(z / temperature, dim=-1)
+            tg = tg_all[s0:s0 + chunk]
+            lps.append(lsm.gather(1, tg.clamp(0, w.shape[0] - 1)[:, None])[:, 0] * (tg >= 0))
+            if want_entropy:
+                ents.append(-(lsm.exp() * lsm).sum(-1))
+        ent = torch.cat(ents).view(targets.shape) if want_entropy else None
+        return torch.cat(lps).view(targets.shape), ent
     logp, ent = R.lm_head_logprobs_ref(h2, w, targets.reshape(-1), softcap=softcap or 0.0, temperature=temperature,
                                        want_entropy=want_entropy, chunk=chunk)
     return logp.view(targets.shape), (ent.view(targets.shape) if ent is not None else None)

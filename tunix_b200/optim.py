@@ -70,6 +70,23 @@ SCHEDULES = {
 }
 
 
+def install_grad_fold_hook(p: nn.Parameter) -> None:
+    """A gradient that autograd delivers through `.grad` (an op without a `main_grad` epilogue) is added to the
+    parameter's slot of the flat buffer as soon as it has been accumulated, and `.grad` is released: no second
+    full-size gradient copy piles up during backward, and an optimizer that reduces a layer's gradients while
+    backward still runs finds them in the flat buffer."""
+    if getattr(p, "_fold_hook", None) is not None or not hasattr(p, "register_post_accumulate_grad_hook"):
+        return
+
+    def fold(param):
+        mg = getattr(param, "main_grad", None)
+        if mg is not None and param.grad is not None:
+            mg.add_(param.grad.to(mg.dtype))
+            param.grad = None
+            param.grad_added_to_main_grad = True
+    p._fold_hook = p.register_post_accumulate_grad_hook(fold)
+
+
 # ------------------------------------------------------------------ flat buffers
 class FlatBuffers:
     """Flat parameter / gradient / state storage for a list of trainable parameters."""
@@ -99,6 +116,7 @@ class FlatBuffers:
                 p.data = view
                 p.main_grad = self.grad_flat[o:o + p.numel()].view(p.shape)
                 p.grad_added_to_main_grad = False
+                install_grad_fold_hook(p)
         self.master = None if dt == torch.float32 else self.param_flat.float()
 
     def master_flat(self) -> torch.Tensor:

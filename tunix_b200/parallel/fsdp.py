@@ -32,7 +32,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import _lib
-from ..optim import AdamW, Optimizer
+from ..optim import AdamW, Optimizer, install_grad_fold_hook
 from . import symm
 
 P, LL, I, F = _lib.P, _lib.LL, _lib.I, _lib.F
@@ -62,10 +62,16 @@ class ShardedAdamW(AdamW):
 
     def __init__(self, learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-4, max_grad_norm=None,
                  group=None, comm: str = "p2p", overlap: bool = True, barrier_timeout_ms: int = 30000,
-                 defer_gather: bool = True, gather_ctas: int = 24):
+                 defer_gather: bool = False, gather_ctas: int = 64):
         super().__init__(learning_rate, b1, b2, eps, weight_decay, max_grad_norm)
         self.group, self.comm, self.overlap = group, comm, overlap
-        self.defer_gather, self.gather_ctas = defer_gather, gather_ctas
+        # tuning overrides for measurements: TUNIX_B200_FSDP_DEFER=0/1, TUNIX_B200_FSDP_GATHER_CTAS=n
+        import os
+        env = os.environ.get
+        self.defer_gather = bool(int(env("TUNIX_B200_FSDP_DEFER", "1" if defer_gather else "0")))
+        self.gather_ctas = int(env("TUNIX_B200_FSDP_GATHER_CTAS", str(gather_ctas)))
+        # "dma": the overlapped all-gather runs on the copy engines; "kernel": on `gather_ctas` CTAs of the pull kernel
+        self.gather_engine = env("TUNIX_B200_FSDP_GATHER", "dma")
         self.barrier_timeout_ms = barrier_timeout_ms
         self._update_pending = True
         self._reduced: set = set()
@@ -117,6 +123,7 @@ class ShardedAdamW(AdamW):
                 p.data = view
                 p.main_grad = self.grad_flat[o:o + p.numel()].view(p.shape)
                 p.grad_added_to_main_grad = False
+                install_grad_fold_hook(p)
         # shard-local state
         self.master = torch.zeros(self.shard_total, dtype=torch.float32, device=dev)
         self.m = torch.zeros_like(self.master)
@@ -182,7 +189,8 @@ class ShardedAdamW(AdamW):
         # the parameter pulls of the last update may still be in flight when the next forward starts: every
         # part of the model waits for its own bucket, anything unrecognised waits for all of them
         layers = getattr(model, "layers", None)
-        if layers is None:
+        if layers is None or type(model).__name__ != "Transformer" or getattr(model, "tp", None) is not None:
+            # other model classes read parameters outside the embed -> layers -> norm -> head order this relies on
             self.defer_gather = False
             return
         model.register_forward_pre_hook(lambda m, a: self.wait_bucket(-1))
@@ -378,11 +386,18 @@ class ShardedAdamW(AdamW):
                 grads_free = torch.cuda.Event()
                 grads_free.record(stream)
             for b in sorted(self.bucket_tables):         # -1 (embeddings), layers 0..L-1, then the head
-                tab, n = self.bucket_tables[b]
-                _lib.check(lib.tb_allgather_pull(self.shard16_buf.c_ptrs, tab.data_ptr(), n, self.rank, self.world,
-                                                 self.param_flat.data_ptr(), self.gather_ctas if deferred else 0,
-                                                 stream.cuda_stream), "tb_allgather_pull")
-                self.comm_launches += 1
+                if deferred and self.gather_engine == "dma":
+                    # copy engines move the pieces (one peer-to-peer copy per tensor and peer): no SM is taken
+                    # from the forward pass that runs meanwhile
+                    for dst, src in self._dma_plan(b):
+                        dst.copy_(src, non_blocking=True)
+                        self.comm_launches += 1
+                else:
+                    tab, n = self.bucket_tables[b]
+                    _lib.check(lib.tb_allgather_pull(self.shard16_buf.c_ptrs, tab.data_ptr(), n, self.rank, self.world,
+                                                     self.param_flat.data_ptr(), self.gather_ctas if deferred else 0,
+                                                     stream.cuda_stream), "tb_allgather_pull")
+                    self.comm_launches += 1
                 if deferred:
                     e = torch.cuda.Event()
                     e.record(stream)
@@ -392,6 +407,24 @@ class ShardedAdamW(AdamW):
             self.barrier.wait(slot=2)
         if deferred:
             main.wait_event(grads_free)      # the gradient buffer may be zeroed from here on
+
+    def _dma_plan(self, b: int) -> list:
+        """[(destination view in the resident parameters, source view in a peer's bf16 shard)] of bucket `b`."""
+        plans = getattr(self, "_dma_plans", None)
+        if plans is None:
+            plans = self._dma_plans = {}
+        if b not in plans:
+            W, out = self.world, []
+            peers = [self.shard16_buf.peer_tensor(p) for p in range(W)]
+            for i in self._bucket_param_idx_cached(b):
+                s_ = self.lens[i] // W
+                for k in range(W):
+                    p = (self.rank + 1 + k) % W                      # peers first, own piece last
+                    src = peers[p][self.shard_offsets[i]:self.shard_offsets[i] + s_]
+                    dst = self.param_flat[self.offsets[i] + p * s_: self.offsets[i] + (p + 1) * s_]
+                    out.append((dst, src))
+            plans[b] = out
+        return plans[b]
 
     def wait_bucket(self, b: int) -> None:
         """Make the current stream wait until bucket `b` of the parameters holds the latest update."""
@@ -483,6 +516,20 @@ class ShardedAdamW(AdamW):
         if self.world == 1:
             return super()._state_tensors()
         return {"mu": self.m, "nu": self.v, "master": self.master}
+
+
+def shard_optimizer(opt: Optimizer, group=None, **kw) -> Optimizer:
+    """The sharded form of an (unbound) AdamW over `group`, with the same schedule and hyper-parameters. Optimizers
+    that are already sharded, already bound to parameters, or of another kind come back unchanged; so does
+    everything in a single-rank job."""
+    if getattr(opt, "is_sharded", False) or opt.buffers is not None or type(opt) not in (AdamW,) and \
+            type(opt).__name__ != "Adam":
+        return opt
+    if not dist.is_initialized() or dist.get_world_size(group) <= 1:
+        return opt
+    new = ShardedAdamW(opt._lr, opt.b1, opt.b2, opt.eps, opt.weight_decay, opt.max_grad_norm, group=group, **kw)
+    new.step_count = opt.step_count
+    return new
 
 
 class _ShardedBuffersFacade:

@@ -1,14 +1,27 @@
 """RLCluster (alias RLEngine): owns the models of an RL job, their placement, the rollout engine, the
 inference worker for frozen models and the trainers (tunix/rl/rl_cluster.py:102-1366).
 
-One process per GPU. `ClusterConfig.role_to_mesh` maps each role to a mesh (a set of ranks); in the
-colocated layout (all roles on all ranks, the default and the layout of the GRPO benchmark config) phases
-alternate on the same GPUs: rollout -> reference / old log-probs -> actor update -> weight sync.
+One process per GPU. `ClusterConfig.role_to_mesh` maps each role to a mesh (a set of ranks,
+`rl/placement.py`). Every rank of the job constructs an `RLCluster` with the models of the roles it hosts:
+
+* colocated (all roles on the actor's ranks, the default and the layout of the GRPO benchmark config): phases
+  alternate on the same GPUs: rollout -> reference / old log-probs -> actor update -> weight sync. Every rank is
+  a data-parallel replica of the loop over its own prompts.
+* disaggregated (rollout, and possibly the reference, on other ranks than the actor): the actor's ranks run the
+  loop; the other ranks call `serve()` and answer rounds of work (`generate`, `ref_logps`), see
+  `placement.RoleExchange`. `generate_begin` opens a round early so that generation of the next batch runs while
+  the actor trains on the current one.
+
+What the mesh of a role asks for is applied here (the reference's `_load_model` reshards every model onto its
+mesh, :228-287): an `fsdp` axis turns the actor's AdamW into the sharded optimizer over that group and stores a
+frozen reference / critic / reward model as row blocks whose GEMMs gather them on use (`parallel/fsdp3.py`,
+forward only); a `tp` axis slices the actor with `parallel/tp.py`.
 
 Weight sharing (:196-226): when the rollout model and the actor are the same object the sync is free; with
 LoRA the reference policy is the actor with adapters disabled, so actor, reference and sampler share one
-copy of the backbone. Otherwise `sync_weights` copies (LoRA-only when adapters exist) into the rollout
-model; across ranks `rl/reshard.py` moves shards peer to peer.
+copy of the backbone. Otherwise `sync_weights` moves the actor's weights into the sampler's own copy with
+`rl/reshard.py`: the source ranks stage, the rollout ranks pull their rectangles peer to peer, whatever the two
+layouts are (the same call serves the colocated separate-copy case, where every pull is local).
 """
 from __future__ import annotations
 
@@ -26,6 +39,7 @@ from ..common.datatypes import Mode, Role
 from ..lora import disable_adapters, is_lora_enabled, lora_state_dict
 from ..sft import metrics_logger as ml
 from . import common
+from .placement import RoleExchange, RolePlacement
 from .inference.inference_worker import InferenceWorker
 from .rollout.base_rollout import BaseRollout, RolloutOutput
 from .rollout.vanilla_rollout import VanillaRollout
@@ -33,36 +47,93 @@ from .trainer import Trainer
 
 
 class RLCluster:
-    def __init__(self, *, actor, reference=None, critic=None, reward=None, rollout_model=None, tokenizer,
-                 cluster_config: ClusterConfig, perf_tracer=None, metrics_logger: Optional[ml.MetricsLogger] = None):
+    def __init__(self, *, actor=None, reference=None, critic=None, reward=None, rollout_model=None, tokenizer,
+                 cluster_config: ClusterConfig, perf_tracer=None, metrics_logger: Optional[ml.MetricsLogger] = None,
+                 placement: Optional[RolePlacement] = None, separate_rollout_copy: bool = False):
+        """`actor` ... `rollout_model`: the models of the roles THIS rank hosts (None for the others; a rollout
+        rank of a disaggregated job passes `rollout_model` only). `separate_rollout_copy`: in the colocated layout
+        give the sampler its own copy of the weights, refreshed by `sync_weights`, instead of sharing the actor's."""
         self.cluster_config = cluster_config
         self.tokenizer = tokenizer
         self.perf = perf_tracer
         tcfg = cluster_config.training_config
+        self.placement = placement or RolePlacement(cluster_config.role_to_mesh)
+        pl = self.placement
+        self.exchange = RoleExchange(pl, on_sync=self._transfer_weights)
+        self.is_controller = pl.is_controller
+        if pl.has(Role.ACTOR) and actor is None:
+            raise ValueError(f"rank {pl.rank} hosts the actor (ranks {pl.ranks(Role.ACTOR)}) but got no actor model")
+        if not pl.has(Role.ACTOR):
+            actor = None
         self.train_actor = actor
-        self.critic = critic
-        self.reward = reward
-        self._lora = is_lora_enabled(actor)
+        self.critic = critic if pl.has(Role.CRITIC) else None
+        self.reward = reward if pl.has(Role.REWARD) else None
+        self._lora = actor is not None and is_lora_enabled(actor)
         # reference: explicit model, or the actor's frozen backbone when adapters are present
-        self._ref_shares_backbone = reference is None and self._lora
-        self.reference = reference
-        self.rollout_actor = rollout_model if rollout_model is not None else actor
-        self._rollout_shares_weights = self.rollout_actor is actor
+        self._ref_shares_backbone = reference is None and self._lora and pl.same(Role.REFERENCE, Role.ACTOR)
+        self.reference = reference if pl.has(Role.REFERENCE) else None
+        if pl.has(Role.ROLLOUT):
+            if rollout_model is None and actor is not None and separate_rollout_copy:
+                import copy
+                rollout_model = copy.deepcopy(actor)
+                for p in rollout_model.parameters():
+                    p.requires_grad_(False)
+            if rollout_model is None and actor is None:
+                raise ValueError(f"rank {pl.rank} hosts the rollout role but got neither a rollout model nor an actor")
+            self.rollout_actor = rollout_model if rollout_model is not None else actor
+        else:
+            self.rollout_actor = None
+        self._rollout_shares_weights = self.rollout_actor is not None and self.rollout_actor is actor and \
+            pl.same(Role.ROLLOUT, Role.ACTOR)
+        self._apply_mesh_strategies()
         self.global_steps = 0
+        self.last_weight_sync_seconds: Optional[float] = None
+        self.last_weight_sync_bytes = 0
+        self._resharder = None
+        self._prefetch = None
         self._buffered_metrics: dict = {}
         self._metrics_step = None
         self.metrics_logger = metrics_logger or ml.MetricsLogger(tcfg.metrics_logging_options)
-        self._init_rollout()
+        self.rollout = None
+        if self.rollout_actor is not None:
+            self._init_rollout()
         models = {}
         if self.reference is not None:
             models["reference"] = self.reference
-        if critic is not None:
-            models["critic"] = critic
-        if reward is not None:
-            models["reward"] = reward
+        if self.critic is not None:
+            models["critic"] = self.critic
+        if self.reward is not None:
+            models["reward"] = self.reward
         self.inference_worker = InferenceWorker(models)
-        self._init_trainers()
+        self.actor_trainer = self.critic_trainer = None
+        if self.train_actor is not None:
+            self._init_trainers()
         self._anchor = None   # pinned-host copy of the start-of-step policy (for off-policy old log-probs)
+        self.exchange.register(Role.ROLLOUT, "generate", self._serve_generate)
+        self.exchange.register(Role.REFERENCE, "ref_logps", self._serve_ref_logps)
+
+    def _apply_mesh_strategies(self) -> None:
+        """Turn the axes of each role's mesh into the parallel form of the model this rank holds."""
+        pl, tcfg = self.placement, self.cluster_config.training_config
+        if self.train_actor is not None:
+            tp = pl.axis_size(Role.ACTOR, "tp")
+            if tp > 1 and getattr(self.train_actor, "tp", None) is None:
+                from ..parallel import tp as tp_lib
+                dev = next(self.train_actor.parameters()).device
+                tp_lib.apply_tensor_parallel(self.train_actor, tp_lib.TPContext(group=pl.axis_group(Role.ACTOR, "tp"),
+                                                                                device=dev))
+            if pl.axis_size(Role.ACTOR, "fsdp") > 1 and tcfg.actor_optimizer is not None:
+                from ..parallel import fsdp
+                tcfg.actor_optimizer = fsdp.shard_optimizer(tcfg.actor_optimizer, pl.axis_group(Role.ACTOR, "fsdp"))
+        if getattr(self.cluster_config, "shard_frozen_models", True):
+            for role, model in ((Role.REFERENCE, self.reference), (Role.CRITIC, None), (Role.REWARD, self.reward)):
+                if model is None or pl.axis_size(role, "fsdp") <= 1 or getattr(model, "dp_shard", None) is not None:
+                    continue
+                if any(p.requires_grad for p in model.parameters()) or not hasattr(model, "layers"):
+                    continue
+                from ..parallel import fsdp3
+                dev = next(model.parameters()).device
+                fsdp3.apply_weight_sharding(model, fsdp3.CommContext(group=pl.axis_group(role, "fsdp"), device=dev))
 
     # ----------------------------------------------------------------- setup
     def _rollout_config(self, mode=Mode.TRAIN) -> RolloutConfig:
@@ -117,7 +188,14 @@ class RLCluster:
     def generate(self, prompts: Sequence[Any], mode=Mode.TRAIN, micro_batch_size: Optional[int] = None,
                  apply_chat_template: bool = False, prompt_token_ids: Optional[Sequence[Sequence[int]]] = None,
                  **kwargs) -> RolloutOutput:
-        """Generate completions in micro-batches and merge them into one RolloutOutput."""
+        """Generate completions in micro-batches and merge them into one RolloutOutput. When the rollout role sits
+        on other ranks the prompts travel there in a round (or the round opened by `generate_begin` is closed)."""
+        if not self.exchange.is_local(Role.ROLLOUT):
+            return self._generate_remote(prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids, kwargs)
+        return self._generate_local(prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids, **kwargs)
+
+    def _generate_local(self, prompts, mode=Mode.TRAIN, micro_batch_size=None, apply_chat_template=False,
+                        prompt_token_ids=None, **kwargs) -> RolloutOutput:
         rc = self._rollout_config(mode)
         if apply_chat_template and prompt_token_ids is None:
             prompts = [self.tokenizer.apply_chat_template([{"role": "user", "content": p}] if isinstance(p, str) else p,
@@ -143,6 +221,103 @@ class RLCluster:
             logprobs=(list(itertools.chain.from_iterable(o.logprobs for o in outs)) if outs[0].logprobs is not None else None),
             prompt_lengths=(np.concatenate([o.prompt_lengths for o in outs]) if outs[0].prompt_lengths is not None else None))
 
+    # -------------------------------------------------- generation on other ranks
+    @staticmethod
+    def _split_output(out: RolloutOutput) -> list:
+        n = len(out.tokens)
+        return [{"text": out.text[i], "tokens": np.asarray(out.tokens[i]),
+                 "prompt": np.asarray(out.left_padded_prompt_tokens[i]),
+                 "logprobs": None if out.logprobs is None else np.asarray(out.logprobs[i]),
+                 "plen": None if out.prompt_lengths is None else int(out.prompt_lengths[i])} for i in range(n)]
+
+    def _merge_output(self, rows: list) -> RolloutOutput:
+        P = max(len(r["prompt"]) for r in rows)
+        pad = self.tokenizer.pad_id()
+        prm = np.stack([np.pad(r["prompt"], (P - len(r["prompt"]), 0), constant_values=pad) for r in rows])
+        return RolloutOutput(text=[r["text"] for r in rows], logits=None, tokens=[r["tokens"] for r in rows],
+                             left_padded_prompt_tokens=prm,
+                             logprobs=None if rows[0]["logprobs"] is None else [r["logprobs"] for r in rows],
+                             prompt_lengths=None if rows[0]["plen"] is None else np.asarray([r["plen"] for r in rows]))
+
+    def _serve_generate(self, items: list) -> list:
+        """Rollout ranks: one engine call per group of items that share their settings."""
+        out: list = [None] * len(items)
+        groups: dict = {}
+        for i, it in enumerate(items):
+            groups.setdefault((it["mode"], it["mb"], it["ids"] is not None), []).append(i)
+        for (mode, mb, by_ids), idx in groups.items():
+            prompts = None if by_ids else [items[i]["prompt"] for i in idx]
+            ids = [items[i]["ids"] for i in idx] if by_ids else None
+            res = self._generate_local(prompts, Mode(mode), mb, False, ids)
+            for i, row in zip(idx, self._split_output(res)):
+                out[i] = row
+        return out
+
+    def _generate_items(self, prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids) -> list:
+        if apply_chat_template and prompt_token_ids is None:
+            prompts = [self.tokenizer.apply_chat_template([{"role": "user", "content": p}] if isinstance(p, str) else p,
+                                                          add_generation_prompt=True, tokenize=False) for p in prompts]
+        n = len(prompt_token_ids) if prompt_token_ids is not None else len(prompts)
+        return [{"mode": str(mode), "mb": micro_batch_size, "prompt": None if prompt_token_ids is not None else prompts[i],
+                 "ids": None if prompt_token_ids is None else [int(t) for t in prompt_token_ids[i]]} for i in range(n)]
+
+    def generate_begin(self, prompts, mode=Mode.TRAIN, micro_batch_size=None, apply_chat_template: bool = False,
+                       prompt_token_ids=None) -> bool:
+        """Open the generation round for these prompts now and return; the matching `generate(...)` call (same
+        prompts) collects the result. Between the two this rank is free to train while the rollout ranks work.
+        No-op (False) when the rollout role is local."""
+        if self.exchange.is_local(Role.ROLLOUT):
+            return False
+        self.generate_finish()
+        items = self._generate_items(prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids)
+        self._prefetch = {"items": items, "round": self.exchange.begin(Role.ROLLOUT, "generate", items), "rows": None}
+        return True
+
+    def generate_finish(self) -> None:
+        """Close an open generation round (its results are kept for the `generate` call that asks for them)."""
+        pf = self._prefetch
+        if pf is not None and pf["round"] is not None:
+            pf["rows"] = self.exchange.end(pf["round"])
+            pf["round"] = None
+
+    def _generate_remote(self, prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids, kwargs) -> RolloutOutput:
+        if kwargs:
+            raise ValueError(f"generation on other ranks takes no extra arguments, got {sorted(kwargs)}")
+        items = self._generate_items(prompts, mode, micro_batch_size, apply_chat_template, prompt_token_ids)
+        pf = self._prefetch
+        if pf is not None and pf["items"] == items:
+            self.generate_finish()
+            rows, self._prefetch = pf["rows"], None
+        else:
+            self.generate_finish()
+            with self._span("rollout"):
+                rows = self.exchange.call(Role.ROLLOUT, "generate", items)
+        return self._merge_output(rows)
+
+    def _serve_ref_logps(self, items: list) -> list:
+        """Reference ranks: log-probs of the rows other ranks sent (grouped by the settings they share)."""
+        dev = next(self.reference.parameters()).device
+        out: list = [None] * len(items)
+        groups: dict = {}
+        for i, it in enumerate(items):
+            groups.setdefault((it["pad"], it["eos"], it["mb"], tuple(sorted(it["kw"].items())), len(it["p"]), len(it["c"])),
+                              []).append(i)
+        chunk = self.cluster_config.training_config.compute_logps_chunk_size
+        for (pad, eos, mb, kw, _, _), idx in groups.items():
+            p = torch.as_tensor(np.stack([items[i]["p"] for i in idx]), device=dev)
+            c = torch.as_tensor(np.stack([items[i]["c"] for i in idx]), device=dev)
+            m = None if items[idx[0]]["m"] is None else torch.as_tensor(np.stack([items[i]["m"] for i in idx]), device=dev)
+            fn = lambda pp, cc, mm: self.inference_worker.get_ref_per_token_logps(  # noqa: E731
+                pp, cc, pad, eos, completion_mask=mm, chunk_size=chunk, **dict(kw))
+            res = self._mb_apply(fn, (p, c, m), mb).float().cpu().numpy()
+            for i, row in zip(idx, res):
+                out[i] = row
+        return out
+
+    def serve(self) -> int:
+        """Ranks that host no part of the training loop: answer rounds until the controllers close the cluster."""
+        return self.exchange.serve()
+
     # ---------------------------------------------------------------- logps
     def _mb_apply(self, fn: Callable, tensors: tuple, micro_batch_size: Optional[int]):
         n = tensors[0].shape[0]
@@ -153,6 +328,15 @@ class RLCluster:
     def get_ref_per_token_logps(self, prompt_tokens, completion_tokens, pad_id, eos_id, micro_batch_size=None,
                                 completion_mask=None, **kw):
         chunk = self.cluster_config.training_config.compute_logps_chunk_size
+        if not self._ref_shares_backbone and not self.exchange.is_local(Role.REFERENCE):
+            with self._span("refer_inference"):
+                host = lambda t: None if t is None else t.detach().cpu().numpy()  # noqa: E731
+                P, C, M = host(prompt_tokens), host(completion_tokens), host(completion_mask)
+                items = [{"p": P[i], "c": C[i], "m": None if M is None else M[i], "pad": pad_id, "eos": eos_id,
+                          "mb": micro_batch_size, "kw": {k: v for k, v in kw.items() if v is not None}}
+                         for i in range(P.shape[0])]
+                rows = self.exchange.call(Role.REFERENCE, "ref_logps", items)
+                return torch.as_tensor(np.stack(rows), device=prompt_tokens.device)
         with self._span("refer_inference"):
             if self._ref_shares_backbone:
                 def fn(p, c, m):
@@ -168,7 +352,11 @@ class RLCluster:
             return self._mb_apply(fn, (prompt_tokens, completion_tokens, completion_mask), micro_batch_size)
 
     def get_old_per_token_logps(self, prompt_tokens, completion_tokens, micro_batch_size=None, completion_mask=None, **kw):
-        """Log-probs under the rollout policy's weights (the sampler's model)."""
+        """Log-probs under the rollout policy's weights (the sampler's model). With the sampler on other ranks the
+        actor's own weights stand in: they are what the sampler received at the last sync."""
+        if self.rollout is None or not self.exchange.is_local(Role.ROLLOUT):
+            return self.get_actor_per_token_logps(prompt_tokens, completion_tokens, self.tokenizer.pad_id(),
+                                                  self.tokenizer.eos_id(), micro_batch_size, completion_mask, **kw)
         with self._span("old_logps"):
             fn = lambda p, c, m: self.rollout.get_per_token_logps(p, c, m)  # noqa: E731
             return self._mb_apply(fn, (prompt_tokens, completion_tokens, completion_mask), micro_batch_size)
@@ -203,16 +391,82 @@ class RLCluster:
             self.critic_trainer.train(train_ds, eval_ds, skip_jit)
 
     def sync_weights(self) -> None:
-        """Push the actor's weights (LoRA-only when adapters exist) into the rollout engine; bump global step."""
+        """Controllers: bring the sampler's weights up to date with the actor's; bump the global step. Ranks in
+        `serve()` join the transfer when it crosses ranks."""
         with self._span("weight_sync"):
+            self.generate_finish()
             if not self._rollout_shares_weights:
-                if self._lora:
-                    self.rollout.update_params(lora_state_dict(self.train_actor))
-                else:
-                    self.rollout.update_params({n: p.detach() for n, p in self.train_actor.named_parameters()})
+                self.exchange.sync()
             if self.cluster_config.gc_collect_after_weight_sync:
                 gc.collect()
         self.global_steps += 1
+
+    def _transfer_weights(self) -> None:
+        """Every rank that takes part: actor ranks offer, rollout ranks pull (`rl/reshard.py`). With adapters on
+        both sides only the adapters travel; an adapter-free sampler receives `W + scale * B A`."""
+        pl = self.placement
+        if pl.world == 1 or (pl.same(Role.ROLLOUT, Role.ACTOR) and not self._needs_plan()):
+            # same process, same layout: a device copy per tensor
+            t0 = time.perf_counter()
+            wait = getattr(getattr(self.actor_trainer, "optimizer", None), "wait_params", None)
+            if wait is not None:
+                wait()
+            if self._lora and is_lora_enabled(self.rollout_actor):
+                src = lora_state_dict(self.train_actor)
+            else:
+                from .reshard import model_sources
+                src = model_sources(self.train_actor, merge_lora=self._lora)
+            self.rollout.update_params(src)
+            self.last_weight_sync_bytes = sum(t.numel() * t.element_size() for t in src.values())
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            self.last_weight_sync_seconds = time.perf_counter() - t0
+            return
+        from .reshard import WeightReshard, model_sources
+        t0 = time.perf_counter()
+        src, dst = {}, {}
+        sampler_lora = self._rollout_has_adapters()          # collective on its first call: every rank makes it
+        if self.train_actor is not None:
+            wait = getattr(self.actor_trainer.optimizer, "wait_params", None)
+            if wait is not None:
+                wait()
+            src = lora_state_dict(self.train_actor) if (self._lora and sampler_lora) else \
+                model_sources(self.train_actor, merge_lora=self._lora)
+        if self.rollout_actor is not None and self.rollout_actor is not self.train_actor:
+            dst = {n: p for n, p in self.rollout_actor.named_parameters() if not sampler_lora or "lora_" in n}
+        if self._resharder is None or self._resharder_key != (tuple(src), tuple(dst)):
+            # the plan (who pulls which rectangle from whom) is built once; sources are re-read on every run
+            self._resharder = WeightReshard(src, dst, key_map=self._tied_head_map())
+            self._resharder_key = (tuple(src), tuple(dst))
+        else:
+            self._resharder.src = dict(src)
+        self._resharder.run()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.last_weight_sync_bytes = self._resharder.bytes_pulled
+        self.last_weight_sync_seconds = time.perf_counter() - t0
+
+    def _needs_plan(self) -> bool:
+        """Same ranks but different layouts (a sliced actor feeding a whole sampler) need the rectangle plan."""
+        a, r = self.train_actor, self.rollout_actor
+        return any(getattr(p, "shard_spec", None) is not None for m in (a, r) if m is not None for p in m.parameters())
+
+    def _rollout_has_adapters(self) -> bool:
+        flag = getattr(self, "_rollout_lora", None)
+        if flag is None:
+            mine = self.rollout_actor is not None and is_lora_enabled(self.rollout_actor)
+            flag = mine
+            pl = self.placement
+            if pl.world > 1 and not pl.same(Role.ROLLOUT, Role.ACTOR):
+                import torch.distributed as dist
+                box = [None] * pl.world
+                dist.all_gather_object(box, bool(mine) if self.rollout_actor is not None else None, group=pl.host_group)
+                flag = any(b for b in box if b is not None)
+            self._rollout_lora = flag
+        return flag
+
+    def _tied_head_map(self):
+        return None
 
     def snapshot_anchor(self) -> None:
         """Pinned-host copy of the current policy (tunix/rl/rl_cluster.py:515-517,1297-1300)."""
@@ -264,6 +518,11 @@ class RLCluster:
 
     def close(self) -> None:
         self.flush_metrics()
+        if self.is_controller:
+            self.generate_finish()
+            self.exchange.stop()
+        if self.actor_trainer is None:
+            return
         self.actor_trainer.close()
         if self.critic_trainer is not None:
             self.critic_trainer.close()

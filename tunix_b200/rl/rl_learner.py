@@ -47,11 +47,17 @@ class RLLearner(abc.ABC):
         self._data_shuffle_seed = data_shuffle_seed
         self._iter_steps = 0
         self._eval_iter_steps = 0
+        if not rl_cluster.is_controller:
+            raise RuntimeError("this rank hosts no part of the training loop: call rl_cluster.serve() on it instead of "
+                               "building a learner")
         self.should_sync_weights = not rl_cluster._rollout_shares_weights
         self._producer_error: Optional[BaseException] = None
-        self.pad_id = rl_cluster.rollout.pad_id()
-        self.eos_id = rl_cluster.rollout.eos_id()
+        self.pad_id = rl_cluster.tokenizer.pad_id()
+        self.eos_id = rl_cluster.tokenizer.eos_id()
         self.device = next(rl_cluster.train_actor.parameters()).device
+        # generation on other ranks: open the next batch's round before training on the current one
+        self.rollout_is_remote = not rl_cluster.exchange.is_local("rollout")
+        self.off_policy_steps = int(getattr(algo_config, "off_policy_steps", 1 if self.rollout_is_remote else 0))
 
     # ---------------------------------------------------------- to implement
     @abc.abstractmethod
@@ -160,6 +166,14 @@ class RLLearner(abc.ABC):
                 next(it)
             except StopIteration:
                 return
+        if self.rollout_is_remote:
+            try:
+                self._train_remote_rollout(it, eval_ds)
+            finally:
+                self.rl_cluster.close()
+                if self.reward_manager is not None and hasattr(self.reward_manager, "close"):
+                    self.reward_manager.close()
+            return
         executor = futures.ThreadPoolExecutor(max_workers=1, thread_name_prefix="rl-producer")
         try:
             while True:
@@ -189,6 +203,50 @@ class RLLearner(abc.ABC):
             self.rl_cluster.close()
             if self.reward_manager is not None and hasattr(self.reward_manager, "close"):
                 self.reward_manager.close()
+
+    def _open_round(self, batch: dict) -> None:
+        """Send the prompts of `batch` to the rollout ranks now; `_generate_and_compute_advantage` picks the result up."""
+        rep = self._repeat(batch, self._num_generations())
+        mb = self.tcfg.rollout_micro_batch_size and self.tcfg.rollout_micro_batch_size * self._num_generations()
+        self.rl_cluster.generate_begin(rep.get("prompts"), mode=Mode.TRAIN, micro_batch_size=mb,
+                                       prompt_token_ids=rep.get("prompt_token_ids"))
+
+    def _train_remote_rollout(self, it: Iterator, eval_ds) -> None:
+        """The loop when the sampler lives on other ranks (tunix/rl/rl_learner.py:151-156: rollout and training
+        overlap when their meshes differ). With `off_policy_steps` >= 1 the round for batch k+1 is opened before
+        the update on batch k, so the rollout ranks generate while this rank trains; the weights they use are then
+        one update old. With 0 every batch is generated from the latest weights and nothing overlaps."""
+        max_steps = self.tcfg.max_steps
+        ahead = self.off_policy_steps >= 1
+        nxt = next(it, None)
+        if nxt is not None and ahead:
+            self._open_round(nxt)
+        while nxt is not None:
+            if max_steps is not None and self.rl_cluster.global_steps >= max_steps:
+                break
+            cur = nxt
+            q: SimpleDataQueue = SimpleDataQueue()
+            self._prepare_data(iter([cur]), q, Mode.TRAIN, 1)          # closes the round of `cur`, scores it
+            nxt = next(it, None)
+            last = max_steps is not None and self.rl_cluster.global_steps + 1 >= max_steps
+            if nxt is not None and ahead and not last:
+                self._open_round(nxt)
+            got_any = False
+
+            def counted():
+                nonlocal got_any
+                for ex in self._batches_from_queue(q):
+                    got_any = True
+                    self._iter_steps += 1
+                    yield ex
+            self._train_on(counted())
+            if not got_any:
+                break
+            self.rl_cluster.sync_weights()       # closes an open round first: rounds do not nest
+            self.rl_cluster.flush_metrics()
+            if eval_ds is not None and self.tcfg.eval_every_n_steps and \
+                    self.rl_cluster.global_steps % self.tcfg.eval_every_n_steps == 0:
+                self._run_eval(eval_ds)
 
     def _run_eval(self, eval_ds: Iterable[dict]) -> None:
         rewards = []

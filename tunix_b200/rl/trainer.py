@@ -22,6 +22,19 @@ class Trainer(PeftTrainer):
         self.rl_metrics_to_log = rl_metrics_to_log
         return self
 
+    def _shard_and_move(self, batch):
+        """RL examples are produced on this rank from this rank's own rollouts: they are moved to the device but
+        never sliced by rank (the SFT trainer slices a global batch that every rank received in full)."""
+        import dataclasses
+
+        from ..sft.peft_trainer import _to_device
+        if dataclasses.is_dataclass(batch) and not isinstance(batch, type):
+            return dataclasses.replace(batch, **{f.name: _to_device(getattr(batch, f.name), self.device)
+                                                 for f in dataclasses.fields(batch)})
+        if isinstance(batch, dict):
+            return {k: _to_device(v, self.device) for k, v in batch.items()}
+        return batch
+
     def set_global_step(self, step: int) -> None:
         self.global_step = step
 

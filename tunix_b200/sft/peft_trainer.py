@@ -246,6 +246,9 @@ class PeftTrainer:
                 dist.all_reduce(total)
         if tp is not None and tp.world > 1:
             dist.all_reduce(total, group=tp.group)      # every tp rank scored its own sequences
+            rep = getattr(self.model, "dp_replica_group", None)
+            if rep is not None:
+                dist.all_reduce(total, group=rep)
         if dps is not None and dps.world > 1 and not sharded:
             dist.all_reduce(total, group=dps.group)
         if total.is_cuda:
@@ -257,8 +260,9 @@ class PeftTrainer:
             return self.optimizer.step(denominator, denominator_is_local=True)
         tp = getattr(self.model, "tp", None)
         if tp is not None and tp.world > 1:
-            from ..parallel import tp as tp_lib
+            from ..parallel import strategy, tp as tp_lib
             self.optimizer.buffers.collect_autograd_grads()
+            strategy.sum_replica_grads(self.model, self.optimizer)      # data-parallel replicas of the tp group
             tp_lib.allreduce_replicated_grads(self.model, tp)
             return self.optimizer.step(denominator, sumsq=tp_lib.grad_sumsq(self.model, tp))
         dps = getattr(self.model, "dp_shard", None)
