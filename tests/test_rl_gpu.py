@@ -1,4 +1,6 @@
 """RL token kernels (clipped objective + KL with analytic derivatives, GAE scan) against PyTorch autograd."""
+import os
+
 import pytest
 import torch
 
@@ -94,3 +96,25 @@ def test_agentic_grpo_with_engine_server_mode():
     _lib.raise_if_kernel_error()
     assert cl.global_steps == 2 and learner.policy_version == 2
     assert len(served) == 8                  # 2 steps x 2 prompts x 2 generations, one request each
+
+
+def test_disaggregated_grpo_on_two_gpus_syncs_weights_peer_to_peer(tmp_path):
+    """Rank 0 trains, rank 1 samples on the paged engine; after the run the sampler's weights (built from another seed)
+    equal the actor's: they crossed NVLink through the reshard plan's block pulls."""
+    import json
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "res.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29771", os.path.join(root, "tests", "rl_placement_worker.py"), out]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    r = json.load(open(out))
+    assert r[0]["controller"] and not r[1]["controller"] and r[0]["steps"] == 2
+    assert r[1]["served"] == 2 and r[0]["rounds"] == 2            # one generation round per step; the reference is local
+    assert r[0]["fused"] and r[1]["fused"] and r[1]["sync_bytes"] > 0
+    assert r[0]["max_abs_diff"] == 0.0

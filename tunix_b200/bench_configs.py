@@ -101,48 +101,78 @@ def tiny_lora_cpu(args) -> dict:
 
 
 def grpo(args) -> dict:
-    """Config 3: Qwen3-8B GRPO, colocated sampler, 64 prompts x 8 generations, prompt 256, up to 768 sampled tokens."""
+    """Config 3: Qwen3-8B GRPO, 64 prompts x 8 generations, prompt 256, up to 768 sampled tokens, the sampler's weights
+    refreshed from the actor's after every update.
+
+    --layout colocated      every rank hosts actor (sharded optimizer), reference (row-sharded, gathered inside the
+                            GEMMs, unless --replicated-reference) and a sampler copy of its own
+    --layout disaggregated  the first half of the ranks trains, the second half hosts the sampler: generation of the
+                            next batch overlaps the update, weights cross NVLink peer to peer (`rl/reshard.py`)"""
     from . import optim
     from .common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+    from .common.datatypes import Role
     from .models.config import get_config
     from .models.transformer import create_model
-    from .parallel import fsdp
     from .rl.algorithm_config import GRPOConfig
     from .rl.grpo.grpo_learner import GRPOLearner
+    from .rl.placement import RolePlacement
     from .rl.rl_cluster import RLCluster
     rank, world = _dist()
     dev = torch.device("cuda", torch.cuda.current_device())
     cfg = get_config("qwen3_8b").replace(dtype=torch.bfloat16, max_position=1032)
     if args.layers:
         cfg = cfg.replace(num_layers=args.layers)
-    actor = create_model(cfg, device=dev, seed=0)
-    ref = create_model(cfg, device=dev, seed=0)
-    for p in ref.parameters():
-        p.requires_grad_(False)
+    disagg = args.layout == "disaggregated" and world >= 2
+    r2m = {}
+    if disagg:
+        half = world // 2
+        r2m = {Role.ACTOR: list(range(half)), Role.REFERENCE: list(range(half)), Role.ROLLOUT: list(range(half, world))}
+    pl = RolePlacement(r2m)
+    n_ctl = len(pl.controllers)
+    actor = create_model(cfg, device=dev, seed=0) if pl.has(Role.ACTOR) else None
+    ref = None
+    if pl.has(Role.REFERENCE):
+        ref = create_model(cfg, device=dev, seed=0)
+        for p in ref.parameters():
+            p.requires_grad_(False)
+    sampler = None
+    if disagg and pl.has(Role.ROLLOUT):
+        sampler = create_model(cfg, device=dev, seed=0)
+        for p in sampler.parameters():
+            p.requires_grad_(False)
     tok = IdTokenizer(cfg.vocab_size)
     G = 8
-    per_rank = max(args.prompts // world, 1)
-    opt = fsdp.ShardedAdamW(1e-6, max_grad_norm=1.0) if world > 1 else optim.AdamW(1e-6, max_grad_norm=1.0)
-    tcfg = RLTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, actor_optimizer=opt, mini_batch_size=per_rank * G,
-                            train_micro_batch_size=args.micro, rollout_micro_batch_size=per_rank * G,
+    per_rank = max(args.prompts // n_ctl, 1)
+    tcfg = RLTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, actor_optimizer=optim.AdamW(1e-6, max_grad_norm=1.0),
+                            mini_batch_size=per_rank * G, train_micro_batch_size=args.micro, rollout_micro_batch_size=per_rank * G,
                             compute_logps_micro_batch_size=args.micro * 2, pbar_description=None)
     rc = RolloutConfig(max_tokens_to_generate=768, max_prompt_length=256, temperature=1.0, top_p=1.0, seed=2,
                        kv_cache_size=1032, eos_tokens=[-1], max_running_requests=args.max_running)
-    cluster = RLCluster(actor=actor, reference=ref, tokenizer=tok,
-                        cluster_config=ClusterConfig(role_to_mesh={}, training_config=tcfg, rollout_config=rc, rollout_engine="paged"))
+    cluster = RLCluster(actor=actor, reference=ref, rollout_model=sampler, tokenizer=tok, placement=pl,
+                        separate_rollout_copy=not disagg,
+                        cluster_config=ClusterConfig(role_to_mesh=r2m, training_config=tcfg, rollout_config=rc, rollout_engine="paged",
+                                                     shard_frozen_models=not args.replicated_reference))
+    out = {"config": "grpo_qwen3_8b", "n_gpus": world, "layers": cfg.num_layers, "layout": pl.layout, "generations": G,
+           "reference": "replicated" if args.replicated_reference or world == 1 else "row-sharded (gathered in the GEMMs)"}
+    if not cluster.is_controller:
+        cluster.serve()
+        res = {"sync_s": cluster.last_weight_sync_seconds, "sync_bytes": cluster.last_weight_sync_bytes}
+        allres = [None] * world
+        dist.all_gather_object(allres, res)
+        return out
 
     def reward(prompts, completions, completion_ids=None, completion_lengths=None, **_):
-        out = []
+        res = []
         for ids, n in zip(completion_ids, completion_lengths):
             ids = np.asarray(ids[:int(n)])
-            out.append(float((ids % 7 == 0).mean() if len(ids) else 0.0) - 0.001 * float(n))
-        return out
+            res.append(float((ids % 7 == 0).mean() if len(ids) else 0.0) - 0.001 * float(n))
+        return res
     learner = GRPOLearner(cluster, [reward], GRPOConfig(num_generations=G, beta=0.04, epsilon=0.2))
     rng = np.random.default_rng(2 + rank)
     data = [{"prompts": [" ".join(map(str, rng.integers(3, cfg.vocab_size, 256))) for _ in range(per_rank)]}
             for _ in range(args.steps)]
     orig = learner._generate_and_compute_advantage
-    roll_t, starts = [], []
+    roll_t, starts, sync_t = [], [], []
 
     def timed(*a, **kw):
         torch.cuda.synchronize()
@@ -153,21 +183,37 @@ def grpo(args) -> dict:
         roll_t.append(time.perf_counter() - t0)
         return r
     learner._generate_and_compute_advantage = timed
+    orig_sync = cluster.sync_weights
+
+    def timed_sync():
+        orig_sync()
+        sync_t.append((cluster.last_weight_sync_seconds, cluster.last_weight_sync_bytes))
+    cluster.sync_weights = timed_sync
     torch.cuda.synchronize()
-    if dist.is_initialized():
-        dist.barrier()
     t_begin = time.perf_counter()
     learner.train(data)                      # a step = rollout + scoring + reference log-probs + update + weight sync
     torch.cuda.synchronize()
     t_end = time.perf_counter()
     bounds = starts + [t_end]
     times = [bounds[i + 1] - bounds[i] for i in range(len(starts))] or [t_end - t_begin]
-    step_s = _max_over_ranks(times[-1], dev)
-    gen_tokens = per_rank * G * 768 * world
-    return {"config": "grpo_qwen3_8b", "n_gpus": world, "layers": cfg.num_layers, "prompts": per_rank * world, "generations": G,
-            "step_seconds": step_s, "first_step_seconds": _max_over_ranks(times[0], dev),
-            "rollout_and_scoring_seconds": _max_over_ranks(roll_t[-1], dev) if roll_t else None,
-            "rollout_tokens_per_step": gen_tokens, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}
+    mine = {"sync_s": sync_t[-1][0] if sync_t else None, "sync_bytes": sync_t[-1][1] if sync_t else 0,
+            "step": times[-1], "first": times[0], "roll": roll_t[-1] if roll_t else None}
+    allres = [mine]
+    if world > 1:
+        allres = [None] * world
+        dist.all_gather_object(allres, mine)
+    ctl = [r for r in allres if r and "step" in r]
+    syncs = [r for r in allres if r and r.get("sync_s")]
+    sync_s = max((r["sync_s"] for r in syncs), default=None)
+    pulled = max((r["sync_bytes"] for r in syncs), default=0)
+    out.update({"prompts": per_rank * n_ctl, "step_seconds": max(r["step"] for r in ctl),
+                "first_step_seconds": max(r["first"] for r in ctl),
+                "rollout_and_scoring_seconds": max((r["roll"] for r in ctl if r["roll"] is not None), default=None),
+                "rollout_tokens_per_step": per_rank * G * 768 * n_ctl,
+                "weight_sync_seconds": sync_s, "weight_sync_bytes_per_rank": pulled,
+                "weight_sync_gb_per_s_per_rank": (pulled / sync_s / 1e9) if sync_s and pulled else None,
+                "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30})
+    return out
 
 
 def dpo(args) -> dict:
@@ -266,6 +312,8 @@ def main(argv=None) -> int:
     ap.add_argument("--micro", type=int, default=4)
     ap.add_argument("--ep-capacity", type=float, default=0.0, help="moe: fixed-capacity expert-parallel buffers (0 = exact)")
     ap.add_argument("--max-running", type=int, default=256, help="sequences decoded together by the rollout engine")
+    ap.add_argument("--layout", default="colocated", choices=["colocated", "disaggregated"], help="grpo: where the sampler lives")
+    ap.add_argument("--replicated-reference", action="store_true", help="grpo: keep the reference model whole on every rank")
     args = ap.parse_args(argv)
     res = {"tiny_lora_cpu": tiny_lora_cpu, "grpo": grpo, "dpo": dpo, "moe": moe}[args.config](args)
     if not dist.is_initialized() or dist.get_rank() == 0:
