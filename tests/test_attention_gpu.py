@@ -45,6 +45,13 @@ CASES = [
     (1, 64, 320, 4, 4, 128, True, 0, 0.0, False),
     (1, 256, 256, 2, 2, 128, False, 0, 0.0, False),
     (1, 1024, 1024, 8, 2, 128, True, 0, 0.0, False),
+    # two query tiles per CTA: ragged last tile, a window narrower than a tile, more keys than queries, segments with a
+    # soft-cap, no causal mask
+    (1, 448, 448, 2, 1, 128, True, 0, 0.0, False),
+    (2, 300, 300, 2, 2, 64, True, 64, 0.0, False),
+    (1, 384, 640, 4, 2, 128, True, 0, 0.0, False),
+    (1, 512, 512, 2, 1, 128, True, 0, 30.0, True),
+    (1, 640, 640, 2, 2, 64, False, 0, 0.0, False),
 ]
 
 
@@ -65,6 +72,14 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item()
 
 
+def _close(a, b, what=""):
+    """Element-wise, next to the norm: a handful of wrong elements cannot hide in a large tensor."""
+    a, b = a.float(), b.float()
+    tol = 0.03 * b.abs().max().item() + 1e-6
+    bad = (a - b).abs() > tol + 0.05 * b.abs()
+    assert not bad.any(), (what, int(bad.sum()), (a - b).abs().max().item(), tol)
+
+
 @pytest.mark.parametrize("case", CASES)
 def test_attention_forward(case):
     from tunix_b200 import _lib
@@ -76,6 +91,24 @@ def test_attention_forward(case):
     _lib.raise_if_kernel_error()
     ref = ref_attention(q, k, v, scale, causal, window, softcap, seg_q, seg_k)
     assert _rel(o, ref) < 2e-2, _rel(o, ref)
+    _close(o, ref, "o")
+    # log-sum-exp of every row that sees at least one key
+    s_ = torch.einsum("bqnh,bknh->bnqk", q.float(), k.float().repeat_interleave(N // KH, dim=2)) * scale
+    if softcap > 0:
+        s_ = softcap * torch.tanh(s_ / softcap)
+    qpos = torch.arange(Tq, device="cuda")[:, None] + (Tk - Tq)
+    kpos = torch.arange(Tk, device="cuda")[None, :]
+    m = torch.ones(Tq, Tk, dtype=torch.bool, device="cuda")
+    if causal:
+        m &= kpos <= qpos
+    if window > 0:
+        m &= kpos > qpos - window
+    m = m[None, None].expand(B, 1, Tq, Tk)
+    if seg_q is not None:
+        m = m & (seg_q[:, None, :, None] == seg_k[:, None, None, :])
+    want = torch.logsumexp(s_.masked_fill(~m, float("-inf")), dim=-1)
+    seen = torch.isfinite(want)
+    assert torch.allclose(lse[seen], want[seen], atol=2e-2, rtol=1e-3)
 
 
 @pytest.mark.parametrize("case", CASES)
@@ -96,3 +129,6 @@ def test_attention_backward(case):
     assert _rel(dv, vf.grad) < 3e-2, ("dv", _rel(dv, vf.grad))
     assert _rel(dk, kf.grad) < 3e-2, ("dk", _rel(dk, kf.grad))
     assert _rel(dq, qf.grad) < 3e-2, ("dq", _rel(dq, qf.grad))
+    _close(dv, vf.grad, "dv")
+    _close(dk, kf.grad, "dk")
+    _close(dq, qf.grad, "dq")

@@ -69,3 +69,65 @@ def test_tagged_tracer_query_sequence_and_lanes(tmp_path):
     write_chrome_trace(tr.query(), str(tmp_path / "t.json"))
     ev = json.load(open(tmp_path / "t.json"))["traceEvents"]
     assert sum(e["ph"] == "X" for e in ev) == 3
+
+
+def _fake_step(tr, now, layout_gaps):
+    """A scripted global step on a tracer with a hand-driven clock: two micro-batches of rollout -> scoring -> update."""
+    from tunix_b200.perf.trace import Span
+    spans = []
+
+    def add(name, b, e, parent=None):
+        s = Span(name, b, e, parent=parent, timeline="main")
+        tr._spans.append(s)
+        spans.append(s)
+        return s
+    g = add("global_step", 0.0, 20.0)
+    add("rollout", 0.0, 4.0, g)
+    add("refer_inference", 4.0, 5.0, g)
+    t0 = add("actor_train", 5.0, 8.0, g)
+    add("peft_train_step", 5.5, 7.5, t0)
+    add("rollout", 4.0, 9.0, g)              # the next micro-batch was generated while the first one trained
+    add("refer_inference", 9.5, 10.5, g)     # 1.5 s after the first update ended
+    t1 = add("actor_train", 10.5, 14.0, g)
+    add("peft_train_step", 11.0, 13.0, t1)
+    add("weight_sync", 16.0, 17.0, g)
+    return g
+
+
+def test_three_layout_exporters_and_selection_from_ranks():
+    from tunix_b200.perf.export import PerfMetricsExport, layout_of
+    tr = PerfTracer()
+    g = _fake_step(tr, None, None)
+    colo = PerfMetricsExport.from_role_to_ranks({"rollout": [0, 1], "actor": [0, 1], "refer": [0, 1]})
+    apart = PerfMetricsExport.from_role_to_ranks({"rollout": [2, 3], "actor": [0, 1], "refer": [0, 1]})
+    full = PerfMetricsExport.from_role_to_ranks({"rollout": [2], "actor": [0], "refer": [1]})
+    assert (colo.layout, apart.layout, full.layout) == ("colocated", "rollout_disaggregated", "fully_disaggregated")
+    with __import__("pytest").raises(ValueError):
+        layout_of({"rollout": [0], "actor": [0], "refer": [1]})
+    m = colo(tr)                                                    # finds the last global step by itself
+    assert m["perf/global_step_time"] == 20.0 and m["perf/weight_sync_time"] == 1.0
+    assert m["perf/sum/rollout_time"] == 9.0 and m["perf/mean/actor_train_time"] == 3.25
+    assert m["perf/sum/actor_train_step_time"] == 4.0 and "perf/rollout_idle_time" not in m
+    m = apart(tr, g)
+    assert m["perf/rollout_idle_time"] == 7.0 and m["perf/first_micro_batch_rollout_time"] == 4.0
+    assert m["perf/sum/between_micro_batch_gap_time"] == 1.5 and m["perf/mean/between_micro_batch_gap_time"] == 0.75
+    m = full(tr, g)
+    assert m["perf/sum/refer_gap_time"] == 6.5 and m["perf/sum/actor_gap_time"] == 9.0 and m["perf/rollout_idle_time"] == 7.0
+
+
+def test_export_from_cluster_config_writes_a_trace_per_step(tmp_path):
+    from tunix_b200.common.configs import ClusterConfig, PerfMetricsOptions, RLTrainingConfig
+    from tunix_b200.common.datatypes import Role
+    from tunix_b200.perf.export import PerfMetricsExport
+    from tunix_b200.rl.placement import RolePlacement
+    tc = RLTrainingConfig(eval_every_n_steps=1, perf_metrics_options=PerfMetricsOptions(enable_trace_writer=True,
+                                                                                       log_dir=str(tmp_path)))
+    r2m = {Role.ACTOR: [0, 1], Role.REFERENCE: [0, 1], Role.ROLLOUT: [2, 3]}
+    fn = PerfMetricsExport.from_cluster_config(ClusterConfig(role_to_mesh=r2m, training_config=tc),
+                                               RolePlacement(r2m, world=4, rank=0, make_groups=False))
+    assert fn.layout == "rollout_disaggregated"
+    tr = PerfTracer()
+    _fake_step(tr, None, None)
+    assert fn(tr)["perf/rollout_idle_time"] == 7.0
+    ev = json.load(open(tmp_path / "step_000001.rank0.json"))["traceEvents"]
+    assert sum(e.get("ph") == "X" for e in ev) == 10

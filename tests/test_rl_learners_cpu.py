@@ -60,6 +60,32 @@ def test_grpo_learner_runs_and_updates_lora_only(tmp_path):
     cl2.close()
 
 
+def test_learner_reports_the_layouts_perf_metrics_every_step():
+    from tunix_b200.perf.trace import PerfTracer
+    actor = create_model(_cfg(), seed=0)
+    ref = create_model(_cfg(), seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=4,
+                          train_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3,
+                       kv_cache_size=32, eos_tokens=[63])
+    tracer = PerfTracer()
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(), perf_tracer=tracer, separate_rollout_copy=True,
+                   cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.04)).train(
+        [{"prompts": ["ab", "cd", "ef", "gh"]} for _ in range(2)])
+    lg = cl.metrics_logger
+    steps = lg.get_metric_history("", "perf/global_step_time", "train")
+    assert len(steps) == 2 and all(t > 0 for t in steps)
+    for name in ("perf/sum/rollout_time", "perf/sum/refer_inference_time", "perf/sum/actor_train_time", "perf/weight_sync_time"):
+        assert lg.get_metric_history("", name, "train")[-1] > 0, name
+    assert lg.get_metric_history("", "perf/global_step_time", "train")[-1] >= \
+        lg.get_metric_history("", "perf/sum/actor_train_time", "train")[-1]
+    # the sampler's own copy follows the actor
+    a = torch.cat([p.detach().reshape(-1) for p in actor.parameters()])
+    r = torch.cat([p.detach().reshape(-1) for p in cl.rollout_actor.parameters()])
+    assert cl.rollout_actor is not actor and torch.equal(a, r)
+
+
 def test_grpo_full_weight_with_reference_and_gspo():
     actor = create_model(_cfg(), seed=0)
     ref = create_model(_cfg(), seed=0)

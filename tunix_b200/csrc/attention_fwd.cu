@@ -17,6 +17,7 @@
 // (tunix/models/llama3/model.py:379-396, tunix/models/qwen3/model.py:607-793,
 //  tunix/models/gemma/model.py:442-483).
 #include "common.cuh"
+#include <cstdlib>
 
 using namespace tb;
 
@@ -338,6 +339,368 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnArgs& a, l
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Two query tiles per CTA (head dim 64 / 128, more than 128 query rows).
+//
+// The one-tile kernel above leaves the tensor pipe idle most of the time: its four softmax warps
+// sit one per scheduler, every K tile is fetched only after the previous S = Q K^T has retired
+// (one K buffer), and the P buffer is single. Here a CTA owns 256 query rows of one head as two
+// 128-row tiles a and b:
+//   warps 0-3 / 4-7 : softmax of tile a / b, one thread per query row (TMEM lanes 0-127 each)
+//   warp 8          : one thread issues every tcgen05.mma: S_a, S_b of key block j+1 are queued
+//                     before it waits for P_a(j), P_b(j), so the tensor pipe always has work
+//                     from one tile while the other tile's rows are in the softmax
+//   warp 9          : one thread runs the TMA ring (K_0 V_0 K_1 V_1 ... over NSTG stages, three
+//                     key blocks ahead); a stage is handed back by a tcgen05.commit
+// TMEM: S_a[2] | S_b[2] | O_a | O_b = 4*64 + 2*H columns. K / V tiles are read once per 256 rows.
+// ---------------------------------------------------------------------------------------------
+template <int H>
+struct Fwd2Cfg {
+  static constexpr int HS = H / 64;
+  static constexpr int Q_BYTES = HS * 128 * 128;    // one 128-row tile
+  static constexpr int KV_BYTES = HS * BKV * 128;
+  static constexpr int P_BYTES = 128 * 128;
+  static constexpr int NSTG = H == 128 ? 6 : 8;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_RING = 2 * Q_BYTES;
+  static constexpr int OFF_P = OFF_RING + NSTG * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  __host__ __device__ static constexpr int tm_s(int x, int buf) { return x * 128 + buf * 64; }
+  __host__ __device__ static constexpr int tm_o(int x) { return 256 + x * H; }
+};
+
+template <int H>
+__global__ void __launch_bounds__(320, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  using C_ = Fwd2Cfg<H>;
+  constexpr int NSTG = C_::NSTG;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t sQ = sbase + C_::OFF_Q, sRing = sbase + C_::OFF_RING, sP = sbase + C_::OFF_P,
+                 bars = sbase + C_::OFF_BAR;
+  // barriers (8 bytes each): 0 Q | 1..NSTG full | 9..8+NSTG free | 17-20 S[x][buf] | 21-22 P[x] | 23-24 PV[x]
+  const uint32_t barQ = bars, barFull0 = bars + 8, barFree0 = bars + 72, barS0 = bars + 136, barP0 = bars + 168,
+                 barPV0 = bars + 184;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sptr + C_::OFF_BAR + 224);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sptr + C_::OFF_BAR + 228);
+
+  const int warp = threadIdx.x >> 5;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int n = blockIdx.y, b = blockIdx.z;
+  const int kvh = n / (a.N / a.KH);
+  const int q0 = qt * 256;
+
+  // key-block range of each tile, relative to the first block the CTA touches
+  int kstart[2], kend[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int q0x = q0 + x * 128;
+    int ke = a.Tk, ks = 0;
+    if (a.causal) ke = min(a.Tk, q0x + 128 + a.q_off);
+    if (a.window > 0) ks = max(0, q0x + a.q_off - a.window + 1);
+    if (q0x >= a.Tq || ke <= ks) { ks = 0; ke = 0; }
+    kstart[x] = ks;
+    kend[x] = ke;
+  }
+  int jb0 = 1 << 30;
+#pragma unroll
+  for (int x = 0; x < 2; ++x)
+    if (kend[x] > 0) jb0 = min(jb0, kstart[x] / BKV);
+  int lo[2], hi[2], nblk = 0;
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    lo[x] = hi[x] = 0;
+    if (kend[x] > 0) {
+      lo[x] = kstart[x] / BKV - jb0;
+      hi[x] = (kend[x] + BKV - 1) / BKV - jb0;
+      nblk = max(nblk, hi[x]);
+    }
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(barQ, 1);
+    for (int s = 0; s < NSTG; ++s) {
+      mbar_init(barFull0 + 8 * s, 1);
+      mbar_init(barFree0 + 8 * s, 1);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(barS0 + 8 * i, 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(barP0 + 8 * x, 128);
+      mbar_init(barPV0 + 8 * x, 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32((const void*)tmem_slot), C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA ring
+    if (nblk > 0 && elect_one()) {
+      mbar_expect_tx(barQ, 2 * C_::Q_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < C_::HS; ++c)
+          tma_load_2d(sQ + x * C_::Q_BYTES + c * (128 * 128), &tmQ, barQ, n * H + 64 * c, b * a.Tq + q0 + x * 128);
+      const int ntiles = 2 * nblk;
+      for (int t = 0; t < ntiles; ++t) {
+        const int s = t % NSTG, use = t / NSTG;
+        if (use > 0 &&
+            !mbar_wait_bounded(barFree0 + 8 * s, (use - 1) & 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER))
+          break;
+        const uint32_t bar = barFull0 + 8 * s;
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+        mbar_expect_tx(bar, C_::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < C_::HS; ++c)
+          tma_load_2d(sRing + s * C_::KV_BYTES + c * (BKV * 128), tm, bar, kvh * H + 64 * c,
+                      b * a.Tk + (jb0 + (t >> 1)) * BKV);
+      }
+    }
+  } else if (warp == 8) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (nblk > 0 && elect_one()) {
+      const uint32_t idesc_s = make_idesc_bf16(128, BKV, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, H, 0, 1);
+      auto stage_of = [&](int t) { return sRing + (t % NSTG) * C_::KV_BYTES; };
+      auto wait_full = [&](int t) {
+        return mbar_wait_bounded(barFull0 + 8 * (t % NSTG), (t / NSTG) & 1, abort_flag, a.status, ST_TIMEOUT_MMA);
+      };
+      auto issue_s = [&](int x, int j) {
+        const int i = j - lo[x];
+        const uint32_t d = tmem + C_::tm_s(x, i & 1);
+        const uint32_t kb = stage_of(2 * j);
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint64_t ad = make_smem_desc(sQ + x * C_::Q_BYTES + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(kb + (kk >> 2) * (BKV * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16_ss(d, ad, bd, idesc_s, kk != 0);
+        }
+        umma_commit(barS0 + 8 * (2 * x + (i & 1)));
+      };
+      auto issue_s_block = [&](int j) {        // both tiles' S of key block j; the K stage goes back when they retire
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+          if (j >= lo[x] && j < hi[x]) issue_s(x, j);
+        umma_commit(barFree0 + 8 * ((2 * j) % NSTG));
+      };
+      bool ok = mbar_wait_bounded(barQ, 0, abort_flag, a.status, ST_TIMEOUT_MMA) && wait_full(0);
+      if (ok) {
+        tc_fence_after();
+        issue_s_block(0);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        if (j + 1 < nblk) {
+          if (!wait_full(2 * j + 2)) { ok = false; break; }
+          tc_fence_after();
+          issue_s_block(j + 1);
+        }
+        if (!wait_full(2 * j + 1)) { ok = false; break; }
+        const uint32_t vb = stage_of(2 * j + 1);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (j < lo[x] || j >= hi[x]) continue;
+          const int i = j - lo[x];
+          if (!mbar_wait_bounded(barP0 + 8 * x, i & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            const uint64_t ad = make_smem_desc(sP + x * C_::P_BYTES + kk * 32, 16, 1024);
+            const uint64_t bd = make_smem_desc(vb + kk * 2048, BKV * 128, 1024);
+            umma_f16_ss(tmem + C_::tm_o(x), ad, bd, idesc_o, (i | kk) != 0);
+          }
+          umma_commit(barPV0 + 8 * x);
+        }
+        if (ok) umma_commit(barFree0 + 8 * ((2 * j + 1) % NSTG));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    const int x = warp >> 2;               // tile
+    const int r = threadIdx.x & 127;       // row inside the tile == TMEM lane
+    const int qi = q0 + x * 128 + r;
+    const bool row_valid = qi < a.Tq;
+    const int qpos = qi + a.q_off;
+    const int q0x = q0 + x * 128;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const int my_seg = (a.seg_q && row_valid) ? a.seg_q[(long long)b * a.Tq + qi] : 0;
+    const float sc2 = a.scale * LOG2E;
+    const int nx = hi[x] - lo[x];
+    const uint32_t barS = barS0 + 16 * x, barP = barP0 + 8 * x, barPV = barPV0 + 8 * x;
+    const uint32_t tO = tmem + lane_addr + C_::tm_o(x);
+    float m_used = 0.f, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nx && ok; ++i) {
+      const int j = lo[x] + i;
+      if (!mbar_wait_bounded(barS + 8 * (i & 1), (i >> 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sraw[64];
+      {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_s(x, i & 1), t0);
+        tmem_ld_32x32(tmem + lane_addr + C_::tm_s(x, i & 1) + 32, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) { sraw[c] = t0[c]; sraw[32 + c] = t1[c]; }
+      }
+      const int k0 = (jb0 + j) * BKV;
+      const int* segk = a.seg_k ? a.seg_k + (long long)b * a.Tk + k0 : nullptr;
+      const bool need_mask = (k0 + BKV > a.Tk) || (segk != nullptr) ||
+                             (a.causal && (k0 + BKV - 1 > q0x + a.q_off)) ||
+                             (a.window > 0 && (k0 <= q0x + 127 + a.q_off - a.window));
+      const bool fast = !need_mask && a.softcap <= 0.f;
+      float mx = -INFINITY;
+      if (fast) {
+        // raw scores: the scale is folded into the exponent's FMA below (scale > 0 keeps the max where it is)
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sraw[c]));
+        mx *= sc2;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int kp = k0 + c;
+          float s = __uint_as_float(sraw[c]);
+          if (a.softcap > 0.f) s = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
+          else s *= sc2;
+          bool keep = kp < a.Tk;
+          if (a.causal) keep = keep && (kp <= qpos);
+          if (a.window > 0) keep = keep && (kp > qpos - a.window);
+          if (segk) keep = keep && (kp < a.Tk) && (__ldg(segk + (kp < a.Tk ? c : 0)) == my_seg);
+          s = keep ? s : -INFINITY;
+          sraw[c] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+      }
+      float alpha = 1.f;
+      bool need = false;
+      if (mx != -INFINITY) {
+        if (l == 0.f) {
+          m_used = mx;  // nothing accumulated yet for this row: O is exactly zero
+        } else if (mx > m_used + RESCALE_THRESHOLD) {
+          alpha = exp2f(m_used - mx);
+          m_used = mx;
+          need = true;
+        }
+      }
+      const bool warp_need = __any_sync(0xffffffffu, need);
+      float psum0 = 0.f, psum1 = 0.f;
+      uint32_t pk[32];
+      const float mul = fast ? sc2 : 1.f;
+      const float neg_m = -m_used;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float p0 = exp2f(fmaf(__uint_as_float(sraw[2 * c]), mul, neg_m));
+        const float p1 = exp2f(fmaf(__uint_as_float(sraw[2 * c + 1]), mul, neg_m));
+        psum0 += p0;
+        psum1 += p1;
+        pk[c] = pack_bf16(p0, p1);
+      }
+      l = l * alpha + (psum0 + psum1);
+      if (i > 0) {
+        // PV(i-1) retired: P buffer reusable and O consistent
+        if (!mbar_wait_bounded(barPV, (i - 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        tc_fence_after();
+        if (warp_need) {
+#pragma unroll 1
+          for (int c = 0; c < H / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(tO + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_32x16(tO + c * 16, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      uint8_t* prow = sptr + C_::OFF_P + x * C_::P_BYTES + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 v = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(barP);
+    }
+    // ------------------------------------------------------------- epilogue
+    if (ok && nx > 0) ok = mbar_wait_bounded(barPV, (nx - 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+    __nv_bfloat16* orow = a.O + ((long long)b * a.Tq + qi) * a.ldo + (long long)n * H;
+#pragma unroll 1
+    for (int c = 0; c < H / 32; ++c) {
+      uint32_t o[32];
+      if (nx > 0 && ok) {
+        tmem_ld_32x32(tO + c * 32, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0;
+      }
+      if (row_valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(o[8 * g + 0]) * inv_l, __uint_as_float(o[8 * g + 1]) * inv_l);
+          v.y = pack_bf16(__uint_as_float(o[8 * g + 2]) * inv_l, __uint_as_float(o[8 * g + 3]) * inv_l);
+          v.z = pack_bf16(__uint_as_float(o[8 * g + 4]) * inv_l, __uint_as_float(o[8 * g + 5]) * inv_l);
+          v.w = pack_bf16(__uint_as_float(o[8 * g + 6]) * inv_l, __uint_as_float(o[8 * g + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+        }
+      }
+    }
+    if (row_valid && a.lse)
+      a.lse[((long long)b * a.N + n) * a.Tq + qi] = (l > 0.f) ? (m_used / LOG2E + logf(l)) : INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // copies in flight land before the CTA's memory goes away
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C_::TMEM_COLS);
+  }
+}
+
+template <int H>
+int launch_fwd2(const void* q, const void* k, const void* v, const AttnArgs& a, long long ldq,
+                long long ldk, long long ldv, cudaStream_t stream) {
+  using C_ = Fwd2Cfg<H>;
+  CUtensorMap tq, tk, tv;
+  if (tb_make_tmap_2d_bf16(&tq, q, (uint64_t)a.B * a.Tq, (uint64_t)a.N * H, ldq, 128, 64, 1)) return -3;
+  if (tb_make_tmap_2d_bf16(&tk, k, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldk, BKV, 64, 1)) return -3;
+  if (tb_make_tmap_2d_bf16(&tv, v, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldv, BKV, 64, 1)) return -3;
+  static DeviceOnce once;
+  if (once.first() &&
+      cudaFuncSetAttribute(attn_fwd2_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess)
+    return -5;
+  dim3 grid((a.Tq + 255) / 256, a.N, a.B);
+  attn_fwd2_kernel<H><<<grid, 320, C_::SMEM_BYTES, stream>>>(tq, tk, tv, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// The two-tile kernel serves head dims up to 128 once there are more than 128 query rows; TUNIX_B200_ATTN_ONE_TILE=1
+// keeps every call on the one-tile kernel (A/B measurements).
+bool use_two_tiles(int H, int Tq) {
+  static const bool off = getenv("TUNIX_B200_ATTN_ONE_TILE") != nullptr;
+  return !off && H <= 128 && Tq > 128;
+}
+
 }  // namespace
 
 // q: [B*Tq, N*H] row stride ldq; k, v: [B*Tk, KH*H]; o: [B*Tq, N*H]; lse: [B, N, Tq] fp32 (may be null).
@@ -353,6 +716,8 @@ TB_API int tb_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   a.scale = scale; a.softcap = softcap; a.causal = causal; a.window = window; a.q_off = q_off;
   a.seg_q = seg_q; a.seg_k = seg_k;
   a.O = reinterpret_cast<__nv_bfloat16*>(o); a.ldo = ldo; a.lse = lse; a.status = status;
+  if (use_two_tiles(H, Tq))
+    return H == 64 ? launch_fwd2<64>(q, k, v, a, ldq, ldk, ldv, stream) : launch_fwd2<128>(q, k, v, a, ldq, ldk, ldv, stream);
   switch (H) {
     case 64: return launch_fwd<64>(q, k, v, a, ldq, ldk, ldv, stream);
     case 128: return launch_fwd<128>(q, k, v, a, ldq, ldk, ldv, stream);

@@ -9,9 +9,18 @@ from .trace import PerfTracer
 
 
 def write_trace(tracer: PerfTracer, path: str, process_name: str = "tunix_b200") -> str:
+    return write_spans(tracer.spans(), path, tracer.t0, process_name)
+
+
+def write_spans(spans: list, path: str, t0: float = 0.0, process_name: str = "tunix_b200") -> str:
+    """The same file from a list of spans (one global step, one rank): what the metrics exporters write per step."""
+    class _T:
+        pass
+    tracer = _T()
+    tracer.t0 = t0
     events = [{"name": "process_name", "ph": "M", "pid": 0, "args": {"name": process_name}}]
     tids: dict = {}
-    for s in tracer.spans():
+    for s in spans:
         tid = tids.setdefault(s.timeline, len(tids))
         ev = {"name": s.name, "ph": "X", "pid": 0, "tid": tid, "ts": (s.begin - tracer.t0) * 1e6,
               "dur": s.duration * 1e6, "args": {k: v for k, v in s.tags.items()}}

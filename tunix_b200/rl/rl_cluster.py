@@ -248,7 +248,7 @@ class RLCluster:
         for (mode, mb, by_ids), idx in groups.items():
             prompts = None if by_ids else [items[i]["prompt"] for i in idx]
             ids = [items[i]["ids"] for i in idx] if by_ids else None
-            res = self._generate_local(prompts, Mode(mode), mb, False, ids)
+            res = self._generate_local(prompts, Mode(mode), mb, False, ids)     # records its own "rollout" span
             for i, row in zip(idx, self._split_output(res)):
                 out[i] = row
         return out
@@ -309,7 +309,8 @@ class RLCluster:
             m = None if items[idx[0]]["m"] is None else torch.as_tensor(np.stack([items[i]["m"] for i in idx]), device=dev)
             fn = lambda pp, cc, mm: self.inference_worker.get_ref_per_token_logps(  # noqa: E731
                 pp, cc, pad, eos, completion_mask=mm, chunk_size=chunk, **dict(kw))
-            res = self._mb_apply(fn, (p, c, m), mb).float().cpu().numpy()
+            with self._span("refer_inference"):
+                res = self._mb_apply(fn, (p, c, m), mb).float().cpu().numpy()
             for i, row in zip(idx, res):
                 out[i] = row
         return out
@@ -393,8 +394,8 @@ class RLCluster:
     def sync_weights(self) -> None:
         """Controllers: bring the sampler's weights up to date with the actor's; bump the global step. Ranks in
         `serve()` join the transfer when it crosses ranks."""
+        self.generate_finish()
         with self._span("weight_sync"):
-            self.generate_finish()
             if not self._rollout_shares_weights:
                 self.exchange.sync()
             if self.cluster_config.gc_collect_after_weight_sync:

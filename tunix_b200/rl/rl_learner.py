@@ -180,7 +180,6 @@ class RLLearner(abc.ABC):
                 if max_steps is not None and self.rl_cluster.global_steps >= max_steps:
                     break
                 q: SimpleDataQueue = SimpleDataQueue()
-                fut = executor.submit(self._prepare_data, it, q, Mode.TRAIN, 1)
                 got_any = False
 
                 def counted():
@@ -189,11 +188,14 @@ class RLLearner(abc.ABC):
                         got_any = True
                         self._iter_steps += 1
                         yield ex
-                self._train_on(counted())
-                fut.result()
-                if not got_any:
-                    break
-                self.rl_cluster.sync_weights()
+                with self._step_group() as step_span:
+                    fut = executor.submit(self._prepare_data, it, q, Mode.TRAIN, 1)
+                    self._train_on(counted())
+                    fut.result()
+                    if not got_any:
+                        break
+                    self.rl_cluster.sync_weights()
+                self._export_perf(step_span)
                 self.rl_cluster.flush_metrics()
                 if eval_ds is not None and self.tcfg.eval_every_n_steps and \
                         self.rl_cluster.global_steps % self.tcfg.eval_every_n_steps == 0:
@@ -203,6 +205,29 @@ class RLLearner(abc.ABC):
             self.rl_cluster.close()
             if self.reward_manager is not None and hasattr(self.reward_manager, "close"):
                 self.reward_manager.close()
+
+    def _step_group(self):
+        """Span group around one global step (a no-op context without a tracer)."""
+        import contextlib
+        perf = self.rl_cluster.perf
+        return perf.span_group("global_step", step=self.rl_cluster.global_steps) if perf is not None \
+            else contextlib.nullcontext()
+
+    def _export_perf(self, step_span) -> None:
+        """Reduce the step's spans to the layout's perf metrics and hand them to the metrics buffer (:627-658)."""
+        perf = self.rl_cluster.perf
+        if perf is None or step_span is None:
+            return
+        fn = getattr(self, "_perf_export_fn", None)
+        if fn is None:
+            from ..perf.export import PerfMetricsExport
+            opts = self.tcfg.perf_metrics_options
+            custom = getattr(opts, "custom_export_fn", None) if opts is not None else None
+            fn = custom or PerfMetricsExport.from_cluster_config(self.rl_cluster.cluster_config, self.rl_cluster.placement)
+            self._perf_export_fn = fn
+        metrics = fn(perf, step_span)
+        self.rl_cluster.buffer_metrics({k: (v, np.mean) for k, v in metrics.items()}, Mode.TRAIN,
+                                       step=self.rl_cluster.global_steps - 1)
 
     def _open_round(self, batch: dict) -> None:
         """Send the prompts of `batch` to the rollout ranks now; `_generate_and_compute_advantage` picks the result up."""
@@ -226,11 +251,6 @@ class RLLearner(abc.ABC):
                 break
             cur = nxt
             q: SimpleDataQueue = SimpleDataQueue()
-            self._prepare_data(iter([cur]), q, Mode.TRAIN, 1)          # closes the round of `cur`, scores it
-            nxt = next(it, None)
-            last = max_steps is not None and self.rl_cluster.global_steps + 1 >= max_steps
-            if nxt is not None and ahead and not last:
-                self._open_round(nxt)
             got_any = False
 
             def counted():
@@ -239,10 +259,17 @@ class RLLearner(abc.ABC):
                     got_any = True
                     self._iter_steps += 1
                     yield ex
-            self._train_on(counted())
-            if not got_any:
-                break
-            self.rl_cluster.sync_weights()       # closes an open round first: rounds do not nest
+            with self._step_group() as step_span:
+                self._prepare_data(iter([cur]), q, Mode.TRAIN, 1)          # closes the round of `cur`, scores it
+                nxt = next(it, None)
+                last = max_steps is not None and self.rl_cluster.global_steps + 1 >= max_steps
+                if nxt is not None and ahead and not last:
+                    self._open_round(nxt)
+                self._train_on(counted())
+                if not got_any:
+                    break
+                self.rl_cluster.sync_weights()       # closes an open round first: rounds do not nest
+            self._export_perf(step_span)
             self.rl_cluster.flush_metrics()
             if eval_ds is not None and self.tcfg.eval_every_n_steps and \
                     self.rl_cluster.global_steps % self.tcfg.eval_every_n_steps == 0:
