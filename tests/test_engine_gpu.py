@@ -399,3 +399,116 @@ def test_http_front_end_and_model_client_over_the_real_engine():
         assert "tunix_b200_http_requests_total 7" in text
     _lib.raise_if_kernel_error()
     assert eng.pool.free_pages == eng.pool.num_pages
+
+
+def test_engine_prefix_cache_shares_prompt_pages_between_generations():
+    """Eight generations of one prompt (a GRPO group): the prompt is prefilled once, the other seven reuse its full
+    pages and compute only the tail; greedy outputs equal those of an engine without the cache, and a second call
+    with the same prompt (a follow-up) hits the pages the first one left behind."""
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import PagedEngine
+    model = _model()
+    cc = CacheConfig(cache_size=256, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(1)
+    pa = [1] + rng.integers(3, 500, size=69).tolist()          # 70 tokens: 4 full pages of 16 + a tail of 6
+    pb = [1] + rng.integers(3, 500, size=31).tolist()          # 32 tokens: exactly 2 pages (the last token is recomputed)
+    prompts = [pa] * 8 + [pb] * 3
+    plain = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=16, prefix_caching=False)
+    ref = plain(prompt_token_ids=prompts, max_generation_steps=12, return_logprobs=True, eos_tokens=[2])
+    eng = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=16)
+    out = eng(prompt_token_ids=prompts, max_generation_steps=12, return_logprobs=True, eos_tokens=[2])
+    _lib.raise_if_kernel_error()
+    assert eng.pool.hit_tokens == 7 * 64 + 2 * 32 and eng.pool.prompt_tokens == 8 * 70 + 3 * 32
+    same = total = 0
+    for a, b, la, lb in zip(ref.tokens, out.tokens, ref.logprobs, out.logprobs):
+        n = min(len(a), len(b))
+        same += int((np.asarray(a[:n]) == np.asarray(b[:n])).sum())
+        total += max(len(a), len(b))
+        assert abs(la[0] - lb[0]) < 5e-2
+    assert same / total > 0.9, (same, total)
+    assert eng.pool.free_pages == eng.pool.num_pages           # cached pages are evictable: nothing is lost
+    hits = eng.pool.hit_tokens
+    again = eng(prompt_token_ids=[pa + [int(t) for t in out.tokens[0][:10]]], max_generation_steps=4, eos_tokens=[2])
+    assert eng.pool.hit_tokens - hits == 64 and len(again.tokens[0]) >= 1      # prompt pages of the first call
+
+
+def test_engine_small_pool_queues_and_preempts_instead_of_failing():
+    """A pool far smaller than slots x full length: requests wait for pages, and when the running sequences outgrow the
+    pool the youngest goes back to the queue. Every request is still answered, with the greedy tokens of a roomy engine."""
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import PagedEngine
+    model = _model()
+    cc = CacheConfig(cache_size=128, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(2)
+    prompts = [[1] + rng.integers(3, 500, size=int(n)).tolist() for n in (20, 35, 18, 40, 25, 30)]
+    roomy = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=6, prefix_caching=False)
+    ref = roomy(prompt_token_ids=prompts, max_generation_steps=48, eos_tokens=[-1])
+    # 14 pages = 224 tokens: three prompts fit at first, none of the six reaches 40 + 48 tokens side by side
+    tight = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=6, num_pages=14, check_every=4, prefix_caching=False)
+    out = tight(prompt_token_ids=prompts, max_generation_steps=48, eos_tokens=[-1])
+    _lib.raise_if_kernel_error()
+    assert tight.preemptions > 0
+    same = total = 0
+    for a, b in zip(ref.tokens, out.tokens):
+        assert len(b) == 48
+        same += int((np.asarray(a) == np.asarray(b)).sum())
+        total += 48
+    assert same / total > 0.9, (same, total)
+    assert tight.pool.free_pages == 14
+    with pytest.raises(RuntimeError, match="cannot hold"):
+        PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=2, num_pages=2)(
+            prompt_token_ids=[prompts[3]], max_generation_steps=4, eos_tokens=[-1])
+
+
+def test_engine_chunked_prefill_forbidden_tokens_and_final_softcap():
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import PagedEngine
+    from tunix_b200.generate.sampler import Sampler
+    model = _model(final_logit_softcap=20.0)
+    cc = CacheConfig(cache_size=256, num_layers=2, num_kv_heads=2, head_dim=64)
+    rng = np.random.default_rng(3)
+    prompts = [[1] + rng.integers(3, 500, size=int(n)).tolist() for n in (100, 37, 64)]
+    whole = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=4, prefix_caching=False)
+    a = whole(prompt_token_ids=prompts, max_generation_steps=10, return_logprobs=True, eos_tokens=[2])
+    pieces = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=4, prefix_caching=False, prefill_chunk=32)
+    b = pieces(prompt_token_ids=prompts, max_generation_steps=10, return_logprobs=True, eos_tokens=[2])
+    _lib.raise_if_kernel_error()
+    for x, y, lx, ly in zip(a.tokens, b.tokens, a.logprobs, b.logprobs):
+        assert int(x[0]) == int(y[0]) and abs(lx[0] - ly[0]) < 5e-2        # the prompt's last hidden state is the same
+    # the soft-capped log-probability of the first token equals the dense sampler's
+    dense = Sampler(model, Tok(), cc)(prompt_token_ids=prompts, max_generation_steps=2, return_logprobs=True, eos_tokens=[2])
+    for ld, la in zip(dense.logprobs, a.logprobs):
+        assert abs(ld[0] - la[0]) < 5e-2
+    # forbidden ids never come out, and the rest of the distribution is renormalised without them
+    banned = sorted({int(t) for row in a.tokens for t in row})[:6]
+    c = whole(prompt_token_ids=prompts, max_generation_steps=10, return_logprobs=True, eos_tokens=[2], forbidden_tokens=banned)
+    assert not ({int(t) for row in c.tokens for t in row} & set(banned))
+    d = Sampler(model, Tok(), cc)(prompt_token_ids=prompts, max_generation_steps=2, return_logprobs=True, eos_tokens=[2],
+                                  forbidden_tokens=banned)
+    for ld, lc, td, tc_ in zip(d.logprobs, c.logprobs, d.tokens, c.tokens):
+        assert int(td[0]) == int(tc_[0]) and abs(ld[0] - lc[0]) < 5e-2
+
+
+def test_engine_decodes_a_mixture_of_experts_model_like_the_dense_sampler():
+    from tunix_b200 import _lib
+    from tunix_b200.common.configs import CacheConfig
+    from tunix_b200.generate.engine import PagedEngine
+    from tunix_b200.generate.sampler import Sampler
+    model = _model(num_experts=8, num_experts_per_tok=2, moe_hidden_dim=128, hidden_dim=128)
+    cc = CacheConfig(cache_size=128, num_layers=2, num_kv_heads=2, head_dim=64)
+    prompts = [[1, 5, 9, 77, 30], [1, 200, 3], [1] + list(range(10, 40))]
+    dense = Sampler(model, Tok(), cc)(prompt_token_ids=prompts, max_generation_steps=12, return_logprobs=True, eos_tokens=[2])
+    for graph in (False, True):
+        eng = PagedEngine(model, Tok(), cc, page_size=16, max_running_requests=4, use_cuda_graph=graph)
+        out = eng(prompt_token_ids=prompts, max_generation_steps=12, return_logprobs=True, eos_tokens=[2])
+        _lib.raise_if_kernel_error()
+        same = total = 0
+        for a, b, la, lb in zip(dense.tokens, out.tokens, dense.logprobs, out.logprobs):
+            n = min(len(a), len(b))
+            same += int((np.asarray(a[:n]) == np.asarray(b[:n])).sum())
+            total += n
+            assert abs(la[0] - lb[0]) < 6e-2
+        assert same / total > 0.85, (graph, same, total)

@@ -106,3 +106,36 @@ def test_ppo_learner_runs():
     learner.train([{"prompts": ["ab", "cd", "ef", "gh"]}])
     assert cl.global_steps == 1
     assert cl.critic_trainer.train_steps == 1
+
+
+def test_micro_batch_items_are_merged_to_the_service_target_and_every_pass_ends_with_an_update():
+    """A dataset that yields micro-batches of 2 prompts, mini-batch 4, rollout micro-batch 4: two items are merged into
+    one generate-and-score pass; the step's micro-batches carry explicit update flags (last one always updates)."""
+    actor = create_model(_cfg(), seed=0)
+    ref = create_model(_cfg(), seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=4,
+                          train_micro_batch_size=1, rollout_micro_batch_size=4, compute_logps_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3, kv_cache_size=32,
+                       eos_tokens=[63])
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(),
+                   cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    learner = GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.04))
+    calls = []
+    orig = learner._generate_and_compute_advantage
+
+    def spy(batch, mode=None):
+        calls.append(len(batch["prompts"]))
+        return orig(batch, mode)
+    learner._generate_and_compute_advantage = spy
+    flags = []
+    orig_train = cl.actor_trainer._train_step
+
+    def spy_step(batch, is_update):
+        flags.append(bool(is_update))
+        return orig_train(batch, is_update)
+    cl.actor_trainer._train_step = spy_step
+    assert learner._service_target() == 4
+    learner.train([{"prompts": [f"{chr(97 + i)}b", f"{chr(98 + i)}c"]} for i in range(4)])      # 4 items of 2 prompts
+    assert cl.global_steps == 2 and calls == [8, 8]             # 2 items x 2 prompts x G per pass
+    assert flags == [False, False, False, True] * 2             # 4 micro-batches of 1 prompt x G, accumulation 4
+    assert cl.actor_trainer.train_steps == 2

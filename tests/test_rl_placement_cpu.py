@@ -45,7 +45,7 @@ def _run(rank, world, port, layout, out):
         r2m = {Role.ACTOR: [0, 1], Role.ROLLOUT: [2], Role.REFERENCE: [3]}
     pl = RolePlacement(r2m)
     tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=3, actor_optimizer=optim.AdamW(1e-2, weight_decay=0.0),
-                          mini_batch_size=4, train_micro_batch_size=2)
+                          mini_batch_size=2, train_micro_batch_size=1)
     rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3, kv_cache_size=32,
                        eos_tokens=[63])
     cc = ClusterConfig(role_to_mesh=r2m, training_config=tc, rollout_config=rc)

@@ -143,9 +143,13 @@ def grpo(args) -> dict:
     tok = IdTokenizer(cfg.vocab_size)
     G = 8
     per_rank = max(args.prompts // n_ctl, 1)
+    # batch sizes count prompts; every prompt stands for its G generations (a micro-batch of `micro` prompts is
+    # micro x G sequences)
+    micro = max(1, min(args.micro, per_rank))
     tcfg = RLTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, actor_optimizer=optim.AdamW(1e-6, max_grad_norm=1.0),
-                            mini_batch_size=per_rank * G, train_micro_batch_size=args.micro, rollout_micro_batch_size=per_rank * G,
-                            compute_logps_micro_batch_size=args.micro * 2, pbar_description=None)
+                            mini_batch_size=per_rank, train_micro_batch_size=micro, rollout_micro_batch_size=per_rank,
+                            compute_logps_micro_batch_size=micro * 2 if per_rank % (micro * 2) == 0 else micro,
+                            pbar_description=None)
     rc = RolloutConfig(max_tokens_to_generate=768, max_prompt_length=256, temperature=1.0, top_p=1.0, seed=2,
                        kv_cache_size=1032, eos_tokens=[-1], max_running_requests=args.max_running)
     cluster = RLCluster(actor=actor, reference=ref, rollout_model=sampler, tokenizer=tok, placement=pl,

@@ -347,12 +347,17 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnArgs& a, l
 // sit one per scheduler, every K tile is fetched only after the previous S = Q K^T has retired
 // (one K buffer), and the P buffer is single. Here a CTA owns 256 query rows of one head as two
 // 128-row tiles a and b:
-//   warps 0-3 / 4-7 : softmax of tile a / b, one thread per query row (TMEM lanes 0-127 each)
-//   warp 8          : one thread issues every tcgen05.mma: S_a, S_b of key block j+1 are queued
-//                     before it waits for P_a(j), P_b(j), so the tensor pipe always has work
-//                     from one tile while the other tile's rows are in the softmax
-//   warp 9          : one thread runs the TMA ring (K_0 V_0 K_1 V_1 ... over NSTG stages, three
-//                     key blocks ahead); a stage is handed back by a tcgen05.commit
+//   warps 0-7 / 8-15 : softmax of tile a / b. TWO threads per query row: warps 0-3 take key columns
+//                      0-31 of a block, warps 4-7 columns 32-63 (same TMEM lanes, other columns); the
+//                      two halves of a row exchange their maxima through shared memory once per block
+//                      and each rescales / writes back its half of O. With one thread per row an SM
+//                      holds two softmax warps per scheduler and the kernel is bound by instruction
+//                      latency (ncu: 0.32 instructions per cycle and scheduler, tensor pipe 29 %).
+//   warp 16          : one thread issues every tcgen05.mma: S_a, S_b of key block j+1 are queued
+//                      before it waits for P_a(j), P_b(j), so the tensor pipe always has work
+//                      from one tile while the other tile's rows are in the softmax
+//   warp 17          : one thread runs the TMA ring (K_0 V_0 K_1 V_1 ... over NSTG stages, three
+//                      key blocks ahead); a stage is handed back by a tcgen05.commit
 // TMEM: S_a[2] | S_b[2] | O_a | O_b = 4*64 + 2*H columns. K / V tiles are read once per 256 rows.
 // ---------------------------------------------------------------------------------------------
 template <int H>
@@ -366,14 +371,15 @@ struct Fwd2Cfg {
   static constexpr int OFF_RING = 2 * Q_BYTES;
   static constexpr int OFF_P = OFF_RING + NSTG * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_MX = OFF_BAR + 256;      // row maxima / sums exchanged between the two column halves
+  static constexpr int SMEM_BYTES = OFF_MX + 2 * 2 * 2 * 128 * 4 + 1024;
   static constexpr int TMEM_COLS = 512;
   __host__ __device__ static constexpr int tm_s(int x, int buf) { return x * 128 + buf * 64; }
   __host__ __device__ static constexpr int tm_o(int x) { return 256 + x * H; }
 };
 
 template <int H>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
   using C_ = Fwd2Cfg<H>;
@@ -383,9 +389,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sptr = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t sQ = sbase + C_::OFF_Q, sRing = sbase + C_::OFF_RING, sP = sbase + C_::OFF_P,
                  bars = sbase + C_::OFF_BAR;
-  // barriers (8 bytes each): 0 Q | 1..NSTG full | 9..8+NSTG free | 17-20 S[x][buf] | 21-22 P[x] | 23-24 PV[x]
+  // barriers (8 bytes each): 0 Q | 1..NSTG full | 9..8+NSTG free | 17-20 S[x][buf] | 21-22 P[x] | 23-24 PV[x] |
+  //                          25-26 row-max exchange[x]
   const uint32_t barQ = bars, barFull0 = bars + 8, barFree0 = bars + 72, barS0 = bars + 136, barP0 = bars + 168,
-                 barPV0 = bars + 184;
+                 barPV0 = bars + 184, barX0 = bars + 200;
+  float* s_mx = reinterpret_cast<float*>(sptr + C_::OFF_MX);     // [2 parities][2 tiles][2 halves][128 rows]
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sptr + C_::OFF_BAR + 224);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sptr + C_::OFF_BAR + 228);
 
@@ -430,13 +438,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 4; ++i) mbar_init(barS0 + 8 * i, 1);
     for (int x = 0; x < 2; ++x) {
-      mbar_init(barP0 + 8 * x, 128);
+      mbar_init(barP0 + 8 * x, 256);
       mbar_init(barPV0 + 8 * x, 1);
+      mbar_init(barX0 + 8 * x, 256);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(smem_u32((const void*)tmem_slot), C_::TMEM_COLS);
     tmem_relinquish();
   }
@@ -445,7 +454,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 9) {
+  if (warp == 17) {
     // ------------------------------------------------------------------ TMA ring
     if (nblk > 0 && elect_one()) {
       mbar_expect_tx(barQ, 2 * C_::Q_BYTES);
@@ -469,25 +478,30 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       b * a.Tk + (jb0 + (t >> 1)) * BKV);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 16) {
     // ---------------------------------------------------------------- MMA issuer
     if (nblk > 0 && elect_one()) {
       const uint32_t idesc_s = make_idesc_bf16(128, BKV, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(128, H, 0, 1);
-      auto stage_of = [&](int t) { return sRing + (t % NSTG) * C_::KV_BYTES; };
+      // Descriptors are built once: the start-address field sits in the low bits, so the descriptor of a tile
+      // further along is the base plus (byte offset >> 4). The issuing thread is the one serial resource both
+      // tiles share; every instruction it does not spend on descriptor arithmetic goes to issuing MMAs.
+      const uint64_t qd0 = make_smem_desc(sQ, 16, 1024);
+      const uint64_t kd0 = make_smem_desc(sRing, 16, 1024);
+      const uint64_t pd0 = make_smem_desc(sP, 16, 1024);
+      const uint64_t vd0 = make_smem_desc(sRing, BKV * 128, 1024);
       auto wait_full = [&](int t) {
         return mbar_wait_bounded(barFull0 + 8 * (t % NSTG), (t / NSTG) & 1, abort_flag, a.status, ST_TIMEOUT_MMA);
       };
       auto issue_s = [&](int x, int j) {
         const int i = j - lo[x];
         const uint32_t d = tmem + C_::tm_s(x, i & 1);
-        const uint32_t kb = stage_of(2 * j);
+        const uint64_t qd = qd0 + (uint64_t)((x * C_::Q_BYTES) >> 4);
+        const uint64_t kd = kd0 + (uint64_t)((((2 * j) % NSTG) * C_::KV_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < H / 16; ++kk) {
-          const uint64_t ad = make_smem_desc(sQ + x * C_::Q_BYTES + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc(kb + (kk >> 2) * (BKV * 128) + (kk & 3) * 32, 16, 1024);
-          umma_f16_ss(d, ad, bd, idesc_s, kk != 0);
-        }
+        for (int kk = 0; kk < H / 16; ++kk)
+          umma_f16_ss(d, qd + (uint64_t)(((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4),
+                      kd + (uint64_t)(((kk >> 2) * (BKV * 128) + (kk & 3) * 32) >> 4), idesc_s, kk != 0);
         umma_commit(barS0 + 8 * (2 * x + (i & 1)));
       };
       auto issue_s_block = [&](int j) {        // both tiles' S of key block j; the K stage goes back when they retire
@@ -508,19 +522,18 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           issue_s_block(j + 1);
         }
         if (!wait_full(2 * j + 1)) { ok = false; break; }
-        const uint32_t vb = stage_of(2 * j + 1);
+        const uint64_t vd = vd0 + (uint64_t)((((2 * j + 1) % NSTG) * C_::KV_BYTES) >> 4);
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (j < lo[x] || j >= hi[x]) continue;
           const int i = j - lo[x];
           if (!mbar_wait_bounded(barP0 + 8 * x, i & 1, abort_flag, a.status, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
+          const uint64_t pd = pd0 + (uint64_t)((x * C_::P_BYTES) >> 4);
 #pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk) {
-            const uint64_t ad = make_smem_desc(sP + x * C_::P_BYTES + kk * 32, 16, 1024);
-            const uint64_t bd = make_smem_desc(vb + kk * 2048, BKV * 128, 1024);
-            umma_f16_ss(tmem + C_::tm_o(x), ad, bd, idesc_o, (i | kk) != 0);
-          }
+          for (int kk = 0; kk < BKV / 16; ++kk)
+            umma_f16_ss(tmem + C_::tm_o(x), pd + (uint64_t)((kk * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                        (i | kk) != 0);
           umma_commit(barPV0 + 8 * x);
         }
         if (ok) umma_commit(barFree0 + 8 * ((2 * j + 1) % NSTG));
@@ -528,8 +541,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ softmax warps
-    const int x = warp >> 2;               // tile
-    const int r = threadIdx.x & 127;       // row inside the tile == TMEM lane
+    const int x = warp >> 3;               // tile
+    const int half = (warp >> 2) & 1;      // which 32 of the block's 64 key columns
+    const int r = ((warp & 3) << 5) | (threadIdx.x & 31);   // row inside the tile == TMEM lane
     const int qi = q0 + x * 128 + r;
     const bool row_valid = qi < a.Tq;
     const int qpos = qi + a.q_off;
@@ -537,57 +551,69 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int my_seg = (a.seg_q && row_valid) ? a.seg_q[(long long)b * a.Tq + qi] : 0;
     const float sc2 = a.scale * LOG2E;
-    const int nx = hi[x] - lo[x];
-    const uint32_t barS = barS0 + 16 * x, barP = barP0 + 8 * x, barPV = barPV0 + 8 * x;
-    const uint32_t tO = tmem + lane_addr + C_::tm_o(x);
-    float m_used = 0.f, l = 0.f;
+    const int lo_x = x ? lo[1] : lo[0];
+    const int nx = (x ? hi[1] : hi[0]) - lo_x;
+    const uint32_t barS = barS0 + 16 * x, barP = barP0 + 8 * x, barPV = barPV0 + 8 * x, barX = barX0 + 8 * x;
+    constexpr int HH = H / 2;              // this thread's columns of O
+    const uint32_t tO = tmem + lane_addr + C_::tm_o(x) + half * HH;
+    float m_used = 0.f, l = 0.f;           // l: this half's share of the row sum
+    bool seen = false;                     // a key was visible to this row (decided on the maximum both halves share)
     bool ok = true;
     for (int i = 0; i < nx && ok; ++i) {
-      const int j = lo[x] + i;
+      const int j = lo_x + i;
       if (!mbar_wait_bounded(barS + 8 * (i & 1), (i >> 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sraw[64];
-      {
-        uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_s(x, i & 1), t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_s(x, i & 1) + 32, t1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) { sraw[c] = t0[c]; sraw[32 + c] = t1[c]; }
-      }
+      uint32_t sraw[32];
+      tmem_ld_32x32(tmem + lane_addr + C_::tm_s(x, i & 1) + half * 32, sraw);
+      tmem_ld_wait();
       const int k0 = (jb0 + j) * BKV;
-      const int* segk = a.seg_k ? a.seg_k + (long long)b * a.Tk + k0 : nullptr;
+      const int kh = k0 + half * 32;
+      const int* segk = a.seg_k ? a.seg_k + (long long)b * a.Tk + kh : nullptr;
       const bool need_mask = (k0 + BKV > a.Tk) || (segk != nullptr) ||
                              (a.causal && (k0 + BKV - 1 > q0x + a.q_off)) ||
                              (a.window > 0 && (k0 <= q0x + 127 + a.q_off - a.window));
       const bool fast = !need_mask && a.softcap <= 0.f;
       float mx = -INFINITY;
       if (fast) {
-        // raw scores: the scale is folded into the exponent's FMA below (scale > 0 keeps the max where it is)
+        // raw scores: the scale is folded into the exponent's FMA below (scale > 0 keeps the max where it is);
+        // four independent chains instead of one of 32
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sraw[c]));
-        mx *= sc2;
+        for (int c = 0; c < 32; c += 4) {
+          m0 = fmaxf(m0, __uint_as_float(sraw[c]));
+          m1 = fmaxf(m1, __uint_as_float(sraw[c + 1]));
+          m2 = fmaxf(m2, __uint_as_float(sraw[c + 2]));
+          m3 = fmaxf(m3, __uint_as_float(sraw[c + 3]));
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sc2;
       } else {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const int kp = k0 + c;
-          float s = __uint_as_float(sraw[c]);
-          if (a.softcap > 0.f) s = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
-          else s *= sc2;
+        for (int c = 0; c < 32; ++c) {
+          const int kp = kh + c;
+          float sv = __uint_as_float(sraw[c]);
+          if (a.softcap > 0.f) sv = a.softcap * tanhf(sv * a.scale / a.softcap) * LOG2E;
+          else sv *= sc2;
           bool keep = kp < a.Tk;
           if (a.causal) keep = keep && (kp <= qpos);
           if (a.window > 0) keep = keep && (kp > qpos - a.window);
           if (segk) keep = keep && (kp < a.Tk) && (__ldg(segk + (kp < a.Tk ? c : 0)) == my_seg);
-          s = keep ? s : -INFINITY;
-          sraw[c] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
+          sv = keep ? sv : -INFINITY;
+          sraw[c] = __float_as_uint(sv);
+          mx = fmaxf(mx, sv);
         }
       }
+      // the row's maximum over both halves: both threads then take the same rescaling decision
+      float* slot = s_mx + (((i & 1) * 2 + x) * 2) * 128;
+      slot[half * 128 + r] = mx;
+      mbar_arrive(barX);
+      if (!mbar_wait_bounded(barX, i & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      mx = fmaxf(mx, slot[(half ^ 1) * 128 + r]);
       float alpha = 1.f;
       bool need = false;
       if (mx != -INFINITY) {
-        if (l == 0.f) {
-          m_used = mx;  // nothing accumulated yet for this row: O is exactly zero
+        if (!seen) {
+          m_used = mx;  // no key has been visible to this row yet: O and both halves' sums are exactly zero
+          seen = true;
         } else if (mx > m_used + RESCALE_THRESHOLD) {
           alpha = exp2f(m_used - mx);
           m_used = mx;
@@ -595,26 +621,28 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       const bool warp_need = __any_sync(0xffffffffu, need);
-      float psum0 = 0.f, psum1 = 0.f;
-      uint32_t pk[32];
+      float p0s = 0.f, p1s = 0.f, p2s = 0.f, p3s = 0.f;
+      uint32_t pk[16];
       const float mul = fast ? sc2 : 1.f;
       const float neg_m = -m_used;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float p0 = exp2f(fmaf(__uint_as_float(sraw[2 * c]), mul, neg_m));
-        const float p1 = exp2f(fmaf(__uint_as_float(sraw[2 * c + 1]), mul, neg_m));
-        psum0 += p0;
-        psum1 += p1;
-        pk[c] = pack_bf16(p0, p1);
+      for (int c = 0; c < 16; c += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(sraw[2 * c]), mul, neg_m));
+        const float e1 = exp2f(fmaf(__uint_as_float(sraw[2 * c + 1]), mul, neg_m));
+        const float e2 = exp2f(fmaf(__uint_as_float(sraw[2 * c + 2]), mul, neg_m));
+        const float e3 = exp2f(fmaf(__uint_as_float(sraw[2 * c + 3]), mul, neg_m));
+        p0s += e0; p1s += e1; p2s += e2; p3s += e3;
+        pk[c] = pack_bf16(e0, e1);
+        pk[c + 1] = pack_bf16(e2, e3);
       }
-      l = l * alpha + (psum0 + psum1);
+      l = l * alpha + ((p0s + p1s) + (p2s + p3s));
       if (i > 0) {
         // PV(i-1) retired: P buffer reusable and O consistent
         if (!mbar_wait_bounded(barPV, (i - 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
         if (warp_need) {
 #pragma unroll 1
-          for (int c = 0; c < H / 16; ++c) {
+          for (int c = 0; c < HH / 16; ++c) {
             uint32_t o[16];
             tmem_ld_32x16(tO + c * 16, o);
             tmem_ld_wait();
@@ -625,11 +653,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
+      // this half of the P row -> smem, K-major 128-byte swizzle: 16-byte chunk c of row r lands at c ^ (r & 7)
       uint8_t* prow = sptr + C_::OFF_P + x * C_::P_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 v = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+        *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = v;
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -638,10 +667,16 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------- epilogue
     if (ok && nx > 0) ok = mbar_wait_bounded(barPV, (nx - 1) & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE);
     tc_fence_after();
+    // the row sum is the two halves' shares together
+    float* lslot = s_mx + ((nx & 1) * 2 + x) * 2 * 128;
+    lslot[half * 128 + r] = l;
+    mbar_arrive(barX);
+    if (ok) ok = mbar_wait_bounded(barX, nx & 1, abort_flag, a.status, ST_TIMEOUT_EPILOGUE);
+    if (ok) l += lslot[(half ^ 1) * 128 + r];
     const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-    __nv_bfloat16* orow = a.O + ((long long)b * a.Tq + qi) * a.ldo + (long long)n * H;
+    __nv_bfloat16* orow = a.O + ((long long)b * a.Tq + qi) * a.ldo + (long long)n * H + half * HH;
 #pragma unroll 1
-    for (int c = 0; c < H / 32; ++c) {
+    for (int c = 0; c < HH / 32; ++c) {
       uint32_t o[32];
       if (nx > 0 && ok) {
         tmem_ld_32x32(tO + c * 32, o);
@@ -662,7 +697,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-    if (row_valid && a.lse)
+    if (row_valid && a.lse && half == 0)
       a.lse[((long long)b * a.N + n) * a.Tq + qi] = (l > 0.f) ? (m_used / LOG2E + logf(l)) : INFINITY;
   }
 
@@ -671,7 +706,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // copies in flight land before the CTA's memory goes away
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tc_fence_after();
     tmem_dealloc(tmem, C_::TMEM_COLS);
   }
@@ -690,7 +725,7 @@ int launch_fwd2(const void* q, const void* k, const void* v, const AttnArgs& a, 
       cudaFuncSetAttribute(attn_fwd2_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess)
     return -5;
   dim3 grid((a.Tq + 255) / 256, a.N, a.B);
-  attn_fwd2_kernel<H><<<grid, 320, C_::SMEM_BYTES, stream>>>(tq, tk, tv, a);
+  attn_fwd2_kernel<H><<<grid, 576, C_::SMEM_BYTES, stream>>>(tq, tk, tv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -6,7 +6,11 @@
 //  * top-k / top-p as probability thresholds found by bisection (count(p >= t) >= k, mass(p >= t) >= top_p):
 //    no sort, no [B, V] scratch; each iteration re-reads the row, which stays in L2;
 //  * the draw is Gumbel-max over the kept tokens with a counter-based Philox stream keyed by
-//    (seed, step, row, token), so a sequence's randomness does not depend on batch composition.
+//    (seed, step, row, token), so a sequence's randomness does not depend on batch composition;
+//  * the final logit soft-cap (cap * tanh(z / cap), Gemma-2/3) and a list of forbidden token ids
+//    (tunix/generate/sampler.py:84-85,407) are applied to the row in place by the first pass, so the
+//    engine needs no [B, V] element-wise kernel in front of this one and the returned log-probability
+//    is the one of the distribution that was sampled from.
 //
 // Replaces lax.top_k + softmax + cumsum mask + categorical of the reference (tunix/generate/sampler.py:112-168).
 #include "common.cuh"
@@ -42,9 +46,10 @@ struct ArgMax {
 __device__ __forceinline__ ArgMax amax(ArgMax a, ArgMax b) { return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a; }
 
 __global__ void __launch_bounds__(1024)
-sample_kernel(const float* __restrict__ logits, long long ld, int V, float inv_temp, int top_k, float top_p,
+sample_kernel(float* __restrict__ logits, long long ld, int V, float inv_temp, int top_k, float top_p,
               unsigned long long seed, int step_host, const int* __restrict__ step_dev, int greedy,
-              long long* __restrict__ tokens, float* __restrict__ logprobs) {
+              long long* __restrict__ tokens, float* __restrict__ logprobs, float softcap,
+              const int* __restrict__ forbidden, int n_forbidden) {
   pdl_trigger();
   pdl_wait();
   const int step = step_dev ? *step_dev : step_host;  // device-resident step keeps the launch graph-capturable
@@ -52,8 +57,21 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, float inv_t
   __shared__ float s_a[32];
   __shared__ int s_i[32];
   const int row = blockIdx.x;
-  const float* z = logits + (long long)row * ld;
+  float* z = logits + (long long)row * ld;
   const int tid = threadIdx.x, nt = blockDim.x;
+
+  if (softcap > 0.f) {
+    const float inv_cap = 1.f / softcap;
+    for (int i = tid; i < V; i += nt) z[i] = softcap * tanhf(z[i] * inv_cap);
+  }
+  if (n_forbidden > 0) {
+    __syncthreads();                                    // the capped values are in place before they are overwritten
+    for (int j = tid; j < n_forbidden; j += nt) {
+      const int t = forbidden[j];
+      if (t >= 0 && t < V) z[t] = -INFINITY;
+    }
+  }
+  if (softcap > 0.f || n_forbidden > 0) __syncthreads();
 
   float m = -INFINITY;
   for (int i = tid; i < V; i += nt) m = fmaxf(m, z[i] * inv_temp);
@@ -153,6 +171,20 @@ TB_API int tb_sample(const float* logits, long long ld, int B, int V, float temp
   if (B <= 0) return 0;
   const int greedy = temperature <= 0.f;
   const float inv_temp = greedy ? 1.f : 1.f / temperature;
+  return launch_pdl(sample_kernel, dim3(B), dim3(1024), 0, stream, const_cast<float*>(logits), ld, V, inv_temp, top_k, top_p,
+                    seed, step, step_dev, greedy, tokens, logprobs, 0.f, (const int*)nullptr, 0) == cudaSuccess ? 0 : -5;
+}
+
+// The same with the final logit soft-cap and forbidden token ids applied inside the kernel. The logits row is
+// MODIFIED in place (capped values, -inf at the forbidden ids): it is the caller's scratch.
+// softcap <= 0 disables the cap; forbidden: device int32 [n_forbidden] or null.
+TB_API int tb_sample_ex(float* logits, long long ld, int B, int V, float temperature, int top_k, float top_p,
+                        unsigned long long seed, int step, const int* step_dev, long long* tokens, float* logprobs,
+                        float softcap, const int* forbidden, int n_forbidden, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (n_forbidden < 0 || (n_forbidden > 0 && !forbidden)) return -2;
+  const int greedy = temperature <= 0.f;
+  const float inv_temp = greedy ? 1.f : 1.f / temperature;
   return launch_pdl(sample_kernel, dim3(B), dim3(1024), 0, stream, logits, ld, V, inv_temp, top_k, top_p, seed, step, step_dev,
-                    greedy, tokens, logprobs) == cudaSuccess ? 0 : -5;
+                    greedy, tokens, logprobs, softcap, forbidden, n_forbidden) == cudaSuccess ? 0 : -5;
 }

@@ -33,9 +33,17 @@ from .sampler import next_power_of_2, pad_prompts_left
 
 
 class PagePool:
-    """Device page pools for every layer plus the host-side free list."""
+    """Device page pools for every layer plus the host-side bookkeeping.
 
-    def __init__(self, cfg, num_pages: int, page_size: int, max_seqs: int, max_pages_per_seq: int, device, dtype):
+    Which request holds which pages is kept by `experimental.generate.kv_cache_manager.KVCacheManager`: pages are
+    reference counted, full pages are hashed by their token content (chained over the prefix), a released hashed
+    page stays resident until the pool needs it (least recently released first), and a new request re-points to every
+    cached page of its prompt's prefix (tunix/experimental/generate/single_type_kv_cache_manager.py:49-177). The
+    table row of a slot is what the kernels read."""
+
+    def __init__(self, cfg, num_pages: int, page_size: int, max_seqs: int, max_pages_per_seq: int, device, dtype,
+                 prefix_caching: bool = True):
+        from ..experimental.generate import kv_cache_manager as kvm
         self.page_size, self.num_pages, self.max_pages = page_size, num_pages, max_pages_per_seq
         row = cfg.num_kv_heads * cfg.head_dim
         # zero-initialised: rows of a page that were never written must hold finite values
@@ -43,33 +51,58 @@ class PagePool:
         self.v = [torch.zeros(num_pages, page_size, row, dtype=dtype, device=device) for _ in range(cfg.num_layers)]
         self.table_host = np.full((max_seqs, max_pages_per_seq), -1, np.int32)
         self.table = torch.full((max_seqs, max_pages_per_seq), -1, dtype=torch.int32, device=device)
-        self._free = list(range(num_pages - 1, -1, -1))
-        self._owned: dict = {}
+        self.Error = kvm.PagePoolError
+        self.mgr = kvm.KVCacheManager(kvm.PagePool(num_pages), page_size, enable_prefix_caching=prefix_caching)
+        self._rid: dict = {}            # slot -> request id inside the manager
+        self._seq = 0
+        self.hit_tokens = 0             # prompt tokens served from cached pages since construction
+        self.prompt_tokens = 0
 
     @property
     def free_pages(self) -> int:
-        return len(self._free)
+        return self.mgr.pool.num_free + len(self.mgr._lru)      # evictable cached pages count as free
 
-    def reserve(self, slot: int, n_tokens: int) -> None:
-        need = (n_tokens + self.page_size - 1) // self.page_size
-        if need > self.max_pages:
-            raise ValueError(f"sequence of {n_tokens} tokens needs {need} pages, table holds {self.max_pages}")
-        have = self._owned.setdefault(slot, [])
-        while len(have) < need:
-            if not self._free:
-                raise RuntimeError("out of KV pages")
-            p = self._free.pop()
-            self.table_host[slot, len(have)] = p
-            have.append(p)
+    def _row(self, slot: int) -> None:
+        self.table_host[slot] = self.mgr.page_table(self._rid[slot], self.max_pages)
+
+    def open(self, slot: int, token_ids, n_new: int) -> int:
+        """Pages for a new request in `slot`: its prompt plus `n_new` tokens. Returns how many leading prompt tokens
+        already sit in cached pages. Raises `self.Error` when the pool cannot serve it (nothing is taken then)."""
+        n = len(token_ids) + n_new
+        if (n + self.page_size - 1) // self.page_size > self.max_pages:
+            raise ValueError(f"sequence of {n} tokens does not fit the page table ({self.max_pages} pages)")
+        self._seq += 1
+        rid = f"{slot}#{self._seq}"
+        _, cached = self.mgr.allocate_for_request(rid, token_ids, n_new)
+        self._rid[slot] = rid
+        self.mgr.cache_full_pages(rid, token_ids, len(token_ids))   # later requests may share these pages
+        self._row(slot)
+        self.hit_tokens += cached
+        self.prompt_tokens += len(token_ids)
+        return cached
+
+    def grow(self, slot: int, total_tokens: int) -> None:
+        """Make sure `slot` owns pages for `total_tokens` tokens. Raises `self.Error` when the pool is exhausted."""
+        total_tokens = min(total_tokens, self.max_pages * self.page_size)
+        before = len(self.mgr._req[self._rid[slot]])
+        self.mgr.append_pages(self._rid[slot], total_tokens)
+        if len(self.mgr._req[self._rid[slot]]) != before:
+            self._row(slot)
+
+    def publish(self, slot: int, token_ids) -> None:
+        """Hash the pages that `token_ids` (prompt + generated) filled, so that a later turn of the same conversation
+        finds them."""
+        if slot in self._rid:
+            self.mgr.cache_full_pages(self._rid[slot], token_ids, len(token_ids))
+
+    def pages_of(self, slot: int) -> list:
+        return [p.page_id for p in self.mgr._req[self._rid[slot]] if p is not None]
 
     def release(self, slot: int) -> None:
-        pages = self._owned.pop(slot, [])
-        if not pages:
+        rid = self._rid.pop(slot, None)
+        if rid is None:
             return
-        for p in pages:
-            if p in self._free:
-                raise RuntimeError(f"double free of page {p}")
-            self._free.append(p)
+        self.mgr.free_request(rid)
         self.table_host[slot, :] = -1
 
     def sync_table(self) -> None:
@@ -79,7 +112,8 @@ class PagePool:
 class PagedEngine(BaseSampler):
     def __init__(self, transformer, tokenizer, cache_config: CacheConfig, page_size: int = 64,
                  max_running_requests: int = 64, use_cuda_graph: bool = True, check_every: int = 16,
-                 use_pdl: bool = False, pack_weights: bool = True):
+                 use_pdl: bool = False, pack_weights: bool = True, num_pages: Optional[int] = None,
+                 prefix_caching: bool = True, prefill_chunk: int = 0):
         self._model = transformer
         self.tokenizer = tokenizer
         self.cfg = transformer.config
@@ -88,8 +122,8 @@ class PagedEngine(BaseSampler):
         self.dtype = next(transformer.parameters()).dtype
         if self.device.type != "cuda" or self.dtype != torch.bfloat16:
             raise ValueError("PagedEngine runs bf16 models on CUDA; use Sampler elsewhere")
-        if self.cfg.is_moe:
-            raise NotImplementedError("MoE decode goes through Sampler")
+        if self.cfg.is_moe and getattr(transformer.layers[0].mlp, "ep", None) is not None:
+            raise NotImplementedError("expert-parallel MoE decode goes through Sampler")
         if self.cfg.family == "gemma4":
             raise NotImplementedError("Gemma-4 decode (per-layer inputs, shared KV, 512-wide heads) goes through Sampler")
         self.page_size = page_size
@@ -106,6 +140,14 @@ class PagedEngine(BaseSampler):
         self._packed = None
         self.check_every = check_every
         self.max_pages_per_seq = (self.cache_size + page_size - 1) // page_size
+        # pages in the pool: by default enough for every slot at full length (nothing ever queues for memory); a
+        # smaller pool makes requests wait for pages and, when running sequences outgrow it, sends the youngest one
+        # back to the queue
+        self.num_pages = num_pages
+        self.prefix_caching = prefix_caching
+        self.prefill_chunk = prefill_chunk      # > 0: prompts are prefilled in pieces of at most this many tokens
+        self.preemptions = 0
+        self.forbidden: Optional[torch.Tensor] = None
         self.pool: Optional[PagePool] = None
         self._graph = None
         self._graph_key = None
@@ -138,9 +180,9 @@ class PagedEngine(BaseSampler):
 
     def _ensure_pool(self, n_seqs: int) -> None:
         if self.pool is None:
-            pages = self.max_running * self.max_pages_per_seq
+            pages = self.num_pages or self.max_running * self.max_pages_per_seq
             self.pool = PagePool(self.cfg, pages, self.page_size, self.max_running, self.max_pages_per_seq, self.device,
-                                 self.dtype)
+                                 self.dtype, self.prefix_caching)
 
     # ---------------------------------------------------------------- the model
     @staticmethod
@@ -182,7 +224,8 @@ class PagedEngine(BaseSampler):
         for layer in self._model.layers:
             at = layer.self_attn
             self._wqkv.append(self._fused_weight([at.q_proj, at.k_proj, at.v_proj]))
-            self._wgu.append(self._fused_weight([layer.mlp.gate_proj, layer.mlp.up_proj]))
+            # a mixture-of-experts block keeps its stacked expert weights and runs through the grouped GEMM
+            self._wgu.append(None if self.cfg.is_moe else self._fused_weight([layer.mlp.gate_proj, layer.mlp.up_proj]))
 
     @staticmethod
     def _plain(mod) -> bool:
@@ -198,8 +241,10 @@ class PagedEngine(BaseSampler):
         srcs = []
         for i, layer in enumerate(self._model.layers):
             at, mlp = layer.self_attn, layer.mlp
+            dense = not self.cfg.is_moe
             srcs.append({"qkv": self._wqkv[i], "o": at.o_proj.weight.data if self._plain(at.o_proj) else None,
-                         "gu": self._wgu[i], "down": mlp.down_proj.weight.data if self._plain(mlp.down_proj) else None})
+                         "gu": self._wgu[i],
+                         "down": mlp.down_proj.weight.data if dense and self._plain(mlp.down_proj) else None})
         srcs.append({"head": self._model.head_weight()})
         for src in srcs:
             for name, w in src.items():
@@ -257,6 +302,9 @@ class PagedEngine(BaseSampler):
     def _mlp(self, layer, i, h, residual=None, decode=False):
         wgu = self._wgu[i]
         if wgu is None:
+            if self.cfg.is_moe and h.dim() == 2:      # decode rows: the expert block wants [batch, time, D]
+                r3 = residual[:, None] if residual is not None else None
+                return layer.mlp(h[:, None], residual=r3)[:, 0]
             return layer.mlp(h, residual=residual)
         Fd = wgu.shape[0] // 2
         h2 = h.reshape(-1, h.shape[-1])
@@ -278,22 +326,39 @@ class PagedEngine(BaseSampler):
         x = attn_out          # o_proj already added the residual
         return self._mlp(layer, i, layer.post_attention_layernorm(x), residual=x, decode=decode)
 
-    def _prefill(self, toks, positions, seg, slots):
-        """toks [B,P] left padded. Writes K/V pages, returns hidden state of the last position [B, D]."""
+    def _prefill(self, toks, positions, seg, slots, prev_len=None, write_from=None):
+        """toks [B,P] left padded: the prompt tokens this call computes. `prev_len` [B] (or None): tokens of each row
+        that already sit in its pages (a prefix-cache hit, or the earlier chunks of a long prompt): their K/V are
+        gathered from the pages and attended to. K/V of this call's tokens are written at positions >= write_from
+        (a row never rewrites pages it shares). Returns the hidden state of the last position [B, D]."""
         cfg, pool = self.cfg, self.pool
         B, P = toks.shape
+        KH, H = cfg.num_kv_heads, cfg.head_dim
         x = F.embedding(toks, self._model.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         pos_flat = positions.reshape(-1).contiguous()
-        wpos = torch.where(seg.reshape(-1) > 0, pos_flat, torch.full_like(pos_flat, -1))
+        valid = seg.reshape(-1) > 0
+        if write_from is not None:
+            valid = valid & (pos_flat >= write_from.repeat_interleave(P))
+        wpos = torch.where(valid, pos_flat, torch.full_like(pos_flat, -1))
         seq_ids = slots.repeat_interleave(P)
+        Tc, pidx, seg_k = 0, None, seg
+        if prev_len is not None:
+            Tc = (int(prev_len.max()) + pool.page_size - 1) // pool.page_size * pool.page_size
+        if Tc > 0:
+            pidx = pool.table[slots.long(), :Tc // pool.page_size].clamp(min=0).long()          # [B, pages]
+            seg_c = (torch.arange(Tc, device=toks.device)[None] < prev_len[:, None]).to(torch.int32)
+            seg_k = torch.cat([seg_c, seg], 1).contiguous()
         for i, layer in enumerate(self._model.layers):
             h = layer.input_layernorm(x)
             q, k, v = self._attn_in(layer, h.view(B * P, -1), pos_flat, i)
             K.kv_write(k.view(B * P, -1), v, seq_ids, wpos, pool.table, pool.page_size, pool.k[i], pool.v[i])
             at = layer.self_attn
-            o = F.attention(q.view(B, P, cfg.num_heads, cfg.head_dim), k.view(B, P, cfg.num_kv_heads, cfg.head_dim),
-                            v.view(B, P, cfg.num_kv_heads, cfg.head_dim), scale=at.scale, causal=True, window=at.window,
-                            softcap=cfg.attn_logit_softcap, seg_q=seg, seg_k=seg)
+            k4, v4 = k.view(B, P, KH, H), v.view(B, P, KH, H)
+            if Tc > 0:
+                k4 = torch.cat([pool.k[i][pidx].view(B, Tc, KH, H), k4], 1)
+                v4 = torch.cat([pool.v[i][pidx].view(B, Tc, KH, H), v4], 1)
+            o = F.attention(q.view(B, P, cfg.num_heads, H), k4, v4, scale=at.scale, causal=True, window=at.window,
+                            softcap=cfg.attn_logit_softcap, q_off=Tc if Tc > 0 else None, seg_q=seg, seg_k=seg_k)
             o = o.reshape(B, P, -1)
             a = at.o_proj(o, residual=None if cfg.post_norms else x)
             x = self._mlp_and_norms(layer, i, x, a)
@@ -340,19 +405,20 @@ class PagedEngine(BaseSampler):
             logits = K.gemm_packed(hlast, ph, out=out, out_dtype=torch.float32)
         else:
             logits = K.gemm(hlast, self._model.head_weight(), out=out, out_dtype=torch.float32)
-        if self.cfg.final_logit_softcap:
-            c = self.cfg.final_logit_softcap
-            logits.copy_(c * torch.tanh(logits / c))
-        return logits
+        return logits          # raw: the final soft-cap is applied by the sampling kernel (`_sample`)
+
+    def _sample(self, logits, st, out_tokens, out_logprobs) -> None:
+        p = st["params"]
+        S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
+                 out_tokens=out_tokens, out_logprobs=out_logprobs, step_tensor=st["step"],
+                 softcap=float(self.cfg.final_logit_softcap or 0.0), forbidden=self.forbidden)
 
     def _sample_into(self, hlast, st) -> None:
         """Sample one token per slot of the running batch and advance the slots that are still generating. A
         finished (or empty) slot idles: position -1 and length 0 make the next step write no K/V and attend to
         nothing, and its output goes to the spare last column."""
         logits = self._logits(hlast, out=st["logits"])
-        p = st["params"]
-        S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
-                 out_tokens=st["next"], out_logprobs=st["next_lp"], step_tensor=st["step"])
+        self._sample(logits, st, st["next"], st["next_lp"])
         done = st["done"]
         tok = torch.where(done, st["pad"], st["next"])
         idx = torch.where(done, st["dump_col"], st["out_pos"])[:, None]
@@ -374,8 +440,10 @@ class PagedEngine(BaseSampler):
                  eos_tokens: Optional[Sequence[int]] = None, forbidden_tokens=None, temperature: float = 0.0,
                  top_p: Optional[float] = None, top_k: Optional[int] = None, beam_size=None, seed: Optional[int] = None,
                  pad_output: bool = False, *, prompt_token_ids=None) -> SamplerOutput:
-        if forbidden_tokens or beam_size or return_logits or echo:
-            raise NotImplementedError("forbidden tokens, beam search, logits and echo are served by Sampler")
+        if beam_size or return_logits or echo:
+            raise NotImplementedError("beam search, logits and echo are served by Sampler")
+        self.forbidden = torch.as_tensor(sorted({int(t) for t in forbidden_tokens}), dtype=torch.int32, device=self.device) \
+            if forbidden_tokens else None
         if (input_strings is None) == (prompt_token_ids is None):
             raise ValueError("give exactly one of input_strings / prompt_token_ids")
         if isinstance(input_strings, str):
@@ -467,6 +535,9 @@ class PagedEngine(BaseSampler):
                 reqs = [waiting.pop() for _ in range(min(n_free, len(waiting)))]
                 return [(r, toks_np[r], int(lens_np[r]), max_steps) for r in reqs]
 
+            def give_back(self, items):
+                waiting.extend(r for r, *_ in reversed(items))      # back to the head of the queue, order kept
+
             def more_waiting(self):
                 return bool(waiting)
 
@@ -487,9 +558,17 @@ class PagedEngine(BaseSampler):
         state. The decode step always runs over all slots (one captured graph); idle slots cost a row of the
         GEMMs and no attention work.
 
+        Pages are handed out as sequences grow: a request is admitted with pages for its prompt and the steps up to
+        the next check point, and every check point tops the running slots up. A request that finds no room stays in
+        the queue; when running sequences outgrow the pool, the one with the least progress goes back to the head of
+        the queue (its pages are released, it is generated again from its prompt later) instead of failing the call.
+        Prompt pages are shared through the prefix cache: a request whose prompt starts with tokens that already sit
+        in cached pages (the other generations of its GRPO group, an earlier turn of its conversation) prefills only
+        what is left.
+
         `source` hands out requests and takes results: take(n_free) -> [(id, padded prompt row, prompt length,
-        token limit)], more_waiting(), deliver(id, tokens, logprobs), and idle(), called when no slot is busy and
-        take() returned nothing: it may block for new work and returns False to end the loop."""
+        token limit)], give_back(items), more_waiting(), deliver(id, tokens, logprobs), and idle(), called when no
+        slot is busy and take() returned nothing: it may block for new work and returns False to end the loop."""
         dev = self.device
         self._ensure_pool(B)
         pool = self.pool
@@ -497,9 +576,21 @@ class PagedEngine(BaseSampler):
             pool.release(s)
         i64 = dict(dtype=torch.int64, device=dev)
         slot_req = [None] * B
+        slot_item = [None] * B                      # the request as take() gave it (for give_back)
         slot_cnt = [0] * B                          # tokens a slot's request has produced at most (host-side bound)
         slot_lim = [0] * B
+        slot_plen = [0] * B
         graph = None
+
+        def prompt_ids(item):
+            _rid, row, ln, _lim = item
+            return [int(t) for t in row[len(row) - ln:]]
+
+        def idle_slot(s):
+            st["done"][s] = True
+            st["positions"][s] = -1
+            st["seq_lens"][s] = 0
+
         while True:
             # ---- check point: harvest finished slots, admit waiting requests (repeats while an admitted request
             # finishes with its very first token)
@@ -514,21 +605,47 @@ class PagedEngine(BaseSampler):
                     for j, s in enumerate(fin):
                         c = int(cnt_h[j])
                         source.deliver(slot_req[s], toks_h[j, :c], lps_h[j, :c])
-                        slot_req[s] = None
+                        # the K/V of everything but the last sampled token is in the pages: a follow-up turn finds it
+                        pool.publish(s, prompt_ids(slot_item[s]) + [int(t) for t in toks_h[j, :max(c - 1, 0)]])
+                        slot_req[s] = slot_item[s] = None
                         pool.release(s)
                 free = [s for s in range(B) if slot_req[s] is None]
                 new = source.take(len(free)) if free else []
                 if not new:
                     break
-                take = free[:len(new)]
-                for s, (rid, _row, ln, lim) in zip(take, new):
-                    slot_req[s] = rid
-                    slot_cnt[s] = 1
-                    slot_lim[s] = max(1, min(int(lim), max_steps))
-                    pool.reserve(s, ln + slot_lim[s] + 1)
+                admitted = []                        # (slot, item, cached tokens)
+                for n_i, item in enumerate(new):
+                    s = free[len(admitted)]
+                    lim = max(1, min(int(item[3]), max_steps))
+                    try:
+                        cached = pool.open(s, prompt_ids(item), min(lim, self.check_every) + 1)
+                    except pool.Error:
+                        source.give_back(new[n_i:])   # no room now: they wait for pages
+                        break
+                    slot_req[s], slot_item[s] = item[0], item
+                    slot_cnt[s], slot_lim[s], slot_plen[s] = 1, lim, item[2]
+                    admitted.append((s, item, cached))
+                if not admitted:
+                    if all(r is None for r in slot_req):
+                        raise RuntimeError(f"the page pool ({pool.num_pages} pages of {pool.page_size} tokens) cannot hold "
+                                           f"a single request of {new[0][2]} prompt tokens")
+                    break
                 pool.sync_table()
-                self._admit(st, take, np.stack([row for _, row, _, _ in new]), np.asarray([ln for _, _, ln, _ in new]),
-                            pad_id, [slot_lim[s] for s in take])
+                # requests whose cached pages are written by another request of this round wait for that prefill
+                produced: dict = {}
+                waves: dict = {}
+                for s, item, cached in admitted:
+                    pages = pool.pages_of(s)
+                    n_cached = cached // pool.page_size
+                    wave = 1 + max((produced.get(pg, -1) for pg in pages[:n_cached]), default=-1)
+                    for pg in pages[n_cached:item[2] // pool.page_size]:
+                        produced.setdefault(pg, wave)
+                    waves.setdefault(wave, []).append((s, item, cached))
+                for wave in sorted(waves):
+                    grp = waves[wave]
+                    self._admit(st, [s for s, _, _ in grp], np.stack([it[1] for _, it, _ in grp]),
+                                np.asarray([it[2] for _, it, _ in grp]), pad_id, [slot_lim[s] for s, _, _ in grp],
+                                [c for _, _, c in grp])
             if all(r is None for r in slot_req):
                 if source.idle():
                     continue
@@ -537,8 +654,31 @@ class PagedEngine(BaseSampler):
             # to the next look at the done flags
             if graph is None and self.use_graph and max_steps > 2:
                 graph = self._capture(st)
-            left = [slot_lim[s] - slot_cnt[s] for s in range(B) if slot_req[s] is not None]
+            running = [s for s in range(B) if slot_req[s] is not None]
+            left = [slot_lim[s] - slot_cnt[s] for s in running]
             n_steps = max(1, min(self.check_every, min(left) if source.more_waiting() else max(left)))
+            # pages for the steps ahead; when the pool runs dry the youngest sequence makes room
+            changed = False
+            while True:
+                try:
+                    for s in running:
+                        before = len(pool.pages_of(s))
+                        pool.grow(s, slot_plen[s] + min(slot_cnt[s] + n_steps, slot_lim[s]) + 1)
+                        changed |= len(pool.pages_of(s)) != before
+                    break
+                except pool.Error:
+                    if len(running) <= 1:
+                        raise RuntimeError("the page pool cannot hold one sequence at its full length") from None
+                    victim = min(running, key=lambda s: (slot_cnt[s], -s))
+                    source.give_back([slot_item[victim]])
+                    idle_slot(victim)
+                    pool.release(victim)
+                    slot_req[victim] = slot_item[victim] = None
+                    running.remove(victim)
+                    self.preemptions += 1
+                    changed = True
+            if changed:
+                pool.sync_table()
             for _ in range(n_steps):
                 if graph is not None:
                     graph.replay()
@@ -547,23 +687,43 @@ class PagedEngine(BaseSampler):
             for s in range(B):
                 slot_cnt[s] += n_steps
 
-    def _admit(self, st, slots_list, toks_np, lens_np, pad_id, limits) -> None:
-        """Prefill the given prompts into their slots, sample each one's first token and set the slot state."""
+    def _admit(self, st, slots_list, toks_np, lens_np, pad_id, limits, cached=None) -> None:
+        """Prefill the given prompts into their slots, sample each one's first token and set the slot state.
+        `cached[i]` leading tokens of prompt i already sit in (shared) pages and are not computed again, except that
+        the last prompt token always is: its hidden state gives the first sampled token. Long remainders are
+        prefilled in pieces of `prefill_chunk` tokens, each attending to the pages written before it."""
         dev = self.device
-        P = toks_np.shape[1]
-        toks = torch.from_numpy(np.ascontiguousarray(toks_np)).to(dev)
-        lens = torch.from_numpy(np.ascontiguousarray(lens_np)).to(dev)
-        seg = (torch.arange(P, device=dev)[None] >= (P - lens)[:, None]).to(torch.int32)
-        positions = torch.clamp(torch.cumsum(seg, -1) - 1, min=0).to(torch.int32)
-        slots = torch.as_tensor(slots_list, dtype=torch.int32, device=dev)
-        hlast = self._prefill(toks, positions, seg, slots)
-        logits = self._logits(hlast)
-        p = st["params"]
         g = len(slots_list)
+        ps = self.pool.page_size
+        cached = [0] * g if cached is None else list(cached)
+        lens_l = [int(x) for x in lens_np]
+        use = [min(c, (ln - 1) // ps * ps) for c, ln in zip(cached, lens_l)]       # tokens taken from the pages
+        newlen = [ln - u for ln, u in zip(lens_l, use)]
+        Pn = max(newlen)
+        P = toks_np.shape[1]
+        new_np = np.full((g, Pn), pad_id, np.int64)
+        for i in range(g):
+            new_np[i, Pn - newlen[i]:] = toks_np[i, P - newlen[i]:]
+        toks = torch.from_numpy(new_np).to(dev)
+        nl = torch.as_tensor(newlen, device=dev)
+        prev = torch.as_tensor(use, dtype=torch.int32, device=dev)
+        wfrom = torch.as_tensor(cached, dtype=torch.int32, device=dev)
+        lens = torch.as_tensor(lens_l, device=dev)
+        seg = (torch.arange(Pn, device=dev)[None] >= (Pn - nl)[:, None]).to(torch.int32)
+        positions = (torch.clamp(torch.cumsum(seg, -1) - 1, min=0) + prev[:, None]).to(torch.int32)
+        slots = torch.as_tensor(slots_list, dtype=torch.int32, device=dev)
+        chunk = self.prefill_chunk if self.prefill_chunk and self.prefill_chunk > 0 else Pn
+        hlast = None
+        for c0 in range(0, Pn, chunk):
+            c1 = min(Pn, c0 + chunk)
+            before = prev + seg[:, :c0].sum(-1).to(torch.int32)                     # tokens of each row already in pages
+            use_prev = before if (c0 > 0 or any(use)) else None
+            hlast = self._prefill(toks[:, c0:c1].contiguous(), positions[:, c0:c1].contiguous(),
+                                  seg[:, c0:c1].contiguous(), slots, use_prev, wfrom)
+        logits = self._logits(hlast)
         nxt = torch.zeros(g, dtype=torch.int64, device=dev)
         nlp = torch.zeros(g, device=dev)
-        S.sample(logits, p["temperature"], p["top_p"], p["top_k"], p["seed"], 0, want_logprob=True,
-                 out_tokens=nxt, out_logprobs=nlp, step_tensor=st["step"])
+        self._sample(logits, st, nxt, nlp)
         ix = slots.to(torch.int64)
         lim = torch.as_tensor(limits, dtype=torch.int64, device=dev)
         st["out_tokens"][ix] = pad_id
@@ -689,6 +849,12 @@ class EngineServer:
                 out.append((rid, row, len(ids), lim))
             self.admitted += len(out)
         return out
+
+    def give_back(self, items):
+        with self._cv:
+            for rid, row, ln, lim in reversed(items):
+                self._queue.appendleft((rid, [int(t) for t in row[len(row) - ln:]], lim))
+            self.admitted -= len(items)
 
     def more_waiting(self):
         with self._cv:

@@ -25,7 +25,8 @@ def route_positions(idx: torch.Tensor, num_experts: int):
     by (token, slot), so the layout is deterministic. max_rows bounds seg_off[E] without reading it."""
     T, k = idx.shape
     flat = idx.reshape(-1).long()
-    counts = torch.bincount(flat, minlength=num_experts)
+    # scatter-add instead of bincount: no read-back of the largest id, so the step stays capturable in a CUDA graph
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=idx.device).scatter_add_(0, flat, torch.ones_like(flat))
     padded = (counts + 127) // 128 * 128
     seg_off = torch.zeros(num_experts + 1, dtype=torch.int64, device=idx.device)
     seg_off[1:] = torch.cumsum(padded, 0)

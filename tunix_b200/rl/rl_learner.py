@@ -101,26 +101,83 @@ class RLLearner(abc.ABC):
                 out[k] = v
         return out
 
+    @staticmethod
+    def _item_size(batch: dict) -> int:
+        for key in ("prompts", "prompt_token_ids"):
+            if batch.get(key) is not None:
+                return len(batch[key])
+        return len(next(iter(batch.values())))
+
+    @staticmethod
+    def _merge_items(items: list) -> dict:
+        """Several prompt batches as one: lists are concatenated, arrays / tensors stacked along dim 0."""
+        if len(items) == 1:
+            return items[0]
+        out = {}
+        for k in items[0]:
+            vals = [it[k] for it in items]
+            v0 = vals[0]
+            if isinstance(v0, (list, tuple)):
+                out[k] = [x for v in vals for x in v]
+            elif isinstance(v0, np.ndarray):
+                out[k] = np.concatenate(vals, 0)
+            elif isinstance(v0, torch.Tensor):
+                out[k] = torch.cat(vals, 0)
+            else:
+                out[k] = v0
+        return out
+
+    def _service_target(self) -> int:
+        """Prompts to collect before one generate-and-score pass: the least common multiple of the rollout and the
+        log-prob micro-batch sizes, so that neither service runs a ragged last micro-batch
+        (tunix/rl/rl_learner.py:278-330)."""
+        a, b = self.tcfg.rollout_micro_batch_size or 1, self.tcfg.compute_logps_micro_batch_size or 1
+        return math.lcm(int(a), int(b))
+
     def _prepare_data(self, iterator: Iterator, data_queue: SimpleDataQueue, mode: Mode, num_batches: int) -> None:
-        """Producer: consume `num_batches` prompt batches, enqueue train micro-batches, then a None sentinel."""
+        """Producer: consume `num_batches` prompt batches, enqueue train micro-batches, then a None sentinel.
+
+        Batches smaller than the service target (a dataset that yields micro-batches) are merged until they reach
+        it, generated and scored in one pass, and split again into train micro-batches; a remainder at the end of
+        the step is processed as it is."""
         try:
             G, mu = self._num_generations(), self._num_iterations()
             mb = self.tcfg.train_micro_batch_size
+            target = self._service_target()
             produced: list[common.TrainExample] = []
-            for _ in range(num_batches):
-                try:
-                    batch = next(iterator)
-                except StopIteration:
-                    break
-                batch = self._repeat(batch, G)
+            held: list = []
+            held_n = 0
+
+            def flush():
+                nonlocal held, held_n
+                if not held:
+                    return
+                batch = self._repeat(self._merge_items(held), G)
+                held, held_n = [], 0
                 with torch.no_grad():
                     ex = self._generate_and_compute_advantage(batch, mode)
                 n = ex.completion_ids.shape[0]
                 step_mb = (mb * G) if mb else n
                 for sl in rl_utils.chunk_slices(n, step_mb):
-                    piece = rl_utils.slice_example(ex, sl)
-                    produced.append(piece)
-                    data_queue.put(piece)
+                    produced.append(rl_utils.slice_example(ex, sl))
+
+            for _ in range(num_batches):
+                try:
+                    batch = next(iterator)
+                except StopIteration:
+                    break
+                held.append(batch)
+                held_n += self._item_size(batch)
+                if held_n >= target:
+                    flush()
+            flush()
+            # one pass over the step's micro-batches updates every `gradient_accumulation_steps` of them and, whatever
+            # that count is, at its last one: a global step never ends with gradients left unapplied
+            acc = max(int(self.grad_acc_steps or 1), 1)
+            for k, piece in enumerate(produced):
+                if piece.is_update_step is None:
+                    piece.is_update_step = ((k + 1) % acc == 0) or k == len(produced) - 1
+                data_queue.put(piece)
             if mode == Mode.TRAIN:
                 for it in range(1, mu):
                     order = list(range(len(produced)))
@@ -160,8 +217,17 @@ class RLLearner(abc.ABC):
         global batch of prompts (mini_batch_size prompts)."""
         it = iter(train_ds)
         max_steps = self.tcfg.max_steps
+        # a dataset may yield whole global batches or micro-batches of them: a global step takes as many items as
+        # make up `mini_batch_size` prompts
+        first = next(it, None)
+        if first is None:
+            return
+        import itertools
+        it = itertools.chain([first], it)
+        mini = self.tcfg.mini_batch_size
+        self._items_per_step = max(1, int(mini) // max(self._item_size(first), 1)) if mini else 1
         # resume: skip consumed prompt batches
-        for _ in range(self.rl_cluster.global_steps):
+        for _ in range(self.rl_cluster.global_steps * self._items_per_step):
             try:
                 next(it)
             except StopIteration:
@@ -189,7 +255,7 @@ class RLLearner(abc.ABC):
                         self._iter_steps += 1
                         yield ex
                 with self._step_group() as step_span:
-                    fut = executor.submit(self._prepare_data, it, q, Mode.TRAIN, 1)
+                    fut = executor.submit(self._prepare_data, it, q, Mode.TRAIN, self._items_per_step)
                     self._train_on(counted())
                     fut.result()
                     if not got_any:
