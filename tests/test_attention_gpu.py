@@ -80,8 +80,13 @@ def _close(a, b, what=""):
     assert not bad.any(), (what, int(bad.sum()), (a - b).abs().max().item(), tol)
 
 
+@pytest.mark.parametrize("two_tile", [False, True])
 @pytest.mark.parametrize("case", CASES)
-def test_attention_forward(case):
+def test_attention_forward(case, two_tile, monkeypatch):
+    """Both forward kernels: one 128-row query tile per CTA (the default) and two tiles per CTA (opt-in)."""
+    if two_tile and (case[5] > 128 or case[1] <= 128):
+        pytest.skip("the two-tile kernel serves head dims up to 128 and more than 128 query rows")
+    monkeypatch.setenv("TUNIX_B200_ATTN_TWO_TILE", "1" if two_tile else "0")
     from tunix_b200 import _lib
     from tunix_b200.ops import kernels as k_
     B, Tq, Tk, N, KH, H, causal, window, softcap, segs = case

@@ -64,3 +64,48 @@ def test_automodel_random():
                                             num_layers=1, vocab_size=128, embed_dim=64, hidden_dim=128, num_heads=2,
                                             head_dim=32, num_kv_heads=1)
     assert path is None and model.config.family == "llama3" and len(model.layers) == 1
+
+
+def test_reads_a_checkpoint_that_orbax_wrote_in_its_ocdbt_layout():
+    """tests/data/orbax_ocdbt_checkpoint is the checkpoint fixture of the reference's own trainer tests (two dense
+    layers w1 [2,4] / w2 [4,2], fp32, zstd-compressed zarr chunks inside an OCDBT store)."""
+    import os
+    import numpy as np
+    import torch
+    from tunix_b200.sft import ocdbt
+    from tunix_b200.sft.checkpoint_manager import CheckpointManager, _load_item
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "orbax_ocdbt_checkpoint")
+    store = ocdbt.OcdbtStore(os.path.join(root, "model_params")).items()
+    assert len(store) == 17 and "w1.kernel.value/.zarray" in store and "w2.kernel.value/1.0" in store
+    tree = ocdbt.load_tree(os.path.join(root, "model_params"))
+    assert sorted(tree) == [("w1", "bias", "value"), ("w1", "kernel", "value"), ("w2", "bias", "value"), ("w2", "kernel", "value")]
+    k1 = tree[("w1", "kernel", "value")]
+    assert k1.shape == (2, 4) and k1.dtype == np.float32 and abs(float(k1[0, 0]) - 0.7567299) < 1e-6
+    assert abs(float(k1[1, 3]) - (-0.7722851)) < 1e-6                       # last chunk (1.1) landed in its corner
+    assert tree[("w2", "kernel", "value")].shape == (4, 2) and float(np.abs(tree[("w1", "bias", "value")]).sum()) == 0.0
+    item = _load_item(os.path.join(root, "model_params"))
+    assert torch.equal(item["w1"]["kernel"]["value"], torch.from_numpy(k1))
+    assert CheckpointManager(os.path.dirname(root)).all_steps() == []       # the directory name is not a step number
+
+    # restore into a module whose parameter names match the tree ('<layer>.<kernel|bias>.value')
+    class Leaf(torch.nn.Module):
+        def __init__(self, *shape):
+            super().__init__()
+            self.value = torch.nn.Parameter(torch.zeros(*shape))
+
+    class Layer(torch.nn.Module):
+        def __init__(self, i, o):
+            super().__init__()
+            self.kernel, self.bias = Leaf(i, o), Leaf(o)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1, self.w2 = Layer(2, 4), Layer(4, 2)
+    import shutil, tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        shutil.copytree(root, os.path.join(tmp, "1"))
+        net = Net()
+        step, meta = CheckpointManager(tmp).maybe_restore(net)
+        assert step == 1 and meta == {}
+        assert torch.equal(net.w2.kernel.value.detach(), torch.from_numpy(tree[("w2", "kernel", "value")]))

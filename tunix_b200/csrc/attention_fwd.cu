@@ -729,11 +729,14 @@ int launch_fwd2(const void* q, const void* k, const void* v, const AttnArgs& a, 
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-// The two-tile kernel serves head dims up to 128 once there are more than 128 query rows; TUNIX_B200_ATTN_ONE_TILE=1
-// keeps every call on the one-tile kernel (A/B measurements).
+// The two-tile kernel is opt-in (TUNIX_B200_ATTN_TWO_TILE=1, read at every call): measured on B200 at B = 8, T = 2048,
+// 32 / 8 heads of 128 it reaches 580 TFLOP/s against 630 for two co-resident one-tile CTAs per SM, so the one-tile
+// kernel stays the default. What was ruled out on the way: the single K buffer (the ring made no difference), the
+// number of softmax warps (one or two threads per row: 568 vs 581), descriptor arithmetic in the issuing thread
+// (precomputed: 578).
 bool use_two_tiles(int H, int Tq) {
-  static const bool off = getenv("TUNIX_B200_ATTN_ONE_TILE") != nullptr;
-  return !off && H <= 128 && Tq > 128;
+  const char* on = getenv("TUNIX_B200_ATTN_TWO_TILE");
+  return on != nullptr && on[0] == '1' && H <= 128 && Tq > 128;
 }
 
 }  // namespace

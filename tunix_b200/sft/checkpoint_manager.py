@@ -15,6 +15,11 @@ Saves run on a background thread after a device->host copy (async checkpointing)
 fixed step interval or "at least N seconds since the last save", keep the latest `max_to_keep`.
 `maybe_restore` returns `(step, custom_metadata)`.
 
+Reading: `_load_item` also reads item directories that Orbax wrote in its OCDBT layout (`sft/ocdbt.py`; checked
+against a checkpoint written by the reference's own test suite). Writing stays plain zarr-v2 directories per array,
+the non-OCDBT form of the same layout; whether Orbax accepts them has not been checked here (Orbax is not
+installable offline).
+
 Several ranks: the decision to save is taken on rank 0 and broadcast (a wall-clock policy would otherwise let
 ranks disagree and hang the collectives below); every rank then takes part in gathering sharded state (a
 sharded optimizer's `state_dict()`, parameters that carry `shard_spec = (dim, index, count)` from the tensor /
@@ -144,6 +149,16 @@ def _save_item(path: str, tree: dict) -> None:
 
 
 def _load_item(path: str) -> dict:
+    if os.path.exists(os.path.join(path, "manifest.ocdbt")):
+        # written by Orbax itself in its OCDBT layout: arrays packed into a B+tree key-value store (`sft/ocdbt.py`)
+        from . import ocdbt
+        out: dict = {}
+        for key, arr in ocdbt.load_tree(path).items():
+            d = out
+            for k in key[:-1]:
+                d = d.setdefault(k, {})
+            d[key[-1]] = torch.from_numpy(np.ascontiguousarray(arr))
+        return out
     with open(os.path.join(path, "_METADATA")) as f:
         md = json.load(f)["tree_metadata"]
     out: dict = {}
