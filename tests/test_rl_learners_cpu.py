@@ -139,3 +139,33 @@ def test_micro_batch_items_are_merged_to_the_service_target_and_every_pass_ends_
     assert cl.global_steps == 2 and calls == [8, 8]             # 2 items x 2 prompts x G per pass
     assert flags == [False, False, False, True] * 2             # 4 micro-batches of 1 prompt x G, accumulation 4
     assert cl.actor_trainer.train_steps == 2
+
+
+def test_grpo_on_a_moe_actor_replays_the_samplers_routing():
+    """`return_routed_experts` on the rollout config: the dense sampler records every token's experts, the learner lays
+    them out over the padded stream and the update's forward pass is routed exactly as the sampler was."""
+    cfg = _cfg().replace(num_experts=4, num_experts_per_tok=2, moe_hidden_dim=32)
+    actor = create_model(cfg, seed=0)
+    ref = create_model(cfg, seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=1, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
+                          train_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=5, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3, kv_cache_size=32,
+                       eos_tokens=[63], return_routed_experts=True)
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(),
+                   cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    out = cl.generate(["abc", "de"])
+    assert out.routed_experts is not None and len(out.routed_experts) == 2
+    for r_, t_, pl in zip(out.routed_experts, out.tokens, out.prompt_lengths):
+        assert r_.shape == (int(pl) + len(t_) - 1, 1, 2) and r_.min() >= 0 and r_.max() < 4
+    learner = GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.04))
+    seen = []
+    orig = actor.forward
+
+    def spy(*a, **kw):
+        if kw.get("routed_experts") is not None and torch.is_grad_enabled():
+            seen.append(kw["routed_experts"].clone())
+        return orig(*a, **kw)
+    actor.forward = spy
+    learner.train([{"prompts": ["ab", "cd"]}])
+    assert cl.global_steps == 1 and seen and seen[0].dim() == 4 and int(seen[0].max()) < 4
+    assert (seen[0] == -1).any()                  # padding slots are left to the model's own router

@@ -137,3 +137,37 @@ def test_config_validation():
         GRPOConfig(loss_agg_mode="nope")
     assert DAPOConfig(num_generations=4).epsilon_high == 0.28
     assert PPOConfig().epsilon_low == 0.2
+
+
+def test_align_routed_experts_pads_like_the_trainer_and_replay_reproduces_the_samplers_routing():
+    import numpy as np
+    import torch
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.rl import common
+    L, k = 2, 2
+    r = lambda n, base: (np.arange(n * L * k).reshape(n, L, k) % 5 + base).astype(np.int16)  # noqa: E731
+    out = common.align_routed_experts([r(5, 0), r(9, 1)], [2, 4], prompt_width=4, completion_width=3)
+    assert out.shape == (2, 7, L, k) and out.dtype == np.int16
+    a = r(5, 0)                                   # prompt 3 + completion 2: left pad 1, right pad 1
+    assert (out[0, 0] == -1).all() and (out[0, 1:4] == a[:3]).all() and (out[0, 4:6] == a[3:]).all() and (out[0, 6] == -1).all()
+    b = r(9, 1)                                   # prompt 5 + completion 4: prompt keeps its tail, completion its head
+    assert (out[1, :4] == b[1:5]).all() and (out[1, 4:] == b[5:8]).all()
+    assert common.align_routed_experts([r(5, 0), None], [2, 4], 4, 3) is None and common.align_routed_experts(None, [], 4, 3) is None
+    # replay: a model forced to the routing that ANOTHER set of router weights chose gives the log-probs of that routing
+    cfg = ModelConfig.tiny_llama().replace(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1, num_experts=4, num_experts_per_tok=2, moe_hidden_dim=32)
+    model = create_model(cfg, seed=0)
+    toks = torch.randint(3, 64, (2, 7), generator=torch.Generator().manual_seed(1))
+    model(toks, skip_lm_head=True)
+    own = model.routed_experts_of_last_forward()                       # [2, 7, L, k]
+    assert own.shape == (2, 7, 2, 2)
+    forced = (own + 1) % 4                                             # a different, valid choice everywhere
+    h_own, _ = model(toks, skip_lm_head=True)
+    h_forced, _ = model(toks, skip_lm_head=True, routed_experts=forced)
+    assert torch.equal(model.routed_experts_of_last_forward(), forced) and not torch.allclose(h_own, h_forced)
+    h_unset, _ = model(toks, skip_lm_head=True, routed_experts=torch.full_like(own, -1))
+    assert torch.allclose(h_unset, h_own)                               # -1 leaves every token to the model's router
+    lp = common.compute_per_token_logps(model, toks[:, :3], toks[:, 3:], 0, 1, routed_experts=forced.numpy())
+    lp2 = common.compute_per_token_logps(model, toks[:, :3], toks[:, 3:], 0, 1)
+    assert lp.shape == (2, 4) and not torch.allclose(lp, lp2)

@@ -79,10 +79,13 @@ class Sampler(BaseSampler):
                  temperature: float = 0.0, top_p: Optional[float] = None, top_k: Optional[int] = None,
                  beam_size: Optional[int] = None, seed: Optional[int] = None, pad_output: bool = False, *,
                  prompt_token_ids: Optional[Sequence[Sequence[int]]] = None,
-                 model_inputs: Optional[dict] = None) -> SamplerOutput:
+                 model_inputs: Optional[dict] = None, return_routed_experts: bool = False) -> SamplerOutput:
         """`model_inputs`: extra keyword tensors for the prefill pass of a multimodal model (e.g. `pixel_values`,
         `pixel_position_ids`, `input_features`): the prompts carry the placeholder tokens, the decode steps are
-        text only (tunix/generate/sampler.py: images / audio hooks)."""
+        text only (tunix/generate/sampler.py: images / audio hooks). `return_routed_experts`: for a mixture-of-experts
+        model, also return per sequence the experts every token was routed to, `[prompt + completion - 1 or so,
+        num_layers, top_k]` (prompt tokens, then one row per token that was fed back), for router replay in the
+        trainer."""
         if (input_strings is None) == (prompt_token_ids is None):
             raise ValueError("give exactly one of input_strings / prompt_token_ids")
         if isinstance(input_strings, str):
@@ -114,6 +117,10 @@ class Sampler(BaseSampler):
         hidden, cache = self._model(toks, positions=positions, cache=cache, segment_ids=seg, skip_lm_head=True, **extra)
         last_h = hidden[:, -1:]
         next_pos = positions[:, -1:] + 1
+        routed_steps = None
+        if return_routed_experts and hasattr(self._model, "routed_experts_of_last_forward"):
+            r0 = self._model.routed_experts_of_last_forward()
+            routed_steps = [r0] if r0 is not None else None           # [B, plen, L, k], left-padded like the prompt
         forbidden = torch.as_tensor(sorted(set(forbidden_tokens)), device=dev) if forbidden_tokens else None
         eos_t = torch.as_tensor(eos_ids, device=dev)
         out_tokens = torch.full((B, max_generation_steps), pad_id, dtype=torch.long, device=dev)
@@ -143,9 +150,18 @@ class Sampler(BaseSampler):
                                         skip_lm_head=True)
             last_h = hidden
             next_pos = next_pos + 1
+            if routed_steps is not None:
+                routed_steps.append(self._model.routed_experts_of_last_forward())
         self._model.train(was_training)
-        return self._finish(prompts, plens, out_tokens[:, :max(n_steps, 0)], out_logps, out_logits, eos_ids, pad_id, echo,
-                            pad_output, max_generation_steps)
+        out = self._finish(prompts, plens, out_tokens[:, :max(n_steps, 0)], out_logps, out_logits, eos_ids, pad_id, echo,
+                           pad_output, max_generation_steps)
+        if routed_steps is not None:
+            allr = torch.cat(routed_steps, 1).to(torch.int16).cpu().numpy()          # [B, plen + fed tokens, L, k]
+            P = prompts.shape[1]
+            # per sequence: its real prompt tokens, then the completion tokens that were fed back (all but the last)
+            out.routed_experts = [allr[b, P - int(plens[b]):P + max(len(out.tokens[b]) - (len(prompts[b]) if echo else 0) - 1, 0)]
+                                  for b in range(B)]
+        return out
 
     # ------------------------------------------------------------ post-process
     def _finish(self, prompts, plens, gen: torch.Tensor, logps, logits, eos_ids, pad_id, echo, pad_output, max_steps):

@@ -232,17 +232,18 @@ class DecoderLayer(nn.Module):
             self.post_attn_norm = mk()   # Gemma-2/3: norm on the attention output before the residual add
             self.post_ffw_norm = mk()
 
-    def forward(self, x, positions, rope, cache=None, segment_ids=None, attention_mask=None):
+    def forward(self, x, positions, rope, cache=None, segment_ids=None, attention_mask=None, forced_experts=None):
         cfg = self.cfg
         h = self.input_layernorm(x)
+        kw = {"forced_experts": forced_experts} if (forced_experts is not None and cfg.is_moe) else {}
         if cfg.post_norms:
             a, new_cache = self.self_attn(h, positions, rope, cache, segment_ids, attention_mask)
             x = x + self.post_attn_norm(a)
-            m = self.mlp(self.post_attention_layernorm(x))
+            m = self.mlp(self.post_attention_layernorm(x), **kw)
             x = x + self.post_ffw_norm(m)
         else:
             x, new_cache = self.self_attn(h, positions, rope, cache, segment_ids, attention_mask, residual=x)
-            x = self.mlp(self.post_attention_layernorm(x), residual=x)
+            x = self.mlp(self.post_attention_layernorm(x), residual=x, **kw)
         return x, new_cache
 
 
@@ -310,7 +311,9 @@ class Transformer(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_tokens, positions=None, cache=None, attention_mask=None, segment_ids=None,
-                skip_lm_head: bool = False, output_hidden_states: bool = False):
+                skip_lm_head: bool = False, output_hidden_states: bool = False, routed_experts=None):
+        """`routed_experts` int [B, T, num_layers, top_k] replays the sampler's expert choice in every MoE layer
+        (router replay, tunix/models/qwen3/model.py:895-939); entries < 0 leave a token to the layer's own router."""
         cfg = self.config
         B, T = input_tokens.shape
         emb_tokens = input_tokens
@@ -323,10 +326,12 @@ class Transformer(nn.Module):
         x = F.embedding(emb_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         return self.forward_embeddings(x, positions=positions, cache=cache, attention_mask=attention_mask,
                                        segment_ids=segment_ids, skip_lm_head=skip_lm_head,
-                                       output_hidden_states=output_hidden_states, batch_shape=(B, T))
+                                       output_hidden_states=output_hidden_states, batch_shape=(B, T),
+                                       routed_experts=routed_experts)
 
     def forward_embeddings(self, x, positions=None, cache=None, attention_mask=None, segment_ids=None,
-                           skip_lm_head: bool = False, output_hidden_states: bool = False, batch_shape=None):
+                           skip_lm_head: bool = False, output_hidden_states: bool = False, batch_shape=None,
+                           routed_experts=None):
         """The decoder stack on input embeddings `x` (what `forward` runs after the token lookup; multimodal front
         ends call it with image soft tokens spliced in). `batch_shape` = (B, T) of the full batch when `x` is this
         rank's shard of it."""
@@ -344,11 +349,12 @@ class Transformer(nn.Module):
             rope = self._rope(cfg.layer_type(i) == "local", dev)
             if hook is not None and x.requires_grad:
                 x = _GradBoundary.apply(x, i, hook)
+            forced = routed_experts[:, :, i] if (routed_experts is not None and cfg.is_moe) else None
             if use_remat:
-                x, _ = _torch_checkpoint(layer, x, positions, rope, None, segment_ids, attention_mask,
+                x, _ = _torch_checkpoint(layer, x, positions, rope, None, segment_ids, attention_mask, forced,
                                          use_reentrant=False)
             else:
-                x, c = layer(x, positions, rope, None if cache is None else cache[i], segment_ids, attention_mask)
+                x, c = layer(x, positions, rope, None if cache is None else cache[i], segment_ids, attention_mask, forced)
                 if new_cache is not None:
                     new_cache.append(c)
         if hook is not None and x.requires_grad:
@@ -367,6 +373,12 @@ class Transformer(nn.Module):
         return F.lm_head_logprobs(hidden, self.head_weight(), targets, softcap=self.config.final_logit_softcap,
                                   temperature=temperature, want_entropy=want_entropy,
                                   chunk=chunk or self.config.logprob_chunk)
+
+    def routed_experts_of_last_forward(self):
+        """[B, T, num_layers, top_k] expert ids the MoE layers chose in the last forward (None for dense models)."""
+        rows = [l.mlp.last_routed_experts for l in self.layers
+                if isinstance(l.mlp, MoELayer) and l.mlp.last_routed_experts is not None]
+        return torch.stack(rows, 2) if rows and len(rows) == len(self.layers) else None
 
     def aux_loss(self):
         """Sum of MoE router auxiliary losses of the last forward (None for dense models)."""

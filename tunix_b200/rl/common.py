@@ -118,8 +118,12 @@ def compute_per_token_logps(model, prompt_tokens, completion_tokens, pad_id, eos
             positions = build_positions_from_mask(mask)
         seg = mask
 
+    extra = {}
+    if routed_experts is not None and getattr(getattr(model, "config", None), "is_moe", False):
+        extra["routed_experts"] = torch.as_tensor(routed_experts, device=ids.device).long()
+
     def run():
-        hidden, _ = model(ids, positions=positions, segment_ids=seg, skip_lm_head=True)
+        hidden, _ = model(ids, positions=positions, segment_ids=seg, skip_lm_head=True, **extra)
         h = hidden[:, P - 1:-1]
         return model.token_logprobs(h, completion_tokens, temperature=temperature or 1.0,
                                     want_entropy=return_entropy, chunk=chunk_size or None)
@@ -130,6 +134,38 @@ def compute_per_token_logps(model, prompt_tokens, completion_tokens, pad_id, eos
     else:
         logp, ent = run()
     return (logp, ent) if return_entropy else logp
+
+
+UNSET_ROUTED_EXPERT = -1      # a router-replay slot the trainer leaves to the model's own router (0 is a real expert)
+
+
+def align_routed_experts(routed_experts, completion_lengths, prompt_width: int, completion_width: int):
+    """The sampler's routing, laid out over the trainer's padded `[prompt | completion]` stream.
+
+    The sampler reports `[prompt_len + completion_len, num_layers, top_k]` per generation; the trainer sees prompts
+    left-padded to `prompt_width` and completions right-padded to `completion_width`. Routing is padded the same
+    way (over-long prompts keep their tail, over-long completions their head), so that every replayed expert stays
+    with the token it was captured for; everything else is `UNSET_ROUTED_EXPERT`. Replay is all-or-nothing: one
+    missing row and the batch falls back to the model's own router (returns None)
+    (tunix/rl/common.py:331-393). Returns int16 `[B, prompt_width + completion_width, num_layers, top_k]`."""
+    import numpy as np
+    if not routed_experts or any(r is None for r in routed_experts):
+        return None
+    if len(routed_experts) != len(completion_lengths):
+        raise ValueError(f"got {len(routed_experts)} routing rows but {len(completion_lengths)} completion lengths")
+    rows = []
+    for routed, clen in zip(routed_experts, completion_lengths):
+        routed = np.asarray(routed, dtype=np.int16)
+        if routed.ndim != 3:
+            raise ValueError(f"routed_experts must be [length, num_layers, top_k]; got shape {routed.shape}")
+        split = max(routed.shape[0] - int(clen), 0)
+        p_part = routed[max(split - prompt_width, 0):split]
+        c_part = routed[split:split + min(routed.shape[0] - split, completion_width)]
+        row = np.full((prompt_width + completion_width,) + routed.shape[1:], UNSET_ROUTED_EXPERT, dtype=np.int16)
+        row[prompt_width - p_part.shape[0]:prompt_width] = p_part
+        row[prompt_width:prompt_width + c_part.shape[0]] = c_part
+        rows.append(row)
+    return np.stack(rows)
 
 
 def get_per_token_logps(model, input_tokens, positions, segment_ids=None, logits_to_keep: Optional[int] = None):

@@ -104,10 +104,13 @@ class GRPOLearner(RLLearner):
                            "completions/min_length": (float(lens.min()), np.min)}, mode)
         for fn in self.metric_fns:
             cl.buffer_metrics(fn(prompts=prompt_texts, completions=out.text, rewards=rewards, advantages=adv), mode)
+        # router replay: the experts the sampler chose, laid out over the padded [prompt | completion] stream
+        routed = common.align_routed_experts(out.routed_experts, lens, P, C) if getattr(out, "routed_experts", None) else None
         return common.TrainExample(prompt_ids=prompt_ids, prompt_mask=prompt_mask, completion_ids=completion_ids,
                                    completion_mask=completion_mask,
                                    advantages=torch.from_numpy(np.asarray(adv, np.float32)).to(dev),
-                                   ref_per_token_logps=ref_logps, old_per_token_logps=old_logps)
+                                   ref_per_token_logps=ref_logps, old_per_token_logps=old_logps,
+                                   routed_experts=None if routed is None else torch.from_numpy(routed).to(dev))
 
 
 GrpoLearner = GRPOLearner

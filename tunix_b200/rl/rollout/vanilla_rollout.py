@@ -24,7 +24,10 @@ class VanillaRollout(BaseRollout):
     def generate(self, prompts, rollout_config: RolloutConfig, **kwargs) -> RolloutOutput:
         tok_prompts = kwargs.get("prompt_token_ids")
         call = self._engine if self._engine is not None else self._sampler
-        out = call(input_strings=None if tok_prompts is not None else prompts,
+        extra = {}
+        if self._engine is None and getattr(rollout_config, "return_routed_experts", False):
+            extra["return_routed_experts"] = True        # dense sampler only: the paged engine does not record routing
+        out = call(**extra, input_strings=None if tok_prompts is not None else prompts,
                    prompt_token_ids=tok_prompts,
                    max_generation_steps=rollout_config.max_tokens_to_generate,
                    max_prompt_length=rollout_config.max_prompt_length, temperature=rollout_config.temperature,
