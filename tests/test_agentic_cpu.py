@@ -215,3 +215,74 @@ def test_episode_over_http_against_a_remote_engine_server():
     down = HTTPModelClient(http.url, retries=1, timeout=2.0)
     with pytest.raises(RemoteModelError, match="no answer"):
         down.generate([1, 2], 1)
+
+
+def test_partial_rollout_resume_context_limit_and_routed_experts():
+    tok = CharTok()
+    calls = []
+
+    async def model_call(chat_completions=None, prompt_token_ids=None, max_tokens=None):
+        calls.append(len(prompt_token_ids))
+        n = len(calls)
+        text = '<tool_call>{"name": "calculator", "arguments": {"expression": "%d+1"}}</tool_call>' % n if n < 3 else \
+            '<tool_call>{"name": "finish", "arguments": {"response": "3"}}</tool_call>'
+        ids = tok.encode(text)
+        return {"text": text, "tokens": ids, "logprobs": [-0.25] * len(ids), "policy_version": 7 + n // 2,
+                "routed_experts": np.full((len(ids), 2, 2), n, np.int16)}
+
+    def engine(**kw):
+        env = ToolEnvironment(task={"question": "count", "answer": "3"}, tools=[CalculatorTool()], reward_fn="exact_match", max_steps=6)
+        return TrajectoryCollectEngine(ToolAgent(tools={"calculator": CalculatorTool()}), env, model_call=model_call, tokenizer=tok,
+                                       chat_parser=get_parser("qwen"), max_steps=6, **kw)
+    eng = engine()
+    part = asyncio.run(eng.collect("Token", max_new_steps=1))
+    assert part["status"] == TrajectoryStatus.PARTIAL and part["num_turns"] == 1 and len(calls) == 1
+    ctx_after_first = calls[0]
+    out = asyncio.run(eng.resume("Token"))                                       # same agent, environment and token context
+    assert out["status"] == TrajectoryStatus.SUCCEEDED and out["num_turns"] == 3 and out["trajectory_reward"] == 1.0
+    assert calls[1] > ctx_after_first and calls[2] > calls[1]                    # every call sees the whole conversation so far
+    assert out["policy_versions"] == [7, 8, 8] and out["policy_version"] == 7   # the oldest weights that contributed
+    assert [int(r[0, 0, 0]) for r in out["routed_experts"]] == [1, 2, 3]
+    with pytest.raises(RuntimeError):
+        asyncio.run(eng.resume("Token"))                                         # a finished episode cannot be resumed
+    # context window: the second call would start beyond the limit
+    calls.clear()
+    short = engine(max_context_tokens=ctx_after_first + 10)
+    out = asyncio.run(short.collect("Token"))
+    assert out["status"] == TrajectoryStatus.MAX_CONTEXT_LIMIT_REACHED and out["num_turns"] == 1
+
+
+def test_agentic_learner_pack_first_scoring_eval_and_trajectory_log():
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import ClusterConfig, RLTrainingConfig, RolloutConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.rl.agentic.agentic_grpo_learner import AgenticGRPOLearner
+    from tunix_b200.rl.algorithm_config import GRPOConfig
+    from tunix_b200.rl.rl_cluster import RLCluster
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
+    actor, ref = create_model(cfg, seed=0), create_model(cfg, seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=2,
+                          train_micro_batch_size=2)
+    rc = RolloutConfig(max_tokens_to_generate=5, max_prompt_length=16, temperature=1.0, seed=1, kv_cache_size=64, eos_tokens=[63])
+    cl = RLCluster(actor=actor, reference=ref, tokenizer=CharTok(), cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    ref_calls, logged = [], []
+    orig_ref = cl.get_ref_per_token_logps
+
+    def spy_ref(p, c, *a, **kw):
+        ref_calls.append((tuple(p.shape), tuple(c.shape), kw.get("segment_ids") is not None))
+        return orig_ref(p, c, *a, **kw)
+    cl.get_ref_per_token_logps = spy_ref
+
+    def length_reward(prompts, completions, completion_lengths=None, **kw):
+        return [float(n % 3) for n in completion_lengths]
+    learner = AgenticGRPOLearner(cl, [length_reward], GRPOConfig(num_generations=2, beta=0.04), max_concurrency=4,
+                                 chat_parser=get_parser("raw"), pack_first=True, pack_budget=48, trajectory_logger=logged.extend)
+    before = torch.cat([p.detach().reshape(-1).clone() for p in actor.parameters()])
+    learner.train([{"prompts": ["ab", "cd"]}, {"prompts": ["ef", "gh"]}], eval_ds=[{"prompts": ["xy"]}])
+    assert cl.global_steps == 2 and not torch.equal(before, torch.cat([p.detach().reshape(-1) for p in actor.parameters()]))
+    # the reference scored packed rows (no prompt side, segment ids given), not padded groups
+    assert ref_calls and all(p[1] == 0 and seg for p, _, seg in ref_calls)
+    assert len(logged) == 8 and {"conversation_tokens", "trajectory_reward", "policy_version"} <= set(logged[0])
+    assert cl.metrics_logger.metric_exists("", "eval/rewards/mean", "eval")
+    assert len(cl.metrics_logger.get_metric_history("", "eval/episodes", "eval")) == 2      # after each of the two steps

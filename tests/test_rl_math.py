@@ -171,3 +171,36 @@ def test_align_routed_experts_pads_like_the_trainer_and_replay_reproduces_the_sa
     lp = common.compute_per_token_logps(model, toks[:, :3], toks[:, 3:], 0, 1, routed_experts=forced.numpy())
     lp2 = common.compute_per_token_logps(model, toks[:, :3], toks[:, 3:], 0, 1)
     assert lp.shape == (2, 4) and not torch.allclose(lp, lp2)
+
+
+def test_per_token_logps_on_packed_rows_equal_the_padded_ones():
+    """Two sequences packed into one row (segment ids, restarted positions, no prompt side) give the same completion
+    log-probs as the padded [prompt | completion] layout."""
+    import numpy as np
+    import torch
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.rl import common, utils as rl_utils
+    cfg = ModelConfig.tiny_llama().replace(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+    g = torch.Generator().manual_seed(2)
+    pad = 0
+    prompts = torch.tensor([[pad, pad, 5, 6, 7], [9, 10, 11, 12, 13]])
+    pmask = (prompts != pad).int()
+    comps = torch.tensor([[20, 21, 22, pad], [30, 31, 32, 33]])
+    cmask = (comps != pad).int()
+    padded = common.compute_per_token_logps(model, prompts, comps, pad, 1, completion_mask=cmask)
+    ex = common.TrainExample(prompt_ids=prompts, prompt_mask=pmask, completion_ids=comps, completion_mask=cmask,
+                             advantages=torch.tensor([1.0, -1.0]))
+    packed = list(rl_utils.pack_sequences([ex], budget=20, pack_size=1, pad_id=pad, device=torch.device("cpu")))
+    assert len(packed) == 1 and packed[0].completion_ids.shape == (1, 20) and packed[0].prompt_ids.shape[1] == 0
+    pk = packed[0]
+    lp = common.compute_per_token_logps(model, pk.prompt_ids, pk.completion_ids, pad, 1, completion_mask=pk.completion_mask,
+                                        segment_ids=pk.segment_ids, segment_positions=pk.segment_positions)
+    got = lp[0][pk.completion_mask[0] > 0]
+    want = torch.cat([padded[0][:3], padded[1]])                    # sequence 0 has three completion tokens, sequence 1 four
+    order = pk.completion_ids[0][pk.completion_mask[0] > 0]
+    if int(order[0]) == 30:                                         # the packer may place the longer sequence first
+        want = torch.cat([padded[1], padded[0][:3]])
+    assert torch.allclose(got, want, atol=1e-5), (got, want)

@@ -28,7 +28,8 @@ class AgenticGRPOLearner(AgenticRLLearner):
         tr.with_rl_metrics_to_log({k: np.mean for k in ("kl", "pg_clipfrac", "ppo_kl", "entropy")})
         self.advantage_fn = function_registry.get_advantage_estimator(algo_config.advantage_estimator)
 
-    def _process_group(self, items: list) -> Optional[common.TrainExample]:
+    def _process_group(self, items: list, defer_logps: bool = False) -> Optional[common.TrainExample]:
+        """`defer_logps`: leave the reference log-probs out; the caller computes them after packing."""
         cfg, dev = self.algo_config, self.device
         trajs = [it.traj for it in sorted(items, key=lambda x: x.episode_id)]
         valid = np.asarray([t["status"] not in INVALID_TRAJECTORY_STATUSES and t["conversation_masks"].sum() > 0
@@ -70,7 +71,7 @@ class AgenticGRPOLearner(AgenticRLLearner):
                                  completion_mask=t_(cmask), advantages=t_(np.asarray(adv, np.float32)),
                                  old_per_token_logps=t_(old) if cfg.use_rollout_logps else None,
                                  policy_version=self.policy_version)
-        if getattr(cfg, "beta", 0.0) != 0.0:
+        if getattr(cfg, "beta", 0.0) != 0.0 and not defer_logps:
             ctx_mask = t_((cids != self.pad_id).astype(np.int32))
             ex.ref_per_token_logps = self.rl_cluster.get_ref_per_token_logps(
                 ex.prompt_ids, ex.completion_ids, self.pad_id, self.eos_id, completion_mask=ctx_mask,

@@ -76,12 +76,19 @@ class AgenticRLLearner(abc.ABC):
     def __init__(self, rl_cluster: RLCluster, reward_fns, algo_config, *, agent_class=ModelAgent, agent_kwargs=None,
                  env_class=TaskEnvironment, env_kwargs=None, chat_parser=None, max_concurrency: int = 16,
                  off_policy_steps: int = 0, max_turns: int = 1, episode_timeout: float = 600.0, metric_fns=None,
-                 server_mode: bool = False, model_client=None):
+                 server_mode: bool = False, model_client=None, pack_first: bool = False, pack_budget: Optional[int] = None,
+                 trajectory_logger=None):
         """`model_client`: an `async (chat_completions, prompt_token_ids, max_tokens) -> {"text", "tokens",
         "logprobs"}` that replaces the cluster's own rollout engine for the episodes' model calls, e.g.
         `http_model_client.HTTPModelClient` in front of engines in another process. Keeping those engines' weights
         current is then the deployment's job (`experimental.weight_sync`)."""
         self.model_client = model_client
+        # pack first (tunix/rl/agentic/agentic_grpo_learner.py:338-442,649): the groups of a prompt batch are packed
+        # into rows of `pack_budget` tokens BEFORE the reference (and, when asked for, the old-policy) log-probs are
+        # computed, so that those forward passes run on dense packed rows instead of rows padded to the longest
+        # conversation of a group
+        self.pack_first, self.pack_budget = pack_first, pack_budget
+        self.trajectory_logger = trajectory_logger      # object with .log(items) or a callable; gets every finished group
         self.rl_cluster, self.algo_config = rl_cluster, algo_config
         self.tcfg = rl_cluster.cluster_config.training_config
         self.agent_class, self.agent_kwargs = agent_class, dict(agent_kwargs or {})
@@ -190,7 +197,69 @@ class AgenticRLLearner(abc.ABC):
 
     # ------------------------------------------------------------- consumer
     @abc.abstractmethod
-    def _process_group(self, items: list) -> Optional[common.TrainExample]: ...
+    def _process_group(self, items: list, defer_logps: bool = False) -> Optional[common.TrainExample]: ...
+
+    def _log_trajectories(self, items: list) -> None:
+        lg = self.trajectory_logger
+        if lg is None:
+            return
+        rows = [{"episode_id": getattr(it, "episode_id", None), "group_id": getattr(it, "group_id", None),
+                 "policy_version": self.policy_version, **{k: (v.tolist() if hasattr(v, "tolist") else v)
+                                                           for k, v in getattr(it, "traj", {}).items()}} for it in items]
+        (lg.log if hasattr(lg, "log") else lg)(rows)
+
+    def _pack_and_score(self, examples: list) -> list:
+        """Pack the step's examples into dense rows, then compute the deferred log-probs on the packed rows."""
+        from .. import utils as rl_utils
+        rc = self.rl_cluster._rollout_config(Mode.TRAIN)
+        budget = self.pack_budget or self.tcfg.max_seq_token_per_tpu or (rc.max_prompt_length + rc.max_tokens_to_generate)
+        longest = max(int(e.prompt_mask.sum(1).max()) + int((e.completion_ids != self.pad_id).sum(1).max()) for e in examples)
+        budget = max(budget, longest)
+        packed = list(rl_utils.pack_sequences(examples, budget, pack_size=max(self.tcfg.train_micro_batch_size or 1, 1),
+                                              pad_id=self.pad_id, device=self.device,
+                                              max_segments=self.tcfg.max_segments_per_packed_row))
+        beta = getattr(self.algo_config, "beta", 0.0)
+        for ex in packed:
+            if beta != 0.0:
+                ex.ref_per_token_logps = self.rl_cluster.get_ref_per_token_logps(
+                    ex.prompt_ids, ex.completion_ids, self.pad_id, self.eos_id, completion_mask=ex.completion_mask,
+                    temperature=self.algo_config.temperature, segment_ids=ex.segment_ids,
+                    segment_positions=ex.segment_positions)
+            if not self.algo_config.use_rollout_logps and ex.old_per_token_logps is None:
+                # no update has happened since the last weight sync: the actor's weights are the sampler's
+                ex.old_per_token_logps = self.rl_cluster.get_actor_per_token_logps(
+                    ex.prompt_ids, ex.completion_ids, self.pad_id, self.eos_id, completion_mask=ex.completion_mask,
+                    temperature=self.algo_config.temperature, segment_ids=ex.segment_ids,
+                    segment_positions=ex.segment_positions)
+        return packed
+
+    def evaluate(self, eval_ds: Iterable[dict]) -> dict:
+        """Run the agentic loop over `eval_ds` without training: mean trajectory reward, share of valid episodes and
+        turns per episode, logged in eval mode (the reference evaluates inside its agentic loop every
+        `eval_every_n_steps`)."""
+        async def run():
+            self._batcher = self._batcher or _ModelCallBatcher(self._generate_batch, max_batch=self.max_concurrency)
+            rewards, valid, turns = [], [], []
+            for bi, batch in enumerate(eval_ds):
+                orch = RolloutOrchestrator(engine_factory=self._engine_factory, group_size=self.algo_config.num_generations,
+                                           max_concurrency=self.max_concurrency)
+                prod = asyncio.create_task(orch.run_producers_from_stream(self._make_pairs(batch, bi)))
+                async for groups in orch.yield_batches(1):
+                    for g in groups:
+                        for it in g:
+                            rewards.append(float(it.traj["trajectory_reward"]))
+                            valid.append(it.traj["status"] not in _INVALID)
+                            turns.append(it.traj["num_turns"])
+                await prod
+            return rewards, valid, turns
+        from .agents.agent_types import INVALID_TRAJECTORY_STATUSES as _INVALID
+        rewards, valid, turns = asyncio.run_coroutine_threadsafe(run(), self._loop).result()
+        out = {"eval/rewards/mean": float(np.mean(rewards)) if rewards else 0.0,
+               "eval/trajectory/valid_frac": float(np.mean(valid)) if valid else 0.0,
+               "eval/trajectory/num_turns": float(np.mean(turns)) if turns else 0.0, "eval/episodes": len(rewards)}
+        self.rl_cluster.buffer_metrics({k: (v, np.mean) for k, v in out.items()}, Mode.EVAL)
+        self.rl_cluster.flush_metrics()
+        return out
 
     def train(self, train_ds: Iterable[dict], eval_ds=None) -> None:
         out_q: queue.Queue = queue.Queue()
@@ -210,12 +279,18 @@ class AgenticRLLearner(abc.ABC):
                 if kind == "done":
                     break
                 if kind == "group":
-                    ex = self._process_group(payload)
+                    self._log_trajectories(payload)
+                    ex = self._process_group(payload, defer_logps=self.pack_first)
                     if ex is not None:
                         pending.append(ex)
-                        self.rl_cluster.update_actor([ex], None)
+                        if not self.pack_first:
+                            self.rl_cluster.update_actor([ex], None)
                     continue
-                # batch_end: extra iterations over the collected groups, then weight sync under the lock
+                # batch_end: (pack-first: pack, score and train now;) extra iterations over the collected groups,
+                # then weight sync under the lock
+                if self.pack_first and pending:
+                    pending = self._pack_and_score(pending)
+                    self.rl_cluster.update_actor(list(pending), None)
                 for _ in range(1, mu):
                     self.rl_cluster.update_actor(list(pending), None)
                 pending = []
@@ -228,11 +303,16 @@ class AgenticRLLearner(abc.ABC):
                     if srv is not None:
                         srv.resume()            # re-reads the updated weights before the next admission
                 self.rl_cluster.flush_metrics()
+                if eval_ds is not None and self.tcfg.eval_every_n_steps and \
+                        self.rl_cluster.global_steps % self.tcfg.eval_every_n_steps == 0:
+                    self.evaluate(eval_ds)
                 permits.release()
                 if max_steps is not None and self.rl_cluster.global_steps >= max_steps:
                     break
         finally:
             fut.cancel()
+            for _ in range(self.off_policy_steps + 2):      # a producer parked on the permit must not outlive the loop
+                permits.release()
             self.close()
 
     def close(self) -> None:

@@ -31,6 +31,8 @@ class Step:
     env_tokens: Optional[np.ndarray] = None
     env_masks: Optional[np.ndarray] = None
     logprobs: Optional[np.ndarray] = None
+    policy_version: Optional[Any] = None          # version of the weights this step's tokens were sampled with
+    routed_experts: Optional[np.ndarray] = None   # [tokens of the call, num_layers, top_k] when the sampler reports it
 
 
 class TrajectoryStatus(enum.Enum):
@@ -42,6 +44,7 @@ class TrajectoryStatus(enum.Enum):
     ENV_TIMEOUT = enum.auto()
     FAILED = enum.auto()
     CANCELLED = enum.auto()
+    PARTIAL = enum.auto()          # handed back unfinished by collect(max_new_steps=...); resume() continues it
 
 
 INVALID_TRAJECTORY_STATUSES = frozenset({TrajectoryStatus.FAILED, TrajectoryStatus.TIMEOUT,

@@ -5,7 +5,16 @@ Limits: per-episode wall-clock `timeout`, `max_steps`, `max_response_length` tok
 environment turns (context limit), per env-step timeout. Every turn records assistant token ids, their
 sampled log-probs and masks (assistant 1 / environment 0); later turns are prompted with the recorded ids
 (exact token continuity). Monte-Carlo returns are filled at the end. Output modes: "Trajectory" (objects),
-"Token" (flattened arrays for training), "Steps", "Conversation"."""
+"Token" (flattened arrays for training), "Steps", "Conversation".
+
+Also (tunix/rl/agentic/trajectory/trajectory_collect_engine.py:407-470,877-...):
+* routed experts: a model call that reports `routed_experts` (mixture-of-experts router replay) has them stored on
+  its step and concatenated, per token of the conversation, in the "Token" output;
+* context window: with `max_context_tokens` the episode ends (MAX_CONTEXT_LIMIT_REACHED) before a model call whose
+  prompt would not leave room for a reply;
+* partial rollouts: `collect(..., max_new_steps=k)` stops after k further turns with status PARTIAL and keeps agent,
+  environment and token context alive; `resume()` continues the same episode (typically after a weight sync; every
+  step records the `policy_version` its tokens were sampled with)."""
 from __future__ import annotations
 
 import asyncio
@@ -22,7 +31,7 @@ class TrajectoryCollectEngine:
     def __init__(self, agent, env, *, model_call: Callable[..., Awaitable[dict]], tokenizer=None, chat_parser=None,
                  max_steps: int = 10, gamma: float = 1.0, timeout: float = 600.0, env_step_timeout: Optional[float] = None,
                  max_response_length: Optional[int] = None, final_reward_fn: Optional[Callable] = None,
-                 overlong_filter: bool = False):
+                 overlong_filter: bool = False, max_context_tokens: Optional[int] = None):
         self.agent, self.env = agent, env
         self.model_call = model_call
         self.tokenizer, self.chat_parser = tokenizer, chat_parser
@@ -31,32 +40,49 @@ class TrajectoryCollectEngine:
         self.max_response_length = max_response_length
         self.final_reward_fn = final_reward_fn
         self.overlong_filter = overlong_filter
+        self.max_context_tokens = max_context_tokens
+        self._used = 0
+        self._started = False
         self._start = 0.0
         self._prompt_tokens: Optional[np.ndarray] = None
         self._context: list = []
 
     # --------------------------------------------------------------- episode
-    async def collect(self, mode: str = "Trajectory"):
+    async def collect(self, mode: str = "Trajectory", max_new_steps: Optional[int] = None):
+        """Run the episode (or, after a PARTIAL return, continue it). `max_new_steps`: hand the episode back after
+        this many further turns if it is not over by then."""
         traj = self.agent.trajectory
+        partial = False
         try:
-            await self._reset()
+            if not self._started:
+                await self._reset()
+                self._started, self._used = True, 0
             traj = self.agent.trajectory
             traj.status = TrajectoryStatus.RUNNING
-            used = 0
-            for _ in range(self.max_steps):
+            new_steps = 0
+            while True:
+                if len(traj.steps) >= self.max_steps:
+                    traj.status = TrajectoryStatus.MAX_STEPS_REACHED
+                    break
+                if max_new_steps is not None and new_steps >= max_new_steps:
+                    traj.status, partial = TrajectoryStatus.PARTIAL, True
+                    break
                 if time.monotonic() - self._start > self.timeout:
                     traj.status = TrajectoryStatus.TIMEOUT
                     break
-                done, n_tok = await self._one_step(traj, used)
-                used += n_tok
+                if self.max_context_tokens is not None and self._prompt_tokens is not None and \
+                        len(self._context) + 1 > self.max_context_tokens:
+                    traj.status = TrajectoryStatus.MAX_CONTEXT_LIMIT_REACHED     # no room left for a reply
+                    break
+                done, n_tok = await self._one_step(traj, self._used)
+                self._used += n_tok
+                new_steps += 1
                 if done:
                     traj.status = TrajectoryStatus.SUCCEEDED
                     break
-                if self.max_response_length is not None and used >= self.max_response_length:
+                if self.max_response_length is not None and self._used >= self.max_response_length:
                     traj.status = TrajectoryStatus.MAX_CONTEXT_LIMIT_REACHED
                     break
-            else:
-                traj.status = TrajectoryStatus.MAX_STEPS_REACHED
         except asyncio.CancelledError:
             traj.status = TrajectoryStatus.CANCELLED
             raise
@@ -66,14 +92,22 @@ class TrajectoryCollectEngine:
             traj.status = TrajectoryStatus.FAILED
             traj.env_time["error"] = f"{type(e).__name__}: {e}"
         finally:
-            try:
-                t0 = time.monotonic()
-                self.env.close()
-                traj.env_time["close_latency"] = time.monotonic() - t0
-            except Exception:
-                pass
-        self._finalize(traj)
+            if not partial:
+                try:
+                    t0 = time.monotonic()
+                    self.env.close()
+                    traj.env_time["close_latency"] = time.monotonic() - t0
+                except Exception:
+                    pass
+        if not partial:
+            self._finalize(traj)
         return self._format(traj, mode)
+
+    async def resume(self, mode: str = "Trajectory", max_new_steps: Optional[int] = None):
+        """Continue an episode that `collect(max_new_steps=...)` handed back as PARTIAL."""
+        if not self._started or self.agent.trajectory.status != TrajectoryStatus.PARTIAL:
+            raise RuntimeError("resume() continues an episode that collect() returned as PARTIAL")
+        return await self.collect(mode, max_new_steps)
 
     async def _reset(self):
         self._start = time.monotonic()
@@ -111,6 +145,8 @@ class TrajectoryCollectEngine:
         step.assistant_tokens = a_tok
         step.assistant_masks = np.ones(len(a_tok), np.int32)
         step.logprobs = np.asarray(out.get("logprobs", np.zeros(len(a_tok))), np.float32)
+        step.policy_version = out.get("policy_version")
+        step.routed_experts = None if out.get("routed_experts") is None else np.asarray(out["routed_experts"], np.int16)
         self._context.extend(a_tok.tolist())
         t0 = time.monotonic()
         coro = self.env.step_async(action.action)
@@ -155,8 +191,13 @@ class TrajectoryCollectEngine:
             toks, masks, lps = concat_conversation(self._prompt_tokens, traj.steps)
             if traj.masked_out:
                 masks = np.zeros_like(masks)
+            routed = [getattr(s_, "routed_experts", None) for s_ in traj.steps]
+            versions = [getattr(s_, "policy_version", None) for s_ in traj.steps]
             return {"prompt_tokens": self._prompt_tokens if self._prompt_tokens is not None else np.zeros(0, np.int64),
                     "conversation_tokens": toks, "conversation_masks": masks, "old_logprobs": lps,
                     "trajectory_reward": traj.reward, "status": traj.status, "masked_out": traj.masked_out,
-                    "policy_version": None, "num_turns": len(traj.steps)}
+                    "policy_version": min((v for v in versions if v is not None), default=None),
+                    "policy_versions": versions, "num_turns": len(traj.steps),
+                    # one routing array per model call (None when any call did not report its routing)
+                    "routed_experts": routed if routed and all(r is not None for r in routed) else None}
         raise ValueError(f"unknown output mode {mode!r}")

@@ -124,7 +124,12 @@ def compute_per_token_logps(model, prompt_tokens, completion_tokens, pad_id, eos
 
     def run():
         hidden, _ = model(ids, positions=positions, segment_ids=seg, skip_lm_head=True, **extra)
-        h = hidden[:, P - 1:-1]
+        if P > 0:
+            h = hidden[:, P - 1:-1]
+        else:
+            # packed rows have no prompt side: token t is predicted from position t - 1, and nothing predicts the
+            # first token of a row (it is a prompt token, masked out of every loss)
+            h = torch.cat([torch.zeros_like(hidden[:, :1]), hidden[:, :-1]], dim=1)
         return model.token_logprobs(h, completion_tokens, temperature=temperature or 1.0,
                                     want_entropy=return_entropy, chunk=chunk_size or None)
 
