@@ -83,6 +83,19 @@ def main():
     res["dx_cap"] = rel(xs.grad, xr.grad[sl])
     res["dgate_cap"] = rel(part.gate_proj.grad, full.gate_proj.grad[rank * n:(rank + 1) * n])
     part.ep.capacity_factor = None
+    # experts recomputed in backward from the rows that were received (no second exchange): same gradients
+    for p in part.parameters():
+        p.grad = None
+    xs = x_all[sl].clone().requires_grad_()
+    ws_ = w_all[sl].clone().requires_grad_()
+    out = ep_lib.expert_parallel_forward(part, xs, ws_, idx_all[sl], recompute=True)
+    out.backward(dout_all[sl])
+    _lib.raise_if_kernel_error()
+    res["out_rc"] = rel(out, ref[sl])
+    res["dx_rc"] = rel(xs.grad, xr.grad[sl])
+    res["dw_rc"] = rel(ws_.grad, wr.grad[sl])
+    res["dgate_rc"] = rel(part.gate_proj.grad, full.gate_proj.grad[rank * n:(rank + 1) * n])
+    res["ddown_rc"] = rel(part.down_proj.grad, full.down_proj.grad[rank * n:(rank + 1) * n])
     allres = [None] * world
     dist.all_gather_object(allres, res)
     if rank == 0:

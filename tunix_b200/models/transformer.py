@@ -193,7 +193,7 @@ class MoELayer(nn.Module):
         self.ep = None        # parallel.ep.EPContext once shard_experts has kept this rank's experts
         self.ep_group = None
 
-    def forward(self, x, residual=None, forced_experts: Optional[torch.Tensor] = None):
+    def forward(self, x, residual=None, forced_experts: Optional[torch.Tensor] = None, recompute_experts: bool = False):
         cfg = self.cfg
         B, T, D = x.shape
         E, k = cfg.num_experts, cfg.num_experts_per_tok
@@ -213,7 +213,7 @@ class MoELayer(nn.Module):
             frac = frac / max(idx.numel(), 1)
             self.last_aux_loss = cfg.router_aux_loss_coef * E * (frac * probs.mean(0)).sum()
         from ..parallel import moe_dispatch
-        y = moe_dispatch.expert_forward(self, xt, w, idx)
+        y = moe_dispatch.expert_forward(self, xt, w, idx, recompute=recompute_experts)
         y = y.view(B, T, D)
         return y if residual is None else y + residual
 
@@ -245,6 +245,20 @@ class DecoderLayer(nn.Module):
             x, new_cache = self.self_attn(h, positions, rope, cache, segment_ids, attention_mask, residual=x)
             x = self.mlp(self.post_attention_layernorm(x), residual=x, **kw)
         return x, new_cache
+
+
+def _moe_layer_split_remat(layer: DecoderLayer, x, positions, rope, segment_ids, attention_mask, forced):
+    """Activation recomputation for an expert-parallel MoE layer that does not repeat the token exchange: the
+    attention half (norm, projections, attention, second norm) is recomputed in backward as usual, the expert block
+    keeps the rows it received and rebuilds only its own activations (`ops.moe.local_experts(recompute=True)`).
+    Recomputing the whole layer instead would run dispatch and combine, both all-to-all exchanges with their
+    barriers, a second time in every backward pass."""
+    def attn_half(x_):
+        h = layer.input_layernorm(x_)
+        x1, _ = layer.self_attn(h, positions, rope, None, segment_ids, attention_mask, residual=x_)
+        return x1, layer.post_attention_layernorm(x1)
+    x1, h2 = _torch_checkpoint(attn_half, x, use_reentrant=False)
+    return layer.mlp(h2, residual=x1, forced_experts=forced, recompute_experts=True)
 
 
 class _GradBoundary(torch.autograd.Function):
@@ -350,7 +364,10 @@ class Transformer(nn.Module):
             if hook is not None and x.requires_grad:
                 x = _GradBoundary.apply(x, i, hook)
             forced = routed_experts[:, :, i] if (routed_experts is not None and cfg.is_moe) else None
-            if use_remat:
+            if use_remat and cfg.is_moe and not cfg.post_norms and getattr(layer.mlp, "ep", None) is not None \
+                    and getattr(layer.mlp.ep, "fused", False):
+                x = _moe_layer_split_remat(layer, x, positions, rope, segment_ids, attention_mask, forced)
+            elif use_remat:
                 x, _ = _torch_checkpoint(layer, x, positions, rope, None, segment_ids, attention_mask, forced,
                                          use_reentrant=False)
             else:

@@ -125,7 +125,7 @@ class _LocalExpertsFn(torch.autograd.Function):
     are ready to be summed, and its gradient <dy, y> is formed here as <dy W_down, h> without keeping y."""
 
     @staticmethod
-    def forward(ctx, xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind):
+    def forward(ctx, xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind, recompute=False):
         R, D = xp.shape
         E, Fd, _ = gate_w.shape
         dev = xp.device
@@ -138,15 +138,29 @@ class _LocalExpertsFn(torch.autograd.Function):
         hs = K.moe_row_scale(K.glu_fwd(g, u, kind), wrow)
         y = torch.empty((R, D), dtype=torch.bfloat16, device=dev)
         K.gemm_grouped(hs, down_w.view(E * D, Fd), y, D, t_down)
-        ctx.save_for_backward(xp, g, u, wrow, seg_off, gate_w, up_w, down_w)
-        ctx.kind = kind
+        # `recompute`: keep only the dispatched rows; gate / up are rebuilt in backward by two local grouped GEMMs.
+        # This is activation recomputation that stays on this rank: the rows are not exchanged a second time.
+        if recompute:
+            ctx.save_for_backward(xp, wrow, seg_off, gate_w, up_w, down_w)
+        else:
+            ctx.save_for_backward(xp, g, u, wrow, seg_off, gate_w, up_w, down_w)
+        ctx.kind, ctx.recompute = kind, recompute
         ctx.w_refs = (gate_w, up_w, down_w)
         return y
 
     @staticmethod
     @torch.autograd.function.once_differentiable      # the saved buffers are overwritten below: one backward per forward
     def backward(ctx, dy):
-        xp, g, u, wrow, seg_off, gate_w, up_w, down_w = ctx.saved_tensors
+        if ctx.recompute:
+            xp, wrow, seg_off, gate_w, up_w, down_w = ctx.saved_tensors
+            E, Fd, D = gate_w.shape
+            t_up = K.moe_tiles_rows(seg_off, xp.shape[0], Fd, D, Fd)
+            g = torch.empty((xp.shape[0], Fd), dtype=torch.bfloat16, device=xp.device)
+            u = torch.empty_like(g)
+            K.gemm_grouped(xp, gate_w.view(E * Fd, D), g, Fd, t_up)
+            K.gemm_grouped(xp, up_w.view(E * Fd, D), u, Fd, t_up)
+        else:
+            xp, g, u, wrow, seg_off, gate_w, up_w, down_w = ctx.saved_tensors
         E, Fd, D = gate_w.shape
         R, dev = xp.shape[0], dy.device
         dy = dy.contiguous()
@@ -181,10 +195,10 @@ class _LocalExpertsFn(torch.autograd.Function):
             dxp = xp
             K.gemm_grouped(dg, gate_w.view(E * Fd, D), dxp, D, t_dx, b_mn=True)
             K.gemm_grouped(du, up_w.view(E * Fd, D), dxp, D, t_dx, b_mn=True, accumulate=True)
-        return dxp, dwrow, None, None, d_gate, d_up, d_down, None
+        return dxp, dwrow, None, None, d_gate, d_up, d_down, None, None
 
 
-def local_experts(xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind: str = "silu"):
+def local_experts(xp, wrow, seg_off, counts, gate_w, up_w, down_w, kind: str = "silu", recompute: bool = False):
     """y[r] = wrow[r] * expert_of_segment(r)(xp[r]) for rows laid out in this rank's expert segments."""
     return _LocalExpertsFn.apply(xp, wrow.float().contiguous(), seg_off, counts, gate_w, up_w, down_w,
-                                 K.GLU_SILU if kind == "silu" else K.GLU_GELU)
+                                 K.GLU_SILU if kind == "silu" else K.GLU_GELU, recompute)

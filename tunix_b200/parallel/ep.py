@@ -117,7 +117,8 @@ class _Plan:
         T = WT // W
         E_loc = num_experts // W
         flat = idx_all.reshape(-1).long()
-        counts = torch.bincount(flat, minlength=num_experts)
+        # scatter-add, not bincount: bincount reads the largest id back to the host, a synchronisation per layer
+        counts = torch.zeros(num_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
         padded = (counts + 127) // 128 * 128
         pad2 = padded.view(W, E_loc)
         seg_start = (torch.cumsum(pad2, 1) - pad2).reshape(-1)            # row where an expert starts on its owner
@@ -236,8 +237,10 @@ def _reference_local_share(layer, x_all, w_all, idx_all, first_expert: int, n_lo
     return out
 
 
-def expert_parallel_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, residual=None):
-    """x [T, D] this rank's tokens; weights / idx [T, k] over ALL experts. Returns [T, D]."""
+def expert_parallel_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, residual=None,
+                            recompute: bool = False):
+    """x [T, D] this rank's tokens; weights / idx [T, k] over ALL experts. Returns [T, D]. `recompute`: keep the
+    dispatched rows and rebuild the experts' activations in backward on this rank (no second exchange)."""
     ep: EPContext = layer.ep
     W, r = ep.world, ep.rank
     E = layer.cfg.num_experts
@@ -257,7 +260,7 @@ def expert_parallel_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: 
     wrow = torch.zeros(plan.rows + 1, dtype=torch.float32, device=x.device).index_put((plan.own_dest,),
                                                                                          w_all.reshape(-1))[:plan.rows]
     y = moe_ops.local_experts(xp, wrow, plan.seg_off, plan.counts, layer.gate_proj, layer.up_proj, layer.down_proj,
-                              layer.cfg.activation)
+                              layer.cfg.activation, recompute=recompute)
     return _Combine.apply(y, residual, plan, ep)
 
 

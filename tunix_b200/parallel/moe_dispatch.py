@@ -32,11 +32,11 @@ def _experts_on_rows(layer, xs: torch.Tensor, counts, first_expert: int = 0) -> 
     return out
 
 
-def expert_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+def expert_forward(layer, x: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor, recompute: bool = False) -> torch.Tensor:
     """x [T, D]; weights, idx [T, k]. Returns sum_k w * expert_{idx}(x)  [T, D]."""
     if getattr(layer, "ep", None) is not None and layer.ep.world > 1:
         from . import ep
-        return ep.expert_parallel_forward(layer, x, weights, idx)
+        return ep.expert_parallel_forward(layer, x, weights, idx, recompute=recompute)
     T, D = x.shape
     k = idx.shape[1]
     E = layer.cfg.num_experts
