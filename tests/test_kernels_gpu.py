@@ -246,13 +246,120 @@ def test_fused_lm_head_logprobs_match_reference(rows, V, D, softcap, temp):
     assert torch.allclose(logp, ref_lp, atol=3e-2, rtol=2e-2), float((logp - ref_lp).abs().max())
     assert torch.allclose(ent, ref_ent, atol=3e-2, rtol=2e-2)
     g = torch.randn(rows, device="cuda")
-    (logp * g).sum().backward()
+    g2 = torch.randn(rows, device="cuda") * 0.3
+    ((logp * g).sum() + (ent * g2).sum()).backward()          # both gradient terms of the fused epilogue
     _check_status()
     hr = h.detach().float().requires_grad_()
     wr = w.detach().float().requires_grad_()
     zr = hr @ wr.t()
     if softcap:
         zr = softcap * torch.tanh(zr / softcap)
-    lp2 = torch.log_softmax(zr / temp, -1).gather(-1, tg.clamp(min=0)[:, None]).squeeze(-1)
-    (torch.where(tg >= 0, lp2, torch.zeros_like(lp2)) * g).sum().backward()
+    lsm = torch.log_softmax(zr / temp, -1)
+    lp2 = lsm.gather(-1, tg.clamp(min=0)[:, None]).squeeze(-1)
+    ent2 = -(lsm.exp() * lsm).sum(-1)
+    ((torch.where(tg >= 0, lp2, torch.zeros_like(lp2)) * g).sum() + (ent2 * g2).sum()).backward()
     assert _rel_err(h.grad, hr.grad) < 3e-2 and _rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("M,N,K,r", [(2048, 4096, 1024, 16), (2304, 2560, 520, 8), (4096, 2048, 2048, 64), (2048, 4096, 512, 72),
+                                     (128, 256, 64, 16)])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_with_second_segment(M, N, K, r, b_mn):
+    """A @ B^T + A2 @ B2^T in one launch (adapter rank r as extra k-blocks; the last shape falls back to two GEMMs)."""
+    k = _k()
+    torch.manual_seed(11)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    A2 = torch.randn(M, r, device="cuda", dtype=torch.bfloat16)
+    B2 = torch.randn(N, r, device="cuda", dtype=torch.bfloat16) * 4
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t() + A2.float() @ B2.float().t()
+    b, b2 = (B.t().contiguous(), B2.t().contiguous()) if b_mn else (B, B2)
+    out = k.gemm_ext(A, b, A2, b2, b_mn=b_mn)
+    _check_status()
+    assert _rel_err(out, ref) < 1e-2
+    # the low-rank part alone must be right too (it is small next to the main product)
+    low = out.float() - (A.float() @ B.float().t())
+    assert _rel_err(low, A2.float() @ B2.float().t()) < 0.2
+    out = k.gemm_ext(A, b, A2, b2, b_mn=b_mn, bias=bias, residual=res)
+    _check_status()
+    full = ref + bias.float() + res.float()
+    assert _rel_err(out, full) < 1e-2
+    assert torch.allclose(out.float(), full, atol=0.02 * full.abs().max().item(), rtol=2e-2)
+
+
+@pytest.mark.parametrize("with_bias,with_res", [(False, False), (True, True)])
+def test_lora_linear_matches_fp32(with_bias, with_res):
+    """Fused LoRA projection (forward, input gradient, adapter gradients) against fp32 PyTorch."""
+    from tunix_b200.ops import functional as F
+    torch.manual_seed(5)
+    M, D, O, r, s = 2048, 1024, 3072, 16, 2.0
+    x = (torch.randn(4, M // 4, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(O, D, device="cuda") * 0.05).to(torch.bfloat16)
+    a = (torch.randn(r, D, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    b = (torch.randn(O, r, device="cuda") * 0.2).to(torch.bfloat16).requires_grad_()
+    bias = (torch.randn(O, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_() if with_bias else None
+    res = (torch.randn(4, M // 4, O, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_() if with_res else None
+    y = F.lora_linear(x, w, bias, a, b, s, res)
+    g = torch.randn_like(y)
+    y.backward(g)
+    _check_status()
+    xf, af, bf = (t.detach().float().requires_grad_() for t in (x, a, b))
+    yf = xf @ w.float().t() + s * (xf @ af.t()) @ bf.t()
+    if with_bias:
+        yf = yf + bias.detach().float()
+    if with_res:
+        yf = yf + res.detach().float()
+    yf.backward(g.float())
+    assert _rel_err(y, yf) < 1e-2
+    assert _rel_err(x.grad, xf.grad) < 1e-2
+    assert _rel_err(a.grad, af.grad) < 2e-2
+    assert _rel_err(b.grad, bf.grad) < 2e-2
+    if with_res:
+        assert torch.equal(res.grad, g)
+    if with_bias:
+        assert _rel_err(bias.grad, g.float().sum((0, 1))) < 1e-2
+
+
+def test_qlora_linear_keeps_no_expanded_weight():
+    """A LoRA projection over an NF4 base: same values and gradients as the projection over the expanded weight, and
+    between forward and backward nothing of the size of the expanded weight stays allocated."""
+    from tunix_b200 import lora
+    from tunix_b200.models.transformer import Linear
+    torch.manual_seed(2)
+    D, O = 2048, 4096
+    lin = Linear(D, O, dtype=torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        lin.weight.normal_(0, 0.05)
+
+    class _M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj = lin
+
+    m = _M()
+    lora.apply_lora_to_model(m, lora.LoraProvider(rank=16, alpha=32.0, weight_qtype="nf4", module_path=".*proj"))
+    with torch.no_grad():
+        lin.lora_b.normal_(0, 0.05)
+    w_full = lin.quant.dequantize().float()
+    x = (torch.randn(2, 1024, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    y = lin(x)                                   # first call allocates the shared scratch
+    del y
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    y = lin(x)
+    torch.cuda.synchronize()
+    held = torch.cuda.memory_allocated() - before
+    weight_bytes = D * O * 2
+    # y itself (2 * 1024 * O * 2 bytes) plus the rank-16 intermediate, but no [O, D] bf16 tensor
+    assert held < 2 * 1024 * O * 2 + weight_bytes // 4, (held, weight_bytes)
+    g = torch.randn_like(y)
+    y.backward(g)
+    _check_status()
+    xf = x.detach().float().requires_grad_()
+    af, bf = lin.lora_a.detach().float().requires_grad_(), lin.lora_b.detach().float().requires_grad_()
+    yf = xf @ w_full.t() + lin.lora_scale * (xf @ af.t()) @ bf.t()
+    yf.backward(g.float())
+    assert _rel_err(y, yf) < 1e-2 and _rel_err(x.grad, xf.grad) < 1e-2
+    assert _rel_err(lin.lora_a.grad, af.grad) < 2e-2 and _rel_err(lin.lora_b.grad, bf.grad) < 2e-2

@@ -27,6 +27,7 @@ U = ctypes.c_uint
 
 _CUDA_SIGS = {
     "tb_gemm_bf16": [P, P, P, I, I, I, LL, LL, LL, I, P, P, LL, F, P, I, P],
+    "tb_gemm_bf16_ext": [P, P, P, I, I, I, LL, LL, LL, I, P, P, LL, F, P, P, I, LL, LL, P, P],
     "tb_tmap_cache_clear": [],
     "tb_rmsnorm_fwd": [P, LL, P, P, LL, P, I, I, F, F, P],
     "tb_rmsnorm_bwd": [P, LL, P, LL, P, P, P, LL, P, I, I, F, I, P],

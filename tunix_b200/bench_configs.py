@@ -236,7 +236,11 @@ def dpo(args) -> dict:
     pairs = max(args.pairs // world, 1)
     tc = DPOTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, beta=0.1, max_prompt_length=512, max_response_length=512,
                            pbar_description=None, gradient_accumulation_steps=max(pairs // args.micro, 1))
-    tr = DPOTrainer(model, None, optim.AdamW(5e-6), tc)
+    opt = optim.AdamW(5e-6)
+    if world > 1:          # data parallel: adapter gradients summed and the Adam state split over the ranks
+        from .parallel import fsdp
+        opt = fsdp.shard_optimizer(opt)
+    tr = DPOTrainer(model, None, opt, tc)
     g = torch.Generator().manual_seed(3 + rank)
     mb = min(args.micro, pairs)
 

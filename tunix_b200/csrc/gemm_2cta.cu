@@ -39,6 +39,9 @@ enum { GF_A_MN = 1, GF_B_MN = 2, GF_OUT_F32 = 4, GF_ACCUM = 8, GF_BIAS = 16, GF_
 
 struct Args2 {
   int M, N, K, flags;
+  // second contraction segment accumulated into the same TMEM tile: C += A2[M, K2] * B2[N, K2]^T with the layouts of
+  // A and B (a low-rank adapter update x A^T B^T carried by the base projection's GEMM); K2 = 0 when absent
+  int K2;
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
@@ -52,6 +55,14 @@ struct Args2 {
   const int* targets;
   float* partial;
   float inv_temp, softcap;
+  // logit-gradient epilogue (lm_head backward): the accumulator z is turned in registers into
+  //   dz = dlogp (1[j == target] - p_j) - dent p_j (z_j - lse + entropy),  p_j = exp(z_j - lse),
+  // chained through temperature and soft-cap, and written as bf16; the fp32 logits never reach memory.
+  // dz_lse != nullptr selects it; dz_dlogp / dz_dent / dz_ent may be null.
+  const float* dz_lse;
+  const float* dz_dlogp;
+  const float* dz_dent;
+  const float* dz_ent;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -102,7 +113,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
 }
 
 __global__ void __launch_bounds__(192, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Args2 args) {
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const Args2 args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -119,7 +131,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int M = args.M, N = args.N, K = args.K;
-  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN, num_kb = (K + BK - 1) / BK;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+  const int num_kb1 = (K + BK - 1) / BK;                         // k-blocks of the main operands ...
+  const int num_kb = num_kb1 + (args.K2 + BK - 1) / BK;          // ... followed by those of the second segment
   const int num_tiles = num_m * num_n;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const bool a_mn = args.flags & GF_A_MN, b_mn = args.flags & GF_B_MN;
@@ -135,6 +149,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
     *abort_flag = 0;
     mbar_fence_init();
+    if (args.K2 > 0) {
+      prefetch_tensormap(&tmA2);
+      prefetch_tensormap(&tmB2);
+    }
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
   }
@@ -176,18 +194,22 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           const uint32_t sb = sa + A_BYTES;
           const uint32_t fb = mapa_u32(full_bar(stage), 0);           // the leader's barrier for this stage
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-          const int k0 = kb * BK;
+          // the second segment's maps zero-fill past K2, so a rank below 64 costs one padded k-block
+          const bool seg2 = kb >= num_kb1;
+          const CUtensorMap* ta = seg2 ? &tmA2 : &tmA;
+          const CUtensorMap* tb_ = seg2 ? &tmB2 : &tmB;
+          const int k0 = (seg2 ? kb - num_kb1 : kb) * BK;
           if (!a_mn) {
-            tma2_load_2d(sa, &tmA, fb, k0, m0);
+            tma2_load_2d(sa, ta, fb, k0, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < HM / 64; ++j) tma2_load_2d(sa + j * 8192, &tmA, fb, m0 + 64 * j, k0);
+            for (int j = 0; j < HM / 64; ++j) tma2_load_2d(sa + j * 8192, ta, fb, m0 + 64 * j, k0);
           }
           if (!b_mn) {
-            tma2_load_2d(sb, &tmB, fb, k0, n0);
+            tma2_load_2d(sb, tb_, fb, k0, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < HN / 64; ++j) tma2_load_2d(sb + j * 8192, &tmB, fb, n0 + 64 * j, k0);
+            for (int j = 0; j < HN / 64; ++j) tma2_load_2d(sb + j * 8192, tb_, fb, n0 + 64 * j, k0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -244,11 +266,22 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
     const uint32_t tempty_leader0 = mapa_u32(tempty_bar(0), 0), tempty_leader1 = mapa_u32(tempty_bar(1), 0);
     const bool lse_mode = args.partial != nullptr;
+    const bool dz_mode = args.dz_lse != nullptr;
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mt, nt;
       tile_coords(t, mt, nt);
       const int row = mt * BM + (int)rank * HM + q * 32 + lane;
       const int n0 = nt * BN;
+      float dz_l = 0.f, dz_gl = 0.f, dz_ge = 0.f, dz_en = 0.f;
+      int dz_t = -1;
+      if (dz_mode && row < M) {
+        dz_l = args.dz_lse[row];
+        dz_ge = args.dz_dent ? args.dz_dent[row] : 0.f;
+        dz_en = (args.dz_dent && args.dz_ent) ? args.dz_ent[row] : 0.f;
+        dz_t = args.targets ? args.targets[row] : -1;
+        if (dz_t < 0 || dz_t >= N) dz_t = -1;
+        dz_gl = (dz_t >= 0 && args.dz_dlogp) ? args.dz_dlogp[row] : 0.f;
+      }
       if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, args.status, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
@@ -311,6 +344,22 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
           const bool full = (col0 + 32 <= N);
+          if (dz_mode) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float capped = v[i], chain = args.inv_temp;
+              if (args.softcap > 0.f) {
+                const float th = tanhf(v[i] / args.softcap);
+                capped = args.softcap * th;
+                chain *= (1.f - th * th);
+              }
+              const float z = capped * args.inv_temp;
+              const float p = __expf(z - dz_l);
+              float d = dz_gl * ((col0 + i == dz_t ? 1.f : 0.f) - p);
+              if (dz_ge != 0.f) d -= dz_ge * p * (z - dz_l + dz_en);
+              v[i] = d * chain;
+            }
+          }
           if (has_bias) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -403,6 +452,16 @@ struct LseArgs {           // log-softmax epilogue request; partial == nullptr f
   const int* targets = nullptr;
   float* partial = nullptr;
   float inv_temp = 1.f, softcap = 0.f;
+  const float* dz_lse = nullptr;       // logit-gradient epilogue when set
+  const float* dz_dlogp = nullptr;
+  const float* dz_dent = nullptr;
+  const float* dz_ent = nullptr;
+};
+struct Seg2 {              // second contraction segment; K2 == 0 when absent
+  const void* A2 = nullptr;
+  const void* B2 = nullptr;
+  int K2 = 0;
+  long long lda2 = 0, ldb2 = 0;
 };
 
 // partial [M, num_n, 4] -> logp[row] = z[target] - lse (0 for targets outside [0, V)), lse, entropy = lse - E[z]
@@ -446,7 +505,7 @@ __global__ void lse_combine_kernel(const float* __restrict__ partial, const int*
 namespace {
 int launch_2cta(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
                 int flags, const void* bias, const void* resid, long long ldr, float alpha, int* status,
-                cudaStream_t stream, const LseArgs& lse) {
+                cudaStream_t stream, const LseArgs& lse, const Seg2& seg = Seg2{}) {
   static const bool off = getenv("TUNIX_B200_NO_2CTA") != nullptr;
   if (off) return 0;
   static DeviceOnce once;
@@ -470,12 +529,26 @@ int launch_2cta(const void* A, const void* B, void* C, int M, int N, int K, long
   if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB, B, N, K, ldb, HN, BK, 1);
   else       r = tb_make_tmap_2d_bf16(&tmB, B, K, N, ldb, BK, 64, 1);
   if (r) return -4;
+  CUtensorMap tmA2 = tmA, tmB2 = tmB;
+  if (seg.K2 > 0) {
+    if ((seg.lda2 % 8) || (seg.ldb2 % 8) || (reinterpret_cast<uintptr_t>(seg.A2) & 15) ||
+        (reinterpret_cast<uintptr_t>(seg.B2) & 15))
+      return -2;
+    if (!a_mn) r = tb_make_tmap_2d_bf16(&tmA2, seg.A2, M, seg.K2, seg.lda2, HM, BK, 1);
+    else       r = tb_make_tmap_2d_bf16(&tmA2, seg.A2, seg.K2, M, seg.lda2, BK, 64, 1);
+    if (r) return -3;
+    if (!b_mn) r = tb_make_tmap_2d_bf16(&tmB2, seg.B2, N, seg.K2, seg.ldb2, HN, BK, 1);
+    else       r = tb_make_tmap_2d_bf16(&tmB2, seg.B2, seg.K2, N, seg.ldb2, BK, 64, 1);
+    if (r) return -4;
+  }
   Args2 a;
+  a.K2 = seg.K2;
   a.M = M; a.N = N; a.K = K; a.flags = flags; a.C = C; a.ldc = ldc;
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   a.ldr = ldr; a.alpha = alpha; a.status = status;
   a.targets = lse.targets; a.partial = lse.partial; a.inv_temp = lse.inv_temp; a.softcap = lse.softcap;
+  a.dz_lse = lse.dz_lse; a.dz_dlogp = lse.dz_dlogp; a.dz_dent = lse.dz_dent; a.dz_ent = lse.dz_ent;
   const int tiles = num_m * num_n;
   const int use_pairs = tiles < pairs ? tiles : pairs;
   cudaLaunchConfig_t cfg = {};
@@ -490,7 +563,7 @@ int launch_2cta(const void* A, const void* B, void* C, int M, int N, int K, long
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm2_kernel, tmA, tmB, a) != cudaSuccess) return -5;
+  if (cudaLaunchKernelEx(&cfg, gemm2_kernel, tmA, tmB, tmA2, tmB2, a) != cudaSuccess) return -5;
   return 1;
 }
 }  // namespace
@@ -500,6 +573,23 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
                      long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
                      int* status, cudaStream_t stream) {
   return launch_2cta(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream, LseArgs{});
+}
+
+// C = epilogue(A * B^T + A2 * B2^T): the base projection with a low-rank update accumulated into the same TMEM tile
+// (A2 [M, K2] or [K2, M], B2 [N, K2] or [K2, N], laid out like A and B; K2 is the adapter rank, any multiple of 8).
+// Returns 1 when launched, 0 when the problem is too small for the two-SM kernel (the caller then runs the two
+// products separately), negative on error.
+TB_API int tb_gemm_bf16_ext(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                            long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                            const void* A2, const void* B2, int K2, long long lda2, long long ldb2, int* status,
+                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K2 <= 0 || (K2 % 8) || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  Seg2 seg;
+  seg.A2 = A2; seg.B2 = B2; seg.K2 = K2; seg.lda2 = lda2; seg.ldb2 = ldb2;
+  return launch_2cta(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream, LseArgs{}, seg);
 }
 
 // log p(target) (and optionally lse / entropy) of z = softcap(h W^T) / temperature without materialising z:
@@ -517,4 +607,19 @@ TB_API int tb_lm_head_lse(const void* h, long long ldh, const void* w, long long
   const int num_n = (V + BN - 1) / BN;
   lse_combine_kernel<<<(M + 7) / 8, 256, 0, stream>>>(partial, targets, M, num_n, V, logp, lse, entropy);
   return cudaGetLastError() == cudaSuccess ? 1 : -5;
+}
+
+// dz [M, V] (bf16, row stride ldo) = gradient of sum_rows(dlogp * logp + dent * entropy) with respect to the raw
+// logits h W^T, computed in the epilogue of the two-SM GEMM that recomputes those logits: lse (and entropy, when dent
+// is given) are the row statistics saved by the forward pass. dlogp / dent / entropy may be null. Returns 1 when run
+// here, 0 when the problem does not qualify for the two-SM kernel, negative on error.
+TB_API int tb_lm_head_dlogits(const void* h, long long ldh, const void* w, long long ldw, int M, int V, int K,
+                              const int* targets, const float* lse, const float* entropy, const float* dlogp,
+                              const float* dent, float inv_temp, float softcap, void* out, long long ldo, int* status,
+                              cudaStream_t stream) {
+  if (!lse || !out) return -2;
+  LseArgs e;
+  e.targets = targets; e.inv_temp = inv_temp; e.softcap = softcap;
+  e.dz_lse = lse; e.dz_dlogp = dlogp; e.dz_dent = dent; e.dz_ent = entropy;
+  return launch_2cta(h, w, out, M, V, K, ldh, ldw, ldo, 0, nullptr, nullptr, 0, 1.0f, status, stream, e);
 }

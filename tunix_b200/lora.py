@@ -42,6 +42,9 @@ class LoraProvider:
     dropout: float = 0.0
 
 
+_DEQUANT_SCRATCH: dict = {}      # (shape, device) -> bf16 tensor, see NF4Weight.dequantize(shared=True)
+
+
 class NF4Weight:
     """Block-wise 4-bit NormalFloat storage of a frozen weight: two codes per byte + fp32 absmax per block."""
 
@@ -59,14 +62,23 @@ class NF4Weight:
         self.packed = (idx[0::2] << 4) | idx[1::2]
         self.numel = w.numel()
 
-    def dequantize(self) -> torch.Tensor:
+    def dequantize(self, shared: bool = False) -> torch.Tensor:
+        """The bf16 (or original dtype) weight. `shared`: write into a scratch tensor that every NF4 weight of this
+        shape on this device reuses: valid until the next such call, for consumers that run on the same stream
+        right away (a projection's GEMMs); the expanded weight then never outlives the layer that uses it."""
         if self.packed.is_cuda and self.dtype == torch.bfloat16:
             # one kernel: codebook lookup, block scale, bf16 store (csrc/optim.cu)
             from . import _lib
             _lib.register_cuda_sigs({"tb_nf4_dequant": [_lib.P, _lib.P, _lib.I, _lib.P, _lib.LL, _lib.P]})
             if self.packed.numel() % 8:
                 self.packed = torch.cat([self.packed, self.packed.new_zeros(8 - self.packed.numel() % 8)])
-            out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.packed.device)
+            if shared:
+                key = (self.shape, self.packed.device)
+                out = _DEQUANT_SCRATCH.get(key)
+                if out is None:
+                    out = _DEQUANT_SCRATCH[key] = torch.empty(self.shape, dtype=torch.bfloat16, device=self.packed.device)
+            else:
+                out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.packed.device)
             rc = _lib.cuda().tb_nf4_dequant(self.packed.data_ptr(), self.absmax.data_ptr(), self.block, out.data_ptr(),
                                             self.numel, _lib.stream_ptr())
             _lib.check(rc, "tb_nf4_dequant")

@@ -26,6 +26,55 @@ from ..ops import reference as R
 from .config import ModelConfig, RematConfig
 
 
+class _JointRowsFn(torch.autograd.Function):
+    """Parameters that lie back to back in one storage, seen as one tensor without a copy; the gradient of the joint
+    tensor is handed back as row slices."""
+
+    @staticmethod
+    def forward(ctx, joint, *parts):
+        ctx.rows = [p.shape[0] for p in parts]
+        ctx.set_materialize_grads(False)
+        return joint.view_as(joint)
+
+    @staticmethod
+    def backward(ctx, g):
+        if g is None:                  # the consumer added the gradient into the joint `main_grad` itself
+            return (None,) * (1 + len(ctx.rows))
+        return (None, *g.split(ctx.rows, 0))
+
+
+def _joint_rows(parts):
+    """cat(parts, 0) for tensors of equal trailing shape: a view when they already follow each other in memory (the
+    optimizers' flat parameter buffers lay q / k / v weights out that way), a copy otherwise."""
+    first = parts[0]
+    off, adjacent = first.storage_offset(), all(p.is_contiguous() for p in parts)
+    for p in parts:
+        if not adjacent or p.untyped_storage().data_ptr() != first.untyped_storage().data_ptr() or p.storage_offset() != off \
+                or p.shape[1:] != first.shape[1:]:
+            adjacent = False
+            break
+        off += p.numel()
+    if not adjacent:
+        return torch.cat(list(parts), 0)
+    rows = sum(p.shape[0] for p in parts)
+    joint = first.detach().as_strided((rows, *first.shape[1:]), first.stride(), first.storage_offset())
+    if torch.is_grad_enabled() and any(p.requires_grad for p in parts):
+        out = _JointRowsFn.apply(joint, *parts)
+        mgs = [getattr(p, "main_grad", None) for p in parts]
+        if all(m is not None for m in mgs):
+            # gradient slots that follow each other as well: consumers accumulate straight into the joint slot
+            m0, moff, ok = mgs[0], mgs[0].storage_offset(), True
+            for m, p_ in zip(mgs, parts):
+                ok = ok and m.is_contiguous() and m.untyped_storage().data_ptr() == m0.untyped_storage().data_ptr() \
+                    and m.storage_offset() == moff and m.shape == p_.shape
+                moff += m.numel()
+            if ok:
+                out.main_grad = m0.as_strided((rows, *m0.shape[1:]), m0.stride(), m0.storage_offset())
+                out._joint_parts = list(parts)
+        return out
+    return joint
+
+
 class Linear(nn.Module):
     """Linear layer with optional bias, LoRA adapters and NF4-quantised frozen base (QLoRA)."""
 
@@ -55,12 +104,15 @@ class Linear(nn.Module):
                 y = F.lora_delta(x, self.lora_a, self.lora_b, y, self.lora_scale)
                 return y if residual is None else y + residual
             return y
-        w = self.base_weight()
         if self.lora_a is not None and self.lora_enabled:
-            y = F.linear(x, w, self.bias)
-            y = F.lora_delta(x, self.lora_a, self.lora_b, y, self.lora_scale)
-            return y if residual is None else y + residual
-        return F.linear(x, w, self.bias, residual)
+            # a quantised base is expanded inside the function (forward and again in backward) into a scratch that
+            # all layers share, so no expanded weight is kept for the backward pass
+            w = self.weight if self.quant is None else None
+            return F.lora_linear(x, w, self.bias, self.lora_a, self.lora_b, self.lora_scale, residual, quant=self.quant)
+        if self.quant is not None:
+            keeps = torch.is_grad_enabled() and x.requires_grad          # autograd would hold on to the scratch
+            return F.linear(x, self.quant.dequantize(shared=not keeps), self.bias, residual)
+        return F.linear(x, self.weight, self.bias, residual)
 
 
 class RMSNorm(nn.Module):
@@ -103,8 +155,8 @@ class Attention(nn.Module):
             projs = (self.q_proj, self.k_proj, self.v_proj)
             if any(p.lora_a is not None or p.quant is not None for p in projs) or cache is not None:
                 raise NotImplementedError("tensor parallelism covers full-weight training without a KV cache")
-            w = torch.cat([p.weight for p in projs], 0)
-            b = torch.cat([p.bias for p in projs], 0) if self.q_proj.bias is not None else None
+            w = _joint_rows([p.weight for p in projs])
+            b = _joint_rows([p.bias for p in projs]) if self.q_proj.bias is not None else None
             qkv = tp_lib.column_parallel_linear(x, w, b, tp)
             B, N, K = qkv.shape[0], N // tp.world, K // tp.world
             q, k, v = qkv.split([N * H, K * H, K * H], dim=-1)

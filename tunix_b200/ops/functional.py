@@ -140,6 +140,66 @@ class _LoraDeltaFn(torch.autograd.Function):
         return dx, _deliver_grad(ctx.a_ref, da), _deliver_grad(ctx.b_ref, db), dy, None
 
 
+class _LoraLinearFn(torch.autograd.Function):
+    """y = x W^T + scale * (x A^T) B^T (+ bias) (+ residual) with the adapter product carried by the base GEMM: the
+    rank-r intermediate t = scale * x A^T is a second contraction segment of the same launch (forward) and so is
+    dt = scale * dy B in the input gradient dx = dy W + dt A. The [M, out] base output is never written and re-read."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, a, b, scale, residual, quant):
+        x2 = _flat2d(x)
+        r2 = _flat2d(residual) if residual is not None else None
+        w_ref = w
+        if quant is not None:
+            w = quant.dequantize(shared=True)                # consumed by the GEMM below, not kept
+        t = K.gemm(x2, a, alpha=scale)                       # [M, r]
+        y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+        K.gemm_ext(x2, w, t, b, out=y.view(-1, w.shape[0]), bias=bias, residual=r2)
+        ctx.save_for_backward(x2, None if quant is not None else w, a, b, t)
+        ctx.scale, ctx.x_shape, ctx.quant = scale, x.shape, quant
+        ctx.refs = (w_ref, bias, a, b)
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, a, b, t = ctx.saved_tensors
+        w_ref, bias_ref, a_ref, b_ref = ctx.refs
+        dy2 = _flat2d(dy)
+        if ctx.quant is not None and ctx.needs_input_grad[0]:
+            w = ctx.quant.dequantize(shared=True)            # expanded again for the input gradient
+        dt = K.gemm(dy2, b, b_mn=True, alpha=ctx.scale)      # [M, r] = scale * dy B
+        db = K.gemm(dy2, t, a_mn=True, b_mn=True)            # [out, r] (t carries the scale)
+        da = K.gemm(dt, x2, a_mn=True, b_mn=True)            # [r, in]
+        dx = dw = dbias = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm_ext(dy2, w, dt, a, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w_ref, "main_grad", None)
+            if mg is not None:
+                K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                w_ref.grad_added_to_main_grad = True
+            else:
+                dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)
+        if bias_ref is not None and ctx.needs_input_grad[2]:
+            dbias = _deliver_grad(bias_ref, dy2.float().sum(0).to(dy.dtype))
+        return dx, dw, dbias, _deliver_grad(a_ref, da), _deliver_grad(b_ref, db), None, dy if ctx.has_res else None, None
+
+
+def lora_linear(x, w, bias, a, b, scale: float, residual=None, quant=None):
+    """x W^T + scale * x A^T B^T (+ bias) (+ residual); w [out, in], a [r, in], b [out, r]. `quant`: the base weight as
+    a 4-bit object with `dequantize(shared=...)` instead of `w` (QLoRA): it is expanded for the forward GEMM and again
+    for the input-gradient GEMM, never stored in expanded form."""
+    r = a.shape[0]
+    w_dtype = w.dtype if w is not None else quant.dtype
+    if _native(x) and w_dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and r % 8 == 0 and x.shape[-1] % 8 == 0:
+        return _LoraLinearFn.apply(x, w, bias, a, b, float(scale), residual, quant)
+    if w is None:
+        w = quant.dequantize()
+    y = lora_delta(x, a, b, linear(x, w, bias), scale)
+    return y if residual is None else y + residual
+
+
 def lora_delta(x, a, b, base, scale: float):
     """base + scale * x A^T B^T (LoRA update added to an already computed projection)."""
     r = a.shape[0]
@@ -316,7 +376,9 @@ def embedding(ids, table, scale: float = 1.0):
 
 # ---------------------------------------------------------------- lm_head log-probs
 class _LmHeadLogprobFn(torch.autograd.Function):
-    """Chunked lm_head -> log-softmax -> gather. Only [chunk, V] logits ever exist."""
+    """lm_head -> log-softmax -> gather without logits in memory: the forward keeps per-row statistics only, the
+    backward recomputes the logits chunk by chunk and holds a bf16 [chunk, V] gradient between its GEMMs. Problems too
+    small for the two-SM GEMM use an fp32 [chunk, V] logits buffer instead."""
 
     @staticmethod
     def forward(ctx, h, w, targets, softcap, temperature, want_entropy, chunk):
@@ -361,16 +423,21 @@ class _LmHeadLogprobFn(torch.autograd.Function):
         dw = None
         if need_dw and mg is None:
             dw = torch.zeros((V, h2.shape[1]), dtype=torch.float32, device=h2.device)
-        zbuf = torch.empty((min(chunk, max(rows, 1)), V), dtype=torch.float32, device=h2.device)
+        zbuf = None
         dbuf = torch.empty((min(chunk, max(rows, 1)), V), dtype=torch.bfloat16, device=h2.device)
         for s0 in range(0, rows, chunk):
             n = min(chunk, rows - s0)
-            z = zbuf[:n]
-            K.gemm(h2[s0:s0 + n], w, out=z)
-            dz = K.dlogits(z, tg[s0:s0 + n], lse[s0:s0 + n], ent[s0:s0 + n] if ent is not None else None,
-                           dlogp[s0:s0 + n] if dlogp is not None else None,
-                           dent[s0:s0 + n] if dent is not None else None,
-                           softcap=softcap, temperature=temperature, out=dbuf[:n])
+            sl = slice(s0, s0 + n)
+            row_args = (tg[sl], lse[sl], ent[sl] if ent is not None else None, dlogp[sl] if dlogp is not None else None,
+                        dent[sl] if dent is not None else None)
+            dz = dbuf[:n]
+            # the GEMM that recomputes the chunk's logits turns them into their gradient in its epilogue
+            if not K.lm_head_dlogits(h2[sl], w, *row_args, softcap=softcap, temperature=temperature, out=dz):
+                if zbuf is None:
+                    zbuf = torch.empty((min(chunk, max(rows, 1)), V), dtype=torch.float32, device=h2.device)
+                z = zbuf[:n]
+                K.gemm(h2[sl], w, out=z)
+                K.dlogits(z, *row_args, softcap=softcap, temperature=temperature, out=dz)
             if need_dh:
                 K.gemm(dz, w, b_mn=True, out=dh[s0:s0 + n])
             if need_dw:

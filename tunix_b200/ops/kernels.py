@@ -641,7 +641,33 @@ def gae_scan(rewards, values, mask, gamma: float, lam: float):
 _lib.register_cuda_sigs({
     "tb_lm_head_lse": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P,
                        _lib.P, _lib.P, _lib.P],
+    "tb_lm_head_dlogits": [_lib.P, _lib.LL, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P,
+                           _lib.F, _lib.F, _lib.P, _lib.LL, _lib.P, _lib.P],
 })
+
+
+def lm_head_dlogits(h2: torch.Tensor, w: torch.Tensor, targets, lse, entropy, dlogp, dent, *, softcap: float,
+                    temperature: float, out: torch.Tensor) -> bool:
+    """out [rows, V] bf16 = gradient with respect to the raw logits h W^T of sum(dlogp * logp + dent * entropy), from
+    the epilogue of the GEMM that recomputes the logits (no fp32 logits in memory). Returns False when the problem is
+    too small for the two-SM kernel; the caller then recomputes logits into a buffer and runs `dlogits`."""
+    import os
+    if os.environ.get("TUNIX_B200_NO_FUSED_LSE"):
+        return False
+    rows, Kd = h2.shape
+    V = w.shape[0]
+    if rows < 256 or not (_is2d_rowmajor(h2) and _is2d_rowmajor(w)) or h2.stride(0) % 8 or w.stride(0) % 8:
+        return False
+    assert out.dtype == torch.bfloat16 and out.shape == (rows, V) and out.stride(1) == 1
+    rc = _lib.cuda().tb_lm_head_dlogits(h2.data_ptr(), h2.stride(0), w.data_ptr(), w.stride(0), rows, V, Kd,
+                                        _lib.ptr(targets), lse.data_ptr(), _lib.ptr(entropy), _lib.ptr(dlogp),
+                                        _lib.ptr(dent), 1.0 / float(temperature), float(softcap or 0.0), out.data_ptr(),
+                                        out.stride(0), _lib.status_buffer().data_ptr(), _lib.stream_ptr())
+    if rc < 0:
+        _lib.check(rc, "tb_lm_head_dlogits")
+    if rc == 1:
+        _count()
+    return rc == 1
 
 
 def lm_head_lse(h2: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, *, softcap: float, temperature: float,

@@ -212,6 +212,8 @@ def _wgrad_into(w_ref, compute):
     if mg is not None:
         compute(mg, True)
         w_ref.grad_added_to_main_grad = True
+        for part in getattr(w_ref, "_joint_parts", ()):      # a joint view over several parameters' slots
+            part.grad_added_to_main_grad = True
         return None
     return compute(None, False)
 
