@@ -189,6 +189,12 @@ class Attention(nn.Module):
             seg_q = seg_k[:, end:new_end]
             q_off = end
             new_cache = {"k": ck, "v": cv, "seg": cseg, "end": new_end}
+        cp = getattr(self, "cp", None)
+        if cp is not None and cp.world > 1:
+            # context parallel: x holds this rank's tokens; keys and values of all earlier tokens come from the group
+            if cache is not None or attention_mask is not None:
+                raise NotImplementedError("context parallelism covers training without a KV cache or dense mask")
+            k, v, seg_k, q_off = cp.keys_for_local_queries(k, v, segment_ids)
         if attention_mask is not None:
             o = R.attention_ref(q, k, v, scale=self.scale, softcap=cfg.attn_logit_softcap,
                                 mask=attention_mask[:, None] if attention_mask.dim() == 3 else attention_mask)
@@ -340,6 +346,7 @@ class Transformer(nn.Module):
             torch.empty(cfg.vocab_size, cfg.embed_dim, dtype=dt, device=device))
         self._rope_cache: dict = {}
         self.tp = None  # parallel.tp.TPContext once apply_tensor_parallel has sliced the weights
+        self.cp = None  # parallel.cp.ContextParallel once apply_context_parallel has split the sequence axis
 
     # ------------------------------------------------------------------ weights
     @torch.no_grad()
@@ -389,6 +396,14 @@ class Transformer(nn.Module):
                 raise ValueError("tensor parallelism needs the batch divisible by tp and no KV cache")
             n = B // self.tp.world
             emb_tokens = input_tokens[self.tp.rank * n:(self.tp.rank + 1) * n]
+        cp = getattr(self, "cp", None)
+        if cp is not None and cp.world > 1:
+            # context parallel: every rank of the group got the same batch and keeps its slice of the sequence axis
+            if positions is None:
+                positions = torch.arange(T, device=input_tokens.device, dtype=torch.int32)[None].expand(B, T)
+            emb_tokens, positions, segment_ids = cp.slice_seq(input_tokens), cp.slice_seq(positions), cp.slice_seq(segment_ids)
+            routed_experts = cp.slice_seq(routed_experts)
+            T = cp.local_len(T)
         x = F.embedding(emb_tokens, self.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         return self.forward_embeddings(x, positions=positions, cache=cache, attention_mask=attention_mask,
                                        segment_ids=segment_ids, skip_lm_head=skip_lm_head,

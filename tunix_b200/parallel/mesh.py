@@ -67,6 +67,10 @@ class Mesh:
                 g = dist.new_group(members) if len(members) > 1 else None
                 if self.rank in members:
                     self._groups[name] = (g, members)
+        members = [int(r) for r in self.devices.reshape(-1)]
+        whole = None if members == list(range(self.world)) else dist.new_group(members)     # None = the default group
+        if self.rank in members:
+            self._groups["__all__"] = (whole, members)
 
     def axis_size(self, name: str) -> int:
         return self.shape[self.axis_names.index(name)] if name in self.axis_names else 1
@@ -78,6 +82,10 @@ class Mesh:
 
     def group(self, name: str):
         return self._groups.get(name, (None, [self.rank]))[0]
+
+    def all_group(self):
+        """Process group of every rank of the mesh (None when that is the default group)."""
+        return self._groups.get("__all__", (None, [self.rank]))[0]
 
     def group_ranks(self, name: str) -> list:
         return self._groups.get(name, (None, [self.rank]))[1]

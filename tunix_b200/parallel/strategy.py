@@ -11,6 +11,9 @@ tunix/cli/config.py). Here the axes select one of the explicit strategies of thi
     ('fsdp', 'tp')       N x T      tensor parallel inside each group of T adjacent ranks; the N groups are data
                                     parallel replicas whose gradients are summed over the `fsdp` axis before the
                                     update (optimizer state is not sharded in this combination)
+    ('sp',) / ('fsdp', 'sp')        context parallel over `sp` (`parallel/cp.py`: every rank of an `sp` group keeps
+                                    a slice of the sequence axis, attention gathers K / V over the group); the
+                                    weights are whole on every rank and the optimizer is ZeRO-2 over all ranks
 
 `apply_parallelism` is what the CLI entry points and `RLCluster` call; it returns the (possibly new) optimizer and
 a short description for logs.
@@ -26,23 +29,29 @@ import torch.distributed as dist
 
 @dataclasses.dataclass
 class ParallelPlan:
-    kind: str                      # single | zero2 | zero3 | tp | dp_tp
+    kind: str                      # single | zero2 | zero3 | tp | dp_tp | sp
     fsdp: int = 1
     tp: int = 1
+    sp: int = 1
     dp_group: object = None        # gradients are summed over it before the update (dp_tp only)
 
     def describe(self) -> str:
         return {"single": "single rank", "zero2": f"zero2 over {self.fsdp} ranks", "zero3": f"zero3 over {self.fsdp} ranks",
-                "tp": f"tp{self.tp}", "dp_tp": f"dp{self.fsdp} x tp{self.tp}"}[self.kind]
+                "tp": f"tp{self.tp}", "dp_tp": f"dp{self.fsdp} x tp{self.tp}",
+                "sp": f"zero2 over {self.fsdp * self.sp} ranks, sequence over {self.sp}"}[self.kind]
 
 
 def plan_for(mesh, shard_weights: bool = False) -> ParallelPlan:
     if mesh is None or mesh.size <= 1:
         return ParallelPlan("single")
-    fsdp, tp = mesh.axis_size("fsdp"), mesh.axis_size("tp")
-    other = [n for n in mesh.axis_names if n not in ("fsdp", "tp") and mesh.axis_size(n) > 1]
+    fsdp, tp, sp = mesh.axis_size("fsdp"), mesh.axis_size("tp"), mesh.axis_size("sp")
+    other = [n for n in mesh.axis_names if n not in ("fsdp", "tp", "sp") and mesh.axis_size(n) > 1]
     if other:
-        raise ValueError(f"mesh axes {other} have no strategy here; use 'fsdp' and / or 'tp'")
+        raise ValueError(f"mesh axes {other} have no strategy here; use 'fsdp', 'tp' and / or 'sp'")
+    if sp > 1:
+        if tp > 1 or shard_weights:
+            raise ValueError("context parallelism ('sp') combines with 'fsdp' (zero2) only")
+        return ParallelPlan("sp", fsdp, 1, sp)
     if tp > 1 and fsdp > 1:
         if shard_weights:
             raise ValueError("weight sharding (zero3) and tensor parallelism are not combined; drop one of them")
@@ -58,7 +67,13 @@ def apply_parallelism(model, optimizer, mesh, shard_weights: bool = False, devic
     if plan.kind == "single" or not dist.is_initialized():
         return optimizer, plan
     device = device or next(model.parameters()).device
-    if plan.tp > 1:
+    if plan.kind == "sp":
+        from . import cp, fsdp
+        cp.apply_context_parallel(model, mesh.group("sp"))
+        if optimizer is not None:
+            comm = "p2p" if torch.device(device).type == "cuda" else "nccl"
+            optimizer = fsdp.shard_optimizer(optimizer, mesh.all_group(), comm=comm)
+    elif plan.tp > 1:
         from . import tp as tp_lib
         tp_lib.apply_tensor_parallel(model, tp_lib.TPContext(group=mesh.group("tp"), device=device))
         if plan.kind == "dp_tp":

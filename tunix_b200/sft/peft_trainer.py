@@ -76,9 +76,16 @@ def _default_loss_fn(model, input_tokens, input_mask, positions=None, attention_
         hidden, _ = model(input_tokens, positions=positions, attention_mask=attention_mask, segment_ids=segment_ids,
                           skip_lm_head=True)
     from ..parallel.tp import local_batch   # under tensor parallelism `hidden` covers this rank's sequences only
-    targets = local_batch(model, input_tokens)[:, 1:]
-    mask = local_batch(model, input_mask)[:, 1:].to(torch.float32)
-    logp, _ = model.token_logprobs(hidden[:, :-1], targets)
+    cp = getattr(model, "cp", None)
+    if cp is not None and cp.world > 1:
+        # context parallel: `hidden` covers this rank's tokens; targets are shifted over the full sequence first
+        targets, mask = cp.shift_and_slice(input_tokens, input_mask)
+        mask = mask.to(torch.float32)
+        logp, _ = model.token_logprobs(hidden, targets)
+    else:
+        targets = local_batch(model, input_tokens)[:, 1:]
+        mask = local_batch(model, input_mask)[:, 1:].to(torch.float32)
+        logp, _ = model.token_logprobs(hidden[:, :-1], targets)
     nll_sum = -(logp * mask).sum()
     aux = model.aux_loss() if hasattr(model, "aux_loss") else None
     if aux is not None:
@@ -371,8 +378,10 @@ class PeftTrainer:
         return None if buf is None else buf.loss
 
     def _shard_and_move(self, batch):
-        tp = getattr(self.model, "tp", None)
-        batch = sharding_utils.shard_input(batch, self.config.data_sharding_axis, model_parallel=tp.world if tp else 1)
+        tp, cp = getattr(self.model, "tp", None), getattr(self.model, "cp", None)
+        # ranks of one tensor- or context-parallel group work on the same sequences
+        batch = sharding_utils.shard_input(batch, self.config.data_sharding_axis,
+                                           model_parallel=(tp.world if tp else 1) * (cp.world if cp else 1))
         if dataclasses.is_dataclass(batch) and not isinstance(batch, type):
             return dataclasses.replace(batch, **{f.name: _to_device(getattr(batch, f.name), self.device)
                                                  for f in dataclasses.fields(batch)})
