@@ -151,3 +151,82 @@ def test_checkpoint_of_a_tp_sliced_model_holds_whole_tensors_and_restores_each_s
     md = json.load(open(os.path.join(root, "2", "model_params", "_METADATA")))["tree_metadata"]
     assert "('layers', '0', 'self_attn', 'q_proj', 'weight')" in md
     assert sorted(d for d in os.listdir(root) if not d.isdigit()) == []   # no temporary directory left behind
+
+
+def _run_lora(rank, world, port, out, lora_first):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200 import lora, optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.parallel import tp as tp_lib
+    from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig.tiny_llama().replace(num_layers=2, vocab_size=256, embed_dim=64, hidden_dim=128, num_heads=4,
+                                           head_dim=16, num_kv_heads=2)
+    model = create_model(cfg, seed=0)
+    prov = lora.LoraProvider(rank=4, alpha=8.0)
+
+    def nonzero_b(m):            # a zero B would leave A without gradient in the first step
+        g = torch.Generator().manual_seed(11)
+        with torch.no_grad():
+            for n, p in sorted(m.named_parameters()):
+                if n.endswith("lora_b"):
+                    p.copy_(torch.randn(p.shape, generator=g) * 0.05)
+
+    if world == 1:
+        lora.apply_lora_to_model(model, prov, seed=3)
+        nonzero_b(model)
+    elif lora_first:
+        lora.apply_lora_to_model(model, prov, seed=3)
+        nonzero_b(model)
+        tp_lib.apply_tensor_parallel(model, tp_lib.TPContext(device="cpu"))
+    else:
+        tp_lib.apply_tensor_parallel(model, tp_lib.TPContext(device="cpu"))
+        lora.apply_lora_to_model(model, prov, seed=3)
+        # the same B values as the unsplit model: draw the full matrices, keep this rank's rows of the column-split ones
+        g = torch.Generator().manual_seed(11)
+        with torch.no_grad():
+            for n, p in sorted(model.named_parameters()):
+                if n.endswith("lora_b"):
+                    col = any(k in n for k in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"))
+                    full = torch.randn((p.shape[0] * (world if col else 1), p.shape[1]), generator=g) * 0.05
+                    p.copy_(full[rank * p.shape[0]:(rank + 1) * p.shape[0]] if col else full)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, 256, (4, 24), generator=g)
+    mask = torch.ones(4, 24)
+    mask[1, :7] = 0
+    tr = PeftTrainer(model, optim.AdamW(1e-2, max_grad_norm=0.5),
+                     TrainingConfig(eval_every_n_steps=1000, max_steps=3, pbar_description=None))
+    tr.train([TrainingInput(toks, mask)] * 3)
+    torch.save({n: p.detach().clone() for n, p in model.named_parameters() if "lora_" in n}, f"{out}.{rank}")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _check_lora(one, parts):
+    col, row = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"), ("o_proj", "down_proj")
+    assert one and set(one) == set(parts[0])
+    for n, w in one.items():
+        if n.endswith("lora_b") and any(k in n for k in col):
+            got = torch.cat([p[n] for p in parts], 0)
+        elif n.endswith("lora_a") and any(k in n for k in row):
+            got = torch.cat([p[n] for p in parts], 1)
+        else:
+            assert torch.allclose(parts[0][n], parts[1][n], atol=1e-6), n
+            got = parts[0][n]
+        assert torch.allclose(got, w, atol=3e-5, rtol=1e-4), (n, (got - w).abs().max())
+
+
+def test_tp2_lora_training_matches_single_process(tmp_path):
+    """Adapters under tensor parallelism, attached before or after the split: the trained adapters equal the unsplit run."""
+    base = str(tmp_path / "one")
+    _run_lora(0, 1, 0, base, True)
+    one = torch.load(base + ".0")
+    for i, lora_first in enumerate((True, False)):
+        out = str(tmp_path / f"two{i}")
+        mp.spawn(_run_lora, args=(2, 29745 + 2 * i, out, lora_first), nprocs=2, join=True)
+        _check_lora(one, [torch.load(out + f".{r}") for r in range(2)])

@@ -31,6 +31,7 @@ struct BwdArgs {
   int B, Tq, Tk, N, KH;
   float scale, softcap;
   int causal, window, q_off;
+  int dbg;              // TEMPORARY timing probe: bit 0 = skip the dQ atomics
   const int* seg_q;
   const int* seg_k;
   const float* lse;     // [B, N, Tq]
@@ -75,12 +76,16 @@ struct BwdCfg {
 // Schedule (PIPE): while the row threads work on query tile `it` (P, then dS), the tensor core already
 // holds St/dPt of tile it+1 (issued at mid-iteration) and finishes dV/dK/dQt of tile it-1; the dQt of
 // tile it-1 is drained between the two phases of tile it. Handoffs never wait on a just-issued MMA.
-template <int H>
-__global__ void __launch_bounds__(160, 1)
+// RG_: row-thread groups. The BQ_ query columns of a key row are split over RG_ threads (one per warpgroup), so the
+// element-wise work between the MMAs runs on 128 * RG_ threads.
+template <int H, int RG_>
+__global__ void __maxnreg__(RG_ == 2 ? 224 : 255)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const BwdArgs a) {
   using C_ = BwdCfg<H>;
+  constexpr int CW_ = BQ_ / RG_;           // query columns per row thread
+  constexpr int NROW_ = 128 * RG_;         // row threads per CTA (plus the issuer warp)
   constexpr int HO = C_::HO;
   constexpr int NST = C_::NST;
   constexpr bool PIPE = C_::PIPE;
@@ -125,15 +130,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(barSt0 + 8 * s, 1);
       mbar_init(bardPt0 + 8 * s, 1);
     }
-    mbar_init(barPt, 128);
-    mbar_init(bardSt, 128);
+    mbar_init(barPt, NROW_);
+    mbar_init(bardSt, NROW_);
     mbar_init(bardQ, 1);
-    mbar_init(barDQfree, 128);
-    mbar_init(barSync, 128);
+    mbar_init(barDQfree, NROW_);
+    mbar_init(barSync, NROW_);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == 4 * RG_) {
     tmem_alloc(smem_u32((const void*)tmem_slot), C_::TMEM_COLS);
     tmem_relinquish();
   }
@@ -145,7 +150,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto sbuf = [&](int it) { return PIPE ? (it & 1) : 0; };
   auto spar = [&](int it) { return PIPE ? ((it >> 1) & 1) : (it & 1); };
 
-  if (warp == 4) {
+  if (warp == 4 * RG_) {
     // ------------------------------------------------------------ issuer warp
     if (nit > 0 && elect_one()) {
       const uint32_t idesc_s = make_idesc_bf16(128, BQ_, 0, 0);     // K-major x K-major, N = 64
@@ -272,10 +277,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------------------------------- per-key-row math
-    const int r = threadIdx.x;  // key row in tile == TMEM lane
+    const int r = threadIdx.x & 127;     // key row in tile == TMEM lane
+    const int hq = threadIdx.x >> 7;     // which CW_ query columns of the row this thread works on
+    const int c0 = hq * CW_;
     const int kp = k0 + r;
     const bool key_valid = kp < a.Tk;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int my_seg = (a.seg_k && key_valid) ? a.seg_k[(long long)b * a.Tk + kp] : 0;
     bool ok = true;
     auto stat_ptr = [&](int buf, int which) { return s_stat + (buf * 3 + which) * 64; };
@@ -286,8 +293,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     auto fetch_stats = [&](int it, float& v_lse, float& v_delta, int& v_seg) {
       int n, qbase;
       tile_of(it, n, qbase);
-      const int qi = qbase + r;
-      if (r < 64 && qi < a.Tq) {
+      const int qi = qbase + (int)threadIdx.x;
+      if (threadIdx.x < 64 && qi < a.Tq) {
         const long long o = ((long long)b * a.N + n) * a.Tq + qi;
         v_lse = a.lse[o] * LOG2E;
         v_delta = a.delta[o];
@@ -302,20 +309,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     auto drain_dq = [&](int it) {
       int n, qbase;
       tile_of(it, n, qbase);
-      uint32_t t0[32], t1[32];
-      tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)), t0);
-      tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)) + 32, t1);
+      uint32_t t[CW_ / 32][32];
+#pragma unroll
+      for (int j = 0; j < CW_ / 32; ++j) tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)) + c0 + 32 * j, t[j]);
       tmem_ld_wait();
-      if (r < HO) {
-        float* dq = a.dQ + ((long long)b * a.Tq + qbase) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
+      if (r < HO && !(a.dbg & 1)) {
+        float* dq = a.dQ + ((long long)b * a.Tq + qbase + c0) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
         const long long ld = (long long)a.N * H;
         if (qbase + 64 <= a.Tq) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) atomicAdd(dq + i * ld, __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]));
+          for (int i = 0; i < CW_; ++i) atomicAdd(dq + i * ld, __uint_as_float(t[i >> 5][i & 31]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (qbase + i < a.Tq) atomicAdd(dq + i * ld, __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]));
+          for (int i = 0; i < CW_; ++i)
+            if (qbase + c0 + i < a.Tq) atomicAdd(dq + i * ld, __uint_as_float(t[i >> 5][i & 31]));
         }
       }
     };
@@ -323,10 +330,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       float f0, f1;
       int i2;
       fetch_stats(0, f0, f1, i2);
-      if (r < 64) {
-        stat_ptr(0, 0)[r] = f0;
-        stat_ptr(0, 1)[r] = f1;
-        reinterpret_cast<int*>(stat_ptr(0, 2))[r] = i2;
+      if (threadIdx.x < 64) {
+        stat_ptr(0, 0)[threadIdx.x] = f0;
+        stat_ptr(0, 1)[threadIdx.x] = f1;
+        reinterpret_cast<int*>(stat_ptr(0, 2))[threadIdx.x] = i2;
       }
     }
     for (int it = 0; it < nit && ok; ++it) {
@@ -338,9 +345,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (it + 1 < nit) fetch_stats(it + 1, nx_lse, nx_delta, nx_seg);
       int n, qbase;
       tile_of(it, n, qbase);
-      const float* st_lse = stat_ptr(it & 1, 0);
-      const float* st_delta = stat_ptr(it & 1, 1);
-      const int* st_seg = reinterpret_cast<const int*>(stat_ptr(it & 1, 2));
+      const float* st_lse = stat_ptr(it & 1, 0) + c0;          // this thread's columns
+      const float* st_delta = stat_ptr(it & 1, 1) + c0;
+      const int* st_seg = reinterpret_cast<const int*>(stat_ptr(it & 1, 2)) + c0;
       const int pb = PIPE ? (it & 1) : 0;
       // does any (key, query) pair of this tile need masking?
       const int qpos_lo = qbase + a.q_off, qpos_hi = qbase + BQ_ - 1 + a.q_off;
@@ -350,26 +357,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
       BWD_WAIT(barSt0 + 8 * sbuf(it), spar(it), ST_TIMEOUT_EPILOGUE);
       tc_fence_after();
-      float p[64];
+      float p[CW_];
       {
-        uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)), t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + 32, t1);
+        uint32_t t[CW_ / 32][32];
+#pragma unroll
+        for (int j = 0; j < CW_ / 32; ++j) tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + c0 + 32 * j, t[j]);
         tmem_ld_wait();
         const float sc2 = a.scale * LOG2E;
         if (!need_mask && a.softcap <= 0.f) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            p[i] = exp2f(__uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]) * sc2 - st_lse[i]);
+          for (int i = 0; i < CW_; ++i)
+            p[i] = exp2f(__uint_as_float(t[i >> 5][i & 31]) * sc2 - st_lse[i]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const float s = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
-            const int qpos = qbase + i + a.q_off;
+          for (int i = 0; i < CW_; ++i) {
+            const float s = __uint_as_float(t[i >> 5][i & 31]);
+            const int qpos = qbase + c0 + i + a.q_off;
             float z;
             if (a.softcap > 0.f) z = a.softcap * tanhf(s * a.scale / a.softcap) * LOG2E;
             else z = s * sc2;
-            bool keep = key_valid && (qbase + i < a.Tq);
+            bool keep = key_valid && (qbase + c0 + i < a.Tq);
             if (a.causal) keep = keep && (kp <= qpos);
             if (a.window > 0) keep = keep && (kp > qpos - a.window);
             if (a.seg_k) keep = keep && (st_seg[i] == my_seg);
@@ -380,13 +387,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       {
         uint8_t* prow = sptr + C_::OFF_PT + pb * C_::P_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < CW_ / 8; ++c) {
           uint4 v;
           v.x = pack_bf16(p[8 * c + 0], p[8 * c + 1]);
           v.y = pack_bf16(p[8 * c + 2], p[8 * c + 3]);
           v.z = pack_bf16(p[8 * c + 4], p[8 * c + 5]);
           v.w = pack_bf16(p[8 * c + 6], p[8 * c + 7]);
-          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = v;
+          *reinterpret_cast<uint4*>(prow + (((c + c0 / 8) ^ (r & 7)) << 4)) = v;
         }
         fence_proxy_async_smem();
         tc_fence_before();
@@ -403,30 +410,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       BWD_WAIT(bardPt0 + 8 * sbuf(it), spar(it), ST_TIMEOUT_EPILOGUE);
       tc_fence_after();
       {
-        uint32_t t0[32], t1[32];
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_dpt(sbuf(it)), t0);
-        tmem_ld_32x32(tmem + lane_addr + C_::tm_dpt(sbuf(it)) + 32, t1);
+        uint32_t t[CW_ / 32][32];
+#pragma unroll
+        for (int j = 0; j < CW_ / 32; ++j) tmem_ld_32x32(tmem + lane_addr + C_::tm_dpt(sbuf(it)) + c0 + 32 * j, t[j]);
         tmem_ld_wait();
         if (a.softcap > 0.f) {
-          uint32_t s0[32], s1[32];
-          tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)), s0);
-          tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + 32, s1);
+          uint32_t sv[CW_ / 32][32];
+#pragma unroll
+          for (int j = 0; j < CW_ / 32; ++j) tmem_ld_32x32(tmem + lane_addr + C_::tm_st(sbuf(it)) + c0 + 32 * j, sv[j]);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const float s = __uint_as_float(i < 32 ? s0[i & 31] : s1[i & 31]);
+          for (int i = 0; i < CW_; ++i) {
+            const float s = __uint_as_float(sv[i >> 5][i & 31]);
             const float t = tanhf(s * a.scale / a.softcap);
             p[i] *= (1.f - t * t);
           }
         }
         uint8_t* drow = sptr + C_::OFF_DST + pb * C_::P_BYTES + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < CW_ / 8; ++c) {
           float d[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int i = 8 * c + e;
-            const float dp = __uint_as_float(i < 32 ? t0[i & 31] : t1[i & 31]);
+            const float dp = __uint_as_float(t[i >> 5][i & 31]);
             d[e] = p[i] * (dp - st_delta[i]) * a.scale;
           }
           uint4 v;
@@ -434,7 +441,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           v.y = pack_bf16(d[2], d[3]);
           v.z = pack_bf16(d[4], d[5]);
           v.w = pack_bf16(d[6], d[7]);
-          *reinterpret_cast<uint4*>(drow + ((c ^ (r & 7)) << 4)) = v;
+          *reinterpret_cast<uint4*>(drow + (((c + c0 / 8) ^ (r & 7)) << 4)) = v;
         }
         fence_proxy_async_smem();
         tc_fence_before();
@@ -446,10 +453,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         drain_dq(it);
         tc_fence_before();
       }
-      if (it + 1 < nit && r < 64) {
-        stat_ptr((it + 1) & 1, 0)[r] = nx_lse;
-        stat_ptr((it + 1) & 1, 1)[r] = nx_delta;
-        reinterpret_cast<int*>(stat_ptr((it + 1) & 1, 2))[r] = nx_seg;
+      if (it + 1 < nit && threadIdx.x < 64) {
+        stat_ptr((it + 1) & 1, 0)[threadIdx.x] = nx_lse;
+        stat_ptr((it + 1) & 1, 1)[threadIdx.x] = nx_delta;
+        reinterpret_cast<int*>(stat_ptr((it + 1) & 1, 2))[threadIdx.x] = nx_seg;
       }
     }
     if (PIPE && nit > 0 && ok) {
@@ -464,7 +471,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __nv_bfloat16* dkrow = a.dK + ((long long)b * a.Tk + kp) * a.lddk + (long long)kvh * H + half * HO;
     __nv_bfloat16* dvrow = a.dV + ((long long)b * a.Tk + kp) * a.lddv + (long long)kvh * H + half * HO;
 #pragma unroll 1
-    for (int c = 0; c < HO / 32; ++c) {
+    for (int c = hq; c < HO / 32; c += RG_) {      // the row's output columns are shared out between its threads
       uint32_t o[32];
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
@@ -496,7 +503,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (*abort_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
-  if (warp == 4) {
+  if (warp == 4 * RG_) {
     tc_fence_after();
     tmem_dealloc(tmem, C_::TMEM_COLS);
   }
@@ -538,10 +545,14 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
   if (tb_make_tmap_2d_bf16(&tv, v, (uint64_t)a.B * a.Tk, (uint64_t)a.KH * H, ldv, BK_, 64, 1)) return -3;
   static DeviceOnce once;
   if (once.first() &&
-      cudaFuncSetAttribute(attn_bwd_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess)
+      (cudaFuncSetAttribute(attn_bwd_kernel<H, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess ||
+       cudaFuncSetAttribute(attn_bwd_kernel<H, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess))
     return -5;
   dim3 grid((a.Tk + BK_ - 1) / BK_, a.KH * C_::NHALF, a.B);
-  attn_bwd_kernel<H><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  // one row-thread group (160 threads); TUNIX_B200_ATTN_BWD_GROUPS=2 selects two (288 threads)
+  static const bool one_group = [] { const char* e = getenv("TUNIX_B200_ATTN_BWD_GROUPS"); return !(e && atoi(e) == 2); }();
+  if (one_group) attn_bwd_kernel<H, 1><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
+  else attn_bwd_kernel<H, 2><<<grid, 288, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -572,6 +583,7 @@ TB_API int tb_attn_bwd(const void* q, const void* k, const void* v, const void* 
   a.seg_q = seg_q; a.seg_k = seg_k; a.lse = lse; a.delta = delta; a.dQ = dq_accum;
   a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   a.lddk = lddk; a.lddv = lddv; a.status = status;
+  { const char* e = getenv("TUNIX_B200_BWD_DBG"); a.dbg = e ? atoi(e) : 0; }
   switch (H) {
     case 64: return launch_bwd<64>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
     case 128: return launch_bwd<128>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
@@ -670,7 +682,7 @@ TB_API int tb_attn_bwd_noalloc(const void* q, const void* k, const void* v, cons
   BwdArgs a;
   a.B = B; a.Tq = Tq; a.Tk = Tk; a.N = N; a.KH = KH;
   a.scale = scale; a.softcap = softcap; a.causal = causal; a.window = window; a.q_off = Tk - Tq;
-  a.seg_q = nullptr; a.seg_k = nullptr; a.lse = lse; a.delta = delta; a.dQ = dq32;
+  a.seg_q = nullptr; a.seg_k = nullptr; a.lse = lse; a.delta = delta; a.dQ = dq32; a.dbg = 0;
   a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   a.lddk = ldkv; a.lddv = ldkv; a.status = status;
   int rc;

@@ -109,8 +109,21 @@ def apply_lora_to_model(model: nn.Module, provider: LoraProvider, seed: int = 0,
         # Kaiming-uniform A, zero B: the adapted model starts identical to the base model.
         bound = 1.0 / math.sqrt(mod.in_features)
         a.uniform_(-bound, bound, generator=gen)
+        out_rows = mod.out_features
+        tp = getattr(mod, "tp", None)
+        if tp is not None and tp.world > 1:
+            # the projection was sliced for tensor parallelism: the adapter factor on the split side is sliced with it
+            # (the full A is drawn first, so the adapted model is the same for every tp size)
+            if mod.tp_mode == "row":
+                n = mod.in_features // tp.world
+                a = a[:, tp.rank * n:(tp.rank + 1) * n].contiguous()
+            else:
+                out_rows = mod.out_features // tp.world
         mod.lora_a = nn.Parameter(a.to(device=dev, dtype=dt))
-        mod.lora_b = nn.Parameter(torch.zeros(mod.out_features, provider.rank, device=dev, dtype=dt))
+        mod.lora_b = nn.Parameter(torch.zeros(out_rows, provider.rank, device=dev, dtype=dt))
+        if tp is not None and tp.world > 1:
+            sliced = mod.lora_a if mod.tp_mode == "row" else mod.lora_b
+            sliced.shard_spec, sliced.shard_group = ((1 if mod.tp_mode == "row" else 0), tp.rank, tp.world), tp.group
         mod.lora_scale = provider.alpha / provider.rank
         if provider.weight_qtype == "nf4":
             mod.quant = NF4Weight(mod.weight.data, provider.tile_size)
@@ -120,6 +133,9 @@ def apply_lora_to_model(model: nn.Module, provider: LoraProvider, seed: int = 0,
         raise ValueError(f"no module matched LoRA pattern {provider.module_path!r}")
     for pname, p in model.named_parameters():
         p.requires_grad_(is_lora_param_name(pname))
+    if getattr(model, "tp", None) is not None:
+        from .parallel.tp import mark_sharded_params
+        mark_sharded_params(model)
     model._lora_provider = provider
     return model
 

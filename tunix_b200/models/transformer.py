@@ -153,14 +153,23 @@ class Attention(nn.Module):
             # sequence-parallel input [B/tp, T, D]: one all-gather feeds q, k and v of this rank's heads
             from ..parallel import tp as tp_lib
             projs = (self.q_proj, self.k_proj, self.v_proj)
-            if any(p.lora_a is not None or p.quant is not None for p in projs) or cache is not None:
-                raise NotImplementedError("tensor parallelism covers full-weight training without a KV cache")
-            w = _joint_rows([p.weight for p in projs])
-            b = _joint_rows([p.bias for p in projs]) if self.q_proj.bias is not None else None
-            qkv = tp_lib.column_parallel_linear(x, w, b, tp)
-            B, N, K = qkv.shape[0], N // tp.world, K // tp.world
-            q, k, v = qkv.split([N * H, K * H, K * H], dim=-1)
-            q, k, v = (t.contiguous().view(B, T, -1, H) for t in (q, k, v))
+            if cache is not None:
+                raise NotImplementedError("tensor parallelism covers training without a KV cache")
+            self._tp_plain = not any(p.lora_a is not None or p.quant is not None for p in projs + (self.o_proj,))
+            if self._tp_plain:
+                w = _joint_rows([p.weight for p in projs])
+                b = _joint_rows([p.bias for p in projs]) if self.q_proj.bias is not None else None
+                qkv = tp_lib.column_parallel_linear(x, w, b, tp)
+                B, N, K = qkv.shape[0], N // tp.world, K // tp.world
+                q, k, v = qkv.split([N * H, K * H, K * H], dim=-1)
+                q, k, v = (t.contiguous().view(B, T, -1, H) for t in (q, k, v))
+            else:
+                # adapters or a quantised base: gather the tokens once, then this rank's slices run as local projections
+                xg = tp_lib.gather_tokens(x, tp)
+                B, N, K = xg.shape[0], N // tp.world, K // tp.world
+                q = self.q_proj(xg).view(B, T, N, H)
+                k = self.k_proj(xg).view(B, T, K, H)
+                v = self.v_proj(xg).view(B, T, K, H)
         else:
             q = self.q_proj(x).view(B, T, N, H)
             k = self.k_proj(x).view(B, T, K, H)
@@ -203,7 +212,10 @@ class Attention(nn.Module):
                             softcap=cfg.attn_logit_softcap, q_off=q_off, seg_q=seg_q, seg_k=seg_k)
         o = o.reshape(B, T, N * H)
         if tp is not None:
-            return tp_lib.row_parallel_linear(o, self.o_proj.weight, residual, tp), new_cache
+            if self._tp_plain:
+                return tp_lib.row_parallel_linear(o, self.o_proj.weight, residual, tp), new_cache
+            y = tp_lib.scatter_sum_tokens(self.o_proj(o), tp)
+            return (y if residual is None else y + residual), new_cache
         return self.o_proj(o, residual=residual), new_cache
 
 
@@ -221,7 +233,10 @@ class MLP(nn.Module):
         if tp is not None:
             from ..parallel import tp as tp_lib
             if any(p.lora_a is not None or p.quant is not None for p in (self.gate_proj, self.up_proj, self.down_proj)):
-                raise NotImplementedError("tensor parallelism covers full-weight training")
+                xg = tp_lib.gather_tokens(x, tp)
+                h = F.glu(self.gate_proj(xg), self.up_proj(xg), self.kind)
+                y = tp_lib.scatter_sum_tokens(self.down_proj(h), tp)
+                return y if residual is None else y + residual
             gu = tp_lib.column_parallel_linear(x, torch.cat([self.gate_proj.weight, self.up_proj.weight], 0), None, tp)
             g, u = gu.split(gu.shape[-1] // 2, dim=-1)
             h = F.glu(g.contiguous(), u.contiguous(), self.kind)

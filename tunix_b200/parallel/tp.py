@@ -268,6 +268,43 @@ class _RowSP(torch.autograd.Function):
         return dx, dw, (dy_s if ctx.has_res else None), None
 
 
+class _GatherTokens(torch.autograd.Function):
+    """[M/tp, ...] token shard -> all [M, ...] tokens; backward sums the ranks' gradients and keeps the own shard."""
+
+    @staticmethod
+    def forward(ctx, x_s, tp: TPContext):
+        ctx.tp = tp
+        return tp.all_gather_rows(x_s)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.reduce_scatter_rows(g.contiguous()).to(g.dtype), None
+
+
+class _ScatterSumTokens(torch.autograd.Function):
+    """Partial sums [M, ...] on every rank -> this rank's token shard of their sum; backward gathers."""
+
+    @staticmethod
+    def forward(ctx, y, tp: TPContext):
+        ctx.tp = tp
+        return tp.reduce_scatter_rows(y.contiguous()).to(y.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_gather_rows(g.contiguous()), None
+
+
+def gather_tokens(x_s, tp: TPContext):
+    """Sequence-parallel shard [B/tp, ...] -> [B, ...] as a plain collective (the path for projections that carry
+    adapters or a quantised base, whose GEMMs do not gather for themselves)."""
+    return _GatherTokens.apply(x_s, tp) if tp.world > 1 else x_s
+
+
+def scatter_sum_tokens(y, tp: TPContext):
+    """Row-parallel partial outputs [B, ...] -> [B/tp, ...] summed over the group."""
+    return _ScatterSumTokens.apply(y, tp) if tp.world > 1 else y
+
+
 def column_parallel_linear(x_s, w, bias, tp: TPContext):
     """x_s [..., K] sharded over tokens -> [tp * rows, N_local] for all tokens, this rank's output features."""
     lead = x_s.shape[:-1]
@@ -318,15 +355,38 @@ def apply_tensor_parallel(model, tp: TPContext):
                     lin.bias.shard_spec = (0, r, W)
                     lin.bias.shard_group = tp.group
                 lin.tp, lin.tp_mode = tp, "column"
+                if lin.lora_b is not None:         # adapters attached before the split: B follows the output rows
+                    lin.lora_b = nn.Parameter(shard_rows(lin.lora_b.data, r, W), requires_grad=lin.lora_b.requires_grad)
+                    lin.lora_b.shard_spec, lin.lora_b.shard_group = (0, r, W), tp.group
             for lin in (at.o_proj, mlp.down_proj):
                 lin.weight = nn.Parameter(shard_cols(lin.weight.data, r, W), requires_grad=lin.weight.requires_grad)
                 lin.weight.shard_spec = (1, r, W)
                 lin.weight.shard_group = tp.group
                 lin.tp, lin.tp_mode = tp, "row"
+                if lin.lora_a is not None:         # A follows the input columns
+                    lin.lora_a = nn.Parameter(shard_cols(lin.lora_a.data, r, W), requires_grad=lin.lora_a.requires_grad)
+                    lin.lora_a.shard_spec, lin.lora_a.shard_group = (1, r, W), tp.group
+            if any(l.quant is not None for l in (at.q_proj, at.k_proj, at.v_proj, at.o_proj, mlp.gate_proj, mlp.up_proj,
+                                                 mlp.down_proj)):
+                raise NotImplementedError("quantise the base after the tensor-parallel split, not before")
     model.tp = tp
-    for n, p in model.named_parameters():
-        p.tp_sharded = any(k in n for k in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))
+    mark_sharded_params(model)
     return model
+
+
+def mark_sharded_params(model) -> None:
+    """`p.tp_sharded`: True for parameters of which every rank holds a different slice. The rest is held in full by
+    every rank and sees partial gradients (other tokens, or other output / input slices), which
+    `allreduce_replicated_grads` sums. Of an adapter pair, the factor on the split side of its projection is
+    sliced (B of a column-parallel projection, A of a row-parallel one) and the other one is replicated."""
+    col, row = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"), ("o_proj", "down_proj")
+    for n, p in model.named_parameters():
+        if n.endswith("lora_a"):
+            p.tp_sharded = any(k in n for k in row)
+        elif n.endswith("lora_b"):
+            p.tp_sharded = any(k in n for k in col)
+        else:
+            p.tp_sharded = any(k in n for k in col + row)
 
 
 def allreduce_replicated_grads(model, tp: TPContext) -> None:
