@@ -18,6 +18,7 @@
 // Counterpart in the reference: autodiff of the attention in tunix/models/*/model.py
 // (e.g. tunix/models/llama3/model.py:379-396); no hand-written backward exists there.
 #include "common.cuh"
+#include <cstdlib>
 
 using namespace tb;
 
@@ -31,7 +32,6 @@ struct BwdArgs {
   int B, Tq, Tk, N, KH;
   float scale, softcap;
   int causal, window, q_off;
-  int dbg;              // TEMPORARY timing probe: bit 0 = skip the dQ atomics
   const int* seg_q;
   const int* seg_k;
   const float* lse;     // [B, N, Tq]
@@ -79,7 +79,7 @@ struct BwdCfg {
 // RG_: row-thread groups. The BQ_ query columns of a key row are split over RG_ threads (one per warpgroup), so the
 // element-wise work between the MMAs runs on 128 * RG_ threads.
 template <int H, int RG_>
-__global__ void __maxnreg__(RG_ == 2 ? 224 : 255)
+__global__ void __launch_bounds__(128 * RG_ + 32, 1)   // 9 warps are allocated as 12: 168 registers per thread
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const BwdArgs a) {
@@ -313,7 +313,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int j = 0; j < CW_ / 32; ++j) tmem_ld_32x32(tmem + lane_addr + C_::tm_dqt(sbuf(it)) + c0 + 32 * j, t[j]);
       tmem_ld_wait();
-      if (r < HO && !(a.dbg & 1)) {
+      if (r < HO) {
         float* dq = a.dQ + ((long long)b * a.Tq + qbase + c0) * ((long long)a.N * H) + (long long)n * H + half * HO + r;
         const long long ld = (long long)a.N * H;
         if (qbase + 64 <= a.Tq) {
@@ -549,8 +549,9 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
        cudaFuncSetAttribute(attn_bwd_kernel<H, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM_BYTES) != cudaSuccess))
     return -5;
   dim3 grid((a.Tk + BK_ - 1) / BK_, a.KH * C_::NHALF, a.B);
-  // one row-thread group (160 threads); TUNIX_B200_ATTN_BWD_GROUPS=2 selects two (288 threads)
-  static const bool one_group = [] { const char* e = getenv("TUNIX_B200_ATTN_BWD_GROUPS"); return !(e && atoi(e) == 2); }();
+  // two row-thread groups (288 threads; B = 8, T = 2048, 32 / 8 heads, H = 128: 1.55 ms against 1.77 ms with one group);
+  // TUNIX_B200_ATTN_BWD_GROUPS=1 selects the single-warpgroup form for comparison
+  static const bool one_group = [] { const char* e = getenv("TUNIX_B200_ATTN_BWD_GROUPS"); return e && atoi(e) == 1; }();
   if (one_group) attn_bwd_kernel<H, 1><<<grid, 160, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
   else attn_bwd_kernel<H, 2><<<grid, 288, C_::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -583,7 +584,6 @@ TB_API int tb_attn_bwd(const void* q, const void* k, const void* v, const void* 
   a.seg_q = seg_q; a.seg_k = seg_k; a.lse = lse; a.delta = delta; a.dQ = dq_accum;
   a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   a.lddk = lddk; a.lddv = lddv; a.status = status;
-  { const char* e = getenv("TUNIX_B200_BWD_DBG"); a.dbg = e ? atoi(e) : 0; }
   switch (H) {
     case 64: return launch_bwd<64>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
     case 128: return launch_bwd<128>(q, k, v, dout, a, ldq, ldk, ldv, lddo, stream);
@@ -682,7 +682,7 @@ TB_API int tb_attn_bwd_noalloc(const void* q, const void* k, const void* v, cons
   BwdArgs a;
   a.B = B; a.Tq = Tq; a.Tk = Tk; a.N = N; a.KH = KH;
   a.scale = scale; a.softcap = softcap; a.causal = causal; a.window = window; a.q_off = Tk - Tq;
-  a.seg_q = nullptr; a.seg_k = nullptr; a.lse = lse; a.delta = delta; a.dQ = dq32; a.dbg = 0;
+  a.seg_q = nullptr; a.seg_k = nullptr; a.lse = lse; a.delta = delta; a.dQ = dq32;
   a.dK = reinterpret_cast<__nv_bfloat16*>(dk); a.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   a.lddk = ldkv; a.lddv = ldkv; a.status = status;
   int rc;

@@ -526,3 +526,49 @@ TB_API int tb_paged_decode(const void* q, long long ldq, const void* k_pool, con
   return launch_pdl(paged_decode_combine_kernel, dim3(B, N), dim3(128), 0, stream, (const float*)part_acc,
                     (const float*)part_ml, seq_lens, N, H, splits, split_tokens, window, (__nv_bfloat16*)out, ldo) == cudaSuccess ? 0 : -5;
 }
+
+// ------------------------------------------------------------------ per-step bookkeeping of the decode loop
+// One thread per running slot does what the continuous-batching loop needs after a token was sampled:
+//   a finished (or empty) slot writes the padding token to the spare last column and stays idle;
+//   a live slot appends (token, log-prob) at its output cursor, advances the cursor, and finishes when the token is
+//   an end-of-sequence id or the cursor reaches the slot's limit; a slot that is still live is fed the token at the
+//   next step (position = its current length, length + 1), a finished one idles (position -1, length 0).
+// The step counter (Philox offset of the sampling kernel) advances by one.
+namespace {
+__global__ void decode_advance_kernel(const long long* __restrict__ next, const float* __restrict__ next_lp,
+                                      bool* __restrict__ done, long long* __restrict__ out_tokens,
+                                      float* __restrict__ out_lp, long long ld_out, long long* __restrict__ out_pos,
+                                      const long long* __restrict__ limit, const long long* __restrict__ eos, int n_eos,
+                                      long long pad_id, long long* __restrict__ tokens, int* __restrict__ positions,
+                                      int* __restrict__ seq_lens, int* __restrict__ step, int B) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *step += 1;
+  if (i >= B) return;
+  const bool was_done = done[i];
+  const long long tok = was_done ? pad_id : next[i];
+  long long pos = out_pos[i];
+  const long long col = was_done ? ld_out - 1 : pos;
+  out_tokens[(long long)i * ld_out + col] = tok;
+  out_lp[(long long)i * ld_out + col] = next_lp[i];
+  if (!was_done) out_pos[i] = ++pos;
+  bool fin = was_done || pos >= limit[i];
+  for (int e = 0; e < n_eos; ++e) fin = fin || (tok == eos[e]);
+  done[i] = fin;
+  tokens[i] = tok;
+  const int len = seq_lens[i];
+  positions[i] = fin ? -1 : len;
+  seq_lens[i] = fin ? 0 : len + 1;
+}
+}  // namespace
+
+TB_API int tb_decode_advance(const long long* next, const float* next_lp, void* done, long long* out_tokens, float* out_lp,
+                             long long ld_out, long long* out_pos, const long long* limit, const long long* eos, int n_eos,
+                             long long pad_id, long long* tokens, int* positions, int* seq_lens, int* step, int B,
+                             cudaStream_t stream) {
+  if (B <= 0) return 0;
+  return launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, next, next_lp,
+                    reinterpret_cast<bool*>(done), out_tokens, out_lp, ld_out, out_pos, limit, eos, n_eos, pad_id, tokens,
+                    positions, seq_lens, step, B) == cudaSuccess ? 0 : -5;
+}

@@ -73,6 +73,72 @@ sample_kernel(float* __restrict__ logits, long long ld, int V, float inv_temp, i
   }
   if (softcap > 0.f || n_forbidden > 0) __syncthreads();
 
+  const bool filtered = !greedy && ((top_k > 0 && top_k < V) || (top_p > 0.f && top_p < 1.f));
+  if (!filtered) {
+    // No top-k / top-p: one pass over the row. Every thread keeps a running (max, sum exp) pair and its best
+    // Gumbel-perturbed score; the pairs are merged after the loop. The row is read once, four values per load.
+    float lm = -INFINITY, ls = 0.f;
+    ArgMax best{-INFINITY, 0x7fffffff};
+    const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+    const bool vec = (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+    for (int i4 = tid * 4; i4 < V; i4 += nt * 4) {
+      float zz[4];
+      if (vec && i4 + 4 <= V) {
+        const float4 q = *reinterpret_cast<const float4*>(z + i4);
+        zz[0] = q.x; zz[1] = q.y; zz[2] = q.z; zz[3] = q.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) zz[j] = (i4 + j < V) ? z[i4 + j] : -INFINITY;
+      }
+      uint4 r = make_uint4(0, 0, 0, 0);
+      if (!greedy) r = philox(make_uint4((uint32_t)(i4 >> 2), (uint32_t)row, (uint32_t)step, 0x5A17u), key);
+      const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+      float cm = lm;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        zz[j] *= inv_temp;
+        cm = fmaxf(cm, zz[j]);
+      }
+      if (cm > lm) {
+        ls *= __expf(lm - cm);          // exp(-inf) = 0 on the first group
+        lm = cm;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (i4 + j >= V) break;
+        if (zz[j] > -INFINITY) ls += __expf(zz[j] - lm);      // a forbidden token (-inf) adds nothing
+        const float score = greedy ? zz[j] : zz[j] - __logf(-__logf(u01(rr[j])));
+        best = amax(best, ArgMax{score, i4 + j});
+      }
+    }
+    const float m = block_max(lm, red);
+    const float s = block_sum(lm == -INFINITY ? 0.f : ls * __expf(lm - m), red);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = amax(best, other);
+    }
+    if ((tid & 31) == 0) {
+      s_a[tid >> 5] = best.v;
+      s_i[tid >> 5] = best.i;
+    }
+    __syncthreads();
+    if (tid < 32) {
+      ArgMax b = (tid < (nt >> 5)) ? ArgMax{s_a[tid], s_i[tid]} : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ArgMax other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = amax(b, other);
+      }
+      if (tid == 0) {
+        const int tok = b.i < V ? b.i : 0;
+        tokens[row] = tok;
+        if (logprobs) logprobs[row] = z[tok] * inv_temp - m - logf(s);
+      }
+    }
+    return;
+  }
+
   float m = -INFINITY;
   for (int i = tid; i < V; i += nt) m = fmaxf(m, z[i] * inv_temp);
   m = block_max(m, red);

@@ -419,19 +419,8 @@ class PagedEngine(BaseSampler):
         nothing, and its output goes to the spare last column."""
         logits = self._logits(hlast, out=st["logits"])
         self._sample(logits, st, st["next"], st["next_lp"])
-        done = st["done"]
-        tok = torch.where(done, st["pad"], st["next"])
-        idx = torch.where(done, st["dump_col"], st["out_pos"])[:, None]
-        st["out_tokens"].scatter_(1, idx, tok[:, None])
-        st["out_lp"].scatter_(1, idx, st["next_lp"][:, None])
-        st["out_pos"].add_((~done).to(torch.int64))
-        st["done"].copy_(done | (tok[:, None] == st["eos"]).any(-1) | (st["out_pos"] >= st["limit"]))
-        # the sampled token is fed at the next decode step, at the position one past the current length
-        st["tokens"].copy_(tok)
-        live = ~st["done"]
-        st["positions"].copy_(torch.where(live, st["seq_lens"], st["neg1"]))
-        st["seq_lens"].copy_(torch.where(live, st["seq_lens"] + 1, st["zero"]))
-        st["step"].add_(1)
+        # append, mark finished slots, and set up the next step's token / position / length: one kernel for all slots
+        K.decode_advance(st, st["pad_id"])
 
     # --------------------------------------------------------------------- call
     @torch.no_grad()
@@ -510,7 +499,7 @@ class PagedEngine(BaseSampler):
             "neg1": torch.full((B,), -1, **i32), "zero": torch.zeros(B, **i32),
             "logits": torch.empty(B, V, dtype=torch.float32, device=dev),
             "step": torch.zeros(1, **i32),
-            "pad": torch.full((B,), pad_id, **i64),
+            "pad": torch.full((B,), pad_id, **i64), "pad_id": int(pad_id),
             "eos": torch.as_tensor(eos_ids, **i64),
             "ws": (torch.empty(B * N * splits * H, dtype=torch.float32, device=dev),
                    torch.empty(B * N * splits * 2, dtype=torch.float32, device=dev)),

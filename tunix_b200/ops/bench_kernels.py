@@ -47,7 +47,7 @@ def _time(fn, iters: int, warmup: int = 3, flush: bool = True):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "adamw", "logsoftmax", "sample",
-                                       "glu", "moe", "paged_decode", "lm_head"])
+                                       "glu", "moe", "paged_decode", "lm_head", "lm_head_bwd", "lora"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -152,6 +152,42 @@ def main(argv=None) -> int:
         tf = 2.0 * rows * V * D / ms / 1e9
         out.update(shape=[rows, V, D], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf,
                    fused=not bool(os.environ.get("TUNIX_B200_NO_FUSED_LSE")))
+    elif args.kernel == "lm_head_bwd":
+        # forward + backward of the fused log-prob head; TUNIX_B200_NO_FUSED_LSE=1 gives the path with fp32 logits buffers
+        from tunix_b200.ops import functional as F
+        rows, V, D = args.rows, args.vocab, args.dim
+        h = (torch.randn(rows, D, device=dev) * 0.5).to(bf).requires_grad_()
+        w = (torch.randn(V, D, device=dev) * 0.02).to(bf).requires_grad_()
+        tg = torch.randint(0, V, (rows,), device=dev)
+
+        def step():
+            h.grad = w.grad = None
+            lp, _ = F.lm_head_logprobs(h, w, tg, chunk=2048)
+            lp.sum().backward()
+        ms = _time(step, args.iters, args.warmup)
+        tf = 4 * 2.0 * rows * V * D / ms / 1e9          # forward GEMM + recompute + dh + dW
+        out.update(shape=[rows, V, D], ms=ms, tflops=tf, frac_of_peak=tf / peak_tf,
+                   fused=not bool(os.environ.get("TUNIX_B200_NO_FUSED_LSE")))
+    elif args.kernel == "lora":
+        # LoRA projection forward + backward: adapter carried by the base GEMM against base GEMM + two low-rank GEMMs
+        from tunix_b200.ops import functional as F
+        M, N, Kd, r = args.m, args.n, args.k, 16
+        x = (torch.randn(M, Kd, device=dev) * 0.5).to(bf).requires_grad_()
+        w = (torch.randn(N, Kd, device=dev) * 0.02).to(bf)
+        a = (torch.randn(r, Kd, device=dev) * 0.02).to(bf).requires_grad_()
+        b = (torch.randn(N, r, device=dev) * 0.02).to(bf).requires_grad_()
+        g = torch.randn(M, N, device=dev).to(bf)
+
+        def fused():
+            x.grad = a.grad = b.grad = None
+            F.lora_linear(x, w, None, a, b, 2.0).backward(g)
+
+        def unfused():
+            x.grad = a.grad = b.grad = None
+            F.lora_delta(x, a, b, F.linear(x, w), 2.0).backward(g)
+        ms_f, ms_u = _time(fused, args.iters, args.warmup), _time(unfused, args.iters, args.warmup)
+        tf = 2 * 2.0 * M * N * Kd / ms_f / 1e9
+        out.update(shape=[M, N, Kd, r], ms=ms_f, ms_unfused=ms_u, tflops=tf, frac_of_peak=tf / peak_tf)
     elif args.kernel == "paged_decode":
         Bn, ctx, N, KH, H, page = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim, 64
         max_pages = (ctx + page - 1) // page

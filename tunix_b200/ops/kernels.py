@@ -75,6 +75,50 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_ext(a: torch.Tensor, b: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, *, b_mn: bool = False,
+             out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+             residual: torch.Tensor | None = None) -> torch.Tensor:
+    """C = A @ op(B)^T + A2 @ op(B2)^T (+ bias) (+ residual) in ONE launch: the second product (a low-rank adapter
+    update) is a few extra k-blocks accumulated into the same TMEM tile.
+
+    a [M, K], a2 [M, r]; b [N, K] and b2 [N, r] (b_mn=False) or b [K, N] and b2 [r, N] (b_mn=True). Problems too small
+    for the two-SM kernel run as two GEMMs (the second adds the first as its residual)."""
+    assert a.dtype == b.dtype == a2.dtype == b2.dtype == torch.bfloat16
+    assert all(_is2d_rowmajor(t) for t in (a, b, a2, b2))
+    M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    r = a2.shape[1]
+    assert a2.shape[0] == M and (b2.shape == (r, N) if b_mn else b2.shape == (N, r))
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, N) and out.stride(1) == 1
+    flags = GF_B_MN if b_mn else 0
+    ldr = 0
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+        flags |= GF_BIAS
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+        flags |= GF_RESIDUAL
+        ldr = residual.stride(0)
+    if M == 0 or N == 0:
+        return out
+    rc = 0
+    if r % 8 == 0 and a2.stride(0) % 8 == 0 and b2.stride(0) % 8 == 0:
+        status = _lib.status_buffer(a.device)
+        rc = _lib.cuda().tb_gemm_bf16_ext(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), flags,
+            _lib.ptr(bias), _lib.ptr(residual), ldr, 1.0, a2.data_ptr(), b2.data_ptr(), r, a2.stride(0), b2.stride(0),
+            status.data_ptr(), _lib.stream_ptr())
+        if rc < 0:
+            _lib.check(rc, "tb_gemm_bf16_ext")
+    if rc == 1:
+        _count()
+        return out
+    gemm(a, b, b_mn=b_mn, out=out, bias=bias, residual=residual)
+    return gemm(a2, b2, b_mn=b_mn, out=out, residual=out)
+
+
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, add_one: bool = False,
                 want_rstd: bool = True, out: torch.Tensor | None = None):
     """x: [rows, D] (unit inner stride). Returns (y, rstd[rows] fp32 or None)."""
@@ -309,7 +353,25 @@ _lib.register_cuda_sigs({
                         _lib.I, _lib.I, _lib.F, _lib.F, _lib.I, _lib.I, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.P],
     "tb_qkv_post": [_lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.P, _lib.F, _lib.F, _lib.P, _lib.P, _lib.P, _lib.I,
                     _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P],
+    "tb_decode_advance": [_lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.P, _lib.P, _lib.P, _lib.I, _lib.LL, _lib.P,
+                          _lib.P, _lib.P, _lib.P, _lib.I, _lib.P],
 })
+
+
+def decode_advance(st: dict, pad_id: int) -> None:
+    """The continuous-batching loop's bookkeeping after a sampled token, one kernel for all slots (csrc/decode.cu,
+    decode_advance_kernel): append token and log-prob at each live slot's cursor, mark slots that hit an
+    end-of-sequence id or their limit, set up the next step's token / position / length, advance the step counter.
+    `st`: the engine's static decode buffers."""
+    B = st["tokens"].shape[0]
+    rc = _lib.cuda().tb_decode_advance(st["next"].data_ptr(), st["next_lp"].data_ptr(), st["done"].data_ptr(),
+                                       st["out_tokens"].data_ptr(), st["out_lp"].data_ptr(), st["out_tokens"].stride(0),
+                                       st["out_pos"].data_ptr(), st["limit"].data_ptr(), st["eos"].data_ptr(),
+                                       st["eos"].numel(), int(pad_id), st["tokens"].data_ptr(), st["positions"].data_ptr(),
+                                       st["seq_lens"].data_ptr(), st["step"].data_ptr(), B, _lib.stream_ptr())
+    _lib.check(rc, "tb_decode_advance")
+    _count()
+
 
 DECODE_SPLIT_TOKENS = 512
 
