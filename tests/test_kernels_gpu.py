@@ -363,3 +363,22 @@ def test_qlora_linear_keeps_no_expanded_weight():
     yf.backward(g.float())
     assert _rel_err(y, yf) < 1e-2 and _rel_err(x.grad, xf.grad) < 1e-2
     assert _rel_err(lin.lora_a.grad, af.grad) < 2e-2 and _rel_err(lin.lora_b.grad, bf.grad) < 2e-2
+
+
+@pytest.mark.parametrize("M,F,D,kind", [(64, 12288, 1024, "silu"), (16, 1408, 512, "gelu"), (200, 2816, 256, "silu"), (256, 4096, 512, "silu")])
+def test_packed_gemm_with_gated_epilogue(M, F, D, kind):
+    """Fused gate / up projection on a pre-tiled, row-interleaved weight with act(gate) * up in the epilogue."""
+    k = _k()
+    torch.manual_seed(4)
+    x = (torch.randn(M, D, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * F, D, device="cuda") * 0.05).to(torch.bfloat16)
+    pw = k.PackedWeight(w, glu=True)
+    out = k.gemm_packed(x, pw, glu=k.GLU_SILU if kind == "silu" else k.GLU_GELU)
+    _check_status()
+    z = x.float() @ w.float().t()
+    g, u = z[:, :F], z[:, F:]
+    act = torch.nn.functional.silu(g) if kind == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    ref = act * u
+    assert out.shape == (M, F)
+    assert _rel_err(out, ref) < 1e-2
+    assert torch.allclose(out.float(), ref, atol=0.02 * ref.abs().max().item() + 1e-3, rtol=3e-2)

@@ -36,6 +36,10 @@ enum GemmFlags : int {
   GF_ACCUM = 8,        // C += result (reads C)
   GF_BIAS = 16,        // + bias[N] (bf16)
   GF_RESIDUAL = 32,    // + R[M,N] (bf16, row stride ldr)
+  // Gated activation in the epilogue (pre-tiled weights only): the N columns are gate / up projections interleaved in
+  // groups of 16 = [8 gate | 8 up] (tb_pack_weight_glu); the kernel writes act(gate) * up, N / 2 bf16 columns.
+  GF_GLU_SILU = 64,
+  GF_GLU_GELU = 128,
 };
 
 // Grouped mode (mixture-of-experts): the tile list lives in device memory, built by a planning kernel from
@@ -584,6 +588,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool accum = args.flags & GF_ACCUM;
     const bool has_bias = args.flags & GF_BIAS;
     const bool has_res = args.flags & GF_RESIDUAL;
+    const int glu_kind = (args.flags & GF_GLU_SILU) ? 1 : (args.flags & GF_GLU_GELU) ? 2 : 0;
     const float alpha = args.alpha;
     const bool c_al16 = (reinterpret_cast<uintptr_t>(args.C) & 15) == 0;      // vector paths need aligned bases
     const bool r_al16 = (reinterpret_cast<uintptr_t>(args.resid) & 15) == 0;
@@ -620,6 +625,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
           const bool full = (col0 + 32 <= N);
+          if (glu_kind) {
+            // two groups of [8 gate | 8 up] -> 16 outputs at column col0 / 2
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + (long long)row * args.ldc + (col0 >> 1);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              if (col0 + 16 * g >= N) break;
+              float o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float gt = v[16 * g + j], up = v[16 * g + 8 + j];
+                float act;
+                if (glu_kind == 1) {
+                  act = gt / (1.f + __expf(-gt));
+                } else {
+                  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+                  act = 0.5f * gt * (1.f + tanhf(k0 * (gt + k1 * gt * gt * gt)));
+                }
+                o[j] = act * up;
+              }
+              uint4 pk;
+              pk.x = pack_bf16(o[0], o[1]);
+              pk.y = pack_bf16(o[2], o[3]);
+              pk.z = pack_bf16(o[4], o[5]);
+              pk.w = pack_bf16(o[6], o[7]);
+              *reinterpret_cast<uint4*>(cp + 8 * g) = pk;       // ldc % 8 == 0 and col0 % 32 == 0: 16-byte aligned
+            }
+            continue;
+          }
           if (has_bias) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -805,10 +838,19 @@ int tb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&] {
+    return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r != CUDA_SUCCESS) {
+    // A thread that has not touched the runtime yet (an autograd worker whose first operation is one of these
+    // kernels) has no current context, and the driver's encoder refuses to work without one: bind the device's
+    // primary context to this thread and try once more.
+    cudaFree(nullptr);
+    r = encode();
+  }
   if (r != CUDA_SUCCESS) return (int)r;
   std::lock_guard<std::mutex> lk(g_tmap_mu);
   if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
@@ -927,8 +969,11 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
 // the copy bandwidth. tb_pack_weight re-tiles the weight once: block (n tile, k block) holds `w` rows x 64
 // columns contiguously, already in the 128-byte-swizzled order the MMA descriptors expect, and the blocks of
 // one n tile follow each other, so a CTA streams one contiguous range with one bulk copy per pipeline stage.
+// glu_f > 0: W holds glu_f gate rows followed by glu_f up rows; packed row n takes gate row 8 * (n / 16) + n % 16 when
+// n % 16 < 8 and up row 8 * (n / 16) + n % 16 - 8 otherwise, so that every 16 packed rows pair 8 gate rows with
+// their 8 up rows (the GF_GLU_* epilogue of the GEMM).
 __global__ void pack_weight_kernel(const __nv_bfloat16* __restrict__ W, long long ldw, int N, int K, int w, int num_kb,
-                                   uint4* __restrict__ P, long long total) {
+                                   uint4* __restrict__ P, long long total, int glu_f) {
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const int c = (int)(idx & 7);
@@ -937,10 +982,16 @@ __global__ void pack_weight_kernel(const __nv_bfloat16* __restrict__ W, long lon
     const long long blk = rr / w;
     const int kb = (int)(blk % num_kb);
     const long long nt = blk / num_kb;
-    const long long n = nt * w + r;
+    long long n = nt * w + r;
     const int k = kb * BK + c * 8;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (n < N && k < K) v = *reinterpret_cast<const uint4*>(W + n * ldw + k);
+    const bool in_range = n < N;
+    if (glu_f > 0 && in_range) {
+      const long long grp = n >> 4;
+      const int w16 = (int)(n & 15);
+      n = w16 < 8 ? grp * 8 + w16 : (long long)glu_f + grp * 8 + (w16 - 8);
+    }
+    if (in_range && k < K) v = *reinterpret_cast<const uint4*>(W + n * ldw + k);
     P[blk * (long long)w * 8 + (long long)r * 8 + (c ^ (r & 7))] = v;
   }
 }
@@ -976,7 +1027,23 @@ TB_API int tb_pack_weight(const void* W, long long ldw, int N, int K, int w, voi
   const long long want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   pack_weight_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(W), ldw, N, K, w, num_kb,
-                                                     reinterpret_cast<uint4*>(P), total);
+                                                     reinterpret_cast<uint4*>(P), total, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// The same for a fused gate / up weight W = [gate (F rows); up (F rows)] with the rows interleaved for the gated
+// epilogue (see pack_weight_kernel). N = 2 F must be a multiple of 16; w a multiple of 32.
+TB_API int tb_pack_weight_glu(const void* W, long long ldw, int N, int K, int w, void* P, cudaStream_t stream) {
+  if (N <= 0 || K <= 0 || (N % 16) || w < 32 || w > 256 || (w % 16) || (ldw % 8) || (K % 8) ||
+      (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(P) & 127))
+    return -2;
+  const int num_kb = (K + BK - 1) / BK;
+  const long long total = (long long)((N + w - 1) / w) * num_kb * w * 8;
+  const int threads = 256;
+  const long long want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  pack_weight_kernel<<<blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(W), ldw, N, K, w, num_kb,
+                                                     reinterpret_cast<uint4*>(P), total, N / 2);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -988,13 +1055,18 @@ TB_API int tb_gemm_packed_bf16(const void* A, long long lda, const void* P, int 
   if (K <= 0 || (lda % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(P) & 127) ||
       w < 16 || w > 256 || (w % 16) || (flags & (GF_A_MN | GF_B_MN)))
     return -2;
+  const bool glu = flags & (GF_GLU_SILU | GF_GLU_GELU);
+  // gated epilogue: bf16 output of N / 2 columns, nothing else in the epilogue, 16-byte aligned rows
+  if (glu && ((flags & (GF_OUT_F32 | GF_ACCUM | GF_BIAS | GF_RESIDUAL)) || (N % 16) || (ldc % 8) ||
+              (reinterpret_cast<uintptr_t>(C) & 15) || alpha != 1.0f))
+    return -2;
   if (g_sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
   static const bool no_splitk = getenv("TUNIX_B200_NO_SPLITK") != nullptr;
-  if (w == 256 && !no_splitk) {
+  if (w == 256 && !no_splitk && !glu) {
     const int sk = tb_gemm_splitk_try(A, nullptr, C, M, N, K, lda, 8, ldc, flags, bias, resid, ldr, alpha, status, stream, P);
     if (sk != 0) return sk < 0 ? sk : 0;
   }

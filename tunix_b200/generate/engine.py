@@ -258,7 +258,10 @@ class PagedEngine(BaseSampler):
                     if (pw is None) != (w is None) or (pw is not None and (pw.N, pw.K) != tuple(w.shape)):
                         fresh = True
         if fresh:
-            self._packed = [{name: (K.PackedWeight(w) if w is not None else None) for name, w in src.items()} for src in srcs]
+            # the fused gate / up weight is packed with its rows interleaved, so that the GEMM's epilogue applies the
+            # gated activation (no [rows, 2F] intermediate, no separate activation kernel)
+            self._packed = [{name: (K.PackedWeight(w, glu=(name == "gu" and w.shape[0] % 32 == 0)) if w is not None else None)
+                             for name, w in src.items()} for src in srcs]
             self._graph = None          # a captured graph points at the old buffers
             return
         for have, src in zip(self._packed, srcs):
@@ -309,8 +312,12 @@ class PagedEngine(BaseSampler):
         Fd = wgu.shape[0] // 2
         h2 = h.reshape(-1, h.shape[-1])
         pgu = self._pk(i, "gu") if decode else None
-        gu = K.gemm_packed(h2, pgu) if pgu is not None else F.linear(h2, wgu)
-        a = K.glu_fwd(gu[:, :Fd], gu[:, Fd:], K.GLU_SILU if layer.mlp.kind == "silu" else K.GLU_GELU)
+        kind = K.GLU_SILU if layer.mlp.kind == "silu" else K.GLU_GELU
+        if pgu is not None and pgu.glu:
+            a = K.gemm_packed(h2, pgu, glu=kind)
+        else:
+            gu = K.gemm_packed(h2, pgu) if pgu is not None else F.linear(h2, wgu)
+            a = K.glu_fwd(gu[:, :Fd], gu[:, Fd:], kind)
         pdown = self._pk(i, "down") if decode else None
         if pdown is not None:
             r2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None

@@ -9,7 +9,7 @@ import torch
 
 from .. import _lib
 
-GF_A_MN, GF_B_MN, GF_OUT_F32, GF_ACCUM, GF_BIAS, GF_RESIDUAL = 1, 2, 4, 8, 16, 32
+GF_A_MN, GF_B_MN, GF_OUT_F32, GF_ACCUM, GF_BIAS, GF_RESIDUAL, GF_GLU_SILU, GF_GLU_GELU = 1, 2, 4, 8, 16, 32, 64, 128
 
 launch_count = 0  # number of native kernel launches issued through this module
 
@@ -760,6 +760,7 @@ def lm_head_lse(h2: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, *, sof
 _lib.register_cuda_sigs({
     "tb_packed_width": [_lib.I, _lib.I],
     "tb_pack_weight": [_lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P],
+    "tb_pack_weight_glu": [_lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P],
     "tb_gemm_packed_bf16": [_lib.P, _lib.LL, _lib.P, _lib.I, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P, _lib.P,
                             _lib.LL, _lib.F, _lib.P, _lib.P],
 })
@@ -767,11 +768,16 @@ _lib.register_cuda_sigs({
 
 class PackedWeight:
     """A K-major weight [N, K] re-tiled for streaming (csrc/gemm.cu, tb_pack_weight): per (n tile of `width` rows,
-    64-column k block) one contiguous, pre-swizzled block. `refresh` re-packs after the source changed."""
+    64-column k block) one contiguous, pre-swizzled block. `refresh` re-packs after the source changed.
 
-    def __init__(self, weight: torch.Tensor, width: int | None = None):
+    `glu=True`: the weight is [gate rows; up rows]; the rows are interleaved in groups of 16 = 8 gate + their 8 up
+    rows, which lets `gemm_packed(..., glu=kind)` apply the gated activation in its epilogue and write N / 2 columns."""
+
+    def __init__(self, weight: torch.Tensor, width: int | None = None, glu: bool = False):
         assert weight.dtype == torch.bfloat16 and _is2d_rowmajor(weight)
         self.N, self.K = weight.shape
+        self.glu = bool(glu)
+        assert not glu or self.N % 16 == 0
         self.width = int(width) if width else int(_lib.cuda().tb_packed_width(self.N, self.K))
         nbytes = -(-self.N // self.width) * -(-self.K // 64) * self.width * 128
         self.data = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
@@ -779,20 +785,35 @@ class PackedWeight:
 
     def refresh(self, weight: torch.Tensor) -> None:
         assert weight.shape == (self.N, self.K) and weight.dtype == torch.bfloat16 and _is2d_rowmajor(weight)
-        rc = _lib.cuda().tb_pack_weight(weight.data_ptr(), weight.stride(0), self.N, self.K, self.width, self.data.data_ptr(),
-                                        _lib.stream_ptr())
+        fn = _lib.cuda().tb_pack_weight_glu if self.glu else _lib.cuda().tb_pack_weight
+        rc = fn(weight.data_ptr(), weight.stride(0), self.N, self.K, self.width, self.data.data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "tb_pack_weight")
         _count()
 
 
 def gemm_packed(a: torch.Tensor, pw: PackedWeight, *, out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
                 accumulate: bool = False, bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
-                alpha: float = 1.0) -> torch.Tensor:
-    """C = alpha * A @ W^T with W given as a PackedWeight; same epilogue options as `gemm`."""
+                alpha: float = 1.0, glu: int | None = None) -> torch.Tensor:
+    """C = alpha * A @ W^T with W given as a PackedWeight; same epilogue options as `gemm`. `glu` (GLU_SILU / GLU_GELU)
+    with a weight packed with `glu=True`: C [M, N / 2] = act(A @ Wgate^T) * (A @ Wup^T), computed in the epilogue."""
     assert a.dtype == torch.bfloat16 and _is2d_rowmajor(a)
     M, K = a.shape
     assert K == pw.K, f"contraction mismatch {K} vs {pw.K}"
     N = pw.N
+    if glu is not None:
+        assert pw.glu and not accumulate and bias is None and residual is None and alpha == 1.0
+        if out is None:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+        assert out.shape == (M, N // 2) and out.dtype == torch.bfloat16 and out.stride(1) == 1
+        if M == 0:
+            return out
+        rc = _lib.cuda().tb_gemm_packed_bf16(a.data_ptr(), a.stride(0), pw.data.data_ptr(), pw.width, out.data_ptr(),
+                                             out.stride(0), M, N, K, GF_GLU_SILU if glu == GLU_SILU else GF_GLU_GELU, 0, 0, 0, 1.0,
+                                             _lib.status_buffer(a.device).data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "tb_gemm_packed_bf16")
+        _count()
+        return out
+    assert not pw.glu, "a weight packed for the gated epilogue needs glu="
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         assert not accumulate
