@@ -807,6 +807,10 @@ int tb_gemm_2cta_try(const void* A, const void* B, void* C, int M, int N, int K,
                      long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
                      int* status, cudaStream_t stream);
 
+int tb_gemm_pair_splitk_try(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                            long long ldc, int flags, const void* bias, const void* resid, long long ldr, float alpha,
+                            int* status, cudaStream_t stream);
+
 tb_encode_tiled_fn tb_get_encode_tiled() {
   static tb_encode_tiled_fn fn = nullptr;
   static std::once_flag once;
@@ -891,6 +895,11 @@ TB_API int tb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   }
   const bool a_mn = flags & GF_A_MN, b_mn = flags & GF_B_MN;
   static const bool no_splitk = getenv("TUNIX_B200_NO_SPLITK") != nullptr;
+  if (max_ctas <= 0 && !no_splitk && !(flags & (GF_GLU_SILU | GF_GLU_GELU))) {
+    // a few hundred rows: 256x256 tiles on CTA pairs with the K range split over a cluster (gemm_pair_splitk.cu)
+    const int ps = tb_gemm_pair_splitk_try(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream);
+    if (ps != 0) return ps < 0 ? ps : 0;
+  }
   if (max_ctas <= 0 && !no_splitk) {
     // skinny problems: 128x256 tiles with the K range split over a cluster (gemm_splitk.cu)
     const int sk = tb_gemm_splitk_try(A, B, C, M, N, K, lda, ldb, ldc, flags, bias, resid, ldr, alpha, status, stream);
