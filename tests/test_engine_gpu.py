@@ -513,3 +513,27 @@ def test_engine_decodes_a_mixture_of_experts_model_like_the_dense_sampler():
             total += n
             assert abs(la[0] - lb[0]) < 6e-2
         assert same / total > 0.85, (graph, same, total)
+
+
+def test_tensor_parallel_decode_matches_whole_model(tmp_path):
+    """The paged engine on a model sliced over 2 ranks (o / down projections summed over the group, kv heads split over
+    the ranks' page pools) against the engine on the whole model."""
+    import json
+    import os
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "res.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29733", os.path.join(root, "tests", "engine_tp_worker.py"), out]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    for r in json.load(open(out)):
+        for g in (0, 1):
+            assert r[f"agree_graph{g}"] > 0.9, r           # bf16 near-ties may flip an argmax late in a sequence
+            assert r[f"first_lp_graph{g}"] < 5e-2, r
+            assert r[f"ranks_equal_graph{g}"], r
+            assert r[f"sampled_agree_graph{g}"] > 0.6, r    # a flipped draw changes the rest of that sequence

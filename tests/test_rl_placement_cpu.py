@@ -104,3 +104,42 @@ def test_disaggregated_layout_with_serving_ranks(tmp_path):
     # per step: one generation round and one reference round; the serving ranks saw all of them
     assert res[2]["served"] == res[3]["served"] == 6 and res[0]["rounds"] == 6
     assert len(res[0]["rewards"]) == 3
+
+
+def _run_groups(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200.common.datatypes import Role
+    from tunix_b200.parallel.mesh import Mesh
+    from tunix_b200.rl.placement import RoleExchange, RolePlacement
+    # rank 0 trains; ranks 1-4 sample as two tensor-parallel groups of two
+    pl = RolePlacement({Role.ACTOR: [0], Role.ROLLOUT: Mesh((2, 2), ("fsdp", "tp"), ranks=[1, 2, 3, 4])})
+    assert pl.replica_groups(Role.ROLLOUT) == [[1, 2], [3, 4]] and pl.replica_groups(Role.ACTOR) == [[0]]
+    ex = RoleExchange(pl)
+    seen = []
+
+    def handler(items):
+        seen.append(list(items))
+        return [(it, rank) for it in items]
+
+    ex.register(Role.ROLLOUT, "generate", handler)
+    if pl.is_controller:
+        got = ex.call(Role.ROLLOUT, "generate", [10, 11, 12, 13, 14])
+        ex.stop()
+        torch.save({"got": got}, f"{out}.{rank}")
+    else:
+        ex.serve()
+        torch.save({"seen": seen}, f"{out}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_exchange_hands_a_tensor_parallel_group_the_same_items(tmp_path):
+    out = str(tmp_path / "g")
+    mp.spawn(_run_groups, args=(5, 29787, out), nprocs=5, join=True)
+    got = torch.load(out + ".0")["got"]
+    # five items over two groups: 3 + 2; the leader of each group (ranks 1 and 3) reports
+    assert got == [(10, 1), (11, 1), (12, 1), (13, 3), (14, 3)]
+    seen = [torch.load(out + f".{r}")["seen"] for r in range(1, 5)]
+    assert seen[0] == seen[1] == [[10, 11, 12]] and seen[2] == seen[3] == [[13, 14]]

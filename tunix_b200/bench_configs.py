@@ -307,6 +307,7 @@ def moe(args) -> dict:
         times.append(e0.elapsed_time(e1) / 1e3)
     sec = _max_over_ranks(float(np.median(times[1:] or times)), dev)
     return {"config": "moe_qwen3_30b_a3b_sft", "n_gpus": world, "layers": cfg.num_layers, "global_batch": seqs * world, "seq_len": 4096,
+            "ep_capacity_factor": (args.ep_capacity or None) if world > 1 else None,
             "step_seconds": sec, "tokens_per_sec": seqs * world * 4096 / sec, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}
 
 
@@ -318,7 +319,10 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=64)
     ap.add_argument("--pairs", type=int, default=32)
     ap.add_argument("--micro", type=int, default=4)
-    ap.add_argument("--ep-capacity", type=float, default=0.0, help="moe: fixed-capacity expert-parallel buffers (0 = exact)")
+    ap.add_argument("--ep-capacity", type=float, default=2.0,
+                    help="moe: receive buffers of the expert-parallel exchange sized as this multiple of the even share, "
+                         "which needs no host read-back per layer (overflow is flagged and raises at the end of the step); "
+                         "0 = exact sizes read back from the device every layer")
     ap.add_argument("--max-running", type=int, default=256, help="sequences decoded together by the rollout engine")
     ap.add_argument("--layout", default="colocated", choices=["colocated", "disaggregated"], help="grpo: where the sampler lives")
     ap.add_argument("--replicated-reference", action="store_true", help="grpo: keep the reference model whole on every rank")

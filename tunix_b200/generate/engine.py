@@ -42,10 +42,10 @@ class PagePool:
     table row of a slot is what the kernels read."""
 
     def __init__(self, cfg, num_pages: int, page_size: int, max_seqs: int, max_pages_per_seq: int, device, dtype,
-                 prefix_caching: bool = True):
+                 prefix_caching: bool = True, kv_heads: Optional[int] = None):
         from ..experimental.generate import kv_cache_manager as kvm
         self.page_size, self.num_pages, self.max_pages = page_size, num_pages, max_pages_per_seq
-        row = cfg.num_kv_heads * cfg.head_dim
+        row = (kv_heads or cfg.num_kv_heads) * cfg.head_dim       # a tensor-parallel rank keeps its own kv heads only
         # zero-initialised: rows of a page that were never written must hold finite values
         self.k = [torch.zeros(num_pages, page_size, row, dtype=dtype, device=device) for _ in range(cfg.num_layers)]
         self.v = [torch.zeros(num_pages, page_size, row, dtype=dtype, device=device) for _ in range(cfg.num_layers)]
@@ -126,6 +126,14 @@ class PagedEngine(BaseSampler):
             raise NotImplementedError("expert-parallel MoE decode goes through Sampler")
         if self.cfg.family == "gemma4":
             raise NotImplementedError("Gemma-4 decode (per-layer inputs, shared KV, 512-wide heads) goes through Sampler")
+        # Tensor-parallel decode: a model sliced by `parallel.tp.apply_tensor_parallel` runs with this rank's heads and
+        # MLP columns; the partial outputs of the o and down projections are summed over the group (one library
+        # all-reduce of [sequences, D] each, captured in the decode graph). Embedding, norms and lm_head are whole on
+        # every rank, so all ranks of the group compute the same logits and, with the same seed, sample the same
+        # tokens: every rank of the group must be given the same requests in the same order.
+        self.tp = getattr(transformer, "tp", None)
+        self.tpw = self.tp.world if self.tp is not None else 1
+        self.n_heads, self.n_kv = self.cfg.num_heads // self.tpw, self.cfg.num_kv_heads // self.tpw
         self.page_size = page_size
         self.max_running = max_running_requests
         self.use_graph = use_cuda_graph
@@ -182,7 +190,7 @@ class PagedEngine(BaseSampler):
         if self.pool is None:
             pages = self.num_pages or self.max_running * self.max_pages_per_seq
             self.pool = PagePool(self.cfg, pages, self.page_size, self.max_running, self.max_pages_per_seq, self.device,
-                                 self.dtype, self.prefix_caching)
+                                 self.dtype, self.prefix_caching, kv_heads=self.n_kv)
 
     # ---------------------------------------------------------------- the model
     @staticmethod
@@ -278,7 +286,7 @@ class PagedEngine(BaseSampler):
     def _attn_in(self, layer, h2, positions_flat, i):
         """Projections + QK-norm + RoPE on flat rows h2 [n, D] -> q [n,N,H], k [n,K,H], v [n,K*H]."""
         cfg, at = self.cfg, layer.self_attn
-        N, KH, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        N, KH, H = self.n_heads, self.n_kv, cfg.head_dim
         q = F.linear(h2, at.q_proj.base_weight(), at.q_proj.bias).view(-1, N, H)
         k = F.linear(h2, at.k_proj.base_weight(), at.k_proj.bias).view(-1, KH, H)
         v = F.linear(h2, at.v_proj.base_weight(), at.v_proj.bias)
@@ -304,6 +312,8 @@ class PagedEngine(BaseSampler):
 
     def _mlp(self, layer, i, h, residual=None, decode=False):
         wgu = self._wgu[i]
+        if wgu is None and self.tpw > 1:
+            raise NotImplementedError("tensor-parallel decode needs plain MLP weights (no adapters, no quantised base, no MoE)")
         if wgu is None:
             if self.cfg.is_moe and h.dim() == 2:      # decode rows: the expert block wants [batch, time, D]
                 r3 = residual[:, None] if residual is not None else None
@@ -319,10 +329,19 @@ class PagedEngine(BaseSampler):
             gu = K.gemm_packed(h2, pgu) if pgu is not None else F.linear(h2, wgu)
             a = K.glu_fwd(gu[:, :Fd], gu[:, Fd:], kind)
         pdown = self._pk(i, "down") if decode else None
+        if self.tpw > 1:
+            y = K.gemm_packed(a, pdown) if pdown is not None else layer.mlp.down_proj(a)
+            return self._tp_sum(y, None if residual is None else residual.reshape(y.shape)).view(*h.shape[:-1], -1)
         if pdown is not None:
             r2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
             return K.gemm_packed(a, pdown, residual=r2).view(*h.shape[:-1], -1)
         return layer.mlp.down_proj(a.view(*h.shape[:-1], Fd), residual=residual)
+
+    def _tp_sum(self, y, residual):
+        """Sum the ranks' partial projection outputs (in place) and add the residual once."""
+        import torch.distributed as dist
+        dist.all_reduce(y, group=self.tp.group)
+        return y if residual is None else y.add_(residual)
 
     def _mlp_and_norms(self, layer, i, x, attn_out, decode=False):
         cfg = self.cfg
@@ -340,7 +359,7 @@ class PagedEngine(BaseSampler):
         (a row never rewrites pages it shares). Returns the hidden state of the last position [B, D]."""
         cfg, pool = self.cfg, self.pool
         B, P = toks.shape
-        KH, H = cfg.num_kv_heads, cfg.head_dim
+        KH, H = self.n_kv, cfg.head_dim
         x = F.embedding(toks, self._model.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         pos_flat = positions.reshape(-1).contiguous()
         valid = seg.reshape(-1) > 0
@@ -364,10 +383,13 @@ class PagedEngine(BaseSampler):
             if Tc > 0:
                 k4 = torch.cat([pool.k[i][pidx].view(B, Tc, KH, H), k4], 1)
                 v4 = torch.cat([pool.v[i][pidx].view(B, Tc, KH, H), v4], 1)
-            o = F.attention(q.view(B, P, cfg.num_heads, H), k4, v4, scale=at.scale, causal=True, window=at.window,
+            o = F.attention(q.view(B, P, self.n_heads, H), k4, v4, scale=at.scale, causal=True, window=at.window,
                             softcap=cfg.attn_logit_softcap, q_off=Tc if Tc > 0 else None, seg_q=seg, seg_k=seg_k)
             o = o.reshape(B, P, -1)
-            a = at.o_proj(o, residual=None if cfg.post_norms else x)
+            if self.tpw > 1:
+                a = self._tp_sum(at.o_proj(o), None if cfg.post_norms else x)
+            else:
+                a = at.o_proj(o, residual=None if cfg.post_norms else x)
             x = self._mlp_and_norms(layer, i, x, a)
         return self._model.norm(x[:, -1])
 
@@ -375,7 +397,7 @@ class PagedEngine(BaseSampler):
         """One token for every sequence of the wave. `st` holds the static device buffers."""
         cfg, pool = self.cfg, self.pool
         B = st["tokens"].shape[0]
-        N, KH, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        N, KH, H = self.n_heads, self.n_kv, cfg.head_dim
         x = F.embedding(st["tokens"], self._model.embed_tokens, math.sqrt(cfg.embed_dim) if cfg.embed_scale else 1.0)
         pos = st["positions"]           # position of the token being fed = seq_len before it is appended
         lens = st["seq_lens"]           # length including that token
@@ -398,7 +420,10 @@ class PagedEngine(BaseSampler):
                                page_size=pool.page_size, max_ctx=self.cache_size, scale=at.scale,
                                softcap=cfg.attn_logit_softcap, window=at.window, workspace=st["ws"], split_tokens=st["split"])
             po = self._pk(i, "o")
-            if po is not None:
+            if self.tpw > 1:
+                a = K.gemm_packed(o.view(B, N * H), po) if po is not None else at.o_proj(o.view(B, N * H))
+                a = self._tp_sum(a, None if cfg.post_norms else x)
+            elif po is not None:
                 a = K.gemm_packed(o.view(B, N * H), po, residual=None if cfg.post_norms else x)
             else:
                 a = at.o_proj(o.view(B, N * H), residual=None if cfg.post_norms else x)
@@ -487,9 +512,9 @@ class PagedEngine(BaseSampler):
 
     def _new_state(self, B, max_steps, eos_ids, pad_id, temperature, top_p, top_k, seed):
         dev = self.device
-        split = K.decode_split_tokens(B, self.cfg.num_kv_heads, self.cache_size)
+        split = K.decode_split_tokens(B, self.n_kv, self.cache_size)
         splits = (self.cache_size + split - 1) // split
-        N, H, V = self.cfg.num_heads, self.cfg.head_dim, self.cfg.vocab_size
+        N, H, V = self.n_heads, self.cfg.head_dim, self.cfg.vocab_size
         i64 = dict(dtype=torch.int64, device=dev)
         i32 = dict(dtype=torch.int32, device=dev)
         return {

@@ -98,6 +98,17 @@ class RolePlacement:
             return self.group(role)
         return m.group(axis)
 
+    def replica_groups(self, role) -> list:
+        """The role's ranks as groups that each hold ONE copy of the model: the ranks along the `tp` axis of its mesh
+        form a group (they work on the same items together), everything else multiplies the copies."""
+        m = self.meshes.get(_as_role(role))
+        if m is None or m.axis_size("tp") <= 1:
+            return [[r] for r in self.ranks(role)]
+        import numpy as np
+        ax = m.axis_names.index("tp")
+        lines = np.moveaxis(m.devices, ax, -1).reshape(-1, m.shape[ax])
+        return sorted([int(r) for r in line] for line in lines)
+
     @property
     def controllers(self) -> list:
         return self.ranks(Role.ACTOR)
@@ -139,6 +150,7 @@ class _Round:
     counts: list               # items submitted per rank
     results: Optional[list] = None
     local: bool = False
+    report: bool = True        # False on the non-leading ranks of a model-parallel group: the leader reports the results
 
 
 class RoleExchange:
@@ -172,12 +184,13 @@ class RoleExchange:
 
     def _assign(self, role, submitted: list) -> tuple:
         flat = [(r, i, it) for r, items in enumerate(submitted) for i, it in enumerate(items or [])]
-        ranks = self.p.ranks(role)
-        mine = []
-        if self.p.rank in ranks:
-            s, e = split_evenly(len(flat), len(ranks))[ranks.index(self.p.rank)]
-            mine = flat[s:e]
-        return mine, [len(items or []) for items in submitted]
+        groups = self.p.replica_groups(role)          # every rank of a group gets the group's share
+        mine, report = [], True
+        for gi, g in enumerate(groups):
+            if self.p.rank in g:
+                s, e = split_evenly(len(flat), len(groups))[gi]
+                mine, report = flat[s:e], g[0] == self.p.rank
+        return mine, [len(items or []) for items in submitted], report
 
     # -------------------------------------------------------------------- rounds
     def begin(self, role, op: str, items: Sequence) -> _Round:
@@ -189,8 +202,8 @@ class RoleExchange:
             rd = _Round(role, op, [(self.p.rank, i, it) for i, it in enumerate(items)], [], local=True)
         else:
             submitted = self._gather(("work", str(role), op, list(items)))
-            mine, counts = self._assign(role, [s[3] if s and s[0] == "work" else [] for s in submitted])
-            rd = _Round(role, op, mine, counts)
+            mine, counts, report = self._assign(role, [s[3] if s and s[0] == "work" else [] for s in submitted])
+            rd = _Round(role, op, mine, counts, report=report)
         self._open = rd
         return rd
 
@@ -217,7 +230,7 @@ class RoleExchange:
         self.rounds += 1
         if rd.local:
             return rd.results
-        tagged = [(r, i, res) for (r, i, _), res in zip(rd.mine, rd.results)]
+        tagged = [(r, i, res) for (r, i, _), res in zip(rd.mine, rd.results)] if rd.report else []
         everything = self._gather(tagged)
         mine = [None] * (rd.counts[self.p.rank] if self.p.rank < len(rd.counts) else 0)
         for chunk in everything:
@@ -260,8 +273,8 @@ class RoleExchange:
                 continue
             _, role, op, _ = head
             role = _as_role(role)
-            mine, counts = self._assign(role, [s[3] if s and s[0] == "work" else [] for s in submitted])
-            rd = _Round(role, op, mine, counts)
+            mine, counts, report = self._assign(role, [s[3] if s and s[0] == "work" else [] for s in submitted])
+            rd = _Round(role, op, mine, counts, report=report)
             self._execute(rd)
-            self._gather([(r, i, res) for (r, i, _), res in zip(rd.mine, rd.results)])
+            self._gather([(r, i, res) for (r, i, _), res in zip(rd.mine, rd.results)] if report else [])
             served += 1

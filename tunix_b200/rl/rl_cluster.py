@@ -125,6 +125,15 @@ class RLCluster:
             if pl.axis_size(Role.ACTOR, "fsdp") > 1 and tcfg.actor_optimizer is not None:
                 from ..parallel import fsdp
                 tcfg.actor_optimizer = fsdp.shard_optimizer(tcfg.actor_optimizer, pl.axis_group(Role.ACTOR, "fsdp"))
+        if self.rollout_actor is not None and self.rollout_actor is not self.train_actor:
+            # a rollout mesh with a `tp` axis: the sampler's copy is sliced over it and decodes tensor-parallel; the
+            # ranks of one tp group receive the same requests from the exchange
+            tp = pl.axis_size(Role.ROLLOUT, "tp")
+            if tp > 1 and getattr(self.rollout_actor, "tp", None) is None:
+                from ..parallel import tp as tp_lib
+                dev = next(self.rollout_actor.parameters()).device
+                tp_lib.apply_tensor_parallel(self.rollout_actor, tp_lib.TPContext(group=pl.axis_group(Role.ROLLOUT, "tp"),
+                                                                                  device=dev))
         if getattr(self.cluster_config, "shard_frozen_models", True):
             for role, model in ((Role.REFERENCE, self.reference), (Role.CRITIC, None), (Role.REWARD, self.reward)):
                 if model is None or pl.axis_size(role, "fsdp") <= 1 or getattr(model, "dp_shard", None) is not None:

@@ -22,6 +22,13 @@ class VanillaRollout(BaseRollout):
             self._engine = PagedEngine(model, tokenizer, cache_config_or_size)
 
     def generate(self, prompts, rollout_config: RolloutConfig, **kwargs) -> RolloutOutput:
+        want_tp = getattr(rollout_config, "tensor_parallel_size", -1)
+        have_tp = getattr(self._engine, "tpw", 1) if self._engine is not None else 1
+        if want_tp not in (-1, 0, 1) and want_tp != have_tp:
+            # tensor-parallel decode runs on a model that `parallel.tp.apply_tensor_parallel` has sliced over a group of
+            # that size (paged engine only); every rank of the group must be handed the same requests
+            raise NotImplementedError(f"RolloutConfig.tensor_parallel_size={want_tp}, but the rollout model is sliced over "
+                                      f"{have_tp} rank(s): slice it with apply_tensor_parallel and use the paged engine")
         tok_prompts = kwargs.get("prompt_token_ids")
         call = self._engine if self._engine is not None else self._sampler
         extra = {}
