@@ -57,8 +57,9 @@ def main():
     # ---- a sliced model against the whole one
     from tunix_b200.models.config import ModelConfig
     from tunix_b200.models.transformer import create_model
-    cfg = ModelConfig(family="llama3", num_layers=2, vocab_size=512, embed_dim=256, hidden_dim=512, num_heads=4, head_dim=64,
-                      num_kv_heads=2, dtype=torch.bfloat16, max_position=256)
+    # heads and kv heads must divide by the number of ranks (4 / 2 for the 2-rank test, more for larger groups)
+    cfg = ModelConfig(family="llama3", num_layers=2, vocab_size=512, embed_dim=256, hidden_dim=512 * max(world // 4, 1),
+                      num_heads=max(4, world), head_dim=64, num_kv_heads=max(2, world), dtype=torch.bfloat16, max_position=256)
     whole = create_model(cfg, device=dev, seed=0)
     sliced = create_model(cfg, device=dev, seed=0)
     tp_lib.apply_tensor_parallel(sliced, tp)

@@ -145,13 +145,14 @@ def grpo(args) -> dict:
     per_rank = max(args.prompts // n_ctl, 1)
     # batch sizes count prompts; every prompt stands for its G generations (a micro-batch of `micro` prompts is
     # micro x G sequences)
-    micro = max(1, min(args.micro, per_rank))
+    micro = max(1, min(args.micro // G, per_rank))      # --micro counts sequences: 4 -> one prompt = 8 sequences of 1024 tokens
     tcfg = RLTrainingConfig(eval_every_n_steps=10 ** 9, max_steps=args.steps, actor_optimizer=optim.AdamW(1e-6, max_grad_norm=1.0),
                             mini_batch_size=per_rank, train_micro_batch_size=micro, rollout_micro_batch_size=per_rank,
                             compute_logps_micro_batch_size=micro * 2 if per_rank % (micro * 2) == 0 else micro,
                             pbar_description=None)
     rc = RolloutConfig(max_tokens_to_generate=768, max_prompt_length=256, temperature=1.0, top_p=1.0, seed=2,
-                       kv_cache_size=1032, eos_tokens=[-1], max_running_requests=args.max_running)
+                       kv_cache_size=1032, eos_tokens=[-1],
+                       max_running_requests=min(args.max_running, max(args.prompts // max(world - n_ctl, 1) if disagg else per_rank, 1) * G))
     cluster = RLCluster(actor=actor, reference=ref, rollout_model=sampler, tokenizer=tok, placement=pl,
                         separate_rollout_copy=not disagg,
                         cluster_config=ClusterConfig(role_to_mesh=r2m, training_config=tcfg, rollout_config=rc, rollout_engine="paged",
@@ -319,7 +320,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=64)
     ap.add_argument("--pairs", type=int, default=32)
     ap.add_argument("--micro", type=int, default=4)
-    ap.add_argument("--ep-capacity", type=float, default=2.0,
+    ap.add_argument("--ep-capacity", type=float, default=0.0,
                     help="moe: receive buffers of the expert-parallel exchange sized as this multiple of the even share, "
                          "which needs no host read-back per layer (overflow is flagged and raises at the end of the step); "
                          "0 = exact sizes read back from the device every layer")

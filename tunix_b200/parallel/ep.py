@@ -12,7 +12,8 @@ The rows themselves move with two kernels of `csrc/moe.cu`, both plain P2P loads
 and their backward passes are each other: the owner pulls `dout` rows (combine backward), the source
 gather-sums `dxp` rows (dispatch backward). The routing weight rides along as one fp32 per row and is applied
 on the owner (`ops.moe.local_experts`), so rows that travel back are final and the weight's gradient is formed
-where the expert output lives. A flag barrier (`symm.SymmBarrier`) stands before and after every pull.
+where the expert output lives. One flag barrier (`symm.SymmBarrier`) stands between the writes and the pulls of an
+exchange; the buffers alternate (`EPContext.workspace`), which makes a second barrier after the pulls unnecessary.
 
 Without symmetric memory (CPU / gloo) the same result comes from all-gathering the tokens, computing the local
 experts' share for all of them and reduce-scattering the sum: the path the CPU test runs.
@@ -54,12 +55,18 @@ class EPContext:
             raise RuntimeError("expert-parallel capacity exceeded: tokens were dropped; raise capacity_factor")
 
     def workspace(self, kind: str, rows: int, D: int) -> symm.SymmBuffer:
+        """The symmetric buffer an exchange writes its rows into. Two buffers per (kind, shape) are handed out in
+        turn, which is what lets an exchange run on ONE flag barrier (between "everyone has written" and the pulls):
+        a buffer is written again two exchanges of its kind later, and a rank gets past the barrier in between only
+        after every peer has arrived there, that is after every peer has finished pulling from the buffer. Every
+        rank runs the same sequence of exchanges, so all ranks pick the same buffer."""
         key = (kind, rows, D)
-        ws = self._ws.get(key)
-        if ws is None:
-            ws = symm.symm_empty(rows * D, torch.bfloat16, self.device, self.group, zero=True)
-            self._ws[key] = ws
-        return ws
+        pair = self._ws.get(key)
+        if pair is None:
+            pair = self._ws[key] = [[symm.symm_empty(rows * D, torch.bfloat16, self.device, self.group, zero=True)
+                                     for _ in range(2)], 0]
+        pair[1] ^= 1
+        return pair[0][pair[1]]
 
 
 # ------------------------------------------------------------------------------- differentiable collectives
@@ -175,7 +182,6 @@ class _Dispatch(torch.autograd.Function):
         xp = torch.empty((plan.rows, D), dtype=torch.bfloat16, device=x.device)
         K.moe_zero_pad(xp, plan.seg_off, plan.counts)
         K.moe_pull_rows(ws.c_ptrs, ep.world, D, plan.src_rank, plan.src_row, xp)
-        ep.barrier.wait()
         ctx.plan, ctx.ep, ctx.D = plan, ep, D
         return xp
 
@@ -187,7 +193,6 @@ class _Dispatch(torch.autograd.Function):
         ws.tensor.view(plan.max_rows, D)[:plan.rows].copy_(dxp)
         ep.barrier.wait()
         dx = K.moe_gather_sum_peer(ws.c_ptrs, ep.world, D, plan.dst_rank, plan.dst_pos, D)
-        ep.barrier.wait()
         return dx, None, None
 
 
@@ -200,7 +205,6 @@ class _Combine(torch.autograd.Function):
         ws.tensor.view(plan.max_rows, D)[:plan.rows].copy_(y)
         ep.barrier.wait()
         out = K.moe_gather_sum_peer(ws.c_ptrs, ep.world, D, plan.dst_rank, plan.dst_pos, D, residual)
-        ep.barrier.wait()
         ctx.plan, ctx.ep, ctx.D, ctx.has_res = plan, ep, D, residual is not None
         return out
 
@@ -215,7 +219,6 @@ class _Combine(torch.autograd.Function):
         dy = torch.empty((plan.rows, D), dtype=torch.bfloat16, device=dout.device)
         K.moe_zero_pad(dy, plan.seg_off, plan.counts)
         K.moe_pull_rows(ws.c_ptrs, ep.world, D, plan.src_rank, plan.src_row, dy)
-        ep.barrier.wait()
         return dy, (dout if ctx.has_res else None), None, None
 
 

@@ -82,13 +82,39 @@ def sync_replicated_grads(model, comm: CommContext) -> None:
     """Sum over the group the gradients of parameters that every rank holds whole."""
     if comm.world == 1:
         return
+    grads = []
     for p in model.parameters():
         if getattr(p, "dp_sharded", False):
             continue
         g = getattr(p, "main_grad", None)
         g = g if g is not None else p.grad
         if g is not None:
-            dist.all_reduce(g, group=comm.group)
+            grads.append(g)
+    for g in _coalesce_adjacent(grads):
+        dist.all_reduce(g, group=comm.group)
+
+
+def _coalesce_adjacent(tensors: list) -> list:
+    """Contiguous tensors that follow each other in one storage (slots of an optimizer's flat gradient buffer) merged
+    into one flat view per run, so that a model's whole parameters cost one collective per run instead of one per
+    parameter (a mixture-of-experts layer: norms, attention projections and router form one run between the expert
+    weights of neighbouring layers)."""
+    items = [t for t in tensors if t.is_contiguous() and t.numel() > 0]
+    rest = [t for t in tensors if not t.is_contiguous()]
+    items.sort(key=lambda t: (t.untyped_storage().data_ptr(), t.storage_offset()))
+    out, run = [], None            # run = [storage ptr, dtype, start offset, end offset, first tensor]
+    for t in items:
+        key, a, b = t.untyped_storage().data_ptr(), t.storage_offset(), t.storage_offset() + t.numel()
+        if run is not None and run[0] == key and run[1] == t.dtype and run[3] == a:
+            run[3] = b
+            continue
+        if run is not None:
+            out.append(run)
+        run = [key, t.dtype, a, b, t]
+    if run is not None:
+        out.append(run)
+    views = [r[4].new_empty(0).set_(r[4].untyped_storage(), r[2], (r[3] - r[2],)) for r in out]
+    return views + rest
 
 
 def grad_sumsq(model, comm: CommContext) -> torch.Tensor:

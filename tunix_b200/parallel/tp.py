@@ -393,13 +393,17 @@ def allreduce_replicated_grads(model, tp: TPContext) -> None:
     """Sum over the tp group the gradients of parameters every rank holds in full (they saw different tokens)."""
     if tp.world == 1:
         return
+    from .fsdp3 import _coalesce_adjacent
+    grads = []
     for p in model.parameters():
         if getattr(p, "tp_sharded", False):
             continue
         g = getattr(p, "main_grad", None)
         g = g if g is not None else p.grad
         if g is not None:
-            dist.all_reduce(g, group=tp.group)
+            grads.append(g)
+    for g in _coalesce_adjacent(grads):          # neighbouring slots of the flat gradient buffer go in one collective
+        dist.all_reduce(g, group=tp.group)
 
 
 def grad_sumsq(model, tp: TPContext) -> torch.Tensor:
