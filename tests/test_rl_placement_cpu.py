@@ -41,6 +41,8 @@ def _run(rank, world, port, layout, out):
     from tunix_b200.rl.rl_cluster import RLCluster
     if layout == "colocated":
         r2m = {}
+    elif layout == "halves":        # trainer half (actor + reference together), sampler half
+        r2m = {Role.ACTOR: [0, 1], Role.REFERENCE: [0, 1], Role.ROLLOUT: [2, 3]}
     else:
         r2m = {Role.ACTOR: [0, 1], Role.ROLLOUT: [2], Role.REFERENCE: [3]}
     pl = RolePlacement(r2m)
@@ -143,3 +145,14 @@ def test_exchange_hands_a_tensor_parallel_group_the_same_items(tmp_path):
     assert got == [(10, 1), (11, 1), (12, 1), (13, 3), (14, 3)]
     seen = [torch.load(out + f".{r}")["seen"] for r in range(1, 5)]
     assert seen[0] == seen[1] == [[10, 11, 12]] and seen[2] == seen[3] == [[13, 14]]
+
+
+def test_halves_layout_trainers_and_samplers(tmp_path):
+    """The first half of the ranks hosts actor and reference, the second half two samplers."""
+    out = str(tmp_path / "r")
+    mp.spawn(_run, args=(4, 29757, "halves", out), nprocs=4, join=True)
+    res = [torch.load(f"{out}.{r}") for r in range(4)]
+    assert [r["controller"] for r in res] == [True, True, False, False]
+    assert res[0]["steps"] == res[1]["steps"] == 3 and torch.equal(res[0]["actor"], res[1]["actor"])
+    for r in (2, 3):
+        assert torch.allclose(res[r]["sampler"], res[0]["actor"], atol=1e-6)

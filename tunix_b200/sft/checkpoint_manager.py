@@ -174,8 +174,12 @@ def _load_item(path: str) -> dict:
 
 
 class CheckpointManager:
-    def __init__(self, root_directory: Optional[str] = None, options: Any = None):
+    def __init__(self, root_directory: Optional[str] = None, options: Any = None, group=None):
+        """`group`: the process group of the ranks that train this model (None = every rank of the job). Decisions
+        are taken by, and files written by, the group's first rank; the collectives of this class stay inside the
+        group, so ranks that host other roles (samplers of a disaggregated RL job) are not involved."""
         self._root = root_directory
+        self._group = group
         if isinstance(options, dict) or options is None:
             options = CheckpointingOptions.from_dict(options)
         self._opts: CheckpointingOptions = options
@@ -224,11 +228,22 @@ class CheckpointManager:
         if dist is None:
             decision = self._should_save(step, force)
         else:
-            box = [self._should_save(step, force) if dist.get_rank() == 0 else None]
-            dist.broadcast_object_list(box, src=0)
+            box = [self._should_save(step, force) if self._is_writer() else None]
+            dist.broadcast_object_list(box, src=self._src(), group=self._group)
             decision = bool(box[0])
         self._decisions = {(step, force): decision}
         return decision
+
+    def _src(self) -> int:
+        """Global rank of the rank that decides and writes."""
+        dist = _dist()
+        if dist is None or self._group is None:
+            return 0
+        return dist.get_global_rank(self._group, 0)
+
+    def _is_writer(self) -> bool:
+        dist = _dist()
+        return dist is None or dist.get_rank() == self._src()
 
     # --------------------------------------------------------------------- save
     def save(self, step: int, model, optimizer=None, save_only_lora_params: bool = False, force: bool = False,
@@ -238,8 +253,7 @@ class CheckpointManager:
         self._decisions = {}
         self.wait_until_finished()
         from ..lora import is_lora_param_name
-        dist = _dist()
-        writer = dist is None or dist.get_rank() == 0
+        writer = self._is_writer()
         # Collective part (every rank): whole tensors out of sharded ones. Device -> host copies happen here
         # (synchronously) on the rank that writes; file IO on its worker thread.
         owners = dict(model.named_parameters())
@@ -326,10 +340,10 @@ class CheckpointManager:
         self.wait_until_finished()
         dist = _dist()
         if dist is not None:
-            dist.barrier()              # the writing rank has finished its last save
+            dist.barrier(group=self._group)              # the writing rank has finished its last save
             if step is None:
-                box = [self.latest_step() if dist.get_rank() == 0 else None]
-                dist.broadcast_object_list(box, src=0)
+                box = [self.latest_step() if self._is_writer() else None]
+                dist.broadcast_object_list(box, src=self._src(), group=self._group)
                 step = box[0]
         step = self.latest_step() if step is None else step
         if step is None:

@@ -128,8 +128,11 @@ class PeftTrainer:
             "input_tokens": x.input_tokens, "input_mask": x.input_mask,
             **({"images": x.images} if getattr(x, "images", None) is not None else {})}
         self._has_aux = False
+        # the ranks that train this model: a sharded optimizer knows its group (a disaggregated RL job trains on a
+        # subset of the job's ranks); otherwise every rank of the job
         self.checkpoint_manager = ckpt_lib.CheckpointManager(training_config.checkpoint_root_directory,
-                                                             training_config.checkpointing_options)
+                                                             training_config.checkpointing_options,
+                                                             group=getattr(optimizer, "group", None))
         self.metrics_logger = metrics_logger or ml.MetricsLogger(training_config.metrics_logging_options)
         self.metrics_prefix = training_config.metrics_prefix
         self.perf_tracer = perf_tracer
@@ -250,7 +253,7 @@ class PeftTrainer:
             if getattr(self.optimizer, "reduces_denominator", False) and not (tp is not None and tp.world > 1):
                 local = True
             else:
-                dist.all_reduce(total)
+                dist.all_reduce(total, group=getattr(self.optimizer, "group", None))
         if tp is not None and tp.world > 1:
             dist.all_reduce(total, group=tp.group)      # every tp rank scored its own sequences
             rep = getattr(self.model, "dp_replica_group", None)
