@@ -268,20 +268,26 @@ def main() -> int:
     baseline = None
     if "baseline" in arms and main_kind != "zero2-nccl":
         kind = "zero2-nccl" if world > 1 else "library"
-        try:
-            b = run_arm(kind, main_mb, side_steps, False, False)
-            baseline = {"what": ("same model, batch and sharded optimizer with NCCL reduce-scatter / all-gather "
-                                 "instead of the fused peer-memory kernels" if world > 1 else
-                                 "same model, batch and optimizer with stock PyTorch ops (cuBLAS linear, library "
-                                 "fused attention, unfused element-wise ops) instead of this package's kernels"),
-                        "value": tps(b["ms_per_step"]), "ms_per_step": b["ms_per_step"], "steps": side_steps,
-                        "peak_mem_gib": b["peak_mem_gib"]}
-        except Exception as e:  # an out-of-memory baseline must not lose the main number
-            baseline = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+        # the stock-op arm on one GPU keeps more activations than this package's kernels and may not fit next to the
+        # unsharded optimizer state at the main arm's micro-batch: it then runs the same global batch in micro-batches
+        # of half the size (recorded in `micro_batch_per_gpu`)
+        tries = [main_mb] + ([main_mb // 2] if world == 1 and main_mb >= 2 else [])
+        for b_mb in tries:
+            try:
+                b = run_arm(kind, b_mb, side_steps, False, False)
+                baseline = {"what": ("same model, batch and sharded optimizer with NCCL reduce-scatter / all-gather "
+                                     "instead of the fused peer-memory kernels" if world > 1 else
+                                     "same model, batch and optimizer with stock PyTorch ops (cuBLAS linear, library "
+                                     "fused attention, unfused element-wise ops) instead of this package's kernels"),
+                            "value": tps(b["ms_per_step"]), "ms_per_step": b["ms_per_step"], "steps": side_steps,
+                            "micro_batch_per_gpu": b_mb, "peak_mem_gib": b["peak_mem_gib"]}
+                break
+            except Exception as e:  # an out-of-memory baseline must not lose the main number
+                baseline = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                if world > 1:
+                    raise
             gc.collect()
             torch.cuda.empty_cache()
-            if world > 1:
-                raise
     same_mb = None
     if "same_mb" in arms and world > 1 and main_mb != 2 and seqs % 2 == 0:
         try:

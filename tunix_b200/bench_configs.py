@@ -328,6 +328,12 @@ def main(argv=None) -> int:
     ap.add_argument("--layout", default="colocated", choices=["colocated", "disaggregated"], help="grpo: where the sampler lives")
     ap.add_argument("--replicated-reference", action="store_true", help="grpo: keep the reference model whole on every rank")
     args = ap.parse_args(argv)
+    limit = os.environ.get("TUNIX_B200_DUMP_STACKS_AFTER")
+    if limit:
+        # a run that is still going after this many seconds prints the Python stack of every thread of every rank
+        # and exits: where a multi-rank configuration waits, without holding the GPUs until an outer timeout
+        import faulthandler
+        faulthandler.dump_traceback_later(float(limit), exit=True)
     res = {"tiny_lora_cpu": tiny_lora_cpu, "grpo": grpo, "dpo": dpo, "moe": moe}[args.config](args)
     if not dist.is_initialized() or dist.get_rank() == 0:
         print(json.dumps(res))
