@@ -85,12 +85,22 @@ class RLCluster:
             self.rollout_actor = None
         self._rollout_shares_weights = self.rollout_actor is not None and self.rollout_actor is actor and \
             pl.same(Role.ROLLOUT, Role.ACTOR)
-        self._apply_mesh_strategies()
         self.global_steps = 0
         self.last_weight_sync_seconds: Optional[float] = None
         self.last_weight_sync_bytes = 0
         self._resharder = None
+        self._resharder_key = None
         self._prefetch = None
+        self.actor_trainer = self.critic_trainer = None
+        if pl.world > 1 and not pl.same(Role.ROLLOUT, Role.ACTOR) and torch.cuda.is_available() and \
+                all(pl.axis_size(r, "tp") <= 1 for r in (Role.ACTOR, Role.ROLLOUT)):
+            # The cross-rank weight transfer allocates symmetric memory over ALL ranks. It is set up (and run once)
+            # here, before the trainer ranks allocate symmetric memory among themselves (sharded optimizer, sharded
+            # reference): on 4 GPUs (2 trainers + 2 samplers) every rank was found waiting in the symmetric-memory
+            # rendezvous of the transfer's staging buffer when that rendezvous came after the trainers' own ones,
+            # i.e. after the ranks had taken part in different numbers of rendezvous.
+            self._transfer_weights()
+        self._apply_mesh_strategies()
         self._buffered_metrics: dict = {}
         self._metrics_step = None
         self.metrics_logger = metrics_logger or ml.MetricsLogger(tcfg.metrics_logging_options)
@@ -105,7 +115,6 @@ class RLCluster:
         if self.reward is not None:
             models["reward"] = self.reward
         self.inference_worker = InferenceWorker(models)
-        self.actor_trainer = self.critic_trainer = None
         if self.train_actor is not None:
             self._init_trainers()
         self._anchor = None   # pinned-host copy of the start-of-step policy (for off-policy old log-probs)
@@ -437,7 +446,7 @@ class RLCluster:
         src, dst = {}, {}
         sampler_lora = self._rollout_has_adapters()          # collective on its first call: every rank makes it
         if self.train_actor is not None:
-            wait = getattr(self.actor_trainer.optimizer, "wait_params", None)
+            wait = getattr(getattr(self.actor_trainer, "optimizer", None), "wait_params", None)
             if wait is not None:
                 wait()
             src = lora_state_dict(self.train_actor) if (self._lora and sampler_lora) else \
