@@ -286,3 +286,63 @@ def test_agentic_learner_pack_first_scoring_eval_and_trajectory_log():
     assert len(logged) == 8 and {"conversation_tokens", "trajectory_reward", "policy_version"} <= set(logged[0])
     assert cl.metrics_logger.metric_exists("", "eval/rewards/mean", "eval")
     assert len(cl.metrics_logger.get_metric_history("", "eval/episodes", "eval")) == 2      # after each of the two steps
+
+
+def test_collector_engine_pause_resume_versions_and_budget_facts():
+    """The distributed rollout wrapper: sampler calls with derived seeds and per-call limits, a pause that holds the next
+    turn until resume (which then runs under the newer policy version), request-scoped metadata on the item."""
+    import dataclasses
+    from tunix_b200.experimental.rollout import collector as col
+    from tunix_b200.experimental.rollout.sampler import SamplingResponse
+    tok = CharTok()
+    texts = ['<tool_call>{"name": "calculator", "arguments": {"expression": "6*7"}}</tool_call>',
+             '<tool_call>{"name": "finish", "arguments": {"response": "42"}}</tool_call>']
+    seen = []
+
+    class FakeSampler:
+        async def sample(self, reqs):
+            r = reqs[0]
+            seen.append((r.sampling_params.seed, r.sampling_params.max_tokens, len(r.prompt_token_ids)))
+            ids = tok.encode(texts[len(seen) - 1])
+            return [SamplingResponse(request_id=r.request_id, token_ids=ids, logprobs=[-0.25] * len(ids), text=texts[len(seen) - 1])]
+
+    @dataclasses.dataclass
+    class Req:
+        prompt_id: str = "p7"
+        group_index: int = 2
+        generation_kwargs: dict = dataclasses.field(default_factory=lambda: {"temperature": 1.0, "max_tokens": 400})
+        max_turns: int = 4
+        max_response_length: int = 1000
+        target_policy_version: int = 3
+        metadata: dict = dataclasses.field(default_factory=lambda: {"episode_timeout": 30.0, "tag": "x"})
+
+    version = {"v": 3}
+    env = ToolEnvironment(task={"question": "6*7?", "answer": "42"}, tools=[CalculatorTool()], reward_fn="exact_match", max_steps=4)
+    eng = col.TrajectoryCollectorEngine("traj_p7_g2", Req(), FakeSampler(), env, ToolAgent(tools={"calculator": CalculatorTool()}),
+                                        tok, get_parser("qwen"), eos_ids=[tok.encode(">")[0]], policy_version_fn=lambda: version["v"])
+
+    async def run():
+        task = asyncio.ensure_future(eng.run_episode())
+        while len(seen) < 1:
+            await asyncio.sleep(0.001)
+        eng.pause()                       # weight sync begins after the first turn was requested
+        await asyncio.sleep(0.05)
+        n_paused = len(seen)
+        version["v"] = 4
+        eng.resume()
+        return await task, n_paused
+    item, n_paused = asyncio.run(run())
+    assert n_paused <= 2 and len(seen) == 2
+    seed = col.generate_vanilla_rollout_seed("p7", 2)
+    assert seen[0][0] == seed and seen[1][0] == seed and seen[0][1] == 400       # per-call limit = the request's own
+    assert seen[1][1] <= 400 and seen[1][2] > seen[0][2]                          # later turns see the longer context
+    md = item.metadata
+    assert item.group_id == "p7" and item.pair_index == 2 and md["tag"] == "x" and md["status"] == TrajectoryStatus.SUCCEEDED
+    assert md["policy_versions"][0] == 3 and md["policy_versions"][-1] in (3, 4) and md["policy_version"] == 3
+    assert item.traj["trajectory_reward"] == 1.0 and item.traj["policy_versions"] == md["policy_versions"]
+    assert md["raw_length"] == len(item.traj["conversation_tokens"]) and md["clipped"] is False
+    with pytest.raises(TypeError):
+        col.TrajectoryCollectorEngine("t", dataclasses.replace(Req(), metadata={"overlong_filter": "yes"}), FakeSampler(), env,
+                                      ToolAgent(tools={}), tok)
+    with pytest.raises(ValueError):
+        col.response_budget_facts([1], 0, {1})
