@@ -1,0 +1,286 @@
+"""The layered distributed RL run: engine primitives over workers, the four-stage program on top
+(test model: tunix/experimental/orchestrator/{distributed_rl_engine,rl_program}_test.py). CPU, tiny model; worker
+failures are scripted on the host."""
+import asyncio
+
+import numpy as np
+import pytest
+import torch
+
+from tunix_b200.experimental.common.datatypes import GenerationArgs, Role, RolloutRequest, RolloutResponse
+from tunix_b200.experimental.orchestrator.algorithm_adapter import GRPOAdapter
+from tunix_b200.experimental.orchestrator.batch_assembly import BatchConfig
+from tunix_b200.experimental.orchestrator.distributed_rl_engine import DistributedRLEngine
+from tunix_b200.experimental.orchestrator.rl_engine_interface import AbstractRLEngine
+from tunix_b200.experimental.orchestrator.rl_program import StandardRLProgram, _generation_metrics, prompt_coordinates, tag_prompt
+
+
+class _EchoRollout:
+    """A rollout worker double: answers with tokens derived from the prompt and the seed."""
+    def __init__(self, worker_id, fail=False, n=4):
+        self.worker_id, self.fail, self.n = worker_id, fail, n
+        self.seen, self.synced, self.policy_version = [], [], 0
+
+    def submit(self, req):
+        if self.fail:
+            raise ConnectionError(f"{self.worker_id} lost")
+        self.seen.append(req)
+        rng = np.random.default_rng(req.seed)
+        toks = rng.integers(3, 60, min(self.n, req.max_tokens)).tolist()
+        return RolloutResponse(req.request_id, toks, [-0.5] * len(toks), None, policy_version=self.policy_version,
+                               group_id=req.group_id, metadata=dict(req.metadata))
+
+    def sync_weights(self, version, payload=None):
+        self.policy_version = version
+        self.synced.append((version, payload))
+
+
+class _Trainer:
+    """A trainer worker double that records the split-step protocol and keeps a 'checkpoint' in a dict."""
+    def __init__(self, disk):
+        self.disk, self.ops, self.steps, self.pending = disk, [], 0, 0
+
+    def submit(self, req):
+        req = dict(req)
+        op = req.pop("op")
+        self.ops.append((op, req.get("is_last_microbatch")))
+        if op == "fwd_bwd":
+            self.pending += 1
+            return {"loss": 1.0 / (1 + self.steps), "pending_microbatches": self.pending}
+        if op == "update":
+            assert self.pending > 0
+            self.steps, self.pending = self.steps + 1, 0
+            return {"step": self.steps, "grad_norm": 1.0}
+        if op == "save_checkpoint":
+            self.disk["latest"] = dict(req["custom_metadata"])
+            return True
+        if op == "restore_checkpoint":
+            meta = self.disk.get("latest")
+            self.steps = int(meta["step"]) if meta and str(meta["step"]).isdigit() else 0
+            return dict(meta) if meta else 0
+        if op == "get_metrics":
+            return {"train_steps": self.steps}
+        raise KeyError(op)
+
+
+def _prompts(n):
+    rng = np.random.default_rng(0)
+    return [{"prompt_id": f"p{i}", "prompt_ids": [1] + rng.integers(3, 60, 4).tolist()} for i in range(n)]
+
+
+def test_engine_builds_requests_routes_by_prompt_and_reports_failures():
+    a, b = _EchoRollout("r0"), _EchoRollout("r1")
+    eng = DistributedRLEngine([a, b], {Role.ACTOR: _Trainer({})}, export_weights=lambda: "W")
+    assert isinstance(eng, AbstractRLEngine)
+
+    async def go():
+        with pytest.raises(ValueError, match="lacks 'prompt_id'"):
+            await eng.dispatch_rollouts([{"prompt_ids": [1, 2]}])
+        ids = await eng.dispatch_rollouts(_prompts(3), num_generations=4, policy_version=2,
+                                          generation_args=GenerationArgs(max_tokens=3, temperature=0.7))
+        assert ids[:2] == ["req_p0_g0_v2", "req_p0_g1_v2"] and len(ids) == 12
+        got = []
+        while len(got) < 12:
+            got += await eng.poll_rollouts(timeout_s=1.0)
+        assert await eng.poll_rollouts(timeout_s=0.01) == []
+        # the generations of one prompt share a worker; seeds differ inside a group and repeat across runs
+        owner = {}
+        for w in (a, b):
+            for r in w.seen:
+                owner.setdefault(r.group_id, set()).add(w.worker_id)
+                assert r.max_tokens == 3 and r.temperature == 0.7 and r.metadata["lineage"].events[0].operation == "rollout"
+        assert all(len(v) == 1 for v in owner.values())
+        seeds = sorted(r.seed for w in (a, b) for r in w.seen if r.group_id == "p0")
+        assert len(set(seeds)) == 4 and seeds == list(range(seeds[0], seeds[0] + 4))
+        assert all(r.metadata["is_valid"] and r.metadata["num_generations"] == 4 for r in got)
+        # both workers down: the request comes back as an invalid response instead of disappearing
+        a.fail = b.fail = True
+        await eng.dispatch_rollouts(_prompts(1), num_generations=2)
+        bad = []
+        while len(bad) < 2:
+            bad += await eng.poll_rollouts(timeout_s=1.0)
+        assert all(r.finish_reason == "error" and r.metadata["is_valid"] is False for r in bad)
+        with pytest.raises(TypeError, match="Unexpected generate kwargs"):
+            await eng.generate(_prompts(1), temperature=1.0)
+        eng.rollout_pool.mark_up("r0"); eng.rollout_pool.mark_up("r1")
+        a.fail = b.fail = False
+        out = await eng.generate(_prompts(2), GenerationArgs(max_tokens=2))
+        assert [r.group_id for r in out] == ["p0", "p1"] and all(len(r.tokens) == 2 for r in out)
+        assert await eng.sync_weights() == 1 and a.synced == [(1, "W")] and eng.policy_version == 1
+        with pytest.raises(ValueError, match="No inference worker"):
+            await eng.score(Role.REWARD, [])
+        assert (await eng.get_metrics(Role.ROLLOUT))["policy_version"] == 1
+        assert await eng.get_metrics(Role.ACTOR) == {"train_steps": 0}
+        await eng.close()
+    asyncio.run(go())
+
+
+def test_engine_resume_policy_version_rules():
+    async def resume(meta, **kw):
+        disk = {"latest": meta} if meta is not None else {}
+        r = _EchoRollout("r0")
+        eng = DistributedRLEngine([r], {"actor": _Trainer(disk)})
+        step = await eng.resume_from_checkpoint(**kw)
+        await eng.close()
+        return step, eng.policy_version, r.synced, eng.restored_checkpoint_metadata
+    assert asyncio.run(resume(None)) == (0, 0, [], None)
+    step, version, synced, meta = asyncio.run(resume({"step": 3, "global_step": 3, "policy_version": 3}))
+    assert (step, version, synced) == (3, 3, [(3, None)]) and meta["global_step"] == 3
+    # a version recorded inside a step is ignored unless the checkpoint carries off-policy state
+    assert asyncio.run(resume({"step": 6, "global_step": 3, "policy_version": 5}))[:2] == (3, 3)
+    assert asyncio.run(resume({"step": 6, "global_step": 3, "policy_version": 5, "committed_prompt_ids": ["p0"]}))[:2] == (3, 5)
+    assert asyncio.run(resume({"step": 2}, resync_rollout_weights=False))[:3] == (2, 2, [])
+    assert asyncio.run(resume({"step": "x"}))[0] == 0
+
+
+def test_coordinates_and_generation_metrics():
+    assert prompt_coordinates(7, 4) == {"prompt_idx": 7, "batch_idx": 1, "intra_batch_idx": 3}
+    item = {"prompt_id": "a", "metadata": {"k": 1}}
+    assert tag_prompt(item, prompt_coordinates(0, 2))["metadata"] == {"k": 1, "prompt_idx": 0, "batch_idx": 0, "intra_batch_idx": 0}
+    assert item["metadata"] == {"k": 1}
+    mk = lambda n, c: RolloutResponse("r", [], metadata={"raw_length": n, "clipped": c})
+    m = _generation_metrics([[mk(10, True), mk(20, False)], [mk(4, False)], [RolloutResponse("r", [])]])
+    assert m == {"rollout/completions/clip_ratio": 0.25, "rollout/completions/mean_raw_length": 9.5,
+                 "rollout/completions/max_raw_length": 20.0, "rollout/completions/min_raw_length": 4.0}
+    assert _generation_metrics([[RolloutResponse("r", [])]]) == {}
+
+
+def _program(dataset, max_steps, **kw):
+    algo = GRPOAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens)), drop_uniform_groups=True)
+    return StandardRLProgram(algo, dataset, max_steps, num_generations=4, batch_size=2,
+                             batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=48), generation_args=GenerationArgs(max_tokens=4),
+                             poll_timeout_s=0.05, **kw)
+
+
+def test_program_runs_steps_checkpoints_and_resumes():
+    disk = {}
+    a, b, tr = _EchoRollout("r0"), _EchoRollout("r1", fail=True), _Trainer(disk)
+    eng = DistributedRLEngine([a, b], {Role.ACTOR: tr}, export_weights=lambda: "W")
+    begun, ended = [], []
+    prog = _program(_prompts(10), 3, on_step_begin=begun.append, on_step_end=lambda s, r: ended.append((s, r["train_step"])))
+    hist = prog.run(eng)
+    assert [h["step"] for h in hist] == [0, 1, 2] and begun == [0, 1, 2] and ended == [(0, 1), (1, 2), (2, 3)]
+    assert [h["policy_version"] for h in hist] == [1, 2, 3] and prog.step == 3 and prog.last_step_result.step == 2
+    assert all(h["num_rollouts"] == 8 and h["num_microbatches"] >= 1 and 0 <= h["padding_ratio"] < 1 for h in hist)
+    assert all(h["staleness_max"] == 0 for h in hist)                                 # max_staleness = 0: strictly on-policy
+    # every optimizer step: the micro-batches before the last accumulate, the last one closes the step
+    fb = [last for op, last in tr.ops if op == "fwd_bwd"]
+    assert fb.count(True) == 3 and [op for op, _ in tr.ops].count("update") == 3
+    for i, (op, last) in enumerate(tr.ops):
+        if op == "update":
+            assert tr.ops[i - 1] == ("fwd_bwd", True)
+    assert a.synced[0] == (0, "W") and [v for v, _ in a.synced][-3:] == [1, 2, 3]      # bootstrap sync, then one per step
+    assert b.seen == [] and eng.rollout_pool.stats()["r1"]["down"]                    # the dead worker was routed around
+    assert disk["latest"]["global_step"] == 3 and disk["latest"]["policy_version"] == 3
+    asyncio.run(eng.close())
+    # a new process: fresh engine and program over the same checkpoint continue with step 3 and the unseen prompts
+    a2, tr2 = _EchoRollout("r0"), _Trainer(disk)
+    eng2 = DistributedRLEngine([a2], {Role.ACTOR: tr2})
+    prog2 = _program(_prompts(10), 5)
+    hist2 = prog2.run(eng2)
+    assert [h["step"] for h in hist2] == [3, 4] and tr2.steps == 5 and [v for v, _ in a2.synced] == [3, 4, 5]
+    seen = {r.group_id for r in a2.seen}
+    trained = {r.group_id for r in a.seen}
+    assert seen.isdisjoint({f"p{i}" for i in range(6)}) and seen <= {f"p{i}" for i in range(6, 10)}
+    assert trained >= {f"p{i}" for i in range(6)}
+    asyncio.run(eng2.close())
+
+
+def test_program_replaces_filtered_groups_and_stops_at_dataset_end():
+    class Uniform(_EchoRollout):
+        def submit(self, req):
+            out = super().submit(req)
+            if req.group_id in ("p1", "p2"):            # identical responses: no learning signal
+                out.tokens = [7, 7]
+            return out
+    r, tr = Uniform("r0"), _Trainer({})
+    eng = DistributedRLEngine([r], {Role.ACTOR: tr})
+    prog = _program(_prompts(7), None, checkpoint_every=0, sync_weights=False)
+    hist = prog.run(eng)
+    consumed = sum(h["num_rollouts"] for h in hist) // 4
+    assert consumed == 5 and sum(h["filtered_groups"] for h in hist) == 2
+    assert prog.dispatch_window.skipped_prompt_ids == {"p1", "p2"}
+    assert prog.dispatch_window.committed_prompt_ids == {"p0", "p3", "p4", "p5", "p6"}
+    assert hist[-1]["num_rollouts"] == 4                                             # the dataset ran out inside the last step
+    assert all(v == 0 for v, _ in r.synced) and tr.steps == len(hist) == 3
+    asyncio.run(eng.close())
+
+
+def test_program_surfaces_stage_errors():
+    class BadTrainer(_Trainer):
+        def submit(self, req):
+            if req["op"] == "update":
+                raise RuntimeError("optimizer exploded")
+            return super().submit(req)
+    eng = DistributedRLEngine([_EchoRollout("r0")], {Role.ACTOR: BadTrainer({})})
+    with pytest.raises(RuntimeError, match="optimizer exploded"):
+        _program(_prompts(4), 2, sync_weights=False).run(eng)
+    asyncio.run(eng.close())
+
+
+def test_program_on_real_workers_with_checkpoint_resume(tmp_path):
+    """Sampler-backed rollout workers, a split-step trainer worker over a tiny model and its checkpoint manager: two
+    steps, then a second process-worth of objects resumes from the checkpoint directory."""
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import CacheConfig, TrainingConfig
+    from tunix_b200.experimental.train.peft_trainer_v2 import TrainerV2
+    from tunix_b200.experimental.worker.rollout_worker import RolloutWorker, TrainerWorker
+    from tunix_b200.generate.sampler import Sampler
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer
+    from tunix_b200.sft.utils import LossOutput, WeightedMetric
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16,
+                                           num_kv_heads=1)
+
+    def pg_loss(model, input_tokens, completion_mask, advantages, segment_ids=None, positions=None, **_):
+        hidden, _ = model(input_tokens[:, :-1], positions=None if positions is None else positions[:, :-1],
+                          segment_ids=None if segment_ids is None else segment_ids[:, :-1], skip_lm_head=True)
+        lp = model.token_logprobs(hidden.reshape(-1, hidden.shape[-1]), input_tokens[:, 1:].reshape(-1).long())[0]
+        m = completion_mask[:, 1:]
+        return LossOutput(loss=WeightedMetric(-(lp.view(input_tokens.shape[0], -1) * advantages[:, 1:] * m).sum(), m.sum()))
+
+    def to_inputs(batch):
+        out = {k: torch.as_tensor(v) for k, v in batch.items()}
+        out["input_tokens"] = out["input_tokens"].long()
+        return out
+
+    def build():
+        model = create_model(cfg, seed=0)
+        trainer = PeftTrainer(model, optim.AdamW(5e-3), TrainingConfig(
+            eval_every_n_steps=10 ** 9, pbar_description=None, resume_from_checkpoint_on_init=False,
+            checkpoint_root_directory=str(tmp_path / "ckpt")))
+        trainer.with_loss_fn(pg_loss).with_gen_model_input_fn(to_inputs)
+        synced = []
+        workers = [RolloutWorker("rollout-0", Sampler(model, CharTok(), CacheConfig(64, 1, 1, 16)), eos_tokens=[2],
+                                 apply_weights=lambda v, p: synced.append(v)), TrainerWorker("trainer-0", TrainerV2(trainer))]
+        for w in workers:
+            w.start()
+        return model, workers, synced, DistributedRLEngine([workers[0]], {Role.ACTOR: workers[1]})
+    model, workers, synced, eng = build()
+    before = torch.cat([p.detach().reshape(-1).clone() for p in model.parameters()])
+    prog = StandardRLProgram(GRPOAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens))), _prompts(8), 2,
+                             num_generations=4, batch_size=2, batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=48),
+                             generation_args=GenerationArgs(max_tokens=6, temperature=1.0), poll_timeout_s=0.05)
+    hist = prog.run(eng)
+    assert [h["step"] for h in hist] == [0, 1] and all(np.isfinite(h["loss"]) for h in hist)
+    after = torch.cat([p.detach().reshape(-1).clone() for p in model.parameters()])
+    assert not torch.equal(before, after) and synced == [0, 1, 2]
+    assert (asyncio.run(eng.get_metrics(Role.ACTOR)))["train_steps"] == 2
+    asyncio.run(eng.close())
+    for w in workers:
+        w.stop()
+    model2, workers2, synced2, eng2 = build()
+    prog2 = StandardRLProgram(GRPOAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens))), _prompts(8), 3,
+                              num_generations=4, batch_size=2, batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=48),
+                              generation_args=GenerationArgs(max_tokens=6, temperature=1.0), poll_timeout_s=0.05)
+    hist2 = prog2.run(eng2)
+    assert [h["step"] for h in hist2] == [2] and synced2 == [2, 3]
+    meta = eng2.restored_checkpoint_metadata
+    assert meta["global_step"] == 2 and meta["policy_version"] == 2 and meta["num_rollouts"] == 8
+    restored = torch.cat([p.detach().reshape(-1) for p in model2.parameters()])
+    assert not torch.equal(restored, before)                      # weights came from the checkpoint, then one more step
+    asyncio.run(eng2.close())
+    for w in workers2:
+        w.stop()

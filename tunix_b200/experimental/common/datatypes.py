@@ -53,6 +53,32 @@ class HealthReport:
     detail: str = ""
 
 
+class Role(str, enum.Enum):
+    """Roles of the models in an RL job (tunix/experimental/common/datatypes.py, `Role`)."""
+    ACTOR = "actor"
+    CRITIC = "critic"
+    REFERENCE = "reference"
+    REWARD = "reward"
+    ROLLOUT = "rollout"
+
+
+def role_name(role) -> str:
+    return role.value if isinstance(role, enum.Enum) else str(role)
+
+
+@dataclasses.dataclass(frozen=True)
+class GenerationArgs:
+    """Sampling settings of a dispatch; a field left None falls back to the request's own default."""
+    max_tokens: Optional[int] = None
+    temperature: Optional[float] = None
+    top_p: Optional[float] = None
+    top_k: Optional[int] = None
+    seed: Optional[int] = None
+
+    def as_kwargs(self) -> dict:
+        return {k: v for k, v in dataclasses.asdict(self).items() if v is not None}
+
+
 @dataclasses.dataclass
 class RolloutRequest:
     request_id: str

@@ -101,4 +101,22 @@ class TrainerV2(AbstractTrainer):
         if got:
             tr._train_steps = got
             tr._restored_custom_metadata = meta
+        self._restored_step = int(got or 0)
         return got
+
+    def wait_for_checkpoints(self) -> None:
+        """Block until background checkpoint writes have finished."""
+        self.trainer.checkpoint_manager.wait_until_finished()
+
+    def restored_metadata(self) -> Optional[dict]:
+        """The custom metadata of the checkpoint that the last `restore_checkpoint` read (None if there was none),
+        with the restored optimizer step under `step` when the writer did not record one."""
+        if not getattr(self, "_restored_step", 0):
+            return None
+        out = dict(getattr(self.trainer, "_restored_custom_metadata", None) or {})
+        out.setdefault("step", self._restored_step)
+        return out
+
+    def get_metrics(self) -> dict:
+        """Optimizer steps taken and micro-batches waiting for `update`."""
+        return {"train_steps": self.trainer._train_steps, "pending_microbatches": self._pending}

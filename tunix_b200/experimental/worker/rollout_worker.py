@@ -123,9 +123,16 @@ class TrainerWorker(AbstractWorker):
     def _handle(self, req: dict):
         req = dict(req)
         op = req.pop("op")
-        if op not in ("fwd_bwd", "update", "eval_step", "fwd_only", "save_checkpoint", "restore_checkpoint"):
+        if op not in ("fwd_bwd", "update", "eval_step", "fwd_only", "save_checkpoint", "restore_checkpoint", "restored_metadata",
+                      "get_metrics"):
             raise KeyError(f"unknown trainer operation {op!r}")
         out = getattr(self.trainer, op)(**req)
         if op == "update":
             self.policy_version += 1
         return out
+
+    def _drain(self) -> None:
+        """A stopping worker leaves no checkpoint half written: background saves are waited for."""
+        wait = getattr(self.trainer, "wait_for_checkpoints", None)
+        if wait is not None:
+            wait()
