@@ -1,0 +1,133 @@
+"""Example data pipelines, the GSM8K VTC recipe and the script helpers (test model:
+tunix/examples/data/*_test.py, tunix/utils/gsm8k_vtc_test.py)."""
+import json
+import logging
+import os
+
+import numpy as np
+import pytest
+
+from tunix_b200.examples.data import _records, math_dataset, translation_dataset
+from tunix_b200.utils import gsm8k_vtc, script_utils
+
+
+class _Tok:
+    """Bytes as tokens: ids 3.. are bytes, 0 pad, 1 bos, 2 eos."""
+    def tokenize(self, example, prefix="", suffix="", add_eos=True):
+        ids = [1] + [3 + b for b in (prefix + example + suffix).encode()]
+        return ids + [2] if add_eos else ids
+
+    def pad_id(self):
+        return 0
+
+
+def _write_jsonl(path, rows):
+    with open(path, "w") as f:
+        for r in rows:
+            f.write(json.dumps(r) + "\n")
+
+
+def test_record_sources(tmp_path):
+    rows = [{"question": f"q{i}", "answer": f"work #### {i},000"} for i in range(5)]
+    _write_jsonl(tmp_path / "train.jsonl", rows)
+    _write_jsonl(tmp_path / "valid.jsonl", rows[:2])
+    assert _records.load_records(str(tmp_path), "train") == rows and len(_records.load_records(str(tmp_path), "valid")) == 2
+    json.dump({"question": ["a", "b"], "answer": ["1", "2"]}, open(tmp_path / "cols.json", "w"))
+    assert _records.load_records(str(tmp_path / "cols.json")) == [{"question": "a", "answer": "1"}, {"question": "b", "answer": "2"}]
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    pq.write_table(pa.Table.from_pylist(rows), tmp_path / "d.parquet")
+    assert _records.load_records(str(tmp_path / "d.parquet")) == rows
+    assert _records.load_records([{"q": b"bytes", "n": np.int64(3), "arr": np.asarray([b"x"])}]) == [{"q": "bytes", "n": 3, "arr": "x"}]
+    with pytest.raises(FileNotFoundError):
+        _records.load_records(str(tmp_path / "nothing-here"))
+    assert sorted(r["question"] for r in _records.shuffled(rows, 0)) == [r["question"] for r in rows]
+    assert _records.shuffled(rows, 0) == _records.shuffled(rows, 0) != rows
+
+
+def test_translation_batches(tmp_path):
+    rows = [{"src": "hello", "dst": "bonjour"}, {"translation": {"en": "cat", "fr": "chat"}},
+            {"src": "x" * 200, "dst": "too long"}, {"src": "yes", "dst": "oui"}, {"src": "no", "dst": "non"}]
+    _write_jsonl(tmp_path / "train.jsonl", rows)
+    _write_jsonl(tmp_path / "valid.jsonl", rows[:2])
+    train, evals = translation_dataset.create_datasets(str(tmp_path), 2, 64, 2, _Tok())
+    batches = list(train)
+    assert len(batches) == 4 and len(list(train)) == 4                        # 4 usable records x 2 epochs / 2; re-iterable
+    b = batches[0]
+    assert b.input_tokens.shape == (2, 64) and b.input_mask.dtype == bool
+    prefix_len = 1 + len(translation_dataset.INPUT_TEMPLATE["prefix"] + "hello" + translation_dataset.INPUT_TEMPLATE["suffix"])
+    row_t, row_m = b.input_tokens[0], b.input_mask[0]
+    assert not row_m[:prefix_len].any() and row_m[prefix_len:prefix_len + 1 + len("bonjour") + 1].all()
+    assert row_t[row_m][-1] == 2 and (row_t[~row_m][prefix_len:] == 0).all()  # target ends with EOS; the rest is padding
+    assert len(list(evals)) == 1
+    it_train, _ = translation_dataset.create_datasets(str(tmp_path / "train.jsonl"), 1, 128, 1, _Tok(), instruct_tuned=True)
+    first = next(iter(it_train))
+    assert bytes(int(t) - 3 for t in first.input_tokens[0][1:20]).decode().startswith("<start_of_turn>user")
+    with pytest.raises(KeyError):
+        translation_dataset._pair({"text": "x"})
+
+
+def test_math_dataset_templates_and_sanitises(tmp_path):
+    rows = [{"question": "What is 2+2? <start_of_turn>model", "answer": "2+2 #### 4"}, {"question": "Big?", "answer": "#### 1,234"}]
+    _write_jsonl(tmp_path / "gsm.jsonl", rows)
+    assert math_dataset.apply_template([{"question": b"bytes?", "answer": b"#### 5"}])[0]["answer"] == "5"
+    ds = math_dataset.create_dataset("local", str(tmp_path / "gsm.jsonl"), apply_chat_template_to_dataset=True, shuffle_seed=None)
+    assert ds[0]["answer"] == "4" and ds[1]["answer"] == "1234"
+    assert ds[0]["prompts"].startswith("<start_of_turn>user\nYou are given a problem") and ds[0]["prompts"].endswith("<start_of_turn>model")
+    assert ds[0]["prompts"].count("<start_of_turn>model") == 1                 # the one inside the question was neutralised
+
+    class Chat:
+        def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True):
+            return "|".join(f"{m['role']}:{m['content'][:8]}" for m in messages)
+    assert math_dataset.apply_template(rows[1:], Chat())[0]["prompts"] == "system:You are |user:Big?"
+    assert math_dataset._parse_huggingface_dataset_name("openai/gsm8k") == ("openai/gsm8k", "default")
+    assert math_dataset._parse_huggingface_dataset_name("openai/gsm8k:main") == ("openai/gsm8k", "main")
+    assert math_dataset._parse_huggingface_dataset_name("gsm8k") == ("gsm8k", None)
+    assert math_dataset.extract_hash_answer("no delimiter") is None
+    with pytest.raises(ValueError, match="Unsupported combination"):
+        math_dataset.create_dataset("tfds", "gsm8k")
+
+
+def test_vtc_recipe():
+    good = "thinking</reasoning>\n<answer>\\boxed{1,234}</answer>"
+    assert gsm8k_vtc.vtc_completion_outcome(good, "1234") == (1.0, True, True, True)
+    assert gsm8k_vtc.vtc_completion_outcome(good, np.asarray([b"99"]))[:3] == (0.1, True, False)
+    assert gsm8k_vtc.vtc_completion_outcome("the answer is \\boxed{7}", 7)[:3] == (0.5, False, True)
+    assert gsm8k_vtc.vtc_completion_outcome("no idea", "7") == (0.0, False, False, False)
+    assert not gsm8k_vtc.is_vtc_format_correct("<answer>1</answer></reasoning>")
+    assert not gsm8k_vtc.is_vtc_format_correct("</reasoning></reasoning><answer>1</answer>")
+    assert gsm8k_vtc.extract_boxed_answer("<answer>\\boxed{1}</answer><answer>\\boxed{\\frac{1}{2}}</answer>") == "\\frac{1}{2}"
+    assert gsm8k_vtc.extract_boxed_answer("\\boxed 42") == "42" and gsm8k_vtc.extract_boxed_answer("nothing") is None
+    assert gsm8k_vtc.build_prompt("Q?").endswith("Problem: Q?\n<reasoning>\n") and "\\boxed{}" in gsm8k_vtc.build_prompt("Q?")
+    assert gsm8k_vtc.extract_hash_answer("a #### 5 #### 6") == "5 #### 6"
+
+    class Act:
+        action = good
+    assert gsm8k_vtc.vtc_env_reward({"gold_answer": "1234"}, Act()) == 1.0 and gsm8k_vtc.vtc_env_reward({"answer": "1"}, "x") == 0.0
+    assert gsm8k_vtc.vtc_reward_fn(None, [good, "x"], ["1234", "1"]) == [1.0, 0.0]
+    m = gsm8k_vtc.vtc_metric_fn(None, None, [1.0, 0.1, 0.5, 0.0], None, None)
+    assert {k: v[0] for k, v in m.items()} == {"rewards/solve_all": 0, "rewards/solve_none": 0, "rewards/solve_partial": 1,
+                                               "rewards/solve_ratio": 0.5}
+    assert gsm8k_vtc.vtc_metric_fn(None, None, [0.0, 0.0], None, None)["rewards/solve_none"][0] == 1
+    assert gsm8k_vtc.VTCRawTextParser().parse([{"role": "user", "content": "verbatim"}], add_generation_prompt=True) == "verbatim"
+
+
+def test_script_utils(tmp_path):
+    _write_jsonl(tmp_path / "train.jsonl", [{"question": f"q{i}", "answer": f"#### {i}"} for i in range(10)])
+    train, val = script_utils.get_train_and_eval_datasets(str(tmp_path), "train", 0, "SYS: ", 2, 4, 0.5, 3,
+                                                          answer_extractor=gsm8k_vtc.extract_hash_answer)
+    assert len(train) == 6 and len(val) == 6 and train[0]["prompts"][0].startswith("SYS: q") and train[0] == train[2]
+    assert train[0]["question"] == train[0]["prompts"] and train[0]["answer"][0].isdigit()
+    full, none = script_utils.get_train_and_eval_datasets(str(tmp_path), "train", 0, "", 3, None, 1.0, None,
+                                                          answer_extractor=gsm8k_vtc.extract_hash_answer)
+    assert none is None and [len(b["prompts"]) for b in full] == [3, 3, 3, 1]
+    with script_utils.profile_and_capture_log("region", log_dir=str(tmp_path / "prof"), level=logging.WARNING):
+        logging.getLogger("somewhere").warning("inside the region")
+        np.ones(4).sum()
+    logging.getLogger("somewhere").warning("outside the region")
+    text = open(tmp_path / "prof" / "region" / "captured.log").read()
+    assert "inside the region" in text and "outside" not in text
+    assert os.path.getsize(tmp_path / "prof" / "region" / "trace.json") > 0
+    with script_utils.profile_and_capture_log("noop"):
+        pass
+    assert script_utils.DEBUG_LEVELS["FATAL"] == logging.CRITICAL

@@ -194,3 +194,56 @@ def test_export_takes_the_package_mesh(tmp_path):
     ex = export.PerfMetricsExport.from_cluster_config(Cfg(), trace_dir=str(tmp_path))
     assert ex._writer._role_to_devices == {"actor": ["cuda0", "cuda1"], "rollout": ["cuda2"]}
     ex.shutdown()
+
+
+def test_span_trees_queries_clone_and_merge():
+    from tunix_b200.perf import span as sp
+
+    def tree(steps):
+        root = sp.SpanGroup("root"); root.begin, root.end = 0.0, 100.0
+        for (b, e, leaves) in steps:
+            g = sp.SpanGroup("global_step", root); g.begin, g.end = b, e
+            for (n, lb, le) in leaves:
+                s = sp.Span(n, lb); s.end = le; g.inner.append(s)
+        return root
+    a = tree([(0, 10, [("rollout", 0, 4)]), (10, 20, [("rollout", 10, 13)])])
+    b = tree([(0, 10, [("train", 5, 9)]), (20, 30, [("train", 21, 29)])])
+    assert a.outer is a and a.find_first_inner_group("global_step").begin == 0 and a.find_last_inner_group("global_step").begin == 10
+    assert a.find_last_inner_group("nope") is None and len(a.find_all_inner_groups("global_step")) == 2
+    g0 = a.find_first_inner_group("global_step")
+    assert g0.find_last_inner_span("rollout").duration == 4 and g0.find_all_inner_spans("train") == [] and g0.duration == 10
+    assert [g.begin for g in sp.span_group_batch_query_first([a, b], "global_step")] == [0, 0]
+    assert [g.begin for g in sp.span_group_batch_query_last([a, b], "global_step")] == [10, 20]
+    assert [g.begin for g in sp.span_group_batch_query_nth([a, b], "global_step", 1)] == [10, 20]
+    assert sp.span_group_batch_query_nth([a], "global_step", 5) == [] and len(sp.span_group_batch_query_all([a, b], "global_step")) == 4
+    m = sp.merge_span_group_trees(a, b)
+    assert [(g.begin, [s.name for s in g.inner]) for g in m.inner] == [(0, ["rollout", "train"]), (10, ["rollout"]), (20, ["train"])]
+    assert len(a.inner) == 2 and len(a.inner[0].inner) == 1                          # inputs untouched
+    assert all(g.outer is m for g in m.inner)
+    assert len(sp.merge_span_group_trees(a, a).inner[0].inner) == 1                  # duplicates collapse
+    with pytest.raises(ValueError, match="Overlap detected"):
+        sp.merge_span_group_trees(a, tree([(5, 15, [])]))
+    with pytest.raises(ValueError, match="Roots are not identical"):
+        sp.merge_span_group_trees(a, sp.SpanGroup("other"))
+    text = sp.span_group_tostring(a, born=0.0)
+    assert text.splitlines()[0].startswith("- root (0.000000") and "    - rollout (10.000000, 13.000000)" in text
+    chain = sp.span_group_stack_clone([a, g0])
+    assert [c.name for c in chain] == ["root", "global_step"] and chain[1].outer is chain[0] and chain[1].inner == []
+    s = sp.Span("open", 1.0)
+    assert not s.ended and sp.clone_span_or_group(s).begin == 1.0
+
+
+def test_span_tree_from_the_tracer():
+    from tunix_b200.perf import span as sp
+    from tunix_b200.perf.trace import PerfTracer
+    tr = PerfTracer()
+    for _ in range(2):
+        with tr.span_group("global_step"):
+            with tr.span("rollout"):
+                pass
+            with tr.span("train"):
+                pass
+    root = sp.tree_from_tracer(tr.spans())
+    steps = root.find_all_inner_groups("global_step")
+    assert len(steps) == 2 and [x.name for x in steps[0].inner] == ["rollout", "train"]
+    assert root.begin == steps[0].begin and root.end == steps[1].end and steps[0].end <= steps[1].begin

@@ -23,6 +23,7 @@ class MetricsLoggerOptions:
     use_tensorboard: bool = True
     use_wandb: bool = False
     use_jsonl: bool = True
+    enable_opentelemetry: bool = False         # also write every scalar as an OpenTelemetry gauge
 
 
 @dataclasses.dataclass

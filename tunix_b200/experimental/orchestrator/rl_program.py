@@ -31,25 +31,13 @@ import numpy as np
 
 from ..common.datatypes import GenerationArgs, Role
 from ..common.dispatch_window import DispatchWindow
+from ..common.logging_utils import summarize_list
+from ..common.tagging import prompt_coordinates, tag_prompt
 from . import dataset_utils
 from .batch_assembly import BatchConfig, create_batch_assembler, summarize_padding_stats
 
 log = logging.getLogger(__name__)
 _EOF = object()
-
-
-def prompt_coordinates(prompt_idx: int, full_batch_size: int) -> dict:
-    """Where a prompt sits in the dataset (tunix/experimental/common/tagging.py:24-48)."""
-    return {"prompt_idx": int(prompt_idx), "batch_idx": int(prompt_idx) // full_batch_size,
-            "intra_batch_idx": int(prompt_idx) % full_batch_size}
-
-
-def tag_prompt(item: dict, coordinates: Mapping[str, int]) -> dict:
-    """A copy of `item` whose metadata carries the coordinates (existing metadata keys win nothing: coordinates are
-    facts of this run)."""
-    out = dict(item)
-    out["metadata"] = {**dict(item.get("metadata") or {}), **coordinates}
-    return out
 
 
 def _generation_metrics(groups) -> dict:
@@ -371,7 +359,7 @@ class StandardRLProgram(RLProgram):
                     self.policy_version = v if v is not None else self.policy_version + 1
                 gen_metrics = _generation_metrics([g.responses for g in groups])
                 log.info("[pipeline] COMMIT step=%d consumed_version=%d rollout_versions=%s prompts=%s", step, consumed_version,
-                         [int(g.responses[0].policy_version) for g in groups], [g.prompt_id for g in groups])
+                         [int(g.responses[0].policy_version) for g in groups], summarize_list([g.prompt_id for g in groups], 8))
                 self.dispatch_window.record_committed_groups(groups)
                 for g in groups:
                     self._prompts.pop(g.prompt_id, None)

@@ -3,12 +3,19 @@
 `log(prefix, name, value, mode, step)` records into a per-(prefix, mode, name) history and
 forwards scalars to every backend (TensorBoard, W&B offline, JSONL, user factories). Only
 rank 0 writes. Perplexity is aggregated as a geometric mean, everything else arithmetically.
+
+With `enable_opentelemetry` every scalar is also set on a synchronous OpenTelemetry gauge (`:331-381`): instrument
+`tunix.training.<name>` for the known training metrics, `tunix.<normalised name>` otherwise; prefix and mode travel
+as attributes; the logical step is a gauge of its own (`tunix.training.step`), because a step attribute would make a
+new time series per step. `sft.otel_wandb.WandbMetricsExporter` turns those gauges into W&B log calls.
 """
 from __future__ import annotations
 
 import collections
 import json
+import logging
 import os
+import re
 import threading
 import time
 from typing import Any, Callable, Optional, Protocol
@@ -69,6 +76,53 @@ class WandbBackend:
         self._run.finish()
 
 
+OTEL_STEP_METRIC = "tunix.training.step"
+OTEL_PREFIX_ATTRIBUTE = "tunix.metrics.prefix"
+OTEL_MODE_ATTRIBUTE = "tunix.training.mode"
+_OTEL_KNOWN = {"loss": "tunix.training.loss", "perplexity": "tunix.training.perplexity",
+               "learning_rate": "tunix.training.learning_rate", "grad_norm": "tunix.training.grad_norm",
+               "step_time_sec": "tunix.training.step_time", "tflops_per_step": "tunix.training.tflops_per_step"}
+
+
+def otel_metric_name(metric_name: str) -> str:
+    """A valid, namespaced instrument name: known training metrics keep a stable name, anything else becomes
+    `tunix.<name with runs of other characters replaced by dots, lower case>`."""
+    if metric_name in _OTEL_KNOWN:
+        return _OTEL_KNOWN[metric_name]
+    norm = re.sub(r"[^a-zA-Z0-9_.-]+", ".", metric_name).strip(".") or "unnamed"
+    return f"tunix.{norm.lower()}"
+
+
+class OtelGaugeEmitter:
+    def __init__(self, meter_provider=None):
+        from opentelemetry import metrics as otel_metrics
+        provider = meter_provider if meter_provider is not None else otel_metrics.get_meter_provider()
+        self._meter = provider.get_meter("tunix_b200")
+        self._gauges: dict = {}
+        self._last_step: dict = {}
+        self._lock = threading.Lock()
+
+    def _gauge(self, name: str, unit: str = "1"):
+        with self._lock:
+            g = self._gauges.get(name)
+            if g is None:
+                g = self._gauges[name] = self._meter.create_gauge(name, unit=unit)
+            return g
+
+    def emit(self, prefix: str, metric_name: str, value: float, mode, step: Optional[int]) -> None:
+        attrs = {OTEL_MODE_ATTRIBUTE: str(mode)}
+        if prefix:
+            attrs[OTEL_PREFIX_ATTRIBUTE] = prefix
+        self._gauge(otel_metric_name(metric_name)).set(value, attrs)
+        if step is None:
+            return
+        with self._lock:
+            if self._last_step.get((prefix, str(mode))) == step:
+                return
+            self._last_step[(prefix, str(mode))] = step
+        self._gauge(OTEL_STEP_METRIC, "{step}").set(int(step), attrs)
+
+
 def _is_main_process() -> bool:
     try:
         import torch.distributed as dist
@@ -78,9 +132,17 @@ def _is_main_process() -> bool:
 
 
 class MetricsLogger:
-    def __init__(self, metrics_logger_options: Optional[MetricsLoggerOptions] = None, metric_prefix: str = ""):
+    def __init__(self, metrics_logger_options: Optional[MetricsLoggerOptions] = None, metric_prefix: str = "",
+                 otel_meter_provider=None):
         self._history: dict = collections.defaultdict(list)
         self._backends: list = []
+        self._otel: Optional[OtelGaugeEmitter] = None
+        if metrics_logger_options is not None and getattr(metrics_logger_options, "enable_opentelemetry", False) \
+                and _is_main_process():
+            try:
+                self._otel = OtelGaugeEmitter(otel_meter_provider)
+            except ImportError:
+                logging.getLogger(__name__).warning("enable_opentelemetry is set but the opentelemetry package is missing")
         self._prefix = metric_prefix
         self._lock = threading.Lock()
         opts = metrics_logger_options
@@ -119,6 +181,11 @@ class MetricsLogger:
             self._history[key].append(v)
         for b in self._backends:
             b.log_scalar(key, v, step=step)
+        if self._otel is not None:
+            try:
+                self._otel.emit(metrics_prefix, metric_name, v, mode, step)
+            except Exception:                       # telemetry never takes a training step down
+                logging.getLogger(__name__).exception("failed to emit OpenTelemetry metric %s", key)
 
     def metric_exists(self, metrics_prefix: str, metric_name: str, mode) -> bool:
         return len(self._history.get(self._key(metrics_prefix, metric_name, mode), ())) > 0
