@@ -27,6 +27,10 @@ from ..agents.agent_types import Trajectory, TrajectoryStatus
 from ..utils import concat_conversation
 
 
+class _EpisodeTimeout(Exception):
+    """The episode's wall-clock budget ran out inside a model call or an environment step."""
+
+
 class TrajectoryCollectEngine:
     def __init__(self, agent, env, *, model_call: Callable[..., Awaitable[dict]], tokenizer=None, chat_parser=None,
                  max_steps: int = 10, gamma: float = 1.0, timeout: float = 600.0, env_step_timeout: Optional[float] = None,
@@ -86,6 +90,8 @@ class TrajectoryCollectEngine:
         except asyncio.CancelledError:
             traj.status = TrajectoryStatus.CANCELLED
             raise
+        except _EpisodeTimeout:
+            traj.status = TrajectoryStatus.TIMEOUT
         except asyncio.TimeoutError:
             traj.status = TrajectoryStatus.ENV_TIMEOUT
         except Exception as e:  # model, env or reward failure: the episode is invalid, the pipeline goes on
@@ -137,8 +143,15 @@ class TrajectoryCollectEngine:
             self._prompt_tokens = np.asarray(self._render_prompt(False), np.int64)
             self._context = list(self._prompt_tokens)
         budget = None if self.max_response_length is None else max(self.max_response_length - used_tokens, 1)
-        out = await self.model_call(chat_completions=self.agent.chat_completions, prompt_token_ids=list(self._context),
-                                    max_tokens=budget)
+        # the model call may take no longer than what is left of the episode's budget; a call that is cut off is
+        # cancelled (its client sees CancelledError) and the episode ends as TIMEOUT
+        remaining = self.timeout - (time.monotonic() - self._start)
+        try:
+            out = await asyncio.wait_for(self.model_call(chat_completions=self.agent.chat_completions,
+                                                         prompt_token_ids=list(self._context), max_tokens=budget),
+                                         max(remaining, 1e-3))
+        except asyncio.TimeoutError:
+            raise _EpisodeTimeout() from None
         action = await self.agent.update_from_model_async(out["text"])
         step = self.agent.get_current_step()
         a_tok = np.asarray(out.get("tokens", []), np.int64)
@@ -150,7 +163,14 @@ class TrajectoryCollectEngine:
         self._context.extend(a_tok.tolist())
         t0 = time.monotonic()
         coro = self.env.step_async(action.action)
-        obs, reward, done, info = await (asyncio.wait_for(coro, self.env_step_timeout) if self.env_step_timeout else coro)
+        remaining = self.timeout - (time.monotonic() - self._start)
+        limit = min(self.env_step_timeout, remaining) if self.env_step_timeout else remaining
+        try:
+            obs, reward, done, info = await asyncio.wait_for(coro, max(limit, 1e-3))
+        except asyncio.TimeoutError:
+            if self.env_step_timeout and self.env_step_timeout <= remaining:
+                raise                                        # the environment's own limit: ENV_TIMEOUT
+            raise _EpisodeTimeout() from None
         traj.env_time["step_latency"].append(time.monotonic() - t0)
         n_before = len(self.agent.chat_completions)
         await self.agent.update_from_env_async(obs, reward, done, info)
