@@ -70,7 +70,8 @@ class AgenticGRPOLearner(AgenticRLLearner):
         ex = common.TrainExample(prompt_ids=t_(pids), prompt_mask=t_(pmask), completion_ids=t_(cids),
                                  completion_mask=t_(cmask), advantages=t_(np.asarray(adv, np.float32)),
                                  old_per_token_logps=t_(old) if cfg.use_rollout_logps else None,
-                                 policy_version=self.policy_version)
+                                 policy_version=min((int(t["policy_version"]) for t in trajs if t.get("policy_version") is not None),
+                                                    default=self.policy_version))
         if getattr(cfg, "beta", 0.0) != 0.0 and not defer_logps:
             ctx_mask = t_((cids != self.pad_id).astype(np.int32))
             ex.ref_per_token_logps = self.rl_cluster.get_ref_per_token_logps(

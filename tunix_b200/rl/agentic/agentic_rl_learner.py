@@ -18,6 +18,8 @@ import threading
 import time
 from typing import Any, Callable, Iterable, Optional, Sequence
 
+import logging
+
 import numpy as np
 import torch
 
@@ -29,6 +31,9 @@ from .environments.task_environment import TaskEnvironment
 from .pipeline.rollout_orchestrator import RolloutOrchestrator
 from .trajectory.trajectory_collect_engine import TrajectoryCollectEngine
 from .utils import RolloutSyncLock
+
+
+log = logging.getLogger(__name__)
 
 
 class _ModelCallBatcher:
@@ -106,7 +111,8 @@ class AgenticRLLearner(abc.ABC):
         if reward_fns:
             cls = function_registry.get_reward_manager("agentic-sequence-level")
             self.reward_manager = cls(reward_fns, algo_config)
-        self.policy_version = 0
+        self.policy_version = int(rl_cluster.global_steps)      # a resumed run goes on counting from the restored step
+        self.stale_dropped = 0
         self.sync_lock = RolloutSyncLock()
         self.pad_id, self.eos_id = rl_cluster.rollout.pad_id(), rl_cluster.rollout.eos_id()
         self.device = next(rl_cluster.train_actor.parameters()).device
@@ -281,6 +287,8 @@ class AgenticRLLearner(abc.ABC):
                 if kind == "group":
                     self._log_trajectories(payload)
                     ex = self._process_group(payload, defer_logps=self.pack_first)
+                    if ex is not None and self._too_old(ex):
+                        ex = None
                     if ex is not None:
                         pending.append(ex)
                         if not self.pack_first:
@@ -314,6 +322,18 @@ class AgenticRLLearner(abc.ABC):
             for _ in range(self.off_policy_steps + 2):      # a producer parked on the permit must not outlive the loop
                 permits.release()
             self.close()
+
+    def _too_old(self, ex) -> bool:
+        """A group generated more than `off_policy_steps` weight versions ago is not trained on
+        (tunix/rl/agentic/agentic_rl_learner.py:1273-1303); a version of -1 or None means "unknown" and passes."""
+        v = getattr(ex, "policy_version", None)
+        if v is None or int(v) < 0 or self.policy_version - int(v) <= self.off_policy_steps:
+            return False
+        self.stale_dropped += 1
+        log.warning("skipping a group generated at policy version %d: current version %d, off_policy_steps %d", int(v),
+                    self.policy_version, self.off_policy_steps)
+        self.rl_cluster.buffer_metrics({"trajectory/stale_dropped": (1.0, np.sum)}, Mode.TRAIN)
+        return True
 
     def close(self) -> None:
         self.rl_cluster.close()
