@@ -1,5 +1,6 @@
-"""Trajectory stores (tunix/experimental/trajectory/*): an append-only record of rollouts for inspection and
-replay. Records are plain dicts (`trajectory_id`, `group_id`, `policy_version`, `steps`, `reward`, free-form
+"""Record-level trajectory stores (tunix/experimental/trajectory/*): an append-only record of rollouts for inspection
+and replay. (The typed, step-level ATIF stores are `in_memory_store`, `file_store` and `sql_store` beside this module;
+`open_store` gives the explorer a record view of those too.) Records are plain dicts (`trajectory_id`, `group_id`, `policy_version`, `steps`, `reward`, free-form
 `metadata`); the in-memory store indexes them, the file store appends JSON lines through a writer thread so that
 producers never wait on the disk."""
 from __future__ import annotations
@@ -237,6 +238,55 @@ def record_from_trajectory(traj, group_id=None, policy_version: int = 0, **metad
     return rec
 
 
+def record_from_atif(traj) -> dict:
+    """The record form of a stored ATIF trajectory (`trajectory.TunixTrajectory`), as the explorer shows it."""
+    from . import trajectory as T
+    steps, conversation = [], []
+    for s in traj.steps:
+        if isinstance(s, T.TunixAgentStep):
+            calls = [{"name": c.function_name, "arguments": c.arguments} for c in (s.tool_calls or [])]
+            steps.append({"model_response": s.message, "thought": s.reasoning_content or "", "action": calls or None,
+                          "observation": None, "reward": 0.0, "done": False, "mc_return": float(s.mc_return or 0.0)})
+            conversation.append({"role": "assistant", "content": s.message})
+        else:
+            if steps and steps[-1]["observation"] is None and s.step_id > 0:
+                steps[-1].update(observation=s.message, reward=float(getattr(s, "reward", None) or 0.0),
+                                 done=bool(getattr(s, "done", None) or False))
+            if s.message:
+                conversation.append({"role": "system" if T.Source(s.source) == T.Source.SYSTEM else "user", "content": s.message})
+    versions = getattr(traj, "target_policy_versions", None) or [0]
+    return {"trajectory_id": traj.trajectory_id, "group_id": getattr(traj, "prompt_id", None), "policy_version": int(min(versions)),
+            "steps": steps, "reward": float(getattr(traj, "total_reward", None) or 0.0), "created_at": None,
+            "metadata": {"status": getattr(traj, "status", None), "group_index": getattr(traj, "group_index", None),
+                         "session_id": traj.session_id, "conversation": conversation}}
+
+
+class AtifRecordView:
+    """Read-only record view over a step-level ATIF store, for the explorer."""
+
+    def __init__(self, store):
+        self._store = store
+
+    def read(self) -> Iterator[dict]:
+        for meta in self._store.get_trajectories_metadata():
+            yield record_from_atif(self._store.get_trajectories([meta.trajectory_id])[0])
+
+    def put(self, record: dict) -> str:
+        raise TypeError("an ATIF store is written step by step (`add_step`), not from records")
+
+    def close(self) -> None:
+        self._store.close()
+
+
 def open_store(path: str):
-    """Open a store by file type: `.db` / `.sqlite` -> SQL, anything else -> JSON lines."""
+    """Open a store by what the path is: a directory (or `atif:<directory>`) -> ATIF file store, `atif:<sqlite URL or
+    .db path>` -> ATIF SQL store (both as read-only record views), `.db` / `.sqlite` -> record-level SQL store, anything
+    else -> record-level JSON lines."""
+    if path.startswith("atif:") or os.path.isdir(path):
+        target = path[len("atif:"):] if path.startswith("atif:") else path
+        if os.path.isdir(target):
+            from .file_store import FileTrajectoryStore as _AtifFiles
+            return AtifRecordView(_AtifFiles(target))
+        from .sql_store import SqlTrajectoryStore
+        return AtifRecordView(SqlTrajectoryStore(target))
     return SqliteTrajectoryStore(path) if path.endswith((".db", ".sqlite", ".sqlite3")) else FileTrajectoryStore(path)
