@@ -284,3 +284,16 @@ def test_program_on_real_workers_with_checkpoint_resume(tmp_path):
     asyncio.run(eng2.close())
     for w in workers2:
         w.stop()
+
+
+def test_program_logs_consumed_rollouts_to_a_step_level_store():
+    from tunix_b200.experimental.trajectory.in_memory_store import InMemoryTrajectoryStore
+    store = InMemoryTrajectoryStore()
+    eng = DistributedRLEngine([_EchoRollout("r0")], {Role.ACTOR: _Trainer({})})
+    hist = _program(_prompts(2), 1, trajectory_store=store, sync_weights=False, checkpoint_every=0).run(eng)
+    metas = store.get_trajectories_metadata()
+    assert len(metas) == hist[0]["num_rollouts"] == 8 and {m.prompt_id for m in metas} == {"p0", "p1"}
+    full = store.get_trajectories([metas[0].trajectory_id])[0]
+    assert len(full.steps) == 2 and len(full.steps[1].assistant_tokens) == 4 and full.extra["consumed_at_step"] == 0
+    assert metas[0].trajectory_id.startswith("req_p") and sorted(m.group_index for m in metas if m.prompt_id == "p0") == [0, 1, 2, 3]
+    asyncio.run(eng.close())

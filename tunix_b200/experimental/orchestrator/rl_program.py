@@ -259,7 +259,7 @@ class StandardRLProgram(RLProgram):
                 if not payloads:
                     self._filter_group(group, "no learning signal")
                     continue
-                group.payloads = list(payloads)
+                group.payloads, group.responses = list(payloads), valid        # payload i belongs to response i from here on
                 log.info("[pipeline] ARRIVED prompt_id=%s batch_idx=%s policy_version=%d", group.prompt_id,
                          (group.item.get("metadata") or {}).get("batch_idx"), int(valid[0].policy_version))
                 await self._scored_q.put(group)
@@ -279,6 +279,26 @@ class StandardRLProgram(RLProgram):
 
     def _store_trajectories(self, groups, step: int) -> None:
         if self._trajectory_store is None:
+            return
+        if hasattr(self._trajectory_store, "add_step"):          # a step-level ATIF store
+            from ..trajectory import trajectory as T
+            from ..trajectory.converter import create_trajectory_metadata, log_trajectory
+            for g in groups:
+                for i, (p, r) in enumerate(zip(g.payloads, g.responses)):
+                    ex = p.example if isinstance(p.example, Mapping) else {}
+                    meta = create_trajectory_metadata(f"{r.request_id}", prompt_id=g.prompt_id,
+                                                      group_index=int((r.metadata or {}).get("group_index", i)))
+                    meta.status, meta.total_reward = "SUCCEEDED", float(p.reward or 0.0)
+                    meta.target_policy_versions = [int(p.policy_version)]
+                    meta.extra = {"consumed_at_step": step}
+                    steps = [T.TunixEnvStep(step_id=0, source="user", message=str(g.item.get("prompt", "")),
+                                            env_tokens=np.asarray(ex.get("prompt_ids", ()), np.int64)),
+                             T.TunixAgentStep(step_id=1, source="agent", message=r.text or "", llm_call_count=1,
+                                              assistant_tokens=np.asarray(r.tokens, np.int64),
+                                              assistant_masks=np.ones(len(r.tokens), np.int64),
+                                              logprobs=None if r.logprobs is None else np.asarray(r.logprobs, np.float32),
+                                              policy_version=int(r.policy_version))]
+                    log_trajectory(self._trajectory_store, meta.create_trajectory(steps))
             return
         from ..trajectory.store import new_record
         for g in groups:
