@@ -2,6 +2,7 @@
 (test model: tunix/experimental/orchestrator/{distributed_rl_engine,rl_program}_test.py). CPU, tiny model; worker
 failures are scripted on the host."""
 import asyncio
+import time
 
 import numpy as np
 import pytest
@@ -296,4 +297,141 @@ def test_program_logs_consumed_rollouts_to_a_step_level_store():
     full = store.get_trajectories([metas[0].trajectory_id])[0]
     assert len(full.steps) == 2 and len(full.steps[1].assistant_tokens) == 4 and full.extra["consumed_at_step"] == 0
     assert metas[0].trajectory_id.startswith("req_p") and sorted(m.group_index for m in metas if m.prompt_id == "p0") == [0, 1, 2, 3]
+    asyncio.run(eng.close())
+
+
+def test_multi_turn_episodes_through_the_distributed_stack():
+    """FrozenLake episodes run on episode workers (agent + environment + sampler); the program trains on the model's
+    tokens only, with the environment's reward; weights are swapped while episodes are in flight."""
+    import threading
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200.experimental.common.datatypes import WorkerState
+    from tunix_b200.experimental.orchestrator.algorithm_adapter import env_reward
+    from tunix_b200.experimental.rl.agentic import registry as registries
+    from tunix_b200.experimental.rollout import sampler as sampler_lib
+    from tunix_b200.experimental.worker.agentic_rollout_worker import AgenticRolloutWorker
+    from tunix_b200.rl.agentic.environments.frozenlake_environment import FrozenLakeAgent, FrozenLakeEnv, shortest_path
+    from tunix_b200.rl.agentic.parser.chat_template_parser import get_parser
+    for reg, name, cls in ((registries.AGENT_REGISTRY, "frozenlake", FrozenLakeAgent), (registries.ENV_REGISTRY, "frozenlake", FrozenLakeEnv)):
+        if name not in reg:
+            reg.register(name)(cls)
+    tok = CharTok()
+
+    class Scripted:
+        """Walks the shortest path for even seeds, wanders for odd ones; counts calls per policy version."""
+        def __init__(self):
+            self.policy_version, self.calls, self.lock, self.hold, self.turns = 0, [], threading.Lock(), None, {}
+
+        async def sample(self, requests):
+            out = []
+            for r in requests:
+                if self.hold is not None:
+                    await self.hold.wait()
+                with self.lock:
+                    self.calls.append((r.request_id, self.policy_version, r.sampling_params.seed))
+                good = r.sampling_params.seed % 2 == 0
+                turn = self.turns[r.request_id] = self.turns.get(r.request_id, -1) + 1
+                seed = int(str(r.route_key).replace("lake", "").replace("held", "0"))
+                path = shortest_path(FrozenLakeEnv({"seed": seed, "size": 4, "p": 0.8, "max_steps": 8}).grid)
+                reply = f"```{path[min(turn, len(path) - 1)].capitalize() if good else 'Up'}```"
+                ids = tok.encode(reply)
+                out.append(sampler_lib.SamplingResponse(r.request_id, ids, [-0.3] * len(ids), reply, "stop", self.policy_version))
+            return out
+
+        async def pre_weight_sync(self, version): ...
+        async def weight_sync(self, version): ...
+
+        async def post_weight_sync(self, version):
+            self.policy_version = version
+    samplers = [Scripted(), Scripted()]
+    workers = [AgenticRolloutWorker(f"ep-{i}", s, tok, chat_parser=get_parser("qwen"), eos_ids=[2], default_agent="frozenlake",
+                                    default_env="frozenlake") for i, s in enumerate(samplers)]
+    for w in workers:
+        w.start()
+    tr = _Trainer({})
+    eng = DistributedRLEngine(workers, {Role.ACTOR: tr})
+    data = [{"prompt_id": f"lake{i}", "task": {"seed": i, "size": 4, "p": 0.8, "max_steps": 8}, "max_turns": 8} for i in range(4)]
+    prog = StandardRLProgram(GRPOAdapter(reward_fn=env_reward), data, 2, num_generations=4, batch_size=2,
+                             batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=4096, max_prompt_length=1024,
+                                                      max_response_length=2048),
+                             generation_args=GenerationArgs(max_tokens=16, temperature=1.0), poll_timeout_s=0.05, checkpoint_every=0)
+    seen_batches = []
+    real = tr.submit
+
+    def spy(req):
+        if req.get("op") == "fwd_bwd":
+            seen_batches.append(req["batch"])
+        return real(req)
+    tr.submit = spy
+    hist = prog.run(eng)
+    assert [h["step"] for h in hist] == [0, 1] and all(h["num_rollouts"] == 8 for h in hist)
+    assert all(0.0 < h["reward_mean"] < 1.0 and h["reward_std"] > 0 for h in hist)          # half of each group reaches the goal
+    b = seen_batches[0]
+    m = np.asarray(b["completion_mask"])
+    assert 0 < m.sum() < (np.asarray(b["input_tokens"]) != 0).sum()                         # environment and prompt tokens carry no loss
+    assert all(w.state == WorkerState.READY and w.policy_version == 2 for w in workers) and sum(w.served for w in workers) == 16
+    assert {v for s in samplers for _, v, _ in s.calls} == {0, 1}                            # step 1 was generated with version 1
+    # a sync arriving while an episode waits for its model: the episode is held, then goes on under the new version
+    hold = samplers[0].hold = asyncio.Event()
+    req = eng._build_rollout_requests([dict(data[0], prompt_id="held")], num_generations=1, policy_version=2)[0]
+    res = {}
+    t = threading.Thread(target=lambda: res.setdefault("r", workers[0].submit(req)))
+    t.start()
+    deadline = time.monotonic() + 5
+    while workers[0].state != WorkerState.BUSY and time.monotonic() < deadline:
+        time.sleep(0.01)
+    workers[0].sync_weights(3)
+    assert workers[0].state == WorkerState.BUSY and workers[0].policy_version == 3
+    workers[0]._loop.call_soon_threadsafe(hold.set)
+    t.join(10)
+    assert res["r"].metadata["is_valid"] and max(res["r"].metadata["policy_versions"]) == 3
+    asyncio.run(eng.close())
+    for w in workers:
+        w.stop()
+        assert w.state == WorkerState.STOPPED
+
+
+def test_sampler_adapter_batches_concurrent_requests_within_its_window():
+    from tunix_b200.experimental.rollout import sampler as sampler_lib
+    calls = []
+
+    class Engine:
+        def __call__(self, prompt_token_ids, max_generation_steps, temperature, top_p, top_k, seed, return_logprobs, **kw):
+            calls.append((len(prompt_token_ids), max_generation_steps, temperature, seed))
+            import types
+            return types.SimpleNamespace(tokens=[[p[0] + 1] * max_generation_steps for p in prompt_token_ids],
+                                         logprobs=[[-1.0] * max_generation_steps for _ in prompt_token_ids], text=None)
+    ad = sampler_lib.EngineSamplerAdapter(Engine(), batch_window_s=0.01, max_batch=3)
+    mk = lambda i, t=1.0, n=4: sampler_lib.SamplingRequest(f"r{i}", [10 * i], sampler_lib.SamplingParams(max_tokens=n, temperature=t, seed=i))
+
+    async def go():
+        return await asyncio.gather(*(ad.sample([mk(i, n=4 + i)]) for i in range(4)), ad.sample([mk(9, t=0.5)]))
+    out = asyncio.run(go())
+    sizes = sorted(c[0] for c in calls)
+    assert sizes == [1, 1, 3] and ad.engine_calls == 3                 # 3 + 1 of one setting (batch limit 3), 1 of another
+    assert (3, 4, 1.0, 0) in calls                                     # shortest limit and the first request's seed
+    assert [o[0].request_id for o in out] == ["r0", "r1", "r2", "r3", "r9"] and out[1][0].token_ids[0] == 11
+    solo = sampler_lib.EngineSamplerAdapter(Engine())
+    calls.clear()
+    asyncio.run(solo.sample([mk(1), mk(2)]))
+    assert sorted(c[3] for c in calls) == [1, 2] and all(c[0] == 1 for c in calls)      # without a window: own call, own seed
+
+
+def test_polling_does_not_spin_while_nothing_is_in_flight():
+    """A dispatcher parked at the window leaves nothing in flight; the polling stage must wait, not burn the loop."""
+    class CountingEngine(DistributedRLEngine):
+        polls = 0
+
+        async def poll_rollouts(self, timeout_s=1.0):
+            type(self).polls += 1
+            return await super().poll_rollouts(timeout_s)
+
+    class SlowTrainer(_Trainer):
+        def submit(self, req):
+            if req["op"] == "fwd_bwd":
+                time.sleep(0.3)
+            return super().submit(req)
+    eng = CountingEngine([_EchoRollout("r0")], {Role.ACTOR: SlowTrainer({})})
+    _program(_prompts(4), 2, sync_weights=False, checkpoint_every=0).run(eng)
+    assert CountingEngine.polls < 200
     asyncio.run(eng.close())

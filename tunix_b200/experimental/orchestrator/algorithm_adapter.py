@@ -20,11 +20,23 @@ import numpy as np
 from ..common.datatypes import RLTrainerPayload
 
 
+def env_reward(item: dict, r) -> float:
+    """The reward an episode's environment gave (multi-turn workers report it as `trajectory_reward`)."""
+    return float((r.metadata or {}).get("trajectory_reward", 0.0))
+
+
 def _base_example(item: dict, r, advantages: np.ndarray) -> dict:
+    """A response of a multi-turn worker brings its own prompt (rendered by the agent) and a mask that leaves the
+    environment's tokens out of the loss; a single-call response uses the item's prompt and trains on every token."""
     n = len(r.tokens)
-    ex = {"prompt_ids": np.asarray(item["prompt_ids"], np.int32), "completion_ids": np.asarray(r.tokens, np.int32),
-          "completion_mask": np.ones(n, np.float32), "advantages": np.asarray(advantages, np.float32),
-          "lineage": (r.metadata or {}).get("lineage"), "prompt_id": str(item.get("prompt_id", ""))}
+    md = r.metadata or {}
+    mask = np.asarray(md["conversation_masks"], np.float32) if md.get("conversation_masks") is not None else np.ones(n, np.float32)
+    if md.get("masked_out"):
+        mask = np.zeros(n, np.float32)
+    prompt = md["prompt_token_ids"] if md.get("prompt_token_ids") else item["prompt_ids"]
+    ex = {"prompt_ids": np.asarray(prompt, np.int32), "completion_ids": np.asarray(r.tokens, np.int32),
+          "completion_mask": mask, "advantages": np.asarray(advantages, np.float32),
+          "lineage": md.get("lineage"), "prompt_id": str(item.get("prompt_id", ""))}
     if r.logprobs is not None:
         ex["old_per_token_logps"] = np.asarray(r.logprobs, np.float32)
     return ex

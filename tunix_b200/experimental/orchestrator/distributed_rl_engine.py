@@ -117,12 +117,17 @@ class DistributedRLEngine:
                                  "carry a unique 'prompt_id' (as an attribute or a dict key).")
             pid = str(pid)
             ids = _get(p, "prompt_ids", _get(p, "prompt_token_ids"))
+            item_meta = dict(_get(p, "metadata") or {})
+            for k in ("task", "env_config", "agent", "env", "agent_kwargs", "env_kwargs", "max_turns", "max_response_length"):
+                if _get(p, k) is not None:
+                    item_meta.setdefault(k, _get(p, k))       # what an episode worker builds its agent and environment from
             if ids is None:
-                raise ValueError(f"Prompt {pid!r} has no 'prompt_ids' (token ids)")
+                if "task" not in item_meta and "env_config" not in item_meta:
+                    raise ValueError(f"Prompt {pid!r} has neither 'prompt_ids' (token ids) nor a 'task' for an episode worker")
+                ids = []                                      # the agent renders the prompt from the task
             gen = {**base_gen, **dict(_get(p, "generation_kwargs") or {})}
             if _get(p, "max_response_length") is not None:
                 gen["max_tokens"] = min(int(_get(p, "max_response_length")), int(gen.get("max_tokens", 1 << 30)))
-            item_meta = dict(_get(p, "metadata") or {})
             for g in range(num_generations):
                 meta = {**base_meta, **item_meta, "prompt_id": pid, "group_index": g, "num_generations": num_generations}
                 fields = {k: gen[k] for k in _REQUEST_FIELDS if gen.get(k) is not None}
@@ -182,11 +187,11 @@ class DistributedRLEngine:
         return out
 
     async def poll_rollouts(self, timeout_s: float = 1.0) -> list:
-        if self._inflight == 0 and self._done.empty():
-            return []
         got = self._drain(0.0)
         if not got and timeout_s > 0:
-            deadline = time.monotonic() + timeout_s                 # short naps keep the event loop's other stages running
+            # short naps keep the event loop's other stages running; with nothing in flight the call still takes its
+            # time, so that a caller's polling loop cannot spin
+            deadline = time.monotonic() + timeout_s
             while not got and time.monotonic() < deadline:
                 await asyncio.sleep(0.002)
                 got = self._drain(0.0)

@@ -222,7 +222,7 @@ class StandardRLProgram(RLProgram):
                     await asyncio.sleep(0.01)
                     continue
                 if not completed:
-                    await asyncio.sleep(0)
+                    await asyncio.sleep(0.002)          # an engine that answers at once must not turn this loop into a spin
                     continue
                 self._in_flight -= len(completed)
                 for r in completed:

@@ -76,9 +76,13 @@ class AsyncSampler(Protocol):
 
 class EngineSamplerAdapter:
     def __init__(self, engine, *, tokenizer=None, participant=None, eos_tokens: Optional[Sequence[int]] = None,
-                 max_threads: int = 64):
+                 max_threads: int = 64, batch_window_s: float = 0.0, max_batch: int = 64):
         """`engine`: an `EngineServer` (has `submit`) or a batch callable. `participant`: an
-        `experimental.weight_sync.participants.EngineParticipant` that knows where new weights come from."""
+        `experimental.weight_sync.participants.EngineParticipant` that knows where new weights come from.
+        `batch_window_s` > 0 (batch callables only): requests that arrive within the window and share their sampling
+        settings are served by ONE engine call of up to `max_batch` prompts, with the shortest token limit among them
+        and the first request's seed; episodes that run concurrently then decode together instead of one after the
+        other. 0 keeps one engine call, and the request's own seed, per request."""
         from concurrent.futures import ThreadPoolExecutor
         self.engine, self.tokenizer, self.participant = engine, tokenizer, participant
         self.eos_tokens = list(eos_tokens or [])
@@ -88,6 +92,10 @@ class EngineSamplerAdapter:
         self._paused = False
         self._gate: Optional[asyncio.Event] = None
         self.policy_version = 0
+        self._window, self._max_batch = float(batch_window_s), max(int(max_batch), 1)
+        self._pending: list = []
+        self._flusher: Optional[asyncio.Task] = None
+        self.engine_calls = 0
 
     # ------------------------------------------------------------------ lifecycle
     def initialize(self) -> None:
@@ -142,6 +150,49 @@ class EngineSamplerAdapter:
             return SamplingResponse(req.request_id, error=e, finish_reason="error", policy_version=self.policy_version,
                                     latency_s=time.perf_counter() - t0)
 
+    def _many(self, reqs: Sequence[SamplingRequest]) -> list:
+        """One engine call for requests that share their sampling settings."""
+        t0 = time.perf_counter()
+        try:
+            sp = reqs[0].sampling_params
+            limit = min(r.sampling_params.max_tokens for r in reqs)
+            out = self.engine(prompt_token_ids=[list(r.prompt_token_ids) for r in reqs], max_generation_steps=limit,
+                              temperature=sp.temperature, top_p=sp.top_p, top_k=sp.top_k, seed=sp.seed, return_logprobs=sp.return_logprobs,
+                              **({"eos_tokens": self.eos_tokens} if self.eos_tokens else {}))
+            res = []
+            for i, r in enumerate(reqs):
+                toks = [int(t) for t in np.asarray(out.tokens[i])]
+                lps = None if out.logprobs is None or not sp.return_logprobs else [float(x) for x in np.asarray(out.logprobs[i])[:len(toks)]]
+                res.append(SamplingResponse(r.request_id, toks, lps, self.tokenizer.decode(toks) if self.tokenizer is not None else None,
+                                            self._finish(toks), self.policy_version, time.perf_counter() - t0))
+            return res
+        except BaseException as e:
+            return [SamplingResponse(r.request_id, error=e, finish_reason="error", policy_version=self.policy_version,
+                                     latency_s=time.perf_counter() - t0) for r in reqs]
+
+    async def _flush_later(self) -> None:
+        await asyncio.sleep(self._window)
+        loop = asyncio.get_running_loop()
+        while self._pending:
+            first = self._pending[0][0].sampling_params
+            key = (first.temperature, first.top_p, first.top_k, first.return_logprobs)
+            take = [p for p in self._pending if (p[0].sampling_params.temperature, p[0].sampling_params.top_p, p[0].sampling_params.top_k,
+                                                 p[0].sampling_params.return_logprobs) == key][: self._max_batch]
+            ids = {id(p) for p in take}
+            self._pending = [p for p in self._pending if id(p) not in ids]
+            self.engine_calls += 1
+            outs = await loop.run_in_executor(self._pool, self._many, [p[0] for p in take])
+            for (_, fut), o in zip(take, outs):
+                if not fut.done():
+                    fut.set_result(o)
+
+    async def _batched(self, req: SamplingRequest) -> SamplingResponse:
+        fut = asyncio.get_running_loop().create_future()
+        self._pending.append((req, fut))
+        if self._flusher is None or self._flusher.done():
+            self._flusher = asyncio.create_task(self._flush_later())
+        return await fut
+
     async def sample(self, requests: Sequence[SamplingRequest]) -> list:
         if self._gate is None:
             await self.start()
@@ -149,7 +200,11 @@ class EngineSamplerAdapter:
         loop = asyncio.get_running_loop()
         self._inflight += len(requests)
         try:
-            out = await asyncio.gather(*(loop.run_in_executor(self._pool, self._one, r) for r in requests))
+            if self._window > 0 and not self._server:
+                out = await asyncio.gather(*(self._batched(r) for r in requests))
+            else:
+                self.engine_calls += len(requests)
+                out = await asyncio.gather(*(loop.run_in_executor(self._pool, self._one, r) for r in requests))
         finally:
             self._inflight -= len(requests)
         self._served += len(requests)
