@@ -109,3 +109,23 @@ def test_reads_a_checkpoint_that_orbax_wrote_in_its_ocdbt_layout():
         step, meta = CheckpointManager(tmp).maybe_restore(net)
         assert step == 1 and meta == {}
         assert torch.equal(net.w2.kernel.value.detach(), torch.from_numpy(tree[("w2", "kernel", "value")]))
+
+
+def test_family_modules_give_the_family_class_and_presets():
+    import pytest
+    from tunix_b200.models.gemma3 import model as gemma3_lib
+    from tunix_b200.models.llama3 import model as llama_lib, params as llama_params
+    from tunix_b200.models.qwen3 import model as qwen3_lib
+    assert {"llama3p1_8b", "llama3p2_1b", "tiny_llama"} <= set(llama_lib.presets()) and "qwen3_8b" in qwen3_lib.presets()
+    assert "qwen3_8b" not in llama_lib.presets() and "gemma3_1b" in gemma3_lib.presets()
+    m = llama_lib.Llama3(llama_lib.ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2,
+                                                                     head_dim=16, num_kv_heads=1))
+    import torch
+    assert m(torch.randint(0, 64, (1, 5)))[0].shape == (1, 5, 64)
+    with pytest.raises(ValueError, match="family"):
+        qwen3_lib.Qwen3(llama_lib.ModelConfig.tiny_llama())
+    with pytest.raises(ValueError, match="loader serves"):
+        llama_params.create_model_from_safe_tensors("/nowhere", qwen3_lib.ModelConfig.qwen3_0p6b())
+    assert llama_params.key_mapping(llama_lib.ModelConfig.tiny_llama())
+    from tunix_b200.rl.grpo import dapo_learner, drgrpo_learner
+    assert dapo_learner.DAPOConfig(num_generations=2).epsilon_high == 0.28 and drgrpo_learner.DrGRPOLearner.__name__ == "DrGRPOLearner"
