@@ -80,3 +80,26 @@ def test_default_loss_matches_manual_cross_entropy():
     nll = -lsm.gather(-1, b.input_tokens[:, 1:, None])[..., 0]
     ref = (nll * b.input_mask[:, 1:]).sum() / b.input_mask[:, 1:].sum()
     assert torch.allclose(out.loss.value(), ref, atol=1e-5)
+
+
+def test_step_time_and_throughput_metrics_are_logged():
+    import numpy as np
+    import torch
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
+    model = create_model(cfg, seed=0)
+    tr = PeftTrainer(model, optim.AdamW(1e-3), TrainingConfig(eval_every_n_steps=10 ** 9, max_steps=4, gradient_accumulation_steps=2,
+                                                               pbar_description=None))
+    g = torch.Generator().manual_seed(0)
+    data = [TrainingInput(torch.randint(1, 64, (2, 8), generator=g), torch.ones(2, 8, dtype=torch.int32)) for _ in range(8)]
+    tr.train(data)
+    lg = tr.metrics_logger
+    times = lg.get_metric_history("", "step_time_sec", "train")
+    assert len(times) == 3 and (times > 0).all()                       # every step after the first has a predecessor to time against
+    np.testing.assert_allclose(lg.get_metric_history("", "steps_per_sec", "train"), 1.0 / times)
+    n = sum(p.numel() for p in model.parameters())
+    np.testing.assert_allclose(lg.get_metric_history("", "tflops_per_step", "train"), 6.0 * n * 32 / times / 1e12, rtol=1e-6)

@@ -51,6 +51,8 @@ class MetricsBuffer:
     losses: list = dataclasses.field(default_factory=list)
     additional_metrics: dict = dataclasses.field(default_factory=dict)
     grad_norm: Any = None
+    step_time: Optional[float] = None        # host seconds since the previous optimizer step was issued
+    tokens: int = 0                          # tokens of the step's micro-batches on this rank
 
     @property
     def loss(self) -> float:
@@ -148,6 +150,8 @@ class PeftTrainer:
         self._throttler = inflight_throttler.InflightThrottler(training_config.max_inflight_computations)
         self._pbar = None
         self._last_step_time = None
+        self._num_params: Optional[int] = None
+        self._step_tokens = 0
         self.is_managed_externally = False
         if training_config.resume_from_checkpoint_on_init:
             self._train_steps, self._restored_custom_metadata = self.checkpoint_manager.maybe_restore(
@@ -329,6 +333,18 @@ class PeftTrainer:
             else:
                 additional[k] = op([to_host(v) for v in vals])
         self._log_metrics(buf.loss, buf.step, additional, buf.grad_norm)
+        if buf.step_time and buf.step_time > 0 and self._mode == Mode.TRAIN:
+            # host time between the issue of consecutive optimizer steps: with asynchronous launches this is the
+            # steady-state time per step (the in-flight throttle keeps the host at most a few steps ahead)
+            lg, pf = self.metrics_logger, self.metrics_prefix
+            lg.log(pf, "step_time_sec", buf.step_time, self._mode, buf.step)
+            lg.log(pf, "steps_per_sec", 1.0 / buf.step_time, self._mode, buf.step)
+            if buf.tokens:
+                if self._num_params is None:
+                    self._num_params = sum(p.numel() for p in self.model.parameters())
+                from .system_metrics_calculator import approximate_tflops_per_step
+                lg.log(pf, "tflops_per_step", approximate_tflops_per_step(self._num_params, buf.tokens, buf.step_time),
+                       self._mode, buf.step)
 
     def _write_train_metrics(self):
         """Write the metrics of the previous update (one-step delay so host IO overlaps device work)."""
@@ -396,6 +412,7 @@ class PeftTrainer:
     def train(self, train_ds: Iterable[Any], eval_ds: Optional[Iterable[Any]] = None, skip_jit: bool = False):
         cfg = self.config
         self.model.train()
+        self._last_step_time, self._step_tokens = None, 0     # step times are measured inside one call, not across calls
         prof = profiler_lib.Profiler(self._train_steps, cfg.max_steps, cfg.profiler_options)
         if cfg.pbar_description and self._pbar is None and not self.is_managed_externally:
             self._pbar = progress_bar.ProgressBar(self.metrics_logger, self._train_steps, cfg.max_steps,
@@ -452,8 +469,14 @@ class PeftTrainer:
             self._post_process_train_step(aux)
             self._buffered_train_metrics = self._buffer_metrics(self._buffered_train_metrics, metric,
                                                                 self._train_steps, self._aux_metrics(aux))
+            self._step_tokens += _count_tokens(batch)
             if is_update:
                 self._buffered_train_metrics.grad_norm = grad_norm
+                now = time.perf_counter()
+                if self._last_step_time is not None:
+                    self._buffered_train_metrics.step_time = now - self._last_step_time
+                self._last_step_time = now
+                self._buffered_train_metrics.tokens, self._step_tokens = self._step_tokens, 0
                 self._train_steps += 1
                 self._write_train_metrics()
                 if self.checkpoint_manager.should_save(self._train_steps):
@@ -508,6 +531,17 @@ class PeftTrainer:
             self._pbar.close()
             self._pbar = None
         self.metrics_logger.close()
+
+
+def _count_tokens(batch) -> int:
+    """Tokens in a prepared batch (`input_tokens` of a `TrainingInput` or dict; 0 when the batch has another shape)."""
+    toks = batch.get("input_tokens") if isinstance(batch, dict) else getattr(batch, "input_tokens", None)
+    if toks is None:
+        ex = batch.get("train_example") if isinstance(batch, dict) else getattr(batch, "train_example", None)
+        ex = ex if ex is not None else batch
+        p, c = getattr(ex, "prompt_ids", None), getattr(ex, "completion_ids", None)
+        return int(p.numel() + c.numel()) if p is not None and c is not None and hasattr(p, "numel") else 0
+    return int(toks.numel()) if hasattr(toks, "numel") else int(np.size(toks))
 
 
 class GradientAccumulator:
