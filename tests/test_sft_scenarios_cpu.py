@@ -224,3 +224,48 @@ def test_reusing_a_trainer_continues_where_it_stopped_and_learning_rate_follows_
     tr.train([TrainingInput(toks, mask)] * 5)
     lrs = tr.metrics_logger.get_metric_history("", "learning_rate", "train")
     assert tr.train_steps >= 5 and lrs[0] == 0.0 and math.isclose(lrs[2], 1e-2, rel_tol=1e-6) and lrs[-1] < lrs[2]
+
+
+def _failing_rank_worker(rank, world, port, out):
+    import os
+    import sys
+    import time
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tunix_b200 import optim
+    from tunix_b200.common.configs import TrainingConfig
+    from tunix_b200.models.config import ModelConfig
+    from tunix_b200.models.transformer import create_model
+    from tunix_b200.parallel.watchdog import RankFailure
+    from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+    cfg = ModelConfig.tiny_llama().replace(num_layers=1, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=2, head_dim=16, num_kv_heads=1)
+    tr = PeftTrainer(create_model(cfg, seed=0), optim.AdamW(1e-3), TrainingConfig(eval_every_n_steps=10 ** 9, pbar_description=None,
+                                                                                  rank_failure_timeout_s=0.8))
+    g = torch.Generator().manual_seed(rank)
+
+    def batches():
+        for i in range(10 ** 6):
+            if rank == 1 and i == 3:
+                os._exit(0)                                  # the rank disappears between steps, nothing in flight
+            time.sleep(0.05)
+            yield {"input_tokens": torch.randint(1, 64, (2, 8), generator=g), "input_mask": torch.ones(2, 8, dtype=torch.int32),
+                   "_is_local_shard": True}
+    try:
+        tr.train(batches())
+        res = "finished"
+    except RankFailure as e:
+        res = ("rank failure", e.ranks, tr.train_steps)
+    torch.save(res, out)
+    os._exit(0)                                              # no collective teardown with a peer that is gone
+
+
+def test_training_stops_cleanly_when_a_rank_disappears(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_failing_rank_worker, args=(2, 29761, out), nprocs=2, join=True)
+    kind, ranks, steps = torch.load(out)
+    assert kind == "rank failure" and ranks == [1] and steps >= 3

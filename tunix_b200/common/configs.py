@@ -83,6 +83,9 @@ class TrainingConfig:
     pbar_description: Optional[str] = "Training"
     max_seq_token_per_tpu: Optional[int] = None       # packing token budget per row
     max_segments_per_packed_row: Optional[int] = None
+    # multi-rank jobs: a rank whose heartbeat has been silent this long makes every other rank leave `train()` with
+    # `parallel.watchdog.RankFailure` before its next step, instead of waiting in a collective (None = no watchdog)
+    rank_failure_timeout_s: Optional[float] = None
 
     @property
     def sequence_packing_enabled(self) -> bool:

@@ -413,6 +413,7 @@ class PeftTrainer:
         cfg = self.config
         self.model.train()
         self._last_step_time, self._step_tokens = None, 0     # step times are measured inside one call, not across calls
+        watchdog = self._start_watchdog()
         prof = profiler_lib.Profiler(self._train_steps, cfg.max_steps, cfg.profiler_options)
         if cfg.pbar_description and self._pbar is None and not self.is_managed_externally:
             self._pbar = progress_bar.ProgressBar(self.metrics_logger, self._train_steps, cfg.max_steps,
@@ -443,6 +444,12 @@ class PeftTrainer:
                 index += 1
                 continue
             index += 1
+            if watchdog is not None:
+                try:
+                    watchdog.check()        # between steps, nothing of this rank in flight that waits for a peer
+                except BaseException:
+                    watchdog.stop()
+                    raise
             batch = self._prepare_inputs(batch)
             batch = self._shard_and_move(batch)
             self._throttler.wait_for_next()
@@ -489,12 +496,25 @@ class PeftTrainer:
             prof.maybe_deactivate(self._train_steps)
         self._throttler.wait_for_all()
         self._params_ready()
+        if watchdog is not None:
+            watchdog.stop()
         if self.training_hooks:
             self.training_hooks.on_train_end(self)
         if not self.is_managed_externally:
             self.close()
 
     _resume_skip = True
+
+    def _start_watchdog(self):
+        """Heartbeats through the job's store when `rank_failure_timeout_s` is set and there is more than one rank."""
+        timeout = getattr(self.config, "rank_failure_timeout_s", None)
+        if not timeout:
+            return None
+        import torch.distributed as dist
+        if not dist.is_initialized() or dist.get_world_size() < 2:
+            return None
+        from ..parallel.watchdog import Watchdog
+        return Watchdog(interval_s=min(1.0, timeout / 4), timeout_s=timeout).start()
 
     def _params_ready(self) -> None:
         """Order the current stream after any parameter transfer that the optimizer left running on a side stream
