@@ -170,7 +170,7 @@ class RLCluster:
         elif eng in ("vanilla", "paged"):
             cache = max(rc.kv_cache_size, rc.max_prompt_length + rc.max_tokens_to_generate)
             self.rollout = VanillaRollout(self.rollout_actor, self.tokenizer, cache,
-                                          engine="paged" if eng == "paged" else "dense")
+                                          engine="paged" if eng == "paged" else "dense", rollout_config=rc)
         elif eng in ("vllm", "sglang_jax"):
             raise ValueError(f"rollout_engine={eng!r} belongs to the reference's TPU integrations; "
                              "use 'vanilla' or 'paged' (the in-framework engines)")

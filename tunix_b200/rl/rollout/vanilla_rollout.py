@@ -9,8 +9,27 @@ from .. import common
 from .base_rollout import BaseRollout, RolloutOutput
 
 
+def _page_budget(model, cache_size: int, rc: RolloutConfig):
+    """Pages of the KV pool: enough for `max_running_requests` full-length sequences, but no more than
+    `hbm_utilization` of the device memory that is free when the engine is built (requests that find no page wait in
+    the engine's queue). None (= the engine's own sizing) off the GPU."""
+    import torch
+    cfg = model.config
+    dev = next(model.parameters()).device
+    per_seq = -(-int(cache_size) // int(rc.page_size))
+    want = int(rc.max_running_requests) * per_seq
+    if dev.type != "cuda" or not rc.hbm_utilization:
+        return want
+    page_bytes = cfg.num_layers * 2 * cfg.num_kv_heads * cfg.head_dim * int(rc.page_size) * 2
+    free, _ = torch.cuda.mem_get_info(dev)
+    cap = int(free * float(rc.hbm_utilization)) // max(page_bytes, 1)
+    return max(min(want, cap), per_seq)             # never below one full sequence
+
+
 class VanillaRollout(BaseRollout):
-    def __init__(self, model, tokenizer, cache_config_or_size, engine: str = "dense"):
+    def __init__(self, model, tokenizer, cache_config_or_size, engine: str = "dense", rollout_config: RolloutConfig = None):
+        """`rollout_config` (paged engine): its `page_size`, `max_running_requests`, `use_cuda_graph` and
+        `chunked_prefill_size` size the engine; without it the engine's own defaults apply."""
         cfg = model.config
         if isinstance(cache_config_or_size, int):
             cache_config_or_size = CacheConfig(cache_config_or_size, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim)
@@ -19,7 +38,13 @@ class VanillaRollout(BaseRollout):
         self._engine = None
         if engine == "paged":
             from ...generate.engine import PagedEngine
-            self._engine = PagedEngine(model, tokenizer, cache_config_or_size)
+            knobs = {}
+            if rollout_config is not None:
+                knobs = dict(page_size=int(rollout_config.page_size), max_running_requests=int(rollout_config.max_running_requests),
+                             use_cuda_graph=bool(rollout_config.use_cuda_graph),
+                             prefill_chunk=int(rollout_config.chunked_prefill_size or 0))
+                knobs["num_pages"] = _page_budget(model, cache_config_or_size.cache_size, rollout_config)
+            self._engine = PagedEngine(model, tokenizer, cache_config_or_size, **knobs)
 
     def generate(self, prompts, rollout_config: RolloutConfig, **kwargs) -> RolloutOutput:
         want_tp = getattr(rollout_config, "tensor_parallel_size", -1)
