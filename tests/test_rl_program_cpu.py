@@ -435,3 +435,79 @@ def test_polling_does_not_spin_while_nothing_is_in_flight():
     _program(_prompts(4), 2, sync_weights=False, checkpoint_every=0).run(eng)
     assert CountingEngine.polls < 200
     asyncio.run(eng.close())
+
+
+def test_program_over_workers_behind_grpc():
+    """The same engine and program with every worker in its own server on the loopback interface: requests, responses
+    and weights cross the wire (`RemoteWorker`), one rollout server goes away mid-run."""
+    pytest.importorskip("grpc")
+    from tunix_b200.experimental.worker.remote_execution import RemoteWorker, serve_worker
+    from tunix_b200.experimental.worker.rollout_worker import RolloutWorker
+
+    class Out:
+        def __init__(self, toks):
+            self.tokens, self.logprobs, self.text = [toks], [[-0.5] * len(toks)], None
+
+    def engine(prompt_token_ids, max_generation_steps, seed=None, **kw):
+        rng = np.random.default_rng(seed)
+        return Out(rng.integers(3, 60, max_generation_steps).tolist())
+    synced = {"a": [], "b": []}
+    locals_ = [RolloutWorker(f"rollout-{k}", engine, apply_weights=lambda v, p, k=k: synced[k].append((v, float(p["w"].sum()))), eos_tokens=[2])
+               for k in "ab"]
+    tr = _Trainer({})
+
+    class TrainerFacade:
+        """`_Trainer` behind the worker protocol (start / state / submit)."""
+        worker_id, policy_version = "trainer-0", 0
+
+        def start(self): ...
+        def stop(self): ...
+
+        def info(self):
+            from tunix_b200.experimental.orchestrator.worker_registry import WorkerInfo
+            return WorkerInfo(self.worker_id, ("trainer",))
+
+        @property
+        def state(self):
+            from tunix_b200.experimental.common.datatypes import WorkerState
+            return WorkerState.READY
+
+        def submit(self, req):
+            return tr.submit(req)
+
+        def sync_weights(self, version, payload=None): ...
+    servers = [serve_worker(w, "127.0.0.1:0", token="t") for w in locals_] + [serve_worker(TrainerFacade(), "127.0.0.1:0", token="t")]
+    try:
+        remotes = [RemoteWorker(s.address, token="t") for s in servers]
+        for r in remotes[:2]:
+            r.start()
+        eng = DistributedRLEngine({"a": remotes[0], "b": remotes[1]}, {Role.ACTOR: remotes[2]},
+                                  export_weights=lambda: {"w": np.full(1000, float(tr.steps), np.float32)})
+        stopped = []
+
+        def on_end(step, result):
+            if step == 0:                                   # one rollout server disappears between steps
+                servers[1].stop(grace=0)
+                stopped.append(True)
+        hist = _program(_prompts(6), 3, on_step_end=on_end).run(eng)
+        assert [h["step"] for h in hist] == [0, 1, 2] and all(h["num_rollouts"] == 8 for h in hist) and stopped == [True]
+        assert tr.steps == 3 and [v for v, _ in synced["a"]] == [0, 1, 2, 3]
+        assert synced["a"][-1] == (3, 3000.0)               # the payload crossed the wire
+        assert eng.rollout_pool.stats()["b"]["down"] and locals_[0].served > locals_[1].served
+        asyncio.run(eng.close())
+    finally:
+        for s in servers:
+            s.stop(grace=0)
+
+
+def test_worker_that_cannot_take_weights_leaves_the_rotation():
+    good, bad = _EchoRollout("good"), _EchoRollout("bad")
+    bad.sync_weights = lambda v, p=None: (_ for _ in ()).throw(ConnectionError("gone"))
+    eng = DistributedRLEngine([good, bad], {Role.ACTOR: _Trainer({})})
+    assert asyncio.run(eng.sync_weights()) == 1 and good.synced == [(1, None)]
+    assert eng.rollout_pool.live() == ["good"]
+    good.sync_weights = bad.sync_weights
+    with pytest.raises(RuntimeError, match="no rollout worker took policy version 2"):
+        asyncio.run(eng.sync_weights())
+    assert eng.policy_version == 1
+    asyncio.run(eng.close())

@@ -275,9 +275,19 @@ class DistributedRLEngine:
     def _push_weights(self, version: int) -> None:
         payload = self._export_weights() if self._export_weights is not None else None
         live = set(self._pool.live())
+        ok, last = 0, None
         for name, w in self._rollout.items():
-            if name in live:
+            if name not in live:
+                continue
+            try:
                 w.sync_weights(version, payload)
+                ok += 1
+            except Exception as e:          # a worker that cannot take the weights must not serve stale ones: out of rotation
+                last = e
+                log.error("rollout worker %s failed to take policy version %d and is taken out of rotation: %s", name, version, e)
+                self._pool.mark_down(name)
+        if live and ok == 0:
+            raise RuntimeError(f"no rollout worker took policy version {version}") from last
 
     async def sync_weights(self, role=Role.ACTOR, target_roles: Optional[Sequence[Any]] = None,
                            policy_version: Optional[int] = None, **kwargs: Any) -> int:
