@@ -511,3 +511,25 @@ def test_worker_that_cannot_take_weights_leaves_the_rotation():
         asyncio.run(eng.sync_weights())
     assert eng.policy_version == 1
     asyncio.run(eng.close())
+
+
+def test_reference_logprobs_are_attached_to_every_micro_batch():
+    class Ref:
+        calls = 0
+
+        def submit(self, req):
+            assert req["op"] == "per_token_logps" and {"input_tokens", "completion_mask", "segment_ids", "positions"} <= set(req)
+            Ref.calls += 1
+            return np.full(np.asarray(req["input_tokens"]).shape, -2.0, np.float32).tolist()
+    tr = _Trainer({})
+    seen = []
+    real = tr.submit
+    tr.submit = lambda req: (seen.append(req["batch"]) if req.get("op") == "fwd_bwd" else None, real(req))[1]
+    eng = DistributedRLEngine([_EchoRollout("r0")], {Role.ACTOR: tr}, inference_workers={Role.REFERENCE: Ref()})
+    hist = _program(_prompts(2), 1, reference_kl=True, sync_weights=False, checkpoint_every=0).run(eng)
+    assert Ref.calls == hist[0]["num_microbatches"] == len(seen)
+    assert all(b["ref_per_token_logps"].shape == np.asarray(b["input_tokens"]).shape and (b["ref_per_token_logps"] == -2).all() for b in seen)
+    asyncio.run(eng.close())
+    with pytest.raises(ValueError, match="No worker registered for per_token_logps"):
+        e2 = DistributedRLEngine([_EchoRollout("r0")], {Role.CRITIC: _Trainer({})})
+        asyncio.run(e2.per_token_logps(Role.REFERENCE, {"input_tokens": [[1]]}))

@@ -123,7 +123,7 @@ class StandardRLProgram(RLProgram):
                  batch_size: int = 1, assembler=None, batch_config: Optional[BatchConfig] = None, packed: bool = True,
                  generation_args: Optional[GenerationArgs] = None, max_response_length: Optional[int] = None,
                  max_staleness: int = 0, sync_weights: bool = True, checkpoint_every: int = 1, metrics_logger=None,
-                 trajectory_store=None, metrics_prefix: str = "", poll_timeout_s: float = 0.2,
+                 trajectory_store=None, metrics_prefix: str = "", poll_timeout_s: float = 0.2, reference_kl: bool = False,
                  on_step_begin: Optional[Callable[[int], None]] = None, on_step_end: Optional[Callable[[int, Any], None]] = None):
         super().__init__()
         if max_staleness < 0:
@@ -142,6 +142,9 @@ class StandardRLProgram(RLProgram):
         self.metrics_logger, self.metrics_prefix = metrics_logger, metrics_prefix
         self._trajectory_store = trajectory_store          # used, not owned: whoever built it closes it
         self.poll_timeout_s = poll_timeout_s
+        # reference log-probs for a KL term: asked of the REFERENCE role per assembled micro-batch (dense rows: one
+        # forward pass over what the trainer will see), stored in the batch as `ref_per_token_logps`
+        self.reference_kl = bool(reference_kl or getattr(algo, "requires_reference_kl", False))
         self.on_step_begin, self.on_step_end = on_step_begin, on_step_end
         self.dispatch_window = DispatchWindow(max_staleness, lambda: self._step, full_batch_size=batch_size, out_of_order_resume=True)
         self.history: list = []
@@ -321,6 +324,10 @@ class StandardRLProgram(RLProgram):
 
         async def submit(mb, last: bool) -> None:
             nonlocal pending
+            if self.reference_kl:                                # overlaps with the training call that is in flight
+                keys = ("input_tokens", "positions", "segment_ids", "prompt_mask", "completion_mask")
+                ref = await self.engine.per_token_logps(Role.REFERENCE, {k: mb.arrays[k] for k in keys if k in mb.arrays})
+                mb.arrays["ref_per_token_logps"] = np.asarray(ref, np.float32)
             await settle()                                       # one call in flight: the next batch was assembled meanwhile
             pending = asyncio.create_task(self.engine.train_step(mb, role=Role.ACTOR, accumulate_gradients=True,
                                                                  apply_optimizer=last))
