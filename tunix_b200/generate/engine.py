@@ -652,7 +652,7 @@ class PagedEngine(BaseSampler):
                                            f"a single request of {new[0][2]} prompt tokens")
                     break
                 pool.sync_table()
-                # requests whose cached pages are written by another request of this round wait for that prefill
+                # requests whose cached pages are written by another request of this admission pass wait for that prefill
                 produced: dict = {}
                 waves: dict = {}
                 for s, item, cached in admitted:
