@@ -34,7 +34,7 @@ from tunix_b200.experimental.rollout.sampler import EngineSamplerAdapter
 from tunix_b200.experimental.train.peft_trainer_v2 import TrainerV2
 from tunix_b200.experimental.worker.agentic_rollout_worker import AgenticRolloutWorker
 from tunix_b200.experimental.worker.factories import ByteTokenizer, toy_config
-from tunix_b200.experimental.worker.rollout_worker import TrainerWorker
+from tunix_b200.experimental.worker.trainer_worker import TrainerWorker
 from tunix_b200.generate.sampler import Sampler
 from tunix_b200.models.transformer import create_model
 from tunix_b200.rl.agentic.agentic_grpo_learner import AgenticGRPOLearner

@@ -6,7 +6,9 @@ from __future__ import annotations
 import sys
 
 from ..rl.algorithm_config import DAPOConfig, DrGRPOConfig, GRPOConfig
-from ..rl.grpo.grpo_learner import DAPOLearner, DrGRPOLearner, GRPOLearner
+from ..rl.grpo.dapo_learner import DAPOLearner
+from ..rl.grpo.drgrpo_learner import DrGRPOLearner
+from ..rl.grpo.grpo_learner import GRPOLearner
 from ..rl.rl_cluster import RLCluster
 from .base_rl_pipeline import BasePipeline
 

@@ -1,10 +1,10 @@
-"""Rollout, inference and trainer workers on the worker state machine
-(tunix/experimental/worker/{rollout_worker,inference_worker,trainer_worker}.py).
+"""The single-call rollout worker on the worker state machine (tunix/experimental/worker/rollout_worker.py).
 
-Each wraps an in-process engine behind `AbstractWorker` (checked state transitions, admission limit, heartbeat
+It wraps a generation engine behind `AbstractWorker` (checked state transitions, admission limit, heartbeat
 reports), speaks the DTOs of `experimental.common.datatypes`, and describes itself with a `WorkerInfo` for the
-registry. The transport in front of them (the reference's gRPC actor layer) is not part of this package: the
-workers are driven in process."""
+registry. `inference_worker.InferenceWorker` and `trainer_worker.TrainerWorker` are its siblings (also importable from
+here); `agentic_rollout_worker.AgenticRolloutWorker` runs whole episodes; `remote_execution` puts any of them behind
+gRPC."""
 from __future__ import annotations
 
 from typing import Any, Callable, Optional, Sequence
@@ -75,64 +75,12 @@ class RolloutWorker(AbstractWorker):
             self.engine.close()
 
 
-class InferenceWorker(AbstractWorker):
-    """Scores sequences with a frozen model (reference / old-policy log-probs, values, rewards). `score_fns` maps
-    an operation name to `fn(**arrays) -> array`; a request is `{"op": name, **arrays}`."""
-
-    role = "inference"
-
-    def __init__(self, worker_id: str, score_fns: dict, *, apply_weights=None, max_inflight: int = 4, on_report=None):
-        super().__init__(worker_id, max_inflight=max_inflight, on_report=on_report)
-        self.score_fns, self._apply = dict(score_fns), apply_weights
-
-    def info(self) -> WorkerInfo:
-        return WorkerInfo(self.worker_id, (self.role,), attributes={"ops": sorted(self.score_fns)})
-
-    def _initialize(self) -> bool:
-        return False
-
-    def _handle(self, req: dict):
-        req = dict(req)
-        op = req.pop("op")
-        if op not in self.score_fns:
-            raise KeyError(f"{self.worker_id} has no operation {op!r}; known: {sorted(self.score_fns)}")
-        return self.score_fns[op](**req)
-
-    def _sync_weights(self, version: int, payload: Any) -> None:
-        if self._apply is not None:
-            self._apply(version, payload)
-
-
-class TrainerWorker(AbstractWorker):
-    """Drives a trainer through the split-step protocol of the distributed engine: `fwd_bwd` on a micro-batch
-    (gradients accumulate), `update` (optimizer step, version + 1), `eval_step`, `fwd_only`, `save_checkpoint`,
-    `restore_checkpoint`. `trainer` is a `TrainerV2` (`experimental.train.peft_trainer_v2`)."""
-
-    role = "trainer"
-
-    def __init__(self, worker_id: str, trainer, on_report=None):
-        super().__init__(worker_id, max_inflight=1, on_report=on_report)
-        self.trainer = trainer
-
-    def info(self) -> WorkerInfo:
-        return WorkerInfo(self.worker_id, (self.role,))
-
-    def _initialize(self) -> bool:
-        return False
-
-    def _handle(self, req: dict):
-        req = dict(req)
-        op = req.pop("op")
-        if op not in ("fwd_bwd", "update", "eval_step", "fwd_only", "save_checkpoint", "restore_checkpoint", "restored_metadata",
-                      "get_metrics"):
-            raise KeyError(f"unknown trainer operation {op!r}")
-        out = getattr(self.trainer, op)(**req)
-        if op == "update":
-            self.policy_version += 1
-        return out
-
-    def _drain(self) -> None:
-        """A stopping worker leaves no checkpoint half written: background saves are waited for."""
-        wait = getattr(self.trainer, "wait_for_checkpoints", None)
-        if wait is not None:
-            wait()
+def __getattr__(name):
+    """`InferenceWorker` and `TrainerWorker` used to live in this module; they are still importable from it."""
+    if name == "InferenceWorker":
+        from .inference_worker import InferenceWorker
+        return InferenceWorker
+    if name == "TrainerWorker":
+        from .trainer_worker import TrainerWorker
+        return TrainerWorker
+    raise AttributeError(name)

@@ -15,7 +15,7 @@ import torch
 
 from ...common.datatypes import Mode
 from .. import algo_core, common, function_registry
-from ..algorithm_config import DAPOConfig, DrGRPOConfig, GRPOConfig
+from ..algorithm_config import GRPOConfig
 from ..rl_cluster import RLCluster
 from ..rl_learner import RLLearner
 
@@ -116,27 +116,12 @@ class GRPOLearner(RLLearner):
 GrpoLearner = GRPOLearner
 
 
-class DAPOLearner(GRPOLearner):
-    """beta = 0, clip-higher, token-mean aggregation, overlong-buffer reward shaping (soft length penalty)."""
-
-    def __init__(self, rl_cluster, reward_fns, algo_config: DAPOConfig, **kw):
-        super().__init__(rl_cluster, reward_fns, algo_config, **kw)
-
-    def _shape_rewards(self, rewards, completions, lengths):
-        ob = getattr(self.algo_config, "overlong_buffer", None)
-        if not ob or not ob.get("enable", False):
-            return rewards
-        buf = ob["overlong_buffer_length"]
-        penalty = ob.get("overlong_buffer_penalty", 1.0)
-        max_len = ob["max_response_length"]
-        expected = max_len - buf
-        # the reference measures completion length in characters (tunix/rl/grpo/dapo_learner.py:127-133);
-        # token counts are what the budget is about, so tokens are used here.
-        exceed = np.asarray(lengths, np.float32) - expected
-        shaped = np.minimum(-exceed / max(buf, 1) * penalty, 0.0)
-        return rewards + shaped.astype(np.float32)
-
-
-class DrGRPOLearner(GRPOLearner):
-    def __init__(self, rl_cluster, reward_fns, algo_config: DrGRPOConfig, **kw):
-        super().__init__(rl_cluster, reward_fns, algo_config, **kw)
+def __getattr__(name):
+    """The DAPO and Dr. GRPO learners have modules of their own; they stay importable from here."""
+    if name == "DAPOLearner":
+        from .dapo_learner import DAPOLearner
+        return DAPOLearner
+    if name == "DrGRPOLearner":
+        from .drgrpo_learner import DrGRPOLearner
+        return DrGRPOLearner
+    raise AttributeError(name)
