@@ -20,7 +20,6 @@ import copy
 import json
 import time
 
-import numpy as np
 import torch
 
 from tunix_b200 import optim

@@ -17,7 +17,7 @@ from __future__ import annotations
 import asyncio
 import logging
 import zlib
-from typing import Any, Callable, Collection, Optional, Sequence
+from typing import Callable, Collection, Optional, Sequence
 
 import numpy as np
 

@@ -11,7 +11,7 @@ import os
 import re
 import sqlite3
 import threading
-from typing import Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Tuple
 
 
 class Dialect(str, enum.Enum):

@@ -1,8 +1,6 @@
 """The trainer worker (tunix/experimental/worker/trainer_worker.py): the split-step trainer behind the worker state machine."""
 from __future__ import annotations
 
-from typing import Any
-
 from ..orchestrator.worker_registry import WorkerInfo
 from .abstract_worker import AbstractWorker
 

@@ -14,7 +14,7 @@ from typing import Any, Optional, Tuple
 
 import numpy as np
 
-from ..examples.data._records import normalize_record as normalize_single_example
+from ..examples.data._records import normalize_record as normalize_single_example  # noqa: F401 (part of the recipe's API)
 from ..examples.data._records import normalize_value as normalize_example_value
 from ..rl.agentic.parser import chat_template_parser as _parsers
 
