@@ -15,6 +15,7 @@ import importlib
 import importlib.util
 import inspect
 import os
+import re
 import sys
 from typing import Any, Callable, Optional
 
@@ -36,9 +37,24 @@ def _unalias(obj: Any) -> Any:
     return obj
 
 
+_SCI_NUMBER = re.compile(r"^[+-]?(\d+\.?\d*|\.\d+)[eE][+-]?\d+$")
+
+
+def _fix_numbers(obj: Any) -> Any:
+    """YAML 1.1 reads `3e-4` (no dot in the mantissa) as a string; here it is the number it looks like, in override
+    values and in override files alike."""
+    if isinstance(obj, str) and _SCI_NUMBER.match(obj.strip()):
+        return float(obj)
+    if isinstance(obj, dict):
+        return {k: _fix_numbers(v) for k, v in obj.items()}
+    if isinstance(obj, list):
+        return [_fix_numbers(v) for v in obj]
+    return obj
+
+
 def _parse_scalar(text: str) -> Any:
     try:
-        return yaml.safe_load(text)
+        return _fix_numbers(yaml.safe_load(text))
     except yaml.YAMLError:
         return text
 
@@ -85,7 +101,7 @@ class HyperParameters:
             cand = os.path.join(os.path.dirname(os.path.abspath(__file__)), base_path)
             base_path = cand if os.path.exists(cand) else base_path
         with open(base_path) as f:
-            base = _unalias(yaml.safe_load(f))       # YAML anchors make sections share nested dicts: give each its own
+            base = _unalias(_fix_numbers(yaml.safe_load(f)))       # YAML anchors make sections share nested dicts: give each its own
         self._schema = copy.deepcopy(base)
         cfg = base
         cli: dict = {}
@@ -96,7 +112,7 @@ class HyperParameters:
             cli[k.strip()] = v
         if "override_config_file" in cli:
             with open(cli.pop("override_config_file")) as f:
-                cfg = _merge(cfg, yaml.safe_load(f) or {})
+                cfg = _merge(cfg, _fix_numbers(yaml.safe_load(f) or {}))
         env_over = {}
         for k, v in env.items():
             if k.startswith("T_"):
