@@ -533,3 +533,35 @@ def test_reference_logprobs_are_attached_to_every_micro_batch():
     with pytest.raises(ValueError, match="No worker registered for per_token_logps"):
         e2 = DistributedRLEngine([_EchoRollout("r0")], {Role.CRITIC: _Trainer({})})
         asyncio.run(e2.per_token_logps(Role.REFERENCE, {"input_tokens": [[1]]}))
+
+
+@pytest.mark.parametrize("order", ["completion", "prompt_arrival"])
+def test_group_order_decouples_training_order_from_rollout_timing(order):
+    class Uneven(_EchoRollout):
+        """Earlier prompts of a batch take longer, so groups finish in reverse."""
+        def submit(self, req):
+            i = int(req.group_id[1:])
+            time.sleep(0.12 if i % 4 == 0 else 0.0)
+            out = super().submit(req)
+            if req.group_id == "p5":
+                out.tokens = [9, 9]                      # a group without signal in the middle gives up its place
+            return out
+    w = Uneven("r0")
+    w.max = 64
+    eng = DistributedRLEngine([w], {Role.ACTOR: _Trainer({})}, max_threads=32)
+    consumed = []
+    prog = StandardRLProgram(GRPOAdapter(reward_fn=lambda item, r: float(sum(t % 5 for t in r.tokens))), _prompts(8), None,
+                             num_generations=4, batch_size=4, batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=48),
+                             generation_args=GenerationArgs(max_tokens=4), poll_timeout_s=0.02, checkpoint_every=0, sync_weights=False,
+                             group_order=order)
+    real = prog.dispatch_window.record_committed_groups
+    prog.dispatch_window.record_committed_groups = lambda groups: (consumed.extend(g.prompt_id for g in groups), real(groups))[1]
+    prog.run(eng)
+    assert sorted(consumed) == sorted(f"p{i}" for i in range(8) if i != 5)
+    if order == "prompt_arrival":
+        assert consumed == [f"p{i}" for i in range(8) if i != 5]
+    else:
+        assert consumed[:4] != ["p0", "p1", "p2", "p3"]                     # the slow first prompt is not waited for
+    asyncio.run(eng.close())
+    with pytest.raises(ValueError, match="group_order"):
+        _program(_prompts(1), 1, group_order="random")

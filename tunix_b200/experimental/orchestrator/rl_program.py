@@ -124,6 +124,7 @@ class StandardRLProgram(RLProgram):
                  generation_args: Optional[GenerationArgs] = None, max_response_length: Optional[int] = None,
                  max_staleness: int = 0, sync_weights: bool = True, checkpoint_every: int = 1, metrics_logger=None,
                  trajectory_store=None, metrics_prefix: str = "", poll_timeout_s: float = 0.2, reference_kl: bool = False,
+                 group_order: str = "completion",
                  on_step_begin: Optional[Callable[[int], None]] = None, on_step_end: Optional[Callable[[int, Any], None]] = None):
         super().__init__()
         if max_staleness < 0:
@@ -142,6 +143,13 @@ class StandardRLProgram(RLProgram):
         self.metrics_logger, self.metrics_prefix = metrics_logger, metrics_prefix
         self._trajectory_store = trajectory_store          # used, not owned: whoever built it closes it
         self.poll_timeout_s = poll_timeout_s
+        # "completion": the trainer takes groups as they finish (best utilisation). "prompt_arrival": groups reach the
+        # trainer in the order their prompts were dispatched, whatever order they finished in, so that a run does not
+        # depend on rollout timing (a filtered group gives up its place)
+        if group_order not in ("completion", "prompt_arrival"):
+            raise ValueError(f"group_order must be 'completion' or 'prompt_arrival', got {group_order!r}")
+        self.group_order = group_order
+        self._order_next, self._order_pending = 0, {}
         # reference log-probs for a KL term: asked of the REFERENCE role per assembled micro-batch (dense rows: one
         # forward pass over what the trainer will see), stored in the batch as `ref_per_token_logps`
         self.reference_kl = bool(reference_kl or getattr(algo, "requires_reference_kl", False))
@@ -198,7 +206,7 @@ class StandardRLProgram(RLProgram):
                 await self.dispatch_window.wait_for(self._base_step + self._dispatched // self.full_batch_size)
                 if self.max_response_length is not None:
                     item.setdefault("max_response_length", self.max_response_length)
-                item = tag_prompt(item, prompt_coordinates(idx, self.full_batch_size))
+                item = tag_prompt(item, {**prompt_coordinates(idx, self.full_batch_size), "dispatch_seq": self._dispatched})
                 self._prompts[str(item["prompt_id"])] = item
                 self._in_flight += self.num_generations
                 self._dispatched += 1
@@ -213,6 +221,32 @@ class StandardRLProgram(RLProgram):
         self._filtered_groups.append((group.prompt_id, why))
         self._prompts.pop(group.prompt_id, None)
         self.dispatch_window.on_group_filtered(group)
+        self._hand_to_trainer(group, None)
+
+    def _hand_to_trainer(self, group: _Group, scored: Optional[_Group]) -> None:
+        """Queue a scored group for the train stage (`scored` None: the group was filtered and only gives up its place)."""
+        if self.group_order == "completion":
+            if scored is not None:
+                self._scored_q.put_nowait(scored)
+            return
+        seq = (group.item.get("metadata") or {}).get("dispatch_seq")
+        if seq is None:                                   # not dispatched by this program: no place to keep
+            if scored is not None:
+                self._scored_q.put_nowait(scored)
+            return
+        self._order_pending[int(seq)] = scored
+        while self._order_next in self._order_pending:
+            g = self._order_pending.pop(self._order_next)
+            self._order_next += 1
+            if g is not None:
+                self._scored_q.put_nowait(g)
+
+    def _flush_order(self) -> None:
+        """End of the dataset: what is still held goes out in order (places of groups that never completed stay empty)."""
+        for seq in sorted(self._order_pending):
+            g = self._order_pending.pop(seq)
+            if g is not None:
+                self._scored_q.put_nowait(g)
 
     async def polling_stage(self) -> None:
         open_groups: dict = {}
@@ -265,8 +299,9 @@ class StandardRLProgram(RLProgram):
                 group.payloads, group.responses = list(payloads), valid        # payload i belongs to response i from here on
                 log.info("[pipeline] ARRIVED prompt_id=%s batch_idx=%s policy_version=%d", group.prompt_id,
                          (group.item.get("metadata") or {}).get("batch_idx"), int(valid[0].policy_version))
-                await self._scored_q.put(group)
+                self._hand_to_trainer(group, group)
         finally:
+            self._flush_order()
             await self._scored_q.put(_EOF)
 
     # ------------------------------------------------------------------ stage 3: train
@@ -433,6 +468,7 @@ class StandardRLProgram(RLProgram):
         self._raw_q: asyncio.Queue = asyncio.Queue()
         self._scored_q: asyncio.Queue = asyncio.Queue()
         self._in_flight = self._dispatched = 0
+        self._order_next, self._order_pending = 0, {}
         # before any stage starts: the train loop's bound and the dataset prefix to skip both come from the restored step
         await self._resume_from_checkpoint()
         self._base_step = self._step
