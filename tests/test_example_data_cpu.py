@@ -131,3 +131,14 @@ def test_script_utils(tmp_path):
     with script_utils.profile_and_capture_log("noop"):
         pass
     assert script_utils.DEBUG_LEVELS["FATAL"] == logging.CRITICAL
+
+
+def test_gsm8k_vtc_example_script_runs_in_tiny_mode():
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "rl", "grpo_gsm8k_vtc.py")
+    spec = importlib.util.spec_from_file_location("grpo_gsm8k_vtc_example", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = mod.main(["--tiny", "--steps", "2"])
+    assert out["steps"] == 2 and len(out["reward_mean"]) == 2 and len(out["solve_ratio"]) == 2

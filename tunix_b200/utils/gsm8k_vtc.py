@@ -91,7 +91,7 @@ def vtc_reward_fn(prompts, completions, answer, **kwargs) -> list:
     return [vtc_completion_outcome(str(c), a)[0] for c, a in zip(completions, answer)]
 
 
-def vtc_metric_fn(prompts, completions, rewards, advantages, answer, **kwargs) -> dict:
+def vtc_metric_fn(prompts, completions, rewards, advantages, answer=None, **kwargs) -> dict:
     """Per-group rollout metrics, `{name: (value, aggregation)}`; "solved" = reward above the format-only tier."""
     r = np.asarray(rewards, np.float32)
     solve_all, solve_none = bool(np.all(r > 0.1)), bool(np.all(np.isclose(r, 0.0)))
