@@ -16,57 +16,20 @@ from tunix_b200.experimental.orchestrator.rl_engine_interface import AbstractRLE
 from tunix_b200.experimental.orchestrator.rl_program import StandardRLProgram, _generation_metrics, prompt_coordinates, tag_prompt
 
 
-class _EchoRollout:
-    """A rollout worker double: answers with tokens derived from the prompt and the seed."""
+from tunix_b200.experimental.common import test_utils as doubles
+
+
+class _EchoRollout(doubles.EchoRolloutWorker):
     def __init__(self, worker_id, fail=False, n=4):
-        self.worker_id, self.fail, self.n = worker_id, fail, n
-        self.seen, self.synced, self.policy_version = [], [], 0
-
-    def submit(self, req):
-        if self.fail:
-            raise ConnectionError(f"{self.worker_id} lost")
-        self.seen.append(req)
-        rng = np.random.default_rng(req.seed)
-        toks = rng.integers(3, 60, min(self.n, req.max_tokens)).tolist()
-        return RolloutResponse(req.request_id, toks, [-0.5] * len(toks), None, policy_version=self.policy_version,
-                               group_id=req.group_id, metadata=dict(req.metadata))
-
-    def sync_weights(self, version, payload=None):
-        self.policy_version = version
-        self.synced.append((version, payload))
+        super().__init__(worker_id, n=n, fail=fail)
 
 
-class _Trainer:
-    """A trainer worker double that records the split-step protocol and keeps a 'checkpoint' in a dict."""
-    def __init__(self, disk):
-        self.disk, self.ops, self.steps, self.pending = disk, [], 0, 0
-
-    def submit(self, req):
-        req = dict(req)
-        op = req.pop("op")
-        self.ops.append((op, req.get("is_last_microbatch")))
-        if op == "fwd_bwd":
-            self.pending += 1
-            return {"loss": 1.0 / (1 + self.steps), "pending_microbatches": self.pending}
-        if op == "update":
-            assert self.pending > 0
-            self.steps, self.pending = self.steps + 1, 0
-            return {"step": self.steps, "grad_norm": 1.0}
-        if op == "save_checkpoint":
-            self.disk["latest"] = dict(req["custom_metadata"])
-            return True
-        if op == "restore_checkpoint":
-            meta = self.disk.get("latest")
-            self.steps = int(meta["step"]) if meta and str(meta["step"]).isdigit() else 0
-            return dict(meta) if meta else 0
-        if op == "get_metrics":
-            return {"train_steps": self.steps}
-        raise KeyError(op)
+class _Trainer(doubles.RecordingTrainerWorker):
+    pass
 
 
 def _prompts(n):
-    rng = np.random.default_rng(0)
-    return [{"prompt_id": f"p{i}", "prompt_ids": [1] + rng.integers(3, 60, 4).tolist()} for i in range(n)]
+    return doubles.make_prompts(n)
 
 
 def test_engine_builds_requests_routes_by_prompt_and_reports_failures():
@@ -111,7 +74,7 @@ def test_engine_builds_requests_routes_by_prompt_and_reports_failures():
         with pytest.raises(ValueError, match="No inference worker"):
             await eng.score(Role.REWARD, [])
         assert (await eng.get_metrics(Role.ROLLOUT))["policy_version"] == 1
-        assert await eng.get_metrics(Role.ACTOR) == {"train_steps": 0}
+        assert (await eng.get_metrics(Role.ACTOR))["train_steps"] == 0
         await eng.close()
     asyncio.run(go())
 
