@@ -136,6 +136,8 @@ class _FakeEngine:
             for rid in list(running):
                 last, lim, out = running[rid]
                 out.append(last + len(out) + 1)
+                if getattr(source, "streaming", False) and len(out) < lim:
+                    source.progress(rid, out, [0.0] * len(out))
                 if len(out) >= lim:
                     source.deliver(rid, out, [0.0] * len(out))
                     del running[rid]
@@ -174,6 +176,21 @@ def test_engine_server_protocol_on_cpu():
     with pytest.raises(RuntimeError):
         bad.submit([1, 2])
     bad.close()
+
+
+def test_engine_server_reports_tokens_while_a_request_runs():
+    from tunix_b200.generate.engine import EngineServer
+    with EngineServer(_FakeEngine(slots=2), max_new_tokens=6, max_prompt_length=8, eos_tokens=[2]) as srv:
+        pieces, other = [], []
+        fut = srv.submit([1, 20], 5, on_tokens=lambda t, l: pieces.append((t.tolist(), len(l))))
+        quiet = srv.submit([1, 40], 3)                                   # a request without a listener beside it
+        toks, _ = fut.result(10)
+        assert quiet.result(10)[0].tolist() == [41, 42, 43]
+        assert [t for p, _ in pieces for t in p] == toks.tolist() == [21, 22, 23, 24, 25]
+        assert len(pieces) >= 3 and all(len(p) == n for p, n in pieces)      # arrived in several pieces, none repeated
+        assert not srv.streaming                                             # the listener is gone with its request
+        bad = srv.submit([1, 60], 3, on_tokens=lambda t, l: 1 / 0)           # a failing callback does not hurt the request
+        assert bad.result(10)[0].tolist() == [61, 62, 63]
 
 
 def _http(url, body=None):
@@ -227,8 +244,26 @@ def test_openai_style_http_front_end_over_the_engine_server():
             st, ctype, raw = _http(http.url + "/v1/chat/completions", {"messages": msgs, "max_tokens": 2, "stream": True})
             events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
             assert st == 200 and ctype == "text/event-stream" and events[-1] == "[DONE]"
-            assert json.loads(events[0])["choices"][0]["delta"]["content"] == tok.decode([pl + 1, pl + 2])
-            assert json.loads(events[1])["choices"][0]["finish_reason"] == "length"
+            deltas = [json.loads(e)["choices"][0]["delta"] for e in events[:-2]]
+            assert deltas[0]["role"] == "assistant" and all("role" not in d for d in deltas[1:])
+            assert "".join(d["content"] for d in deltas) == tok.decode([pl + 1, pl + 2])
+            assert json.loads(events[-2])["choices"][0] == {"index": 0, "delta": {}, "finish_reason": "length"}
+            # a streamed completion arrives in pieces as the engine produces it; a stop string ends the stream early
+            st, ctype, raw = _http(http.url + "/v1/completions", {"prompt": "hello", "max_tokens": 5, "stream": True})
+            events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
+            texts = [json.loads(e)["choices"][0]["text"] for e in events[:-2]]
+            assert st == 200 and events[-1] == "[DONE]" and len(texts) >= 3
+            assert "".join(texts) == tok.decode([last + k for k in range(1, 6)])
+            assert json.loads(events[-2])["choices"][0] == {"index": 0, "text": "", "finish_reason": "length"}
+            whole = "".join(texts)
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": "hello", "max_tokens": 5, "stream": True, "stop": whole[2:4]})
+            events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
+            assert "".join(json.loads(e)["choices"][0]["text"] for e in events[:-2]) == whole[:2]
+            assert json.loads(events[-2])["choices"][0]["finish_reason"] == "stop"
+            # text that only looks like the beginning of a stop string is delivered once it turns out not to be one
+            st, _, raw = _http(http.url + "/v1/completions", {"prompt": "hello", "max_tokens": 5, "stream": True, "stop": whole[-1] + "#"})
+            events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
+            assert "".join(json.loads(e)["choices"][0]["text"] for e in events[:-2]) == whole
             # concurrency on the wire becomes batch width in the engine
             with ThreadPoolExecutor(8) as ex:
                 res = list(ex.map(lambda i: _http(http.url + "/v1/completions", {"prompt": "x" * (i + 1), "max_tokens": 2}), range(8)))
@@ -284,9 +319,17 @@ def test_openai_front_end_routes_conversations_over_several_engines():
             for _ in range(6):                                                   # no key: spread over the engines
                 assert _http(http.url + "/v1/completions", {"prompt": "x", "max_tokens": 1})[0] == 200
             assert all(s["served"] >= 2 for s in back.pool.stats().values())
+            # streaming through the pool: pieces come from the engine the key belongs to
+            owner = back.pool.owner("a")
+            before = engines[owner].admitted
+            st, ctype, raw = _http(http.url + "/v1/completions", {"prompt": "hi", "max_tokens": 4, "stream": True, "route_key": "a"})
+            events = [e[len("data: "):] for e in raw.decode().strip().split("\n\n")]
+            assert st == 200 and ctype == "text/event-stream" and len(events) >= 4 and events[-1] == "[DONE]"
+            assert len("".join(json.loads(e)["choices"][0]["text"] for e in events[:-2])) == 4 and engines[owner].admitted == before + 1
             for e in engines.values():
                 e.close()
             assert _http(http.url + "/v1/completions", {"prompt": "x"})[0] == 503
+            assert _http(http.url + "/v1/completions", {"prompt": "x", "stream": True})[0] == 503     # also when a stream was asked for
     finally:
         for e in engines.values():
             e.close()

@@ -630,6 +630,17 @@ class PagedEngine(BaseSampler):
                         pool.publish(s, prompt_ids(slot_item[s]) + [int(t) for t in toks_h[j, :max(c - 1, 0)]])
                         slot_req[s] = slot_item[s] = None
                         pool.release(s)
+                if getattr(source, "streaming", False):          # someone listens: report what the running requests have so far
+                    run = [s for s in range(B) if slot_req[s] is not None and not done_h[s]]
+                    if run:
+                        rx = torch.as_tensor(run, **i64)
+                        p_cnt = st["out_pos"][rx].cpu().numpy()
+                        p_tok = st["out_tokens"][rx, :max_steps].cpu().numpy()
+                        p_lp = st["out_lp"][rx, :max_steps].cpu().numpy()
+                        for j, s in enumerate(run):
+                            c = int(p_cnt[j])
+                            if c > 0:
+                                source.progress(slot_req[s], p_tok[j, :c], p_lp[j, :c])
                 free = [s for s in range(B) if slot_req[s] is None]
                 new = source.take(len(free)) if free else []
                 if not new:
@@ -804,6 +815,7 @@ class EngineServer:
         self._cv = threading.Condition()
         self._queue = collections.deque()
         self._futures: dict = {}
+        self._callbacks: dict = {}              # request id -> [callback, tokens already reported]
         self._next_id = 0
         self._paused = False
         self._closed = False
@@ -814,8 +826,15 @@ class EngineServer:
         self._thread.start()
 
     # ------------------------------------------------------------------ client side
-    def submit(self, prompt_token_ids, max_tokens: Optional[int] = None):
-        """Queue one request; the returned future resolves to (tokens int64 [n], logprobs float32 [n])."""
+    streams = True          # `submit(..., on_tokens=...)` reports tokens while a request is still running
+
+    def submit(self, prompt_token_ids, max_tokens: Optional[int] = None, on_tokens=None):
+        """Queue one request; the returned future resolves to (tokens int64 [n], logprobs float32 [n]).
+
+        `on_tokens(new_tokens, new_logprobs)` is called from the engine's loop thread with the tokens produced since
+        the previous call, at every check point of the decode loop and once more when the request finishes (so the
+        pieces concatenate to the final result). It must return quickly. A request that the engine pre-empts for lack
+        of pages starts again from its prompt; pieces already reported are not reported again."""
         from concurrent.futures import Future
         ids = list(prompt_token_ids)[-self.P:]
         if not ids:
@@ -827,12 +846,33 @@ class EngineServer:
             rid = self._next_id
             self._next_id += 1
             self._futures[rid] = fut
+            if on_tokens is not None:
+                self._callbacks[rid] = [on_tokens, 0]
             self._queue.append((rid, ids, min(int(max_tokens or self.max_new_tokens), self.max_new_tokens)))
             self._cv.notify_all()
         return fut
 
-    def generate(self, prompt_token_ids, max_tokens: Optional[int] = None, timeout: Optional[float] = None):
-        return self.submit(prompt_token_ids, max_tokens).result(timeout)
+    def generate(self, prompt_token_ids, max_tokens: Optional[int] = None, timeout: Optional[float] = None, on_tokens=None):
+        return self.submit(prompt_token_ids, max_tokens, on_tokens=on_tokens).result(timeout)
+
+    @property
+    def streaming(self) -> bool:
+        """True while a request with a token callback is queued or running (the loop then reports progress)."""
+        return bool(self._callbacks)
+
+    def progress(self, rid, toks, lps) -> None:
+        """Called by the engine loop with everything request `rid` has produced so far."""
+        with self._cv:
+            cb = self._callbacks.get(rid)
+            if cb is None or len(toks) <= cb[1]:
+                return
+            fn, sent = cb
+            cb[1] = len(toks)
+        try:
+            fn(np.array(toks[sent:], np.int64), np.array(lps[sent:], np.float32))
+        except Exception:                          # a client's callback must not take the engine loop down
+            import logging
+            logging.getLogger(__name__).exception("token callback of request %s failed", rid)
 
     def pause(self, timeout: Optional[float] = None) -> bool:
         """Stop admitting requests and wait until the running ones are delivered. True when drained in time."""
@@ -882,8 +922,10 @@ class EngineServer:
             return bool(self._queue) and not self._paused
 
     def deliver(self, rid, toks, lps):
+        self.progress(rid, toks, lps)              # whatever has not been reported yet
         with self._cv:
             fut = self._futures.pop(rid)
+            self._callbacks.pop(rid, None)
         fut.set_result((np.array(toks, np.int64), np.array(lps, np.float32)))
 
     def idle(self):
@@ -923,6 +965,7 @@ class EngineServer:
                 self._closed = True
                 futs = list(self._futures.values())
                 self._futures.clear()
+                self._callbacks.clear()
             for f in futs:
                 f.set_exception(e)
             self._drained.set()

@@ -16,8 +16,10 @@ Every HTTP request becomes one `submit()` on the engine server and joins the run
 one handler thread per connection waits for its own future, so concurrency on the wire turns directly into batch
 width on the GPU. Sampling parameters are fixed per engine server (they shape its captured decode step): a request
 whose `temperature` / `top_p` differ from the server's is answered with the server's values, reported back under
-`"sampling"`. `stream: true` answers as server-sent events; the engine delivers a request when it finishes, so the
-stream carries one content chunk, a finish chunk and `[DONE]`.
+`"sampling"`. `stream: true` answers as server-sent events. A request for one completion (`n` = 1, one prompt) on a
+back end that reports tokens while it generates (`EngineServer`, `PooledBackend`) is streamed as it is produced: a
+chunk per check point of the engine's decode loop, the text cut at a stop string if one is given, then a finish chunk
+and `[DONE]`. Other streamed requests carry one content chunk per choice, a finish chunk and `[DONE]`.
 
 The back end is anything with `generate(prompt_token_ids, max_tokens) -> (tokens, logprobs)`, i.e.
 `generate.engine.EngineServer`; chat prompts are rendered by a `ChatTemplateParser`. The server is the standard
@@ -164,6 +166,96 @@ class OpenAIServer:
         h.end_headers()
         h.wfile.write(data)
 
+    def _can_stream_live(self, n_prompts: int, n: int) -> bool:
+        return n_prompts == 1 and n == 1 and bool(getattr(self.backend, "streams", False))
+
+    def _stream_live(self, h, prompt, body: dict, make_chunk, finish_chunk) -> None:
+        """Generate one completion and write it as server-sent events while the engine produces it.
+        `make_chunk(text_piece, first)` / `finish_chunk(reason)` build the event payloads."""
+        import queue as queue_lib
+        ids = self.tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        if not ids:
+            raise _BadRequest("empty prompt")
+        max_tokens = body.get("max_tokens")
+        if max_tokens is not None and (not isinstance(max_tokens, int) or max_tokens < 1):
+            raise _BadRequest("max_tokens must be a positive integer")
+        stop = body.get("stop")
+        stops = [stop] if isinstance(stop, str) else (stop or [])
+        events: "queue_lib.Queue" = queue_lib.Queue()
+        done = threading.Event()
+        result: dict = {}
+
+        def run():
+            try:
+                kw = {"route_key": body.get("route_key")} if getattr(self.backend, "routes", False) else {}
+                result["out"] = self.backend.generate(ids, max_tokens, timeout=self.request_timeout,
+                                                      on_tokens=lambda t, l: events.put([int(x) for x in t]), **kw)
+            except BaseException as e:
+                result["error"] = e
+            finally:
+                done.set()
+                events.put(None)
+        t0 = time.perf_counter()
+        with self._lock:
+            self._m["inflight"] += 1
+        threading.Thread(target=run, daemon=True).start()
+        head = events.get()                                 # the first piece, or the end: errors before any token keep their status code
+        if head is None and "error" in result:
+            with self._lock:
+                self._m["inflight"] -= 1
+            raise result["error"]
+        events.put(head) if head is None else None
+        pending_head = [head] if head is not None else []
+        h.send_response(200)
+        h.send_header("Content-Type", "text/event-stream")
+        h.send_header("Cache-Control", "no-cache")
+        h.send_header("Connection", "close")                # no length: the end of the connection ends the stream
+        h.end_headers()
+
+        def write(payload) -> None:
+            h.wfile.write(b"data: " + (payload if isinstance(payload, bytes) else json.dumps(payload).encode()) + b"\n\n")
+            h.wfile.flush()
+        toks: list = []
+        sent_text, held, stopped, first = "", "", False, True
+        try:
+            while True:
+                piece = pending_head.pop() if pending_head else events.get()
+                if piece is None:
+                    break
+                toks.extend(piece)
+                if stopped:
+                    continue                                # the engine runs on to its limit; nothing more is sent
+                text = self.tokenizer.decode(toks)
+                cut = min((i for i in (text.find(x) for x in stops) if i >= 0), default=-1)
+                if cut >= 0:
+                    text, stopped = text[:cut], True
+                elif text.endswith("\ufffd"):
+                    continue                                # half a multi-byte character: wait for the rest
+                else:                                       # the tail may be the beginning of a stop string: keep it back
+                    hold = max((k for x in stops for k in range(1, len(x)) if text.endswith(x[:k])), default=0)
+                    held, text = text[len(text) - hold:] if hold else "", text[:len(text) - hold]
+                if len(text) > len(sent_text):
+                    write(make_chunk(text[len(sent_text):], first))
+                    sent_text, first = text, False
+            if "error" in result:
+                write({"error": {"message": str(result["error"]), "type": "server_error"}})
+            else:
+                if not stopped and held:                    # what was kept back turned out not to be a stop string
+                    write(make_chunk(held, first))
+                limit = getattr(self.backend, "max_new_tokens", None)
+                asked = min(max_tokens or limit or len(toks), limit or len(toks))
+                write(finish_chunk("stop" if stopped or len(toks) < asked else "length"))
+            write(b"[DONE]")
+        finally:
+            dt = time.perf_counter() - t0
+            with self._lock:
+                self._m["inflight"] -= 1
+                self.requests_served += 1
+                self._m["prompt_tokens"] += len(ids)
+                self._m["completion_tokens"] += len(toks)
+                self._m["lat_sum"] += dt
+                self._m["lat_buckets"][next((i for i, le in enumerate(_LAT_BUCKETS) if dt <= le), len(_LAT_BUCKETS))] += 1
+
     def _models(self) -> dict:
         return {"status": "ok", "model": self.model_name, "object": "list",
                 "data": [{"id": self.model_name, "object": "model"}]}
@@ -260,9 +352,14 @@ class OpenAIServer:
             raise _BadRequest("prompt must be a string, a list of token ids, or a list of either")
         n = self._n(body)
         self._apply_stop({"text": ""}, body)                # validate before generating
-        results = [self._apply_stop(r, body) for r in self._many([p for p in prompts for _ in range(n)], body)]
         rid, now = "cmpl-" + uuid.uuid4().hex, int(time.time())
         base = {"id": rid, "object": "text_completion", "created": now, "model": body.get("model") or self.model_name}
+        if body.get("stream") and self._can_stream_live(len(prompts), n):
+            self._stream_live(h, prompts[0], body,
+                              lambda piece, first: dict(base, choices=[{"index": 0, "text": piece, "finish_reason": None}]),
+                              lambda reason: dict(base, choices=[{"index": 0, "text": "", "finish_reason": reason}]))
+            return
+        results = [self._apply_stop(r, body) for r in self._many([p for p in prompts for _ in range(n)], body)]
         choices = [{"index": i, "text": r["text"], "finish_reason": r["finish_reason"],
                     "logprobs": {"token_logprobs": r["logprobs"], "tokens": r["tokens"]} if r["logprobs"] else None}
                    for i, r in enumerate(results)]
@@ -283,10 +380,17 @@ class OpenAIServer:
         prompt = self.chat_parser.parse(msgs, add_generation_prompt=True, is_first_msg=True)
         n = self._n(body)
         self._apply_stop({"text": ""}, body)
-        results = [self._apply_stop(x, body) for x in self._many([prompt] * n, body)]
-        r = results[0]
         rid, now = "chatcmpl-" + uuid.uuid4().hex, int(time.time())
         model = body.get("model") or self.model_name
+        if body.get("stream") and self._can_stream_live(1, n):
+            base = {"id": rid, "object": "chat.completion.chunk", "created": now, "model": model}
+            self._stream_live(h, prompt, body,
+                              lambda piece, first: dict(base, choices=[{"index": 0, "finish_reason": None, "delta": (
+                                  {"role": "assistant", "content": piece} if first else {"content": piece})}]),
+                              lambda reason: dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": reason}]))
+            return
+        results = [self._apply_stop(x, body) for x in self._many([prompt] * n, body)]
+        r = results[0]
         if body.get("stream"):
             base = {"id": rid, "object": "chat.completion.chunk", "created": now, "model": model}
             self._send_sse(h, [
@@ -309,13 +413,16 @@ class PooledBackend:
     def __init__(self, engines: dict):
         from ..experimental.worker.routing import RoutingPool
         self.engines = dict(engines)
-        self.pool = RoutingPool(self.engines, call=lambda e, r: e.generate(r["ids"], r["max_tokens"], timeout=r["timeout"]))
+        self.pool = RoutingPool(self.engines, call=lambda e, r: e.generate(r["ids"], r["max_tokens"], timeout=r["timeout"],
+                                                                           **({"on_tokens": r["on_tokens"]} if r.get("on_tokens") else {})))
+        self.streams = all(getattr(e, "streams", False) for e in self.engines.values())
         limits = [getattr(e, "max_new_tokens", None) for e in self.engines.values()]
         self.max_new_tokens = min(x for x in limits if x is not None) if any(x is not None for x in limits) else None
 
-    def generate(self, ids, max_tokens=None, timeout=None, route_key=None):
+    def generate(self, ids, max_tokens=None, timeout=None, route_key=None, on_tokens=None):
         try:
-            return self.pool.submit({"ids": ids, "max_tokens": max_tokens, "timeout": timeout, "route_key": route_key})
+            return self.pool.submit({"ids": ids, "max_tokens": max_tokens, "timeout": timeout, "route_key": route_key,
+                                     "on_tokens": on_tokens})
         except Exception as e:
             raise RuntimeError(str(e)) from e
 
