@@ -142,3 +142,18 @@ def test_gsm8k_vtc_example_script_runs_in_tiny_mode():
     spec.loader.exec_module(mod)
     out = mod.main(["--tiny", "--steps", "2"])
     assert out["steps"] == 2 and len(out["reward_mean"]) == 2 and len(out["solve_ratio"]) == 2
+
+
+def test_gsm8k_distributed_example_runs_in_tiny_mode(tmp_path):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    from examples.experimental import gsm8k_distributed
+    out = gsm8k_distributed.main(["--tiny", "--steps", "2", "--store", str(tmp_path / "atif")])
+    assert out["steps"] == 2 and out["policy_version"] == 2
+    from tunix_b200.experimental.trajectory.file_store import FileTrajectoryStore
+    st = FileTrajectoryStore(str(tmp_path / "atif"))
+    metas = st.get_trajectories_metadata()
+    assert len(metas) == 2 * 2 * 4 and all(m.prompt_id.startswith("gsm8k-") for m in metas)      # steps x prompts x generations
+    st.close()
