@@ -169,3 +169,26 @@ def test_grpo_on_a_moe_actor_replays_the_samplers_routing():
     learner.train([{"prompts": ["ab", "cd"]}])
     assert cl.global_steps == 1 and seen and seen[0].dim() == 4 and int(seen[0].max()) < 4
     assert (seen[0] == -1).any()                  # padding slots are left to the model's own router
+
+
+def test_step_timelines_are_written_as_a_trace_per_step(tmp_path):
+    import json
+    from tunix_b200.common.configs import PerfMetricsOptions
+    from tunix_b200.perf.trace import PerfTracer
+    actor = create_model(_cfg(), seed=0)
+    tc = RLTrainingConfig(eval_every_n_steps=1000, max_steps=2, actor_optimizer=optim.AdamW(1e-3), mini_batch_size=4, train_micro_batch_size=2,
+                          perf_metrics_options=PerfMetricsOptions(enable_perf_v2=True, enable_trace_writer=True, log_dir=str(tmp_path)))
+    rc = RolloutConfig(max_tokens_to_generate=6, max_prompt_length=8, temperature=1.0, top_p=1.0, seed=3, kv_cache_size=32, eos_tokens=[63])
+    cl = RLCluster(actor=actor, tokenizer=CharTok(), perf_tracer=PerfTracer(),
+                   cluster_config=ClusterConfig(role_to_mesh={}, training_config=tc, rollout_config=rc))
+    learner = GRPOLearner(cl, [reward_mod7], GRPOConfig(num_generations=2, beta=0.0))
+    learner.train([{"prompts": ["ab", "cd", "ef", "gh"]} for _ in range(2)])
+    learner._trace_exporter.close()
+    assert len(learner._trace_exporter.timelines) >= 1
+    hosts = [tl for tid, tl in learner._trace_exporter.timelines.items() if tid.startswith("host-")]
+    assert len(hosts) == 2 and all(len(tl.committed_steps) == 2 for tl in hosts)   # trainer thread and rollout producer; a step each per global step
+    names = {s.name for tl in hosts for step in tl.committed_steps for s in step.values()}
+    assert {"global_step", "rollout", "actor_train"} <= names
+    ev = json.load(open(learner._trace_exporter.trace_file_path))["traceEvents"]
+    slices = [e for e in ev if e["ph"] == "X"]
+    assert any(e["name"].startswith("rollout") for e in slices) and any("step=1" in e["name"] for e in slices)

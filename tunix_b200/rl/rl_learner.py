@@ -294,6 +294,17 @@ class RLLearner(abc.ABC):
         metrics = fn(perf, step_span)
         self.rl_cluster.buffer_metrics({k: (v, np.mean) for k, v in metrics.items()}, Mode.TRAIN,
                                        step=self.rl_cluster.global_steps - 1)
+        opts = self.tcfg.perf_metrics_options
+        if opts is not None and getattr(opts, "enable_perf_v2", False) and getattr(opts, "enable_trace_writer", False) \
+                and getattr(opts, "log_dir", None):
+            exp = getattr(self, "_trace_exporter", None)
+            if exp is None:
+                from ..perf.experimental.bridge import StepTraceExporter
+                pl = self.rl_cluster.placement
+                from .placement import Role
+                roles = {r.value: list(pl.ranks(r)) for r in (Role.ACTOR, Role.ROLLOUT, Role.REFERENCE)}
+                exp = self._trace_exporter = StepTraceExporter(opts.log_dir, roles, device_id=getattr(pl, "rank", 0))
+            exp.step(perf, step_span, self.rl_cluster.global_steps - 1)
 
     def _open_round(self, batch: dict) -> None:
         """Send the prompts of `batch` to the rollout ranks now; `_generate_and_compute_advantage` picks the result up."""
