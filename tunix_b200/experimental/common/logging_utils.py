@@ -1,21 +1,27 @@
 """Short forms of long id lists for log lines (tunix/experimental/common/logging_utils.py:22-46)."""
 from __future__ import annotations
 
-from typing import Any, Sequence
+from typing import Any, Iterable
+
+_ELLIPSIS = "..."
 
 
-def summarize_list(input_list: Sequence[Any], max_length: int = 4) -> str:
-    """`[a, b, ..., y, z]`: at most `max_length` entries, the head gets the odd one; empty and None entries are left out."""
-    items = [str(x) for x in input_list if x is not None and str(x) != ""]
-    if not items:
-        return "[]"
-    if max_length < 2:
+def _printable(values: Iterable[Any]) -> list:
+    """Entries as text; `None` and empty entries carry no information in a log line and are left out."""
+    texts = (str(v) for v in values if v is not None)
+    return [t for t in texts if t]
+
+
+def summarize_list(input_list: Iterable[Any], max_length: int = 4) -> str:
+    """`[a, b, ..., y, z]`: a list printed whole when it has at most `max_length` printable entries, otherwise its first
+    ceil(max_length / 2) and last floor(max_length / 2) entries around an ellipsis."""
+    shown = _printable(input_list)
+    if shown and max_length < 2:
         raise ValueError(f"max_length must be at least 2, got {max_length}")
-    if len(items) <= max_length:
-        return f"[{', '.join(items)}]"
-    tail = max_length // 2
-    head = max_length - tail
-    return f"[{', '.join(items[:head])}, ..., {', '.join(items[-tail:])}]"
+    if len(shown) > max_length:
+        back = max_length >> 1
+        shown = shown[:max_length - back] + [_ELLIPSIS] + shown[len(shown) - back:]
+    return "[" + ", ".join(shown) + "]"
 
 
 summarize_ids = summarize_list

@@ -26,21 +26,29 @@ def _wandb_key(prefix: str, mode: str, metric_name: str) -> str:
     return "/".join(p for p in (prefix, mode, metric_name) if p)
 
 
-def _wandb_payloads(metrics_data) -> Iterator[Tuple[Optional[int], dict]]:
-    groups: dict = {}
-    for rm in metrics_data.resource_metrics:
-        for sm in rm.scope_metrics:
-            for metric in sm.metrics:
+def _points(metrics_data):
+    """(prefix, mode, instrument name, value) of every data point in an export batch."""
+    for resource in metrics_data.resource_metrics:
+        for scope in resource.scope_metrics:
+            for metric in scope.metrics:
                 for point in getattr(metric.data, "data_points", ()):
                     attrs = point.attributes or {}
-                    key = (str(attrs.get(OTEL_PREFIX_ATTRIBUTE, "")), str(attrs.get(OTEL_MODE_ATTRIBUTE, "")))
-                    g = groups.setdefault(key, {"step": None, "values": {}})
-                    if metric.name == OTEL_STEP_METRIC:
-                        g["step"] = int(point.value)
-                    else:
-                        g["values"][_wandb_key(key[0], key[1], metric.name)] = point.value
-    for g in sorted((g for g in groups.values() if g["values"]), key=lambda g: (g["step"] is None, g["step"] or 0)):
-        yield g["step"], g["values"]
+                    yield str(attrs.get(OTEL_PREFIX_ATTRIBUTE, "")), str(attrs.get(OTEL_MODE_ATTRIBUTE, "")), metric.name, point.value
+
+
+def _wandb_payloads(metrics_data) -> Iterator[Tuple[Optional[int], dict]]:
+    """(step, {chart key: value}) per (prefix, mode) group, in ascending step order; groups without a step gauge come
+    last with step None."""
+    steps: dict = {}
+    values: dict = {}
+    for prefix, mode, name, value in _points(metrics_data):
+        if name == OTEL_STEP_METRIC:
+            steps[(prefix, mode)] = int(value)
+        else:
+            values.setdefault((prefix, mode), {})[_wandb_key(prefix, mode, name)] = value
+    order = sorted(values, key=lambda g: (g not in steps, steps.get(g, 0)))
+    for group in order:
+        yield steps.get(group), values[group]
 
 
 class WandbMetricsExporter(otel_export.MetricExporter):
