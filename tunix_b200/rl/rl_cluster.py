@@ -413,9 +413,19 @@ class RLCluster:
         """Controllers: bring the sampler's weights up to date with the actor's; bump the global step. Ranks in
         `serve()` join the transfer when it crosses ranks."""
         self.generate_finish()
+        # `free_kv_during_sync`: the paged engine gives its KV pool back for the time of the transfer (staging buffers
+        # of the transfer then fit where the pool was) and allocates it again afterwards
+        engine = getattr(self.rollout, "_engine", None)
+        free_kv = engine is not None and bool(getattr(self._rollout_config(), "free_kv_during_sync", False))
         with self._span("weight_sync"):
-            if not self._rollout_shares_weights:
-                self.exchange.sync()
+            if free_kv:
+                engine.delete_cache()
+            try:
+                if not self._rollout_shares_weights:
+                    self.exchange.sync()
+            finally:
+                if free_kv:
+                    engine.reinitialize_cache()
             if self.cluster_config.gc_collect_after_weight_sync:
                 gc.collect()
         self.global_steps += 1

@@ -57,7 +57,8 @@ class VanillaRollout(BaseRollout):
         tok_prompts = kwargs.get("prompt_token_ids")
         call = self._engine if self._engine is not None else self._sampler
         extra = {}
-        if self._engine is None and getattr(rollout_config, "return_routed_experts", False):
+        if self._engine is None and (getattr(rollout_config, "return_routed_experts", False)
+                                     or getattr(rollout_config, "store_routed_experts", False)):
             extra["return_routed_experts"] = True        # dense sampler only: the paged engine does not record routing
         out = call(**extra, input_strings=None if tok_prompts is not None else prompts,
                    prompt_token_ids=tok_prompts,
