@@ -291,10 +291,11 @@ class RLLearner(abc.ABC):
             custom = getattr(opts, "custom_export_fn", None) if opts is not None else None
             fn = custom or PerfMetricsExport.from_cluster_config(self.rl_cluster.cluster_config, self.rl_cluster.placement)
             self._perf_export_fn = fn
-        metrics = fn(perf, step_span)
-        self.rl_cluster.buffer_metrics({k: (v, np.mean) for k, v in metrics.items()}, Mode.TRAIN,
-                                       step=self.rl_cluster.global_steps - 1)
         opts = self.tcfg.perf_metrics_options
+        if opts is None or getattr(opts, "enable_perf_v1", True):        # the per-step `perf/...` scalars
+            metrics = fn(perf, step_span)
+            self.rl_cluster.buffer_metrics({k: (v, np.mean) for k, v in metrics.items()}, Mode.TRAIN,
+                                           step=self.rl_cluster.global_steps - 1)
         if opts is not None and getattr(opts, "enable_perf_v2", False) and getattr(opts, "enable_trace_writer", False) \
                 and getattr(opts, "log_dir", None):
             exp = getattr(self, "_trace_exporter", None)
