@@ -528,3 +528,50 @@ def test_group_order_decouples_training_order_from_rollout_timing(order):
     asyncio.run(eng.close())
     with pytest.raises(ValueError, match="group_order"):
         _program(_prompts(1), 1, group_order="random")
+
+
+def test_episode_worker_behind_grpc_serves_frozenlake_episodes():
+    """An episode worker in a server on the loopback interface: the request (task, agent / environment names, lineage)
+    and the response (conversation tokens, masks, environment reward, budget facts) cross the wire."""
+    pytest.importorskip("grpc")
+    from tests.test_sampler_cpu import CharTok
+    from tunix_b200.experimental.rl.agentic import registry as registries
+    from tunix_b200.experimental.rollout import sampler as sampler_lib
+    from tunix_b200.experimental.worker.agentic_rollout_worker import AgenticRolloutWorker
+    from tunix_b200.experimental.worker.remote_execution import RemoteWorker, serve_worker
+    from tunix_b200.rl.agentic.environments.frozenlake_environment import FrozenLakeAgent, FrozenLakeEnv, shortest_path
+    from tunix_b200.rl.agentic.parser.chat_template_parser import get_parser
+    for reg, cls in ((registries.AGENT_REGISTRY, FrozenLakeAgent), (registries.ENV_REGISTRY, FrozenLakeEnv)):
+        if "frozenlake" not in reg:
+            reg.register("frozenlake")(cls)
+    tok = CharTok()
+    task = {"seed": 3, "size": 4, "p": 0.8, "max_steps": 8}
+    path = shortest_path(FrozenLakeEnv(task).grid)
+
+    class Walker:
+        def __init__(self):
+            self.turn = 0
+
+        async def sample(self, requests):
+            out = []
+            for r in requests:
+                reply = f"```{path[min(self.turn, len(path) - 1)].capitalize()}```"
+                self.turn += 1
+                ids = tok.encode(reply)
+                out.append(sampler_lib.SamplingResponse(r.request_id, ids, [-0.2] * len(ids), reply, "stop", 0))
+            return out
+    local = AgenticRolloutWorker("episodes-0", Walker(), tok, chat_parser=get_parser("qwen"), eos_ids=[2])
+    with serve_worker(local, "127.0.0.1:0", token="t") as srv:
+        remote = RemoteWorker(srv.address, token="t")
+        remote.start()
+        eng = DistributedRLEngine([remote], {Role.ACTOR: _Trainer({})})
+        item = {"prompt_id": "lake", "task": task, "agent": "frozenlake", "env": "frozenlake", "max_turns": 8, "max_response_length": 4096}
+        (resp,) = asyncio.run(eng.generate([item], GenerationArgs(max_tokens=32, temperature=1.0)))
+        md = resp.metadata
+        assert md["is_valid"] and md["status"] == "SUCCEEDED" and md["trajectory_reward"] == 1.0 and md["num_turns"] == len(path)
+        masks = np.asarray(md["conversation_masks"])
+        assert len(masks) == len(resp.tokens) == len(resp.logprobs) and 0 < masks.sum() < len(masks)
+        assert md["raw_length"] == len(resp.tokens) and md["clipped"] is False and len(md["prompt_token_ids"]) > 0
+        assert md["lineage"].events[0].component == "engine.dispatch"
+        asyncio.run(eng.close())
+        remote.stop()
