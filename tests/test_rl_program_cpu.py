@@ -575,3 +575,26 @@ def test_episode_worker_behind_grpc_serves_frozenlake_episodes():
         assert md["lineage"].events[0].component == "engine.dispatch"
         asyncio.run(eng.close())
         remote.stop()
+
+
+def test_factory_built_episode_worker_plays_and_takes_weights():
+    from tunix_b200.experimental.worker.factories import export_state, make_agentic_rollout_worker
+    w = make_agentic_rollout_worker("episodes-f", device="cpu", cache_size=1024, max_new_tokens=8)
+    w.start()
+    try:
+        eng = DistributedRLEngine([w], {Role.ACTOR: _Trainer({})})
+        item = {"prompt_id": "lake", "task": {"seed": 1, "size": 4, "p": 0.8, "max_steps": 2}, "max_turns": 2, "max_response_length": 24}
+        out = asyncio.run(eng.generate([item, dict(item, prompt_id="lake2")], GenerationArgs(max_tokens=8, temperature=1.0)))
+        assert len(out) == 2 and all(r.metadata["status"] in ("SUCCEEDED", "MAX_STEPS_REACHED", "MAX_CONTEXT_LIMIT_REACHED") for r in out)
+        assert all(0 < sum(r.metadata["conversation_masks"]) <= 24 + 8 for r in out)
+        before = torch.cat([p.detach().reshape(-1).clone() for p in w.model.parameters()])
+        state = export_state(w.model)
+        name = next(iter(state))
+        kind, arr = state[name]
+        state[name] = (kind, arr * 0)
+        w.sync_weights(5, state)
+        after = torch.cat([p.detach().reshape(-1) for p in w.model.parameters()])
+        assert w.policy_version == 5 and not torch.equal(before, after)
+        asyncio.run(eng.close())
+    finally:
+        w.stop()

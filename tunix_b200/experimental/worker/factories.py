@@ -91,3 +91,48 @@ def make_rollout_worker(worker_id: str, role: str = "rollout", model: str = "toy
     w.model = net
     w.releases_bulk_payloads = True                     # install_state copies into the parameters and keeps nothing
     return w
+
+
+def make_agentic_rollout_worker(worker_id: str, role: str = "rollout", model: str = "toy", seed: int = 0, device: Optional[str] = None,
+                                cache_size: int = 2048, engine: str = "auto", max_new_tokens: int = 256, max_prompt_length: int = 1536,
+                                temperature: float = 1.0, agent: str = "frozenlake", env: str = "frozenlake", chat_parser: str = "qwen",
+                                discover: str = "", batch_window_s: float = 0.002):
+    """An episode worker for launched processes: a model behind the asynchronous sampler protocol, agents and
+    environments looked up by registry key. `discover`: comma-separated import paths or directories whose decorated
+    agent / environment classes are registered before the first request (`registry.auto_discover_modules`); the
+    FrozenLake pair is registered under "frozenlake"."""
+    from ...common.configs import CacheConfig
+    from ...generate.sampler import Sampler
+    from ...models.transformer import create_model
+    from ...rl.agentic.environments.frozenlake_environment import FrozenLakeAgent, FrozenLakeEnv
+    from ...rl.agentic.parser.chat_template_parser import get_parser
+    from ..rl.agentic import registry
+    from ..rollout.sampler import EngineSamplerAdapter
+    from .agentic_rollout_worker import AgenticRolloutWorker
+    for reg, cls in ((registry.AGENT_REGISTRY, FrozenLakeAgent), (registry.ENV_REGISTRY, FrozenLakeEnv)):
+        if "frozenlake" not in reg:
+            reg.register("frozenlake")(cls)
+    if discover:
+        registry.auto_discover_modules(*[p for p in discover.split(",") if p])
+    dev = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    if model == "toy":
+        cfg = toy_config(dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32).replace(max_position=max(cache_size, 256))
+    else:
+        from ...models.config import get_config
+        cfg = get_config(model)
+    net = create_model(cfg, device=dev, seed=seed)
+    tok = ByteTokenizer()
+    cc = CacheConfig(cache_size, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim)
+    if engine == "paged" or (engine == "auto" and dev.type == "cuda"):
+        from ...generate.engine import EngineServer, PagedEngine
+        eng = EngineServer(PagedEngine(net, tok, cc), max_new_tokens=max_new_tokens, max_prompt_length=max_prompt_length,
+                           temperature=temperature, seed=seed, eos_tokens=[tok.eos_id()])
+        sampler = EngineSamplerAdapter(eng, tokenizer=tok, eos_tokens=[tok.eos_id()])
+    else:
+        sampler = EngineSamplerAdapter(Sampler(net, tok, cc), tokenizer=tok, eos_tokens=[tok.eos_id()], batch_window_s=batch_window_s)
+    w = AgenticRolloutWorker(worker_id, sampler, tok, chat_parser=get_parser(chat_parser), eos_ids=[tok.eos_id()], default_agent=agent,
+                             default_env=env, apply_weights=lambda version, payload: install_state(net, payload))
+    w.role = role
+    w.model = net
+    w.releases_bulk_payloads = True
+    return w
