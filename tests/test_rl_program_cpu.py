@@ -598,3 +598,24 @@ def test_factory_built_episode_worker_plays_and_takes_weights():
         asyncio.run(eng.close())
     finally:
         w.stop()
+
+
+def test_program_validation_reports_everything_at_once():
+    from tunix_b200.experimental.orchestrator.startup_validation import StartupValidationError, validate_program
+    eng = DistributedRLEngine([], {Role.CRITIC: _Trainer({})})
+    prog = StandardRLProgram(GRPOAdapter(reward_fn=doubles.token_sum_reward), None, 1, num_generations=4, batch_size=2,
+                             batch_config=BatchConfig(rows_per_microbatch=2, max_packed_len=16), generation_args=GenerationArgs(max_tokens=64),
+                             max_staleness=1, sync_weights=False, reference_kl=True)
+    with pytest.raises(StartupValidationError) as ei:
+        validate_program(prog, eng)
+    text = str(ei.value)
+    for part in ("no rollout worker", "no trainer worker for the actor", "no worker serves the reference role", "cannot fit a packed row",
+                 "sync_weights is off", "no dataset"):
+        assert part in text, part
+    assert len(ei.value.errors) == 6
+    good = DistributedRLEngine([_EchoRollout("r0")], {Role.ACTOR: _Trainer({})})
+    hist = _program(_prompts(2), 1, sync_weights=False, checkpoint_every=0).run(good, validate=True)
+    assert len(hist) == 1
+    with pytest.raises(StartupValidationError):
+        _program(None, 1).run(good, validate=True)
+    asyncio.run(good.close()); asyncio.run(eng.close())

@@ -460,10 +460,13 @@ class StandardRLProgram(RLProgram):
                     await pending
 
     # ------------------------------------------------------------------ entry points
-    async def run_async(self, engine, dataset: Optional[Iterable[Any]] = None, **kwargs) -> list:
+    async def run_async(self, engine, dataset: Optional[Iterable[Any]] = None, validate: bool = False, **kwargs) -> list:
         self.engine = engine
         if dataset is not None:
             self.dataset = dataset
+        if validate:                                    # everything that is wrong with the set-up, in one error
+            from .startup_validation import validate_program
+            validate_program(self, engine)
         self._dispatch_done = asyncio.Event()
         self._raw_q: asyncio.Queue = asyncio.Queue()
         self._scored_q: asyncio.Queue = asyncio.Queue()
@@ -509,7 +512,7 @@ class StandardRLProgram(RLProgram):
         except RuntimeError:
             loop = None
         if loop is not None and loop.is_running():
-            self._bg_task = loop.create_task(self.run_async(engine, dataset, **kwargs))
+            self._bg_task = loop.create_task(self.run_async(engine, dataset, **kwargs))     # kwargs: validate=...
             self._bg_task.add_done_callback(lambda t: t.cancelled() or t.exception())
             return self._bg_task
         return asyncio.run(self.run_async(engine, dataset, **kwargs))

@@ -76,3 +76,38 @@ def validate_startup(registry, alg_config, training_config, validators: Sequence
         errors += list(v.validate(registry, alg_config, training_config))
     if errors:
         raise StartupValidationError(errors)
+
+
+def validate_program(program, engine) -> None:
+    """The same all-at-once check for a `StandardRLProgram` on a `DistributedRLEngine`: the roles the program will call
+    are served, the batch geometry can be assembled, and a window that lets rollouts run ahead comes with weight sync.
+    `StandardRLProgram.run_async(..., validate=True)` calls it before the first dispatch."""
+    errors: list = []
+    rollout = getattr(engine, "_rollout", None)
+    if rollout is not None and not rollout:
+        errors.append("the engine has no rollout worker")
+    trainers = getattr(engine, "_trainers", None)
+    if trainers is not None and "actor" not in trainers:
+        errors.append("the engine has no trainer worker for the actor role")
+    if getattr(program, "reference_kl", False):
+        serving = set(getattr(engine, "_inference", {}) or {}) | set(trainers or {})
+        if "reference" not in serving:
+            errors.append("reference_kl is on, but no worker serves the reference role")
+    _positive_int(getattr(program, "num_generations", None), "num_generations", errors)
+    _positive_int(getattr(program, "full_batch_size", None), "batch_size", errors)
+    cfg = getattr(getattr(program, "assembler", None), "cfg", None)
+    if cfg is not None:
+        _positive_int(cfg.rows_per_microbatch, "rows_per_microbatch", errors)
+        limit = getattr(program, "max_response_length", None) or getattr(getattr(program, "generation_args", None), "max_tokens", None)
+        packed = type(program.assembler).__name__.startswith("SequencePacked")
+        if packed and limit and limit + 1 > cfg.max_packed_len:
+            errors.append(f"a response of up to {limit} tokens cannot fit a packed row of {cfg.max_packed_len} tokens")
+        if not packed and limit and limit > cfg.max_response_length:
+            errors.append(f"responses of up to {limit} tokens are cut to the assembler's max_response_length {cfg.max_response_length}")
+    if getattr(program, "max_staleness", 0) > 0 and not getattr(program, "sync_weights", True):
+        errors.append("max_staleness > 0 lets rollouts run ahead of the trainer, but sync_weights is off: the workers would never "
+                      "see new weights")
+    if getattr(program, "dataset", None) is None:
+        errors.append("the program has no dataset")
+    if errors:
+        raise StartupValidationError(errors)
