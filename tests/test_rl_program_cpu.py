@@ -619,3 +619,32 @@ def test_program_validation_reports_everything_at_once():
     with pytest.raises(StartupValidationError):
         _program(None, 1).run(good, validate=True)
     asyncio.run(good.close()); asyncio.run(eng.close())
+
+
+def test_engine_rotation_follows_the_health_monitor():
+    from tunix_b200.experimental.common.datatypes import HealthReport, WorkerState
+    from tunix_b200.experimental.orchestrator.health_monitor import HealthMonitor
+    now = [100.0]
+    mon = HealthMonitor(heartbeat_timeout_s=5.0, clock=lambda: now[0])
+    a, b = _EchoRollout("a"), _EchoRollout("b")
+    eng = DistributedRLEngine([a, b], {Role.ACTOR: _Trainer({})})
+    for w in ("a", "b"):
+        mon.observe(HealthReport(w, WorkerState.READY, timestamp=now[0]))
+    stop = eng.follow_health(mon, period_s=0.02)
+    try:
+        now[0] += 10.0                                         # both silent ...
+        mon.observe(HealthReport("a", WorkerState.READY, timestamp=now[0]))        # ... then only "a" reports again
+        deadline = time.monotonic() + 3
+        while eng.rollout_pool.live() != ["a"] and time.monotonic() < deadline:
+            time.sleep(0.02)
+        assert eng.rollout_pool.live() == ["a"]
+        out = asyncio.run(eng.generate(_prompts(4), GenerationArgs(max_tokens=2)))
+        assert len(out) == 4 and b.seen == []                  # nothing was sent to the silent worker
+        mon.observe(HealthReport("b", WorkerState.READY, timestamp=now[0]))
+        deadline = time.monotonic() + 3
+        while eng.rollout_pool.live() != ["a", "b"] and time.monotonic() < deadline:
+            time.sleep(0.02)
+        assert eng.rollout_pool.live() == ["a", "b"]
+    finally:
+        stop.set()
+        asyncio.run(eng.close())

@@ -89,6 +89,12 @@ class DistributedRLEngine:
     def rollout_pool(self) -> RoutingPool:
         return self._pool
 
+    def follow_health(self, monitor, period_s: float = 1.0):
+        """Keep the rollout rotation in step with a `HealthMonitor`: workers it reports silent, failed or stuck are taken
+        out before a request has to fail on them, and put back when their reports are healthy again. Returns the event
+        that stops the follower thread."""
+        return self._pool.follow(monitor, period_s)
+
     async def _call(self, fn: Callable, *args, **kwargs):
         return await asyncio.get_running_loop().run_in_executor(self._threads, lambda: fn(*args, **kwargs))
 
