@@ -2,6 +2,7 @@
 (test model: tunix/experimental/orchestrator/{distributed_rl_engine,rl_program}_test.py). CPU, tiny model; worker
 failures are scripted on the host."""
 import asyncio
+import os
 import time
 
 import numpy as np
@@ -648,3 +649,16 @@ def test_engine_rotation_follows_the_health_monitor():
     finally:
         stop.set()
         asyncio.run(eng.close())
+
+
+def test_program_writes_a_json_line_per_consumed_rollout(tmp_path):
+    import json
+    eng = DistributedRLEngine([_EchoRollout("r0")], {Role.ACTOR: _Trainer({})})
+    prog = _program(_prompts(2), 1, trajectory_log_dir=str(tmp_path / "traj"), sync_weights=False, checkpoint_every=0)
+    hist = prog.run(eng)
+    prog.close()
+    files = [f for f in os.listdir(tmp_path / "traj") if f.endswith(".jsonl")]
+    rows = [json.loads(line) for f in files for line in open(tmp_path / "traj" / f)]
+    assert len(rows) == hist[0]["num_rollouts"] == 8 and {r["prompt_id"] for r in rows} == {"p0", "p1"}
+    assert all(len(r["tokens"]) == 4 and r["step"] == 0 and r["request_id"].startswith("req_p") for r in rows)
+    asyncio.run(eng.close())

@@ -124,7 +124,7 @@ class StandardRLProgram(RLProgram):
                  generation_args: Optional[GenerationArgs] = None, max_response_length: Optional[int] = None,
                  max_staleness: int = 0, sync_weights: bool = True, checkpoint_every: int = 1, metrics_logger=None,
                  trajectory_store=None, metrics_prefix: str = "", poll_timeout_s: float = 0.2, reference_kl: bool = False,
-                 group_order: str = "completion",
+                 group_order: str = "completion", trajectory_log_dir: Optional[str] = None,
                  on_step_begin: Optional[Callable[[int], None]] = None, on_step_end: Optional[Callable[[int, Any], None]] = None):
         super().__init__()
         if max_staleness < 0:
@@ -142,6 +142,11 @@ class StandardRLProgram(RLProgram):
         self.max_staleness, self.sync_weights, self.checkpoint_every = max_staleness, sync_weights, checkpoint_every
         self.metrics_logger, self.metrics_prefix = metrics_logger, metrics_prefix
         self._trajectory_store = trajectory_store          # used, not owned: whoever built it closes it
+        # one JSON line per consumed rollout (prompt id, group index, reward, versions, tokens), written by a thread
+        self.trajectory_logger = None
+        if trajectory_log_dir:
+            from ...utils.trajectory_logger import AsyncTrajectoryLogger
+            self.trajectory_logger = AsyncTrajectoryLogger(trajectory_log_dir)
         self.poll_timeout_s = poll_timeout_s
         # "completion": the trainer takes groups as they finish (best utilisation). "prompt_arrival": groups reach the
         # trainer in the order their prompts were dispatched, whatever order they finished in, so that a run does not
@@ -167,6 +172,8 @@ class StandardRLProgram(RLProgram):
         return self._trajectory_store
 
     def close(self) -> None:
+        if self.trajectory_logger is not None:
+            self.trajectory_logger.stop()
         if self.metrics_logger is not None and hasattr(self.metrics_logger, "close"):
             self.metrics_logger.close()
 
@@ -316,6 +323,13 @@ class StandardRLProgram(RLProgram):
         self.metrics_logger.log(prefix, leaf, value, Mode.TRAIN, step)
 
     def _store_trajectories(self, groups, step: int) -> None:
+        if self.trajectory_logger is not None:
+            for g in groups:
+                for p, r in zip(g.payloads, g.responses):
+                    self.trajectory_logger.log({"step": step, "prompt_id": g.prompt_id, "request_id": r.request_id,
+                                                "group_index": (r.metadata or {}).get("group_index"), "reward": float(p.reward or 0.0),
+                                                "rollout_policy_version": int(r.policy_version), "consumed_policy_version": self.policy_version,
+                                                "tokens": np.asarray(r.tokens, np.int64), "finish_reason": r.finish_reason}, block=False)
         if self._trajectory_store is None:
             return
         if hasattr(self._trajectory_store, "add_step"):          # a step-level ATIF store
