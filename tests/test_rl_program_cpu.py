@@ -662,3 +662,22 @@ def test_program_writes_a_json_line_per_consumed_rollout(tmp_path):
     assert len(rows) == hist[0]["num_rollouts"] == 8 and {r["prompt_id"] for r in rows} == {"p0", "p1"}
     assert all(len(r["tokens"]) == 4 and r["step"] == 0 and r["request_id"].startswith("req_p") for r in rows)
     asyncio.run(eng.close())
+
+
+def test_eval_mode_scores_without_training():
+    class Logger:
+        def __init__(self):
+            self.rows = []
+
+        def log(self, prefix, name, value, mode, step):
+            self.rows.append((prefix, name, str(mode), step))
+    tr, r = _Trainer({"latest": {"step": 3, "global_step": 3}}), _EchoRollout("r0")
+    eng = DistributedRLEngine([r], {Role.ACTOR: tr})
+    lg = Logger()
+    hist = _program(_prompts(4), None, mode="eval", metrics_logger=lg).run(eng)
+    assert [h["step"] for h in hist] == [0, 1] and all(h["num_rollouts"] == 8 and h["num_microbatches"] == 0 and h["loss"] is None for h in hist)
+    assert tr.ops == [] and r.synced == [] and "global_step" in tr.disk["latest"]          # no restore, no training, no sync, no save
+    assert {m for _, _, m, _ in lg.rows} == {"eval"} and ("rewards", "mean", "eval", 1) in lg.rows
+    asyncio.run(eng.close())
+    with pytest.raises(ValueError, match="mode must be"):
+        _program(_prompts(1), 1, mode="test")

@@ -124,7 +124,7 @@ class StandardRLProgram(RLProgram):
                  generation_args: Optional[GenerationArgs] = None, max_response_length: Optional[int] = None,
                  max_staleness: int = 0, sync_weights: bool = True, checkpoint_every: int = 1, metrics_logger=None,
                  trajectory_store=None, metrics_prefix: str = "", poll_timeout_s: float = 0.2, reference_kl: bool = False,
-                 group_order: str = "completion", trajectory_log_dir: Optional[str] = None,
+                 group_order: str = "completion", trajectory_log_dir: Optional[str] = None, mode: str = "train",
                  on_step_begin: Optional[Callable[[int], None]] = None, on_step_end: Optional[Callable[[int, Any], None]] = None):
         super().__init__()
         if max_staleness < 0:
@@ -155,6 +155,11 @@ class StandardRLProgram(RLProgram):
             raise ValueError(f"group_order must be 'completion' or 'prompt_arrival', got {group_order!r}")
         self.group_order = group_order
         self._order_next, self._order_pending = 0, {}
+        # "eval": rollouts are generated, scored and reported step by step (rewards, lengths, staleness), but nothing is
+        # assembled, trained, synchronised or checkpointed, and no checkpoint is restored
+        if mode not in ("train", "eval"):
+            raise ValueError(f"mode must be 'train' or 'eval', got {mode!r}")
+        self.mode = mode
         # reference log-probs for a KL term: asked of the REFERENCE role per assembled micro-batch (dense rows: one
         # forward pass over what the trainer will see), stored in the batch as `ref_per_token_logps`
         self.reference_kl = bool(reference_kl or getattr(algo, "requires_reference_kl", False))
@@ -320,7 +325,7 @@ class StandardRLProgram(RLProgram):
         if self.metrics_prefix:
             prefix = f"{self.metrics_prefix}/{prefix}"
         from ...sft.metrics_logger import Mode
-        self.metrics_logger.log(prefix, leaf, value, Mode.TRAIN, step)
+        self.metrics_logger.log(prefix, leaf, value, Mode.TRAIN if self.mode == "train" else Mode.EVAL, step)
 
     def _store_trajectories(self, groups, step: int) -> None:
         if self.trajectory_logger is not None:
@@ -403,6 +408,8 @@ class StandardRLProgram(RLProgram):
                     if not groups and self.on_step_begin:
                         self.on_step_begin(step)
                     groups.append(g)
+                    if self.mode == "eval":
+                        continue
                     tp = time.perf_counter()
                     batches = await asyncio.to_thread(lambda: list(self.assembler.feed(g.payloads)))
                     packing_s += time.perf_counter() - tp
@@ -410,27 +417,28 @@ class StandardRLProgram(RLProgram):
                 if not groups:
                     log.info("dataset exhausted at step %d", step)
                     break
-                tp = time.perf_counter()
-                batches = await asyncio.to_thread(lambda: list(self.assembler.flush()))
-                packing_s += time.perf_counter() - tp
-                await take(batches)
-                if held is None:
-                    raise RuntimeError(f"step {step}: {len(groups)} group(s) produced no micro-batch")
-                await submit(held, True)
-                await settle()
+                if self.mode == "train":
+                    tp = time.perf_counter()
+                    batches = await asyncio.to_thread(lambda: list(self.assembler.flush()))
+                    packing_s += time.perf_counter() - tp
+                    await take(batches)
+                    if held is None:
+                        raise RuntimeError(f"step {step}: {len(groups)} group(s) produced no micro-batch")
+                    await submit(held, True)
+                    await settle()
                 final = results[-1] if results else None
                 payloads = [p for g in groups for p in g.payloads]
                 rewards = np.asarray([p.reward or 0.0 for p in payloads], np.float64)
                 adv = np.asarray([float(np.mean(p.example["advantages"])) for p in payloads
                                   if isinstance(p.example, Mapping) and p.example.get("advantages") is not None
                                   and np.size(p.example["advantages"])], np.float64)
-                if self.checkpoint_every and (step + 1) % self.checkpoint_every == 0:
+                if self.mode == "train" and self.checkpoint_every and (step + 1) % self.checkpoint_every == 0:
                     opt_step = final.get("train_step") if isinstance(final, Mapping) else None
                     await self.engine.save_checkpoint(role=Role.ACTOR, metadata={
                         "step": int(opt_step) if opt_step is not None else step + 1, "global_step": step + 1,
                         "policy_version": self.policy_version + (1 if self.sync_weights else 0), "num_rollouts": len(payloads),
                         "num_microbatches": len(stats), **self.dispatch_window.checkpoint_metadata(groups)})
-                if self.sync_weights:
+                if self.mode == "train" and self.sync_weights:
                     v = await self.engine.sync_weights(role=Role.ACTOR)
                     self.policy_version = v if v is not None else self.policy_version + 1
                 gen_metrics = _generation_metrics([g.responses for g in groups])
@@ -487,10 +495,12 @@ class StandardRLProgram(RLProgram):
         self._in_flight = self._dispatched = 0
         self._order_next, self._order_pending = 0, {}
         # before any stage starts: the train loop's bound and the dataset prefix to skip both come from the restored step
-        await self._resume_from_checkpoint()
+        if self.mode == "train":
+            await self._resume_from_checkpoint()
         self._base_step = self._step
-        engine.configure_worker(role=Role.ACTOR, algo=self.algo, assembler=self.assembler)
-        if self.sync_weights and self._step == 0:           # a resumed run has just pushed the restored weights
+        if self.mode == "train":
+            engine.configure_worker(role=Role.ACTOR, algo=self.algo, assembler=self.assembler)
+        if self.mode == "train" and self.sync_weights and self._step == 0:           # a resumed run has just pushed the restored weights
             await engine.prepare_rollout_policy(role=Role.ACTOR, sync_weights=True, policy_version=self.policy_version)
         train = asyncio.create_task(self.train_stage())
         tasks = [asyncio.create_task(self.rollout_dispatch_stage()), asyncio.create_task(self.polling_stage()),
