@@ -132,3 +132,40 @@ def test_atif_projection_round_trips_agent_steps(step_id, message, tokens, versi
     back = T.TunixAgentStep.from_atif_step(T.Step.from_json(atif.to_json()))
     assert back.step_id == step_id and back.message == message and back.policy_version == version and back.mc_return == mc_return
     assert np.array_equal(back.assistant_tokens, np.asarray(tokens, np.int64)) and (back.extra or {}) == (extra or {})
+
+
+@_settings
+@given(st.integers(0, 3), st.integers(1, 4), st.lists(st.sampled_from(["dispatch", "consume", "filter"]), min_size=1, max_size=60))
+def test_dispatch_window_never_runs_further_ahead_than_allowed(max_staleness, full, events):
+    """Whatever the order of dispatches, consumed batches and filtered groups: a prompt of batch b is only let through
+    while b <= next_batch + max_staleness, and a parked dispatcher is woken by the event that makes room."""
+    import asyncio
+    from tunix_b200.experimental.common.dispatch_window import DispatchWindow
+
+    async def run():
+        step = [0]
+        w = DispatchWindow(max_staleness, lambda: step[0], full_batch_size=full, out_of_order_resume=True)
+        dispatched = 0
+        waiting = None
+        for ev in events:
+            if ev == "dispatch" and waiting is None:
+                batch = dispatched // full
+                waiting = asyncio.ensure_future(w.wait_for(batch))
+                await asyncio.sleep(0)
+            elif ev == "consume":
+                step[0] += 1
+                w.release()
+            elif ev == "filter":
+                w.on_group_filtered([{"prompt_id": f"f{dispatched}"}])
+            await asyncio.sleep(0)
+            await asyncio.sleep(0)
+            if waiting is not None:
+                batch = dispatched // full
+                allowed = batch <= w.next_batch + max_staleness
+                assert waiting.done() == allowed                  # through exactly when the window allows it
+                if waiting.done():
+                    dispatched += 1
+                    waiting = None
+        if waiting is not None:
+            waiting.cancel()
+    asyncio.run(run())
