@@ -162,3 +162,40 @@ def test_cancelled_episode_is_marked_and_the_cancellation_propagates():
             await task
         return eng.agent.trajectory.status
     assert asyncio.run(run()) == TrajectoryStatus.CANCELLED
+
+
+def test_data_queue_bounds_times_out_and_close_releases_blocked_threads():
+    import queue, threading, time
+    from tunix_b200.rl.queue.data_queue import SimpleDataQueue
+    q = SimpleDataQueue(maxsize=2)
+    q.put(1); q.put(2)
+    assert q.qsize() == 2
+    state = {}
+
+    def producer():
+        q.put(3)                                   # full: parks until a get or a close
+        state["put_returned"] = True
+    t = threading.Thread(target=producer); t.start()
+    time.sleep(0.05)
+    assert "put_returned" not in state
+    assert q.get() == 1                            # FIFO, and makes room
+    t.join(2); assert state.get("put_returned")
+    assert [q.get(), q.get()] == [2, 3]
+    t0 = time.monotonic()
+    with pytest.raises(queue.Empty):
+        q.get(timeout=0.05)
+    assert 0.04 <= time.monotonic() - t0 < 1.0
+    with pytest.raises(queue.Empty):
+        q.get(block=False)
+
+    def consumer():
+        try:
+            q.get()
+        except queue.Empty:
+            state["woken"] = True
+    c = threading.Thread(target=consumer); c.start()
+    time.sleep(0.05)
+    q.close()
+    c.join(2); assert state.get("woken") and q.closed
+    q.put(9)                                       # dropped after close
+    assert q.qsize() == 0
